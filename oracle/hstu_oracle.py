@@ -1,0 +1,439 @@
+"""CPU restatement of the reference's PyTorch implementation of the HSTU hot path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this module; it is
+the checker used by ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline /
+reference legs of ``bench.py``.
+
+Parity status: PINNED.  Every function here is checked against outputs of the
+unmodified reference (generative_recommenders/ops/pytorch/*, run in the build
+container through ``oracle/reference_shims.py``) stored as fixtures under
+``tests/golden/`` by ``tests/golden/make_golden.py``.  The reference itself ships no
+golden vectors for this path, so those generated fixtures are the pin.
+
+The restatement differs from the reference in one deliberate way: instead of padding
+the jagged batch to ``[B, H, N, N]`` it walks the sequences one by one (the padded
+rows/columns are multiplied by a zero mask in the reference and dropped by
+``dense_to_jagged``, so they never reach the output).  This keeps memory at
+``H * L_i^2`` and lets the oracle run the larger configurations.
+"""
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+# --------------------------------------------------------------------------------------
+# mask
+# --------------------------------------------------------------------------------------
+def valid_attn_mask(
+    L: int,
+    num_targets: int = 0,
+    has_targets: bool = False,
+    max_attn_len: int = 0,
+    contextual_seq_len: int = 0,
+    min_full_attn_seq_len: int = 0,
+    device: Optional[torch.device] = None,
+) -> torch.Tensor:
+    """Boolean ``[L, L]`` mask of one sequence of length ``L``.
+
+    Follows generative_recommenders/ops/pytorch/pt_hstu_attention.py:33-84
+    (``_get_valid_attn_mask`` with ``causal=True``), restricted to the ``[L, L]``
+    corner that survives ``dense_to_jagged`` (pt_hstu_attention.py:183-187).
+    """
+    ids = torch.arange(L, device=device, dtype=torch.int64)
+    max_id = L
+    if contextual_seq_len > 0:  # :45-48
+        ids = torch.clamp(ids - contextual_seq_len + 1, min=0)
+        max_id = max_id - contextual_seq_len + 1
+    if has_targets:  # :49-54
+        max_id = max_id - num_targets
+        ids = torch.clamp(ids, max=max_id)
+    row = ids.view(L, 1)
+    col = ids.view(1, L)
+    dist = row - col  # :61
+    valid = torch.eye(L, dtype=torch.bool, device=device)  # :62
+    valid = valid | (dist > 0)  # :65
+    if max_attn_len > 0:  # :66-79
+        if min_full_attn_seq_len > 0:
+            valid = valid & ((dist <= max_attn_len) | (row >= max_id - min_full_attn_seq_len))
+        else:
+            valid = valid & (dist <= max_attn_len)
+    if contextual_seq_len > 0:  # :80-83
+        valid = valid | ((row == 0) & (col < max_id))
+    return valid
+
+
+def valid_attn_mask_positions(
+    L: int,
+    num_targets: int = 0,
+    max_attn_len: int = 0,
+    contextual_seq_len: int = 0,
+    min_full_attn_seq_len: int = 0,
+) -> torch.Tensor:
+    """The same mask written on raw positions instead of clamped ids.
+
+    This is the form the CUDA tile scheduler reasons with (interval of visible
+    history columns per row + contextual prefix + self).  It is only defined on the
+    regular domain ``L - num_targets >= contextual_seq_len + 1``; tests check it
+    equals :func:`valid_attn_mask` there.
+    """
+    t, c, W, Fm = num_targets, contextual_seq_len, max_attn_len, min_full_attn_seq_len
+    u = L - t
+    assert u >= c + 1
+    i = torch.arange(L).view(L, 1)
+    j = torch.arange(L).view(1, L)
+    is_ctx_row = i < c
+    is_tgt_row = i >= u
+    eff = torch.minimum(i, torch.tensor(u))  # row position clamped to first target
+    if W == 0:
+        full = torch.ones_like(i, dtype=torch.bool)
+    else:
+        full = (Fm > 0) & ((i >= u - Fm) | is_tgt_row)
+    hi = torch.where(is_tgt_row, torch.tensor(u), i + 1)
+    lo = torch.where(full, torch.tensor(0), torch.clamp(eff - W, min=c))
+    ctx_ok = full | (eff - c + 1 <= W)
+    valid = (j >= lo) & (j < hi) & (j >= c)
+    valid = valid | ((j < c) & (j < hi) & ctx_ok)
+    valid = valid | (is_ctx_row & (j < u))
+    valid = valid | (i == j)
+    return valid
+
+
+# --------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------
+def hstu_mha(
+    max_seq_len: int,
+    alpha: float,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    seq_offsets: torch.Tensor,
+    causal: bool = True,
+    dropout_pr: float = 0.0,
+    training: bool = True,
+    num_targets: Optional[torch.Tensor] = None,
+    attn_scale: Optional[torch.Tensor] = None,
+    max_attn_len: int = 0,
+    contextual_seq_len: int = 0,
+    min_full_attn_seq_len: int = 0,
+    rel_bias: Optional[torch.Tensor] = None,
+    compute_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """Jagged HSTU attention, ``out[i] = sum_j mask(i,j) * SiLU(alpha q_i.k_j) * s * v_j``.
+
+    Follows ``pytorch_hstu_mha`` (pt_hstu_attention.py:130-187): scores ``* alpha``
+    (:151), ``silu(.) / max_seq_len`` (:167) or ``silu(.) * attn_scale`` (:152-165),
+    multiplied by the mask (:179), times V (:182).  ``rel_bias`` (``[N, N]`` or
+    ``[B, N, N]``) is the extension used by the research layer, added to the scores
+    before SiLU and broadcast over heads as in
+    generative_recommenders/research/modeling/sequential/hstu.py:203-211; note that
+    layer uses no ``alpha`` factor (pass ``alpha=1``).
+
+    ``compute_dtype`` upcasts q/k/v first (use ``torch.float32`` to get the fp32
+    answer for bf16 inputs); the result is returned in that dtype.
+    """
+    assert causal, "only causal attention exists in the reference (hstu_attention.py:128)"
+    assert dropout_pr == 0.0, "attention dropout is outside the restated path"
+    if compute_dtype is not None:
+        q, k, v = q.to(compute_dtype), k.to(compute_dtype), v.to(compute_dtype)
+    L_total, H, _ = q.shape
+    offs = seq_offsets.to(torch.int64).cpu().tolist()
+    B = len(offs) - 1
+    nt = None if num_targets is None else num_targets.to(torch.int64).cpu().tolist()
+    outs: List[torch.Tensor] = []
+    for b in range(B):
+        s, e = offs[b], offs[b + 1]
+        L = min(e - s, max_seq_len)  # jagged_to_padded_dense truncates at N
+        qb = q[s : s + L].transpose(0, 1)  # [H, L, A]
+        kb = k[s : s + L].transpose(0, 1)
+        vb = v[s : s + L].transpose(0, 1)
+        qk = torch.einsum("hxa,hya->hxy", qb, kb) * alpha
+        if rel_bias is not None:
+            rb = rel_bias if rel_bias.dim() == 2 else rel_bias[b]
+            qk = qk + rb[:L, :L].to(qk.dtype).unsqueeze(0)
+        if attn_scale is not None:
+            if attn_scale.ndim > 0:
+                sc = attn_scale[s : s + L].to(qk.dtype).view(1, L, 1)
+            else:
+                sc = attn_scale.to(qk.dtype)
+            p = F.silu(qk) * sc
+        else:
+            p = F.silu(qk) / max_seq_len
+        mask = valid_attn_mask(
+            L,
+            num_targets=0 if nt is None else nt[b],
+            has_targets=nt is not None,
+            max_attn_len=max_attn_len,
+            contextual_seq_len=contextual_seq_len,
+            min_full_attn_seq_len=min_full_attn_seq_len,
+            device=q.device,
+        )
+        p = p * mask.unsqueeze(0)
+        ob = torch.einsum("hxy,hyv->hxv", p, vb).transpose(0, 1)  # [L, H, V]
+        if L < e - s:  # rows beyond max_seq_len come back as zeros from dense_to_jagged
+            ob = torch.cat([ob, ob.new_zeros(e - s - L, H, ob.shape[2])], dim=0)
+        outs.append(ob)
+    if not outs:
+        return q.new_zeros(0, H, v.shape[2])
+    return torch.cat(outs, dim=0)
+
+
+def delta_hstu_mha(
+    max_seq_len: int,
+    alpha: float,
+    delta_q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    seq_offsets: torch.Tensor,
+    num_targets: Optional[torch.Tensor] = None,
+    max_attn_len: int = 0,
+    contextual_seq_len: int = 0,
+) -> torch.Tensor:
+    """Attention of the last ``delta`` rows of each sequence against the full K/V.
+
+    Follows ``pytorch_cached_hstu_mha`` (pt_hstu_attention.py:191-251): ``delta_q`` is
+    ``[B * delta, H, A]``, the queries are the last ``delta`` positions of each
+    sequence and use the corresponding rows of the full mask (:231-246).
+    """
+    Ld, H, _ = delta_q.shape
+    offs = seq_offsets.to(torch.int64).cpu().tolist()
+    B = len(offs) - 1
+    delta = Ld // B
+    nt = None if num_targets is None else num_targets.to(torch.int64).cpu().tolist()
+    outs = []
+    for b in range(B):
+        s, e = offs[b], offs[b + 1]
+        L = e - s
+        qb = delta_q[b * delta : (b + 1) * delta].transpose(0, 1)
+        kb = k[s:e].transpose(0, 1)
+        vb = v[s:e].transpose(0, 1)
+        qk = torch.einsum("hxa,hya->hxy", qb, kb) * alpha
+        p = F.silu(qk) / max_seq_len
+        mask = valid_attn_mask(
+            L,
+            num_targets=0 if nt is None else nt[b],
+            has_targets=nt is not None,
+            max_attn_len=max_attn_len,
+            contextual_seq_len=contextual_seq_len,
+            device=delta_q.device,
+        )[L - delta : L]
+        p = p * mask.unsqueeze(0)
+        outs.append(torch.einsum("hxy,hyv->hxv", p, vb).transpose(0, 1))
+    return torch.cat(outs, dim=0)
+
+
+# --------------------------------------------------------------------------------------
+# LayerNorm + linear stages
+# --------------------------------------------------------------------------------------
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+    """fp32 LayerNorm cast back to the input dtype
+    (generative_recommenders/ops/pytorch/pt_layer_norm.py:24-38)."""
+    return F.layer_norm(
+        x.to(torch.float32), (x.shape[-1],), weight.to(torch.float32), bias.to(torch.float32), eps
+    ).to(x.dtype)
+
+
+def hstu_compute_uqvk(
+    x: torch.Tensor,
+    norm_weight: torch.Tensor,
+    norm_bias: torch.Tensor,
+    norm_eps: float,
+    num_heads: int,
+    attn_dim: int,
+    hidden_dim: int,
+    uvqk_weight: torch.Tensor,
+    uvqk_bias: torch.Tensor,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """LN -> addmm -> split [u|v|q|k] -> SiLU(u)
+    (generative_recommenders/ops/hstu_compute.py:54-104; return order u,q,k,v :104)."""
+    normed = layer_norm(x, norm_weight, norm_bias, norm_eps)
+    uvqk = torch.addmm(uvqk_bias, normed, uvqk_weight)
+    u, v, q, k = torch.split(
+        uvqk,
+        [hidden_dim * num_heads, hidden_dim * num_heads, attn_dim * num_heads, attn_dim * num_heads],
+        dim=1,
+    )
+    u = F.silu(u)
+    return (
+        u,
+        q.view(-1, num_heads, attn_dim),
+        k.view(-1, num_heads, attn_dim),
+        v.view(-1, num_heads, hidden_dim),
+    )
+
+
+def norm_mul_dropout(
+    x: torch.Tensor,
+    u: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor,
+    eps: float,
+    concat_u: bool = False,
+    concat_x: bool = False,
+    mul_u_activation_type: str = "none",
+    group_norm: bool = False,
+    num_heads: int = 1,
+    linear_dim: int = -1,
+) -> torch.Tensor:
+    """``y = act(u) * LN(x)`` with the optional ``[u, x, y]`` concat, dropout off
+    (generative_recommenders/ops/pytorch/pt_hstu_linear.py:23-82; the middle block of
+    the concat is the raw, un-normalised ``x`` :71-72)."""
+    dtype = x.dtype
+    x = x.to(torch.float32)
+    u = u.to(torch.float32)
+    if group_norm:
+        y = u * F.group_norm(
+            x.view(-1, num_heads, linear_dim),
+            num_groups=num_heads,
+            weight=weight.to(torch.float32),
+            bias=bias.to(torch.float32),
+            eps=eps,
+        ).view(-1, num_heads * linear_dim)
+        if concat_u and concat_x:
+            y = torch.cat([u, x, y], dim=1)
+    else:
+        mul_u = u
+        if mul_u_activation_type == "sigmoid":
+            mul_u = torch.sigmoid(u)
+        elif mul_u_activation_type == "silu":
+            mul_u = F.silu(u)
+        y = mul_u * F.layer_norm(
+            x, (x.shape[-1],), weight.to(torch.float32), bias.to(torch.float32), eps
+        )
+        if concat_u:
+            y = torch.cat([u, x, y], dim=1) if concat_x else torch.cat([u, y], dim=1)
+        elif concat_x:
+            y = torch.cat([x, y], dim=1)
+    return y.to(dtype)
+
+
+def hstu_compute_output(
+    attn: torch.Tensor,
+    u: torch.Tensor,
+    x: torch.Tensor,
+    norm_weight: torch.Tensor,
+    norm_bias: torch.Tensor,
+    norm_eps: float,
+    output_weight: torch.Tensor,
+    num_heads: int = 1,
+    linear_dim: int = -1,
+    concat_u: bool = False,
+    concat_x: bool = False,
+    mul_u_activation_type: str = "none",
+    group_norm: bool = False,
+) -> torch.Tensor:
+    """``x + norm_mul(attn, u) @ W_out`` (pt_hstu_linear.py:85-120)."""
+    y = norm_mul_dropout(
+        attn, u, norm_weight, norm_bias, norm_eps, concat_u, concat_x,
+        mul_u_activation_type, group_norm, num_heads, linear_dim,
+    )
+    return torch.addmm(x, y, output_weight.to(x.dtype)).to(x.dtype)
+
+
+def stu_layer(
+    x: torch.Tensor,
+    seq_offsets: torch.Tensor,
+    max_seq_len: int,
+    num_targets: Optional[torch.Tensor],
+    params: dict,
+    num_heads: int,
+    attn_dim: int,
+    hidden_dim: int,
+    attn_alpha: Optional[float] = None,
+    max_attn_len: int = 0,
+    contextual_seq_len: int = 0,
+    rel_bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One HSTU layer as ``STULayer.forward`` composes it
+    (generative_recommenders/modules/stu.py:293-356): uqvk stage -> attention ->
+    output stage with ``concat_u=concat_x=True``, ``mul_u_activation_type="none"``,
+    eps 1e-6 (:344-352), ``attn_alpha = 1/sqrt(attention_dim)`` by default (:199).
+    Dropout is off (eval mode)."""
+    alpha = attn_alpha if attn_alpha is not None else 1.0 / (attn_dim ** 0.5)
+    dt = x.dtype
+    u, q, k, v = hstu_compute_uqvk(
+        x, params["input_norm_weight"].to(dt), params["input_norm_bias"].to(dt), 1e-6,
+        num_heads, attn_dim, hidden_dim, params["uvqk_weight"].to(dt), params["uvqk_beta"].to(dt),
+    )
+    attn = hstu_mha(
+        max_seq_len, alpha, q, k, v, seq_offsets, num_targets=num_targets,
+        max_attn_len=max_attn_len, contextual_seq_len=contextual_seq_len, rel_bias=rel_bias,
+    ).reshape(-1, hidden_dim * num_heads)
+    return hstu_compute_output(
+        attn, u, x, params["output_norm_weight"].to(dt), params["output_norm_bias"].to(dt), 1e-6,
+        params["output_weight"].to(dt), num_heads, hidden_dim, concat_u=True, concat_x=True,
+    )
+
+
+# --------------------------------------------------------------------------------------
+# relative position bias (research layer)
+# --------------------------------------------------------------------------------------
+def bucketized_position_bias(table: torch.Tensor, N: int) -> torch.Tensor:
+    """``[N, N]`` bias ``table[clamp(floor(ln(max(|i-j|,1)) / 0.301), 0, nb)]``.
+
+    The bucket function is the one the research model passes to its relative bias
+    (generative_recommenders/research/modeling/sequential/hstu.py:610-613), applied to
+    the position distance instead of a timestamp difference (time bias off); the
+    bias is added to the scores before SiLU and shared by all heads (:203-211).
+    """
+    nb = table.numel() - 1
+    i = torch.arange(N).view(N, 1)
+    j = torch.arange(N).view(1, N)
+    d = (i - j).abs().clamp(min=1).to(torch.float32)
+    bucket = torch.clamp((torch.log(d) / 0.301).long(), min=0, max=nb)
+    return table.to(torch.float32)[bucket]
+
+
+# --------------------------------------------------------------------------------------
+# FP8 block quantisation (no reference arithmetic exists; this states the format)
+# --------------------------------------------------------------------------------------
+def quantize_e4m3_block(x: torch.Tensor, seq_offsets: torch.Tensor, block: int = 128):
+    """Per-(sequence-local ``block``-token block, head) absmax/448 scales.
+
+    Blocks are counted from each sequence's first token so that a block never spans
+    two sequences.  Returns ``(x_q [L,H,D] float8_e4m3fn, scales [n_blocks_total, H]
+    fp32, block_offsets [B+1] int64)`` where sequence ``b`` owns scale rows
+    ``block_offsets[b] .. block_offsets[b+1]``.
+    """
+    offs = seq_offsets.to(torch.int64).cpu().tolist()
+    B = len(offs) - 1
+    xq = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    scales = []
+    boffs = [0]
+    for b in range(B):
+        s, e = offs[b], offs[b + 1]
+        nb = (e - s + block - 1) // block
+        boffs.append(boffs[-1] + nb)
+        for t in range(nb):
+            r0, r1 = s + t * block, min(s + (t + 1) * block, e)
+            blk = x[r0:r1].to(torch.float32)
+            amax = blk.abs().amax(dim=(0, 2))  # [H]
+            sc = torch.clamp(amax, min=1e-12) / 448.0
+            xq[r0:r1] = (blk / sc.view(1, -1, 1)).to(torch.float8_e4m3fn)
+            scales.append(sc)
+    H = x.shape[1]
+    sc_t = torch.stack(scales) if scales else x.new_zeros(0, H, dtype=torch.float32)
+    return xq, sc_t, torch.tensor(boffs, dtype=torch.int64)
+
+
+def dequantize_e4m3_block(xq, scales, block_offsets, seq_offsets, block: int = 128) -> torch.Tensor:
+    offs = seq_offsets.to(torch.int64).cpu().tolist()
+    boffs = block_offsets.to(torch.int64).cpu().tolist()
+    out = xq.to(torch.float32)
+    for b in range(len(offs) - 1):
+        s, e = offs[b], offs[b + 1]
+        for t in range(boffs[b + 1] - boffs[b]):
+            r0, r1 = s + t * block, min(s + (t + 1) * block, e)
+            out[r0:r1] *= scales[boffs[b] + t].view(1, -1, 1)
+    return out
+
+
+def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
+    """``||a-b|| / ||b||`` in fp64 (0 when both are empty or zero)."""
+    a = a.detach().to(torch.float64).cpu()
+    b = b.detach().to(torch.float64).cpu()
+    den = b.norm().item()
+    num = (a - b).norm().item()
+    return num / den if den > 0 else num

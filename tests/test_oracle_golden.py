@@ -1,0 +1,126 @@
+"""The CPU restatement (oracle/hstu_oracle.py) against outputs of the unmodified reference
+stored under tests/golden/ (see tests/golden/make_golden.py)."""
+
+import itertools
+
+import pytest
+import torch
+
+from oracle import hstu_oracle as O
+
+
+def test_masks_match_reference(golden):
+    cases = golden("masks.pt")
+    assert len(cases) > 300
+    for c in cases:
+        m = O.valid_attn_mask(c["L"], num_targets=c["t"] or 0, has_targets=c["t"] is not None,
+                              max_attn_len=c["W"], contextual_seq_len=c["c"], min_full_attn_seq_len=c["F"])
+        assert torch.equal(m.to(torch.uint8), c["mask"]), c
+
+
+def test_position_mask_equals_id_mask():
+    # the tile scheduler's position-space form == the reference's id form on the regular domain
+    n = 0
+    for L, t, c, W, Fm in itertools.product(range(1, 20), [0, 1, 3, 7], [0, 1, 4], [0, 1, 3, 8], [0, 2, 5]):
+        if L - t < c + 1 or (W == 0 and Fm > 0):
+            continue
+        a = O.valid_attn_mask(L, t, True, W, c, Fm)
+        b = O.valid_attn_mask_positions(L, t, W, c, Fm)
+        assert torch.equal(a, b), (L, t, c, W, Fm)
+        n += 1
+    assert n > 1000
+
+
+def _attn(fx):
+    p = fx["params"]
+    q = fx["q"].clone().requires_grad_(True)
+    k = fx["k"].clone().requires_grad_(True)
+    v = fx["v"].clone().requires_grad_(True)
+    out = O.hstu_mha(p["N"], p["alpha"], q, k, v, fx["seq_offsets"], num_targets=fx["num_targets"],
+                     max_attn_len=p["W"], contextual_seq_len=p["ctx"], min_full_attn_seq_len=p["F"])
+    return q, k, v, out
+
+
+def test_attention_matches_reference(golden):
+    fxs = golden("attention.pt")
+    for name, fx in fxs.items():
+        q, k, v, out = _attn(fx)
+        torch.testing.assert_close(out, fx["out"], rtol=1e-5, atol=1e-6, msg=name)
+        if "dq" in fx:
+            out.backward(fx["dout"])
+            torch.testing.assert_close(q.grad, fx["dq"], rtol=1e-5, atol=1e-6, msg=name)
+            torch.testing.assert_close(k.grad, fx["dk"], rtol=1e-5, atol=1e-6, msg=name)
+            torch.testing.assert_close(v.grad, fx["dv"], rtol=1e-5, atol=1e-6, msg=name)
+
+
+def test_delta_attention_matches_reference(golden):
+    fx = golden("delta_attention.pt")
+    out = O.delta_hstu_mha(fx["N"], fx["alpha"], fx["delta_q"], fx["k"], fx["v"], fx["seq_offsets"],
+                           num_targets=fx["num_targets"], contextual_seq_len=fx["ctx"])
+    torch.testing.assert_close(out, fx["out"], rtol=1e-5, atol=1e-6)
+
+
+def test_stages_match_reference(golden):
+    fx = golden("stages.pt")
+    ln = fx["layer_norm"]
+    torch.testing.assert_close(O.layer_norm(ln["x"], ln["w"], ln["b"], ln["eps"]), ln["y"])
+    uq = fx["uqvk"]
+    leaves = [uq[n].clone().requires_grad_(True) for n in ("x", "nw", "nb", "W", "bias")]
+    u, q, k, v = O.hstu_compute_uqvk(leaves[0], leaves[1], leaves[2], uq["eps"], uq["H"], uq["A"], uq["V"],
+                                    leaves[3], leaves[4])
+    for a, b in zip((u, q, k, v), (uq["u"], uq["q"], uq["k"], uq["v"])):
+        torch.testing.assert_close(a, b)
+    torch.autograd.backward([u, q, k, v], [uq["du"], uq["dq"], uq["dk"], uq["dv"]])
+    for a, b in zip(leaves, uq["grads"]):
+        torch.testing.assert_close(a.grad, b, rtol=1e-4, atol=1e-5)
+    assert len(fx["compute_output"]) >= 18
+    for c in fx["compute_output"]:
+        leaves = [c[n].clone().requires_grad_(True) for n in ("attn", "u", "x", "nw", "nb", "Wo")]
+        o = O.hstu_compute_output(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], c["eps"], leaves[5],
+                                  c["H"], c["V"], c["concat_u"], c["concat_x"], c["act"], c["group_norm"])
+        torch.testing.assert_close(o, c["out"], rtol=1e-5, atol=1e-5)
+        o.backward(c["dout"])
+        for a, b in zip(leaves, c["grads"]):
+            torch.testing.assert_close(a.grad, b, rtol=1e-4, atol=1e-5)
+
+
+def test_stu_layer_matches_reference(golden):
+    for c in golden("stu_layer.pt"):
+        x = c["x"].clone().requires_grad_(True)
+        h = x
+        for layer in range(2):
+            pre = "_stu_layers.%d._" % layer
+            params = {n: c["state"][pre + n] for n in ("input_norm_weight", "input_norm_bias", "uvqk_weight",
+                                                        "uvqk_beta", "output_norm_weight", "output_norm_bias",
+                                                        "output_weight")}
+            h = O.stu_layer(h, c["seq_offsets"], c["N"], c["num_targets"] if c["target_aware"] else None,
+                            params, c["H"], c["A"], c["V"], max_attn_len=c["W"], contextual_seq_len=c["ctx"])
+        torch.testing.assert_close(h, c["y"], rtol=1e-4, atol=1e-5)
+        h.backward(c["dy"])
+        torch.testing.assert_close(x.grad, c["dx"], rtol=1e-4, atol=1e-5)
+
+
+def test_position_bias_matches_reference(golden):
+    fx = golden("rel_bias.pt")
+    N = fx["N"]
+    # the research module evaluates bucket(ts[i+1] - ts[j]); with ts = 7 * position this is
+    # bucket(7 * (i + 1 - j)) except in the last row, which repeats the last timestamp
+    ts = fx["timestamps"][0]
+    ext = torch.cat([ts, ts[N - 1:N]])
+    d = (ext[1:].view(N, 1) - ext[:-1].view(1, N)).abs().clamp(min=1).float()
+    bucket = torch.clamp((torch.log(d) / 0.301).long(), 0, 128)
+    torch.testing.assert_close(fx["ts_w"][bucket], fx["rab"])
+    # and the oracle's position-distance form uses the same bucket function
+    b = O.bucketized_position_bias(fx["ts_w"], N)
+    i, j = 9, 2
+    assert b[i, j] == fx["ts_w"][int(torch.log(torch.tensor(7.0)) / 0.301)]
+
+
+def test_fp8_block_quant_roundtrip():
+    g = torch.Generator().manual_seed(0)
+    off = torch.tensor([0, 5, 5, 300, 431])
+    x = torch.randn(431, 2, 16, generator=g)
+    xq, sc, boffs = O.quantize_e4m3_block(x, off)
+    assert boffs.tolist() == [0, 1, 1, 4, 6] and sc.shape == (6, 2)
+    xd = O.dequantize_e4m3_block(xq, sc, boffs, off)
+    assert O.rel_l2(xd, x) < 0.04
