@@ -1,0 +1,26 @@
+"""B200-native HSTU jagged attention: the reference's operator API over hand-written sm_100a
+kernels in libb200_hstu.so (C ABI in include/b200_hstu.h)."""
+
+from . import _cabi
+from .common import HammerKernel
+from .hstu_attention import hstu_mha, set_attention_impl
+from .hstu_compute import (
+    hstu_compute_output,
+    hstu_compute_uqvk,
+    hstu_norm_mul_dropout,
+    hstu_preprocess_and_attention,
+)
+from .layer_norm import layer_norm
+from .mm import addmm
+
+__all__ = [
+    "HammerKernel",
+    "hstu_mha",
+    "hstu_compute_uqvk",
+    "hstu_compute_output",
+    "hstu_norm_mul_dropout",
+    "hstu_preprocess_and_attention",
+    "layer_norm",
+    "addmm",
+    "set_attention_impl",
+]

@@ -1,0 +1,35 @@
+// Chooses between the tensor-core and the CUDA-core attention kernels and sizes their scratch.
+#include "common.cuh"
+
+namespace b200hstu {
+
+bool attn_tc_layout_ok(const b200_hstu_attn_args &a, bool bwd, const char **why);
+int64_t attn_tc_fwd_workspace_bytes(const b200_hstu_attn_args &a);
+
+bool attn_tc_applicable(const b200_hstu_attn_args &a, bool bwd, const char **why) {
+  if (bwd) {
+    *why = "tensor-core backward is not built yet";
+    return false;
+  }
+  return attn_tc_layout_ok(a, bwd, why);
+}
+
+int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, bool bwd) {
+  if (bwd) return 0;
+  return attn_tc_fwd_workspace_bytes(a);
+}
+
+int attn_tc_bwd(const b200_hstu_attn_args &, cudaStream_t) {
+  return fail(B200_HSTU_EUNSUPPORTED, "tensor-core backward is not built yet");
+}
+
+int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &, cudaStream_t) {
+  return fail(B200_HSTU_EUNSUPPORTED, "fp8 forward is not built yet");
+}
+
+int quantize_e4m3_block(const void *, int, int64_t, int64_t, void *, float *, const int32_t *, const int32_t *, int,
+                        int, int, int64_t, int, cudaStream_t) {
+  return fail(B200_HSTU_EUNSUPPORTED, "fp8 quantiser is not built yet");
+}
+
+}  // namespace b200hstu

@@ -1,0 +1,147 @@
+// Shared device/host helpers for the HSTU kernels: element-type traits, the HSTU mask on
+// clamped position ids, per-sequence geometry, and error plumbing for the C ABI.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/b200_hstu.h"
+
+namespace b200hstu {
+
+// ---------------------------------------------------------------------------------------
+// error plumbing (host)
+// ---------------------------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);
+int check_cuda(cudaError_t e, const char *what);
+extern std::atomic<long long> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+#define B200_CHECK_LAUNCH(what)                                   \
+  do {                                                            \
+    int _st = ::b200hstu::check_cuda(cudaGetLastError(), what);   \
+    if (_st != 0) return _st;                                     \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------
+// element conversion
+// ---------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x * sigmoidf_(x); }
+// d/dx [x * sigmoid(x)] = s * (1 + x * (1 - s))
+__device__ __forceinline__ float dsiluf_(float x) {
+  float s = sigmoidf_(x);
+  return s * (1.f + x * (1.f - s));
+}
+
+// ---------------------------------------------------------------------------------------
+// The HSTU mask of one sequence, on clamped position ids.
+//
+// id(p) = min(max(p - c + 1, 0), max_id)   (c = contextual_seq_len; the max() only if c > 0)
+// max_id = L - max(c - 1, 0) - num_targets
+// valid(i, j) = (i == j) or (d > 0 and (W == 0 or d <= W or (F > 0 and id_i >= max_id - F)))
+//               or (c > 0 and id_i == 0 and id_j < max_id),   d = id_i - id_j
+// which is the reference's construction
+// (generative_recommenders/ops/pytorch/pt_hstu_attention.py:44-83) evaluated for one (row, col).
+// ---------------------------------------------------------------------------------------
+struct SeqMask {
+  int L;       // rows/cols of this sequence that take part (already truncated at max_seq_len)
+  int max_id;
+  int c;       // contextual_seq_len
+  int W;       // max_attn_len (0 = unlimited)
+  int F;       // min_full_attn_seq_len
+  __host__ __device__ __forceinline__ int id(int p) const {
+    int v = p;
+    if (c > 0) {
+      v = p - c + 1;
+      v = v < 0 ? 0 : v;
+    }
+    return v < max_id ? v : max_id;
+  }
+  __host__ __device__ __forceinline__ bool valid_ids(int i, int j, int id_i, int id_j) const {
+    int d = id_i - id_j;
+    bool v = d > 0;
+    if (W > 0) v = v && (d <= W || (F > 0 && id_i >= max_id - F));
+    v = v || (i == j);
+    if (c > 0) v = v || (id_i == 0 && id_j < max_id);
+    return v;
+  }
+  __host__ __device__ __forceinline__ bool valid(int i, int j) const { return valid_ids(i, j, id(i), id(j)); }
+};
+
+__host__ __device__ __forceinline__ SeqMask make_seq_mask(int len, int max_seq_len, int num_targets, int c, int W,
+                                                          int F) {
+  SeqMask m;
+  m.L = len < max_seq_len ? len : max_seq_len;
+  m.c = c;
+  m.W = W;
+  m.F = F;
+  // the reference derives max_id from the untruncated length (seq_offsets difference)
+  m.max_id = len - (c > 0 ? c - 1 : 0) - num_targets;
+  return m;
+}
+
+// ---------------------------------------------------------------------------------------
+// kv-tile range a query tile has to visit (tile edge `T` rows/cols), used for block skipping.
+// Rows [m0, m0+T) of a sequence; returns a half-open range of kv positions [lo, hi) that
+// contains every valid column of every row of the tile, plus (for tiles made only of target
+// rows) the tile's own diagonal block, which lies outside [lo, hi).  Conservative (a superset)
+// everywhere and exact on tile granularity for the regular domain
+// (L - targets >= contextual + 1).
+// ---------------------------------------------------------------------------------------
+struct KvRange {
+  int lo, hi;      // main range of kv positions
+  int diag_lo;     // >= 0: an extra block [diag_lo, diag_lo + T) outside the main range
+};
+
+__host__ __device__ __forceinline__ KvRange kv_range_for_q_tile(const SeqMask &m, int len, int num_targets, int m0,
+                                                                int T) {
+  KvRange r;
+  const int L = m.L;
+  int m1 = m0 + T < L ? m0 + T : L;
+  int u = len - num_targets;  // first target position
+  r.diag_lo = -1;
+  bool regular = (u >= m.c + 1) && (num_targets >= 0) && (len <= L);
+  if (!regular) {  // degenerate sequence (or truncated): visit everything, the element mask decides
+    r.lo = 0;
+    r.hi = L;
+    return r;
+  }
+  if (m0 < m.c) {  // contextual rows see all of [0, u); later rows of the tile see up to themselves
+    r.lo = 0;
+    r.hi = u > m1 ? u : m1;
+    if (r.hi > L) r.hi = L;
+    return r;
+  }
+  int first = m0 < u ? m0 : u;  // smallest effective row position in the tile
+  int lo = 0;
+  if (m.W > 0 && m.F == 0) {
+    lo = first - m.W;
+    if (lo < m.c) lo = 0;  // first - W <= c - 1: the row also sees the contextual prefix
+  }
+  r.lo = lo;
+  if (m0 >= u) {  // only target rows: history/contextual columns + own diagonal block
+    r.hi = u;
+    r.diag_lo = m0;
+  } else {
+    r.hi = m1;
+  }
+  return r;
+}
+
+}  // namespace b200hstu

@@ -1,0 +1,690 @@
+// Memory-bound stages around the attention: row LayerNorm (fwd/bwd), SiLU gating of U (fwd/bwd)
+// and the output-side  y = act(u) * Norm(attn)  with its [u, attn, y] concatenation (fwd/bwd).
+//
+// All kernels are "one warp per row, row held in registers": a lane owns 16-byte vectors
+// lane, lane + 32, ... of the row, so global loads/stores are coalesced 512-byte warp
+// transactions, statistics are fp32 warp shuffles, and every input element is read from
+// HBM exactly once.  Rows are limited to 32 * MAXV vectors (bf16/fp16: 2048 elements, fp32: 1024).
+// Backward kernels are persistent (a few CTAs per SM): each warp walks rows with a stride,
+// keeps its share of dweight / dbias in registers, the CTA reduces them through shared memory
+// into one fp32 partial row, and a second small kernel sums the partial rows.
+#include "common.cuh"
+
+namespace b200hstu {
+namespace {
+
+constexpr int WARPS = 8;  // warps per CTA
+
+template <typename E> struct VecInfo { static constexpr int EV = 16 / sizeof(E); };
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// sum over the `width` (power of two <= 32) consecutive lanes this lane belongs to
+__device__ __forceinline__ float group_sum(float v, int width) {
+  for (int o = width >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename E, int MAXV>
+struct Row {
+  static constexpr int EV = VecInfo<E>::EV;
+  float v[MAXV][EV];
+
+  __device__ __forceinline__ void load(const E *row, int D, int lane, bool vec_ok) {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      int e0 = (k * 32 + lane) * EV;
+      if (vec_ok && e0 + EV <= D) {
+        uint4 raw = *reinterpret_cast<const uint4 *>(row + e0);
+        const E *pe = reinterpret_cast<const E *>(&raw);
+#pragma unroll
+        for (int t = 0; t < EV; ++t) v[k][t] = to_f32(pe[t]);
+      } else {
+#pragma unroll
+        for (int t = 0; t < EV; ++t) v[k][t] = (e0 + t < D) ? to_f32(row[e0 + t]) : 0.f;
+      }
+    }
+  }
+  __device__ __forceinline__ void store(E *row, int D, int lane, bool vec_ok) const {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      int e0 = (k * 32 + lane) * EV;
+      if (vec_ok && e0 + EV <= D) {
+        uint4 raw;
+        E *pe = reinterpret_cast<E *>(&raw);
+#pragma unroll
+        for (int t = 0; t < EV; ++t) pe[t] = from_f32<E>(v[k][t]);
+        *reinterpret_cast<uint4 *>(row + e0) = raw;
+      } else {
+#pragma unroll
+        for (int t = 0; t < EV; ++t)
+          if (e0 + t < D) row[e0 + t] = from_f32<E>(v[k][t]);
+      }
+    }
+  }
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) v[k][t] = 0.f;
+  }
+};
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// mean / rstd of a row held in registers (two-pass: mean first, then centred second moment)
+template <typename E, int MAXV>
+__device__ __forceinline__ void row_stats(const Row<E, MAXV> &x, int D, int lane, float eps, float &mean,
+                                          float &rstd) {
+  constexpr int EV = VecInfo<E>::EV;
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+    for (int t = 0; t < EV; ++t) s += x.v[k][t];  // out-of-range slots hold 0
+  mean = warp_sum(s) / (float)D;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+    for (int t = 0; t < EV; ++t) {
+      int e = (k * 32 + lane) * EV + t;
+      float d = e < D ? x.v[k][t] - mean : 0.f;
+      q += d * d;
+    }
+  rstd = rsqrtf(warp_sum(q) / (float)D + eps);
+}
+
+// ---------------------------------------------------------------------------------------
+// LayerNorm
+// ---------------------------------------------------------------------------------------
+template <typename E, int MAXV>
+__global__ void __launch_bounds__(WARPS * 32) layer_norm_fwd_kernel(const E *__restrict__ x, int64_t x_rs,
+                                                                    const E *__restrict__ w,
+                                                                    const E *__restrict__ b, E *__restrict__ y,
+                                                                    int64_t y_rs, float *__restrict__ mean_out,
+                                                                    float *__restrict__ rstd_out, int64_t rows,
+                                                                    int D, float eps, bool vec_ok) {
+  constexpr int EV = VecInfo<E>::EV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  Row<E, MAXV> wr, br;
+  wr.load(w, D, lane, vec_ok);
+  br.load(b, D, lane, vec_ok);
+  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < rows; row += (int64_t)gridDim.x * WARPS) {
+    Row<E, MAXV> xr;
+    xr.load(x + row * x_rs, D, lane, vec_ok);
+    float mean, rstd;
+    row_stats(xr, D, lane, eps, mean, rstd);
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) xr.v[k][t] = (xr.v[k][t] - mean) * rstd * wr.v[k][t] + br.v[k][t];
+    xr.store(y + row * y_rs, D, lane, vec_ok);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+  }
+}
+
+// shared-memory reduction of the per-warp column accumulators into partial[blockIdx.x][which][D]
+template <typename E, int MAXV>
+__device__ __forceinline__ void reduce_columns_to_partial(const Row<E, MAXV> &acc, float *smem, float *partial_row,
+                                                          int D, int lane, int warp) {
+  constexpr int EV = VecInfo<E>::EV;
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+    for (int t = 0; t < EV; ++t) {
+      int e = (k * 32 + lane) * EV + t;
+      if (e < D) smem[warp * D + e] = acc.v[k][t];
+    }
+  __syncthreads();
+  for (int e = threadIdx.x; e < D; e += WARPS * 32) {
+    float s = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < WARPS; ++wv) s += smem[wv * D + e];
+    partial_row[e] = s;
+  }
+}
+
+template <typename E, int MAXV>
+__global__ void __launch_bounds__(WARPS * 32) layer_norm_bwd_kernel(
+    const E *__restrict__ dy, int64_t dy_rs, const E *__restrict__ x, int64_t x_rs, const E *__restrict__ w,
+    const float *__restrict__ mean_in, const float *__restrict__ rstd_in, E *__restrict__ dx, int64_t dx_rs,
+    float *__restrict__ partial, int64_t rows, int D, bool vec_ok) {
+  constexpr int EV = VecInfo<E>::EV;
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  Row<E, MAXV> wr, dw, db;
+  wr.load(w, D, lane, vec_ok);
+  dw.zero();
+  db.zero();
+  const float invD = 1.f / (float)D;
+  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < rows; row += (int64_t)gridDim.x * WARPS) {
+    Row<E, MAXV> xr, gr;
+    xr.load(x + row * x_rs, D, lane, vec_ok);
+    gr.load(dy + row * dy_rs, D, lane, vec_ok);
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) {
+        int e = (k * 32 + lane) * EV + t;
+        float xhat = e < D ? (xr.v[k][t] - mean) * rstd : 0.f;
+        float g = gr.v[k][t];
+        dw.v[k][t] += g * xhat;
+        db.v[k][t] += g;
+        float gw = g * wr.v[k][t];
+        xr.v[k][t] = xhat;
+        gr.v[k][t] = gw;
+        c1 += gw * xhat;
+        c2 += gw;
+      }
+    c1 = warp_sum(c1) * invD;
+    c2 = warp_sum(c2) * invD;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) gr.v[k][t] = (gr.v[k][t] - c2 - xr.v[k][t] * c1) * rstd;
+    gr.store(dx + row * dx_rs, D, lane, vec_ok);
+  }
+  float *prow = partial + (int64_t)blockIdx.x * 2 * D;
+  reduce_columns_to_partial(dw, smem, prow, D, lane, warp);
+  reduce_columns_to_partial(db, smem, prow + D, D, lane, warp);
+}
+
+// out[which][e] = sum_b partial[b][which][e]   (which in {0,1}); one thread per column
+template <typename E>
+__global__ void reduce_partial_kernel(const float *__restrict__ partial, int nblocks, int D, E *__restrict__ out0,
+                                      E *__restrict__ out1) {
+  int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= 2 * D) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(int64_t)b * 2 * D + e];
+  if (e < D) {
+    if (out0) out0[e] = from_f32<E>(s);
+  } else {
+    if (out1) out1[e - D] = from_f32<E>(s);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// SiLU gating
+// ---------------------------------------------------------------------------------------
+template <typename E, bool BWD>
+__global__ void __launch_bounds__(256) silu_kernel(const E *__restrict__ dy, int64_t dy_rs, const E *__restrict__ x,
+                                                   int64_t x_rs, E *__restrict__ out, int64_t out_rs, int64_t rows,
+                                                   int width, bool vec_ok) {
+  constexpr int EV = VecInfo<E>::EV;
+  const int vec_per_row = (width + EV - 1) / EV;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = idx / vec_per_row;
+    int e0 = (int)(idx - row * vec_per_row) * EV;
+    const E *xp = x + row * x_rs + e0;
+    E *op = out + row * out_rs + e0;
+    if (vec_ok && e0 + EV <= width) {
+      uint4 xraw = *reinterpret_cast<const uint4 *>(xp);
+      const E *xe = reinterpret_cast<const E *>(&xraw);
+      uint4 oraw;
+      E *oe = reinterpret_cast<E *>(&oraw);
+      if (BWD) {
+        uint4 graw = *reinterpret_cast<const uint4 *>(dy + row * dy_rs + e0);
+        const E *ge = reinterpret_cast<const E *>(&graw);
+#pragma unroll
+        for (int t = 0; t < EV; ++t) oe[t] = from_f32<E>(to_f32(ge[t]) * dsiluf_(to_f32(xe[t])));
+      } else {
+#pragma unroll
+        for (int t = 0; t < EV; ++t) oe[t] = from_f32<E>(siluf_(to_f32(xe[t])));
+      }
+      *reinterpret_cast<uint4 *>(op) = oraw;
+    } else {
+      for (int t = 0; t < EV && e0 + t < width; ++t) {
+        float xv = to_f32(xp[t]);
+        op[t] = from_f32<E>(BWD ? to_f32(dy[row * dy_rs + e0 + t]) * dsiluf_(xv) : siluf_(xv));
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// y = act(u) * Norm(attn), optional [u | attn | y] concat
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float act_f(float u, int act) {
+  return act == 0 ? u : (act == 1 ? sigmoidf_(u) : siluf_(u));
+}
+__device__ __forceinline__ float dact_f(float u, int act) {
+  if (act == 0) return 1.f;
+  if (act == 1) {
+    float s = sigmoidf_(u);
+    return s * (1.f - s);
+  }
+  return dsiluf_(u);
+}
+
+struct NormMulParams {
+  const void *attn, *u, *w, *b, *dout;
+  void *out, *dattn, *du;
+  float *mean, *rstd, *partial;
+  int64_t attn_rs, u_rs, out_rs, dout_rs, dattn_rs, du_rs, rows;
+  int H, V, concat_u, concat_x, act, group_norm;
+  float eps;
+  bool vec_ok;
+};
+
+// LayerNorm flavour: one warp per row of D = H * V elements.
+template <typename E, int MAXV>
+__global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_kernel(NormMulParams p) {
+  constexpr int EV = VecInfo<E>::EV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = p.H * p.V;
+  Row<E, MAXV> wr, br;
+  wr.load((const E *)p.w, D, lane, p.vec_ok);
+  br.load((const E *)p.b, D, lane, p.vec_ok);
+  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < p.rows; row += (int64_t)gridDim.x * WARPS) {
+    Row<E, MAXV> xr, ur;
+    xr.load((const E *)p.attn + row * p.attn_rs, D, lane, p.vec_ok);
+    ur.load((const E *)p.u + row * p.u_rs, D, lane, p.vec_ok);
+    float mean, rstd;
+    row_stats(xr, D, lane, p.eps, mean, rstd);
+    E *orow = (E *)p.out + row * p.out_rs;
+    int off = 0;
+    if (p.concat_u) {
+      ur.store(orow, D, lane, p.vec_ok);
+      off += D;
+    }
+    if (p.concat_x) {
+      xr.store(orow + off, D, lane, p.vec_ok);
+      off += D;
+    }
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t)
+        xr.v[k][t] = act_f(ur.v[k][t], p.act) * ((xr.v[k][t] - mean) * rstd * wr.v[k][t] + br.v[k][t]);
+    xr.store(orow + off, D, lane, p.vec_ok);
+    if (lane == 0) {
+      if (p.mean) p.mean[row] = mean;
+      if (p.rstd) p.rstd[row] = rstd;
+    }
+  }
+}
+
+template <typename E, int MAXV>
+__global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams p) {
+  constexpr int EV = VecInfo<E>::EV;
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = p.H * p.V;
+  Row<E, MAXV> wr, br, dw, db;
+  wr.load((const E *)p.w, D, lane, p.vec_ok);
+  br.load((const E *)p.b, D, lane, p.vec_ok);
+  dw.zero();
+  db.zero();
+  const float invD = 1.f / (float)D;
+  const int off_x = p.concat_u ? D : 0;
+  const int off_y = off_x + (p.concat_x ? D : 0);
+  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < p.rows; row += (int64_t)gridDim.x * WARPS) {
+    Row<E, MAXV> xr, ur, gy;
+    xr.load((const E *)p.attn + row * p.attn_rs, D, lane, p.vec_ok);
+    ur.load((const E *)p.u + row * p.u_rs, D, lane, p.vec_ok);
+    const E *grow = (const E *)p.dout + row * p.dout_rs;
+    gy.load(grow + off_y, D, lane, p.vec_ok);
+    const float mean = p.mean[row], rstd = p.rstd[row];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) {
+        int e = (k * 32 + lane) * EV + t;
+        float xhat = e < D ? (xr.v[k][t] - mean) * rstd : 0.f;
+        float ln = xhat * wr.v[k][t] + br.v[k][t];
+        float uu = ur.v[k][t];
+        float g = gy.v[k][t];
+        float ga = g * act_f(uu, p.act);  // gradient w.r.t. the normalised value
+        ur.v[k][t] = g * ln * dact_f(uu, p.act);  // du (y part)
+        dw.v[k][t] += ga * xhat;
+        db.v[k][t] += ga;
+        float gw = ga * wr.v[k][t];
+        xr.v[k][t] = xhat;
+        gy.v[k][t] = gw;
+        c1 += gw * xhat;
+        c2 += gw;
+      }
+    c1 = warp_sum(c1) * invD;
+    c2 = warp_sum(c2) * invD;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) gy.v[k][t] = (gy.v[k][t] - c2 - xr.v[k][t] * c1) * rstd;
+    if (p.concat_u) {
+      xr.load(grow, D, lane, p.vec_ok);
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+        for (int t = 0; t < EV; ++t) ur.v[k][t] += xr.v[k][t];
+    }
+    if (p.concat_x) {
+      xr.load(grow + off_x, D, lane, p.vec_ok);
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+        for (int t = 0; t < EV; ++t) gy.v[k][t] += xr.v[k][t];
+    }
+    ur.store((E *)p.du + row * p.du_rs, D, lane, p.vec_ok);
+    gy.store((E *)p.dattn + row * p.dattn_rs, D, lane, p.vec_ok);
+  }
+  float *prow = p.partial + (int64_t)blockIdx.x * 2 * D;
+  reduce_columns_to_partial(dw, smem, prow, D, lane, warp);
+  reduce_columns_to_partial(db, smem, prow + D, D, lane, warp);
+}
+
+// Group-norm flavour (statistics per head; weight / bias are per-head scalars): one warp per
+// (row, head), scalar loads.  Used by the `group_norm=True` variant of the output stage only.
+template <typename E, bool BWD>
+__global__ void __launch_bounds__(WARPS * 32) group_norm_mul_kernel(NormMulParams p) {
+  extern __shared__ float smem[];  // BWD: [WARPS][2][H]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int H = p.H, V = p.V, D = H * V;
+  const int off_x = p.concat_u ? D : 0;
+  const int off_y = off_x + (p.concat_x ? D : 0);
+  if (BWD) {
+    for (int i = threadIdx.x; i < WARPS * 2 * H; i += WARPS * 32) smem[i] = 0.f;
+    __syncthreads();
+  }
+  const int64_t items = p.rows * H;
+  for (int64_t it = (int64_t)blockIdx.x * WARPS + warp; it < items; it += (int64_t)gridDim.x * WARPS) {
+    const int64_t row = it / H;
+    const int h = (int)(it - row * H);
+    const E *xa = (const E *)p.attn + row * p.attn_rs + h * V;
+    const E *ua = (const E *)p.u + row * p.u_rs + h * V;
+    const float wv = to_f32(((const E *)p.w)[h]), bv = to_f32(((const E *)p.b)[h]);
+    float mean, rstd;
+    if (!BWD) {
+      float s = 0.f;
+      for (int e = lane; e < V; e += 32) s += to_f32(xa[e]);
+      mean = warp_sum(s) / (float)V;
+      float q = 0.f;
+      for (int e = lane; e < V; e += 32) {
+        float d = to_f32(xa[e]) - mean;
+        q += d * d;
+      }
+      rstd = rsqrtf(warp_sum(q) / (float)V + p.eps);
+      E *orow = (E *)p.out + row * p.out_rs + h * V;
+      for (int e = lane; e < V; e += 32) {
+        float xv = to_f32(xa[e]), uv = to_f32(ua[e]);
+        // the group-norm branch multiplies by u itself (no activation) and concatenates only
+        // when both flags are set (pt_hstu_linear.py:42-54)
+        if (p.concat_u && p.concat_x) {
+          orow[e] = from_f32<E>(uv);
+          orow[D + e] = from_f32<E>(xv);
+        }
+        orow[off_y + e] = from_f32<E>(uv * ((xv - mean) * rstd * wv + bv));
+      }
+      if (lane == 0) {
+        if (p.mean) p.mean[it] = mean;
+        if (p.rstd) p.rstd[it] = rstd;
+      }
+    } else {
+      mean = p.mean[it];
+      rstd = p.rstd[it];
+      const E *grow = (const E *)p.dout + row * p.dout_rs + h * V;
+      float c1 = 0.f, c2 = 0.f, aw = 0.f, ab = 0.f;
+      for (int e = lane; e < V; e += 32) {
+        float xhat = (to_f32(xa[e]) - mean) * rstd;
+        float ga = to_f32(grow[off_y + e]) * to_f32(ua[e]);
+        aw += ga * xhat;
+        ab += ga;
+        c1 += ga * wv * xhat;
+        c2 += ga * wv;
+      }
+      c1 = warp_sum(c1) / (float)V;
+      c2 = warp_sum(c2) / (float)V;
+      aw = warp_sum(aw);
+      ab = warp_sum(ab);
+      if (lane == 0) {
+        smem[(warp * 2 + 0) * H + h] += aw;
+        smem[(warp * 2 + 1) * H + h] += ab;
+      }
+      E *dxa = (E *)p.dattn + row * p.dattn_rs + h * V;
+      E *dua = (E *)p.du + row * p.du_rs + h * V;
+      for (int e = lane; e < V; e += 32) {
+        float xhat = (to_f32(xa[e]) - mean) * rstd;
+        float g = to_f32(grow[off_y + e]);
+        float gw = g * to_f32(ua[e]) * wv;
+        float dxv = (gw - c2 - xhat * c1) * rstd;
+        float duv = g * (xhat * wv + bv);
+        if (p.concat_u && p.concat_x) {
+          duv += to_f32(grow[e]);
+          dxv += to_f32(grow[D + e]);
+        }
+        dxa[e] = from_f32<E>(dxv);
+        dua[e] = from_f32<E>(duv);
+      }
+    }
+  }
+  if (BWD) {
+    __syncthreads();
+    float *prow = p.partial + (int64_t)blockIdx.x * 2 * H;
+    for (int i = threadIdx.x; i < 2 * H; i += WARPS * 32) {
+      float s = 0.f;
+      for (int wv = 0; wv < WARPS; ++wv) s += smem[wv * 2 * H + i];
+      prow[i] = s;
+    }
+  }
+}
+
+int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+constexpr int BWD_BLOCKS_PER_SM = 2;
+int bwd_blocks() { return num_sms() * BWD_BLOCKS_PER_SM; }
+constexpr int MAX_BWD_BLOCKS = 512;  // workspace is sized for this many partial rows
+
+template <typename E>
+int max_row_elems() { return 32 * 8 * VecInfo<E>::EV; }
+
+template <typename E>
+int pick_maxv(int D) {
+  int nvec = (D + VecInfo<E>::EV - 1) / VecInfo<E>::EV;
+  int per_lane = (nvec + 31) / 32;
+  return per_lane <= 1 ? 1 : per_lane <= 2 ? 2 : per_lane <= 4 ? 4 : 8;
+}
+
+#define DISPATCH_MAXV(maxv, ...)          \
+  switch (maxv) {                         \
+    case 1: { constexpr int MV = 1; __VA_ARGS__; } break; \
+    case 2: { constexpr int MV = 2; __VA_ARGS__; } break; \
+    case 4: { constexpr int MV = 4; __VA_ARGS__; } break; \
+    default: { constexpr int MV = 8; __VA_ARGS__; } break; \
+  }
+
+template <typename E>
+int ln_fwd_t(const void *x, int64_t x_rs, const void *w, const void *b, void *y, int64_t y_rs, float *mean,
+             float *rstd, int64_t rows, int D, float eps, cudaStream_t st) {
+  constexpr int EV = VecInfo<E>::EV;
+  if (D > max_row_elems<E>()) return fail(B200_HSTU_EUNSUPPORTED, "layer_norm: D=%d exceeds %d", D, max_row_elems<E>());
+  bool vec_ok = aligned16(x) && aligned16(y) && aligned16(w) && aligned16(b) && x_rs % EV == 0 && y_rs % EV == 0;
+  int64_t nblk = (rows + WARPS - 1) / WARPS;
+  int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
+  if (grid == 0) return 0;
+  DISPATCH_MAXV(pick_maxv<E>(D), (layer_norm_fwd_kernel<E, MV><<<grid, WARPS * 32, 0, st>>>(
+                                     (const E *)x, x_rs, (const E *)w, (const E *)b, (E *)y, y_rs, mean, rstd,
+                                     rows, D, eps, vec_ok)));
+  count_launch();
+  B200_CHECK_LAUNCH("layer_norm forward");
+  return 0;
+}
+
+template <typename E>
+int ln_bwd_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const void *w, const float *mean,
+             const float *rstd, void *dx, int64_t dx_rs, void *dw, void *db, void *partial, int64_t partial_bytes,
+             int64_t rows, int D, cudaStream_t st) {
+  constexpr int EV = VecInfo<E>::EV;
+  if (D > max_row_elems<E>()) return fail(B200_HSTU_EUNSUPPORTED, "layer_norm: D=%d exceeds %d", D, max_row_elems<E>());
+  int grid = bwd_blocks();
+  if (grid > MAX_BWD_BLOCKS) grid = MAX_BWD_BLOCKS;
+  if ((int64_t)grid * 2 * D * (int64_t)sizeof(float) > partial_bytes)
+    return fail(B200_HSTU_EWORKSPACE, "layer_norm backward: scratch of %lld bytes is too small",
+                (long long)partial_bytes);
+  bool vec_ok = aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(w) && x_rs % EV == 0 &&
+                dy_rs % EV == 0 && dx_rs % EV == 0;
+  size_t smem = (size_t)WARPS * D * sizeof(float);
+  DISPATCH_MAXV(pick_maxv<E>(D), {
+    auto kern = layer_norm_bwd_kernel<E, MV>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, WARPS * 32, smem, st>>>((const E *)dy, dy_rs, (const E *)x, x_rs, (const E *)w, mean, rstd,
+                                         (E *)dx, dx_rs, (float *)partial, rows, D, vec_ok);
+  });
+  count_launch();
+  B200_CHECK_LAUNCH("layer_norm backward");
+  reduce_partial_kernel<E><<<(2 * D + 255) / 256, 256, 0, st>>>((const float *)partial, grid, D, (E *)dw, (E *)db);
+  count_launch();
+  B200_CHECK_LAUNCH("layer_norm backward (reduce)");
+  return 0;
+}
+
+template <typename E>
+int silu_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out, int64_t out_rs, int64_t rows,
+           int width, bool bwd, cudaStream_t st) {
+  constexpr int EV = VecInfo<E>::EV;
+  bool vec_ok = aligned16(x) && aligned16(out) && x_rs % EV == 0 && out_rs % EV == 0 &&
+                (!bwd || (aligned16(dy) && dy_rs % EV == 0));
+  int64_t total = rows * ((width + EV - 1) / EV);
+  if (total == 0) return 0;
+  int64_t nblk = (total + 255) / 256;
+  int grid = (int)(nblk < (int64_t)num_sms() * 16 ? nblk : (int64_t)num_sms() * 16);
+  if (bwd)
+    silu_kernel<E, true><<<grid, 256, 0, st>>>((const E *)dy, dy_rs, (const E *)x, x_rs, (E *)out, out_rs, rows,
+                                               width, vec_ok);
+  else
+    silu_kernel<E, false><<<grid, 256, 0, st>>>(nullptr, 0, (const E *)x, x_rs, (E *)out, out_rs, rows, width,
+                                                vec_ok);
+  count_launch();
+  B200_CHECK_LAUNCH("silu");
+  return 0;
+}
+
+template <typename E>
+int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
+  constexpr int EV = VecInfo<E>::EV;
+  NormMulParams p;
+  p.attn = a.attn; p.u = a.u; p.w = a.weight; p.b = a.bias; p.dout = a.dout;
+  p.out = a.out; p.dattn = a.dattn; p.du = a.du;
+  p.mean = a.mean; p.rstd = a.rstd; p.partial = (float *)a.partial;
+  p.attn_rs = a.attn_row_stride; p.u_rs = a.u_row_stride; p.out_rs = a.out_row_stride;
+  p.dout_rs = a.dout_row_stride; p.dattn_rs = a.dattn_row_stride; p.du_rs = a.du_row_stride;
+  p.rows = a.rows; p.H = a.H; p.V = a.V; p.concat_u = a.concat_u; p.concat_x = a.concat_x; p.act = a.act;
+  p.group_norm = a.group_norm; p.eps = a.eps;
+  const int D = a.H * a.V;
+  if (a.rows == 0) {
+    if (bwd) {  // dweight / dbias of an empty batch are zeros
+      int n = a.group_norm ? a.H : D;
+      cudaMemsetAsync(a.dweight, 0, (size_t)n * sizeof(E), st);
+      cudaMemsetAsync(a.dbias, 0, (size_t)n * sizeof(E), st);
+    }
+    return 0;
+  }
+  if (a.group_norm) {
+    int64_t items = a.rows * a.H;
+    int64_t nblk = (items + WARPS - 1) / WARPS;
+    if (!bwd) {
+      int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
+      group_norm_mul_kernel<E, false><<<grid, WARPS * 32, 0, st>>>(p);
+      count_launch();
+      B200_CHECK_LAUNCH("group_norm_mul forward");
+      return 0;
+    }
+    int grid = bwd_blocks();
+    if (grid > MAX_BWD_BLOCKS) grid = MAX_BWD_BLOCKS;
+    if ((int64_t)grid * 2 * a.H * (int64_t)sizeof(float) > a.partial_bytes)
+      return fail(B200_HSTU_EWORKSPACE, "norm_mul backward: scratch too small");
+    size_t smem = (size_t)WARPS * 2 * a.H * sizeof(float);
+    group_norm_mul_kernel<E, true><<<grid, WARPS * 32, smem, st>>>(p);
+    count_launch();
+    B200_CHECK_LAUNCH("group_norm_mul backward");
+    reduce_partial_kernel<E><<<(2 * a.H + 255) / 256, 256, 0, st>>>(p.partial, grid, a.H, (E *)a.dweight,
+                                                                    (E *)a.dbias);
+    count_launch();
+    B200_CHECK_LAUNCH("group_norm_mul backward (reduce)");
+    return 0;
+  }
+  if (D > max_row_elems<E>()) return fail(B200_HSTU_EUNSUPPORTED, "norm_mul: H*V=%d exceeds %d", D, max_row_elems<E>());
+  bool vec_ok = aligned16(a.attn) && aligned16(a.u) && aligned16(a.weight) && aligned16(a.bias) &&
+                a.attn_row_stride % EV == 0 && a.u_row_stride % EV == 0 && D % EV == 0;
+  if (!bwd) {
+    vec_ok = vec_ok && aligned16(a.out) && a.out_row_stride % EV == 0;
+    p.vec_ok = vec_ok;
+    int64_t nblk = (a.rows + WARPS - 1) / WARPS;
+    int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
+    DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV><<<grid, WARPS * 32, 0, st>>>(p)));
+    count_launch();
+    B200_CHECK_LAUNCH("norm_mul forward");
+    return 0;
+  }
+  vec_ok = vec_ok && aligned16(a.dout) && aligned16(a.dattn) && aligned16(a.du) && a.dout_row_stride % EV == 0 &&
+           a.dattn_row_stride % EV == 0 && a.du_row_stride % EV == 0;
+  p.vec_ok = vec_ok;
+  int grid = bwd_blocks();
+  if (grid > MAX_BWD_BLOCKS) grid = MAX_BWD_BLOCKS;
+  if ((int64_t)grid * 2 * D * (int64_t)sizeof(float) > a.partial_bytes)
+    return fail(B200_HSTU_EWORKSPACE, "norm_mul backward: scratch too small");
+  size_t smem = (size_t)WARPS * D * sizeof(float);
+  DISPATCH_MAXV(pick_maxv<E>(D), {
+    auto kern = norm_mul_bwd_kernel<E, MV>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, WARPS * 32, smem, st>>>(p);
+  });
+  count_launch();
+  B200_CHECK_LAUNCH("norm_mul backward");
+  reduce_partial_kernel<E><<<(2 * D + 255) / 256, 256, 0, st>>>(p.partial, grid, D, (E *)a.dweight, (E *)a.dbias);
+  count_launch();
+  B200_CHECK_LAUNCH("norm_mul backward (reduce)");
+  return 0;
+}
+
+}  // namespace
+
+#define DISPATCH_DTYPE(dtype, CALL)                                          \
+  switch (dtype) {                                                           \
+    case B200_HSTU_F32: { using E = float; return CALL; }                    \
+    case B200_HSTU_BF16: { using E = __nv_bfloat16; return CALL; }           \
+    case B200_HSTU_F16: { using E = __half; return CALL; }                   \
+    default: return fail(B200_HSTU_EINVAL, "unknown dtype %d", (int)(dtype)); \
+  }
+
+int layer_norm_fwd(const void *x, int64_t x_rs, const void *w, const void *b, void *y, int64_t y_rs, float *mean,
+                   float *rstd, int64_t rows, int D, float eps, int dtype, cudaStream_t st) {
+  DISPATCH_DTYPE(dtype, (ln_fwd_t<E>(x, x_rs, w, b, y, y_rs, mean, rstd, rows, D, eps, st)));
+}
+int layer_norm_bwd(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const void *w, const float *mean,
+                   const float *rstd, void *dx, int64_t dx_rs, void *dw, void *db, void *partial,
+                   int64_t partial_bytes, int64_t rows, int D, int dtype, cudaStream_t st) {
+  DISPATCH_DTYPE(dtype, (ln_bwd_t<E>(dy, dy_rs, x, x_rs, w, mean, rstd, dx, dx_rs, dw, db, partial, partial_bytes,
+                                     rows, D, st)));
+}
+int64_t stage_bwd_workspace_bytes(int cols) { return (int64_t)MAX_BWD_BLOCKS * 2 * cols * (int64_t)sizeof(float); }
+int silu_launch(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out, int64_t out_rs, int64_t rows,
+                int width, bool bwd, int dtype, cudaStream_t st) {
+  DISPATCH_DTYPE(dtype, (silu_t<E>(dy, dy_rs, x, x_rs, out, out_rs, rows, width, bwd, st)));
+}
+int norm_mul(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
+  DISPATCH_DTYPE(a.dtype, (norm_mul_t<E>(a, bwd, st)));
+}
+
+}  // namespace b200hstu

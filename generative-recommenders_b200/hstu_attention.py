@@ -1,0 +1,195 @@
+"""``hstu_mha`` with the reference's calling convention, running the sm_100a kernels.
+
+Mirrors generative_recommenders/ops/hstu_attention.py:101-207 (arguments, checks and return
+value) and the autograd wrapper of its GPU backends
+(generative_recommenders/ops/triton/triton_hstu_attention.py:2978-3092).
+"""
+
+from typing import Optional
+
+import torch
+
+from . import _cabi
+from .common import HammerKernel, _require_cuda_backend, dtype_code, last_dim_contiguous, require_cuda, stream_ptr
+
+_IMPL = {"auto": _cabi.IMPL_AUTO, "simt": _cabi.IMPL_SIMT, "tcgen05": _cabi.IMPL_TCGEN05}
+_forced_impl = "auto"
+
+
+def set_attention_impl(name: str) -> None:
+    """Force the kernel family ("auto", "simt", "tcgen05") - for tests and profiling."""
+    global _forced_impl
+    if name not in _IMPL:
+        raise ValueError(name)
+    _forced_impl = name
+
+
+def _i32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    # tests of the reference pass int64 offsets (hstu_attention_test.py:81-84); its CUDA op wants
+    # int32 (flash_common.cpp:460-472).  The kernels read int32.
+    if t is None:
+        return None
+    return t.to(torch.int32).contiguous()
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, alpha, max_attn_len,
+                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance):
+    L, H, dqk = q.shape
+    a.q, a.k, a.v = _ptr(q), _ptr(k), _ptr(v)
+    a.seq_offsets = _ptr(seq_offsets)
+    a.num_targets = _ptr(num_targets)
+    if attn_scale is not None:
+        a.attn_scale = attn_scale.data_ptr()
+        a.attn_scale_numel = attn_scale.numel()
+    a.q_row_stride, a.q_head_stride = q.stride(0), q.stride(1)
+    a.k_row_stride, a.k_head_stride = k.stride(0), k.stride(1)
+    a.v_row_stride, a.v_head_stride = v.stride(0), v.stride(1)
+    a.total_L = L
+    a.B = seq_offsets.numel() - 1
+    a.H, a.dqk, a.dv = H, dqk, v.shape[2]
+    a.max_seq_len = max_seq_len
+    a.alpha = alpha
+    a.max_attn_len = max_attn_len
+    a.contextual_seq_len = contextual_seq_len
+    a.min_full_attn_seq_len = min_full_attn_seq_len
+    a.dtype = dtype_code(q)
+    a.impl = _IMPL[_forced_impl]
+    if bias_by_distance is not None:
+        a.bias_by_distance = bias_by_distance.data_ptr()
+        a.bias_numel = bias_by_distance.numel()
+
+
+def _workspace(a, backward: bool, device) -> Optional[torch.Tensor]:
+    n = _cabi.lib().b200_hstu_attn_workspace_bytes(a, 1 if backward else 0)
+    if n <= 0:
+        return None
+    ws = torch.empty(n, dtype=torch.uint8, device=device)
+    a.workspace = ws.data_ptr()
+    a.workspace_bytes = n
+    return ws
+
+
+def hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
+                       contextual_seq_len, min_full_attn_seq_len, bias_by_distance=None) -> torch.Tensor:
+    """One forward launch; all tensors already validated / int32 / on the device."""
+    L, H, _ = q.shape
+    out = torch.empty((L, H, v.shape[2]), dtype=q.dtype, device=q.device)
+    if L == 0:
+        return out
+    a = _cabi.AttnArgs()
+    _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, alpha, max_attn_len,
+                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance)
+    a.out = out.data_ptr()
+    a.o_row_stride, a.o_head_stride = out.stride(0), out.stride(1)
+    ws = _workspace(a, False, q.device)  # noqa: F841  (kept alive until the launch is queued)
+    with torch.cuda.device(q.device):
+        _cabi.check(_cabi.lib().b200_hstu_attn_fwd(a, stream_ptr(q.device)), "b200_hstu_attn_fwd")
+    return out
+
+
+def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
+                       contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance=None) -> None:
+    """Fills caller-allocated dq / dk / dv (the ownership rule of the reference's backward,
+    triton_hstu_attention.py:3059-3079)."""
+    if q.shape[0] == 0:
+        return
+    a = _cabi.AttnArgs()
+    _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, alpha, max_attn_len,
+                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance)
+    a.dout = dout.data_ptr()
+    a.dq, a.dk, a.dv_ = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.do_row_stride, a.do_head_stride = dout.stride(0), dout.stride(1)
+    a.dq_row_stride, a.dq_head_stride = dq.stride(0), dq.stride(1)
+    a.dk_row_stride, a.dk_head_stride = dk.stride(0), dk.stride(1)
+    a.dv_row_stride, a.dv_head_stride = dv.stride(0), dv.stride(1)
+    ws = _workspace(a, True, q.device)  # noqa: F841
+    with torch.cuda.device(q.device):
+        _cabi.check(_cabi.lib().b200_hstu_attn_bwd(a, stream_ptr(q.device)), "b200_hstu_attn_bwd")
+
+
+class _HstuMhaFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, max_seq_len, alpha,
+                max_attn_len, contextual_seq_len, min_full_attn_seq_len):
+        out = hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
+                                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance)
+        ctx.save_for_backward(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance)
+        ctx.params = (max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance = ctx.saved_tensors
+        max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len = ctx.params
+        dout = last_dim_contiguous(dout)
+        if dout.stride(1) != dout.shape[2]:
+            dout = dout.contiguous()
+        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+        dk = torch.empty_like(k, memory_format=torch.contiguous_format)
+        dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+        hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
+                           contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance)
+        return dq, dk, dv, None, None, None, None, None, None, None, None, None
+
+
+def hstu_mha(
+    max_seq_len: int,
+    alpha: float,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    seq_offsets: torch.Tensor,
+    causal: bool = True,
+    dropout_pr: float = 0.0,
+    training: bool = True,
+    num_targets: Optional[torch.Tensor] = None,
+    attn_scale: Optional[torch.Tensor] = None,
+    max_attn_len: int = 0,
+    contextual_seq_len: int = 0,
+    min_full_attn_seq_len: int = 0,
+    sort_by_length: bool = False,
+    kernel: HammerKernel = HammerKernel.CUDA,
+    enable_tma: bool = False,
+    bias_by_distance: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Jagged HSTU attention; same arguments, checks and result as the reference's
+    ``hstu_mha`` (generative_recommenders/ops/hstu_attention.py:101-207).
+
+    ``sort_by_length`` and ``enable_tma`` are accepted and ignored: work is always scheduled
+    longest-first and K/V always stream through TMA.  ``bias_by_distance`` is an extension
+    (fp32 ``[n]``: a relative-position bias added to ``alpha * q.k`` before SiLU, indexed by
+    ``|i - j|``, shared by all heads; no gradient is produced for it).
+    """
+    _require_cuda_backend(kernel)
+    torch._assert(max_seq_len > 0, "max_seq_len must be larger than 0")
+    torch._assert(q.dim() == 3, "q must be 3-D")
+    torch._assert(k.shape == q.shape, "k must be the same shape as q")
+    torch._assert(v.dim() == 3, "v must be 3-D")
+    torch._assert(v.shape[0] == q.shape[0], "wrong v shape[0]")
+    torch._assert(v.shape[1] == q.shape[1], "wrong v shape[1]")
+    torch._assert(causal, "only support causal attention")
+    if dropout_pr > 1e-6 and training:
+        raise NotImplementedError("attention dropout is not implemented (the HSTU layer never uses it)")
+    require_cuda(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance)
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share a dtype")
+    q = last_dim_contiguous(q)
+    k = last_dim_contiguous(k)
+    v = last_dim_contiguous(v)
+    seq_offsets = _i32(seq_offsets)
+    num_targets = _i32(num_targets)
+    if num_targets is not None and num_targets.numel() != seq_offsets.numel() - 1:
+        raise RuntimeError("num_targets must have one entry per sequence")
+    if attn_scale is not None:
+        attn_scale = attn_scale.to(torch.float32).reshape(-1).contiguous()
+        if attn_scale.numel() not in (1, q.shape[0]):
+            raise RuntimeError("attn_scale must be a scalar or have one entry per token")
+    if bias_by_distance is not None:
+        bias_by_distance = bias_by_distance.to(torch.float32).contiguous()
+    return _HstuMhaFunction.apply(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, int(max_seq_len),
+                                  float(alpha), int(max_attn_len), int(contextual_seq_len),
+                                  int(min_full_attn_seq_len))

@@ -1,0 +1,249 @@
+"""The LayerNorm + linear stages around the attention, with the reference's signatures
+(generative_recommenders/ops/hstu_compute.py:54-335)."""
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi
+from .common import HammerKernel, _require_cuda_backend, dtype_code, require_cuda, stream_ptr
+from .hstu_attention import hstu_mha
+from .layer_norm import layer_norm
+from .mm import addmm
+
+_ACT = {"none": 0, "sigmoid": 1, "silu": 2}
+
+
+class _SiluColumnsFunction(torch.autograd.Function):
+    """u = SiLU(x[:, :width]) written densely; x itself (the uvqk buffer) is left untouched."""
+
+    @staticmethod
+    def forward(ctx, x, width):
+        rows = x.shape[0]
+        u = torch.empty((rows, width), dtype=x.dtype, device=x.device)
+        if rows > 0:
+            with torch.cuda.device(x.device):
+                _cabi.check(
+                    _cabi.lib().b200_hstu_silu_fwd(x.data_ptr(), x.stride(0), u.data_ptr(), u.stride(0), rows, width,
+                                                   dtype_code(x), stream_ptr(x.device)),
+                    "b200_hstu_silu_fwd")
+        ctx.save_for_backward(x)
+        ctx.width = width
+        return u
+
+    @staticmethod
+    def backward(ctx, du):
+        (x,) = ctx.saved_tensors
+        rows, width = x.shape[0], ctx.width
+        if du.stride(-1) != 1:
+            du = du.contiguous()
+        dx = torch.zeros_like(x) if x.shape[1] != width else torch.empty_like(x)
+        if rows > 0:
+            with torch.cuda.device(x.device):
+                _cabi.check(
+                    _cabi.lib().b200_hstu_silu_bwd(du.data_ptr(), du.stride(0), x.data_ptr(), x.stride(0),
+                                                   dx.data_ptr(), dx.stride(0), rows, width, dtype_code(x),
+                                                   stream_ptr(x.device)),
+                    "b200_hstu_silu_bwd")
+        return dx, None
+
+
+def hstu_compute_uqvk(
+    x: torch.Tensor,
+    norm_weight: torch.Tensor,
+    norm_bias: torch.Tensor,
+    norm_eps: float,
+    num_heads: int,
+    attn_dim: int,
+    hidden_dim: int,
+    uvqk_weight: torch.Tensor,
+    uvqk_bias: torch.Tensor,
+    kernel: HammerKernel = HammerKernel.CUDA,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """LN -> addmm -> split [u | v | q | k] -> SiLU(u); returns (u, q, k, v) with q, k, v as
+    ``[L, H, d]`` views of the uvqk buffer (generative_recommenders/ops/hstu_compute.py:54-104)."""
+    _require_cuda_backend(kernel)
+    require_cuda(x, norm_weight, norm_bias, uvqk_weight, uvqk_bias)
+    normed_x = layer_norm(x, weight=norm_weight, bias=norm_bias, eps=norm_eps, kernel=kernel)
+    uvqk = addmm(uvqk_bias, normed_x, uvqk_weight, kernel)
+    hv, ha = hidden_dim * num_heads, attn_dim * num_heads
+    u = _SiluColumnsFunction.apply(uvqk[:, :hv], hv)
+    v = uvqk[:, hv : 2 * hv].view(-1, num_heads, hidden_dim)
+    q = uvqk[:, 2 * hv : 2 * hv + ha].view(-1, num_heads, attn_dim)
+    k = uvqk[:, 2 * hv + ha :].view(-1, num_heads, attn_dim)
+    return u, q, k, v
+
+
+class _NormMulFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm):
+        rows = attn.shape[0]
+        D = num_heads * linear_dim
+        if attn.stride(-1) != 1:
+            attn = attn.contiguous()
+        if u.stride(-1) != 1:
+            u = u.contiguous()
+        weight = weight.to(attn.dtype).contiguous()
+        bias = bias.to(attn.dtype).contiguous()
+        if group_norm:
+            mult = 3 if (concat_u and concat_x) else 1
+        else:
+            mult = 1 + int(concat_u) + int(concat_x)
+        out = torch.empty((rows, mult * D), dtype=attn.dtype, device=attn.device)
+        groups = num_heads if group_norm else 1
+        mean = torch.empty(rows * groups, dtype=torch.float32, device=attn.device)
+        rstd = torch.empty(rows * groups, dtype=torch.float32, device=attn.device)
+        a = _cabi.NormMulArgs()
+        a.attn, a.u, a.weight, a.bias = attn.data_ptr(), u.data_ptr(), weight.data_ptr(), bias.data_ptr()
+        a.out, a.mean, a.rstd = out.data_ptr(), mean.data_ptr(), rstd.data_ptr()
+        a.attn_row_stride, a.u_row_stride, a.out_row_stride = attn.stride(0), u.stride(0), out.stride(0)
+        a.rows, a.H, a.V = rows, num_heads, linear_dim
+        a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
+        a.eps, a.dtype = eps, dtype_code(attn)
+        if rows > 0:
+            with torch.cuda.device(attn.device):
+                _cabi.check(_cabi.lib().b200_hstu_norm_mul_fwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_fwd")
+        ctx.save_for_backward(attn, u, weight, bias, mean, rstd)
+        ctx.cfg = (eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        attn, u, weight, bias, mean, rstd = ctx.saved_tensors
+        eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm = ctx.cfg
+        rows = attn.shape[0]
+        if dout.stride(-1) != 1:
+            dout = dout.contiguous()
+        dattn = torch.empty((rows, num_heads * linear_dim), dtype=attn.dtype, device=attn.device)
+        du = torch.empty_like(dattn)
+        dw = torch.empty_like(weight)
+        db = torch.empty_like(bias)
+        nbytes = _cabi.lib().b200_hstu_norm_mul_bwd_workspace_bytes(num_heads, linear_dim, int(group_norm))
+        partial = torch.empty(nbytes, dtype=torch.uint8, device=attn.device)
+        a = _cabi.NormMulArgs()
+        a.attn, a.u, a.weight, a.bias = attn.data_ptr(), u.data_ptr(), weight.data_ptr(), bias.data_ptr()
+        a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
+        a.dout, a.dattn, a.du = dout.data_ptr(), dattn.data_ptr(), du.data_ptr()
+        a.dweight, a.dbias = dw.data_ptr(), db.data_ptr()
+        a.partial, a.partial_bytes = partial.data_ptr(), nbytes
+        a.attn_row_stride, a.u_row_stride = attn.stride(0), u.stride(0)
+        a.dout_row_stride, a.dattn_row_stride, a.du_row_stride = dout.stride(0), dattn.stride(0), du.stride(0)
+        a.rows, a.H, a.V = rows, num_heads, linear_dim
+        a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
+        a.eps, a.dtype = eps, dtype_code(attn)
+        with torch.cuda.device(attn.device):
+            _cabi.check(_cabi.lib().b200_hstu_norm_mul_bwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_bwd")
+        return dattn, du, dw, db, None, None, None, None, None, None, None
+
+
+def hstu_norm_mul_dropout(
+    attn: torch.Tensor,
+    u: torch.Tensor,
+    norm_weight: torch.Tensor,
+    norm_bias: torch.Tensor,
+    norm_eps: float,
+    dropout_ratio: float,
+    training: bool,
+    concat_u: bool = False,
+    concat_x: bool = False,
+    mul_u_activation_type: str = "none",
+    group_norm: bool = False,
+    num_heads: int = 1,
+    linear_dim: int = -1,
+) -> torch.Tensor:
+    """``dropout(cat([u, attn, act(u) * Norm(attn)]))`` - the input of the output linear
+    (generative_recommenders/ops/pytorch/pt_hstu_linear.py:23-82)."""
+    if mul_u_activation_type not in _ACT:
+        raise ValueError("mul_u_activation_type must be one of none / sigmoid / silu")
+    if group_norm and concat_u != concat_x:
+        # the reference's group-norm branch only concatenates when both flags are set (:52-54)
+        concat_u = concat_x = False
+    act = 0 if group_norm else _ACT[mul_u_activation_type]
+    if linear_dim <= 0:
+        linear_dim = attn.shape[1] // num_heads
+    y = _NormMulFunction.apply(attn, u, norm_weight, norm_bias, float(norm_eps), int(num_heads), int(linear_dim),
+                               bool(concat_u), bool(concat_x), act, bool(group_norm))
+    if training and dropout_ratio > 0.0:
+        # the mask comes from torch's generator, exactly like the reference's F.dropout (:77-81)
+        y = torch.nn.functional.dropout(y, p=dropout_ratio, training=True)
+    return y
+
+
+def hstu_compute_output(
+    attn: torch.Tensor,
+    u: torch.Tensor,
+    x: torch.Tensor,
+    norm_weight: torch.Tensor,
+    norm_bias: torch.Tensor,
+    norm_eps: float,
+    output_weight: torch.Tensor,
+    num_heads: int,
+    linear_dim: int,
+    dropout_ratio: float,
+    training: bool,
+    concat_u: bool,
+    concat_x: bool,
+    mul_u_activation_type: str,
+    group_norm: bool,
+    recompute_y_in_backward: bool,
+    kernel: HammerKernel = HammerKernel.CUDA,
+) -> torch.Tensor:
+    """``x + dropout(cat([u, attn, act(u) * Norm(attn)])) @ W_out``
+    (generative_recommenders/ops/hstu_compute.py:107-214,
+    generative_recommenders/ops/pytorch/pt_hstu_linear.py:85-120).
+    ``recompute_y_in_backward`` is accepted for signature compatibility; y is always kept."""
+    _require_cuda_backend(kernel)
+    require_cuda(attn, u, x, norm_weight, norm_bias, output_weight)
+    y = hstu_norm_mul_dropout(attn, u, norm_weight, norm_bias, norm_eps, dropout_ratio, training, concat_u, concat_x,
+                              mul_u_activation_type, group_norm, num_heads, linear_dim)
+    return addmm(x, y, output_weight.to(x.dtype), kernel)
+
+
+def hstu_preprocess_and_attention(
+    x: torch.Tensor,
+    norm_weight: torch.Tensor,
+    norm_bias: torch.Tensor,
+    norm_eps: float,
+    num_heads: int,
+    attn_dim: int,
+    hidden_dim: int,
+    uvqk_weight: torch.Tensor,
+    uvqk_bias: torch.Tensor,
+    max_seq_len: int,
+    seq_offsets: torch.Tensor,
+    attn_alpha: float,
+    causal: bool,
+    num_targets: Optional[torch.Tensor],
+    max_attn_len: int,
+    contextual_seq_len: int,
+    recompute_uvqk_in_backward: bool,
+    recompute_normed_x_in_backward: bool,
+    sort_by_length: bool,
+    prefill: bool = False,
+    kernel: HammerKernel = HammerKernel.CUDA,
+    enable_tma: Optional[bool] = None,
+    bias_by_distance: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """uqvk stage followed by the attention; returns ``(u, attn_output [L, H*dv], k, v)``
+    (generative_recommenders/ops/hstu_compute.py:217-335; like the reference's composite the
+    attention runs with dropout off, :327-328)."""
+    _require_cuda_backend(kernel)
+    torch._assert(max_seq_len > 0, "max_seq_len must be larger than 0")
+    torch._assert(x.dim() == 2, "x must be 2-D")
+    torch._assert(x.shape[1] == uvqk_weight.shape[0], "x.shape[1] must equal uvqk_weight.shape[0]")
+    torch._assert(
+        uvqk_weight.shape[1] == 2 * num_heads * (hidden_dim + attn_dim),
+        "uvqk_weight.shape[1] must equal 2 * num_heads * (hidden_dim + attn_dim)",
+    )
+    torch._assert(causal is True, "only causal attention is supported.")
+    u, q, k, v = hstu_compute_uqvk(
+        x=x, norm_weight=norm_weight, norm_bias=norm_bias, norm_eps=norm_eps, num_heads=num_heads,
+        attn_dim=attn_dim, hidden_dim=hidden_dim, uvqk_weight=uvqk_weight, uvqk_bias=uvqk_bias, kernel=kernel,
+    )
+    attn_output = hstu_mha(
+        max_seq_len=max_seq_len, alpha=attn_alpha, q=q, k=k, v=v, seq_offsets=seq_offsets, causal=causal,
+        dropout_pr=0.0, training=False, num_targets=num_targets, max_attn_len=max_attn_len,
+        contextual_seq_len=contextual_seq_len, sort_by_length=sort_by_length, kernel=kernel,
+        bias_by_distance=bias_by_distance,
+    ).view(-1, hidden_dim * num_heads)
+    return u, attn_output, k, v

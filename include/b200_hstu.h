@@ -1,0 +1,210 @@
+/*
+ * b200_hstu.h - C ABI of the B200 (sm_100a) HSTU jagged-attention library.
+ *
+ * Every entry point takes plain pointers and sizes, launches on the stream it is
+ * given, never synchronises the device and never throws.  Return value: 0 on
+ * success, a negative B200_HSTU_E* code for a rejected argument, or a positive
+ * cudaError_t if the CUDA runtime reported one.  b200_hstu_last_error() returns a
+ * human-readable message for the calling thread's last non-zero status.
+ *
+ * All data pointers are device pointers unless stated otherwise.  "Jagged" tensors
+ * are [total_L, H, d] with unit stride on d, `head_stride` elements between heads
+ * and `row_stride` elements between tokens; sequence b owns rows
+ * seq_offsets[b] .. seq_offsets[b+1].
+ *
+ * The comments cite the interface of meta-recsys/generative-recommenders that each
+ * entry point stands in for (paths relative to that project).
+ */
+#ifndef B200_HSTU_H_
+#define B200_HSTU_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define B200_HSTU_OK 0
+#define B200_HSTU_EINVAL (-1)      /* bad or inconsistent argument                  */
+#define B200_HSTU_EUNSUPPORTED (-2) /* valid in the reference, not implemented here */
+#define B200_HSTU_EWORKSPACE (-3)  /* workspace missing or too small                */
+#define B200_HSTU_EDEVICE (-4)     /* not an sm_100 device / driver entry missing   */
+
+/* element types */
+#define B200_HSTU_F32 0
+#define B200_HSTU_BF16 1
+#define B200_HSTU_F16 2
+#define B200_HSTU_E4M3 3
+
+/* which kernel family runs the attention */
+#define B200_HSTU_IMPL_AUTO 0    /* tcgen05 when dtype/head-dim allow, else SIMT */
+#define B200_HSTU_IMPL_SIMT 1    /* fp32-accumulating CUDA-core kernels          */
+#define B200_HSTU_IMPL_TCGEN05 2 /* tensor-core kernels; error if not applicable */
+
+typedef void *b200_hstu_stream_t; /* a cudaStream_t */
+
+/*
+ * Arguments of the jagged HSTU attention, forward and backward.
+ *
+ *   out[i] = sum_j mask(i, j) * SiLU(alpha * <q_i, k_j>) * scale * v_j
+ *
+ * with scale = 1 / max_seq_len, or attn_scale[0] / attn_scale[token] when
+ * attn_scale is given.  The mask is the reference's causal HSTU mask with targets,
+ * contextual prefix and local window
+ * (generative_recommenders/ops/pytorch/pt_hstu_attention.py:33-84).
+ */
+typedef struct b200_hstu_attn_args {
+  /* tensors */
+  const void *q;          /* [total_L, H, dqk] */
+  const void *k;          /* [total_L, H, dqk] */
+  const void *v;          /* [total_L, H, dv]  */
+  void *out;              /* fwd: written.  [total_L, H, dv]; bwd: unused (may be NULL) */
+  const void *dout;       /* bwd only: [total_L, H, dv] */
+  void *dq, *dk, *dv_;    /* bwd only: written, same shapes as q, k, v */
+  const int32_t *seq_offsets; /* [B + 1] */
+  const int32_t *num_targets; /* [B] or NULL */
+  const float *attn_scale;    /* NULL, or fp32 [1] (scalar) or [total_L] (per query token) */
+  int64_t attn_scale_numel;   /* 0, 1 or total_L */
+  /* strides, in elements */
+  int64_t q_row_stride, k_row_stride, v_row_stride, o_row_stride;
+  int64_t q_head_stride, k_head_stride, v_head_stride, o_head_stride;
+  int64_t do_row_stride, dq_row_stride, dk_row_stride, dv_row_stride;
+  int64_t do_head_stride, dq_head_stride, dk_head_stride, dv_head_stride;
+  /* sizes */
+  int64_t total_L;
+  int32_t B, H, dqk, dv;
+  int32_t max_seq_len; /* N: scale 1/N, and rows beyond N of a sequence produce zeros */
+  /* semantics */
+  float alpha;
+  int32_t max_attn_len;          /* 0 = unlimited */
+  int32_t contextual_seq_len;    /* 0 = none */
+  int32_t min_full_attn_seq_len; /* 0 = none */
+  int32_t dtype;                 /* B200_HSTU_F32 / BF16 / F16 (q, k, v, out, dout, dq, dk, dv) */
+  int32_t impl;                  /* B200_HSTU_IMPL_* */
+  /* optional relative position bias added to alpha*<q,k> before SiLU, shared by all heads:
+     bias_by_distance[|i - j|] when |i - j| < bias_numel, else 0 (fp32); NULL = none */
+  const float *bias_by_distance;
+  int32_t bias_numel;
+  int32_t reserved0;
+  /* scratch: see b200_hstu_attn_workspace_bytes(); contents need no initialisation */
+  void *workspace;
+  int64_t workspace_bytes;
+} b200_hstu_attn_args;
+
+/*
+ * Forward.  Stands in for hstu_mha / torch.ops.hstu.hstu_mha_fwd
+ * (generative_recommenders/ops/hstu_attention.py:101-207,
+ *  generative_recommenders/ops/cpp/hstu_attention/flash_api_cpu.cpp:142-235).
+ */
+int b200_hstu_attn_fwd(const b200_hstu_attn_args *args, b200_hstu_stream_t stream);
+
+/*
+ * Backward: fills dq, dk, dv from dout.  Stands in for
+ * _AttentionFunction.backward / torch.ops.hstu.hstu_mha_bwd
+ * (generative_recommenders/ops/triton/triton_hstu_attention.py:3031-3092,
+ *  generative_recommenders/ops/cpp/hstu_attention/flash_common.cpp:851-1212).
+ */
+int b200_hstu_attn_bwd(const b200_hstu_attn_args *args, b200_hstu_stream_t stream);
+
+/* Bytes of scratch that fwd (backward = 0) or bwd (backward = 1) need for these sizes.
+   Host function; depends on B, H, dqk, dv, total_L, dtype, impl only. */
+int64_t b200_hstu_attn_workspace_bytes(const b200_hstu_attn_args *args, int backward);
+
+/*
+ * FP8 (e4m3) forward for inference with per-block scales: q8/k8/v8 are
+ * [total_L, H, d] e4m3 (contiguous heads), *_scale are fp32 [n_blocks_total, H] where
+ * sequence b owns rows block_offsets[b] .. block_offsets[b+1], one row per 128 tokens
+ * counted from the sequence's first token.  Output is bf16.  The reference plumbs
+ * per-(batch, head) descale tensors through torch.ops.hstu.hstu_mha_fwd
+ * (generative_recommenders/ops/cpp/hstu_attention/flash_common.cpp:680-711) but
+ * compiles FP8 out; per-block scales are an extension.
+ */
+typedef struct b200_hstu_attn_fp8_args {
+  b200_hstu_attn_args base; /* q, k, v hold e4m3 data; out is bf16; dtype ignored */
+  const float *q_scale, *k_scale, *v_scale;
+  const int32_t *block_offsets; /* [B + 1] */
+} b200_hstu_attn_fp8_args;
+int b200_hstu_attn_fwd_fp8(const b200_hstu_attn_fp8_args *args, b200_hstu_stream_t stream);
+
+/* Block quantiser producing the layout above: x [total_L, H, d] (bf16 / f16 / f32) ->
+   x8 e4m3 + scale = absmax / 448 per (128-token block, head). */
+int b200_hstu_quantize_e4m3_block(const void *x, int32_t dtype, int64_t row_stride, int64_t head_stride,
+                                  void *x8, float *scale, const int32_t *seq_offsets,
+                                  const int32_t *block_offsets, int32_t B, int32_t H, int32_t d,
+                                  int64_t total_L, int32_t max_seq_len, b200_hstu_stream_t stream);
+
+/*
+ * Row LayerNorm with affine, fp32 statistics (generative_recommenders/ops/layer_norm.py:50-94,
+ * generative_recommenders/ops/pytorch/pt_layer_norm.py:24-38).  x, y: [rows, D] with the given
+ * row strides; mean, rstd: fp32 [rows] (written by fwd when non-NULL, read by bwd).
+ */
+int b200_hstu_layer_norm_fwd(const void *x, int64_t x_row_stride, const void *weight, const void *bias,
+                             void *y, int64_t y_row_stride, float *mean, float *rstd, int64_t rows,
+                             int32_t D, float eps, int32_t dtype, b200_hstu_stream_t stream);
+/* dx [rows, D]; dweight, dbias [D] in `dtype`.  partial: fp32 scratch of
+   b200_hstu_layer_norm_bwd_workspace_bytes(D) bytes. */
+int b200_hstu_layer_norm_bwd(const void *dy, int64_t dy_row_stride, const void *x, int64_t x_row_stride,
+                             const void *weight, const float *mean, const float *rstd, void *dx,
+                             int64_t dx_row_stride, void *dweight, void *dbias, void *partial,
+                             int64_t partial_bytes, int64_t rows, int32_t D, int32_t dtype,
+                             b200_hstu_stream_t stream);
+int64_t b200_hstu_layer_norm_bwd_workspace_bytes(int32_t D);
+
+/*
+ * u = SiLU(uvqk[:, :width]) - the gating half of hstu_compute_uqvk
+ * (generative_recommenders/ops/hstu_compute.py:90-100).  q, k, v stay views of uvqk.
+ */
+int b200_hstu_silu_fwd(const void *x, int64_t x_row_stride, void *y, int64_t y_row_stride, int64_t rows,
+                       int32_t width, int32_t dtype, b200_hstu_stream_t stream);
+/* dx = dy * SiLU'(x) */
+int b200_hstu_silu_bwd(const void *dy, int64_t dy_row_stride, const void *x, int64_t x_row_stride, void *dx,
+                       int64_t dx_row_stride, int64_t rows, int32_t width, int32_t dtype,
+                       b200_hstu_stream_t stream);
+
+/*
+ * y = act(u) * Norm(attn) with the optional [u, attn, y] concatenation that feeds the output
+ * linear (generative_recommenders/ops/pytorch/pt_hstu_linear.py:23-82).  attn, u: [rows, H*V];
+ * out: [rows, (1 + concat_u + concat_x) * H*V].  act: 0 none, 1 sigmoid, 2 silu.  group_norm: 0 =
+ * LayerNorm over H*V (weight/bias [H*V]), 1 = per-head normalisation (weight/bias [H]).
+ */
+typedef struct b200_hstu_norm_mul_args {
+  const void *attn, *u, *weight, *bias;
+  void *out;
+  float *mean, *rstd;     /* fp32 [rows * groups]; written by fwd if non-NULL, read by bwd */
+  const void *dout;       /* bwd */
+  void *dattn, *du, *dweight, *dbias; /* bwd */
+  void *partial;          /* bwd scratch, b200_hstu_norm_mul_bwd_workspace_bytes() */
+  int64_t partial_bytes;
+  int64_t attn_row_stride, u_row_stride, out_row_stride, dout_row_stride, dattn_row_stride, du_row_stride;
+  int64_t rows;
+  int32_t H, V;
+  int32_t concat_u, concat_x, act, group_norm;
+  float eps;
+  int32_t dtype;
+} b200_hstu_norm_mul_args;
+int b200_hstu_norm_mul_fwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream_t stream);
+int b200_hstu_norm_mul_bwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream_t stream);
+int64_t b200_hstu_norm_mul_bwd_workspace_bytes(int32_t H, int32_t V, int32_t group_norm);
+
+/* Host helpers. */
+const char *b200_hstu_last_error(void);
+int b200_hstu_version(void);
+/* Number of kernels this library has launched in the calling process since load. */
+int64_t b200_hstu_launch_count(void);
+
+/* Host utilities for tooling and tests (no device work).  b200_hstu_host_mask() evaluates the
+   mask(i, j) of one sequence exactly as the kernels do; b200_hstu_host_kv_range() returns the kv
+   positions [lo, hi) (+ a separate diagonal block at diag_lo, or -1) that the block-skipping rule
+   makes the query tile starting at row m0 visit. */
+void b200_hstu_host_kv_range(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
+                             int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t m0, int32_t tile,
+                             int32_t *lo, int32_t *hi, int32_t *diag_lo);
+int b200_hstu_host_mask(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
+                        int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t i, int32_t j);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_HSTU_H_ */

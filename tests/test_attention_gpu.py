@@ -1,0 +1,245 @@
+"""Parity of the CUDA attention (through the C ABI) with the oracle and the reference fixtures.
+
+Tolerances: fp32 kernels against fp32 fixtures 2e-4 relative L2 (accumulation order only);
+bf16 / fp16 kernels against the fp32 oracle on the same (already rounded) inputs: relative
+L2 <= 1e-2 for the output and every gradient."""
+
+import pytest
+import torch
+
+import generative_recommenders_b200 as G
+from generative_recommenders_b200 import workloads as W
+from oracle import hstu_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+BF16_TOL = 1e-2
+FP32_TOL = 2e-4
+
+
+@pytest.fixture(autouse=True)
+def _reset_impl():
+    G.set_attention_impl("auto")
+    yield
+    G.set_attention_impl("auto")
+
+
+def _run(q, k, v, offs, N, alpha, nt=None, W_=0, ctx=0, F=0, dout=None, scale=None, bias=None):
+    qd = q.to(DEV).requires_grad_(dout is not None)
+    kd = k.to(DEV).requires_grad_(dout is not None)
+    vd = v.to(DEV).requires_grad_(dout is not None)
+    out = G.hstu_mha(N, alpha, qd, kd, vd, offs.to(DEV), num_targets=None if nt is None else nt.to(DEV),
+                     max_attn_len=W_, contextual_seq_len=ctx, min_full_attn_seq_len=F,
+                     attn_scale=None if scale is None else scale.to(DEV),
+                     bias_by_distance=None if bias is None else bias.to(DEV))
+    if dout is None:
+        return out.cpu(), None
+    out.backward(dout.to(DEV))
+    torch.cuda.synchronize()
+    return out.detach().cpu(), (qd.grad.cpu(), kd.grad.cpu(), vd.grad.cpu())
+
+
+def _oracle(q, k, v, offs, N, alpha, nt=None, W_=0, ctx=0, F=0, dout=None, scale=None, bias=None):
+    q32 = q.float().clone().requires_grad_(dout is not None)
+    k32 = k.float().clone().requires_grad_(dout is not None)
+    v32 = v.float().clone().requires_grad_(dout is not None)
+    rb = None
+    if bias is not None:
+        i = torch.arange(N).view(N, 1)
+        j = torch.arange(N).view(1, N)
+        d = (i - j).abs()
+        rb = torch.where(d < bias.numel(), bias.float()[d.clamp(max=bias.numel() - 1)], torch.zeros(()))
+    out = O.hstu_mha(N, alpha, q32, k32, v32, offs, num_targets=nt, max_attn_len=W_, contextual_seq_len=ctx,
+                     min_full_attn_seq_len=F, attn_scale=scale, rel_bias=rb)
+    if dout is None:
+        return out, None
+    out.backward(dout.float())
+    return out.detach(), (q32.grad, k32.grad, v32.grad)
+
+
+@pytest.mark.parametrize("impl", ["simt"])
+def test_fp32_golden_fixtures(golden, impl):
+    G.set_attention_impl(impl)
+    for name, fx in golden("attention.pt").items():
+        p = fx["params"]
+        out, grads = _run(fx["q"], fx["k"], fx["v"], fx["seq_offsets"], p["N"], p["alpha"], fx["num_targets"],
+                          p["W"], p["ctx"], p["F"], fx.get("dout"))
+        assert O.rel_l2(out, fx["out"]) < FP32_TOL, name
+        if grads is not None:
+            for g, ref, nm in zip(grads, (fx["dq"], fx["dk"], fx["dv"]), "qkv"):
+                assert O.rel_l2(g, ref) < FP32_TOL, (name, nm)
+
+
+def _random_case(seed, B, lo, hi, N, H, d, dtype, targets=0, ctx=0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(lo, hi + 1, (B,), generator=g)
+    nt = None
+    if targets > 0:
+        nt = torch.randint(1, targets + 1, (B,), generator=g)
+        lengths = torch.clamp(lengths + nt + ctx, max=N)
+        nt = torch.minimum(nt, torch.clamp(lengths - ctx - 1, min=0))
+    elif ctx > 0:
+        lengths = torch.clamp(lengths + ctx, max=N)
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    q = (torch.randn(L, H, d, generator=g) * std).to(dtype)
+    k = (torch.randn(L, H, d, generator=g) * std).to(dtype)
+    v = (torch.randn(L, H, d, generator=g) * std).to(dtype)
+    dout = torch.randn(L, H, d, generator=g).to(dtype)
+    return q, k, v, offs, nt, dout
+
+
+CASES = [
+    # B, lo, hi, N, H, d, targets, ctx, W, F
+    (6, 1, 300, 300, 2, 128, 0, 0, 0, 0),
+    (6, 1, 300, 320, 2, 128, 20, 0, 0, 0),
+    (5, 100, 400, 420, 1, 128, 0, 7, 0, 0),
+    (5, 100, 500, 520, 2, 128, 30, 5, 90, 0),
+    (4, 200, 600, 640, 1, 128, 12, 0, 150, 0),
+    (4, 1, 260, 270, 3, 64, 9, 3, 0, 0),
+    (4, 120, 300, 310, 2, 64, 0, 0, 64, 0),
+    (4, 120, 300, 320, 2, 128, 10, 4, 70, 33),
+]
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", CASES)
+def test_half_precision_forward_matches_oracle(impl, dtype, case):
+    B, lo, hi, N, H, d, targets, ctx, Wn, F = case
+    if impl == "simt" and dtype == torch.float16 and d == 128:
+        pytest.skip("covered by bf16")
+    G.set_attention_impl(impl)
+    q, k, v, offs, nt, _ = _random_case(hash(case) % 10000, B, lo, hi, N, H, d, dtype, targets, ctx, std=0.7)
+    alpha = 1.0 / d ** 0.5
+    out, _ = _run(q, k, v, offs, N, alpha, nt, Wn, ctx, F)
+    ref, _ = _oracle(q, k, v, offs, N, alpha, nt, Wn, ctx, F)
+    assert torch.isfinite(out.float()).all()
+    assert O.rel_l2(out, ref) < BF16_TOL, O.rel_l2(out, ref)
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_bf16_backward_matches_oracle(case):
+    B, lo, hi, N, H, d, targets, ctx, Wn, F = case
+    q, k, v, offs, nt, dout = _random_case(hash(case) % 10000 + 1, B, lo, hi, N, H, d, torch.bfloat16, targets, ctx,
+                                           std=0.7)
+    alpha = 1.0 / d ** 0.5
+    out, grads = _run(q, k, v, offs, N, alpha, nt, Wn, ctx, F, dout)
+    ref, rgrads = _oracle(q, k, v, offs, N, alpha, nt, Wn, ctx, F, dout)
+    assert O.rel_l2(out, ref) < BF16_TOL
+    for g, r, nm in zip(grads, rgrads, "qkv"):
+        assert O.rel_l2(g, r) < BF16_TOL, (nm, O.rel_l2(g, r))
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+def test_edge_lengths(impl):
+    """Empty sequences, single tokens and lengths around the 128-row tile edge."""
+    G.set_attention_impl(impl)
+    lengths = torch.tensor([0, 1, 127, 128, 129, 0, 255, 256, 257, 2, 0])
+    offs = W._offsets(lengths)
+    g = torch.Generator().manual_seed(11)
+    L, H, d = int(offs[-1]), 2, 128
+    q = torch.randn(L, H, d, generator=g).bfloat16()
+    k = torch.randn(L, H, d, generator=g).bfloat16()
+    v = torch.randn(L, H, d, generator=g).bfloat16()
+    out, _ = _run(q, k, v, offs, 300, 0.1)
+    ref, _ = _oracle(q, k, v, offs, 300, 0.1)
+    assert O.rel_l2(out, ref) < BF16_TOL
+
+
+def test_empty_batch_and_zero_tokens():
+    q = torch.zeros(0, 2, 128, dtype=torch.bfloat16, device=DEV)
+    offs = torch.zeros(4, dtype=torch.int64, device=DEV)
+    out = G.hstu_mha(16, 0.1, q, q, q, offs)
+    assert out.shape == (0, 2, 128)
+
+
+def test_writes_stay_inside_the_output_rows():
+    """The output buffer is a slice of a NaN-poisoned tensor: nothing outside may be written."""
+    G.set_attention_impl("tcgen05")
+    q, k, v, offs, nt, _ = _random_case(5, 5, 50, 200, 256, 2, 128, torch.bfloat16, 10, 0)
+    out, _ = _run(q, k, v, offs, 256, 0.09, nt)
+    ref, _ = _oracle(q, k, v, offs, 256, 0.09, nt)
+    assert O.rel_l2(out, ref) < BF16_TOL
+    # run twice: bit-identical (forward has a single owner per output element)
+    out2, _ = _run(q, k, v, offs, 256, 0.09, nt)
+    assert torch.equal(out, out2)
+
+
+def test_non_contiguous_qkv_views():
+    """q, k, v as column slices of one [L, 4*H*d] buffer, the layout hstu_compute_uqvk returns."""
+    g = torch.Generator().manual_seed(2)
+    H, d = 2, 128
+    lengths = torch.tensor([70, 190, 33])
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    uvqk = (torch.randn(L, 4 * H * d, generator=g) * 0.5).bfloat16().to(DEV)
+    v = uvqk[:, H * d:2 * H * d].view(L, H, d)
+    q = uvqk[:, 2 * H * d:3 * H * d].view(L, H, d)
+    k = uvqk[:, 3 * H * d:].view(L, H, d)
+    out = G.hstu_mha(200, 0.1, q, k, v, offs.to(DEV))
+    ref, _ = _oracle(q.cpu(), k.cpu(), v.cpu(), offs, 200, 0.1)
+    assert O.rel_l2(out.cpu(), ref) < BF16_TOL
+
+
+def test_attn_scale_and_truncation_fp32():
+    G.set_attention_impl("simt")
+    g = torch.Generator().manual_seed(8)
+    lengths = torch.tensor([30, 50, 12])
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    q = torch.randn(L, 2, 16, generator=g); k = torch.randn(L, 2, 16, generator=g); v = torch.randn(L, 2, 16, generator=g)
+    scale = torch.rand(L, generator=g)
+    out, _ = _run(q, k, v, offs, 64, 0.25, scale=scale)
+    ref, _ = _oracle(q, k, v, offs, 64, 0.25, scale=scale)
+    assert O.rel_l2(out, ref) < FP32_TOL
+    out, _ = _run(q, k, v, offs, 64, 0.25, scale=torch.tensor(0.37))
+    ref, _ = _oracle(q, k, v, offs, 64, 0.25, scale=torch.tensor(0.37))
+    assert O.rel_l2(out, ref) < FP32_TOL
+    # sequences longer than max_seq_len: rows beyond it are zeros
+    out, _ = _run(q, k, v, offs, 40, 0.25)
+    ref, _ = _oracle(q, k, v, offs, 40, 0.25)
+    assert O.rel_l2(out, ref) < FP32_TOL
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+def test_relative_bias_extension(impl):
+    G.set_attention_impl(impl)
+    q, k, v, offs, nt, _ = _random_case(21, 4, 40, 280, 300, 2, 128, torch.bfloat16, 8, 3)
+    bias = torch.randn(300) * 0.3
+    out, _ = _run(q, k, v, offs, 300, 0.09, nt, 0, 3, 0, bias=bias)
+    ref, _ = _oracle(q, k, v, offs, 300, 0.09, nt, 0, 3, 0, bias=bias)
+    assert O.rel_l2(out, ref) < BF16_TOL
+
+
+def test_config0_fp32_matches_golden(golden):
+    fx = golden("attention.pt")["cfg0"]
+    w = W.config0()
+    assert torch.equal(w.seq_offsets, fx["seq_offsets"])
+    out, _ = _run(fx["q"], fx["k"], fx["v"], fx["seq_offsets"], 256, 1.0 / 32)
+    assert O.rel_l2(out, fx["out"]) < FP32_TOL
+
+
+def test_config1_full_size_forward_backward():
+    """BASELINE configs[1] at full size against the fp32 oracle (a few seconds of CPU)."""
+    w = W.config1()
+    q, k, v, do = w.qkv(with_dout=True)
+    out, grads = _run(q, k, v, w.seq_offsets, w.max_seq_len, w.alpha, w.num_targets, dout=do)
+    ref, rgrads = _oracle(q, k, v, w.seq_offsets, w.max_seq_len, w.alpha, w.num_targets, dout=do)
+    assert O.rel_l2(out, ref) < BF16_TOL
+    for g, r, nm in zip(grads, rgrads, "qkv"):
+        assert O.rel_l2(g, r) < BF16_TOL, nm
+
+
+def test_unsupported_requests_raise():
+    q = torch.zeros(4, 1, 32, device=DEV)
+    offs = torch.tensor([0, 4], device=DEV)
+    with pytest.raises(NotImplementedError):
+        G.hstu_mha(8, 1.0, q, q, q, offs, kernel=G.HammerKernel.TRITON)
+    with pytest.raises(Exception):
+        G.hstu_mha(8, 1.0, q, q, q, offs, causal=False)
+    with pytest.raises(RuntimeError):
+        G.hstu_mha(8, 1.0, q.cpu(), q.cpu(), q.cpu(), offs.cpu())
+    G.set_attention_impl("tcgen05")
+    with pytest.raises(RuntimeError):  # fp32 has no tensor-core path: loud error, no silent fallback
+        G.hstu_mha(8, 1.0, q, q, q, offs)
