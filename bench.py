@@ -1,0 +1,368 @@
+"""Benchmark of the HSTU jagged-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload config1|config3]
+
+A step is one forward + backward of ``hstu_mha`` over one synthetic batch with the shapes of the
+benchmark configuration (bf16, B=64 sequences per GPU, L ~ U{128..1024}, N=1024, H=4, d=128,
+targets ~ U{1..32}).  With N > 1 (launched by torchrun, one rank per GPU) the batch has 64*N
+sequences split over the ranks by token count; there is no collective on the data path, the
+only collectives are the barrier / max-reduction used for timing.
+
+One JSON line is printed by rank 0.  ``value`` is whole-job TFLOP/s of forward + backward counted
+with the nominal causal formula 3.5 * 4*H*d*sum(L^2)/2, measured with CUDA events with the
+inputs resident in HBM.  ``e2e`` is the same metric through the public ``hstu_mha`` with pinned
+host tensors copied in and results copied out inside the timed region.  ``roofline`` describes
+the dominant kernel, ``cpu_baseline`` the CPU oracle timed on the host cores on a bounded
+sample.
+"""
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+SEQS_PER_GPU = 64
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(1.0)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def make_workload(world, name):
+    from generative_recommenders_b200 import workloads as W
+
+    if name == "config3":
+        return W.config3(256 * world)
+    return W.config1(SEQS_PER_GPU * world)
+
+
+def rank_shard(w, rank, world):
+    from generative_recommenders_b200 import sharding, workloads as W
+
+    if world == 1:
+        return w
+    bins = sharding.partition_by_tokens(w.lengths.tolist(), world)
+    sub = W.subset(w, bins[rank])
+    sub.seed = w.seed + 17 * rank
+    return sub
+
+
+def run_ours(args):
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    w_all = make_workload(world, args.workload)
+    w = rank_shard(w_all, rank, world)
+    fwd_only = args.workload == "config3" or args.fwd_only
+    N, alpha = w.max_seq_len, w.alpha
+    q, k, v, do = w.qkv(device="cpu", with_dout=True)
+    hq, hk, hv, hdo = (t.pin_memory() for t in (q, k, v, do))
+    offs = w.seq_offsets.to(torch.int32).to(dev)
+    nt = None if w.num_targets is None else w.num_targets.to(torch.int32).to(dev)
+    dq_, dk_, dv_, ddo = (t.to(dev) for t in (q, k, v, do))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    kw = dict(num_targets=nt, max_attn_len=w.max_attn_len, contextual_seq_len=w.contextual_seq_len)
+
+    def step(qd, kd, vd, dod):
+        if fwd_only:
+            with torch.no_grad():
+                return G.hstu_mha(N, alpha, qd, kd, vd, offs, **kw), None
+        qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+        qd.grad = kd.grad = vd.grad = None
+        out = G.hstu_mha(N, alpha, qd, kd, vd, offs, **kw)
+        out.backward(dod)
+        return out, (qd.grad, kd.grad, vd.grad)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(dq_, dk_, dv_, ddo)
+    barrier()
+
+    # ---- device-resident timing: per-step CUDA events, L2 flushed (untimed) between steps
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    launches0 = _cabi.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for s, e in ev:
+            flush.zero_()
+            s.record()
+            step(dq_, dk_, dv_, ddo)
+            e.record()
+        barrier()
+    launches = _cabi.launch_count() - launches0
+    ms_total = sum(s.elapsed_time(e) for s, e in ev)
+
+    # ---- forward / backward kernels separately (for the roofline of the dominant kernel)
+    fe = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(min(args.steps, 50))]
+    for a, b, c in fe:
+        flush.zero_()
+        qd = dq_.detach().requires_grad_(not fwd_only); kd = dk_.detach().requires_grad_(not fwd_only)
+        vd = dv_.detach().requires_grad_(not fwd_only)
+        a.record()
+        if fwd_only:
+            with torch.no_grad():
+                out = G.hstu_mha(N, alpha, qd, kd, vd, offs, **kw)
+            b.record()
+        else:
+            out = G.hstu_mha(N, alpha, qd, kd, vd, offs, **kw)
+            b.record()
+            out.backward(ddo)
+        c.record()
+    torch.cuda.synchronize()
+    fwd_ms = sorted(a.elapsed_time(b) for a, b, c in fe)[len(fe) // 2]
+    bwd_ms = sorted(b.elapsed_time(c) for a, b, c in fe)[len(fe) // 2]
+
+    # ---- end to end through the public API from pinned host memory
+    e2e_steps = max(3, min(args.steps, 20))
+    res_host = [torch.empty_like(t).pin_memory() for t in ((q,) if fwd_only else (q, q, k, v))]
+
+    def e2e_step():
+        qd = hq.to(dev, non_blocking=True); kd = hk.to(dev, non_blocking=True)
+        vd = hv.to(dev, non_blocking=True)
+        dod = None if fwd_only else hdo.to(dev, non_blocking=True)
+        out, grads = step(qd, kd, vd, dod)
+        res_host[0].copy_(out, non_blocking=True)
+        if grads is not None:
+            for dst, g in zip(res_host[1:], grads):
+                dst.copy_(g, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    elem = q.element_size()
+    h2d = sum(t.numel() for t in ((q, k, v) if fwd_only else (q, k, v, do))) * elem
+    d2h = sum(t.numel() for t in res_host) * elem
+
+    # ---- reduce over ranks: time = max, work = sum
+    flops_fwd = w.causal_flops_fwd()
+    mult = 1.0 if fwd_only else 3.5
+    stats = torch.tensor([ms_total, e2e_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
+    work = torch.tensor([flops_fwd, float(w.total_tokens), float(launches)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms, fwd_ms, bwd_ms = stats.tolist()
+    flops_fwd_all, tokens_all, launches_all = work.tolist()
+    ms_per_step = ms_total / args.steps
+    value = mult * flops_fwd_all / (ms_per_step * 1e-3) / 1e12
+    e2e_value = mult * flops_fwd_all / (e2e_ms * 1e-3) / 1e12
+
+    peaks, peak_kind = load_peaks()
+    # dominant kernel of the step and its roofline (per GPU: rank 0's share of the work)
+    exact_fwd = 4.0 * w.num_heads * w.attn_dim * w.exact_pairs()
+    if fwd_only or fwd_ms >= bwd_ms:
+        dom, dom_ms, dom_flops = "hstu_attn_fwd_sm100_kernel", fwd_ms, flops_fwd
+    else:
+        dom, dom_ms, dom_flops = "attention backward", bwd_ms, 2.5 * flops_fwd
+    ach = dom_flops / (dom_ms * 1e-3) / 1e12
+    roofline = {"kernel": dom, "bound": "tensor", "achieved": round(ach, 2), "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": round(ach / peaks["bf16_tflops"], 4), "traffic": None,
+                "peak_source": peak_kind, "launch_ms": round(dom_ms, 4),
+                "flops_model": "nominal causal 4*H*d*sum(L^2)/2 (x2.5 for backward)"}
+
+    out = None
+    if rank == 0:
+        out = {
+            "metric": "hstu_mha_%s_tflops" % ("fwd" if fwd_only else "fwd_bwd"),
+            "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[%s]: hstu_mha %s, B=%d seqs/GPU, H=%d, d=%d, N=%d, targets, bf16" % (
+                "3" if args.workload == "config3" else "1", "fwd" if fwd_only else "fwd+bwd", len(w.lengths), w.num_heads, w.attn_dim, N),
+                "global_batch": len(w_all.lengths), "tokens": int(tokens_all), "seq_len": N,
+                "parallelism": "sequence-sharded x%d, no collective" % world,
+                "l2": "256 MiB memset between timed steps (untimed)"},
+            "tokens_per_s": round(tokens_all / (ms_per_step * 1e-3), 1),
+            "fwd_tflops": round(flops_fwd / (fwd_ms * 1e-3) / 1e12, 2),
+            "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
+            "fwd_tflops_exact_pairs": round(exact_fwd / (fwd_ms * 1e-3) / 1e12, 2),
+            "frac_of_nominal_bf16_peak_2250": round(value / world / 2250.0, 4),
+            "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 4)},
+            "gpu_launches": int(launches_all),
+            "clocks": clocks.summary(),
+            "roofline": roofline,
+        }
+        if world == 1:
+            out["cpu_baseline"] = cpu_baseline(w, fwd_only)
+        print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def cpu_oracle_step(w, idx, fwd_only):
+    """One pass of the CPU oracle over the sequences ``idx`` of workload ``w``; returns
+    (seconds, nominal forward FLOPs of those sequences)."""
+    from generative_recommenders_b200 import workloads as W
+    from oracle import hstu_oracle as O
+
+    sub = W.subset(w, idx)
+    q, k, v, do = sub.qkv(with_dout=True)
+    q, k, v, do = (t.float() for t in (q, k, v, do))
+    if not fwd_only:
+        q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    t0 = time.perf_counter()
+    out = O.hstu_mha(sub.max_seq_len, sub.alpha, q, k, v, sub.seq_offsets, num_targets=sub.num_targets,
+                     max_attn_len=sub.max_attn_len, contextual_seq_len=sub.contextual_seq_len)
+    if not fwd_only:
+        out.backward(do)
+    dt = time.perf_counter() - t0
+    return dt, sub.causal_flops_fwd()
+
+
+def cpu_baseline(w, fwd_only):
+    n = min(len(w.lengths), 16)
+    idx = list(range(n))
+    cpu_oracle_step(w, idx[:2], fwd_only)  # warm-up
+    dt, f = cpu_oracle_step(w, idx, fwd_only)
+    mult = 1.0 if fwd_only else 3.5
+    return {"value": round(mult * f / dt / 1e12, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": "first %d sequences of the workload, fp32 oracle, %.2f s" % (n, dt)}
+
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path, as restated by the oracle (the
+    reference checkout itself does not travel to the GPU box), with all host threads."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = make_workload(world, args.workload)
+    fwd_only = args.workload == "config3" or args.fwd_only
+    n = min(len(w.lengths), 8)
+    idx = list(range(n))
+    for _ in range(min(args.warmup, 2)):
+        cpu_oracle_step(w, idx[:2], fwd_only)
+    steps = max(1, min(args.steps, 5))
+    tot_t = tot_f = 0.0
+    for _ in range(steps):
+        dt, f = cpu_oracle_step(w, idx, fwd_only)
+        tot_t += dt
+        tot_f += f
+    mult = 1.0 if fwd_only else 3.5
+    val = mult * tot_f / tot_t / 1e12
+    line = {
+        "impl": "reference", "metric": "hstu_mha_%s_tflops" % ("fwd" if fwd_only else "fwd_bwd"),
+        "value": round(val, 5), "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 2),
+        "ms_per_step": round(tot_t / steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[%s]: hstu_mha, CPU PyTorch path (oracle port), first %d sequences per step" % (
+            "3" if fwd_only else "1", n)},
+        "cpu_baseline": {"value": round(val, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": "first %d sequences per step" % n},
+        "e2e": {"value": round(val, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config1", choices=["config1", "config3"])
+    ap.add_argument("--fwd-only", action="store_true", help="time the forward alone (inference)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

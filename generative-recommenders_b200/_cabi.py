@@ -33,6 +33,7 @@ EXPORTS = [
     "b200_hstu_launch_count",
     "b200_hstu_host_kv_range",
     "b200_hstu_host_mask",
+    "b200_hstu_host_bwd_q_tiles",
 ]
 
 
@@ -140,6 +141,8 @@ def lib():
     L.b200_hstu_launch_count.restype = c_int64
     L.b200_hstu_host_kv_range.argtypes = [c_int32] * 8 + [POINTER(c_int32)] * 3
     L.b200_hstu_host_kv_range.restype = None
+    L.b200_hstu_host_bwd_q_tiles.argtypes = [c_int32] * 7 + [POINTER(c_int32)] * 3
+    L.b200_hstu_host_bwd_q_tiles.restype = None
     L.b200_hstu_host_mask.argtypes = [c_int32] * 8
     L.b200_hstu_host_mask.restype = ctypes.c_int
     _lib = L

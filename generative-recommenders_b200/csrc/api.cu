@@ -3,6 +3,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include "attn_plan.cuh"
 #include "common.cuh"
 
 namespace b200hstu {
@@ -224,6 +225,27 @@ void b200_hstu_host_kv_range(int32_t len, int32_t num_targets, int32_t max_seq_l
   *lo = r.lo;
   *hi = r.hi;
   *diag_lo = r.diag_lo;
+}
+
+/* Host utility: the query tiles (128 rows each) that the backward's K/V-stationary kernel visits
+   for kv tile `kt`: tiles [t_lo, t_lo + n_main) plus `extra_tile` when it is >= 0. */
+void b200_hstu_host_bwd_q_tiles(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
+                                int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t kt, int32_t *t_lo,
+                                int32_t *n_main, int32_t *extra_tile) {
+  AttnGeomParams g;
+  g.seq_offsets = nullptr;
+  g.num_targets = nullptr;
+  g.B = 1;
+  g.H = 1;
+  g.max_seq_len = max_seq_len;
+  g.W = max_attn_len;
+  g.c = contextual_seq_len;
+  g.F = min_full_attn_seq_len;
+  TileItem it;
+  fill_kv_item(it, g, 0, kt, 0, len, num_targets);
+  *t_lo = it.t_lo;
+  *n_main = it.n_main;
+  *extra_tile = it.extra_tile;
 }
 
 /* Host utility: mask(i, j) of one sequence, as the kernels evaluate it. */

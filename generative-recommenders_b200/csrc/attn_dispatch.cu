@@ -5,22 +5,18 @@ namespace b200hstu {
 
 bool attn_tc_layout_ok(const b200_hstu_attn_args &a, bool bwd, const char **why);
 int64_t attn_tc_fwd_workspace_bytes(const b200_hstu_attn_args &a);
+int64_t attn_tc_bwd_workspace_bytes(const b200_hstu_attn_args &a);
 
 bool attn_tc_applicable(const b200_hstu_attn_args &a, bool bwd, const char **why) {
-  if (bwd) {
-    *why = "tensor-core backward is not built yet";
+  if (bwd && a.attn_scale != nullptr && a.attn_scale_numel > 1) {
+    *why = "per-token attn_scale is only handled by the CUDA-core backward";
     return false;
   }
   return attn_tc_layout_ok(a, bwd, why);
 }
 
 int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, bool bwd) {
-  if (bwd) return 0;
-  return attn_tc_fwd_workspace_bytes(a);
-}
-
-int attn_tc_bwd(const b200_hstu_attn_args &, cudaStream_t) {
-  return fail(B200_HSTU_EUNSUPPORTED, "tensor-core backward is not built yet");
+  return bwd ? attn_tc_bwd_workspace_bytes(a) : attn_tc_fwd_workspace_bytes(a);
 }
 
 int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &, cudaStream_t) {

@@ -374,6 +374,12 @@ int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, 
                   int elem_bytes, bool is_bf16) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return fail(B200_HSTU_EDEVICE, "cuTensorMapEncodeTiled is not available from the driver");
+  {
+    // the driver call needs this thread to have the device's primary context current; a thread
+    // that has only inherited its device index (an autograd worker, say) may not have bound it yet
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+  }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)(row_stride_elems * elem_bytes)};
   cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)TILE};

@@ -201,6 +201,11 @@ int64_t b200_hstu_launch_count(void);
 void b200_hstu_host_kv_range(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
                              int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t m0, int32_t tile,
                              int32_t *lo, int32_t *hi, int32_t *diag_lo);
+/* Query tiles (128 rows each) the backward's K/V-stationary kernel visits for kv tile kt:
+   [t_lo, t_lo + n_main) plus extra_tile when it is >= 0. */
+void b200_hstu_host_bwd_q_tiles(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
+                                int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t kt, int32_t *t_lo,
+                                int32_t *n_main, int32_t *extra_tile);
 int b200_hstu_host_mask(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
                         int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t i, int32_t j);
 

@@ -118,9 +118,11 @@ def test_half_precision_forward_matches_oracle(impl, dtype, case):
     assert O.rel_l2(out, ref) < BF16_TOL, O.rel_l2(out, ref)
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
 @pytest.mark.parametrize("case", CASES)
-def test_bf16_backward_matches_oracle(case):
+def test_bf16_backward_matches_oracle(impl, case):
     B, lo, hi, N, H, d, targets, ctx, Wn, F = case
+    G.set_attention_impl(impl)
     q, k, v, offs, nt, dout = _random_case(hash(case) % 10000 + 1, B, lo, hi, N, H, d, torch.bfloat16, targets, ctx,
                                            std=0.7)
     alpha = 1.0 / d ** 0.5

@@ -102,3 +102,31 @@ def test_block_skipping_rule_never_drops_a_valid_pair(T):
             total += (Lt + T - 1) // T
             visited += len({j // T for j in range(lo, hi)} | ({dg // T} if dg >= 0 else set()))
     assert visited < total  # something is skipped
+
+
+def test_backward_tile_rule_never_drops_a_valid_pair():
+    """K/V-stationary backward: every query tile holding a row that sees a column of the kv tile
+    must be in the visited set (128-row tiles)."""
+    lib = _cabi.lib()
+    rng = random.Random(99)
+    T = 128
+    skipped = 0
+    for _ in range(150):
+        N = 700
+        L = rng.randint(1, N)
+        c = rng.choice([0, 0, 2, 7])
+        t = rng.randint(0, max(0, min(L - 1, 150)))
+        W = rng.choice([0, 0, 3, 100, 130, 300])
+        F = rng.choice([0, 0, 40]) if W > 0 else 0
+        mask = O.valid_attn_mask(L, t, True, W, c, F)
+        ntiles = (L + T - 1) // T
+        for kt in range(ntiles):
+            lo, n, ex = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+            lib.b200_hstu_host_bwd_q_tiles(L, t, N, c, W, F, kt, ctypes.byref(lo), ctypes.byref(n), ctypes.byref(ex))
+            visited = set(range(lo.value, lo.value + n.value)) | ({ex.value} if ex.value >= 0 else set())
+            cols = mask[:, kt * T:(kt + 1) * T]
+            rows = torch.nonzero(cols.any(dim=1)).flatten().tolist()
+            need = {r // T for r in rows}
+            assert need <= visited, (L, t, c, W, F, kt, sorted(need), sorted(visited))
+            skipped += ntiles - len(visited)
+    assert skipped > 0
