@@ -34,6 +34,7 @@ EXPORTS = [
     "b200_hstu_host_kv_range",
     "b200_hstu_host_mask",
     "b200_hstu_host_bwd_q_tiles",
+    "b200_hstu_host_interval_mask",
 ]
 
 
@@ -143,6 +144,8 @@ def lib():
     L.b200_hstu_host_kv_range.restype = None
     L.b200_hstu_host_bwd_q_tiles.argtypes = [c_int32] * 7 + [POINTER(c_int32)] * 3
     L.b200_hstu_host_bwd_q_tiles.restype = None
+    L.b200_hstu_host_interval_mask.argtypes = [c_int32] * 9
+    L.b200_hstu_host_interval_mask.restype = ctypes.c_int
     L.b200_hstu_host_mask.argtypes = [c_int32] * 8
     L.b200_hstu_host_mask.restype = ctypes.c_int
     _lib = L

@@ -248,6 +248,36 @@ void b200_hstu_host_bwd_q_tiles(int32_t len, int32_t num_targets, int32_t max_se
   *extra_tile = it.extra_tile;
 }
 
+/* Host utility: mask(i, j) from the closed-form per-row (transposed = 0) or per-column
+   (transposed = 1) intervals the tensor-core kernels use on partially visible tiles; -1 when the
+   sequence is outside the domain where the closed form applies (the kernels then evaluate the
+   exact mask element by element). */
+int b200_hstu_host_interval_mask(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
+                                 int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t i, int32_t j,
+                                 int32_t transposed) {
+  AttnGeomParams g;
+  g.seq_offsets = nullptr;
+  g.num_targets = nullptr;
+  g.B = 1;
+  g.H = 1;
+  g.max_seq_len = max_seq_len;
+  g.W = max_attn_len;
+  g.c = contextual_seq_len;
+  g.F = min_full_attn_seq_len;
+  TileItem it;
+  fill_common(it, g, 0, 0, 0, len, num_targets);
+  if (!it.regular) return -1;
+  if (i >= it.m.L || j >= it.m.L) return 0;
+  if (!transposed) {
+    RowInterval r = row_interval(it, i);
+    int base = j & ~31;
+    return (row_mask_bits(r, base, it.m.L) >> (j - base)) & 1u;
+  }
+  ColInterval r = col_interval(it, j);
+  int base = i & ~31;
+  return (col_mask_bits(r, base, it.m.L) >> (i - base)) & 1u;
+}
+
 /* Host utility: mask(i, j) of one sequence, as the kernels evaluate it. */
 int b200_hstu_host_mask(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
                         int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t i, int32_t j) {

@@ -7,17 +7,22 @@
 // (the math of generative_recommenders/ops/triton/triton_hstu_attention.py:1905-2020; no softmax
 // statistics and no `out` are needed).
 //
-// Two persistent kernels, each element of every gradient has exactly one owner, so there are no
-// atomics, no fp32 dQ scratch, no convert pass, and the result is bit-reproducible:
-//   * dkdv kernel - one work item per (sequence, 128-row K/V tile, head).  K and V stay in shared
-//     memory; Q and dO tiles of every query tile that can see the K/V tile stream through 2-stage
-//     TMA rings.  S^T = K Q^T and dP^T = V dO^T land in TMEM, 128 threads (one K/V row each) turn
-//     them into bf16 P^T and dS^T written back over the same TMEM columns, and those feed
-//     dV += P^T dO and dK += dS^T Q as TMEM A-operands (dO and Q are the MN-major B operands).
-//   * dq kernel - one work item per (sequence, 128-row query tile, head), the forward's loop
-//     structure: Q and dO stay, K and V stream; S = Q K^T and dP = dO V^T in TMEM, dS written over
-//     dP, dQ += dS K with K as the MN-major B operand.
-// Constant factors are folded into the epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
+// Two launches of one persistent kernel template; each element of every gradient has exactly one
+// owner, so there are no atomics, no fp32 dQ scratch, no convert pass, and the result is
+// bit-reproducible:
+//   * DKDV = true  - a work item is (sequence, 128-row K/V tile, head).  K and V stay in shared
+//     memory; the Q and dO tiles of every query tile that can see the K/V tile stream through
+//     2-stage TMA rings.  Stage 1: S^T = K Q^T and dP^T = V dO^T into TMEM.  The 128 threads that
+//     own one K/V row each turn them into bf16 P^T and dS^T written back over the same TMEM
+//     columns.  Stage 2: dV += P^T dO and dK += dS^T Q with the TMEM tiles as A operands (dO and
+//     Q are MN-major B operands).
+//   * DKDV = false - a work item is (sequence, 128-row query tile, head): Q and dO stay, K and V
+//     stream; stage 1: S = Q K^T, dP = dO V^T; stage 2: dQ += dS K.
+// Every streamed tile is processed as two 64-column halves (a, b) owned by two warpgroups, and the
+// MMA issue order  stage2_a(i), stage1_a(i+1), stage2_b(i), stage1_b(i+1)  lets the tensor pipe
+// work on one half while the CUDA cores activate the other.  TMEM: 4 x 64 columns of stage-1
+// tiles + two (DKDV) or one 128-column accumulators.  Constant factors are folded into the
+// epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
 #include "attn_plan.cuh"
 #include "sm100_ptx.cuh"
 
@@ -31,13 +36,13 @@ int device_sm_count();
 
 namespace {
 
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;
 constexpr int STAGES = 2;
 
 struct BwdParams {
   AttnGeomParams g;
   const PlanHeader *plan;
-  const int2 *items;
+  const ItemDesc *items;
   int *status;
   void *dq, *dk, *dv;
   int64_t dq_rs, dq_hs, dk_rs, dk_hs, dv_rs, dv_hs;
@@ -114,28 +119,32 @@ __device__ __forceinline__ void zero_rows_beyond(uint16_t *base, int64_t rs, int
   }
 }
 
-// =========================================================================================
-// dK / dV kernel: K/V-stationary
-// =========================================================================================
-template <int D, bool IS_BF16>
+
+constexpr int HALF = 64;  // streamed-tile columns owned by one warpgroup
+
+template <int D, bool IS_BF16, bool DKDV>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
-    hstu_attn_bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                                    const __grid_constant__ CUtensorMap tmap_v,
-                                    const __grid_constant__ CUtensorMap tmap_do, const BwdParams p) {
+    hstu_attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                               const BwdParams p) {
   using SM = BwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sK = smem_base + SM::A_OFF, sV = smem_base + SM::B_OFF;
-  const uint32_t sQ = smem_base + SM::X_OFF, sDO = smem_base + SM::Y_OFF;
+  // stationary pair X0 (K | Q), X1 (V | dO); streamed rings Y0 (Q | K), Y1 (dO | V)
+  const uint32_t sX0 = smem_base + SM::A_OFF, sX1 = smem_base + SM::B_OFF;
+  const uint32_t sY0 = smem_base + SM::X_OFF, sY1 = smem_base + SM::Y_OFF;
+  const CUtensorMap *mapX0 = DKDV ? &tmap_k : &tmap_q;
+  const CUtensorMap *mapX1 = DKDV ? &tmap_v : &tmap_do;
+  const CUtensorMap *mapY0 = DKDV ? &tmap_q : &tmap_k;
+  const CUtensorMap *mapY1 = DKDV ? &tmap_do : &tmap_v;
   const uint32_t bars = smem_base + SM::BAR_OFF;
-  const uint32_t kv_full = bars + 0, kv_empty = bars + 8;
-  const uint32_t q_full = bars + 16, q_empty = q_full + 8 * STAGES;       // Q ring
-  const uint32_t do_full = q_empty + 8 * STAGES, do_empty = do_full + 8 * STAGES;  // dO ring
-  const uint32_t st_full = do_empty + 8 * STAGES;   // S^T and dP^T ready (MMA -> threads)
-  const uint32_t pt_full = st_full + 8;             // P^T and dS^T written (threads -> MMA)
-  const uint32_t acc_full = pt_full + 8;            // dK, dV complete
-  const uint32_t acc_empty = acc_full + 8;          // dK, dV read out
+  const uint32_t x_full = bars + 0, x_empty = bars + 8;
+  const uint32_t y0_full = bars + 16, y0_empty = y0_full + 8 * STAGES;
+  const uint32_t y1_full = y0_empty + 8 * STAGES, y1_empty = y1_full + 8 * STAGES;
+  const uint32_t t_full = y1_empty + 8 * STAGES;   // [2] stage-1 tiles of half a / b ready
+  const uint32_t w_full = t_full + 16;             // [2] bf16 tiles of half a / b written
+  const uint32_t acc_full = w_full + 16, acc_empty = acc_full + 8;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + SM::MISC_OFF);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + SM::MISC_OFF + 8);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,18 +152,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(kv_full, 1);
-    mbar_init(kv_empty, 1);
+    mbar_init(x_full, 1);
+    mbar_init(x_empty, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(q_full + 8 * s, 1);
-      mbar_init(q_empty + 8 * s, 1);
-      mbar_init(do_full + 8 * s, 1);
-      mbar_init(do_empty + 8 * s, 1);
+      mbar_init(y0_full + 8 * s, 1);
+      mbar_init(y0_empty + 8 * s, 1);
+      mbar_init(y1_full + 8 * s, 1);
+      mbar_init(y1_empty + 8 * s, 1);
     }
-    mbar_init(st_full, 1);
-    mbar_init(pt_full, 4);
+    for (int hf = 0; hf < 2; ++hf) {
+      mbar_init(t_full + 8 * hf, 1);
+      mbar_init(w_full + 8 * hf, 4);
+    }
     mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 4);
+    mbar_init(acc_empty, 8);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -165,421 +176,302 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tST = tmem_base;          // S^T  -> P^T   (columns 0..127)
-  const uint32_t tDPT = tmem_base + 128;   // dP^T -> dS^T
-  const uint32_t tDV = tmem_base + 256;
-  const uint32_t tDK = tmem_base + 384;
+  // TMEM columns: T0_a [0,64) T0_b [64,128) T1_a [128,192) T1_b [192,256) ACC0 [256,384) ACC1 [384,512)
+  //   T0 = S^T | S,  T1 = dP^T | dP,  ACC0 = dV | dQ,  ACC1 = dK | unused
   const int num_items = p.plan->num_items * p.H;
+  const int stride = gridDim.x;
 
   if (warp == 0) {
-    if (lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && (int)blockIdx.x < num_items) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
       uint32_t it_cnt = 0, cnt = 0;
       bool ok = true;
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += gridDim.x, ++it_cnt) {
-        const int2 e = p.items[idx / p.H];
+      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
+      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
+        const ItemDesc dsc = nxt;
+        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
         const int h = idx % p.H;
         TileItem it;
-        load_item<true>(it, p.g, e.x, e.y);
-        ok = mbar_wait(wc, kv_empty, (it_cnt & 1) ^ 1, 401);
+        if (DKDV) fill_kv_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        else fill_q_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        ok = mbar_wait(wc, x_empty, (it_cnt & 1) ^ 1, 401);
         if (!ok) break;
-        mbar_arrive_expect_tx(kv_full, 2 * SM::TILE_BYTES);
+        mbar_arrive_expect_tx(x_full, 2 * SM::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < SM::CHUNKS; ++c) {
-          tma_load_2d(sK + c * SM::CHUNK_BYTES, &tmap_k, h * D + c * 64, it.start + it.m0, kv_full);
-          tma_load_2d(sV + c * SM::CHUNK_BYTES, &tmap_v, h * D + c * 64, it.start + it.m0, kv_full);
+          tma_load_2d(sX0 + c * SM::CHUNK_BYTES, mapX0, h * D + c * 64, it.start + it.m0, x_full);
+          tma_load_2d(sX1 + c * SM::CHUNK_BYTES, mapX1, h * D + c * 64, it.start + it.m0, x_full);
         }
         for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
           const int s = cnt % STAGES;
           const uint32_t par = ((cnt / STAGES) & 1) ^ 1;
           const int row = it.start + it.tile_at(j) * TILE;
-          ok = mbar_wait(wc, q_empty + 8 * s, par, 402);
+          ok = mbar_wait(wc, y0_empty + 8 * s, par, 402);
           if (!ok) break;
-          mbar_arrive_expect_tx(q_full + 8 * s, SM::TILE_BYTES);
+          mbar_arrive_expect_tx(y0_full + 8 * s, SM::TILE_BYTES);
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sQ + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, row, q_full + 8 * s);
-          ok = mbar_wait(wc, do_empty + 8 * s, par, 403);
+            tma_load_2d(sY0 + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY0, h * D + c * 64, row, y0_full + 8 * s);
+          ok = mbar_wait(wc, y1_empty + 8 * s, par, 403);
           if (!ok) break;
-          mbar_arrive_expect_tx(do_full + 8 * s, SM::TILE_BYTES);
+          mbar_arrive_expect_tx(y1_full + 8 * s, SM::TILE_BYTES);
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sDO + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_do, h * D + c * 64, row, do_full + 8 * s);
+            tma_load_2d(sY1 + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row, y1_full + 8 * s);
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (warp-uniform)
+    if ((int)blockIdx.x < num_items) {
       constexpr uint32_t FMT = IS_BF16 ? 1u : 0u;
-      const uint32_t idesc_kk = make_idesc(FMT, FMT, 0, 0, TILE, TILE);  // K-major x K-major -> 128 x 128
-      const uint32_t idesc_mn = make_idesc(FMT, FMT, 0, 1, TILE, D);     // TMEM A x MN-major B -> 128 x D
-      const uint64_t k_desc = make_smem_desc(sK, 16, 1024);
-      const uint64_t v_desc = make_smem_desc(sV, 16, 1024);
+      const uint32_t idesc_1 = make_idesc(FMT, FMT, 0, 0, TILE, HALF);  // 128 x 64, both operands K-major
+      const uint32_t idesc_2 = make_idesc(FMT, FMT, 0, 1, TILE, D);     // 128 x D, TMEM A, MN-major B
+      const uint64_t x0_desc = make_smem_desc(sX0, 16, 1024);
+      const uint64_t x1_desc = make_smem_desc(sX1, 16, 1024);
       uint32_t it_cnt = 0, cnt = 0;
       bool ok = true;
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += gridDim.x, ++it_cnt) {
-        const int2 e = p.items[idx / p.H];
+
+      // stage 1 of half hf for the streamed tile in ring slot s: T0_hf = X0 Y0_hf^T, T1_hf = X1 Y1_hf^T
+      auto stage1 = [&](int hf, int s) {
+        const uint64_t y0_desc = make_smem_desc(sY0 + s * SM::TILE_BYTES + hf * HALF * 128, 16, 1024);
+        const uint64_t y1_desc = make_smem_desc(sY1 + s * SM::TILE_BYTES + hf * HALF * 128, 16, 1024);
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
+            mma_ss(tmem_base + hf * HALF, desc_advance(x0_desc, off), desc_advance(y0_desc, off), idesc_1, ks > 0);
+          }
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
+            mma_ss(tmem_base + 128 + hf * HALF, desc_advance(x1_desc, off), desc_advance(y1_desc, off), idesc_1,
+                   ks > 0);
+          }
+          tc_commit(t_full + 8 * hf);
+        }
+        __syncwarp();
+      };
+
+      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
+      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
+        const ItemDesc dsc = nxt;
+        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
         TileItem it;
-        load_item<true>(it, p.g, e.x, e.y);
-        ok = mbar_wait(wc, kv_full, it_cnt & 1, 501);
+        if (DKDV) fill_kv_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        else fill_q_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        ok = mbar_wait(wc, x_full, it_cnt & 1, 501);
         if (!ok) break;
         const int n = it.n_tiles;
-        for (int j = 0; j < n; ++j, ++cnt) {
+        // first streamed tile: stage 1 of both halves
+        {
           const int s = cnt % STAGES;
-          const uint32_t par = (cnt / STAGES) & 1;
-          ok = mbar_wait(wc, q_full + 8 * s, par, 502);
+          ok = mbar_wait(wc, y0_full + 8 * s, (cnt / STAGES) & 1, 502);
+          if (!ok) break;
+          ok = mbar_wait(wc, y1_full + 8 * s, (cnt / STAGES) & 1, 503);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t q_desc = make_smem_desc(sQ + s * SM::TILE_BYTES, 16, 1024);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
-            mma_ss(tST, desc_advance(k_desc, off), desc_advance(q_desc, off), idesc_kk, ks > 0);
-          }
-          ok = mbar_wait(wc, do_full + 8 * s, par, 503);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t do_desc = make_smem_desc(sDO + s * SM::TILE_BYTES, 16, 1024);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
-            mma_ss(tDPT, desc_advance(v_desc, off), desc_advance(do_desc, off), idesc_kk, ks > 0);
-          }
-          tc_commit(st_full);
-          if (j == 0) {  // previous item's dK / dV must have been read out before they are overwritten
+          stage1(0, s);
+          stage1(1, s);
+        }
+        for (int j = 0; j < n; ++j, ++cnt) {
+          const int s = cnt % STAGES, sn = (cnt + 1) % STAGES;
+          const bool has_next = j + 1 < n;
+          if (j == 0) {  // the previous item's accumulators must have been read out
             ok = mbar_wait(wc, acc_empty, (it_cnt & 1) ^ 1, 504);
             if (!ok) break;
           }
-          ok = mbar_wait(wc, pt_full, cnt & 1, 505);
+          bool next_ready = false;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            ok = mbar_wait(wc, w_full + 8 * hf, cnt & 1, 505);
+            if (!ok) break;
+            tc_fence_after();
+            // stage 2: the 64 rows of this half of the streamed tile are the contraction dimension.
+            // MN-major B: 64-column blocks 16 KB apart, 16 rows (one MMA) = 2 KB, half b starts 8 KB in.
+            const uint64_t y0_mn = make_smem_desc(sY0 + s * SM::TILE_BYTES + hf * HALF * 128, SM::CHUNK_BYTES, 1024);
+            const uint64_t y1_mn = make_smem_desc(sY1 + s * SM::TILE_BYTES + hf * HALF * 128, SM::CHUNK_BYTES, 1024);
+            const uint32_t acc_on = (j > 0 || hf > 0) ? 1u : 0u;
+            if (elect_one()) {
+              if (DKDV) {
+#pragma unroll
+                for (int ks = 0; ks < HALF / 16; ++ks)  // dV += P^T dO
+                  mma_ts(tmem_base + 256, tmem_base + hf * HALF + ks * 8, desc_advance(y1_mn, ks * 2048), idesc_2,
+                         (acc_on || ks > 0) ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < HALF / 16; ++ks)  // dK += dS^T Q
+                  mma_ts(tmem_base + 384, tmem_base + 128 + hf * HALF + ks * 8, desc_advance(y0_mn, ks * 2048),
+                         idesc_2, (acc_on || ks > 0) ? 1u : 0u);
+              } else {
+#pragma unroll
+                for (int ks = 0; ks < HALF / 16; ++ks)  // dQ += dS K
+                  mma_ts(tmem_base + 256, tmem_base + 128 + hf * HALF + ks * 8, desc_advance(y0_mn, ks * 2048),
+                         idesc_2, (acc_on || ks > 0) ? 1u : 0u);
+              }
+            }
+            __syncwarp();
+            if (has_next) {
+              if (!next_ready) {
+                ok = mbar_wait(wc, y0_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 506);
+                if (!ok) break;
+                ok = mbar_wait(wc, y1_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 507);
+                if (!ok) break;
+                next_ready = true;
+                tc_fence_after();
+              }
+              stage1(hf, sn);
+            }
+          }
           if (!ok) break;
-          tc_fence_after();
-          // B operands: dO / Q tiles as [128 q rows][D] MN-major (q is the contraction dimension)
-          const uint64_t do_mn = make_smem_desc(sDO + s * SM::TILE_BYTES, SM::CHUNK_BYTES, 1024);
-          const uint64_t q_mn = make_smem_desc(sQ + s * SM::TILE_BYTES, SM::CHUNK_BYTES, 1024);
-#pragma unroll
-          for (int ks = 0; ks < TILE / 16; ++ks)
-            mma_ts(tDV, tST + ks * 8, desc_advance(do_mn, ks * 2048), idesc_mn, (j > 0 || ks > 0) ? 1u : 0u);
-          tc_commit(do_empty + 8 * s);
-#pragma unroll
-          for (int ks = 0; ks < TILE / 16; ++ks)
-            mma_ts(tDK, tDPT + ks * 8, desc_advance(q_mn, ks * 2048), idesc_mn, (j > 0 || ks > 0) ? 1u : 0u);
-          tc_commit(q_empty + 8 * s);
+          if (elect_one()) {  // the streamed tile of this iteration has no readers left
+            tc_commit(y0_empty + 8 * s);
+            tc_commit(y1_empty + 8 * s);
+          }
+          __syncwarp();
         }
         if (!ok) break;
-        tc_commit(kv_empty);
-        tc_commit(acc_full);
-        if (n == 0) {
-          // nothing visited this tile (cannot happen for a non-empty tile: the diagonal is always valid)
+        if (elect_one()) {
+          tc_commit(x_empty);
+          tc_commit(acc_full);
         }
+        __syncwarp();
       }
     }
   } else {
+    // ------------------------------------------------------------------ activation + epilogue warps
+    const int hf = warp >= 6 ? 1 : 0;          // which half of every streamed tile
     const int quad = warp & 3;
-    const int row_in_tile = quad * 32 + lane;  // K/V row owned by this thread
+    const int row_in_tile = quad * 32 + lane;  // stationary-tile row owned by this thread
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const uint32_t tT0 = tmem_base + hf * HALF + lane_off;
+    const uint32_t tT1 = tmem_base + 128 + hf * HALF + lane_off;
     uint32_t it_cnt = 0, cnt = 0;
     bool ok = true;
     const float sc = p.attn_scale ? p.attn_scale[0] : p.inv_n;
-    for (int idx = blockIdx.x; idx < num_items && ok; idx += gridDim.x, ++it_cnt) {
-      const int2 e = p.items[idx / p.H];
-      const int h = idx % p.H;
-      TileItem it;
-      load_item<true>(it, p.g, e.x, e.y);
-      const int L = it.m.L;
-      const int jcol = it.m0 + row_in_tile;  // kv position
-      const int id_j = it.m.id(jcol);
-      for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
-        const int m0 = it.tile_at(j) * TILE;  // first query row of the streamed tile
-        // mask can be skipped when the (query tile, kv tile) pair is fully visible and every query
-        // row of the tile exists
-        TileItem qi = it;
-        qi.m0 = m0;
-        const bool full = tile_pair_is_full(qi, it.m0) && (m0 + TILE <= L) && p.bias == nullptr;
-        ok = mbar_wait(wc, st_full, cnt & 1, 601);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rs[32], rp[32];
-          tmem_ld32(tST + lane_off + c * 32, rs);
-          tmem_ld32(tDPT + lane_off + c * 32, rp);
-          tc_wait_ld();
-          uint32_t pk[16], dk[16];
-#pragma unroll
-          for (int x = 0; x < 32; x += 2) {
-            float pv[2], dv[2];
-#pragma unroll
-            for (int y = 0; y < 2; ++y) {
-              const int i = m0 + c * 32 + x + y;  // query position
-              float hh = __uint_as_float(rs[x + y]) * p.half_alpha;
-              if (p.bias != nullptr) {
-                int dist = i > jcol ? i - jcol : jcol - i;
-                if (dist < p.bias_numel) hh += 0.5f * p.bias[dist];
-              }
-              float sl, dsl;
-              silu_and_grad(hh, sl, dsl);
-              float ds = __uint_as_float(rp[x + y]) * dsl;
-              bool valid = full || (i < L && jcol < L && it.m.valid_ids(i, jcol, it.m.id(i), id_j));
-              pv[y] = valid ? sl : 0.f;
-              dv[y] = valid ? ds : 0.f;
-            }
-            pk[x / 2] = pack2h(pv[0], pv[1], IS_BF16);
-            dk[x / 2] = pack2h(dv[0], dv[1], IS_BF16);
-          }
-          tmem_st16(tST + lane_off + c * 16, pk);
-          tmem_st16(tDPT + lane_off + c * 16, dk);
-        }
-        tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(pt_full);
-      }
-      if (!ok) break;
-      ok = mbar_wait(wc, acc_full, it_cnt & 1, 602);
-      if (!ok) break;
-      tc_fence_after();
-      const bool rv = jcol < L;
-      uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + jcol) * p.dv_rs + (int64_t)h * p.dv_hs;
-      uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + jcol) * p.dk_rs + (int64_t)h * p.dk_hs;
-      store_acc_rows<D, IS_BF16>(tDV + lane_off, sc, dvrow, rv);
-      store_acc_rows<D, IS_BF16>(tDK + lane_off, sc * p.alpha, dkrow, rv);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty);
-      if (it.len > L && it.m0 + TILE >= L) {
-        zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, it.start, L, it.len, row_in_tile);
-        zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dv), p.dv_rs, p.dv_hs, h, it.start, L, it.len, row_in_tile);
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (*abort_flag) {
-    uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 20000ull) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
-// =========================================================================================
-// dQ kernel: Q/dO-stationary
-// =========================================================================================
-template <int D, bool IS_BF16>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
-    hstu_attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                                  const __grid_constant__ CUtensorMap tmap_v,
-                                  const __grid_constant__ CUtensorMap tmap_do, const BwdParams p) {
-  using SM = BwdSmem<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sQ = smem_base + SM::A_OFF, sDO = smem_base + SM::B_OFF;
-  const uint32_t sK = smem_base + SM::X_OFF, sV = smem_base + SM::Y_OFF;
-  const uint32_t bars = smem_base + SM::BAR_OFF;
-  const uint32_t qd_full = bars + 0, qd_empty = bars + 8;
-  const uint32_t k_full = bars + 16, k_empty = k_full + 8 * STAGES;
-  const uint32_t v_full = k_empty + 8 * STAGES, v_empty = v_full + 8 * STAGES;
-  const uint32_t sp_full = v_empty + 8 * STAGES;    // S and dP ready
-  const uint32_t ds_full = sp_full + 8;             // dS written
-  const uint32_t acc_full = ds_full + 8, acc_empty = acc_full + 8;
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + SM::MISC_OFF);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + SM::MISC_OFF + 8);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  WaitCtx wc{abort_flag, p.status};
-
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    mbar_init(qd_full, 1);
-    mbar_init(qd_empty, 1);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(k_full + 8 * s, 1);
-      mbar_init(k_empty + 8 * s, 1);
-      mbar_init(v_full + 8 * s, 1);
-      mbar_init(v_empty + 8 * s, 1);
-    }
-    mbar_init(sp_full, 1);
-    mbar_init(ds_full, 4);
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 4);
-    fence_mbar_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base;           // S
-  const uint32_t tDP = tmem_base + 128;    // dP -> dS
-  const uint32_t tDQ = tmem_base + 256;
-  const int num_items = p.plan->num_items * p.H;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
-      uint32_t it_cnt = 0, cnt = 0;
-      bool ok = true;
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += gridDim.x, ++it_cnt) {
-        const int2 e = p.items[idx / p.H];
+    if ((int)blockIdx.x < num_items) {
+      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
+      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
+        const ItemDesc dsc = nxt;
+        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
         const int h = idx % p.H;
         TileItem it;
-        load_item<false>(it, p.g, e.x, e.y);
-        ok = mbar_wait(wc, qd_empty, (it_cnt & 1) ^ 1, 701);
-        if (!ok) break;
-        mbar_arrive_expect_tx(qd_full, 2 * SM::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < SM::CHUNKS; ++c) {
-          tma_load_2d(sQ + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, it.start + it.m0, qd_full);
-          tma_load_2d(sDO + c * SM::CHUNK_BYTES, &tmap_do, h * D + c * 64, it.start + it.m0, qd_full);
-        }
+        if (DKDV) fill_kv_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        else fill_q_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        const int L = it.m.L;
+        const int own = it.m0 + row_in_tile;  // kv position (DKDV) or query position
+        const int id_own = it.m.id(own);
+        const bool exact_only = !it.regular || p.bias != nullptr;
+        ColInterval ci;
+        RowInterval ri;
+        if (DKDV) ci = col_interval(it, own); else ri = row_interval(it, own);
         for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
-          const int s = cnt % STAGES;
-          const uint32_t par = ((cnt / STAGES) & 1) ^ 1;
-          const int row = it.start + it.tile_at(j) * TILE;
-          ok = mbar_wait(wc, k_empty + 8 * s, par, 702);
+          const int o0 = it.tile_at(j) * TILE;  // first position of the streamed tile
+          const int c0 = o0 + hf * HALF;        // first position of this half
+          bool full;
+          if (DKDV) {  // streamed = query tile o0, stationary = kv tile it.m0; all query rows must exist
+            TileItem qi = it;
+            qi.m0 = o0;
+            full = !exact_only && tile_pair_is_full(qi, it.m0) && (o0 + TILE <= L);
+          } else {
+            full = !exact_only && tile_pair_is_full(it, o0);
+          }
+          ok = mbar_wait(wc, t_full + 8 * hf, cnt & 1, 601);
           if (!ok) break;
-          mbar_arrive_expect_tx(k_full + 8 * s, SM::TILE_BYTES);
+          tc_fence_after();
+          if (!exact_only) {
+            uint32_t rs[2][32], rp[2][32];
+            tmem_ld32(tT0, rs[0]);
+            tmem_ld32(tT0 + 32, rs[1]);
+            tmem_ld32(tT1, rp[0]);
+            tmem_ld32(tT1 + 32, rp[1]);
+            tc_wait_ld();
 #pragma unroll
-          for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sK + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_k, h * D + c * 64, row, k_full + 8 * s);
-          ok = mbar_wait(wc, v_empty + 8 * s, par, 703);
-          if (!ok) break;
-          mbar_arrive_expect_tx(v_full + 8 * s, SM::TILE_BYTES);
+            for (int c = 0; c < 2; ++c) {
+              uint32_t bits = 0xffffffffu;
+              if (!full) bits = DKDV ? col_mask_bits(ci, c0 + c * 32, L) : row_mask_bits(ri, c0 + c * 32, L);
+              uint32_t pk[16], dk[16];
 #pragma unroll
-          for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sV + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_v, h * D + c * 64, row, v_full + 8 * s);
+              for (int x = 0; x < 16; ++x) {
+                float sl0, dsl0, sl1, dsl1;
+                silu_and_grad(__uint_as_float(rs[c][2 * x]) * p.half_alpha, sl0, dsl0);
+                silu_and_grad(__uint_as_float(rs[c][2 * x + 1]) * p.half_alpha, sl1, dsl1);
+                float ds0 = __uint_as_float(rp[c][2 * x]) * dsl0, ds1 = __uint_as_float(rp[c][2 * x + 1]) * dsl1;
+                const bool v0 = bits & (1u << (2 * x)), v1 = bits & (1u << (2 * x + 1));
+                if (DKDV) pk[x] = pack2h(v0 ? sl0 : 0.f, v1 ? sl1 : 0.f, IS_BF16);
+                dk[x] = pack2h(v0 ? ds0 : 0.f, v1 ? ds1 : 0.f, IS_BF16);
+              }
+              if (DKDV) tmem_st16(tT0 + c * 16, pk);
+              tmem_st16(tT1 + c * 16, dk);
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+              uint32_t rs[32], rp[32], pk[16], dk[16];
+              tmem_ld32(tT0 + c * 32, rs);
+              tmem_ld32(tT1 + c * 32, rp);
+              tc_wait_ld();
+#pragma unroll
+              for (int x = 0; x < 32; x += 2) {
+                float pv[2], dv[2];
+#pragma unroll
+                for (int y = 0; y < 2; ++y) {
+                  const int other = c0 + c * 32 + x + y;
+                  const int qi_ = DKDV ? other : own, kj_ = DKDV ? own : other;
+                  float hh = __uint_as_float(rs[x + y]) * p.half_alpha;
+                  if (p.bias != nullptr) {
+                    int dist = qi_ > kj_ ? qi_ - kj_ : kj_ - qi_;
+                    if (dist < p.bias_numel) hh += 0.5f * p.bias[dist];
+                  }
+                  float sl, dsl;
+                  silu_and_grad(hh, sl, dsl);
+                  float ds = __uint_as_float(rp[x + y]) * dsl;
+                  const int id_other = it.m.id(other);
+                  bool valid = qi_ < L && kj_ < L &&
+                               it.m.valid_ids(qi_, kj_, DKDV ? id_other : id_own, DKDV ? id_own : id_other);
+                  pv[y] = valid ? sl : 0.f;
+                  dv[y] = valid ? ds : 0.f;
+                }
+                pk[x / 2] = pack2h(pv[0], pv[1], IS_BF16);
+                dk[x / 2] = pack2h(dv[0], dv[1], IS_BF16);
+              }
+              if (DKDV) tmem_st16(tT0 + c * 16, pk);
+              tmem_st16(tT1 + c * 16, dk);
+            }
+          }
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(w_full + 8 * hf);
         }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t FMT = IS_BF16 ? 1u : 0u;
-      const uint32_t idesc_kk = make_idesc(FMT, FMT, 0, 0, TILE, TILE);
-      const uint32_t idesc_mn = make_idesc(FMT, FMT, 0, 1, TILE, D);
-      const uint64_t q_desc = make_smem_desc(sQ, 16, 1024);
-      const uint64_t do_desc = make_smem_desc(sDO, 16, 1024);
-      uint32_t it_cnt = 0, cnt = 0;
-      bool ok = true;
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += gridDim.x, ++it_cnt) {
-        const int2 e = p.items[idx / p.H];
-        TileItem it;
-        load_item<false>(it, p.g, e.x, e.y);
-        ok = mbar_wait(wc, qd_full, it_cnt & 1, 801);
         if (!ok) break;
-        const int n = it.n_tiles;
-        for (int j = 0; j < n; ++j, ++cnt) {
-          const int s = cnt % STAGES;
-          const uint32_t par = (cnt / STAGES) & 1;
-          ok = mbar_wait(wc, k_full + 8 * s, par, 802);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t k_desc = make_smem_desc(sK + s * SM::TILE_BYTES, 16, 1024);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
-            mma_ss(tS, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_kk, ks > 0);
-          }
-          ok = mbar_wait(wc, v_full + 8 * s, par, 803);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t v_desc = make_smem_desc(sV + s * SM::TILE_BYTES, 16, 1024);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
-            mma_ss(tDP, desc_advance(do_desc, off), desc_advance(v_desc, off), idesc_kk, ks > 0);
-          }
-          tc_commit(v_empty + 8 * s);
-          tc_commit(sp_full);
-          if (j == 0) {
-            ok = mbar_wait(wc, acc_empty, (it_cnt & 1) ^ 1, 804);
-            if (!ok) break;
-          }
-          ok = mbar_wait(wc, ds_full, cnt & 1, 805);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t k_mn = make_smem_desc(sK + s * SM::TILE_BYTES, SM::CHUNK_BYTES, 1024);
-#pragma unroll
-          for (int ks = 0; ks < TILE / 16; ++ks)
-            mma_ts(tDQ, tDP + ks * 8, desc_advance(k_mn, ks * 2048), idesc_mn, (j > 0 || ks > 0) ? 1u : 0u);
-          tc_commit(k_empty + 8 * s);
-        }
-        if (!ok) break;
-        tc_commit(qd_empty);
-        tc_commit(acc_full);
-      }
-    }
-  } else {
-    const int quad = warp & 3;
-    const int row_in_tile = quad * 32 + lane;
-    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    uint32_t it_cnt = 0, cnt = 0;
-    bool ok = true;
-    const float sc = p.attn_scale ? p.attn_scale[0] : p.inv_n;
-    for (int idx = blockIdx.x; idx < num_items && ok; idx += gridDim.x, ++it_cnt) {
-      const int2 e = p.items[idx / p.H];
-      const int h = idx % p.H;
-      TileItem it;
-      load_item<false>(it, p.g, e.x, e.y);
-      const int L = it.m.L;
-      const int i = it.m0 + row_in_tile;
-      const int id_i = it.m.id(i);
-      for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
-        const int n0 = it.tile_at(j) * TILE;
-        const bool full = tile_pair_is_full(it, n0) && p.bias == nullptr;
-        ok = mbar_wait(wc, sp_full, cnt & 1, 901);
+        // epilogue: the two warpgroups split the accumulator columns in halves
+        ok = mbar_wait(wc, acc_full, it_cnt & 1, 602);
         if (!ok) break;
         tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rs[32], rp[32];
-          tmem_ld32(tS + lane_off + c * 32, rs);
-          tmem_ld32(tDP + lane_off + c * 32, rp);
-          tc_wait_ld();
-          uint32_t dk[16];
-#pragma unroll
-          for (int x = 0; x < 32; x += 2) {
-            float dv[2];
-#pragma unroll
-            for (int y = 0; y < 2; ++y) {
-              const int jj = n0 + c * 32 + x + y;
-              float hh = __uint_as_float(rs[x + y]) * p.half_alpha;
-              if (p.bias != nullptr) {
-                int dist = i > jj ? i - jj : jj - i;
-                if (dist < p.bias_numel) hh += 0.5f * p.bias[dist];
-              }
-              float sl, dsl;
-              silu_and_grad(hh, sl, dsl);
-              float ds = __uint_as_float(rp[x + y]) * dsl;
-              bool valid = full || (i < L && jj < L && it.m.valid_ids(i, jj, id_i, it.m.id(jj)));
-              dv[y] = valid ? ds : 0.f;
-            }
-            dk[x / 2] = pack2h(dv[0], dv[1], IS_BF16);
-          }
-          tmem_st16(tDP + lane_off + c * 16, dk);
+        const bool rv = own < L;
+        const int col0 = hf * (D / 2);
+        if (DKDV) {
+          uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + own) * p.dv_rs + (int64_t)h * p.dv_hs + col0;
+          uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + own) * p.dk_rs + (int64_t)h * p.dk_hs + col0;
+          store_acc_rows<D / 2, IS_BF16>(tmem_base + 256 + col0 + lane_off, sc, dvrow, rv);
+          store_acc_rows<D / 2, IS_BF16>(tmem_base + 384 + col0 + lane_off, sc * p.alpha, dkrow, rv);
+        } else {
+          uint16_t *dqrow = reinterpret_cast<uint16_t *>(p.dq) + (int64_t)(it.start + own) * p.dq_rs + (int64_t)h * p.dq_hs + col0;
+          store_acc_rows<D / 2, IS_BF16>(tmem_base + 256 + col0 + lane_off, sc * p.alpha, dqrow, rv);
         }
-        tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(ds_full);
+        if (lane == 0) mbar_arrive(acc_empty);
+        if (hf == 0 && it.len > L && it.m0 + TILE >= L) {
+          if (DKDV) {
+            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, it.start, L, it.len, row_in_tile);
+            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dv), p.dv_rs, p.dv_hs, h, it.start, L, it.len, row_in_tile);
+          } else {
+            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dq), p.dq_rs, p.dq_hs, h, it.start, L, it.len, row_in_tile);
+          }
+        }
       }
-      if (!ok) break;
-      ok = mbar_wait(wc, acc_full, it_cnt & 1, 902);
-      if (!ok) break;
-      tc_fence_after();
-      uint16_t *dqrow = reinterpret_cast<uint16_t *>(p.dq) + (int64_t)(it.start + i) * p.dq_rs + (int64_t)h * p.dq_hs;
-      store_acc_rows<D, IS_BF16>(tDQ + lane_off, sc * p.alpha, dqrow, i < L);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty);
-      if (it.len > L && it.m0 + TILE >= L)
-        zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dq), p.dq_rs, p.dq_hs, h, it.start, L, it.len, row_in_tile);
     }
   }
 
@@ -600,8 +492,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
 // scratch: two work lists (kv-stationary and q-stationary)
 int64_t attn_tc_bwd_workspace_bytes(const b200_hstu_attn_args &a) {
-  int64_t one = (plan_bytes(a.total_L, a.B) + 255) / 256 * 256;
-  return 2 * one;
+  return 2 * plan_bytes(a.total_L, a.B);
 }
 
 template <int D, bool IS_BF16>
@@ -637,36 +528,36 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.inv_n = 1.f / (float)a.max_seq_len;
   p.H = a.H;
   const int max_items = (int)plan_max_items(a.total_L, a.B);
-  const int64_t one = (plan_bytes(a.total_L, a.B) + 255) / 256 * 256;
+  const int64_t one = plan_bytes(a.total_L, a.B);
   PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(a.workspace);
   PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + one);
-  attn_plan_kernel<true><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr_kv, reinterpret_cast<int2 *>(hdr_kv + 1), max_items);
+  attn_plan_kernel<PLAN_KV_TILE><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), max_items);
   count_launch();
   B200_CHECK_LAUNCH("attention plan (kv)");
-  attn_plan_kernel<false><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr_q, reinterpret_cast<int2 *>(hdr_q + 1), max_items);
+  attn_plan_kernel<PLAN_Q_TILE><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1), max_items);
   count_launch();
   B200_CHECK_LAUNCH("attention plan (q)");
   int64_t upper = (int64_t)max_items * a.H;
   int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {
-    auto kern = hstu_attn_bwd_dkdv_sm100_kernel<D, IS_BF16>;
+    auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
     if (e != cudaSuccess) return check_cuda(e, "backward smem attribute");
     BwdParams pk = p;
     pk.plan = hdr_kv;
-    pk.items = reinterpret_cast<int2 *>(hdr_kv + 1);
+    pk.items = reinterpret_cast<ItemDesc *>(hdr_kv + 1);
     pk.status = &hdr_kv->status;
     kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pk);
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dk, dv)");
   }
   {
-    auto kern = hstu_attn_bwd_dq_sm100_kernel<D, IS_BF16>;
+    auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
     if (e != cudaSuccess) return check_cuda(e, "backward smem attribute");
     BwdParams pq = p;
     pq.plan = hdr_q;
-    pq.items = reinterpret_cast<int2 *>(hdr_q + 1);
+    pq.items = reinterpret_cast<ItemDesc *>(hdr_q + 1);
     pq.status = &hdr_q->status;
     kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pq);
     count_launch();

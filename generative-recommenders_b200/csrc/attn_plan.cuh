@@ -1,10 +1,17 @@
-// Work planning for the persistent tensor-core attention kernels.
+// Work planning and tile geometry for the persistent tensor-core attention kernels.
 //
-// A tiny one-CTA kernel turns seq_offsets / num_targets into a list of (sequence, 128-row tile)
-// work items ordered longest-first (counting sort on the number of opposite-side tiles an item
-// has to visit).  Persistent CTAs then take items blockIdx.x, blockIdx.x + gridDim.x, ... so the
-// expensive tiles of long sequences are spread over all SMs first and the cheap ones fill the
-// tail.  The list lives in caller-provided scratch; nothing in it needs initialisation.
+// A tiny one-CTA kernel turns seq_offsets / num_targets into a list of work items ordered
+// longest-first (counting sort on the number of opposite-side tiles an item has to visit).  Each
+// item is a self-contained 32-byte descriptor (sequence, tile, first row, length, targets), so a
+// persistent CTA needs one load per item and can fetch the next descriptor while it works on the
+// current one.  Persistent CTAs take items blockIdx.x, blockIdx.x + gridDim.x, ... which spreads
+// the expensive tiles of long sequences over all SMs first and lets the cheap ones fill the tail.
+// The list lives in caller-provided scratch; nothing in it needs initialisation.
+//
+// Item kinds:
+//   PLAN_Q_PAIR  forward: two consecutive 128-row query tiles of one sequence (they share K/V)
+//   PLAN_Q_TILE  backward dQ: one 128-row query tile
+//   PLAN_KV_TILE backward dK/dV: one 128-row key/value tile
 #pragma once
 
 #include "common.cuh"
@@ -15,10 +22,18 @@ constexpr int TILE = 128;          // rows of a query tile == rows of a key/valu
 constexpr int PLAN_BUCKETS = 1024; // cost buckets of the counting sort
 constexpr int PLAN_THREADS = 1024;
 
+enum PlanKind { PLAN_Q_PAIR = 0, PLAN_Q_TILE = 1, PLAN_KV_TILE = 2 };
+
 struct PlanHeader {
-  int num_items;   // number of (sequence, tile) items
+  int num_items;   // number of work items
   int status;      // 0 = ok, else the site id of the first bounded wait that gave up
   int pad[2];
+};
+
+struct __align__(16) ItemDesc {
+  int b, t;            // sequence, tile (or tile-pair) index inside the sequence
+  int start, len, nt;  // first token row, untruncated length, number of targets
+  int pad[3];
 };
 
 struct AttnGeomParams {
@@ -32,25 +47,33 @@ struct TileItem {
   int m0;                 // first row of the tile inside the sequence
   SeqMask m;
   int t_lo, n_main;       // opposite-side tiles [t_lo, t_lo + n_main)
-  int extra_tile;         // >= 0: one more tile outside the main range (target rows' own diagonal)
+  int extra_tile;         // >= 0: one more tile outside the main range
   int n_tiles;
   int u;                  // first target position
-  bool regular;           // tile classification shortcuts are valid
+  bool regular;           // closed-form row intervals / tile classification are valid
   __host__ __device__ __forceinline__ int tile_at(int j) const { return j < n_main ? t_lo + j : extra_tile; }
+  __host__ __device__ __forceinline__ bool visits(int t) const {
+    return (t >= t_lo && t < t_lo + n_main) || t == extra_tile;
+  }
 };
 
-// kv tiles that the query tile `mt` of sequence `b` visits
-__host__ __device__ __forceinline__ void fill_q_item(TileItem &it, const AttnGeomParams &g, int b, int mt, int start,
+__host__ __device__ __forceinline__ void fill_common(TileItem &it, const AttnGeomParams &g, int b, int t, int start,
                                                      int len, int nt) {
   it.b = b;
-  it.mt = mt;
+  it.mt = t;
   it.start = start;
   it.len = len;
   it.nt = nt;
-  it.m0 = mt * TILE;
-  it.m = make_seq_mask(it.len, g.max_seq_len, it.nt, g.c, g.W, g.F);
-  it.u = it.len - it.nt;
-  it.regular = (it.u >= g.c + 1) && (it.nt >= 0) && (it.len <= it.m.L);
+  it.m0 = t * TILE;
+  it.m = make_seq_mask(len, g.max_seq_len, nt, g.c, g.W, g.F);
+  it.u = len - nt;
+  it.regular = (it.u >= g.c + 1) && (nt >= 0) && (len <= it.m.L);
+}
+
+// kv tiles that the query tile `mt` of a sequence visits
+__host__ __device__ __forceinline__ void fill_q_item(TileItem &it, const AttnGeomParams &g, int b, int mt, int start,
+                                                     int len, int nt) {
+  fill_common(it, g, b, mt, start, len, nt);
   KvRange r = kv_range_for_q_tile(it.m, it.len, it.nt, it.m0, TILE);
   it.t_lo = r.lo / TILE;
   int t_hi = (r.hi + TILE - 1) / TILE;
@@ -82,19 +105,11 @@ __host__ __device__ __forceinline__ bool tile_pair_is_full(const TileItem &it, i
   return true;
 }
 
-// q tiles that the kv tile `nt_` of a sequence has to visit (backward, kv-stationary): a
+// q tiles that the kv tile `kt` of a sequence has to visit (backward, kv-stationary): a
 // conservative contiguous range [t_lo, t_hi) plus, when contextual rows exist, tile 0.
 __host__ __device__ __forceinline__ void fill_kv_item(TileItem &it, const AttnGeomParams &g, int b, int kt, int start,
                                                       int len, int nt) {
-  it.b = b;
-  it.mt = kt;
-  it.start = start;
-  it.len = len;
-  it.nt = nt;
-  it.m0 = kt * TILE;
-  it.m = make_seq_mask(it.len, g.max_seq_len, it.nt, g.c, g.W, g.F);
-  it.u = it.len - it.nt;
-  it.regular = (it.u >= g.c + 1) && (it.nt >= 0) && (it.len <= it.m.L);
+  fill_common(it, g, b, kt, start, len, nt);
   const int L = it.m.L;
   const int ntiles = (L + TILE - 1) / TILE;
   int t_lo = kt, t_hi = ntiles;
@@ -126,7 +141,7 @@ __host__ __device__ __forceinline__ void fill_kv_item(TileItem &it, const AttnGe
       if (t_hi < kt + 1) t_hi = kt + 1;
       if (t_hi > ntiles) t_hi = ntiles;
     }
-    if (g.c > 0 && kt > 0) it.extra_tile = 0;  // contextual rows (tile 0) see every non-target column
+    if (g.c > 0 && kt > 0 && n0 < it.u) it.extra_tile = 0;  // contextual rows see every non-target column
   }
   it.t_lo = t_lo;
   it.n_main = t_hi - t_lo;
@@ -134,8 +149,159 @@ __host__ __device__ __forceinline__ void fill_kv_item(TileItem &it, const AttnGe
   it.n_tiles = it.n_main + (it.extra_tile >= 0 ? 1 : 0);
 }
 
-template <bool KV_STATIONARY>
-__global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams g, PlanHeader *hdr, int2 *items,
+// ---------------------------------------------------------------------------------------
+// Two consecutive query tiles A (2p) and B (2p+1) that walk the union of their kv tiles
+// ---------------------------------------------------------------------------------------
+struct PairItem {
+  TileItem A, B;
+  bool hasB;
+  int t_lo, n_main;
+  int extra0, extra1;   // up to two tiles outside the main range (target rows' own diagonal blocks)
+  int n_extra;
+  int n_tiles;
+  __host__ __device__ __forceinline__ int tile_at(int j) const {
+    return j < n_main ? t_lo + j : (j == n_main ? extra0 : extra1);
+  }
+};
+
+__host__ __device__ __forceinline__ void fill_pair_item(PairItem &p, const AttnGeomParams &g, int b, int pair,
+                                                        int start, int len, int nt) {
+  fill_q_item(p.A, g, b, 2 * pair, start, len, nt);
+  const int ntiles = (p.A.m.L + TILE - 1) / TILE;
+  p.hasB = (2 * pair + 1) < ntiles;
+  int lo = p.A.t_lo, hi = p.A.t_lo + p.A.n_main;
+  if (p.hasB) {
+    fill_q_item(p.B, g, b, 2 * pair + 1, start, len, nt);
+    lo = p.B.t_lo < lo ? p.B.t_lo : lo;
+    int bh = p.B.t_lo + p.B.n_main;
+    hi = bh > hi ? bh : hi;
+  } else {
+    p.B = p.A;
+    p.B.n_main = 0;
+    p.B.extra_tile = -1;
+    p.B.n_tiles = 0;
+  }
+  p.t_lo = lo;
+  p.n_main = hi - lo;
+  p.n_extra = 0;
+  p.extra0 = p.extra1 = -1;
+  int ea = p.A.extra_tile, eb = p.hasB ? p.B.extra_tile : -1;
+  if (ea >= 0 && (ea < lo || ea >= hi)) {
+    p.extra0 = ea;
+    p.n_extra = 1;
+  }
+  if (eb >= 0 && (eb < lo || eb >= hi) && eb != ea) {
+    if (p.n_extra == 0) p.extra0 = eb; else p.extra1 = eb;
+    ++p.n_extra;
+  }
+  p.n_tiles = p.n_main + p.n_extra;
+}
+
+// ---------------------------------------------------------------------------------------
+// Closed-form mask of one query row on the regular domain: the valid columns of row i are
+//   [lo, hi)  united with  [0, ctx_hi)  united with  {i}
+// (history window, contextual prefix, self).  Equals SeqMask::valid() for every column < L.
+// ---------------------------------------------------------------------------------------
+struct RowInterval {
+  int lo, hi, ctx_hi, self;
+};
+
+__host__ __device__ __forceinline__ RowInterval row_interval(const TileItem &it, int i) {
+  RowInterval r;
+  const int c = it.m.c, W = it.m.W, F = it.m.F, u = it.u;
+  r.self = i;
+  if (i < c) {  // contextual row: everything before the targets
+    r.lo = 0;
+    r.hi = u;
+    r.ctx_hi = 0;
+    return r;
+  }
+  const bool tgt = i >= u;
+  const int eff = tgt ? u : i;
+  const bool full = (W == 0) || (F > 0 && (tgt || i >= u - F));
+  r.hi = tgt ? u : i + 1;
+  int lo = full ? c : eff - W;
+  r.lo = lo < c ? c : lo;
+  const bool ctx_ok = full || (eff - c + 1 <= W);
+  r.ctx_hi = ctx_ok ? (c < r.hi ? c : r.hi) : 0;
+  return r;
+}
+
+__host__ __device__ __forceinline__ uint32_t low_bits(int n) {  // n clamped to [0, 32] -> n low bits set
+  n = n < 0 ? 0 : n;
+  return n >= 32 ? 0xffffffffu : ((1u << n) - 1u);
+}
+
+// validity bits of columns base .. base+31 for the row described by r (columns >= L are cleared)
+__host__ __device__ __forceinline__ uint32_t row_mask_bits(const RowInterval &r, int base, int L) {
+  uint32_t bits = low_bits(r.hi - base) & ~low_bits(r.lo - base);
+  bits |= low_bits(r.ctx_hi - base);
+  int d = r.self - base;
+  if (d >= 0 && d < 32) bits |= 1u << d;
+  return bits & low_bits(L - base);
+}
+
+// The transposed view for the K/V-stationary backward: the valid query rows of key column j are
+//   [a1, b1)  u  [a2, b2)  u  [0, c3)  u  [a4, L)  u  {j}
+// (history rows inside the window, history rows of the full-attention tail, contextual rows,
+// target rows).  Equals SeqMask::valid(i, j) for every row < L on the regular domain.
+struct ColInterval {
+  int a1, b1, a2, b2, c3, a4, self;
+};
+
+__host__ __device__ __forceinline__ ColInterval col_interval(const TileItem &it, int j) {
+  ColInterval r;
+  const int c = it.m.c, W = it.m.W, F = it.m.F, u = it.u, L = it.m.L;
+  r.self = j;
+  r.a1 = r.b1 = r.a2 = r.b2 = 0;
+  r.c3 = 0;
+  r.a4 = L;
+  if (j >= u) return r;  // a target column is seen by its own row only
+  const int jc = j > c - 1 ? j : c - 1;  // contextual columns behave like position c - 1 for the window
+  int lo1 = jc + 1 > c ? jc + 1 : c;
+  r.a1 = lo1;
+  r.b1 = (W == 0) ? u : (jc + W + 1 < u ? jc + W + 1 : u);
+  if (W > 0 && F > 0) {
+    r.a2 = lo1 > u - F ? lo1 : u - F;
+    r.b2 = u;
+  }
+  r.c3 = c;
+  if (W == 0 || F > 0 || u - jc <= W) r.a4 = u;
+  return r;
+}
+
+__host__ __device__ __forceinline__ uint32_t range_bits(int a, int b, int base) {
+  return low_bits(b - base) & ~low_bits(a - base);
+}
+
+// validity bits of query rows base .. base+31 for the key column described by r
+__host__ __device__ __forceinline__ uint32_t col_mask_bits(const ColInterval &r, int base, int L) {
+  uint32_t bits = range_bits(r.a1, r.b1, base) | range_bits(r.a2, r.b2, base) | low_bits(r.c3 - base) |
+                  range_bits(r.a4, L, base);
+  int d = r.self - base;
+  if (d >= 0 && d < 32) bits |= 1u << d;
+  return bits & low_bits(L - base);
+}
+
+template <int KIND>
+__host__ __device__ __forceinline__ int item_cost(const AttnGeomParams &g, int b, int t, int len, int nt) {
+  if (KIND == PLAN_Q_PAIR) {
+    PairItem p;
+    fill_pair_item(p, g, b, t, 0, len, nt);
+    return p.A.n_tiles + p.B.n_tiles;
+  } else if (KIND == PLAN_Q_TILE) {
+    TileItem it;
+    fill_q_item(it, g, b, t, 0, len, nt);
+    return it.n_tiles;
+  } else {
+    TileItem it;
+    fill_kv_item(it, g, b, t, 0, len, nt);
+    return it.n_tiles;
+  }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams g, PlanHeader *hdr, ItemDesc *items,
                                                                  int max_items) {
   __shared__ int hist[PLAN_BUCKETS];
   __shared__ int total;
@@ -144,30 +310,32 @@ __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams 
   __syncthreads();
   for (int pass = 0; pass < 2; ++pass) {
     for (int b = threadIdx.x; b < g.B; b += PLAN_THREADS) {
-      int len = g.seq_offsets[b + 1] - g.seq_offsets[b];
-      int L = len < g.max_seq_len ? len : g.max_seq_len;
-      int ntiles = (L + TILE - 1) / TILE;
-      for (int t = 0; t < ntiles; ++t) {
-        TileItem it;
-        int nt = g.num_targets ? g.num_targets[b] : 0;
-        if (KV_STATIONARY)
-          fill_kv_item(it, g, b, t, 0, len, nt);
-        else
-          fill_q_item(it, g, b, t, 0, len, nt);
-        int cost = it.n_tiles < PLAN_BUCKETS - 1 ? it.n_tiles : PLAN_BUCKETS - 1;
-        int bucket = PLAN_BUCKETS - 1 - cost;  // expensive first
+      const int start = g.seq_offsets[b];
+      const int len = g.seq_offsets[b + 1] - start;
+      const int nt = g.num_targets ? g.num_targets[b] : 0;
+      const int L = len < g.max_seq_len ? len : g.max_seq_len;
+      const int ntiles = (L + TILE - 1) / TILE;
+      const int nunits = KIND == PLAN_Q_PAIR ? (ntiles + 1) / 2 : ntiles;
+      for (int t = 0; t < nunits; ++t) {
+        int cost = item_cost<KIND>(g, b, t, len, nt);
+        cost = cost < PLAN_BUCKETS - 1 ? cost : PLAN_BUCKETS - 1;
+        const int bucket = PLAN_BUCKETS - 1 - cost;  // expensive first
         if (pass == 0) {
           atomicAdd(&hist[bucket], 1);
         } else {
           int pos = atomicAdd(&hist[bucket], 1);
-          if (pos < max_items) items[pos] = make_int2(b, t);
+          if (pos < max_items) {
+            ItemDesc d;
+            d.b = b; d.t = t; d.start = start; d.len = len; d.nt = nt;
+            d.pad[0] = d.pad[1] = d.pad[2] = 0;
+            items[pos] = d;
+          }
         }
       }
     }
     __syncthreads();
     if (pass == 0) {
-      // exclusive prefix sum over the buckets (single thread: 1024 adds)
-      if (threadIdx.x == 0) {
+      if (threadIdx.x == 0) {  // exclusive prefix sum over the buckets
         int run = 0;
         for (int i = 0; i < PLAN_BUCKETS; ++i) {
           int c = hist[i];
@@ -186,21 +354,19 @@ __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams 
   }
 }
 
-// device-side convenience: read the sequence geometry, then fill
-template <bool KV_STATIONARY>
-__device__ __forceinline__ void load_item(TileItem &it, const AttnGeomParams &g, int b, int t) {
-  int start = g.seq_offsets[b];
-  int len = g.seq_offsets[b + 1] - start;
-  int nt = g.num_targets ? g.num_targets[b] : 0;
-  if (KV_STATIONARY)
-    fill_kv_item(it, g, b, t, start, len, nt);
-  else
-    fill_q_item(it, g, b, t, start, len, nt);
+__device__ __forceinline__ ItemDesc load_desc(const ItemDesc *items, int idx) {
+  const int4 *p4 = reinterpret_cast<const int4 *>(items + idx);
+  int4 a = __ldg(p4), b = __ldg(p4 + 1);
+  ItemDesc d;
+  d.b = a.x; d.t = a.y; d.start = a.z; d.len = a.w; d.nt = b.x;
+  d.pad[0] = d.pad[1] = d.pad[2] = 0;
+  return d;
 }
 
 inline int64_t plan_max_items(int64_t total_L, int B) { return total_L / TILE + B + 1; }
 inline int64_t plan_bytes(int64_t total_L, int B) {
-  return (int64_t)sizeof(PlanHeader) + plan_max_items(total_L, B) * (int64_t)sizeof(int2);
+  int64_t n = (int64_t)sizeof(PlanHeader) + plan_max_items(total_L, B) * (int64_t)sizeof(ItemDesc);
+  return (n + 255) / 256 * 256;
 }
 
 }  // namespace b200hstu

@@ -206,6 +206,11 @@ void b200_hstu_host_kv_range(int32_t len, int32_t num_targets, int32_t max_seq_l
 void b200_hstu_host_bwd_q_tiles(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
                                 int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t kt, int32_t *t_lo,
                                 int32_t *n_main, int32_t *extra_tile);
+/* mask(i, j) from the closed-form row (transposed = 0) / column (transposed = 1) intervals used on
+   partially visible tiles; -1 when the closed form does not apply to this sequence. */
+int b200_hstu_host_interval_mask(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
+                                 int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t i, int32_t j,
+                                 int32_t transposed);
 int b200_hstu_host_mask(int32_t len, int32_t num_targets, int32_t max_seq_len, int32_t contextual_seq_len,
                         int32_t max_attn_len, int32_t min_full_attn_seq_len, int32_t i, int32_t j);
 

@@ -130,3 +130,26 @@ def test_backward_tile_rule_never_drops_a_valid_pair():
             assert need <= visited, (L, t, c, W, F, kt, sorted(need), sorted(visited))
             skipped += ntiles - len(visited)
     assert skipped > 0
+
+
+def test_closed_form_row_and_column_masks_equal_the_exact_mask():
+    """The per-row / per-column interval masks of the tensor-core kernels == the reference mask."""
+    lib = _cabi.lib()
+    rng = random.Random(5)
+    checked = 0
+    for _ in range(250):
+        N = 80
+        L = rng.randint(1, N)
+        c = rng.choice([0, 0, 1, 3, 6])
+        t = rng.randint(0, max(0, min(L - 1, 12)))
+        W = rng.choice([0, 0, 1, 5, 17, 60])
+        F = rng.choice([0, 0, 4, 9]) if W > 0 else 0
+        mask = O.valid_attn_mask(L, t, True, W, c, F)
+        for tr in (0, 1):
+            got = [[lib.b200_hstu_host_interval_mask(L, t, N, c, W, F, i, j, tr) for j in range(L)] for i in range(L)]
+            if got[0][0] == -1:
+                assert L - t < c + 1
+                continue
+            assert torch.equal(torch.tensor(got, dtype=torch.bool), mask), (L, t, c, W, F, tr)
+            checked += 1
+    assert checked > 300
