@@ -4,6 +4,7 @@ kernels in libb200_hstu.so (C ABI in include/b200_hstu.h)."""
 from . import _cabi
 from .common import HammerKernel
 from .hstu_attention import hstu_mha, set_attention_impl
+from .hstu_attention_fp8 import hstu_mha_fp8, quantize_e4m3_block
 from .hstu_compute import (
     hstu_compute_output,
     hstu_compute_uqvk,
@@ -16,6 +17,8 @@ from .mm import addmm
 __all__ = [
     "HammerKernel",
     "hstu_mha",
+    "hstu_mha_fp8",
+    "quantize_e4m3_block",
     "hstu_compute_uqvk",
     "hstu_compute_output",
     "hstu_norm_mul_dropout",

@@ -531,12 +531,10 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   const int64_t one = plan_bytes(a.total_L, a.B);
   PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(a.workspace);
   PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + one);
-  attn_plan_kernel<PLAN_KV_TILE><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), max_items);
+  attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
+      p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1), max_items);
   count_launch();
-  B200_CHECK_LAUNCH("attention plan (kv)");
-  attn_plan_kernel<PLAN_Q_TILE><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1), max_items);
-  count_launch();
-  B200_CHECK_LAUNCH("attention plan (q)");
+  B200_CHECK_LAUNCH("attention plan (backward)");
   int64_t upper = (int64_t)max_items * a.H;
   int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {

@@ -19,13 +19,4 @@ int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, bool bwd) {
   return bwd ? attn_tc_bwd_workspace_bytes(a) : attn_tc_fwd_workspace_bytes(a);
 }
 
-int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &, cudaStream_t) {
-  return fail(B200_HSTU_EUNSUPPORTED, "fp8 forward is not built yet");
-}
-
-int quantize_e4m3_block(const void *, int, int64_t, int64_t, void *, float *, const int32_t *, const int32_t *, int,
-                        int, int, int64_t, int, cudaStream_t) {
-  return fail(B200_HSTU_EUNSUPPORTED, "fp8 quantiser is not built yet");
-}
-
 }  // namespace b200hstu

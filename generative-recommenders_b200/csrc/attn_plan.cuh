@@ -301,9 +301,10 @@ __host__ __device__ __forceinline__ int item_cost(const AttnGeomParams &g, int b
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams g, PlanHeader *hdr, ItemDesc *items,
-                                                                 int max_items) {
+__device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *hdr, ItemDesc *items, int max_items) {
+  static_assert(PLAN_BUCKETS == PLAN_THREADS, "one bucket per thread in the scan");
   __shared__ int hist[PLAN_BUCKETS];
+  __shared__ int warp_sums[32];
   __shared__ int total;
   for (int i = threadIdx.x; i < PLAN_BUCKETS; i += PLAN_THREADS) hist[i] = 0;
   if (threadIdx.x == 0) total = 0;
@@ -335,15 +336,30 @@ __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams 
     }
     __syncthreads();
     if (pass == 0) {
-      if (threadIdx.x == 0) {  // exclusive prefix sum over the buckets
-        int run = 0;
-        for (int i = 0; i < PLAN_BUCKETS; ++i) {
-          int c = hist[i];
-          hist[i] = run;
-          run += c;
-        }
-        total = run;
+      // exclusive prefix sum over the buckets: one bucket per thread, warp scans + scan of warp sums
+      const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+      const int mine = hist[threadIdx.x];
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
       }
+      if (lane == 31) warp_sums[wid] = incl;
+      __syncthreads();
+      if (wid == 0) {
+        int ws = warp_sums[lane];
+        int wincl = ws;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          int v = __shfl_up_sync(0xffffffffu, wincl, o);
+          if (lane >= o) wincl += v;
+        }
+        warp_sums[lane] = wincl - ws;  // exclusive offset of each warp
+        if (lane == 31) total = wincl;
+      }
+      __syncthreads();
+      hist[threadIdx.x] = warp_sums[wid] + incl - mine;
       __syncthreads();
     }
   }
@@ -352,6 +368,22 @@ __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams 
     hdr->status = 0;
     hdr->pad[0] = hdr->pad[1] = 0;
   }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams g, PlanHeader *hdr, ItemDesc *items,
+                                                                 int max_items) {
+  plan_body<KIND>(g, hdr, items, max_items);
+}
+
+// two work lists in one launch (one CTA each): the backward's K/V-tile and query-tile lists
+template <int KIND0, int KIND1>
+__global__ void __launch_bounds__(PLAN_THREADS) attn_plan2_kernel(AttnGeomParams g, PlanHeader *hdr0, ItemDesc *items0,
+                                                                  PlanHeader *hdr1, ItemDesc *items1, int max_items) {
+  if (blockIdx.x == 0)
+    plan_body<KIND0>(g, hdr0, items0, max_items);
+  else
+    plan_body<KIND1>(g, hdr1, items1, max_items);
 }
 
 __device__ __forceinline__ ItemDesc load_desc(const ItemDesc *items, int idx) {

@@ -1,0 +1,65 @@
+"""FP8 (e4m3, per-128-token-block scales) forward against the fp32 oracle.
+
+Two comparisons: against the oracle run on the de-quantised tensors (what the kernel should
+compute: bf16-level agreement), and against the oracle on the unquantised tensors (the acceptance
+bound rel-L2 <= 5e-2)."""
+
+import pytest
+import torch
+
+import generative_recommenders_b200 as G
+from generative_recommenders_b200 import workloads as W
+from oracle import hstu_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def test_block_quantiser_matches_oracle():
+    g = torch.Generator().manual_seed(0)
+    lengths = torch.tensor([5, 0, 300, 131, 128])
+    offs = W._offsets(lengths)
+    x = torch.randn(int(offs[-1]), 2, 128, generator=g).bfloat16()
+    x8, sc, bo = G.quantize_e4m3_block(x.to(DEV), offs.to(DEV))
+    r8, rsc, rbo = O.quantize_e4m3_block(x.float(), offs)
+    assert bo.cpu().tolist() == rbo.tolist()
+    n = int(rbo[-1])
+    torch.testing.assert_close(sc[:n].cpu(), rsc, rtol=1e-6, atol=0)
+    assert torch.equal(x8.cpu().view(torch.uint8), r8.view(torch.uint8))
+
+
+@pytest.mark.parametrize("case", [
+    # lengths, targets, window, ctx
+    ([128], None, 0, 0),
+    ([384], None, 0, 0),
+    ([100, 300, 1, 257], None, 0, 0),
+    ([400, 700, 330], [256, 256, 256], 300, 0),
+    ([200, 500, 129], [7, 30, 2], 90, 3),
+])
+def test_fp8_forward(case):
+    lengths, nt, Wn, ctx = case
+    g = torch.Generator().manual_seed(sum(lengths))
+    lengths = torch.tensor(lengths)
+    offs = W._offsets(lengths)
+    L, H, d, N = int(offs[-1]), 2, 128, 1024
+    q = torch.randn(L, H, d, generator=g); k = torch.randn(L, H, d, generator=g); v = torch.randn(L, H, d, generator=g)
+    ntt = None if nt is None else torch.tensor(nt)
+    offs_d = offs.to(DEV)
+    q8, qs, bo = G.quantize_e4m3_block(q.to(DEV), offs_d)
+    k8, ks, _ = G.quantize_e4m3_block(k.to(DEV), offs_d)
+    v8, vs, _ = G.quantize_e4m3_block(v.to(DEV), offs_d)
+    out = G.hstu_mha_fp8(N, 1.0 / 128, q8, k8, v8, qs, ks, vs, bo, offs_d,
+                         num_targets=None if ntt is None else ntt.to(DEV), max_attn_len=Wn, contextual_seq_len=ctx)
+    torch.cuda.synchronize()
+    nblk = int(bo[-1])
+    deq = [O.dequantize_e4m3_block(t8.cpu(), s[:nblk].cpu(), bo.cpu().long(), offs)
+           for t8, s in ((q8, qs), (k8, ks), (v8, vs))]
+    ref_q = O.hstu_mha(N, 1.0 / 128, deq[0], deq[1], deq[2], offs, num_targets=ntt, max_attn_len=Wn,
+                       contextual_seq_len=ctx)
+    ref = O.hstu_mha(N, 1.0 / 128, q, k, v, offs, num_targets=ntt, max_attn_len=Wn, contextual_seq_len=ctx)
+    e_kernel = O.rel_l2(out, ref_q)
+    e_total = O.rel_l2(out, ref)
+    print("fp8 kernel-vs-dequantised %.4f, vs unquantised %.4f" % (e_kernel, e_total))
+    assert torch.isfinite(out.float()).all()
+    assert e_kernel < 1e-2, e_kernel   # arithmetic of the kernel itself: bf16-level
+    assert e_total < 5e-2, e_total     # acceptance bound for fp8 against the unquantised fp32 result
