@@ -178,7 +178,9 @@ def run_ours(args):
     launches = _cabi.launch_count() - launches0
     ms_total = sum(s.elapsed_time(e) for s, e in ev)
 
-    # ---- forward / backward kernels separately (for the roofline of the dominant kernel)
+    # ---- forward / backward separately, with the library's per-kernel event timing switched on
+    # (CUDA events recorded by the library around each kernel on the launch stream)
+    _cabi.profile_enable(True)
     fe = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(min(args.steps, 50))]
     for a, b, c in fe:
@@ -198,6 +200,12 @@ def run_ours(args):
     torch.cuda.synchronize()
     fwd_ms = sorted(a.elapsed_time(b) for a, b, c in fe)[len(fe) // 2]
     bwd_ms = sorted(b.elapsed_time(c) for a, b, c in fe)[len(fe) // 2]
+    kernel_ms = {}
+    for kind in ("plan", "attn_fwd", "attn_bwd_dkdv", "attn_bwd_dq"):
+        v = _cabi.profile_collect(kind)
+        if v:
+            kernel_ms[kind] = sum(v) / len(v)
+    _cabi.profile_enable(False)
 
     # ---- end to end through the public API from pinned host memory
     e2e_steps = max(3, min(args.steps, 20))
@@ -241,17 +249,35 @@ def run_ours(args):
     e2e_value = mult * flops_fwd_all / (e2e_ms * 1e-3) / 1e12
 
     peaks, peak_kind = load_peaks()
-    # dominant kernel of the step and its roofline (per GPU: rank 0's share of the work)
+    # dominant kernel of the step and its roofline (rank 0's share of the work).  Algorithmic FLOPs
+    # per launch with F = 4*H*d*sum(L^2)/2: forward F (two GEMMs); backward dK/dV kernel 2F (S^T, dP^T,
+    # dV, dK); backward dQ kernel 0.5F (the dQ GEMM; its recomputation of S and dP is overhead of the
+    # two-kernel design and is not counted).
     exact_fwd = 4.0 * w.num_heads * w.attn_dim * w.exact_pairs()
-    if fwd_only or fwd_ms >= bwd_ms:
-        dom, dom_ms, dom_flops = "hstu_attn_fwd_sm100_kernel", fwd_ms, flops_fwd
-    else:
-        dom, dom_ms, dom_flops = "attention backward", bwd_ms, 2.5 * flops_fwd
+    algo = {"attn_fwd": 1.0, "attn_bwd_dkdv": 2.0, "attn_bwd_dq": 0.5}
+    names = {"attn_fwd": "hstu_attn_fwd_sm100_kernel", "attn_bwd_dkdv": "hstu_attn_bwd_sm100_kernel<DKDV=true>",
+             "attn_bwd_dq": "hstu_attn_bwd_sm100_kernel<DKDV=false>"}
+    cand = {k_: v_ for k_, v_ in kernel_ms.items() if k_ in algo}
+    if cand:
+        dom = max(cand, key=cand.get)
+        dom_ms, dom_flops, dom_name = cand[dom], algo[dom] * flops_fwd, names[dom]
+    else:  # CUDA-core path (no per-kernel events): fall back to the step halves
+        dom_name, dom_ms, dom_flops = ("attention forward", fwd_ms, flops_fwd) if (fwd_only or fwd_ms >= bwd_ms) \
+            else ("attention backward", bwd_ms, 2.5 * flops_fwd)
     ach = dom_flops / (dom_ms * 1e-3) / 1e12
-    roofline = {"kernel": dom, "bound": "tensor", "achieved": round(ach, 2), "peak": peaks["bf16_tflops"],
-                "unit": "TFLOP/s", "frac": round(ach / peaks["bf16_tflops"], 4), "traffic": None,
-                "peak_source": peak_kind, "launch_ms": round(dom_ms, 4),
-                "flops_model": "nominal causal 4*H*d*sum(L^2)/2 (x2.5 for backward)"}
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(tpath):
+        try:
+            traffic = json.load(open(tpath)).get(dom_name, {}).get(w.name)
+        except Exception:
+            traffic = None
+    roofline = {"kernel": dom_name, "bound": "tensor", "achieved": round(ach, 2), "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": round(ach / peaks["bf16_tflops"], 4), "traffic": traffic,
+                "peak_source": peak_kind + " (cuBLAS bf16 burst)", "launch_ms": round(dom_ms, 4),
+                "flops_per_launch": dom_flops,
+                "flops_model": "nominal causal F = 4*H*d*sum(L^2)/2; fwd F, bwd dK/dV kernel 2F, bwd dQ kernel 0.5F",
+                "kernel_ms": {k_: round(v_, 4) for k_, v_ in kernel_ms.items()}}
 
     out = None
     if rank == 0:

@@ -35,6 +35,8 @@ EXPORTS = [
     "b200_hstu_host_mask",
     "b200_hstu_host_bwd_q_tiles",
     "b200_hstu_host_interval_mask",
+    "b200_hstu_profile_enable",
+    "b200_hstu_profile_collect",
 ]
 
 
@@ -144,6 +146,10 @@ def lib():
     L.b200_hstu_host_kv_range.restype = None
     L.b200_hstu_host_bwd_q_tiles.argtypes = [c_int32] * 7 + [POINTER(c_int32)] * 3
     L.b200_hstu_host_bwd_q_tiles.restype = None
+    L.b200_hstu_profile_enable.argtypes = [ctypes.c_int]
+    L.b200_hstu_profile_enable.restype = None
+    L.b200_hstu_profile_collect.argtypes = [ctypes.c_int, POINTER(c_float), ctypes.c_int]
+    L.b200_hstu_profile_collect.restype = ctypes.c_int
     L.b200_hstu_host_interval_mask.argtypes = [c_int32] * 9
     L.b200_hstu_host_interval_mask.restype = ctypes.c_int
     L.b200_hstu_host_mask.argtypes = [c_int32] * 8
@@ -162,3 +168,21 @@ def check(status, what):
 
 def launch_count():
     return int(lib().b200_hstu_launch_count())
+
+
+PROFILE_KINDS = {
+    "plan": 0, "attn_fwd": 1, "attn_bwd_dkdv": 2, "attn_bwd_dq": 3, "attn_fwd_fp8": 4, "layer_norm_fwd": 5,
+    "layer_norm_bwd": 6, "silu": 7, "norm_mul_fwd": 8, "norm_mul_bwd": 9, "quantize": 10, "attn_simt": 11,
+}
+
+
+def profile_enable(on: bool) -> None:
+    lib().b200_hstu_profile_enable(1 if on else 0)
+
+
+def profile_collect(kind: str):
+    """Durations (ms) of the launches of one kernel kind since profiling was enabled; call after
+    a device synchronisation."""
+    buf = (c_float * 512)()
+    n = lib().b200_hstu_profile_collect(PROFILE_KINDS[kind], buf, 512)
+    return [buf[i] for i in range(n)]

@@ -30,6 +30,37 @@ int check_cuda(cudaError_t e, const char *what) {
   return (int)e;
 }
 
+// ---------------------------------------------------------------------------------------
+// per-kernel event timing (off by default)
+// ---------------------------------------------------------------------------------------
+namespace {
+constexpr int PROF_RING = 512;
+struct ProfileState {
+  bool on = false;
+  cudaEvent_t start[PROF_KINDS][PROF_RING];
+  cudaEvent_t stop[PROF_KINDS][PROF_RING];
+  bool created[PROF_KINDS][PROF_RING] = {};
+  int count[PROF_KINDS] = {};
+};
+ProfileState g_prof;
+}  // namespace
+
+ProfileScope::ProfileScope(int kind_, cudaStream_t st_) : kind(kind_), st(st_), stop(nullptr) {
+  if (!g_prof.on || kind < 0 || kind >= PROF_KINDS) return;
+  int slot = g_prof.count[kind] % PROF_RING;
+  if (!g_prof.created[kind][slot]) {
+    cudaEventCreate(&g_prof.start[kind][slot]);
+    cudaEventCreate(&g_prof.stop[kind][slot]);
+    g_prof.created[kind][slot] = true;
+  }
+  cudaEventRecord(g_prof.start[kind][slot], st);
+  stop = g_prof.stop[kind][slot];
+  ++g_prof.count[kind];
+}
+ProfileScope::~ProfileScope() {
+  if (stop != nullptr) cudaEventRecord(stop, st);
+}
+
 // implemented in the kernel translation units
 int attn_simt(const b200_hstu_attn_args &a, cudaStream_t st, bool bwd);
 bool attn_tc_applicable(const b200_hstu_attn_args &a, bool bwd, const char **why);
@@ -208,6 +239,24 @@ int b200_hstu_norm_mul_bwd(const b200_hstu_norm_mul_args *a, b200_hstu_stream_t 
 
 int64_t b200_hstu_norm_mul_bwd_workspace_bytes(int32_t H, int32_t V, int32_t group_norm) {
   return stage_bwd_workspace_bytes(group_norm ? H : H * V);
+}
+
+void b200_hstu_profile_enable(int on) {
+  g_prof.on = on != 0;
+  for (int k = 0; k < PROF_KINDS; ++k) g_prof.count[k] = 0;
+}
+
+int b200_hstu_profile_collect(int kind, float *out_ms, int max_n) {
+  if (kind < 0 || kind >= PROF_KINDS || out_ms == nullptr) return 0;
+  int n = g_prof.count[kind] < PROF_RING ? g_prof.count[kind] : PROF_RING;
+  if (n > max_n) n = max_n;
+  int got = 0;
+  for (int i = 0; i < n; ++i) {
+    float ms = 0.f;
+    if (g_prof.created[kind][i] && cudaEventElapsedTime(&ms, g_prof.start[kind][i], g_prof.stop[kind][i]) == cudaSuccess)
+      out_ms[got++] = ms;
+  }
+  return got;
 }
 
 const char *b200_hstu_last_error(void) { return g_err; }

@@ -531,8 +531,12 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   const int64_t one = plan_bytes(a.total_L, a.B);
   PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(a.workspace);
   PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + one);
-  attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
-      p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1), max_items);
+  {
+    ProfileScope prof(PROF_PLAN, st);
+    attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
+        p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1),
+        max_items);
+  }
   count_launch();
   B200_CHECK_LAUNCH("attention plan (backward)");
   int64_t upper = (int64_t)max_items * a.H;
@@ -545,6 +549,7 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pk.plan = hdr_kv;
     pk.items = reinterpret_cast<ItemDesc *>(hdr_kv + 1);
     pk.status = &hdr_kv->status;
+    ProfileScope prof(PROF_ATTN_BWD_DKDV, st);
     kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pk);
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dk, dv)");
@@ -557,6 +562,7 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pq.plan = hdr_q;
     pq.items = reinterpret_cast<ItemDesc *>(hdr_q + 1);
     pq.status = &hdr_q->status;
+    ProfileScope prof(PROF_ATTN_BWD_DQ, st);
     kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pq);
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dq)");

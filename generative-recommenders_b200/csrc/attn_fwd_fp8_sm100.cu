@@ -621,7 +621,10 @@ int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &fa, cudaStream_t st) {
   p.block_offsets = fa.block_offsets;
   p.trace = nullptr;
   const int max_items = (int)plan_max_items(a.total_L, a.B);
-  attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items);
+  {
+    ProfileScope prof(PROF_PLAN, st);
+    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items);
+  }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");
   auto kern = hstu_attn_fwd_fp8_sm100_kernel<D>;
@@ -629,7 +632,10 @@ int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &fa, cudaStream_t st) {
   if (e != cudaSuccess) return check_cuda(e, "fp8 forward smem attribute");
   int64_t upper = (int64_t)max_items * a.H;
   int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
-  kern<<<grid, FWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, p);
+  {
+    ProfileScope prof(PROF_ATTN_FWD_FP8, st);
+    kern<<<grid, FWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, p);
+  }
   count_launch();
   B200_CHECK_LAUNCH("tcgen05 fp8 attention forward");
   return 0;

@@ -588,7 +588,10 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
       p.trace = reinterpret_cast<ulonglong2 *>(reinterpret_cast<uint8_t *>(a.workspace) + need);
   }
   const int max_items = (int)plan_max_items(a.total_L, a.B);
-  attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items);
+  {
+    ProfileScope prof(PROF_PLAN, st);
+    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items);
+  }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");
   auto kern = hstu_attn_fwd_sm100_kernel<D, IS_BF16>;
@@ -596,7 +599,10 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   if (e != cudaSuccess) return check_cuda(e, "forward smem attribute");
   int64_t upper = (int64_t)max_items * a.H;
   int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
-  kern<<<grid, FWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, p);
+  {
+    ProfileScope prof(PROF_ATTN_FWD, st);
+    kern<<<grid, FWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, p);
+  }
   count_launch();
   B200_CHECK_LAUNCH("tcgen05 attention forward");
   return 0;

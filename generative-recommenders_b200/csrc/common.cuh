@@ -22,6 +22,22 @@ int check_cuda(cudaError_t e, const char *what);
 extern std::atomic<long long> g_launches;
 inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// Optional per-kernel timing: when enabled (b200_hstu_profile_enable), every launch of a hot
+// kernel is bracketed by a cudaEvent pair on the launch stream; b200_hstu_profile_collect() reads
+// the durations back after the caller has synchronised.  Off by default (no events are created).
+enum ProfileKind {
+  PROF_PLAN = 0, PROF_ATTN_FWD = 1, PROF_ATTN_BWD_DKDV = 2, PROF_ATTN_BWD_DQ = 3, PROF_ATTN_FWD_FP8 = 4,
+  PROF_LN_FWD = 5, PROF_LN_BWD = 6, PROF_SILU = 7, PROF_NORM_MUL_FWD = 8, PROF_NORM_MUL_BWD = 9,
+  PROF_QUANT = 10, PROF_ATTN_SIMT = 11, PROF_KINDS = 12
+};
+struct ProfileScope {
+  int kind;
+  cudaStream_t st;
+  cudaEvent_t stop;
+  ProfileScope(int kind, cudaStream_t st);
+  ~ProfileScope();
+};
+
 #define B200_CHECK_LAUNCH(what)                                   \
   do {                                                            \
     int _st = ::b200hstu::check_cuda(cudaGetLastError(), what);   \

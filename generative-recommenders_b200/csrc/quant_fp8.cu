@@ -70,6 +70,7 @@ int quantize_e4m3_block(const void *x, int dtype, int64_t row_stride, int64_t he
   int gx = (int)(max_blocks < 65535 ? max_blocks : 65535);
   if (gx < 1) gx = 1;
   dim3 grid((unsigned)gx, (unsigned)H);
+  ProfileScope prof(PROF_QUANT, st);
   switch (dtype) {
     case B200_HSTU_F32:
       quantize_e4m3_block_kernel<float><<<grid, 256, 0, st>>>((const float *)x, row_stride, head_stride, (uint8_t *)x8,

@@ -523,6 +523,7 @@ int ln_fwd_t(const void *x, int64_t x_rs, const void *w, const void *b, void *y,
   int64_t nblk = (rows + WARPS - 1) / WARPS;
   int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
   if (grid == 0) return 0;
+  ProfileScope prof(PROF_LN_FWD, st);
   DISPATCH_MAXV(pick_maxv<E>(D), (layer_norm_fwd_kernel<E, MV><<<grid, WARPS * 32, 0, st>>>(
                                      (const E *)x, x_rs, (const E *)w, (const E *)b, (E *)y, y_rs, mean, rstd,
                                      rows, D, eps, vec_ok)));
@@ -545,6 +546,7 @@ int ln_bwd_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const v
   bool vec_ok = aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(w) && x_rs % EV == 0 &&
                 dy_rs % EV == 0 && dx_rs % EV == 0;
   size_t smem = (size_t)WARPS * D * sizeof(float);
+  ProfileScope prof(PROF_LN_BWD, st);
   DISPATCH_MAXV(pick_maxv<E>(D), {
     auto kern = layer_norm_bwd_kernel<E, MV>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -569,6 +571,7 @@ int silu_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out
   if (total == 0) return 0;
   int64_t nblk = (total + 255) / 256;
   int grid = (int)(nblk < (int64_t)num_sms() * 16 ? nblk : (int64_t)num_sms() * 16);
+  ProfileScope prof(PROF_SILU, st);
   if (bwd)
     silu_kernel<E, true><<<grid, 256, 0, st>>>((const E *)dy, dy_rs, (const E *)x, x_rs, (E *)out, out_rs, rows,
                                                width, vec_ok);
@@ -632,6 +635,7 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     p.vec_ok = vec_ok;
     int64_t nblk = (a.rows + WARPS - 1) / WARPS;
     int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
+    ProfileScope prof(PROF_NORM_MUL_FWD, st);
     DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV><<<grid, WARPS * 32, 0, st>>>(p)));
     count_launch();
     B200_CHECK_LAUNCH("norm_mul forward");
@@ -645,6 +649,7 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
   if ((int64_t)grid * 2 * D * (int64_t)sizeof(float) > a.partial_bytes)
     return fail(B200_HSTU_EWORKSPACE, "norm_mul backward: scratch too small");
   size_t smem = (size_t)WARPS * D * sizeof(float);
+  ProfileScope prof(PROF_NORM_MUL_BWD, st);
   DISPATCH_MAXV(pick_maxv<E>(D), {
     auto kern = norm_mul_bwd_kernel<E, MV>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

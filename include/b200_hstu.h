@@ -188,6 +188,19 @@ int b200_hstu_norm_mul_fwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream
 int b200_hstu_norm_mul_bwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream_t stream);
 int64_t b200_hstu_norm_mul_bwd_workspace_bytes(int32_t H, int32_t V, int32_t group_norm);
 
+/*
+ * Optional per-kernel timing for benchmarks.  After b200_hstu_profile_enable(1) every launch of a
+ * hot kernel is bracketed by a cudaEvent pair on its launch stream; once the caller has
+ * synchronised the device, b200_hstu_profile_collect(kind, out_ms, max_n) writes up to max_n
+ * durations (milliseconds, oldest first, at most the 512 most recent launches since the last
+ * enable) and returns how many.  Kinds: 0 work-list planning, 1 attention forward, 2 backward
+ * dK/dV, 3 backward dQ, 4 fp8 forward, 5 layer_norm forward, 6 layer_norm backward, 7 SiLU
+ * gating, 8 norm_mul forward, 9 norm_mul backward, 10 e4m3 quantiser, 11 CUDA-core attention.
+ * Enabling resets the counters; b200_hstu_profile_enable(0) turns the events off again.
+ */
+void b200_hstu_profile_enable(int on);
+int b200_hstu_profile_collect(int kind, float *out_ms, int max_n);
+
 /* Host helpers. */
 const char *b200_hstu_last_error(void);
 int b200_hstu_version(void);
