@@ -202,9 +202,9 @@ def run_ours(args):
     bwd_ms = sorted(b.elapsed_time(c) for a, b, c in fe)[len(fe) // 2]
     kernel_ms = {}
     for kind in ("plan", "attn_fwd", "attn_bwd_dkdv", "attn_bwd_dq"):
-        v = _cabi.profile_collect(kind)
-        if v:
-            kernel_ms[kind] = sum(v) / len(v)
+        vals = _cabi.profile_collect(kind)
+        if vals:
+            kernel_ms[kind] = sum(vals) / len(vals)
     _cabi.profile_enable(False)
 
     # ---- end to end through the public API from pinned host memory

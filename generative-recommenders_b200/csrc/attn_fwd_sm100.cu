@@ -53,7 +53,7 @@ struct FwdParams {
   float half_alpha;   // alpha / 2
   float inv_n;        // 1 / max_seq_len
   int H;
-  // optional timeline of CTA 0 (4 roles x TRACE_RECORDS records of {ns, tag}); NULL = off
+  // optional timeline of CTA 0 (4 roles x TRACE_RECORDS records of {SM clock, tag}); NULL = off
   ulonglong2 *trace;
 };
 
@@ -68,7 +68,7 @@ struct Tracer {
     n = 0;
   }
   __device__ __forceinline__ void mark(unsigned tag) {
-    if (buf != nullptr && n < TRACE_RECORDS) buf[n++] = make_ulonglong2(globaltimer_ns(), tag);
+    if (buf != nullptr && n < TRACE_RECORDS) buf[n++] = make_ulonglong2((unsigned long long)clock64(), tag);
   }
 };
 
@@ -200,9 +200,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(s_full + 8 * x, 1);
-      mbar_init(p_full + 8 * x, 4);
+      mbar_init(p_full + 8 * x, 8);
       mbar_init(o_full + 8 * x, 1);
-      mbar_init(o_empty + 8 * x, 4);
+      mbar_init(o_empty + 8 * x, 8);
     }
     fence_mbar_init();
   }
@@ -407,16 +407,18 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
   } else {
     // ------------------------------------------------------------------ SiLU + epilogue warps
-    const int X = warp >= 6 ? 1 : 0;           // query tile A or B
+    // All eight warps work on one score tile at a time (A, then B, then A ...): the activation is
+    // bound by the MUFU rate of the whole SM, so a tile is finished soonest - and its P handed
+    // back to the tensor pipe soonest - when every warp works on it.  Warps 2-5 take columns
+    // [0,64) of the tile, warps 6-9 columns [64,128); thread = one query row.
+    const int wg = warp >= 6 ? 1 : 0;
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const uint32_t tS = tmem_base + X * 128 + lane_off;
-    const uint32_t tO = tmem_base + 256 + X * 128 + lane_off;
-    uint32_t my_tiles = 0, my_items = 0;
+    uint32_t my_tiles[2] = {0, 0}, my_items[2] = {0, 0};
     bool ok = true;
     Tracer tr;
-    tr.init(p.trace, 2 + X, quad == 2 && lane == 0);
+    tr.init(p.trace, 2 + wg, quad == 2 && lane == 0);
     if ((int)blockIdx.x < num_items) {
       ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
       for (int idx = blockIdx.x; idx < num_items && ok; idx += stride) {
@@ -425,99 +427,121 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const int h = idx % p.H;
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
-        if (X == 1 && !pr.hasB) continue;
-        const TileItem &it = X == 0 ? pr.A : pr.B;
-        const int L = it.m.L;
-        const int i = it.m0 + row_in_tile;
-        const int id_i = it.m.id(i);
-        const RowInterval ri = row_interval(it, i);
-        const bool exact_only = !it.regular || p.bias != nullptr;
-        for (int j = 0; j < pr.n_tiles; ++j) {
+        const int L = pr.A.m.L;
+        const bool exact_only = !pr.A.regular || p.bias != nullptr;
+        const int iA = pr.A.m0 + row_in_tile, iB = pr.B.m0 + row_in_tile;
+        const RowInterval riA = row_interval(pr.A, iA), riB = row_interval(pr.B, iB);
+        for (int j = 0; j < pr.n_tiles && ok; ++j) {
           const int t = pr.tile_at(j);
-          if (!it.visits(t)) continue;
           const int n0 = t * TILE;
-          const bool full = !exact_only && tile_pair_is_full(it, n0);
-          tr.mark(30);
-          ok = mbar_wait(wc, s_full + 8 * X, my_tiles & 1, 301);
-          if (!ok) break;
-          tc_fence_after();
-          tr.mark(31);
-          if (!exact_only) {
-            uint32_t sreg[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sreg[c]);
+          for (int X = 0; X < 2; ++X) {
+            const TileItem &it = X == 0 ? pr.A : pr.B;
+            if (!((X == 0 || pr.hasB) && it.visits(t))) continue;
+            const int i = X == 0 ? iA : iB;
+            const RowInterval &ri = X == 0 ? riA : riB;
+            const bool full = !exact_only && tile_pair_is_full(it, n0);
+            const uint32_t tS = tmem_base + X * 128 + lane_off;
+            tr.mark(30);
+            ok = mbar_wait(wc, s_full + 8 * X, my_tiles[X] & 1, 301);
+            if (!ok) break;
+            tc_fence_after();
+            tr.mark(31);
+            uint32_t sreg[2][32];
+            tmem_ld32(tS + wg * 64, sreg[0]);
+            tmem_ld32(tS + wg * 64 + 32, sreg[1]);
             tc_wait_ld();
+            // P is written over the first 64 columns of S: every warp must have its scores in
+            // registers before anyone stores
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             tr.mark(32);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
               uint32_t packed[16];
+              const int col0 = n0 + wg * 64 + c * 32;
               if (full)
                 silu_chunk<IS_BF16, false>(sreg[c], packed, p.half_alpha, 0xffffffffu);
+              else if (!exact_only)
+                silu_chunk<IS_BF16, true>(sreg[c], packed, p.half_alpha, row_mask_bits(ri, col0, L));
               else
-                silu_chunk<IS_BF16, true>(sreg[c], packed, p.half_alpha, row_mask_bits(ri, n0 + c * 32, L));
-              tmem_st16(tS + c * 16, packed);
+                silu_chunk_exact<IS_BF16>(sreg[c], packed, p.half_alpha, it.m, i, it.m.id(i), col0, p.bias,
+                                          p.bias_numel);
+              tmem_st16(tS + wg * 32 + c * 16, packed);
             }
-          } else {
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-              uint32_t r[32], packed[16];
-              tmem_ld32(tS + c * 32, r);
-              tc_wait_ld();
-              silu_chunk_exact<IS_BF16>(r, packed, p.half_alpha, it.m, i, id_i, n0 + c * 32, p.bias, p.bias_numel);
-              tmem_st16(tS + c * 16, packed);
-            }
+            tr.mark(37);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + 8 * X);
+            tr.mark(33);
+            ++my_tiles[X];
           }
-          tr.mark(37);
-          tc_wait_st();
-          tr.mark(38);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(p_full + 8 * X);
-          tr.mark(33);
-          ++my_tiles;
         }
         if (!ok) break;
-        // epilogue: O (fp32, TMEM) -> scale -> 16-bit -> global, valid rows only
-        tr.mark(34);
-        ok = mbar_wait(wc, o_full + 8 * X, my_items & 1, 302);
-        if (!ok) break;
-        tc_fence_after();
-        tr.mark(35);
-        float scale = p.inv_n;
-        if (p.attn_scale != nullptr && i < L)
-          scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)d.start + i];
-        uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + i) * p.o_rs + (int64_t)h * p.o_hs;
+        // epilogue: O (fp32, TMEM) -> scale -> 16-bit -> global, valid rows only; the two warpgroups
+        // split the D columns
 #pragma unroll
-        for (int c0 = 0; c0 < D / 32; c0 += 2) {
-          uint32_t r[2][32];
-          tmem_ld32(tO + c0 * 32, r[0]);
-          tmem_ld32(tO + c0 * 32 + 32, r[1]);
-          tc_wait_ld();
-          if (i < L) {
+        for (int X = 0; X < 2; ++X) {
+          if (X == 1 && !pr.hasB) continue;
+          const TileItem &it = X == 0 ? pr.A : pr.B;
+          const int i = X == 0 ? iA : iB;
+          tr.mark(34);
+          ok = mbar_wait(wc, o_full + 8 * X, my_items[X] & 1, 302);
+          if (!ok) break;
+          tc_fence_after();
+          tr.mark(35);
+          float scale = p.inv_n;
+          if (p.attn_scale != nullptr && i < L)
+            scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)d.start + i];
+          const int cbase = wg * (D / 2);
+          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + i) * p.o_rs +
+                           (int64_t)h * p.o_hs + cbase;
+          const uint32_t tO = tmem_base + 256 + X * 128 + lane_off + cbase;
+          if (D == 128) {
+            uint32_t r[2][32];
+            tmem_ld32(tO, r[0]);
+            tmem_ld32(tO + 32, r[1]);
+            tc_wait_ld();
+            if (i < L) {
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
+              for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                  uint4 o4;
+                  o4.x = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 0]) * scale, __uint_as_float(r[cc][8 * x + 1]) * scale);
+                  o4.y = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 2]) * scale, __uint_as_float(r[cc][8 * x + 3]) * scale);
+                  o4.z = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 4]) * scale, __uint_as_float(r[cc][8 * x + 5]) * scale);
+                  o4.w = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 6]) * scale, __uint_as_float(r[cc][8 * x + 7]) * scale);
+                  *reinterpret_cast<uint4 *>(orow + cc * 32 + x * 8) = o4;
+                }
+            }
+          } else {
+            uint32_t r[32];
+            tmem_ld32(tO, r);
+            tc_wait_ld();
+            if (i < L) {
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
                 uint4 o4;
-                o4.x = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 0]) * scale, __uint_as_float(r[cc][8 * x + 1]) * scale);
-                o4.y = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 2]) * scale, __uint_as_float(r[cc][8 * x + 3]) * scale);
-                o4.z = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 4]) * scale, __uint_as_float(r[cc][8 * x + 5]) * scale);
-                o4.w = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 6]) * scale, __uint_as_float(r[cc][8 * x + 7]) * scale);
-                *reinterpret_cast<uint4 *>(orow + (c0 + cc) * 32 + x * 8) = o4;
+                o4.x = pack2<IS_BF16>(__uint_as_float(r[8 * x + 0]) * scale, __uint_as_float(r[8 * x + 1]) * scale);
+                o4.y = pack2<IS_BF16>(__uint_as_float(r[8 * x + 2]) * scale, __uint_as_float(r[8 * x + 3]) * scale);
+                o4.z = pack2<IS_BF16>(__uint_as_float(r[8 * x + 4]) * scale, __uint_as_float(r[8 * x + 5]) * scale);
+                o4.w = pack2<IS_BF16>(__uint_as_float(r[8 * x + 6]) * scale, __uint_as_float(r[8 * x + 7]) * scale);
+                *reinterpret_cast<uint4 *>(orow + x * 8) = o4;
               }
             }
           }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(o_empty + 8 * X);
-        tr.mark(36);
-        ++my_items;
-        // rows at or beyond max_seq_len of an over-long sequence come back as zeros
-        if (d.len > L && it.m0 + TILE >= L) {
-          for (int r2 = L + row_in_tile; r2 < d.len; r2 += TILE) {
-            uint16_t *zr = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + r2) * p.o_rs + (int64_t)h * p.o_hs;
-            for (int x = 0; x < D; x += 8) *reinterpret_cast<uint4 *>(zr + x) = make_uint4(0, 0, 0, 0);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_empty + 8 * X);
+          tr.mark(36);
+          ++my_items[X];
+          // rows at or beyond max_seq_len of an over-long sequence come back as zeros
+          if (wg == 0 && d.len > L && it.m0 + TILE >= L) {
+            for (int r2 = L + row_in_tile; r2 < d.len; r2 += TILE) {
+              uint16_t *zr = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + r2) * p.o_rs + (int64_t)h * p.o_hs;
+              for (int x = 0; x < D; x += 8) *reinterpret_cast<uint4 *>(zr + x) = make_uint4(0, 0, 0, 0);
+            }
           }
         }
       }
