@@ -18,6 +18,8 @@ EXPORTS = [
     "b200_hstu_attn_fwd",
     "b200_hstu_attn_bwd",
     "b200_hstu_attn_workspace_bytes",
+    "b200_hstu_attn_fwd_static_scratch",
+    "b200_hstu_attn_fwd_static_scratch_max_bytes",
     "b200_hstu_attn_fwd_fp8",
     "b200_hstu_quantize_e4m3_block",
     "b200_hstu_layer_norm_fwd",
@@ -105,6 +107,10 @@ def lib():
     L.b200_hstu_attn_fwd.restype = ctypes.c_int
     L.b200_hstu_attn_bwd.argtypes = [POINTER(AttnArgs), c_void_p]
     L.b200_hstu_attn_bwd.restype = ctypes.c_int
+    L.b200_hstu_attn_fwd_static_scratch.argtypes = [POINTER(AttnArgs), c_void_p]
+    L.b200_hstu_attn_fwd_static_scratch.restype = ctypes.c_int
+    L.b200_hstu_attn_fwd_static_scratch_max_bytes.argtypes = []
+    L.b200_hstu_attn_fwd_static_scratch_max_bytes.restype = c_int64
     L.b200_hstu_attn_workspace_bytes.argtypes = [POINTER(AttnArgs), ctypes.c_int]
     L.b200_hstu_attn_workspace_bytes.restype = c_int64
     L.b200_hstu_attn_fwd_fp8.argtypes = [POINTER(AttnFp8Args), c_void_p]

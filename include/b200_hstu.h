@@ -108,6 +108,21 @@ int b200_hstu_attn_fwd(const b200_hstu_attn_args *args, b200_hstu_stream_t strea
  */
 int b200_hstu_attn_bwd(const b200_hstu_attn_args *args, b200_hstu_stream_t stream);
 
+/*
+ * Forward for callers that cannot allocate device memory (a server that owns all of HBM through
+ * its own arena, code running where the allocator must not be touched, a bare C caller with no
+ * allocator at hand).  Same arguments and result as b200_hstu_attn_fwd(), but args->workspace is
+ * ignored: the work list lives in a 1 MiB array inside the library's device image (held by every
+ * context that loads the library until exit).  Batches needing more (total_L / 128 + B + 1 >
+ * 32 766 items) are rejected with B200_HSTU_EWORKSPACE.  The first call on a device looks the
+ * array up with cudaGetSymbolAddress - make it outside any stream capture; no call allocates.
+ * One array per device is shared by all calls: back-to-back calls on one stream are fine, calls
+ * that may overlap on the GPU race.  This entry point has no counterpart in the reference (its
+ * ops allocate their scratch per call through torch).
+ */
+int b200_hstu_attn_fwd_static_scratch(const b200_hstu_attn_args *args, b200_hstu_stream_t stream);
+int64_t b200_hstu_attn_fwd_static_scratch_max_bytes(void);
+
 /* Bytes of scratch that fwd (backward = 0) or bwd (backward = 1) need for these sizes.
    Host function; depends on B, H, dqk, dv, total_L, dtype, impl only. */
 int64_t b200_hstu_attn_workspace_bytes(const b200_hstu_attn_args *args, int backward);
