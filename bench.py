@@ -375,17 +375,284 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _dist_setup():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    return world, rank, local_rank, dev, dist
+
+
+def run_stack(args):
+    """configs[2]: 8-layer HSTU stack, D=512, H=4, d=128, forward + backward (training step without the
+    optimizer: the path is the layer stack), bf16, relative bias on.  configs[4]: 4-layer stack, D=1024,
+    H=8, d=128, inference forward; the fixed batch is split over the ranks by token count (strong
+    scaling), no collective on the data path."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi, sharding, workloads as W
+
+    world, rank, local_rank, dev, dist = _dist_setup()
+    train = args.workload == "config2_stack"
+    if train:
+        w_all = W.config2_attention(args.batch or 128)
+        D, layers, cfg = 512, 8, G.STULayerConfig(embedding_dim=512, num_heads=4, hidden_dim=128, attention_dim=128,
+                                                  output_dropout_ratio=0.0, contextual_seq_len=6, rel_bias_buckets=128)
+    else:
+        w_all = W.config4(args.batch or 2048)
+        D, layers, cfg = 1024, 4, G.STULayerConfig(embedding_dim=1024, num_heads=8, hidden_dim=128, attention_dim=128,
+                                                   output_dropout_ratio=0.0, contextual_seq_len=16)
+    bins = sharding.partition_by_tokens(w_all.lengths.tolist(), world)
+    w = W.subset(w_all, bins[rank]) if world > 1 else w_all
+    torch.manual_seed(20260 + (2 if train else 4))
+    stack = G.STUStack([G.STULayer(cfg) for _ in range(layers)]).to(dev).to(torch.bfloat16)
+    stack.train(False)
+    g = torch.Generator().manual_seed(w_all.seed + 7 + rank)
+    L = w.total_tokens
+    hx = torch.randn(L, D, generator=g).to(torch.bfloat16).pin_memory()
+    hdy = torch.randn(L, D, generator=g).to(torch.bfloat16).pin_memory() if train else None
+    x = hx.to(dev)
+    dy = hdy.to(dev) if train else None
+    lengths = w.lengths.to(dev)
+    offs = w.seq_offsets.to(torch.int32).to(dev)
+    nt = w.num_targets.to(torch.int32).to(dev)
+    N = w.max_seq_len
+    params = [p_ for p_ in stack.parameters()]
+
+    def step(xin, dyin):
+        if train:
+            xin = xin.detach().requires_grad_(True)
+            for p_ in params:
+                p_.grad = None
+            y = stack(xin, lengths, offs, N, nt)
+            y.backward(dyin)
+            return y, xin.grad
+        with torch.no_grad():
+            return stack(xin, lengths, offs, N, nt), None
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(x, dy)
+    barrier()
+    graph = None
+    if args.graph and train:
+        sx, sdy = x.clone(), dy.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step(sx, sdy)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            gy, gdx = step(sx, sdy)
+        run = graph.replay
+    else:
+        run = lambda: step(x, dy)  # noqa: E731
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    steps = args.steps
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    launches0 = _cabi.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for s_, e_ in ev:
+            flush.zero_()
+            s_.record()
+            run()
+            e_.record()
+        barrier()
+    launches = _cabi.launch_count() - launches0
+    ms_total = sum(s_.elapsed_time(e_) for s_, e_ in ev)
+    # end to end: pinned host activations in, result back
+    res_host = torch.empty_like(hx)
+    e2e_steps = max(2, min(steps, 5))
+
+    def e2e_step():
+        xd = hx.to(dev, non_blocking=True)
+        dyd = hdy.to(dev, non_blocking=True) if train else None
+        y, dx = step(xd, dyd)
+        res_host.copy_(dx if train else y, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    stats = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    work = torch.tensor([float(L), w.causal_flops_fwd() * layers, float(launches)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms = stats.tolist()
+    tokens_all, attn_flops_all, launches_all = work.tolist()
+    ms_per_step = ms_total / steps
+    if rank == 0:
+        H, d = cfg.num_heads, cfg.attention_dim
+        gemm_flops = tokens_all * layers * (2.0 * D * 4 * H * d + 2.0 * 3 * H * d * D)
+        mult = 3.0 if train else 1.0
+        out = {
+            "metric": "hstu_stack_tokens_per_s", "value": round(tokens_all / (ms_per_step * 1e-3), 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "strong" if not train else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "configs[%s]: %d-layer HSTU stack %s, D=%d, H=%d, d=%d, B=%d, N=%d%s" % (
+                "2" if train else "4", layers, "fwd+bwd" if train else "inference fwd", D, H, d, len(w_all.lengths), N,
+                ", CUDA graph replay" if graph is not None else ""),
+                "global_batch": len(w_all.lengths), "tokens": int(tokens_all), "seq_len": N,
+                "parallelism": "sequence-sharded x%d by token count, no collective" % world,
+                "l2": "256 MiB memset between timed steps (untimed)"},
+            "attn_tflops_nominal": round((3.5 if train else 1.0) * attn_flops_all / (ms_per_step * 1e-3) / 1e12, 2),
+            "total_tflops_nominal": round((mult * gemm_flops + (3.5 if train else 1.0) * attn_flops_all) /
+                                          (ms_per_step * 1e-3) / 1e12, 2),
+            "e2e": {"value": round(tokens_all / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": int(hx.numel() * 2 * (2 if train else 1)), "d2h_bytes_per_step": int(hx.numel() * 2),
+                    "ms_per_step": round(e2e_ms, 4)},
+            "gpu_launches": int(launches_all), "clocks": clocks.summary(),
+        }
+        print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_fp8(args):
+    """configs[3] inference forward with e4m3 q/k/v (per-128-token-block scales) next to the bf16 run of the
+    same tensors."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi, workloads as W
+    from oracle import hstu_oracle as O
+
+    world, rank, local_rank, dev, dist = _dist_setup()
+    w = W.config3(args.batch or 256)
+    q, k, v = w.qkv(device=dev)
+    offs = w.seq_offsets.to(torch.int32).to(dev)
+    nt = w.num_targets.to(torch.int32).to(dev)
+    q8, qs, bo = G.quantize_e4m3_block(q, offs)
+    k8, ks, _ = G.quantize_e4m3_block(k, offs)
+    v8, vs, _ = G.quantize_e4m3_block(v, offs)
+    kw = dict(num_targets=nt, max_attn_len=w.max_attn_len)
+    f8 = lambda: G.hstu_mha_fp8(w.max_seq_len, w.alpha, q8, k8, v8, qs, ks, vs, bo, offs, **kw)  # noqa: E731
+    f16 = lambda: G.hstu_mha(w.max_seq_len, w.alpha, q, k, v, offs, **kw)  # noqa: E731
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            o8 = f8()
+            o16 = f16()
+        torch.cuda.synchronize()
+        err = O.rel_l2(o8, o16)
+        res = {}
+        _cabi.profile_enable(True)
+        for name, fn in (("fp8", f8), ("bf16", f16)):
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+            for s_, e_ in ev:
+                s_.record()
+                fn()
+                e_.record()
+            torch.cuda.synchronize()
+            res[name] = sum(s_.elapsed_time(e_) for s_, e_ in ev) / args.steps
+        kms = {kk: (lambda vv: sum(vv) / len(vv) if vv else None)(_cabi.profile_collect(kk)) for kk in ("attn_fwd_fp8", "attn_fwd")}
+        _cabi.profile_enable(False)
+    exact = 4.0 * w.num_heads * w.attn_dim * w.exact_pairs()
+    out = {
+        "metric": "hstu_mha_fwd_fp8_tflops_exact_pairs", "value": round(exact / (res["fp8"] * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(res["fp8"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 (fp32 accumulate, bf16 out)",
+        "data": "synthetic",
+        "config": {"workload": "configs[3]: inference forward, B=%d, N=8192, H=4, d=128, window 1024, 256 targets; "
+                               "inputs (%.0f MB per tensor in bf16) are larger than L2" % (len(w.lengths), q.numel() * 2 / 1e6),
+                   "tokens": w.total_tokens},
+        "bf16_ms": round(res["bf16"], 4), "bf16_tflops_exact_pairs": round(exact / (res["bf16"] * 1e-3) / 1e12, 2),
+        "nominal_causal_tflops_fp8": round(w.causal_flops_fwd() / (res["fp8"] * 1e-3) / 1e12, 2),
+        "kernel_ms": kms, "rel_l2_fp8_vs_bf16": round(err, 5), "tokens_per_s": round(w.total_tokens / (res["fp8"] * 1e-3), 1),
+    }
+    print(json.dumps(out), flush=True)
+
+
+def run_stages(args):
+    """Achieved HBM GB/s of the memory-bound stage kernels (bf16, D = H*dv = 512, rows = tokens of
+    configs[4]'s first 400 sequences), from the library's per-kernel events."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi, workloads as W
+
+    world, rank, local_rank, dev, dist = _dist_setup()
+    rows = int(W.config4(400).total_tokens)
+    D = 512
+    g = torch.Generator().manual_seed(5)
+    mk = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16).to(dev)  # noqa: E731
+    x, dy = mk(rows, D), mk(rows, D)
+    w_, b_ = mk(D), mk(D)
+    uvqk = mk(rows, 4 * D)
+    attn, u, dcat = mk(rows, D), mk(rows, D), mk(rows, 3 * D)
+    peaks, peak_kind = load_peaks()
+
+    def timed(kind, fn, nbytes):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        _cabi.profile_enable(True)
+        for _ in range(max(5, min(args.steps, 30))):
+            fn()
+        torch.cuda.synchronize()
+        v = _cabi.profile_collect(kind)
+        _cabi.profile_enable(False)
+        ms = sorted(v)[len(v) // 2]
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"ms": round(ms, 4), "bytes": int(nbytes), "gb_per_s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+
+    res = {}
+    xr = x.clone().requires_grad_(True)
+    wr = w_.clone().requires_grad_(True)
+    br = b_.clone().requires_grad_(True)
+    res["layer_norm_fwd"] = timed("layer_norm_fwd", lambda: G.layer_norm(x, w_, b_, 1e-6), rows * D * 2 * 2 + rows * 8)
+    y = G.layer_norm(xr, wr, br, 1e-6)
+    res["layer_norm_bwd"] = timed("layer_norm_bwd", lambda: torch.autograd.grad(y, (xr, wr, br), dy, retain_graph=True),
+                                  rows * D * 2 * 3 + rows * 8)
+    res["silu_u"] = timed("silu", lambda: G.hstu_compute._SiluColumnsFunction.apply(uvqk[:, :D], D), rows * D * 2 * 2)
+    res["norm_mul_fwd"] = timed("norm_mul_fwd", lambda: G.hstu_norm_mul_dropout(attn, u, w_, b_, 1e-6, 0.0, False, True, True,
+                                                                                  "none", False, 4, 128), rows * D * 2 * 5 + rows * 8)
+    ar = attn.clone().requires_grad_(True)
+    ur = u.clone().requires_grad_(True)
+    yc = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.0, False, True, True, "none", False, 4, 128)
+    res["norm_mul_bwd"] = timed("norm_mul_bwd", lambda: torch.autograd.grad(yc, (ar, ur, wr, br), dcat, retain_graph=True),
+                                rows * D * 2 * 7 + rows * 8)
+    out = {"metric": "hstu_stage_hbm_gb_per_s", "value": res["norm_mul_fwd"]["gb_per_s"], "unit": "GB/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": 3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2)" % (rows, rows * D * 2 / 1e6)},
+           "hbm_peak_gb_per_s": peaks["hbm_gbs"], "peak_source": peak_kind + " (copy)", "stages": res}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="config1", choices=["config1", "config3"])
+    ap.add_argument("--workload", default="config1",
+                    choices=["config1", "config3", "config3_fp8", "config2_stack", "config4_stack", "stages"])
+    ap.add_argument("--graph", action="store_true", help="config2_stack: replay the step from a CUDA graph")
+    ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (stack workloads)")
     ap.add_argument("--fwd-only", action="store_true", help="time the forward alone (inference)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in ("config2_stack", "config4_stack"):
+        run_stack(args)
+    elif args.workload == "stages":
+        run_stages(args)
+    elif args.workload == "config3_fp8":
+        run_fp8(args)
     else:
         run_ours(args)
 

@@ -1,7 +1,7 @@
 """B200-native HSTU jagged attention: the reference's operator API over hand-written sm_100a
 kernels in libb200_hstu.so (C ABI in include/b200_hstu.h)."""
 
-from . import _cabi
+from . import _cabi, hstu_compute
 from .common import HammerKernel
 from .hstu_attention import hstu_mha, set_attention_impl
 from .hstu_attention_fp8 import hstu_mha_fp8, quantize_e4m3_block
@@ -13,6 +13,7 @@ from .hstu_compute import (
 )
 from .layer_norm import layer_norm
 from .mm import addmm
+from .stu import STULayer, STULayerConfig, STUStack
 
 __all__ = [
     "HammerKernel",
@@ -25,5 +26,8 @@ __all__ = [
     "hstu_preprocess_and_attention",
     "layer_norm",
     "addmm",
+    "STULayer",
+    "STULayerConfig",
+    "STUStack",
     "set_attention_impl",
 ]

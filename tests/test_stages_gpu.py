@@ -125,3 +125,44 @@ def test_stu_layer_golden_fp32(golden):
             for n, t in params[layer].items():
                 ref = c["param_grads"]["_stu_layers.%d._%s" % (layer, n)]
                 assert O.rel_l2(t.grad, ref) < 2e-3, (layer, n)
+
+
+def test_stu_module_loads_reference_state_and_matches(golden):
+    """STUStack module: loads the reference STUStack state_dict and reproduces its output and
+    input gradient."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for c in golden("stu_layer.pt"):
+        cfg = G.STULayerConfig(embedding_dim=c["D"], num_heads=c["H"], hidden_dim=c["V"], attention_dim=c["A"],
+                               output_dropout_ratio=0.0, target_aware=c["target_aware"], max_attn_len=c["W"],
+                               contextual_seq_len=c["ctx"])
+        stack = G.STUStack([G.STULayer(cfg), G.STULayer(cfg)]).to(DEV).eval()
+        missing = stack.load_state_dict(c["state"], strict=True)
+        assert not missing.missing_keys and not missing.unexpected_keys
+        x = c["x"].to(DEV).requires_grad_(True)
+        y = stack(x, c["lengths"].to(DEV), c["seq_offsets"].to(DEV), c["N"], c["num_targets"].to(DEV))
+        assert O.rel_l2(y, c["y"]) < 1e-4
+        y.backward(c["dy"].to(DEV))
+        assert O.rel_l2(x.grad, c["dx"]) < 1e-3
+        for name, prm in stack.named_parameters():
+            assert O.rel_l2(prm.grad, c["param_grads"][name]) < 2e-3, name
+
+
+def test_bf16_stack_with_relative_bias_runs_and_matches_oracle():
+    """configs[2]-like layer: bf16, contextual prefix, targets, bucketised relative bias."""
+    from generative_recommenders_b200 import workloads as W
+    from generative_recommenders_b200.stu import position_bias_by_distance
+    torch.manual_seed(0)
+    cfg = G.STULayerConfig(embedding_dim=256, num_heads=2, hidden_dim=128, attention_dim=128,
+                           output_dropout_ratio=0.0, contextual_seq_len=6, rel_bias_buckets=128)
+    layer = G.STULayer(cfg).to(DEV).eval()
+    lengths = torch.tensor([40, 300, 17, 200])
+    nt = torch.tensor([3, 20, 1, 9])
+    offs = W._offsets(lengths)
+    x = torch.randn(int(offs[-1]), 256).bfloat16()
+    y = layer(x.to(DEV), lengths.to(DEV), offs.to(DEV), 512, nt.to(DEV))
+    params = {n[1:]: p.detach().float().cpu() for n, p in layer.named_parameters()}
+    bias = position_bias_by_distance(params["rel_bias_table"], 512)
+    i = torch.arange(512).view(-1, 1); j = torch.arange(512).view(1, -1)
+    rb = bias[(i - j).abs()]
+    ref = O.stu_layer(x.float(), offs, 512, nt, params, 2, 128, 128, contextual_seq_len=6, rel_bias=rb)
+    assert O.rel_l2(y, ref) < 2e-2
