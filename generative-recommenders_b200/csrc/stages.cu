@@ -73,6 +73,29 @@ struct Row {
   }
 };
 
+// A row as raw 16-byte vectors: loaded one row ahead of its use, so the global loads of row r+1 are
+// in flight while row r is reduced and stored (vector path only: aligned pointers and strides).
+template <typename E, int MAXV>
+struct RawRow {
+  static constexpr int EV = VecInfo<E>::EV;
+  uint4 v[MAXV];
+  __device__ __forceinline__ void load(const E *row, int D, int lane) {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      int e0 = (k * 32 + lane) * EV;
+      v[k] = (e0 + EV <= D) ? __ldg(reinterpret_cast<const uint4 *>(row + e0)) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  __device__ __forceinline__ void unpack(Row<E, MAXV> &r) const {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const E *pe = reinterpret_cast<const E *>(&v[k]);
+#pragma unroll
+      for (int t = 0; t < EV; ++t) r.v[k][t] = to_f32(pe[t]);
+    }
+  }
+};
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // mean / rstd of a row held in registers (two-pass: mean first, then centred second moment)
@@ -113,9 +136,23 @@ __global__ void __launch_bounds__(WARPS * 32) layer_norm_fwd_kernel(const E *__r
   Row<E, MAXV> wr, br;
   wr.load(w, D, lane, vec_ok);
   br.load(b, D, lane, vec_ok);
-  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < rows; row += (int64_t)gridDim.x * WARPS) {
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  constexpr bool PF = MAXV <= 4;  // one-row-ahead prefetch only while the registers allow it
+  const bool pf = PF && vec_ok;
+  RawRow<E, PF ? MAXV : 1> nxt;
+  if (pf && row < rows) nxt.load(x + row * x_rs, D, lane);
+  for (; row < rows; row += step) {
     Row<E, MAXV> xr;
-    xr.load(x + row * x_rs, D, lane, vec_ok);
+    bool loaded = false;
+    if constexpr (PF) {
+      if (pf) {
+        nxt.unpack(xr);
+        if (row + step < rows) nxt.load(x + (row + step) * x_rs, D, lane);
+        loaded = true;
+      }
+    }
+    if (!loaded) xr.load(x + row * x_rs, D, lane, vec_ok);
     float mean, rstd;
     row_stats(xr, D, lane, eps, mean, rstd);
 #pragma unroll
@@ -165,11 +202,45 @@ __global__ void __launch_bounds__(WARPS * 32) layer_norm_bwd_kernel(
   dw.zero();
   db.zero();
   const float invD = 1.f / (float)D;
-  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < rows; row += (int64_t)gridDim.x * WARPS) {
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  constexpr bool PF = MAXV <= 2;
+  const bool pf = PF && vec_ok;
+  RawRow<E, PF ? MAXV : 1> nx, ng;
+  float nmean = 0.f, nrstd = 0.f;
+  if constexpr (PF) {
+    if (pf && row < rows) {
+      nx.load(x + row * x_rs, D, lane);
+      ng.load(dy + row * dy_rs, D, lane);
+      nmean = mean_in[row];
+      nrstd = rstd_in[row];
+    }
+  }
+  for (; row < rows; row += step) {
     Row<E, MAXV> xr, gr;
-    xr.load(x + row * x_rs, D, lane, vec_ok);
-    gr.load(dy + row * dy_rs, D, lane, vec_ok);
-    const float mean = mean_in[row], rstd = rstd_in[row];
+    float mean, rstd;
+    bool loaded = false;
+    if constexpr (PF) {
+      if (pf) {
+        nx.unpack(xr);
+        ng.unpack(gr);
+        mean = nmean;
+        rstd = nrstd;
+        if (row + step < rows) {
+          nx.load(x + (row + step) * x_rs, D, lane);
+          ng.load(dy + (row + step) * dy_rs, D, lane);
+          nmean = mean_in[row + step];
+          nrstd = rstd_in[row + step];
+        }
+        loaded = true;
+      }
+    }
+    if (!loaded) {
+      xr.load(x + row * x_rs, D, lane, vec_ok);
+      gr.load(dy + row * dy_rs, D, lane, vec_ok);
+      mean = mean_in[row];
+      rstd = rstd_in[row];
+    }
     float c1 = 0.f, c2 = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k)
@@ -222,35 +293,84 @@ __global__ void __launch_bounds__(256) silu_kernel(const E *__restrict__ dy, int
                                                    int64_t x_rs, E *__restrict__ out, int64_t out_rs, int64_t rows,
                                                    int width, bool vec_ok) {
   constexpr int EV = VecInfo<E>::EV;
+  constexpr int UNR = 4;  // independent 16-byte vectors in flight per thread
   const int vec_per_row = (width + EV - 1) / EV;
   const int64_t total = rows * vec_per_row;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    int64_t row = idx / vec_per_row;
-    int e0 = (int)(idx - row * vec_per_row) * EV;
-    const E *xp = x + row * x_rs + e0;
-    E *op = out + row * out_rs + e0;
-    if (vec_ok && e0 + EV <= width) {
-      uint4 xraw = *reinterpret_cast<const uint4 *>(xp);
-      const E *xe = reinterpret_cast<const E *>(&xraw);
-      uint4 oraw;
-      E *oe = reinterpret_cast<E *>(&oraw);
-      if (BWD) {
-        uint4 graw = *reinterpret_cast<const uint4 *>(dy + row * dy_rs + e0);
-        const E *ge = reinterpret_cast<const E *>(&graw);
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < total; base += nthreads * UNR) {
+    uint4 xraw[UNR], graw[UNR];
+    int64_t rowi[UNR];
+    int e0[UNR];
+    bool fast[UNR];
 #pragma unroll
-        for (int t = 0; t < EV; ++t) oe[t] = from_f32<E>(to_f32(ge[t]) * dsiluf_(to_f32(xe[t])));
-      } else {
-#pragma unroll
-        for (int t = 0; t < EV; ++t) oe[t] = from_f32<E>(siluf_(to_f32(xe[t])));
-      }
-      *reinterpret_cast<uint4 *>(op) = oraw;
-    } else {
-      for (int t = 0; t < EV && e0 + t < width; ++t) {
-        float xv = to_f32(xp[t]);
-        op[t] = from_f32<E>(BWD ? to_f32(dy[row * dy_rs + e0 + t]) * dsiluf_(xv) : siluf_(xv));
+    for (int k = 0; k < UNR; ++k) {
+      const int64_t idx = base + k * nthreads;
+      fast[k] = false;
+      if (idx < total) {
+        rowi[k] = idx / vec_per_row;
+        e0[k] = (int)(idx - rowi[k] * vec_per_row) * EV;
+        fast[k] = vec_ok && e0[k] + EV <= width;
+        if (fast[k]) {
+          xraw[k] = __ldg(reinterpret_cast<const uint4 *>(x + rowi[k] * x_rs + e0[k]));
+          if (BWD) graw[k] = __ldg(reinterpret_cast<const uint4 *>(dy + rowi[k] * dy_rs + e0[k]));
+        }
       }
     }
+#pragma unroll
+    for (int k = 0; k < UNR; ++k) {
+      const int64_t idx = base + k * nthreads;
+      if (idx >= total) continue;
+      E *op = out + rowi[k] * out_rs + e0[k];
+      if (fast[k]) {
+        const E *xe = reinterpret_cast<const E *>(&xraw[k]);
+        const E *ge = reinterpret_cast<const E *>(&graw[k]);
+        uint4 oraw;
+        E *oe = reinterpret_cast<E *>(&oraw);
+#pragma unroll
+        for (int t = 0; t < EV; ++t)
+          oe[t] = from_f32<E>(BWD ? to_f32(ge[t]) * dsiluf_(to_f32(xe[t])) : siluf_(to_f32(xe[t])));
+        *reinterpret_cast<uint4 *>(op) = oraw;
+      } else {
+        const E *xp = x + rowi[k] * x_rs + e0[k];
+        for (int t = 0; t < EV && e0[k] + t < width; ++t) {
+          float xv = to_f32(xp[t]);
+          op[t] = from_f32<E>(BWD ? to_f32(dy[rowi[k] * dy_rs + e0[k] + t]) * dsiluf_(xv) : siluf_(xv));
+        }
+      }
+    }
+  }
+}
+
+// Row-shaped variant (one warp per row, next row's vectors prefetched): used when a row fits the
+// register budget and everything is 16-byte aligned - the usual case of slicing u out of uvqk.
+template <typename E, int MAXV, bool BWD>
+__global__ void __launch_bounds__(WARPS * 32) silu_rows_kernel(const E *__restrict__ dy, int64_t dy_rs,
+                                                               const E *__restrict__ x, int64_t x_rs,
+                                                               E *__restrict__ out, int64_t out_rs, int64_t rows,
+                                                               int width) {
+  constexpr int EV = VecInfo<E>::EV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  RawRow<E, MAXV> nx, ng;
+  if (row < rows) {
+    nx.load(x + row * x_rs, width, lane);
+    if (BWD) ng.load(dy + row * dy_rs, width, lane);
+  }
+  for (; row < rows; row += step) {
+    Row<E, MAXV> xr, gr;
+    nx.unpack(xr);
+    if (BWD) ng.unpack(gr);
+    if (row + step < rows) {
+      nx.load(x + (row + step) * x_rs, width, lane);
+      if (BWD) ng.load(dy + (row + step) * dy_rs, width, lane);
+    }
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t)
+        xr.v[k][t] = BWD ? gr.v[k][t] * dsiluf_(xr.v[k][t]) : siluf_(xr.v[k][t]);
+    xr.store(out + row * out_rs, width, lane, true);
   }
 }
 
@@ -288,10 +408,35 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_kernel(NormMulParams 
   Row<E, MAXV> wr, br;
   wr.load((const E *)p.w, D, lane, p.vec_ok);
   br.load((const E *)p.b, D, lane, p.vec_ok);
-  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < p.rows; row += (int64_t)gridDim.x * WARPS) {
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  constexpr bool PF = MAXV <= 2;
+  const bool pf = PF && p.vec_ok;
+  RawRow<E, PF ? MAXV : 1> nx, nu;
+  if constexpr (PF) {
+    if (pf && row < p.rows) {
+      nx.load((const E *)p.attn + row * p.attn_rs, D, lane);
+      nu.load((const E *)p.u + row * p.u_rs, D, lane);
+    }
+  }
+  for (; row < p.rows; row += step) {
     Row<E, MAXV> xr, ur;
-    xr.load((const E *)p.attn + row * p.attn_rs, D, lane, p.vec_ok);
-    ur.load((const E *)p.u + row * p.u_rs, D, lane, p.vec_ok);
+    bool loaded = false;
+    if constexpr (PF) {
+      if (pf) {
+        nx.unpack(xr);
+        nu.unpack(ur);
+        if (row + step < p.rows) {
+          nx.load((const E *)p.attn + (row + step) * p.attn_rs, D, lane);
+          nu.load((const E *)p.u + (row + step) * p.u_rs, D, lane);
+        }
+        loaded = true;
+      }
+    }
+    if (!loaded) {
+      xr.load((const E *)p.attn + row * p.attn_rs, D, lane, p.vec_ok);
+      ur.load((const E *)p.u + row * p.u_rs, D, lane, p.vec_ok);
+    }
     float mean, rstd;
     row_stats(xr, D, lane, p.eps, mean, rstd);
     E *orow = (E *)p.out + row * p.out_rs;
@@ -331,13 +476,52 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
   const float invD = 1.f / (float)D;
   const int off_x = p.concat_u ? D : 0;
   const int off_y = off_x + (p.concat_x ? D : 0);
-  for (int64_t row = (int64_t)blockIdx.x * WARPS + warp; row < p.rows; row += (int64_t)gridDim.x * WARPS) {
-    Row<E, MAXV> xr, ur, gy;
-    xr.load((const E *)p.attn + row * p.attn_rs, D, lane, p.vec_ok);
-    ur.load((const E *)p.u + row * p.u_rs, D, lane, p.vec_ok);
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  constexpr bool PF = MAXV <= 2;
+  const bool pf = PF && p.vec_ok;
+  constexpr int RV = PF ? MAXV : 1;
+  RawRow<E, RV> nx, nu, ngy, ngu, ngx;
+  float nmean = 0.f, nrstd = 0.f;
+  auto prefetch = [&](int64_t r) {
+    if constexpr (PF) {
+      const E *grow = (const E *)p.dout + r * p.dout_rs;
+      nx.load((const E *)p.attn + r * p.attn_rs, D, lane);
+      nu.load((const E *)p.u + r * p.u_rs, D, lane);
+      ngy.load(grow + off_y, D, lane);
+      if (p.concat_u) ngu.load(grow, D, lane);
+      if (p.concat_x) ngx.load(grow + off_x, D, lane);
+      nmean = p.mean[r];
+      nrstd = p.rstd[r];
+    }
+  };
+  if (pf && row < p.rows) prefetch(row);
+  for (; row < p.rows; row += step) {
+    Row<E, MAXV> xr, ur, gy, tmp;
+    RawRow<E, RV> cgu, cgx;  // this row's concat gradients (the prefetch buffers get overwritten below)
+    float mean, rstd;
     const E *grow = (const E *)p.dout + row * p.dout_rs;
-    gy.load(grow + off_y, D, lane, p.vec_ok);
-    const float mean = p.mean[row], rstd = p.rstd[row];
+    bool loaded = false;
+    if constexpr (PF) {
+      if (pf) {
+        nx.unpack(xr);
+        nu.unpack(ur);
+        ngy.unpack(gy);
+        cgu = ngu;
+        cgx = ngx;
+        mean = nmean;
+        rstd = nrstd;
+        if (row + step < p.rows) prefetch(row + step);
+        loaded = true;
+      }
+    }
+    if (!loaded) {
+      xr.load((const E *)p.attn + row * p.attn_rs, D, lane, p.vec_ok);
+      ur.load((const E *)p.u + row * p.u_rs, D, lane, p.vec_ok);
+      gy.load(grow + off_y, D, lane, p.vec_ok);
+      mean = p.mean[row];
+      rstd = p.rstd[row];
+    }
     float c1 = 0.f, c2 = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k)
@@ -365,18 +549,26 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
 #pragma unroll
       for (int t = 0; t < EV; ++t) gy.v[k][t] = (gy.v[k][t] - c2 - xr.v[k][t] * c1) * rstd;
     if (p.concat_u) {
-      xr.load(grow, D, lane, p.vec_ok);
+      if (loaded) {
+        if constexpr (PF) cgu.unpack(tmp);
+      } else {
+        tmp.load(grow, D, lane, p.vec_ok);
+      }
 #pragma unroll
       for (int k = 0; k < MAXV; ++k)
 #pragma unroll
-        for (int t = 0; t < EV; ++t) ur.v[k][t] += xr.v[k][t];
+        for (int t = 0; t < EV; ++t) ur.v[k][t] += tmp.v[k][t];
     }
     if (p.concat_x) {
-      xr.load(grow + off_x, D, lane, p.vec_ok);
+      if (loaded) {
+        if constexpr (PF) cgx.unpack(tmp);
+      } else {
+        tmp.load(grow + off_x, D, lane, p.vec_ok);
+      }
 #pragma unroll
       for (int k = 0; k < MAXV; ++k)
 #pragma unroll
-        for (int t = 0; t < EV; ++t) gy.v[k][t] += xr.v[k][t];
+        for (int t = 0; t < EV; ++t) gy.v[k][t] += tmp.v[k][t];
     }
     ur.store((E *)p.du + row * p.du_rs, D, lane, p.vec_ok);
     gy.store((E *)p.dattn + row * p.dattn_rs, D, lane, p.vec_ok);
@@ -492,7 +684,7 @@ int num_sms() {
   return g_num_sms;
 }
 
-constexpr int BWD_BLOCKS_PER_SM = 2;
+constexpr int BWD_BLOCKS_PER_SM = 3;
 int bwd_blocks() { return num_sms() * BWD_BLOCKS_PER_SM; }
 constexpr int MAX_BWD_BLOCKS = 512;  // workspace is sized for this many partial rows
 
@@ -569,8 +761,25 @@ int silu_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out
                 (!bwd || (aligned16(dy) && dy_rs % EV == 0));
   int64_t total = rows * ((width + EV - 1) / EV);
   if (total == 0) return 0;
-  int64_t nblk = (total + 255) / 256;
-  int grid = (int)(nblk < (int64_t)num_sms() * 16 ? nblk : (int64_t)num_sms() * 16);
+  if (vec_ok && width % EV == 0 && width <= 32 * 4 * EV) {
+    int64_t nblk = (rows + WARPS - 1) / WARPS;
+    int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
+    ProfileScope prof(PROF_SILU, st);
+    int maxv = pick_maxv<E>(width);
+    if (bwd) {
+      DISPATCH_MAXV(maxv, (silu_rows_kernel<E, (MV > 4 ? 4 : MV), true><<<grid, WARPS * 32, 0, st>>>(
+                              (const E *)dy, dy_rs, (const E *)x, x_rs, (E *)out, out_rs, rows, width)));
+    } else {
+      DISPATCH_MAXV(maxv, (silu_rows_kernel<E, (MV > 4 ? 4 : MV), false><<<grid, WARPS * 32, 0, st>>>(
+                              nullptr, 0, (const E *)x, x_rs, (E *)out, out_rs, rows, width)));
+    }
+    count_launch();
+    B200_CHECK_LAUNCH("silu (rows)");
+    return 0;
+  }
+  int64_t nblk = (total + 256 * 4 - 1) / (256 * 4);
+  int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
+  if (grid < 1) grid = 1;
   ProfileScope prof(PROF_SILU, st);
   if (bwd)
     silu_kernel<E, true><<<grid, 256, 0, st>>>((const E *)dy, dy_rs, (const E *)x, x_rs, (E *)out, out_rs, rows,
