@@ -103,7 +103,7 @@ class ClockSampler:
 def make_workload(world, name):
     from generative_recommenders_b200 import workloads as W
 
-    if name == "config3":
+    if name in ("config3", "config3_fp8"):
         return W.config3(256 * world)
     return W.config1(SEQS_PER_GPU * world)
 
@@ -330,6 +330,10 @@ def cpu_oracle_step(w, idx, fwd_only):
 
 
 def cpu_baseline(w, fwd_only):
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:
+        pass
     n = min(len(w.lengths), 16)
     idx = list(range(n))
     cpu_oracle_step(w, idx[:2], fwd_only)  # warm-up
@@ -346,6 +350,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm may use every host core
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     w = make_workload(world, args.workload)
     fwd_only = args.workload == "config3" or args.fwd_only
     n = min(len(w.lengths), 8)
