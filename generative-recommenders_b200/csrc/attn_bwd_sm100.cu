@@ -18,9 +18,9 @@
 //     Q are MN-major B operands).
 //   * DKDV = false - a work item is (sequence, 128-row query tile, head): Q and dO stay, K and V
 //     stream; stage 1: S = Q K^T, dP = dO V^T; stage 2: dQ += dS K.
-// Every streamed tile is processed as two 64-column halves (a, b) owned by two warpgroups, and the
-// MMA issue order  stage2_a(i), stage1_a(i+1), stage2_b(i), stage1_b(i+1)  lets the tensor pipe
-// work on one half while the CUDA cores activate the other.  TMEM: 4 x 64 columns of stage-1
+// Every streamed tile is processed as two 64-column halves (a, b); all eight activation warps work
+// on one half at a time, and the MMA issue order  stage2_a(i), stage1_a(i+1), stage2_b(i),
+// stage1_b(i+1)  lets the tensor pipe work on one half while the CUDA cores activate the other.  TMEM: 4 x 64 columns of stage-1
 // tiles + two (DKDV) or one 128-column accumulators.  Constant factors are folded into the
 // epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
 #include "attn_plan.cuh"
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     }
     for (int hf = 0; hf < 2; ++hf) {
       mbar_init(t_full + 8 * hf, 1);
-      mbar_init(w_full + 8 * hf, 4);
+      mbar_init(w_full + 8 * hf, 8);
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 8);
@@ -340,12 +340,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     }
   } else {
     // ------------------------------------------------------------------ activation + epilogue warps
-    const int hf = warp >= 6 ? 1 : 0;          // which half of every streamed tile
+    // All eight warps work on one half of the streamed tile at a time (a, then b): the half is
+    // finished - and handed back to the tensor pipe - soonest when every warp works on it.
+    // Warps 2-5 take columns [0,32) of the half, warps 6-9 columns [32,64); thread = one row of
+    // the stationary tile.
+    const int wg = warp >= 6 ? 1 : 0;
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;  // stationary-tile row owned by this thread
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const uint32_t tT0 = tmem_base + hf * HALF + lane_off;
-    const uint32_t tT1 = tmem_base + 128 + hf * HALF + lane_off;
     uint32_t it_cnt = 0, cnt = 0;
     bool ok = true;
     const float sc = p.attn_scale ? p.attn_scale[0] : p.inv_n;
@@ -365,9 +367,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         ColInterval ci;
         RowInterval ri;
         if (DKDV) ci = col_interval(it, own); else ri = row_interval(it, own);
-        for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
+        for (int j = 0; j < it.n_tiles && ok; ++j, ++cnt) {
           const int o0 = it.tile_at(j) * TILE;  // first position of the streamed tile
-          const int c0 = o0 + hf * HALF;        // first position of this half
           bool full;
           if (DKDV) {  // streamed = query tile o0, stationary = kv tile it.m0; all query rows must exist
             TileItem qi = it;
@@ -376,47 +377,42 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           } else {
             full = !exact_only && tile_pair_is_full(it, o0);
           }
-          ok = mbar_wait(wc, t_full + 8 * hf, cnt & 1, 601);
-          if (!ok) break;
-          tc_fence_after();
-          if (!exact_only) {
-            uint32_t rs[2][32], rp[2][32];
-            tmem_ld32(tT0, rs[0]);
-            tmem_ld32(tT0 + 32, rs[1]);
-            tmem_ld32(tT1, rp[0]);
-            tmem_ld32(tT1 + 32, rp[1]);
-            tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+          for (int hf = 0; hf < 2; ++hf) {
+            const int c0 = o0 + hf * HALF + wg * 32;  // first streamed position of this thread's 32 columns
+            const uint32_t tT0 = tmem_base + hf * HALF + lane_off;
+            const uint32_t tT1 = tmem_base + 128 + hf * HALF + lane_off;
+            ok = mbar_wait(wc, t_full + 8 * hf, cnt & 1, 601);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t rs[32], rp[32];
+            tmem_ld32(tT0 + wg * 32, rs);
+            tmem_ld32(tT1 + wg * 32, rp);
+            tc_wait_ld();
+            // the 16-bit tiles are written over the first 32 columns of T0 / T1: every warp must
+            // hold its scores in registers before anyone stores
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            uint32_t pk[16], dk[16];
+            if (!exact_only) {
               uint32_t bits = 0xffffffffu;
-              if (!full) bits = DKDV ? col_mask_bits(ci, c0 + c * 32, L) : row_mask_bits(ri, c0 + c * 32, L);
-              uint32_t pk[16], dk[16];
+              if (!full) bits = DKDV ? col_mask_bits(ci, c0, L) : row_mask_bits(ri, c0, L);
 #pragma unroll
               for (int x = 0; x < 16; ++x) {
                 float sl0, dsl0, sl1, dsl1;
-                silu_and_grad(__uint_as_float(rs[c][2 * x]) * p.half_alpha, sl0, dsl0);
-                silu_and_grad(__uint_as_float(rs[c][2 * x + 1]) * p.half_alpha, sl1, dsl1);
-                float ds0 = __uint_as_float(rp[c][2 * x]) * dsl0, ds1 = __uint_as_float(rp[c][2 * x + 1]) * dsl1;
+                silu_and_grad(__uint_as_float(rs[2 * x]) * p.half_alpha, sl0, dsl0);
+                silu_and_grad(__uint_as_float(rs[2 * x + 1]) * p.half_alpha, sl1, dsl1);
+                float ds0 = __uint_as_float(rp[2 * x]) * dsl0, ds1 = __uint_as_float(rp[2 * x + 1]) * dsl1;
                 const bool v0 = bits & (1u << (2 * x)), v1 = bits & (1u << (2 * x + 1));
                 if (DKDV) pk[x] = pack2h(v0 ? sl0 : 0.f, v1 ? sl1 : 0.f, IS_BF16);
                 dk[x] = pack2h(v0 ? ds0 : 0.f, v1 ? ds1 : 0.f, IS_BF16);
               }
-              if (DKDV) tmem_st16(tT0 + c * 16, pk);
-              tmem_st16(tT1 + c * 16, dk);
-            }
-          } else {
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-              uint32_t rs[32], rp[32], pk[16], dk[16];
-              tmem_ld32(tT0 + c * 32, rs);
-              tmem_ld32(tT1 + c * 32, rp);
-              tc_wait_ld();
+            } else {
 #pragma unroll
               for (int x = 0; x < 32; x += 2) {
                 float pv[2], dv[2];
 #pragma unroll
                 for (int y = 0; y < 2; ++y) {
-                  const int other = c0 + c * 32 + x + y;
+                  const int other = c0 + x + y;
                   const int qi_ = DKDV ? other : own, kj_ = DKDV ? own : other;
                   float hh = __uint_as_float(rs[x + y]) * p.half_alpha;
                   if (p.bias != nullptr) {
@@ -435,14 +431,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 pk[x / 2] = pack2h(pv[0], pv[1], IS_BF16);
                 dk[x / 2] = pack2h(dv[0], dv[1], IS_BF16);
               }
-              if (DKDV) tmem_st16(tT0 + c * 16, pk);
-              tmem_st16(tT1 + c * 16, dk);
             }
+            if (DKDV) tmem_st16(tT0 + wg * 16, pk);
+            tmem_st16(tT1 + wg * 16, dk);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(w_full + 8 * hf);
           }
-          tc_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(w_full + 8 * hf);
         }
         if (!ok) break;
         // epilogue: the two warpgroups split the accumulator columns in halves
@@ -450,7 +446,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         if (!ok) break;
         tc_fence_after();
         const bool rv = own < L;
-        const int col0 = hf * (D / 2);
+        const int col0 = wg * (D / 2);
         if (DKDV) {
           uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + own) * p.dv_rs + (int64_t)h * p.dv_hs + col0;
           uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + own) * p.dk_rs + (int64_t)h * p.dk_hs + col0;
@@ -463,7 +459,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty);
-        if (hf == 0 && it.len > L && it.m0 + TILE >= L) {
+        if (wg == 0 && it.len > L && it.m0 + TILE >= L) {
           if (DKDV) {
             zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, it.start, L, it.len, row_in_tile);
             zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dv), p.dv_rs, p.dv_hs, h, it.start, L, it.len, row_in_tile);

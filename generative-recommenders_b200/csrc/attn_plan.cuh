@@ -309,15 +309,20 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
   for (int i = threadIdx.x; i < PLAN_BUCKETS; i += PLAN_THREADS) hist[i] = 0;
   if (threadIdx.x == 0) total = 0;
   __syncthreads();
+  // threads are laid out as 64 sequences x 16 tile slots so that the (sequence, tile) pairs of a
+  // batch are costed in parallel instead of one thread walking all tiles of a sequence
+  constexpr int TSLOTS = 16;
+  constexpr int BSLOTS = PLAN_THREADS / TSLOTS;
+  const int tslot = threadIdx.x % TSLOTS, bslot = threadIdx.x / TSLOTS;
   for (int pass = 0; pass < 2; ++pass) {
-    for (int b = threadIdx.x; b < g.B; b += PLAN_THREADS) {
+    for (int b = bslot; b < g.B; b += BSLOTS) {
       const int start = g.seq_offsets[b];
       const int len = g.seq_offsets[b + 1] - start;
       const int nt = g.num_targets ? g.num_targets[b] : 0;
       const int L = len < g.max_seq_len ? len : g.max_seq_len;
       const int ntiles = (L + TILE - 1) / TILE;
       const int nunits = KIND == PLAN_Q_PAIR ? (ntiles + 1) / 2 : ntiles;
-      for (int t = 0; t < nunits; ++t) {
+      for (int t = tslot; t < nunits; t += TSLOTS) {
         int cost = item_cost<KIND>(g, b, t, len, nt);
         cost = cost < PLAN_BUCKETS - 1 ? cost : PLAN_BUCKETS - 1;
         const int bucket = PLAN_BUCKETS - 1 - cost;  // expensive first
