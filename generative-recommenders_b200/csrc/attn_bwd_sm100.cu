@@ -531,7 +531,7 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     ProfileScope prof(PROF_PLAN, st);
     attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
         p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1),
-        max_items);
+        max_items, 0);
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan (backward)");

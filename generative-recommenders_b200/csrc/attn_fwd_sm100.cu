@@ -41,7 +41,7 @@ constexpr int KV_STAGES = 2;
 
 struct FwdParams {
   AttnGeomParams g;
-  const PlanHeader *plan;
+  PlanHeader *plan;
   const ItemDesc *items;
   int *status;
   void *out;
@@ -81,9 +81,10 @@ struct FwdSmem {
   static constexpr int K_OFF = Q_OFF + 2 * TILE_BYTES;
   static constexpr int V_OFF = K_OFF + KV_STAGES * TILE_BYTES;
   static constexpr int BAR_OFF = V_OFF + KV_STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 8;
+  static constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 8 + 2 * SCHED_SLOTS;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-  static constexpr int TOTAL = MISC_OFF + 64;
+  static constexpr int SCHED_OFF = MISC_OFF + 64;
+  static constexpr int TOTAL = SCHED_OFF + SCHED_SLOTS * SCHED_SLOT_BYTES;
   // slack for manual 1024-byte alignment; at least 116 KB so that two CTAs (each of which
   // allocates all 512 TMEM columns) can never share an SM
   static constexpr int DYN_BYTES = (TOTAL + 1024) > 116 * 1024 ? (TOTAL + 1024) : 116 * 1024;
@@ -182,6 +183,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   const uint32_t p_full = s_full + 16;               // [2]: P_A, P_B written
   const uint32_t o_full = p_full + 16;               // [2]: O_A, O_B complete
   const uint32_t o_empty = o_full + 16;              // [2]: O_A, O_B read out
+  const uint32_t sched_full = o_empty + 16;          // [SCHED_SLOTS] next work item published
+  const uint32_t sched_empty = sched_full + 8 * SCHED_SLOTS;
+  uint8_t *sched_ring = smem_gen + SM::SCHED_OFF;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + SM::MISC_OFF);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + SM::MISC_OFF + 8);
 
@@ -204,6 +208,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(o_full + 8 * x, 1);
       mbar_init(o_empty + 8 * x, 8);
     }
+    for (int x = 0; x < SCHED_SLOTS; ++x) {
+      mbar_init(sched_full + 8 * x, 1);
+      mbar_init(sched_empty + 8 * x, SCHED_CONSUMERS);
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -216,7 +224,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   const uint32_t tmem_base = *tmem_slot;
   // TMEM columns: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512)
   const int num_items = p.plan->num_items * p.H;
-  const int stride = gridDim.x;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -228,10 +235,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       bool ok = true;
       Tracer tr;
       tr.init(p.trace, 0, true);
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
-        const ItemDesc d = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      while (idx < num_items && ok) {
+        // claim the next (item, head) index now; its descriptor is fetched and published below,
+        // after this item's loads have been issued
+        const int nidx = atomicAdd(&p.plan->next, 1);
         const int h = idx % p.H;
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
@@ -267,6 +276,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           for (int c = 0; c < SM::CHUNKS; ++c)
             tma_load_2d(sV + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_v, h * D + c * 64, row, v_full + 8 * s);
         }
+        if (!ok) break;
+        ItemDesc nd = d;
+        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
+        ++it_cnt;
+        sched_publish(wc, sched_ring, sched_full, sched_empty, it_cnt, nd.b, nd.t, nd.start, nd.len, nd.nt, nidx, ok);
+        d = nd;
+        idx = nidx;
       }
     }
   } else if (warp == 1) {
@@ -301,10 +317,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         __syncwarp();
       };
 
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
-        const ItemDesc d = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      for (; idx < num_items && ok; ++it_cnt) {
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
         tr.mark(10);
@@ -403,6 +418,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           }
           __syncwarp();
         }
+        if (!ok) break;
+        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, d.b, d.t, d.start, d.len, d.nt, idx,
+                         lane == 0);
       }
     }
   } else {
@@ -420,10 +438,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     Tracer tr;
     tr.init(p.trace, 2 + wg, quad == 2 && lane == 0);
     if ((int)blockIdx.x < num_items) {
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride) {
-        const ItemDesc d = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      uint32_t item_no = 0;
+      while (idx < num_items && ok) {
         const int h = idx % p.H;
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
@@ -544,6 +562,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             }
           }
         }
+        if (!ok) break;
+        ++item_no;
+        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, item_no, d.b, d.t, d.start, d.len, d.nt, idx,
+                         lane == 0);
       }
     }
   }
@@ -612,17 +634,17 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
       p.trace = reinterpret_cast<ulonglong2 *>(reinterpret_cast<uint8_t *>(a.workspace) + need);
   }
   const int max_items = (int)plan_max_items(a.total_L, a.B);
+  const int64_t upper = (int64_t)max_items * a.H;
+  const int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {
     ProfileScope prof(PROF_PLAN, st);
-    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items);
+    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, grid);
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");
   auto kern = hstu_attn_fwd_sm100_kernel<D, IS_BF16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
   if (e != cudaSuccess) return check_cuda(e, "forward smem attribute");
-  int64_t upper = (int64_t)max_items * a.H;
-  int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {
     ProfileScope prof(PROF_ATTN_FWD, st);
     kern<<<grid, FWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, p);

@@ -25,9 +25,10 @@ constexpr int PLAN_THREADS = 1024;
 enum PlanKind { PLAN_Q_PAIR = 0, PLAN_Q_TILE = 1, PLAN_KV_TILE = 2 };
 
 struct PlanHeader {
-  int num_items;   // number of work items
+  int num_items;   // number of work items (to be multiplied by the number of heads)
   int status;      // 0 = ok, else the site id of the first bounded wait that gave up
-  int pad[2];
+  int next;        // dynamic scheduling: next unclaimed (item, head) index; starts at the grid size
+  int pad;
 };
 
 struct __align__(16) ItemDesc {
@@ -301,7 +302,8 @@ __host__ __device__ __forceinline__ int item_cost(const AttnGeomParams &g, int b
 }
 
 template <int KIND>
-__device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *hdr, ItemDesc *items, int max_items) {
+__device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *hdr, ItemDesc *items, int max_items,
+                                          int first_dynamic) {
   static_assert(PLAN_BUCKETS == PLAN_THREADS, "one bucket per thread in the scan");
   __shared__ int hist[PLAN_BUCKETS];
   __shared__ int warp_sums[32];
@@ -371,24 +373,26 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
   if (threadIdx.x == 0) {
     hdr->num_items = total < max_items ? total : max_items;
     hdr->status = 0;
-    hdr->pad[0] = hdr->pad[1] = 0;
+    hdr->next = first_dynamic;
+    hdr->pad = 0;
   }
 }
 
 template <int KIND>
 __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams g, PlanHeader *hdr, ItemDesc *items,
-                                                                 int max_items) {
-  plan_body<KIND>(g, hdr, items, max_items);
+                                                                 int max_items, int first_dynamic) {
+  plan_body<KIND>(g, hdr, items, max_items, first_dynamic);
 }
 
 // two work lists in one launch (one CTA each): the backward's K/V-tile and query-tile lists
 template <int KIND0, int KIND1>
 __global__ void __launch_bounds__(PLAN_THREADS) attn_plan2_kernel(AttnGeomParams g, PlanHeader *hdr0, ItemDesc *items0,
-                                                                  PlanHeader *hdr1, ItemDesc *items1, int max_items) {
+                                                                  PlanHeader *hdr1, ItemDesc *items1, int max_items,
+                                                                  int first_dynamic) {
   if (blockIdx.x == 0)
-    plan_body<KIND0>(g, hdr0, items0, max_items);
+    plan_body<KIND0>(g, hdr0, items0, max_items, first_dynamic);
   else
-    plan_body<KIND1>(g, hdr1, items1, max_items);
+    plan_body<KIND1>(g, hdr1, items1, max_items, first_dynamic);
 }
 
 __device__ __forceinline__ ItemDesc load_desc(const ItemDesc *items, int idx) {
@@ -399,6 +403,25 @@ __device__ __forceinline__ ItemDesc load_desc(const ItemDesc *items, int idx) {
   d.pad[0] = d.pad[1] = d.pad[2] = 0;
   return d;
 }
+
+// ---------------------------------------------------------------------------------------
+// Dynamic work distribution inside a persistent CTA.
+//
+// Every CTA starts with the (item, head) index blockIdx.x and claims further indices from the
+// counter in the plan header with atomicAdd, so CTAs that drew cheap items simply take more of
+// them.  One thread (the TMA producer) claims the index, reads the item's descriptor and publishes
+// both through a small shared-memory ring guarded by mbarriers; the MMA warp and the activation
+// warps pick them up from there (no global-memory latency on their critical path).  An index at or
+// beyond the total ends the loop of every role.
+// ---------------------------------------------------------------------------------------
+constexpr int SCHED_SLOTS = 4;
+constexpr int SCHED_SLOT_BYTES = 32;
+constexpr int SCHED_CONSUMERS = 9;  // MMA warp + 8 activation warps, one arrival each
+
+struct SchedMsg {
+  ItemDesc d;
+  int idx;
+};
 
 inline int64_t plan_max_items(int64_t total_L, int B) { return total_L / TILE + B + 1; }
 inline int64_t plan_bytes(int64_t total_L, int B) {

@@ -84,6 +84,35 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx &ctx, uint32_t bar, uint
   }
 }
 
+// ------------------------------------------------------------------ work ring (see attn_plan.cuh)
+// slot layout: int4 {b, t, start, len}, int4 {nt, idx, 0, 0}
+__device__ __forceinline__ void sched_publish(const WaitCtx &wc, uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                              uint32_t n, int b, int t, int start, int len, int nt, int idx, bool &ok) {
+  // item ordinals start at 1 here (item 0 of a CTA is blockIdx.x and never goes through the ring)
+  const uint32_t m = n - 1, slot = m & 3u;
+  ok = mbar_wait(wc, empty0 + 8 * slot, ((m >> 2) & 1) ^ 1, 901);
+  if (!ok) return;
+  int4 *dst = reinterpret_cast<int4 *>(ring + slot * 32);
+  dst[0] = make_int4(b, t, start, len);
+  dst[1] = make_int4(nt, idx, 0, 0);
+  asm volatile("fence.acq_rel.cta;" ::: "memory");
+  mbar_arrive(full0 + 8 * slot);
+}
+__device__ __forceinline__ bool sched_fetch(const WaitCtx &wc, const uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                            uint32_t n, int &b, int &t, int &start, int &len, int &nt, int &idx,
+                                            bool arrive) {
+  const uint32_t m = n - 1, slot = m & 3u;
+  if (!mbar_wait(wc, full0 + 8 * slot, (m >> 2) & 1, 902)) return false;
+  const volatile int4 *src = reinterpret_cast<const volatile int4 *>(ring + slot * 32);
+  int4 a, c;
+  a.x = src[0].x; a.y = src[0].y; a.z = src[0].z; a.w = src[0].w;
+  c.x = src[1].x; c.y = src[1].y;
+  b = a.x; t = a.y; start = a.z; len = a.w; nt = c.x; idx = c.y;
+  __syncwarp();
+  if (arrive) mbar_arrive(empty0 + 8 * slot);
+  return true;
+}
+
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
