@@ -3,16 +3,21 @@
 //
 //   out[i] = scale_i * sum_j mask(i,j) * SiLU(alpha * q_i.k_j) * v_j
 //
-// One persistent CTA per SM walks a longest-first list of work items; an item is a pair of
-// consecutive 128-row query tiles (A, B) of one sequence and one head, which share every K/V
-// tile they visit.  Ten warps, specialised:
-//   warp 0      TMA producer: the two Q tiles once per item, K and V tiles through 2-stage rings
-//   warp 1      MMA issuer (one lane): S_X = Q_X K^T into TMEM, O_X += P_X V with P_X read back
-//               from TMEM (X = A, B); owns TMEM allocation
-//   warps 2-5   tile A, one query row per thread: tcgen05.ld S_A -> SiLU (one MUFU tanh per
-//               score) -> mask (only on tiles that are not fully visible, from a per-row bit mask)
-//               -> bf16 P_A written over S_A in TMEM; at the end scale O_A and store valid rows
-//   warps 6-9   the same for tile B
+// One persistent CTA per SM takes work items from a longest-first list (the first one by CTA
+// index, the rest through an atomic counter); an item is a pair of consecutive 128-row query
+// tiles (A, B) of one sequence and one head, which share every K/V tile they visit.  Fourteen
+// warps, specialised:
+//   warp 0       TMA producer: the two Q tiles once per item, K and V tiles through 2-stage
+//                rings; claims the next item and publishes it to the other warps
+//   warp 1       MMA issuer (one lane): S_X = Q_X K^T into TMEM, O_X += P_X V with P_X read back
+//                from TMEM (X = A, B); owns TMEM allocation.  While the last kv tile of an item
+//                is being finished it already issues the first S tiles of the next item.
+//   warps 2-9    activation: all eight work on one score tile at a time (A, B, A, ...), one query
+//                row per thread, half the columns per warpgroup: tcgen05.ld S -> SiLU (one MUFU
+//                tanh per pair of scores) -> mask (only on tiles that are not fully visible, from
+//                a per-row bit mask) -> 16-bit P written over S in TMEM
+//   warps 10-13  epilogue: O_X (fp32, TMEM) -> scale -> 16-bit -> global, valid rows only, while
+//                the activation warps are already busy with the next item
 // The issue order  PV_A(j), S_A(j+1), PV_B(j), S_B(j+1)  keeps the tensor pipe busy with tile B
 // while the CUDA cores activate tile A and vice versa.  TMEM: S_A, S_B, O_A, O_B = 4 x 128
 // columns.
@@ -36,7 +41,8 @@ int device_sm_count();
 
 namespace {
 
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 448;
+constexpr int FWD_SCHED_CONSUMERS = 13;  // MMA warp, 8 activation warps, 4 epilogue warps: one arrival each
 constexpr int KV_STAGES = 2;
 
 struct FwdParams {
@@ -163,6 +169,48 @@ __device__ __forceinline__ void silu_chunk_exact(const uint32_t (&r)[32], uint32
   }
 }
 
+// One score tile on the element-wise path, kept out of line: it is rarely taken and several
+// times the size of the interval paths, which should stay close together in the instruction
+// cache.  Same steps as the inline paths: scores to registers, barrier, P over S.
+template <bool IS_BF16>
+__device__ __noinline__ void exact_tile(uint32_t tS, int wg, float half_alpha, SeqMask m, int i, int col0,
+                                        const float *bias, int bias_numel) {
+  uint32_t sreg[2][32];
+  tmem_ld32(tS + wg * 64, sreg[0]);
+  tmem_ld32(tS + wg * 64 + 32, sreg[1]);
+  tc_wait_ld();
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  const int id_i = m.id(i);
+  uint32_t packed[16];
+  silu_chunk_exact<IS_BF16>(sreg[0], packed, half_alpha, m, i, id_i, col0, bias, bias_numel);
+  tmem_st16(tS + wg * 32, packed);
+  silu_chunk_exact<IS_BF16>(sreg[1], packed, half_alpha, m, i, id_i, col0 + 32, bias, bias_numel);
+  tmem_st16(tS + wg * 32 + 16, packed);
+}
+
+// One partially visible score tile on the regular domain (row intervals), also out of line: the
+// loop over fully visible tiles is the hot one.
+template <bool IS_BF16>
+__device__ __noinline__ void masked_tile(uint32_t tS, int wg, float half_alpha, int lo, int hi, int ctx_hi, int self,
+                                         int col0, int L) {
+  uint32_t sreg[2][32];
+  tmem_ld32(tS + wg * 64, sreg[0]);
+  tmem_ld32(tS + wg * 64 + 32, sreg[1]);
+  tc_wait_ld();
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  RowInterval ri;
+  ri.lo = lo;
+  ri.hi = hi;
+  ri.ctx_hi = ctx_hi;
+  ri.self = self;
+  const uint32_t b0 = row_mask_bits(ri, col0, L), b1 = row_mask_bits(ri, col0 + 32, L);
+  uint32_t p0[16], p1[16];
+  silu_chunk<IS_BF16, true>(sreg[0], p0, half_alpha, b0);
+  tmem_st16(tS + wg * 32, p0);
+  silu_chunk<IS_BF16, true>(sreg[1], p1, half_alpha, b1);
+  tmem_st16(tS + wg * 32 + 16, p1);
+}
+
 template <int D, bool IS_BF16>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     hstu_attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -206,11 +254,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(s_full + 8 * x, 1);
       mbar_init(p_full + 8 * x, 8);
       mbar_init(o_full + 8 * x, 1);
-      mbar_init(o_empty + 8 * x, 8);
+      mbar_init(o_empty + 8 * x, 4);
     }
     for (int x = 0; x < SCHED_SLOTS; ++x) {
       mbar_init(sched_full + 8 * x, 1);
-      mbar_init(sched_empty + 8 * x, SCHED_CONSUMERS);
+      mbar_init(sched_empty + 8 * x, FWD_SCHED_CONSUMERS);
     }
     fence_mbar_init();
   }
@@ -319,18 +367,19 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
       ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
       int idx = blockIdx.x;
+      bool pre_issued = false;   // the S tiles of this item's first kv tile were issued during the previous item
       for (; idx < num_items && ok; ++it_cnt) {
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
         tr.mark(10);
-        ok = mbar_wait(wc, q_full, it_cnt & 1, 202);
-        if (!ok) break;
-        tr.mark(11);
         const int n = pr.n_tiles;
         int remaining[2] = {pr.A.n_tiles, pr.B.n_tiles};
         bool started[2] = {false, false};
-        // first kv tile: both S
-        {
+        if (!pre_issued) {
+          // first kv tile: both S
+          ok = mbar_wait(wc, q_full, it_cnt & 1, 202);
+          if (!ok) break;
+          tr.mark(11);
           const int t0 = pr.tile_at(0);
           ok = mbar_wait(wc, k_full + 8 * (kv_cnt % KV_STAGES), (kv_cnt / KV_STAGES) & 1, 201);
           if (!ok) break;
@@ -340,6 +389,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           if (elect_one()) tc_commit(k_empty + 8 * (kv_cnt % KV_STAGES));
           __syncwarp();
         }
+        pre_issued = false;
+        ItemDesc nd = d;
+        int nidx = idx;
+        bool next_item = false, next_b = false;
         for (int j = 0; j < n; ++j, ++kv_cnt) {
           const int t = pr.tile_at(j);
           const bool has_next = j + 1 < n;
@@ -401,6 +454,31 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
               issue_s(X, kv_cnt + 1);
               tr.mark(18 + X);
             }
+            if (X == 0 && j == n - 1) {
+              // The S_A buffer is free from here on: fetch the next item and issue its first S_A
+              // ahead of this item's last P_B V, so that the activation warps find a score tile
+              // waiting when they finish this item.  Q of the next item is loaded as soon as the
+              // S tiles issued so far have completed (q_empty above); its first K tile goes to the
+              // ring slot after this one.
+              ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, nd.b, nd.t, nd.start, nd.len,
+                               nd.nt, nidx, lane == 0);
+              if (!ok) break;
+              if (nidx < num_items) {
+                PairItem np;
+                fill_pair_item(np, p.g, nd.b, nd.t, nd.start, nd.len, nd.nt);
+                const int nt0 = np.tile_at(0);
+                const bool next_a = np.A.visits(nt0);
+                next_b = np.hasB && np.B.visits(nt0);
+                next_item = true;
+                ok = mbar_wait(wc, q_full, (it_cnt + 1) & 1, 209);
+                if (!ok) break;
+                ok = mbar_wait(wc, k_full + 8 * sn, ((kv_cnt + 1) / KV_STAGES) & 1, 210);
+                if (!ok) break;
+                tc_fence_after();
+                if (next_a) issue_s(0, kv_cnt + 1);
+                tr.mark(21);
+              }
+            }
           }
           if (!ok) break;
           // keep the ring phases in step even if neither tile used this slot
@@ -412,19 +490,23 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             ok = mbar_wait(wc, k_full + 8 * sn, ((kv_cnt + 1) / KV_STAGES) & 1, 208);
             if (!ok) break;
           }
+          if (j == n - 1 && next_item) {
+            if (next_b) issue_s(1, kv_cnt + 1);
+            pre_issued = true;
+          }
           if (elect_one()) {
             tc_commit(v_empty + 8 * s);
-            if (has_next) tc_commit(k_empty + 8 * sn);
+            if (has_next || (j == n - 1 && next_item)) tc_commit(k_empty + 8 * sn);
           }
           __syncwarp();
         }
         if (!ok) break;
-        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, d.b, d.t, d.start, d.len, d.nt, idx,
-                         lane == 0);
+        d = nd;
+        idx = nidx;
       }
     }
-  } else {
-    // ------------------------------------------------------------------ SiLU + epilogue warps
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ activation warps
     // All eight warps work on one score tile at a time (A, then B, then A ...): the activation is
     // bound by the MUFU rate of the whole SM, so a tile is finished soonest - and its P handed
     // back to the tensor pipe soonest - when every warp works on it.  Warps 2-5 take columns
@@ -433,10 +515,91 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    uint32_t my_tiles[2] = {0, 0}, my_items[2] = {0, 0};
+    uint32_t tiles_a = 0, tiles_b = 0;   // score tiles processed so far (barrier phases)
     bool ok = true;
     Tracer tr;
     tr.init(p.trace, 2 + wg, quad == 2 && lane == 0);
+    if ((int)blockIdx.x < num_items) {
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      uint32_t item_no = 0;
+      while (idx < num_items && ok) {
+        PairItem pr;
+        fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
+        const int L = pr.A.m.L;
+        const SeqMask m = pr.A.m;
+        const bool exact_only = !pr.A.regular || p.bias != nullptr;
+        const int iA = pr.A.m0 + row_in_tile, iB = pr.B.m0 + row_in_tile;
+        const RowInterval riA = row_interval(pr.A, iA), riB = row_interval(pr.B, iB);
+        // kv tiles on which no element of the tile pair is masked
+        FullRange frA = full_tile_range(pr.A), frB = full_tile_range(pr.B);
+        if (exact_only) frA.hi = frA.lo = frB.hi = frB.lo = 0;
+        // which kv tiles each query tile visits (B visits nothing when the pair has no second tile)
+        const int va_lo = pr.A.t_lo, va_hi = pr.A.t_lo + pr.A.n_main, va_x = pr.A.extra_tile;
+        const int vb_lo = pr.B.t_lo, vb_hi = pr.B.t_lo + pr.B.n_main, vb_x = pr.B.extra_tile;
+        const int n_tiles = pr.n_tiles, t_lo = pr.t_lo, n_main = pr.n_main, x0 = pr.extra0, x1 = pr.extra1;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const int t = j < n_main ? t_lo + j : (j == n_main ? x0 : x1);
+          // the loop over the two query tiles stays rolled: one copy of the hot code
+#pragma unroll 1
+          for (int X = 0; X < 2; ++X) {
+            const bool isb = X != 0;
+            const int v_lo = isb ? vb_lo : va_lo, v_hi = isb ? vb_hi : va_hi, v_x = isb ? vb_x : va_x;
+            if (!((t >= v_lo && t < v_hi) || t == v_x)) continue;
+            const int f_lo = isb ? frB.lo : frA.lo, f_hi = isb ? frB.hi : frA.hi;
+            const bool full = t >= f_lo && t < f_hi;
+            const uint32_t tS = tmem_base + X * 128 + lane_off;
+            const int col0 = t * TILE + wg * 64;
+            tr.mark(30);
+            ok = mbar_wait(wc, s_full + 8 * X, (isb ? tiles_b : tiles_a) & 1, 301);
+            if (!ok) break;
+            tc_fence_after();
+            tr.mark(31);
+            if (full) {
+              uint32_t sreg[2][32];
+              tmem_ld32(tS + wg * 64, sreg[0]);
+              tmem_ld32(tS + wg * 64 + 32, sreg[1]);
+              tc_wait_ld();
+              // P is written over the first 64 columns of S: every warp must have its scores in
+              // registers before anyone stores
+              asm volatile("bar.sync 1, 256;" ::: "memory");
+              tr.mark(32);
+              // one straight-line block, so that the second half's MUFU work is scheduled under
+              // the first half's packing and store
+              uint32_t p0[16], p1[16];
+              silu_chunk<IS_BF16, false>(sreg[0], p0, p.half_alpha, 0xffffffffu);
+              tmem_st16(tS + wg * 32, p0);
+              silu_chunk<IS_BF16, false>(sreg[1], p1, p.half_alpha, 0xffffffffu);
+              tmem_st16(tS + wg * 32 + 16, p1);
+            } else if (!exact_only) {
+              masked_tile<IS_BF16>(tS, wg, p.half_alpha, isb ? riB.lo : riA.lo, isb ? riB.hi : riA.hi,
+                                   isb ? riB.ctx_hi : riA.ctx_hi, isb ? riB.self : riA.self, col0, L);
+            } else {
+              exact_tile<IS_BF16>(tS, wg, p.half_alpha, m, isb ? iB : iA, col0, p.bias, p.bias_numel);
+            }
+            tr.mark(37);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + 8 * X);
+            tr.mark(33);
+            if (isb) ++tiles_b; else ++tiles_a;
+          }
+        }
+        if (!ok) break;
+        ++item_no;
+        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, item_no, d.b, d.t, d.start, d.len, d.nt, idx,
+                         lane == 0);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    // O (fp32, TMEM) -> scale -> 16-bit -> global; thread = one query row, valid rows only
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    uint32_t my_items[2] = {0, 0};
+    bool ok = true;
     if ((int)blockIdx.x < num_items) {
       ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
       int idx = blockIdx.x;
@@ -446,116 +609,44 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
         const int L = pr.A.m.L;
-        const bool exact_only = !pr.A.regular || p.bias != nullptr;
-        const int iA = pr.A.m0 + row_in_tile, iB = pr.B.m0 + row_in_tile;
-        const RowInterval riA = row_interval(pr.A, iA), riB = row_interval(pr.B, iB);
-        for (int j = 0; j < pr.n_tiles && ok; ++j) {
-          const int t = pr.tile_at(j);
-          const int n0 = t * TILE;
-#pragma unroll
-          for (int X = 0; X < 2; ++X) {
-            const TileItem &it = X == 0 ? pr.A : pr.B;
-            if (!((X == 0 || pr.hasB) && it.visits(t))) continue;
-            const int i = X == 0 ? iA : iB;
-            const RowInterval &ri = X == 0 ? riA : riB;
-            const bool full = !exact_only && tile_pair_is_full(it, n0);
-            const uint32_t tS = tmem_base + X * 128 + lane_off;
-            tr.mark(30);
-            ok = mbar_wait(wc, s_full + 8 * X, my_tiles[X] & 1, 301);
-            if (!ok) break;
-            tc_fence_after();
-            tr.mark(31);
-            uint32_t sreg[2][32];
-            tmem_ld32(tS + wg * 64, sreg[0]);
-            tmem_ld32(tS + wg * 64 + 32, sreg[1]);
-            tc_wait_ld();
-            // P is written over the first 64 columns of S: every warp must have its scores in
-            // registers before anyone stores
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            tr.mark(32);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              uint32_t packed[16];
-              const int col0 = n0 + wg * 64 + c * 32;
-              if (full)
-                silu_chunk<IS_BF16, false>(sreg[c], packed, p.half_alpha, 0xffffffffu);
-              else if (!exact_only)
-                silu_chunk<IS_BF16, true>(sreg[c], packed, p.half_alpha, row_mask_bits(ri, col0, L));
-              else
-                silu_chunk_exact<IS_BF16>(sreg[c], packed, p.half_alpha, it.m, i, it.m.id(i), col0, p.bias,
-                                          p.bias_numel);
-              tmem_st16(tS + wg * 32 + c * 16, packed);
-            }
-            tr.mark(37);
-            tc_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * X);
-            tr.mark(33);
-            ++my_tiles[X];
-          }
-        }
-        if (!ok) break;
-        // epilogue: O (fp32, TMEM) -> scale -> 16-bit -> global, valid rows only; the two warpgroups
-        // split the D columns
 #pragma unroll
         for (int X = 0; X < 2; ++X) {
           if (X == 1 && !pr.hasB) continue;
-          const TileItem &it = X == 0 ? pr.A : pr.B;
-          const int i = X == 0 ? iA : iB;
-          tr.mark(34);
+          const int m0 = X == 0 ? pr.A.m0 : pr.B.m0;
+          const int i = m0 + row_in_tile;
           ok = mbar_wait(wc, o_full + 8 * X, my_items[X] & 1, 302);
           if (!ok) break;
           tc_fence_after();
-          tr.mark(35);
           float scale = p.inv_n;
           if (p.attn_scale != nullptr && i < L)
             scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)d.start + i];
-          const int cbase = wg * (D / 2);
-          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + i) * p.o_rs +
-                           (int64_t)h * p.o_hs + cbase;
-          const uint32_t tO = tmem_base + 256 + X * 128 + lane_off + cbase;
-          if (D == 128) {
-            uint32_t r[2][32];
-            tmem_ld32(tO, r[0]);
-            tmem_ld32(tO + 32, r[1]);
-            tc_wait_ld();
-            if (i < L) {
+          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + i) * p.o_rs + (int64_t)h * p.o_hs;
+          const uint32_t tO = tmem_base + 256 + X * 128 + lane_off;
+          uint32_t r[2][32];
+          tmem_ld32(tO, r[0]);
 #pragma unroll
-              for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                  uint4 o4;
-                  o4.x = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 0]) * scale, __uint_as_float(r[cc][8 * x + 1]) * scale);
-                  o4.y = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 2]) * scale, __uint_as_float(r[cc][8 * x + 3]) * scale);
-                  o4.z = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 4]) * scale, __uint_as_float(r[cc][8 * x + 5]) * scale);
-                  o4.w = pack2<IS_BF16>(__uint_as_float(r[cc][8 * x + 6]) * scale, __uint_as_float(r[cc][8 * x + 7]) * scale);
-                  *reinterpret_cast<uint4 *>(orow + cc * 32 + x * 8) = o4;
-                }
-            }
-          } else {
-            uint32_t r[32];
-            tmem_ld32(tO, r);
+          for (int cc = 0; cc < D / 32; ++cc) {
             tc_wait_ld();
+            if (cc + 1 < D / 32) tmem_ld32(tO + (cc + 1) * 32, r[(cc + 1) & 1]);
             if (i < L) {
+              const uint32_t(&v)[32] = r[cc & 1];
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
                 uint4 o4;
-                o4.x = pack2<IS_BF16>(__uint_as_float(r[8 * x + 0]) * scale, __uint_as_float(r[8 * x + 1]) * scale);
-                o4.y = pack2<IS_BF16>(__uint_as_float(r[8 * x + 2]) * scale, __uint_as_float(r[8 * x + 3]) * scale);
-                o4.z = pack2<IS_BF16>(__uint_as_float(r[8 * x + 4]) * scale, __uint_as_float(r[8 * x + 5]) * scale);
-                o4.w = pack2<IS_BF16>(__uint_as_float(r[8 * x + 6]) * scale, __uint_as_float(r[8 * x + 7]) * scale);
-                *reinterpret_cast<uint4 *>(orow + x * 8) = o4;
+                o4.x = pack2<IS_BF16>(__uint_as_float(v[8 * x + 0]) * scale, __uint_as_float(v[8 * x + 1]) * scale);
+                o4.y = pack2<IS_BF16>(__uint_as_float(v[8 * x + 2]) * scale, __uint_as_float(v[8 * x + 3]) * scale);
+                o4.z = pack2<IS_BF16>(__uint_as_float(v[8 * x + 4]) * scale, __uint_as_float(v[8 * x + 5]) * scale);
+                o4.w = pack2<IS_BF16>(__uint_as_float(v[8 * x + 6]) * scale, __uint_as_float(v[8 * x + 7]) * scale);
+                *reinterpret_cast<uint4 *>(orow + cc * 32 + x * 8) = o4;
               }
             }
           }
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(o_empty + 8 * X);
-          tr.mark(36);
           ++my_items[X];
           // rows at or beyond max_seq_len of an over-long sequence come back as zeros
-          if (wg == 0 && d.len > L && it.m0 + TILE >= L) {
+          if (d.len > L && m0 + TILE >= L) {
             for (int r2 = L + row_in_tile; r2 < d.len; r2 += TILE) {
               uint16_t *zr = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + r2) * p.o_rs + (int64_t)h * p.o_hs;
               for (int x = 0; x < D; x += 8) *reinterpret_cast<uint4 *>(zr + x) = make_uint4(0, 0, 0, 0);

@@ -106,6 +106,34 @@ __host__ __device__ __forceinline__ bool tile_pair_is_full(const TileItem &it, i
   return true;
 }
 
+// The kv tiles t for which tile_pair_is_full(it, t * TILE) holds form one range [lo, hi)
+// (possibly empty): every condition above is a lower or an upper bound on n0.
+struct FullRange {
+  int lo, hi;
+};
+__host__ __device__ __forceinline__ FullRange full_tile_range(const TileItem &it) {
+  FullRange r = {0, 0};
+  if (!it.regular) return r;
+  const SeqMask &m = it.m;
+  if (it.m0 < m.c) return r;
+  const int lim = it.m0 < it.u ? it.m0 : it.u;
+  int lo = m.c > 0 ? (m.c + TILE - 1) / TILE : 0;
+  if (m.W > 0) {
+    if (m.F > 0) return r;
+    const int rows_end = it.m0 + TILE < m.L ? it.m0 + TILE : m.L;
+    const int eff_last = rows_end - 1 < it.u ? rows_end - 1 : it.u;
+    const int first = eff_last - m.W;   // n0 >= first
+    if (first > 0) {
+      const int t = (first + TILE - 1) / TILE;
+      lo = t > lo ? t : lo;
+    }
+  }
+  r.lo = lo;
+  r.hi = lim > 0 ? lim / TILE : 0;      // (t + 1) * TILE <= lim
+  if (r.hi < r.lo) r.hi = r.lo;
+  return r;
+}
+
 // q tiles that the kv tile `kt` of a sequence has to visit (backward, kv-stationary): a
 // conservative contiguous range [t_lo, t_hi) plus, when contextual rows exist, tile 0.
 __host__ __device__ __forceinline__ void fill_kv_item(TileItem &it, const AttnGeomParams &g, int b, int kt, int start,
