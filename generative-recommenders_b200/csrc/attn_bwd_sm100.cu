@@ -12,17 +12,25 @@
 // bit-reproducible:
 //   * DKDV = true  - a work item is (sequence, 128-row K/V tile, head).  K and V stay in shared
 //     memory; the Q and dO tiles of every query tile that can see the K/V tile stream through
-//     2-stage TMA rings.  Stage 1: S^T = K Q^T and dP^T = V dO^T into TMEM.  The 128 threads that
+//     2-stage TMA rings.  Stage 1: S^T = K Q^T and dP^T = V dO^T into TMEM.  The threads that
 //     own one K/V row each turn them into bf16 P^T and dS^T written back over the same TMEM
 //     columns.  Stage 2: dV += P^T dO and dK += dS^T Q with the TMEM tiles as A operands (dO and
 //     Q are MN-major B operands).
 //   * DKDV = false - a work item is (sequence, 128-row query tile, head): Q and dO stay, K and V
-//     stream; stage 1: S = Q K^T, dP = dO V^T; stage 2: dQ += dS K.
-// Every streamed tile is processed as two 64-column halves (a, b); all eight activation warps work
-// on one half at a time, and the MMA issue order  stage2_a(i), stage1_a(i+1), stage2_b(i),
-// stage1_b(i+1)  lets the tensor pipe work on one half while the CUDA cores activate the other.  TMEM: 4 x 64 columns of stage-1
-// tiles + two (DKDV) or one 128-column accumulators.  Constant factors are folded into the
-// epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
+//     stream; stage 1: S = Q K^T, dP = dO V^T; stage 2: dQ += dS K.  Consecutive items alternate
+//     between two dQ accumulators, so an item never waits for the previous one to be stored.
+// Fourteen warps, specialised:
+//   warp 0       TMA producer; claims the next item from an atomic counter and publishes it
+//   warp 1       MMA issuer; owns TMEM.  Every streamed tile is processed as two 64-column halves
+//                (a, b) in the order  stage2_a(i), stage1_a(i+1), stage2_b(i), stage1_b(i+1),  so
+//                the tensor pipe works on one half while the CUDA cores activate the other; during
+//                the last tile of an item the stage-1 tiles of the next item are issued instead.
+//                The stationary tiles are released as soon as the item's last stage 1 is issued.
+//   warps 2-9    activation: all eight work on one half at a time, one row of the stationary tile
+//                per thread, 32 of the half's 64 columns per warpgroup
+//   warps 10-13  epilogue: accumulators (fp32, TMEM) -> scale -> 16-bit -> global
+// TMEM: 4 x 64 columns of stage-1 tiles + two 128-column accumulators.  Constant factors are
+// folded into the epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
 #include "attn_plan.cuh"
 #include "sm100_ptx.cuh"
 
@@ -36,12 +44,13 @@ int device_sm_count();
 
 namespace {
 
-constexpr int BWD_THREADS = 320;
+constexpr int BWD_THREADS = 448;
 constexpr int STAGES = 2;
+constexpr int BWD_SCHED_CONSUMERS = 13;  // MMA warp, 8 activation warps, 4 epilogue warps: one arrival each
 
 struct BwdParams {
   AttnGeomParams g;
-  const PlanHeader *plan;
+  PlanHeader *plan;
   const ItemDesc *items;
   int *status;
   void *dq, *dk, *dv;
@@ -63,9 +72,10 @@ struct BwdSmem {
   static constexpr int X_OFF = B_OFF + TILE_BYTES;                // streamed ring 0 (Q or K)
   static constexpr int Y_OFF = X_OFF + STAGES * TILE_BYTES;       // streamed ring 1 (dO or V)
   static constexpr int BAR_OFF = Y_OFF + STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 24;
+  static constexpr int NUM_BARS = 32;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-  static constexpr int TOTAL = MISC_OFF + 64;
+  static constexpr int SCHED_OFF = MISC_OFF + 64;
+  static constexpr int TOTAL = SCHED_OFF + SCHED_SLOTS * SCHED_SLOT_BYTES;
   static constexpr int DYN_BYTES = (TOTAL + 1024) > 116 * 1024 ? (TOTAL + 1024) : 116 * 1024;
 };
 
@@ -88,22 +98,104 @@ __device__ __forceinline__ void silu_and_grad(float h, float &silu, float &dsilu
   dsilu = fmaf(silu, om, sg);
 }
 
+constexpr int HALF = 64;  // streamed-tile columns processed at a time
+
+// One half of a streamed tile, 32 columns per thread: scores and dP from TMEM, P (kv-stationary
+// launch only) and dS back over them as 16-bit tiles.  `bits` marks the visible columns; with
+// MASKED = false all of them are.
+template <bool IS_BF16, bool DKDV, bool MASKED>
+__device__ __forceinline__ void act_half(uint32_t tT0, uint32_t tT1, int wg, float half_alpha, uint32_t bits) {
+  uint32_t rs[32], rp[32];
+  tmem_ld32(tT0 + wg * 32, rs);
+  tmem_ld32(tT1 + wg * 32, rp);
+  tc_wait_ld();
+  // the 16-bit tiles are written over the first 32 columns of T0 / T1: every warp must hold its
+  // scores in registers before anyone stores
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  uint32_t pk[16], dk[16];
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    float sl0, dsl0, sl1, dsl1;
+    silu_and_grad(__uint_as_float(rs[2 * x]) * half_alpha, sl0, dsl0);
+    silu_and_grad(__uint_as_float(rs[2 * x + 1]) * half_alpha, sl1, dsl1);
+    float ds0 = __uint_as_float(rp[2 * x]) * dsl0, ds1 = __uint_as_float(rp[2 * x + 1]) * dsl1;
+    if (MASKED) {
+      const bool v0 = bits & (1u << (2 * x)), v1 = bits & (1u << (2 * x + 1));
+      sl0 = v0 ? sl0 : 0.f;
+      sl1 = v1 ? sl1 : 0.f;
+      ds0 = v0 ? ds0 : 0.f;
+      ds1 = v1 ? ds1 : 0.f;
+    }
+    if (DKDV) pk[x] = pack2h(sl0, sl1, IS_BF16);
+    dk[x] = pack2h(ds0, ds1, IS_BF16);
+  }
+  if (DKDV) tmem_st16(tT0 + wg * 16, pk);
+  tmem_st16(tT1 + wg * 16, dk);
+}
+
+// The partially visible and the element-wise variants stay out of line: the loop over fully
+// visible tiles is the hot one and should stay small.
+template <bool IS_BF16, bool DKDV>
+__device__ __noinline__ void act_half_masked(uint32_t tT0, uint32_t tT1, int wg, float half_alpha, uint32_t bits) {
+  act_half<IS_BF16, DKDV, true>(tT0, tT1, wg, half_alpha, bits);
+}
+
+template <bool IS_BF16, bool DKDV>
+__device__ __noinline__ void act_half_exact(uint32_t tT0, uint32_t tT1, int wg, float half_alpha, SeqMask m, int own,
+                                            int c0, const float *bias, int bias_numel) {
+  uint32_t rs[32], rp[32];
+  tmem_ld32(tT0 + wg * 32, rs);
+  tmem_ld32(tT1 + wg * 32, rp);
+  tc_wait_ld();
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  const int L = m.L;
+  const int id_own = m.id(own);
+  uint32_t pk[16], dk[16];
+#pragma unroll
+  for (int x = 0; x < 32; x += 2) {
+    float pv[2], dv[2];
+#pragma unroll
+    for (int y = 0; y < 2; ++y) {
+      const int other = c0 + x + y;
+      const int qi_ = DKDV ? other : own, kj_ = DKDV ? own : other;
+      float hh = __uint_as_float(rs[x + y]) * half_alpha;
+      if (bias != nullptr) {
+        int dist = qi_ > kj_ ? qi_ - kj_ : kj_ - qi_;
+        if (dist < bias_numel) hh += 0.5f * bias[dist];
+      }
+      float sl, dsl;
+      silu_and_grad(hh, sl, dsl);
+      float ds = __uint_as_float(rp[x + y]) * dsl;
+      const int id_other = m.id(other);
+      bool valid = qi_ < L && kj_ < L && m.valid_ids(qi_, kj_, DKDV ? id_other : id_own, DKDV ? id_own : id_other);
+      pv[y] = valid ? sl : 0.f;
+      dv[y] = valid ? ds : 0.f;
+    }
+    pk[x / 2] = pack2h(pv[0], pv[1], IS_BF16);
+    dk[x / 2] = pack2h(dv[0], dv[1], IS_BF16);
+  }
+  if (DKDV) tmem_st16(tT0 + wg * 16, pk);
+  tmem_st16(tT1 + wg * 16, dk);
+}
+
 // Stores one 128 x D fp32 accumulator (TMEM) as scaled 16-bit rows of a jagged tensor.
 template <int D, bool IS_BF16>
 __device__ __forceinline__ void store_acc_rows(uint32_t tacc, float scale, uint16_t *row_ptr, bool row_valid) {
-#pragma unroll 1
+  uint32_t r[2][32];
+  tmem_ld32(tacc, r[0]);
+#pragma unroll
   for (int c = 0; c < D / 32; ++c) {
-    uint32_t r[32];
-    tmem_ld32(tacc + c * 32, r);
     tc_wait_ld();
+    if (c + 1 < D / 32) tmem_ld32(tacc + (c + 1) * 32, r[(c + 1) & 1]);
     if (row_valid) {
+      const uint32_t(&v)[32] = r[c & 1];
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
         uint4 o4;
-        o4.x = pack2h(__uint_as_float(r[8 * x + 0]) * scale, __uint_as_float(r[8 * x + 1]) * scale, IS_BF16);
-        o4.y = pack2h(__uint_as_float(r[8 * x + 2]) * scale, __uint_as_float(r[8 * x + 3]) * scale, IS_BF16);
-        o4.z = pack2h(__uint_as_float(r[8 * x + 4]) * scale, __uint_as_float(r[8 * x + 5]) * scale, IS_BF16);
-        o4.w = pack2h(__uint_as_float(r[8 * x + 6]) * scale, __uint_as_float(r[8 * x + 7]) * scale, IS_BF16);
+        o4.x = pack2h(__uint_as_float(v[8 * x + 0]) * scale, __uint_as_float(v[8 * x + 1]) * scale, IS_BF16);
+        o4.y = pack2h(__uint_as_float(v[8 * x + 2]) * scale, __uint_as_float(v[8 * x + 3]) * scale, IS_BF16);
+        o4.z = pack2h(__uint_as_float(v[8 * x + 4]) * scale, __uint_as_float(v[8 * x + 5]) * scale, IS_BF16);
+        o4.w = pack2h(__uint_as_float(v[8 * x + 6]) * scale, __uint_as_float(v[8 * x + 7]) * scale, IS_BF16);
         *reinterpret_cast<uint4 *>(row_ptr + c * 32 + x * 8) = o4;
       }
     }
@@ -119,8 +211,11 @@ __device__ __forceinline__ void zero_rows_beyond(uint16_t *base, int64_t rs, int
   }
 }
 
-
-constexpr int HALF = 64;  // streamed-tile columns owned by one warpgroup
+template <bool DKDV>
+__device__ __forceinline__ void fill_bwd_item(TileItem &it, const AttnGeomParams &g, const ItemDesc &d) {
+  if (DKDV) fill_kv_item(it, g, d.b, d.t, d.start, d.len, d.nt);
+  else fill_q_item(it, g, d.b, d.t, d.start, d.len, d.nt);
+}
 
 template <int D, bool IS_BF16, bool DKDV>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -143,8 +238,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   const uint32_t y0_full = bars + 16, y0_empty = y0_full + 8 * STAGES;
   const uint32_t y1_full = y0_empty + 8 * STAGES, y1_empty = y1_full + 8 * STAGES;
   const uint32_t t_full = y1_empty + 8 * STAGES;   // [2] stage-1 tiles of half a / b ready
-  const uint32_t w_full = t_full + 16;             // [2] bf16 tiles of half a / b written
-  const uint32_t acc_full = w_full + 16, acc_empty = acc_full + 8;
+  const uint32_t w_full = t_full + 16;             // [2] 16-bit tiles of half a / b written
+  const uint32_t acc_full = w_full + 16;           // [2] accumulator set complete
+  const uint32_t acc_empty = acc_full + 16;        // [2] accumulator set stored
+  const uint32_t sched_full = acc_empty + 16;      // [SCHED_SLOTS] next work item published
+  const uint32_t sched_empty = sched_full + 8 * SCHED_SLOTS;
+  uint8_t *sched_ring = smem_gen + SM::SCHED_OFF;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + SM::MISC_OFF);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + SM::MISC_OFF + 8);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -160,12 +259,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       mbar_init(y1_full + 8 * s, 1);
       mbar_init(y1_empty + 8 * s, 1);
     }
-    for (int hf = 0; hf < 2; ++hf) {
-      mbar_init(t_full + 8 * hf, 1);
-      mbar_init(w_full + 8 * hf, 8);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(t_full + 8 * x, 1);
+      mbar_init(w_full + 8 * x, 8);
+      mbar_init(acc_full + 8 * x, 1);
+      mbar_init(acc_empty + 8 * x, 4);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 8);
+    for (int x = 0; x < SCHED_SLOTS; ++x) {
+      mbar_init(sched_full + 8 * x, 1);
+      mbar_init(sched_empty + 8 * x, BWD_SCHED_CONSUMERS);
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -177,9 +280,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // TMEM columns: T0_a [0,64) T0_b [64,128) T1_a [128,192) T1_b [192,256) ACC0 [256,384) ACC1 [384,512)
-  //   T0 = S^T | S,  T1 = dP^T | dP,  ACC0 = dV | dQ,  ACC1 = dK | unused
+  //   T0 = S^T | S,  T1 = dP^T | dP;  kv-stationary: ACC0 = dV, ACC1 = dK (one set);
+  //   q-stationary: ACC0 / ACC1 = dQ of even / odd items (two sets)
   const int num_items = p.plan->num_items * p.H;
-  const int stride = gridDim.x;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -187,14 +290,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
       uint32_t it_cnt = 0, cnt = 0;
       bool ok = true;
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
-        const ItemDesc dsc = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      while (idx < num_items && ok) {
+        const int nidx = atomicAdd(&p.plan->next, 1);
         const int h = idx % p.H;
         TileItem it;
-        if (DKDV) fill_kv_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
-        else fill_q_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        fill_bwd_item<DKDV>(it, p.g, d);
         ok = mbar_wait(wc, x_empty, (it_cnt & 1) ^ 1, 401);
         if (!ok) break;
         mbar_arrive_expect_tx(x_full, 2 * SM::TILE_BYTES);
@@ -220,6 +322,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           for (int c = 0; c < SM::CHUNKS; ++c)
             tma_load_2d(sY1 + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row, y1_full + 8 * s);
         }
+        if (!ok) break;
+        ItemDesc nd = d;
+        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
+        ++it_cnt;
+        sched_publish(wc, sched_ring, sched_full, sched_empty, it_cnt, nd.b, nd.t, nd.start, nd.len, nd.nt, nidx, ok);
+        d = nd;
+        idx = nidx;
       }
     }
   } else if (warp == 1) {
@@ -253,19 +362,25 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         __syncwarp();
       };
+      // the stationary tiles have no reader left once the item's last stage 1 has been issued
+      auto release_x = [&]() {
+        if (elect_one()) tc_commit(x_empty);
+        __syncwarp();
+      };
 
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
-        const ItemDesc dsc = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      bool pre_issued = false;  // stage 1 of this item's first tile was issued while the previous item finished
+      for (; idx < num_items && ok; ++it_cnt) {
         TileItem it;
-        if (DKDV) fill_kv_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
-        else fill_q_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
-        ok = mbar_wait(wc, x_full, it_cnt & 1, 501);
-        if (!ok) break;
+        fill_bwd_item<DKDV>(it, p.g, d);
         const int n = it.n_tiles;
-        // first streamed tile: stage 1 of both halves
-        {
+        // accumulator set of this item and how often it has been used before
+        const int aset = DKDV ? 0 : (int)(it_cnt & 1);
+        const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
+        if (!pre_issued) {
+          ok = mbar_wait(wc, x_full, it_cnt & 1, 501);
+          if (!ok) break;
           const int s = cnt % STAGES;
           ok = mbar_wait(wc, y0_full + 8 * s, (cnt / STAGES) & 1, 502);
           if (!ok) break;
@@ -274,12 +389,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tc_fence_after();
           stage1(0, s);
           stage1(1, s);
+          if (n == 1) release_x();
         }
+        pre_issued = false;
+        ItemDesc nd = d;
+        int nidx = idx;
+        bool next_item = false;
+        int next_n = 0;
         for (int j = 0; j < n; ++j, ++cnt) {
           const int s = cnt % STAGES, sn = (cnt + 1) % STAGES;
           const bool has_next = j + 1 < n;
-          if (j == 0) {  // the previous item's accumulators must have been read out
-            ok = mbar_wait(wc, acc_empty, (it_cnt & 1) ^ 1, 504);
+          if (j == 0) {  // the previous user of this accumulator set must have been stored
+            ok = mbar_wait(wc, acc_empty + 8 * aset, (ause & 1) ^ 1, 504);
             if (!ok) break;
           }
           bool next_ready = false;
@@ -306,9 +427,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
               } else {
 #pragma unroll
                 for (int ks = 0; ks < HALF / 16; ++ks)  // dQ += dS K
-                  mma_ts(tmem_base + 256, tmem_base + 128 + hf * HALF + ks * 8, desc_advance(y0_mn, ks * 2048),
-                         idesc_2, (acc_on || ks > 0) ? 1u : 0u);
+                  mma_ts(tmem_base + 256 + aset * 128, tmem_base + 128 + hf * HALF + ks * 8,
+                         desc_advance(y0_mn, ks * 2048), idesc_2, (acc_on || ks > 0) ? 1u : 0u);
               }
+              if (!has_next && hf == 1) tc_commit(acc_full + 8 * aset);
             }
             __syncwarp();
             if (has_next) {
@@ -321,6 +443,33 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_fence_after();
               }
               stage1(hf, sn);
+              if (hf == 1 && j == n - 2) release_x();
+            } else if (hf == 0) {
+              // Last tile of the item: the half-a tiles are free from here on.  Fetch the next
+              // item and issue stage 1 of its first tile, half a now and half b after this
+              // item's last stage 2; its stationary tiles were requested when this item's last
+              // stage 1 was issued, its first streamed tile goes to the other ring slot.
+              ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, nd.b, nd.t, nd.start, nd.len,
+                               nd.nt, nidx, lane == 0);
+              if (!ok) break;
+              if (nidx < num_items) {
+                TileItem ni;
+                fill_bwd_item<DKDV>(ni, p.g, nd);
+                next_n = ni.n_tiles;
+                next_item = true;
+                ok = mbar_wait(wc, x_full, (it_cnt + 1) & 1, 508);
+                if (!ok) break;
+                ok = mbar_wait(wc, y0_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 509);
+                if (!ok) break;
+                ok = mbar_wait(wc, y1_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 510);
+                if (!ok) break;
+                tc_fence_after();
+                stage1(0, sn);
+              }
+            } else if (next_item) {
+              stage1(1, sn);
+              if (next_n == 1) release_x();
+              pre_issued = true;
             }
           }
           if (!ok) break;
@@ -331,15 +480,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           __syncwarp();
         }
         if (!ok) break;
-        if (elect_one()) {
-          tc_commit(x_empty);
-          tc_commit(acc_full);
-        }
-        __syncwarp();
+        d = nd;
+        idx = nidx;
       }
     }
-  } else {
-    // ------------------------------------------------------------------ activation + epilogue warps
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ activation warps
     // All eight warps work on one half of the streamed tile at a time (a, then b): the half is
     // finished - and handed back to the tensor pipe - soonest when every warp works on it.
     // Warps 2-5 take columns [0,32) of the half, warps 6-9 columns [32,64); thread = one row of
@@ -348,21 +494,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;  // stationary-tile row owned by this thread
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    uint32_t it_cnt = 0, cnt = 0;
+    uint32_t cnt = 0, item_no = 0;
     bool ok = true;
-    const float sc = p.attn_scale ? p.attn_scale[0] : p.inv_n;
     if ((int)blockIdx.x < num_items) {
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
-        const ItemDesc dsc = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
-        const int h = idx % p.H;
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      while (idx < num_items && ok) {
         TileItem it;
-        if (DKDV) fill_kv_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
-        else fill_q_item(it, p.g, dsc.b, dsc.t, dsc.start, dsc.len, dsc.nt);
+        fill_bwd_item<DKDV>(it, p.g, d);
         const int L = it.m.L;
         const int own = it.m0 + row_in_tile;  // kv position (DKDV) or query position
-        const int id_own = it.m.id(own);
         const bool exact_only = !it.regular || p.bias != nullptr;
         ColInterval ci;
         RowInterval ri;
@@ -377,7 +518,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           } else {
             full = !exact_only && tile_pair_is_full(it, o0);
           }
-#pragma unroll
+#pragma unroll 1
           for (int hf = 0; hf < 2; ++hf) {
             const int c0 = o0 + hf * HALF + wg * 32;  // first streamed position of this thread's 32 columns
             const uint32_t tT0 = tmem_base + hf * HALF + lane_off;
@@ -385,55 +526,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             ok = mbar_wait(wc, t_full + 8 * hf, cnt & 1, 601);
             if (!ok) break;
             tc_fence_after();
-            uint32_t rs[32], rp[32];
-            tmem_ld32(tT0 + wg * 32, rs);
-            tmem_ld32(tT1 + wg * 32, rp);
-            tc_wait_ld();
-            // the 16-bit tiles are written over the first 32 columns of T0 / T1: every warp must
-            // hold its scores in registers before anyone stores
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            uint32_t pk[16], dk[16];
-            if (!exact_only) {
-              uint32_t bits = 0xffffffffu;
-              if (!full) bits = DKDV ? col_mask_bits(ci, c0, L) : row_mask_bits(ri, c0, L);
-#pragma unroll
-              for (int x = 0; x < 16; ++x) {
-                float sl0, dsl0, sl1, dsl1;
-                silu_and_grad(__uint_as_float(rs[2 * x]) * p.half_alpha, sl0, dsl0);
-                silu_and_grad(__uint_as_float(rs[2 * x + 1]) * p.half_alpha, sl1, dsl1);
-                float ds0 = __uint_as_float(rp[2 * x]) * dsl0, ds1 = __uint_as_float(rp[2 * x + 1]) * dsl1;
-                const bool v0 = bits & (1u << (2 * x)), v1 = bits & (1u << (2 * x + 1));
-                if (DKDV) pk[x] = pack2h(v0 ? sl0 : 0.f, v1 ? sl1 : 0.f, IS_BF16);
-                dk[x] = pack2h(v0 ? ds0 : 0.f, v1 ? ds1 : 0.f, IS_BF16);
-              }
+            if (full) {
+              act_half<IS_BF16, DKDV, false>(tT0, tT1, wg, p.half_alpha, 0xffffffffu);
+            } else if (!exact_only) {
+              const uint32_t bits = DKDV ? col_mask_bits(ci, c0, L) : row_mask_bits(ri, c0, L);
+              act_half_masked<IS_BF16, DKDV>(tT0, tT1, wg, p.half_alpha, bits);
             } else {
-#pragma unroll
-              for (int x = 0; x < 32; x += 2) {
-                float pv[2], dv[2];
-#pragma unroll
-                for (int y = 0; y < 2; ++y) {
-                  const int other = c0 + x + y;
-                  const int qi_ = DKDV ? other : own, kj_ = DKDV ? own : other;
-                  float hh = __uint_as_float(rs[x + y]) * p.half_alpha;
-                  if (p.bias != nullptr) {
-                    int dist = qi_ > kj_ ? qi_ - kj_ : kj_ - qi_;
-                    if (dist < p.bias_numel) hh += 0.5f * p.bias[dist];
-                  }
-                  float sl, dsl;
-                  silu_and_grad(hh, sl, dsl);
-                  float ds = __uint_as_float(rp[x + y]) * dsl;
-                  const int id_other = it.m.id(other);
-                  bool valid = qi_ < L && kj_ < L &&
-                               it.m.valid_ids(qi_, kj_, DKDV ? id_other : id_own, DKDV ? id_own : id_other);
-                  pv[y] = valid ? sl : 0.f;
-                  dv[y] = valid ? ds : 0.f;
-                }
-                pk[x / 2] = pack2h(pv[0], pv[1], IS_BF16);
-                dk[x / 2] = pack2h(dv[0], dv[1], IS_BF16);
-              }
+              act_half_exact<IS_BF16, DKDV>(tT0, tT1, wg, p.half_alpha, it.m, own, c0, p.bias, p.bias_numel);
             }
-            if (DKDV) tmem_st16(tT0 + wg * 16, pk);
-            tmem_st16(tT1 + wg * 16, dk);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -441,25 +541,48 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           }
         }
         if (!ok) break;
-        // epilogue: the two warpgroups split the accumulator columns in halves
-        ok = mbar_wait(wc, acc_full, it_cnt & 1, 602);
+        ++item_no;
+        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, item_no, d.b, d.t, d.start, d.len, d.nt, idx,
+                         lane == 0);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    // accumulators (fp32, TMEM) -> scale -> 16-bit -> global; thread = one row of the stationary tile
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    uint32_t it_cnt = 0;
+    bool ok = true;
+    const float sc = p.attn_scale ? p.attn_scale[0] : p.inv_n;
+    if ((int)blockIdx.x < num_items) {
+      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
+      int idx = blockIdx.x;
+      while (idx < num_items && ok) {
+        const int h = idx % p.H;
+        TileItem it;
+        fill_bwd_item<DKDV>(it, p.g, d);
+        const int L = it.m.L;
+        const int own = it.m0 + row_in_tile;
+        const bool rv = own < L;
+        const int aset = DKDV ? 0 : (int)(it_cnt & 1);
+        const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
+        ok = mbar_wait(wc, acc_full + 8 * aset, ause & 1, 602);
         if (!ok) break;
         tc_fence_after();
-        const bool rv = own < L;
-        const int col0 = wg * (D / 2);
         if (DKDV) {
-          uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + own) * p.dv_rs + (int64_t)h * p.dv_hs + col0;
-          uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + own) * p.dk_rs + (int64_t)h * p.dk_hs + col0;
-          store_acc_rows<D / 2, IS_BF16>(tmem_base + 256 + col0 + lane_off, sc, dvrow, rv);
-          store_acc_rows<D / 2, IS_BF16>(tmem_base + 384 + col0 + lane_off, sc * p.alpha, dkrow, rv);
+          uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + own) * p.dv_rs + (int64_t)h * p.dv_hs;
+          uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + own) * p.dk_rs + (int64_t)h * p.dk_hs;
+          store_acc_rows<D, IS_BF16>(tmem_base + 256 + lane_off, sc, dvrow, rv);
+          store_acc_rows<D, IS_BF16>(tmem_base + 384 + lane_off, sc * p.alpha, dkrow, rv);
         } else {
-          uint16_t *dqrow = reinterpret_cast<uint16_t *>(p.dq) + (int64_t)(it.start + own) * p.dq_rs + (int64_t)h * p.dq_hs + col0;
-          store_acc_rows<D / 2, IS_BF16>(tmem_base + 256 + col0 + lane_off, sc * p.alpha, dqrow, rv);
+          uint16_t *dqrow = reinterpret_cast<uint16_t *>(p.dq) + (int64_t)(it.start + own) * p.dq_rs + (int64_t)h * p.dq_hs;
+          store_acc_rows<D, IS_BF16>(tmem_base + 256 + aset * 128 + lane_off, sc * p.alpha, dqrow, rv);
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty);
-        if (wg == 0 && it.len > L && it.m0 + TILE >= L) {
+        if (lane == 0) mbar_arrive(acc_empty + 8 * aset);
+        if (it.len > L && it.m0 + TILE >= L) {
           if (DKDV) {
             zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, it.start, L, it.len, row_in_tile);
             zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dv), p.dv_rs, p.dv_hs, h, it.start, L, it.len, row_in_tile);
@@ -467,6 +590,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dq), p.dq_rs, p.dq_hs, h, it.start, L, it.len, row_in_tile);
           }
         }
+        ++it_cnt;
+        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt, d.b, d.t, d.start, d.len, d.nt, idx,
+                         lane == 0);
       }
     }
   }
@@ -525,18 +651,18 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.H = a.H;
   const int max_items = (int)plan_max_items(a.total_L, a.B);
   const int64_t one = plan_bytes(a.total_L, a.B);
+  const int64_t upper = (int64_t)max_items * a.H;
+  const int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(a.workspace);
   PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + one);
   {
     ProfileScope prof(PROF_PLAN, st);
     attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
         p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1),
-        max_items, 0);
+        max_items, grid);
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan (backward)");
-  int64_t upper = (int64_t)max_items * a.H;
-  int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {
     auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
