@@ -31,6 +31,8 @@
 //   warps 10-13  epilogue: accumulators (fp32, TMEM) -> scale -> 16-bit -> global
 // TMEM: 4 x 64 columns of stage-1 tiles + two 128-column accumulators.  Constant factors are
 // folded into the epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
+#include <stdlib.h>
+
 #include "attn_plan.cuh"
 #include "sm100_ptx.cuh"
 
@@ -38,8 +40,8 @@ namespace b200hstu {
 
 using namespace ptx;
 
-int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
-                  int elem_bytes, bool is_bf16);
+int make_tile_map_rows(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
+                       int elem_bytes, bool is_bf16, int box_rows);
 int device_sm_count();
 
 namespace {
@@ -60,6 +62,7 @@ struct BwdParams {
   int bias_numel;
   float half_alpha, alpha, inv_n;
   int H;
+  ulonglong2 *trace;  // optional timeline of CTA 0 (see Tracer); NULL = off
 };
 
 template <int D>
@@ -72,7 +75,7 @@ struct BwdSmem {
   static constexpr int X_OFF = B_OFF + TILE_BYTES;                // streamed ring 0 (Q or K)
   static constexpr int Y_OFF = X_OFF + STAGES * TILE_BYTES;       // streamed ring 1 (dO or V)
   static constexpr int BAR_OFF = Y_OFF + STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 32;
+  static constexpr int NUM_BARS = 40;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
   static constexpr int SCHED_OFF = MISC_OFF + 64;
   static constexpr int TOTAL = SCHED_OFF + SCHED_SLOTS * SCHED_SLOT_BYTES;
@@ -235,9 +238,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   const CUtensorMap *mapY1 = DKDV ? &tmap_do : &tmap_v;
   const uint32_t bars = smem_base + SM::BAR_OFF;
   const uint32_t x_full = bars + 0, x_empty = bars + 8;
-  const uint32_t y0_full = bars + 16, y0_empty = y0_full + 8 * STAGES;
-  const uint32_t y1_full = y0_empty + 8 * STAGES, y1_empty = y1_full + 8 * STAGES;
-  const uint32_t t_full = y1_empty + 8 * STAGES;   // [2] stage-1 tiles of half a / b ready
+  // the streamed rings are filled and released in half tiles (64 rows): index 2 * slot + half
+  const uint32_t y0_full = bars + 16, y0_empty = y0_full + 16 * STAGES;
+  const uint32_t y1_full = y0_empty + 16 * STAGES, y1_empty = y1_full + 16 * STAGES;
+  const uint32_t t_full = y1_empty + 16 * STAGES;  // [2] stage-1 tiles of half a / b ready
   const uint32_t w_full = t_full + 16;             // [2] 16-bit tiles of half a / b written
   const uint32_t acc_full = w_full + 16;           // [2] accumulator set complete
   const uint32_t acc_empty = acc_full + 16;        // [2] accumulator set stored
@@ -248,12 +252,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + SM::MISC_OFF + 8);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wc{abort_flag, p.status};
+  const uint64_t cta_t0 = p.trace != nullptr ? globaltimer_ns() : 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(x_full, 1);
     mbar_init(x_empty, 1);
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < 2 * STAGES; ++s) {
       mbar_init(y0_full + 8 * s, 1);
       mbar_init(y0_empty + 8 * s, 1);
       mbar_init(y1_full + 8 * s, 1);
@@ -290,6 +295,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
       uint32_t it_cnt = 0, cnt = 0;
       bool ok = true;
+      Tracer tr;
+      tr.init(p.trace, 0, true);
       ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
       int idx = blockIdx.x;
       while (idx < num_items && ok) {
@@ -297,30 +304,38 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int h = idx % p.H;
         TileItem it;
         fill_bwd_item<DKDV>(it, p.g, d);
+        tr.mark(1);
         ok = mbar_wait(wc, x_empty, (it_cnt & 1) ^ 1, 401);
         if (!ok) break;
+        tr.mark(2);
         mbar_arrive_expect_tx(x_full, 2 * SM::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < SM::CHUNKS; ++c) {
           tma_load_2d(sX0 + c * SM::CHUNK_BYTES, mapX0, h * D + c * 64, it.start + it.m0, x_full);
           tma_load_2d(sX1 + c * SM::CHUNK_BYTES, mapX1, h * D + c * 64, it.start + it.m0, x_full);
         }
-        for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
+        for (int j = 0; j < it.n_tiles && ok; ++j, ++cnt) {
           const int s = cnt % STAGES;
           const uint32_t par = ((cnt / STAGES) & 1) ^ 1;
           const int row = it.start + it.tile_at(j) * TILE;
-          ok = mbar_wait(wc, y0_empty + 8 * s, par, 402);
-          if (!ok) break;
-          mbar_arrive_expect_tx(y0_full + 8 * s, SM::TILE_BYTES);
 #pragma unroll
-          for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sY0 + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY0, h * D + c * 64, row, y0_full + 8 * s);
-          ok = mbar_wait(wc, y1_empty + 8 * s, par, 403);
-          if (!ok) break;
-          mbar_arrive_expect_tx(y1_full + 8 * s, SM::TILE_BYTES);
+          for (int hf = 0; hf < 2; ++hf) {
+            const int b = 8 * (2 * s + hf);
+            const uint32_t off = s * SM::TILE_BYTES + hf * HALF * 128;
+            ok = mbar_wait(wc, y0_empty + b, par, 402);
+            if (!ok) break;
+            tr.mark(3);
+            mbar_arrive_expect_tx(y0_full + b, SM::TILE_BYTES / 2);
 #pragma unroll
-          for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sY1 + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row, y1_full + 8 * s);
+            for (int c = 0; c < SM::CHUNKS; ++c)
+              tma_load_2d(sY0 + off + c * SM::CHUNK_BYTES, mapY0, h * D + c * 64, row + hf * HALF, y0_full + b);
+            ok = mbar_wait(wc, y1_empty + b, par, 403);
+            if (!ok) break;
+            mbar_arrive_expect_tx(y1_full + b, SM::TILE_BYTES / 2);
+#pragma unroll
+            for (int c = 0; c < SM::CHUNKS; ++c)
+              tma_load_2d(sY1 + off + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row + hf * HALF, y1_full + b);
+          }
         }
         if (!ok) break;
         ItemDesc nd = d;
@@ -341,9 +356,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const uint64_t x1_desc = make_smem_desc(sX1, 16, 1024);
       uint32_t it_cnt = 0, cnt = 0;
       bool ok = true;
+      Tracer tr;
+      tr.init(p.trace, 1, lane == 0);
 
-      // stage 1 of half hf for the streamed tile in ring slot s: T0_hf = X0 Y0_hf^T, T1_hf = X1 Y1_hf^T
-      auto stage1 = [&](int hf, int s) {
+      // stage 1 of half hf of streamed tile number `tile_no` (ring slot tile_no % STAGES):
+      // T0_hf = X0 Y0_hf^T, T1_hf = X1 Y1_hf^T
+      auto stage1 = [&](int hf, uint32_t tile_no) -> bool {
+        const int s = tile_no % STAGES;
+        const uint32_t par = (tile_no / STAGES) & 1;
+        const int b = 8 * (2 * s + hf);
+        if (!mbar_wait(wc, y0_full + b, par, 502)) return false;
+        if (!mbar_wait(wc, y1_full + b, par, 503)) return false;
+        tc_fence_after();
         const uint64_t y0_desc = make_smem_desc(sY0 + s * SM::TILE_BYTES + hf * HALF * 128, 16, 1024);
         const uint64_t y1_desc = make_smem_desc(sY1 + s * SM::TILE_BYTES + hf * HALF * 128, 16, 1024);
         if (elect_one()) {
@@ -359,8 +383,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                    ks > 0);
           }
           tc_commit(t_full + 8 * hf);
+          // q-stationary launch: stage 2 does not read V again, its half can be refilled already
+          if (!DKDV) tc_commit(y1_empty + b);
         }
         __syncwarp();
+        return true;
       };
       // the stationary tiles have no reader left once the item's last stage 1 has been issued
       auto release_x = [&]() {
@@ -375,20 +402,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         TileItem it;
         fill_bwd_item<DKDV>(it, p.g, d);
         const int n = it.n_tiles;
+        tr.mark(10);
         // accumulator set of this item and how often it has been used before
         const int aset = DKDV ? 0 : (int)(it_cnt & 1);
         const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
         if (!pre_issued) {
           ok = mbar_wait(wc, x_full, it_cnt & 1, 501);
           if (!ok) break;
-          const int s = cnt % STAGES;
-          ok = mbar_wait(wc, y0_full + 8 * s, (cnt / STAGES) & 1, 502);
-          if (!ok) break;
-          ok = mbar_wait(wc, y1_full + 8 * s, (cnt / STAGES) & 1, 503);
-          if (!ok) break;
           tc_fence_after();
-          stage1(0, s);
-          stage1(1, s);
+          ok = stage1(0, cnt) && stage1(1, cnt);
+          if (!ok) break;
           if (n == 1) release_x();
         }
         pre_issued = false;
@@ -397,18 +420,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         bool next_item = false;
         int next_n = 0;
         for (int j = 0; j < n; ++j, ++cnt) {
-          const int s = cnt % STAGES, sn = (cnt + 1) % STAGES;
+          const int s = cnt % STAGES;
           const bool has_next = j + 1 < n;
           if (j == 0) {  // the previous user of this accumulator set must have been stored
             ok = mbar_wait(wc, acc_empty + 8 * aset, (ause & 1) ^ 1, 504);
             if (!ok) break;
           }
-          bool next_ready = false;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
+            tr.mark(12 + hf);
             ok = mbar_wait(wc, w_full + 8 * hf, cnt & 1, 505);
             if (!ok) break;
             tc_fence_after();
+            tr.mark(14 + hf);
             // stage 2: the 64 rows of this half of the streamed tile are the contraction dimension.
             // MN-major B: 64-column blocks 16 KB apart, 16 rows (one MMA) = 2 KB, half b starts 8 KB in.
             const uint64_t y0_mn = make_smem_desc(sY0 + s * SM::TILE_BYTES + hf * HALF * 128, SM::CHUNK_BYTES, 1024);
@@ -431,18 +455,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                          desc_advance(y0_mn, ks * 2048), idesc_2, (acc_on || ks > 0) ? 1u : 0u);
               }
               if (!has_next && hf == 1) tc_commit(acc_full + 8 * aset);
+              // this half of the streamed tile has no readers left
+              tc_commit(y0_empty + 8 * (2 * s + hf));
+              if (DKDV) tc_commit(y1_empty + 8 * (2 * s + hf));
             }
             __syncwarp();
+            tr.mark(16 + hf);
             if (has_next) {
-              if (!next_ready) {
-                ok = mbar_wait(wc, y0_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 506);
-                if (!ok) break;
-                ok = mbar_wait(wc, y1_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 507);
-                if (!ok) break;
-                next_ready = true;
-                tc_fence_after();
-              }
-              stage1(hf, sn);
+              ok = stage1(hf, cnt + 1);
+              if (!ok) break;
+              tr.mark(18 + hf);
               if (hf == 1 && j == n - 2) release_x();
             } else if (hf == 0) {
               // Last tile of the item: the half-a tiles are free from here on.  Fetch the next
@@ -459,25 +481,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 next_item = true;
                 ok = mbar_wait(wc, x_full, (it_cnt + 1) & 1, 508);
                 if (!ok) break;
-                ok = mbar_wait(wc, y0_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 509);
-                if (!ok) break;
-                ok = mbar_wait(wc, y1_full + 8 * sn, ((cnt + 1) / STAGES) & 1, 510);
-                if (!ok) break;
                 tc_fence_after();
-                stage1(0, sn);
+                ok = stage1(0, cnt + 1);
+                if (!ok) break;
+                tr.mark(20);
               }
             } else if (next_item) {
-              stage1(1, sn);
+              ok = stage1(1, cnt + 1);
+              if (!ok) break;
+              tr.mark(21);
               if (next_n == 1) release_x();
               pre_issued = true;
             }
           }
           if (!ok) break;
-          if (elect_one()) {  // the streamed tile of this iteration has no readers left
-            tc_commit(y0_empty + 8 * s);
-            tc_commit(y1_empty + 8 * s);
-          }
-          __syncwarp();
         }
         if (!ok) break;
         d = nd;
@@ -496,6 +513,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     uint32_t cnt = 0, item_no = 0;
     bool ok = true;
+    Tracer tr;
+    tr.init(p.trace, 2, warp == 2 && lane == 0);
     if ((int)blockIdx.x < num_items) {
       ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
       int idx = blockIdx.x;
@@ -523,9 +542,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             const int c0 = o0 + hf * HALF + wg * 32;  // first streamed position of this thread's 32 columns
             const uint32_t tT0 = tmem_base + hf * HALF + lane_off;
             const uint32_t tT1 = tmem_base + 128 + hf * HALF + lane_off;
+            tr.mark(30);
             ok = mbar_wait(wc, t_full + 8 * hf, cnt & 1, 601);
             if (!ok) break;
             tc_fence_after();
+            tr.mark(31);
             if (full) {
               act_half<IS_BF16, DKDV, false>(tT0, tT1, wg, p.half_alpha, 0xffffffffu);
             } else if (!exact_only) {
@@ -534,10 +555,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             } else {
               act_half_exact<IS_BF16, DKDV>(tT0, tT1, wg, p.half_alpha, it.m, own, c0, p.bias, p.bias_numel);
             }
+            tr.mark(37);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(w_full + 8 * hf);
+            tr.mark(33);
           }
         }
         if (!ok) break;
@@ -554,6 +577,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     uint32_t it_cnt = 0;
     bool ok = true;
+    Tracer tr;
+    tr.init(p.trace, 3, warp == 10 && lane == 0);
     const float sc = p.attn_scale ? p.attn_scale[0] : p.inv_n;
     if ((int)blockIdx.x < num_items) {
       ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
@@ -567,9 +592,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const bool rv = own < L;
         const int aset = DKDV ? 0 : (int)(it_cnt & 1);
         const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
+        tr.mark(34);
         ok = mbar_wait(wc, acc_full + 8 * aset, ause & 1, 602);
         if (!ok) break;
         tc_fence_after();
+        tr.mark(35);
         if (DKDV) {
           uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + own) * p.dv_rs + (int64_t)h * p.dv_hs;
           uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + own) * p.dk_rs + (int64_t)h * p.dk_hs;
@@ -582,6 +609,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty + 8 * aset);
+        tr.mark(36);
         if (it.len > L && it.m0 + TILE >= L) {
           if (DKDV) {
             zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, it.start, L, it.len, row_in_tile);
@@ -608,6 +636,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+  // timeline: start and end time of every CTA (second half of the last role's records)
+  if (p.trace != nullptr && threadIdx.x == 0 && blockIdx.x < TRACE_RECORDS / 2)
+    p.trace[3 * TRACE_RECORDS + TRACE_RECORDS / 2 + blockIdx.x] = make_ulonglong2(cta_t0, globaltimer_ns());
 }
 
 }  // namespace
@@ -625,10 +656,17 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
                 (long long)attn_tc_bwd_workspace_bytes(a), (long long)a.workspace_bytes);
   CUtensorMap mq, mk, mv, mdo;
   int rc;
-  if ((rc = make_tile_map(&mq, a.q, a.total_L, (int64_t)a.H * D, a.q_row_stride, 2, IS_BF16)) != 0) return rc;
-  if ((rc = make_tile_map(&mk, a.k, a.total_L, (int64_t)a.H * D, a.k_row_stride, 2, IS_BF16)) != 0) return rc;
-  if ((rc = make_tile_map(&mv, a.v, a.total_L, (int64_t)a.H * D, a.v_row_stride, 2, IS_BF16)) != 0) return rc;
-  if ((rc = make_tile_map(&mdo, a.dout, a.total_L, (int64_t)a.H * D, a.do_row_stride, 2, IS_BF16)) != 0) return rc;
+  // stationary operands are fetched as whole 128-row tiles, streamed ones in 64-row halves
+  CUtensorMap mqh, mkh, mvh, mdoh;
+  const int64_t cols = (int64_t)a.H * D;
+  if ((rc = make_tile_map_rows(&mq, a.q, a.total_L, cols, a.q_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
+  if ((rc = make_tile_map_rows(&mk, a.k, a.total_L, cols, a.k_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
+  if ((rc = make_tile_map_rows(&mv, a.v, a.total_L, cols, a.v_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
+  if ((rc = make_tile_map_rows(&mdo, a.dout, a.total_L, cols, a.do_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
+  if ((rc = make_tile_map_rows(&mqh, a.q, a.total_L, cols, a.q_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
+  if ((rc = make_tile_map_rows(&mkh, a.k, a.total_L, cols, a.k_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
+  if ((rc = make_tile_map_rows(&mvh, a.v, a.total_L, cols, a.v_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
+  if ((rc = make_tile_map_rows(&mdoh, a.dout, a.total_L, cols, a.do_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
   BwdParams p;
   p.g.seq_offsets = a.seq_offsets;
   p.g.num_targets = a.num_targets;
@@ -649,8 +687,15 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.alpha = a.alpha;
   p.inv_n = 1.f / (float)a.max_seq_len;
   p.H = a.H;
+  p.trace = nullptr;
   const int max_items = (int)plan_max_items(a.total_L, a.B);
   const int64_t one = plan_bytes(a.total_L, a.B);
+  // B200_HSTU_TRACE=dkdv|dq and a scratch buffer with TRACE_BYTES of extra room: CTA 0 of that
+  // launch records a timeline of its roles behind the work lists (a profiling aid, off by default)
+  static const char *want_trace = getenv("B200_HSTU_TRACE");
+  ulonglong2 *trace_buf = nullptr;
+  if (want_trace != nullptr && a.workspace_bytes >= 2 * one + TRACE_BYTES)
+    trace_buf = reinterpret_cast<ulonglong2 *>(reinterpret_cast<uint8_t *>(a.workspace) + 2 * one);
   const int64_t upper = (int64_t)max_items * a.H;
   const int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(a.workspace);
@@ -671,8 +716,9 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pk.plan = hdr_kv;
     pk.items = reinterpret_cast<ItemDesc *>(hdr_kv + 1);
     pk.status = &hdr_kv->status;
+    if (trace_buf != nullptr && want_trace[0] == 'd' && want_trace[1] == 'k') pk.trace = trace_buf;
     ProfileScope prof(PROF_ATTN_BWD_DKDV, st);
-    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pk);
+    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mqh, mk, mv, mdoh, pk);
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dk, dv)");
   }
@@ -684,8 +730,9 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pq.plan = hdr_q;
     pq.items = reinterpret_cast<ItemDesc *>(hdr_q + 1);
     pq.status = &hdr_q->status;
+    if (trace_buf != nullptr && want_trace[0] == 'd' && want_trace[1] == 'q') pq.trace = trace_buf;
     ProfileScope prof(PROF_ATTN_BWD_DQ, st);
-    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pq);
+    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mkh, mvh, mdo, pq);
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dq)");
   }

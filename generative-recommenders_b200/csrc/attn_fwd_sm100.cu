@@ -63,21 +63,6 @@ struct FwdParams {
   ulonglong2 *trace;
 };
 
-constexpr int TRACE_RECORDS = 1024;
-constexpr int64_t TRACE_BYTES = 4 * TRACE_RECORDS * (int64_t)sizeof(ulonglong2);
-
-struct Tracer {
-  ulonglong2 *buf;
-  int n;
-  __device__ __forceinline__ void init(ulonglong2 *base, int role, bool on) {
-    buf = (base != nullptr && on && blockIdx.x == 0) ? base + role * TRACE_RECORDS : nullptr;
-    n = 0;
-  }
-  __device__ __forceinline__ void mark(unsigned tag) {
-    if (buf != nullptr && n < TRACE_RECORDS) buf[n++] = make_ulonglong2((unsigned long long)clock64(), tag);
-  }
-};
-
 template <int D>
 struct FwdSmem {
   static constexpr int CHUNKS = D / 64;                 // 64-column (128-byte) TMA boxes per tile

@@ -25,9 +25,9 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D map over a jagged [rows, H*d] tensor of 16-bit elements (or 8-bit with elem_bytes = 1):
-// box = 128 rows x 128 bytes, 128-byte swizzle, zero fill outside.
-int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
-                  int elem_bytes, bool is_bf16) {
+// box = box_rows rows x 128 bytes, 128-byte swizzle, zero fill outside.
+int make_tile_map_rows(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
+                       int elem_bytes, bool is_bf16, int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return fail(B200_HSTU_EDEVICE, "cuTensorMapEncodeTiled is not available from the driver");
   {
@@ -38,7 +38,7 @@ int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, 
   }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)(row_stride_elems * elem_bytes)};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)TILE};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                            : (is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
@@ -46,6 +46,11 @@ int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, 
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B200_HSTU_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return 0;
+}
+
+int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
+                  int elem_bytes, bool is_bf16) {
+  return make_tile_map_rows(m, base, rows, cols, row_stride_elems, elem_bytes, is_bf16, TILE);
 }
 
 int device_sm_count() {

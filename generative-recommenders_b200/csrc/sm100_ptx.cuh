@@ -244,5 +244,23 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return y;
 }
 
+// ------------------------------------------------------------------ timeline (profiling aid)
+// Optional record of {SM clock, tag} pairs written by one thread per role of CTA 0; off (NULL)
+// unless the caller of a launch asks for it and provides the room.
+constexpr int TRACE_RECORDS = 1024;
+constexpr int64_t TRACE_BYTES = 4 * TRACE_RECORDS * (int64_t)sizeof(ulonglong2);
+
+struct Tracer {
+  ulonglong2 *buf;
+  int n;
+  __device__ __forceinline__ void init(ulonglong2 *base, int role, bool on) {
+    buf = (base != nullptr && on && blockIdx.x == 0) ? base + role * TRACE_RECORDS : nullptr;
+    n = 0;
+  }
+  __device__ __forceinline__ void mark(unsigned tag) {
+    if (buf != nullptr && n < TRACE_RECORDS) buf[n++] = make_ulonglong2((unsigned long long)clock64(), tag);
+  }
+};
+
 }  // namespace ptx
 }  // namespace b200hstu
