@@ -21,16 +21,23 @@
 //     between two dQ accumulators, so an item never waits for the previous one to be stored.
 // Fourteen warps, specialised:
 //   warp 0       TMA producer; claims the next item from an atomic counter and publishes it
-//   warp 1       MMA issuer; owns TMEM.  Every streamed tile is processed as two 64-column halves
-//                (a, b) in the order  stage2_a(i), stage1_a(i+1), stage2_b(i), stage1_b(i+1),  so
-//                the tensor pipe works on one half while the CUDA cores activate the other; during
-//                the last tile of an item the stage-1 tiles of the next item are issued instead.
-//                The stationary tiles are released as soon as the item's last stage 1 is issued.
-//   warps 2-9    activation: all eight work on one half at a time, one row of the stationary tile
-//                per thread, 32 of the half's 64 columns per warpgroup
+//   warp 1       MMA issuer; owns TMEM.  Per streamed tile i four 128 x 128 x 128 products:
+//                G1 = X0 Y0^T (scores), G2 = X1 Y1^T (dP), G3 (kv-stationary launch only) and G4
+//                (stage 2), issued in the order  G3(i), G1(i+1), G4(i), G2(i+1):  the tensor pipe
+//                computes the next tile's scores while the CUDA cores turn dP into dS, and the
+//                next dP while they turn scores into P.  During the last tile of an item the
+//                G1 / G2 of the next item's first tile are issued instead.  The stationary tiles
+//                are released as soon as the item's last G2 is issued.
+//   warps 2-9    activation, one row of the stationary tile per thread, 64 of the 128 columns per
+//                warpgroup.  Phase A: scores -> P (16-bit, written over the scores) and silu',
+//                which stays in registers as packed halves; phase B: dP -> dS = dP silu' (16-bit,
+//                written over dP).  Every thread writes only over columns it has read itself
+//                (warpgroup 0: columns [0,32), warpgroup 1: [64,96) of the 128-column region), so no
+//                barrier between the warps is needed; stage 2 takes its K steps from those two
+//                column ranges.
 //   warps 10-13  epilogue: accumulators (fp32, TMEM) -> scale -> 16-bit -> global
-// TMEM: 4 x 64 columns of stage-1 tiles + two 128-column accumulators.  Constant factors are
-// folded into the epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
+// TMEM: scores / P [0,128), dP / dS [128,256), two 128-column accumulators.  Constant factors
+// are folded into the epilogues: dV * scale, dK * scale*alpha, dQ * scale*alpha.
 #include <stdlib.h>
 
 #include "attn_plan.cuh"
@@ -47,7 +54,8 @@ int device_sm_count();
 namespace {
 
 constexpr int BWD_THREADS = 448;
-constexpr int STAGES = 2;
+constexpr int Y0_STAGES = 3;  // streamed operand read by G1 and by G4 (Q | K): longest lifetime
+constexpr int Y1_STAGES = 2;  // streamed operand read by G2 (and G3): dO | V
 constexpr int BWD_SCHED_CONSUMERS = 13;  // MMA warp, 8 activation warps, 4 epilogue warps: one arrival each
 
 struct BwdParams {
@@ -73,8 +81,8 @@ struct BwdSmem {
   static constexpr int A_OFF = 0;                                 // stationary tile 0 (K or Q)
   static constexpr int B_OFF = A_OFF + TILE_BYTES;                // stationary tile 1 (V or dO)
   static constexpr int X_OFF = B_OFF + TILE_BYTES;                // streamed ring 0 (Q or K)
-  static constexpr int Y_OFF = X_OFF + STAGES * TILE_BYTES;       // streamed ring 1 (dO or V)
-  static constexpr int BAR_OFF = Y_OFF + STAGES * TILE_BYTES;
+  static constexpr int Y_OFF = X_OFF + Y0_STAGES * TILE_BYTES;    // streamed ring 1 (dO or V)
+  static constexpr int BAR_OFF = Y_OFF + Y1_STAGES * TILE_BYTES;
   static constexpr int NUM_BARS = 40;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
   static constexpr int SCHED_OFF = MISC_OFF + 64;
@@ -101,59 +109,53 @@ __device__ __forceinline__ void silu_and_grad(float h, float &silu, float &dsilu
   dsilu = fmaf(silu, om, sg);
 }
 
-constexpr int HALF = 64;  // streamed-tile columns processed at a time
+// silu' of a pair, kept between the two activation phases as packed fp16 (values in [-0.1, 1.1])
+__device__ __forceinline__ uint32_t pack_keep(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+__device__ __forceinline__ float2 unpack_keep(uint32_t u) {
+  return __half22float2(*reinterpret_cast<__half2 *>(&u));
+}
 
-// One half of a streamed tile, 32 columns per thread: scores and dP from TMEM, P (kv-stationary
-// launch only) and dS back over them as 16-bit tiles.  `bits` marks the visible columns; with
+// Phase A on 32 score columns of one thread: P (kv-stationary launch) written over the scores,
+// silu' (zero where masked) returned in `keep`.  `bits` marks the visible columns; with
 // MASKED = false all of them are.
 template <bool IS_BF16, bool DKDV, bool MASKED>
-__device__ __forceinline__ void act_half(uint32_t tT0, uint32_t tT1, int wg, float half_alpha, uint32_t bits) {
-  uint32_t rs[32], rp[32];
-  tmem_ld32(tT0 + wg * 32, rs);
-  tmem_ld32(tT1 + wg * 32, rp);
+__device__ __forceinline__ void phase_a_chunk(uint32_t t_in, uint32_t t_out, float half_alpha, uint32_t bits,
+                                              uint32_t (&keep)[16]) {
+  uint32_t rs[32];
+  tmem_ld32(t_in, rs);
   tc_wait_ld();
-  // the 16-bit tiles are written over the first 32 columns of T0 / T1: every warp must hold its
-  // scores in registers before anyone stores
-  asm volatile("bar.sync 1, 256;" ::: "memory");
-  uint32_t pk[16], dk[16];
+  uint32_t pk[16];
 #pragma unroll
   for (int x = 0; x < 16; ++x) {
     float sl0, dsl0, sl1, dsl1;
     silu_and_grad(__uint_as_float(rs[2 * x]) * half_alpha, sl0, dsl0);
     silu_and_grad(__uint_as_float(rs[2 * x + 1]) * half_alpha, sl1, dsl1);
-    float ds0 = __uint_as_float(rp[2 * x]) * dsl0, ds1 = __uint_as_float(rp[2 * x + 1]) * dsl1;
     if (MASKED) {
       const bool v0 = bits & (1u << (2 * x)), v1 = bits & (1u << (2 * x + 1));
       sl0 = v0 ? sl0 : 0.f;
       sl1 = v1 ? sl1 : 0.f;
-      ds0 = v0 ? ds0 : 0.f;
-      ds1 = v1 ? ds1 : 0.f;
+      dsl0 = v0 ? dsl0 : 0.f;
+      dsl1 = v1 ? dsl1 : 0.f;
     }
     if (DKDV) pk[x] = pack2h(sl0, sl1, IS_BF16);
-    dk[x] = pack2h(ds0, ds1, IS_BF16);
+    keep[x] = pack_keep(dsl0, dsl1);
   }
-  if (DKDV) tmem_st16(tT0 + wg * 16, pk);
-  tmem_st16(tT1 + wg * 16, dk);
+  if (DKDV) tmem_st16(t_out, pk);
 }
 
-// The partially visible and the element-wise variants stay out of line: the loop over fully
-// visible tiles is the hot one and should stay small.
+// Phase A, element-wise variant (sequences outside the regular domain, or a relative bias)
 template <bool IS_BF16, bool DKDV>
-__device__ __noinline__ void act_half_masked(uint32_t tT0, uint32_t tT1, int wg, float half_alpha, uint32_t bits) {
-  act_half<IS_BF16, DKDV, true>(tT0, tT1, wg, half_alpha, bits);
-}
-
-template <bool IS_BF16, bool DKDV>
-__device__ __noinline__ void act_half_exact(uint32_t tT0, uint32_t tT1, int wg, float half_alpha, SeqMask m, int own,
-                                            int c0, const float *bias, int bias_numel) {
-  uint32_t rs[32], rp[32];
-  tmem_ld32(tT0 + wg * 32, rs);
-  tmem_ld32(tT1 + wg * 32, rp);
-  tc_wait_ld();
-  asm volatile("bar.sync 1, 256;" ::: "memory");
+__device__ __forceinline__ void phase_a_exact_chunk(uint32_t t_in, uint32_t t_out, float half_alpha, const SeqMask &m,
+                                                    int own, int id_own, int c0, const float *bias, int bias_numel,
+                                                    uint32_t (&keep)[16]) {
   const int L = m.L;
-  const int id_own = m.id(own);
-  uint32_t pk[16], dk[16];
+  uint32_t rs[32];
+  tmem_ld32(t_in, rs);
+  tc_wait_ld();
+  uint32_t pk[16];
 #pragma unroll
   for (int x = 0; x < 32; x += 2) {
     float pv[2], dv[2];
@@ -168,17 +170,90 @@ __device__ __noinline__ void act_half_exact(uint32_t tT0, uint32_t tT1, int wg, 
       }
       float sl, dsl;
       silu_and_grad(hh, sl, dsl);
-      float ds = __uint_as_float(rp[x + y]) * dsl;
       const int id_other = m.id(other);
       bool valid = qi_ < L && kj_ < L && m.valid_ids(qi_, kj_, DKDV ? id_other : id_own, DKDV ? id_own : id_other);
       pv[y] = valid ? sl : 0.f;
-      dv[y] = valid ? ds : 0.f;
+      dv[y] = valid ? dsl : 0.f;
     }
     pk[x / 2] = pack2h(pv[0], pv[1], IS_BF16);
-    dk[x / 2] = pack2h(dv[0], dv[1], IS_BF16);
+    keep[x / 2] = pack_keep(dv[0], dv[1]);
   }
-  if (DKDV) tmem_st16(tT0 + wg * 16, pk);
-  tmem_st16(tT1 + wg * 16, dk);
+  if (DKDV) tmem_st16(t_out, pk);
+}
+
+// Phase B on 32 dP columns of one thread: dS = dP silu' written over dP as a 16-bit tile.
+template <bool IS_BF16>
+__device__ __forceinline__ void phase_b_chunk(uint32_t t_in, uint32_t t_out, const uint32_t (&keep)[16]) {
+  uint32_t rp[32];
+  tmem_ld32(t_in, rp);
+  tc_wait_ld();
+  uint32_t dk[16];
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    const float2 g = unpack_keep(keep[x]);
+    dk[x] = pack2h(__uint_as_float(rp[2 * x]) * g.x, __uint_as_float(rp[2 * x + 1]) * g.y, IS_BF16);
+  }
+  tmem_st16(t_out, dk);
+}
+
+// What the activation warps do for one streamed tile: phase A, hand the score region back, phase
+// B, hand the dP region back.  MODE 0: every element visible; 1: per-row / per-column bit masks;
+// 2: element-wise mask and bias.
+struct ActTile {
+  uint32_t tS, tP;          // this thread's 64 score / dP columns in TMEM
+  uint32_t t_full, w_full;  // barrier pairs
+  uint32_t parity;
+  float half_alpha;
+  int lane;
+};
+
+template <bool IS_BF16, bool DKDV, int MODE>
+__device__ __forceinline__ bool act_tile_body(const WaitCtx &wc, const ActTile &a, uint32_t bits0, uint32_t bits1,
+                                              const SeqMask &m, int own, int c0, const float *bias, int bias_numel,
+                                              Tracer &tr) {
+  uint32_t keep0[16], keep1[16];
+  tr.mark(30);
+  if (!mbar_wait(wc, a.t_full, a.parity, 601)) return false;
+  tc_fence_after();
+  tr.mark(31);
+  if (MODE == 0) {
+    phase_a_chunk<IS_BF16, DKDV, false>(a.tS, a.tS, a.half_alpha, 0xffffffffu, keep0);
+    phase_a_chunk<IS_BF16, DKDV, false>(a.tS + 32, a.tS + 16, a.half_alpha, 0xffffffffu, keep1);
+  } else if (MODE == 1) {
+    phase_a_chunk<IS_BF16, DKDV, true>(a.tS, a.tS, a.half_alpha, bits0, keep0);
+    phase_a_chunk<IS_BF16, DKDV, true>(a.tS + 32, a.tS + 16, a.half_alpha, bits1, keep1);
+  } else {
+    const int id_own = m.id(own);
+    phase_a_exact_chunk<IS_BF16, DKDV>(a.tS, a.tS, a.half_alpha, m, own, id_own, c0, bias, bias_numel, keep0);
+    phase_a_exact_chunk<IS_BF16, DKDV>(a.tS + 32, a.tS + 16, a.half_alpha, m, own, id_own, c0 + 32, bias, bias_numel,
+                                       keep1);
+  }
+  tr.mark(37);
+  if (DKDV) tc_wait_st();
+  tc_fence_before();
+  __syncwarp();
+  if (a.lane == 0) mbar_arrive(a.w_full);
+  tr.mark(33);
+  if (!mbar_wait(wc, a.t_full + 8, a.parity, 603)) return false;
+  tc_fence_after();
+  tr.mark(32);
+  phase_b_chunk<IS_BF16>(a.tP, a.tP, keep0);
+  phase_b_chunk<IS_BF16>(a.tP + 32, a.tP + 16, keep1);
+  tc_wait_st();
+  tc_fence_before();
+  __syncwarp();
+  if (a.lane == 0) mbar_arrive(a.w_full + 8);
+  tr.mark(34);
+  return true;
+}
+
+// The element-wise variant stays out of line: it is several times the size of the interval path.
+template <bool IS_BF16, bool DKDV>
+__device__ __noinline__ bool act_tile_exact(WaitCtx wc, ActTile a, SeqMask m, int own, int c0, const float *bias,
+                                            int bias_numel) {
+  Tracer off;
+  off.init(nullptr, 0, false);
+  return act_tile_body<IS_BF16, DKDV, 2>(wc, a, 0u, 0u, m, own, c0, bias, bias_numel, off);
 }
 
 // Stores one 128 x D fp32 accumulator (TMEM) as scaled 16-bit rows of a jagged tensor.
@@ -237,12 +312,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   const CUtensorMap *mapY0 = DKDV ? &tmap_q : &tmap_k;
   const CUtensorMap *mapY1 = DKDV ? &tmap_do : &tmap_v;
   const uint32_t bars = smem_base + SM::BAR_OFF;
-  const uint32_t x_full = bars + 0, x_empty = bars + 8;
-  // the streamed rings are filled and released in half tiles (64 rows): index 2 * slot + half
-  const uint32_t y0_full = bars + 16, y0_empty = y0_full + 16 * STAGES;
-  const uint32_t y1_full = y0_empty + 16 * STAGES, y1_empty = y1_full + 16 * STAGES;
-  const uint32_t t_full = y1_empty + 16 * STAGES;  // [2] stage-1 tiles of half a / b ready
-  const uint32_t w_full = t_full + 16;             // [2] 16-bit tiles of half a / b written
+  const uint32_t x_full = bars + 0, x_empty = bars + 16;   // [2]: stationary tile 0 (K | Q), tile 1 (V | dO)
+  const uint32_t y0_full = bars + 32, y0_empty = y0_full + 8 * Y0_STAGES;
+  const uint32_t y1_full = y0_empty + 8 * Y0_STAGES, y1_empty = y1_full + 8 * Y1_STAGES;
+  const uint32_t t_full = y1_empty + 8 * Y1_STAGES;  // [2] scores ready, dP ready
+  const uint32_t w_full = t_full + 16;               // [2] P written (scores consumed), dS written
   const uint32_t acc_full = w_full + 16;           // [2] accumulator set complete
   const uint32_t acc_empty = acc_full + 16;        // [2] accumulator set stored
   const uint32_t sched_full = acc_empty + 16;      // [SCHED_SLOTS] next work item published
@@ -256,11 +330,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(x_full, 1);
-    mbar_init(x_empty, 1);
-    for (int s = 0; s < 2 * STAGES; ++s) {
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(x_full + 8 * x, 1);
+      mbar_init(x_empty + 8 * x, 1);
+    }
+    for (int s = 0; s < Y0_STAGES; ++s) {
       mbar_init(y0_full + 8 * s, 1);
       mbar_init(y0_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < Y1_STAGES; ++s) {
       mbar_init(y1_full + 8 * s, 1);
       mbar_init(y1_empty + 8 * s, 1);
     }
@@ -284,8 +362,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: T0_a [0,64) T0_b [64,128) T1_a [128,192) T1_b [192,256) ACC0 [256,384) ACC1 [384,512)
-  //   T0 = S^T | S,  T1 = dP^T | dP;  kv-stationary: ACC0 = dV, ACC1 = dK (one set);
+  // TMEM columns: TS [0,128) scores (S^T | S) then P, TP [128,256) dP (dP^T | dP) then dS,
+  //   ACC0 [256,384), ACC1 [384,512);  kv-stationary: ACC0 = dV, ACC1 = dK (one set);
   //   q-stationary: ACC0 / ACC1 = dQ of even / odd items (two sets)
   const int num_items = p.plan->num_items * p.H;
 
@@ -301,45 +379,49 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       int idx = blockIdx.x;
       while (idx < num_items && ok) {
         const int nidx = atomicAdd(&p.plan->next, 1);
+        ItemDesc nd = d;
+        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
         const int h = idx % p.H;
         TileItem it;
         fill_bwd_item<DKDV>(it, p.g, d);
         tr.mark(1);
-        ok = mbar_wait(wc, x_empty, (it_cnt & 1) ^ 1, 401);
-        if (!ok) break;
-        tr.mark(2);
-        mbar_arrive_expect_tx(x_full, 2 * SM::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < SM::CHUNKS; ++c) {
-          tma_load_2d(sX0 + c * SM::CHUNK_BYTES, mapX0, h * D + c * 64, it.start + it.m0, x_full);
-          tma_load_2d(sX1 + c * SM::CHUNK_BYTES, mapX1, h * D + c * 64, it.start + it.m0, x_full);
-        }
-        for (int j = 0; j < it.n_tiles && ok; ++j, ++cnt) {
-          const int s = cnt % STAGES;
-          const uint32_t par = ((cnt / STAGES) & 1) ^ 1;
+        // order of requests = order of first use: X0, Y0(0) feed G1; X1, Y1(0) feed G2
+        for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
+          const int s0 = cnt % Y0_STAGES, s1 = cnt % Y1_STAGES;
           const int row = it.start + it.tile_at(j) * TILE;
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            const int b = 8 * (2 * s + hf);
-            const uint32_t off = s * SM::TILE_BYTES + hf * HALF * 128;
-            ok = mbar_wait(wc, y0_empty + b, par, 402);
+          if (j == 0) {
+            ok = mbar_wait(wc, x_empty, (it_cnt & 1) ^ 1, 401);
             if (!ok) break;
-            tr.mark(3);
-            mbar_arrive_expect_tx(y0_full + b, SM::TILE_BYTES / 2);
+            tr.mark(2);
+            mbar_arrive_expect_tx(x_full, SM::TILE_BYTES);
 #pragma unroll
             for (int c = 0; c < SM::CHUNKS; ++c)
-              tma_load_2d(sY0 + off + c * SM::CHUNK_BYTES, mapY0, h * D + c * 64, row + hf * HALF, y0_full + b);
-            ok = mbar_wait(wc, y1_empty + b, par, 403);
-            if (!ok) break;
-            mbar_arrive_expect_tx(y1_full + b, SM::TILE_BYTES / 2);
-#pragma unroll
-            for (int c = 0; c < SM::CHUNKS; ++c)
-              tma_load_2d(sY1 + off + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row + hf * HALF, y1_full + b);
+              tma_load_2d(sX0 + c * SM::CHUNK_BYTES, mapX0, h * D + c * 64, it.start + it.m0, x_full);
           }
+          ok = mbar_wait(wc, y0_empty + 8 * s0, ((cnt / Y0_STAGES) & 1) ^ 1, 402);
+          if (!ok) break;
+          tr.mark(3);
+          mbar_arrive_expect_tx(y0_full + 8 * s0, SM::TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < SM::CHUNKS; ++c)
+            tma_load_2d(sY0 + s0 * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY0, h * D + c * 64, row, y0_full + 8 * s0);
+          if (j == 0) {
+            ok = mbar_wait(wc, x_empty + 8, (it_cnt & 1) ^ 1, 404);
+            if (!ok) break;
+            tr.mark(4);
+            mbar_arrive_expect_tx(x_full + 8, SM::TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < SM::CHUNKS; ++c)
+              tma_load_2d(sX1 + c * SM::CHUNK_BYTES, mapX1, h * D + c * 64, it.start + it.m0, x_full + 8);
+          }
+          ok = mbar_wait(wc, y1_empty + 8 * s1, ((cnt / Y1_STAGES) & 1) ^ 1, 403);
+          if (!ok) break;
+          mbar_arrive_expect_tx(y1_full + 8 * s1, SM::TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < SM::CHUNKS; ++c)
+            tma_load_2d(sY1 + s1 * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row, y1_full + 8 * s1);
         }
         if (!ok) break;
-        ItemDesc nd = d;
-        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
         ++it_cnt;
         sched_publish(wc, sched_ring, sched_full, sched_empty, it_cnt, nd.b, nd.t, nd.start, nd.len, nd.nt, nidx, ok);
         d = nd;
@@ -350,7 +432,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     // ------------------------------------------------------------------ MMA issuer (warp-uniform)
     if ((int)blockIdx.x < num_items) {
       constexpr uint32_t FMT = IS_BF16 ? 1u : 0u;
-      const uint32_t idesc_1 = make_idesc(FMT, FMT, 0, 0, TILE, HALF);  // 128 x 64, both operands K-major
+      const uint32_t idesc_1 = make_idesc(FMT, FMT, 0, 0, TILE, TILE);  // 128 x 128, both operands K-major
       const uint32_t idesc_2 = make_idesc(FMT, FMT, 0, 1, TILE, D);     // 128 x D, TMEM A, MN-major B
       const uint64_t x0_desc = make_smem_desc(sX0, 16, 1024);
       const uint64_t x1_desc = make_smem_desc(sX1, 16, 1024);
@@ -359,45 +441,48 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       Tracer tr;
       tr.init(p.trace, 1, lane == 0);
 
-      // stage 1 of half hf of streamed tile number `tile_no` (ring slot tile_no % STAGES):
-      // T0_hf = X0 Y0_hf^T, T1_hf = X1 Y1_hf^T
-      auto stage1 = [&](int hf, uint32_t tile_no) -> bool {
-        const int s = tile_no % STAGES;
-        const uint32_t par = (tile_no / STAGES) & 1;
-        const int b = 8 * (2 * s + hf);
-        if (!mbar_wait(wc, y0_full + b, par, 502)) return false;
-        if (!mbar_wait(wc, y1_full + b, par, 503)) return false;
+      // G1 / G2 of streamed tile number `tile_no`: TS = X0 Y0^T (which = 0), TP = X1 Y1^T (which = 1)
+      // `first_of` >= 0: first tile of item number first_of, whose stationary tile has to have arrived;
+      // `last`: last tile of its item, after which the stationary tile has no reader left
+      auto stage1 = [&](int which, uint32_t tile_no, int first_of, bool last) -> bool {
+        if (first_of >= 0 && !mbar_wait(wc, x_full + 8 * which, first_of & 1, 501 + 10 * which)) return false;
+        const int stages = which == 0 ? Y0_STAGES : Y1_STAGES;
+        const int s = tile_no % stages;
+        const uint32_t par = (tile_no / stages) & 1;
+        if (!mbar_wait(wc, (which == 0 ? y0_full : y1_full) + 8 * s, par, 502 + which)) return false;
         tc_fence_after();
-        const uint64_t y0_desc = make_smem_desc(sY0 + s * SM::TILE_BYTES + hf * HALF * 128, 16, 1024);
-        const uint64_t y1_desc = make_smem_desc(sY1 + s * SM::TILE_BYTES + hf * HALF * 128, 16, 1024);
+        const uint64_t x_desc = which == 0 ? x0_desc : x1_desc;
+        const uint64_t y_desc = make_smem_desc((which == 0 ? sY0 : sY1) + s * SM::TILE_BYTES, 16, 1024);
         if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
-            mma_ss(tmem_base + hf * HALF, desc_advance(x0_desc, off), desc_advance(y0_desc, off), idesc_1, ks > 0);
+            mma_ss(tmem_base + which * 128, desc_advance(x_desc, off), desc_advance(y_desc, off), idesc_1, ks > 0);
           }
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
-            mma_ss(tmem_base + 128 + hf * HALF, desc_advance(x1_desc, off), desc_advance(y1_desc, off), idesc_1,
-                   ks > 0);
-          }
-          tc_commit(t_full + 8 * hf);
-          // q-stationary launch: stage 2 does not read V again, its half can be refilled already
-          if (!DKDV) tc_commit(y1_empty + b);
+          tc_commit(t_full + 8 * which);
+          // q-stationary launch: stage 2 does not read V again, its slot can be refilled already
+          if (!DKDV && which == 1) tc_commit(y1_empty + 8 * s);
+          if (last) tc_commit(x_empty + 8 * which);
         }
         __syncwarp();
         return true;
       };
-      // the stationary tiles have no reader left once the item's last stage 1 has been issued
-      auto release_x = [&]() {
-        if (elect_one()) tc_commit(x_empty);
+      // stage 2 product with the 16-bit tile in TMEM region `src` (0 = P over the scores, 1 = dS over
+      // dP) as A operand: K steps 0-3 sit in columns [0,32), 4-7 in [64,96) of the region.  B is the
+      // streamed tile as MN-major operand: 64-column blocks 16 KB apart, 16 rows (one K step) = 2 KB.
+      auto stage2 = [&](int src, uint32_t acc_col, uint32_t y_smem, uint32_t acc_on) {
+        const uint64_t y_mn = make_smem_desc(y_smem, SM::CHUNK_BYTES, 1024);
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < TILE / 16; ++ks)
+            mma_ts(tmem_base + acc_col, tmem_base + src * 128 + (ks / 4) * 64 + (ks % 4) * 8,
+                   desc_advance(y_mn, ks * 2048), idesc_2, (acc_on || ks > 0) ? 1u : 0u);
+        }
         __syncwarp();
       };
-
       ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
       int idx = blockIdx.x;
-      bool pre_issued = false;  // stage 1 of this item's first tile was issued while the previous item finished
+      bool pre_issued = false;  // G1 / G2 of this item's first tile were issued while the previous item finished
       for (; idx < num_items && ok; ++it_cnt) {
         TileItem it;
         fill_bwd_item<DKDV>(it, p.g, d);
@@ -407,12 +492,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int aset = DKDV ? 0 : (int)(it_cnt & 1);
         const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
         if (!pre_issued) {
-          ok = mbar_wait(wc, x_full, it_cnt & 1, 501);
+          ok = stage1(0, cnt, (int)it_cnt, n == 1) && stage1(1, cnt, (int)it_cnt, n == 1);
           if (!ok) break;
-          tc_fence_after();
-          ok = stage1(0, cnt) && stage1(1, cnt);
-          if (!ok) break;
-          if (n == 1) release_x();
         }
         pre_issued = false;
         ItemDesc nd = d;
@@ -420,81 +501,70 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         bool next_item = false;
         int next_n = 0;
         for (int j = 0; j < n; ++j, ++cnt) {
-          const int s = cnt % STAGES;
+          const int s0 = cnt % Y0_STAGES, s1 = cnt % Y1_STAGES;
           const bool has_next = j + 1 < n;
+          const uint32_t acc_on = j > 0 ? 1u : 0u;
           if (j == 0) {  // the previous user of this accumulator set must have been stored
             ok = mbar_wait(wc, acc_empty + 8 * aset, (ause & 1) ^ 1, 504);
             if (!ok) break;
           }
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            tr.mark(12 + hf);
-            ok = mbar_wait(wc, w_full + 8 * hf, cnt & 1, 505);
-            if (!ok) break;
-            tc_fence_after();
-            tr.mark(14 + hf);
-            // stage 2: the 64 rows of this half of the streamed tile are the contraction dimension.
-            // MN-major B: 64-column blocks 16 KB apart, 16 rows (one MMA) = 2 KB, half b starts 8 KB in.
-            const uint64_t y0_mn = make_smem_desc(sY0 + s * SM::TILE_BYTES + hf * HALF * 128, SM::CHUNK_BYTES, 1024);
-            const uint64_t y1_mn = make_smem_desc(sY1 + s * SM::TILE_BYTES + hf * HALF * 128, SM::CHUNK_BYTES, 1024);
-            const uint32_t acc_on = (j > 0 || hf > 0) ? 1u : 0u;
-            if (elect_one()) {
-              if (DKDV) {
-#pragma unroll
-                for (int ks = 0; ks < HALF / 16; ++ks)  // dV += P^T dO
-                  mma_ts(tmem_base + 256, tmem_base + hf * HALF + ks * 8, desc_advance(y1_mn, ks * 2048), idesc_2,
-                         (acc_on || ks > 0) ? 1u : 0u);
-#pragma unroll
-                for (int ks = 0; ks < HALF / 16; ++ks)  // dK += dS^T Q
-                  mma_ts(tmem_base + 384, tmem_base + 128 + hf * HALF + ks * 8, desc_advance(y0_mn, ks * 2048),
-                         idesc_2, (acc_on || ks > 0) ? 1u : 0u);
-              } else {
-#pragma unroll
-                for (int ks = 0; ks < HALF / 16; ++ks)  // dQ += dS K
-                  mma_ts(tmem_base + 256 + aset * 128, tmem_base + 128 + hf * HALF + ks * 8,
-                         desc_advance(y0_mn, ks * 2048), idesc_2, (acc_on || ks > 0) ? 1u : 0u);
-              }
-              if (!has_next && hf == 1) tc_commit(acc_full + 8 * aset);
-              // this half of the streamed tile has no readers left
-              tc_commit(y0_empty + 8 * (2 * s + hf));
-              if (DKDV) tc_commit(y1_empty + 8 * (2 * s + hf));
-            }
+          // ---- scores consumed (P written): G3, then the next scores
+          tr.mark(12);
+          ok = mbar_wait(wc, w_full, cnt & 1, 505);
+          if (!ok) break;
+          tc_fence_after();
+          tr.mark(14);
+          if (DKDV) {
+            stage2(0, 256, sY1 + s1 * SM::TILE_BYTES, acc_on);  // dV += P^T dO
+            if (elect_one()) tc_commit(y1_empty + 8 * s1);      // dO tile has no reader left
             __syncwarp();
-            tr.mark(16 + hf);
-            if (has_next) {
-              ok = stage1(hf, cnt + 1);
+          }
+          tr.mark(16);
+          if (has_next) {
+            ok = stage1(0, cnt + 1, -1, j == n - 2);
+            if (!ok) break;
+            tr.mark(18);
+          } else {
+            // Last tile of the item: the score region is free from here on.  Fetch the next item
+            // and issue G1 of its first tile now and G2 after this item's last G4; its stationary
+            // tiles were requested when this item's last G2 was issued.
+            ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, nd.b, nd.t, nd.start, nd.len, nd.nt,
+                             nidx, lane == 0);
+            if (!ok) break;
+            if (nidx < num_items) {
+              TileItem ni;
+              fill_bwd_item<DKDV>(ni, p.g, nd);
+              next_n = ni.n_tiles;
+              next_item = true;
+              ok = stage1(0, cnt + 1, (int)it_cnt + 1, next_n == 1);
               if (!ok) break;
-              tr.mark(18 + hf);
-              if (hf == 1 && j == n - 2) release_x();
-            } else if (hf == 0) {
-              // Last tile of the item: the half-a tiles are free from here on.  Fetch the next
-              // item and issue stage 1 of its first tile, half a now and half b after this
-              // item's last stage 2; its stationary tiles were requested when this item's last
-              // stage 1 was issued, its first streamed tile goes to the other ring slot.
-              ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, nd.b, nd.t, nd.start, nd.len,
-                               nd.nt, nidx, lane == 0);
-              if (!ok) break;
-              if (nidx < num_items) {
-                TileItem ni;
-                fill_bwd_item<DKDV>(ni, p.g, nd);
-                next_n = ni.n_tiles;
-                next_item = true;
-                ok = mbar_wait(wc, x_full, (it_cnt + 1) & 1, 508);
-                if (!ok) break;
-                tc_fence_after();
-                ok = stage1(0, cnt + 1);
-                if (!ok) break;
-                tr.mark(20);
-              }
-            } else if (next_item) {
-              ok = stage1(1, cnt + 1);
-              if (!ok) break;
-              tr.mark(21);
-              if (next_n == 1) release_x();
-              pre_issued = true;
+              tr.mark(20);
             }
           }
+          // ---- dS written: G4, then the next dP
+          tr.mark(13);
+          ok = mbar_wait(wc, w_full + 8, cnt & 1, 506);
           if (!ok) break;
+          tc_fence_after();
+          tr.mark(15);
+          if (DKDV) stage2(1, 384, sY0 + s0 * SM::TILE_BYTES, acc_on);               // dK += dS^T Q
+          else stage2(1, 256 + aset * 128, sY0 + s0 * SM::TILE_BYTES, acc_on);       // dQ += dS K
+          if (elect_one()) {
+            if (!has_next) tc_commit(acc_full + 8 * aset);
+            tc_commit(y0_empty + 8 * s0);  // Q | K tile has no reader left
+          }
+          __syncwarp();
+          tr.mark(17);
+          if (has_next) {
+            ok = stage1(1, cnt + 1, -1, j == n - 2);
+            if (!ok) break;
+            tr.mark(19);
+          } else if (next_item) {
+            ok = stage1(1, cnt + 1, (int)it_cnt + 1, next_n == 1);
+            if (!ok) break;
+            tr.mark(21);
+            pre_issued = true;
+          }
         }
         if (!ok) break;
         d = nd;
@@ -503,14 +573,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     }
   } else if (warp < 10) {
     // ------------------------------------------------------------------ activation warps
-    // All eight warps work on one half of the streamed tile at a time (a, then b): the half is
-    // finished - and handed back to the tensor pipe - soonest when every warp works on it.
-    // Warps 2-5 take columns [0,32) of the half, warps 6-9 columns [32,64); thread = one row of
-    // the stationary tile.
+    // thread = one row of the stationary tile; warps 2-5 take columns [0,64) of the streamed tile,
+    // warps 6-9 columns [64,128), each in two chunks of 32
     const int wg = warp >= 6 ? 1 : 0;
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;  // stationary-tile row owned by this thread
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const uint32_t tS = tmem_base + lane_off + wg * 64;        // this thread's score columns; P goes over them
+    const uint32_t tP = tmem_base + 128 + lane_off + wg * 64;  // this thread's dP columns; dS goes over them
     uint32_t cnt = 0, item_no = 0;
     bool ok = true;
     Tracer tr;
@@ -537,30 +607,23 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           } else {
             full = !exact_only && tile_pair_is_full(it, o0);
           }
-#pragma unroll 1
-          for (int hf = 0; hf < 2; ++hf) {
-            const int c0 = o0 + hf * HALF + wg * 32;  // first streamed position of this thread's 32 columns
-            const uint32_t tT0 = tmem_base + hf * HALF + lane_off;
-            const uint32_t tT1 = tmem_base + 128 + hf * HALF + lane_off;
-            tr.mark(30);
-            ok = mbar_wait(wc, t_full + 8 * hf, cnt & 1, 601);
-            if (!ok) break;
-            tc_fence_after();
-            tr.mark(31);
-            if (full) {
-              act_half<IS_BF16, DKDV, false>(tT0, tT1, wg, p.half_alpha, 0xffffffffu);
-            } else if (!exact_only) {
-              const uint32_t bits = DKDV ? col_mask_bits(ci, c0, L) : row_mask_bits(ri, c0, L);
-              act_half_masked<IS_BF16, DKDV>(tT0, tT1, wg, p.half_alpha, bits);
-            } else {
-              act_half_exact<IS_BF16, DKDV>(tT0, tT1, wg, p.half_alpha, it.m, own, c0, p.bias, p.bias_numel);
-            }
-            tr.mark(37);
-            tc_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(w_full + 8 * hf);
-            tr.mark(33);
+          const int c0 = o0 + wg * 64;  // first streamed position of this thread's 64 columns
+          ActTile at;
+          at.tS = tS;
+          at.tP = tP;
+          at.t_full = t_full;
+          at.w_full = w_full;
+          at.parity = cnt & 1;
+          at.half_alpha = p.half_alpha;
+          at.lane = lane;
+          if (!exact_only) {
+            // one code path for fully and partially visible tiles: the tensor pipe, not the
+            // activation, bounds this kernel, and code that runs once per item is slow to fetch
+            const uint32_t b0 = full ? 0xffffffffu : (DKDV ? col_mask_bits(ci, c0, L) : row_mask_bits(ri, c0, L));
+            const uint32_t b1 = full ? 0xffffffffu : (DKDV ? col_mask_bits(ci, c0 + 32, L) : row_mask_bits(ri, c0 + 32, L));
+            ok = act_tile_body<IS_BF16, DKDV, 1>(wc, at, b0, b1, it.m, own, c0, nullptr, 0, tr);
+          } else {
+            ok = act_tile_exact<IS_BF16, DKDV>(wc, at, it.m, own, c0, p.bias, p.bias_numel);
           }
         }
         if (!ok) break;
@@ -592,11 +655,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const bool rv = own < L;
         const int aset = DKDV ? 0 : (int)(it_cnt & 1);
         const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
-        tr.mark(34);
+        tr.mark(40);
         ok = mbar_wait(wc, acc_full + 8 * aset, ause & 1, 602);
         if (!ok) break;
         tc_fence_after();
-        tr.mark(35);
+        tr.mark(41);
         if (DKDV) {
           uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + own) * p.dv_rs + (int64_t)h * p.dv_hs;
           uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + own) * p.dk_rs + (int64_t)h * p.dk_hs;
@@ -609,7 +672,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty + 8 * aset);
-        tr.mark(36);
+        tr.mark(42);
         if (it.len > L && it.m0 + TILE >= L) {
           if (DKDV) {
             zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, it.start, L, it.len, row_in_tile);
@@ -656,17 +719,11 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
                 (long long)attn_tc_bwd_workspace_bytes(a), (long long)a.workspace_bytes);
   CUtensorMap mq, mk, mv, mdo;
   int rc;
-  // stationary operands are fetched as whole 128-row tiles, streamed ones in 64-row halves
-  CUtensorMap mqh, mkh, mvh, mdoh;
   const int64_t cols = (int64_t)a.H * D;
   if ((rc = make_tile_map_rows(&mq, a.q, a.total_L, cols, a.q_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
   if ((rc = make_tile_map_rows(&mk, a.k, a.total_L, cols, a.k_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
   if ((rc = make_tile_map_rows(&mv, a.v, a.total_L, cols, a.v_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
   if ((rc = make_tile_map_rows(&mdo, a.dout, a.total_L, cols, a.do_row_stride, 2, IS_BF16, TILE)) != 0) return rc;
-  if ((rc = make_tile_map_rows(&mqh, a.q, a.total_L, cols, a.q_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
-  if ((rc = make_tile_map_rows(&mkh, a.k, a.total_L, cols, a.k_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
-  if ((rc = make_tile_map_rows(&mvh, a.v, a.total_L, cols, a.v_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
-  if ((rc = make_tile_map_rows(&mdoh, a.dout, a.total_L, cols, a.do_row_stride, 2, IS_BF16, HALF)) != 0) return rc;
   BwdParams p;
   p.g.seq_offsets = a.seq_offsets;
   p.g.num_targets = a.num_targets;
@@ -718,7 +775,7 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pk.status = &hdr_kv->status;
     if (trace_buf != nullptr && want_trace[0] == 'd' && want_trace[1] == 'k') pk.trace = trace_buf;
     ProfileScope prof(PROF_ATTN_BWD_DKDV, st);
-    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mqh, mk, mv, mdoh, pk);
+    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pk);
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dk, dv)");
   }
@@ -732,7 +789,7 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pq.status = &hdr_q->status;
     if (trace_buf != nullptr && want_trace[0] == 'd' && want_trace[1] == 'q') pq.trace = trace_buf;
     ProfileScope prof(PROF_ATTN_BWD_DQ, st);
-    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mkh, mvh, mdo, pq);
+    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pq);
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dq)");
   }
