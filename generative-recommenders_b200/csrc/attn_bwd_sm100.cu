@@ -70,6 +70,7 @@ struct BwdParams {
   int bias_numel;
   float half_alpha, alpha, inv_n;
   int H;
+  int wide_stores;  // dq / dk / dv rows are 32-byte aligned
   ulonglong2 *trace;  // optional timeline of CTA 0 (see Tracer); NULL = off
 };
 
@@ -86,7 +87,7 @@ struct BwdSmem {
   static constexpr int NUM_BARS = 40;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
   static constexpr int SCHED_OFF = MISC_OFF + 64;
-  static constexpr int TOTAL = SCHED_OFF + SCHED_SLOTS * SCHED_SLOT_BYTES;
+  static constexpr int TOTAL = SCHED_OFF + 4 * 64;   // ring of work items (GEOM_SLOTS x GEOM_SLOT_BYTES)
   static constexpr int DYN_BYTES = (TOTAL + 1024) > 116 * 1024 ? (TOTAL + 1024) : 116 * 1024;
 };
 
@@ -256,9 +257,12 @@ __device__ __noinline__ bool act_tile_exact(WaitCtx wc, ActTile a, SeqMask m, in
   return act_tile_body<IS_BF16, DKDV, 2>(wc, a, 0u, 0u, m, own, c0, bias, bias_numel, off);
 }
 
-// Stores one 128 x D fp32 accumulator (TMEM) as scaled 16-bit rows of a jagged tensor.
+// Stores one 128 x D fp32 accumulator (TMEM) as scaled 16-bit rows of a jagged tensor.  One row
+// per thread, so every lane of a store hits another 32-byte sector: `wide` (row pointers 32-byte
+// aligned) writes whole sectors with 256-bit stores, half as many instructions.
 template <int D, bool IS_BF16>
-__device__ __forceinline__ void store_acc_rows(uint32_t tacc, float scale, uint16_t *row_ptr, bool row_valid) {
+__device__ __forceinline__ void store_acc_rows(uint32_t tacc, float scale, uint16_t *row_ptr, bool row_valid,
+                                               bool wide) {
   uint32_t r[2][32];
   tmem_ld32(tacc, r[0]);
 #pragma unroll
@@ -267,14 +271,20 @@ __device__ __forceinline__ void store_acc_rows(uint32_t tacc, float scale, uint1
     if (c + 1 < D / 32) tmem_ld32(tacc + (c + 1) * 32, r[(c + 1) & 1]);
     if (row_valid) {
       const uint32_t(&v)[32] = r[c & 1];
+      uint4 o4[4];
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
-        uint4 o4;
-        o4.x = pack2h(__uint_as_float(v[8 * x + 0]) * scale, __uint_as_float(v[8 * x + 1]) * scale, IS_BF16);
-        o4.y = pack2h(__uint_as_float(v[8 * x + 2]) * scale, __uint_as_float(v[8 * x + 3]) * scale, IS_BF16);
-        o4.z = pack2h(__uint_as_float(v[8 * x + 4]) * scale, __uint_as_float(v[8 * x + 5]) * scale, IS_BF16);
-        o4.w = pack2h(__uint_as_float(v[8 * x + 6]) * scale, __uint_as_float(v[8 * x + 7]) * scale, IS_BF16);
-        *reinterpret_cast<uint4 *>(row_ptr + c * 32 + x * 8) = o4;
+        o4[x].x = pack2h(__uint_as_float(v[8 * x + 0]) * scale, __uint_as_float(v[8 * x + 1]) * scale, IS_BF16);
+        o4[x].y = pack2h(__uint_as_float(v[8 * x + 2]) * scale, __uint_as_float(v[8 * x + 3]) * scale, IS_BF16);
+        o4[x].z = pack2h(__uint_as_float(v[8 * x + 4]) * scale, __uint_as_float(v[8 * x + 5]) * scale, IS_BF16);
+        o4[x].w = pack2h(__uint_as_float(v[8 * x + 6]) * scale, __uint_as_float(v[8 * x + 7]) * scale, IS_BF16);
+      }
+      if (wide) {
+        st_global_256(row_ptr + c * 32, o4[0], o4[1]);
+        st_global_256(row_ptr + c * 32 + 16, o4[2], o4[3]);
+      } else {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) *reinterpret_cast<uint4 *>(row_ptr + c * 32 + x * 8) = o4[x];
       }
     }
   }
@@ -293,6 +303,108 @@ template <bool DKDV>
 __device__ __forceinline__ void fill_bwd_item(TileItem &it, const AttnGeomParams &g, const ItemDesc &d) {
   if (DKDV) fill_kv_item(it, g, d.b, d.t, d.start, d.len, d.nt);
   else fill_q_item(it, g, d.b, d.t, d.start, d.len, d.nt);
+}
+
+// ---------------------------------------------------------------------------------------
+// Work items travel from the producer warp to the other warps as ready-made geometry (64 bytes
+// in a 4-slot shared-memory ring): the tile ranges are worked out once per item, by the warp with
+// the most slack, a whole item ahead of their use.  Code that runs once per item is fetched
+// cold, so the less of it the consumers execute at an item boundary the shorter the boundary.
+// ---------------------------------------------------------------------------------------
+struct __align__(16) ItemGeom {
+  int idx;                   // (item, head) index; >= number of (item, head) pairs: no more work
+  int start, len, nt;        // first token row, untruncated length, number of targets
+  int m0, n_tiles, t_lo, n_main;
+  int extra_tile, L, u, regular;
+  int max_id, pad0, pad1, pad2;
+  __device__ __forceinline__ int tile_at(int j) const { return j < n_main ? t_lo + j : extra_tile; }
+};
+constexpr int GEOM_SLOTS = 4;
+constexpr int GEOM_SLOT_BYTES = 64;
+
+__device__ __forceinline__ void geom_from_item(ItemGeom &g, const TileItem &it, int idx) {
+  g.idx = idx;
+  g.start = it.start; g.len = it.len; g.nt = it.nt;
+  g.m0 = it.m0; g.n_tiles = it.n_tiles; g.t_lo = it.t_lo; g.n_main = it.n_main;
+  g.extra_tile = it.extra_tile; g.L = it.m.L; g.u = it.u; g.regular = it.regular ? 1 : 0;
+  g.max_id = it.m.max_id; g.pad0 = g.pad1 = g.pad2 = 0;
+}
+// the fields the activation and epilogue code reads (no tile ranges are recomputed)
+__device__ __forceinline__ void item_from_geom(TileItem &it, const ItemGeom &g, const AttnGeomParams &gp) {
+  it.b = 0; it.mt = g.m0 / TILE;
+  it.start = g.start; it.len = g.len; it.nt = g.nt;
+  it.m0 = g.m0;
+  it.m.L = g.L; it.m.max_id = g.max_id; it.m.c = gp.c; it.m.W = gp.W; it.m.F = gp.F;
+  it.t_lo = g.t_lo; it.n_main = g.n_main; it.extra_tile = g.extra_tile; it.n_tiles = g.n_tiles;
+  it.u = g.u; it.regular = g.regular != 0;
+}
+// item ordinals n = 0, 1, 2, ... use slot n % 4
+__device__ __forceinline__ bool geom_publish(const WaitCtx &wc, uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                             uint32_t n, const ItemGeom &g) {
+  const uint32_t slot = n & (GEOM_SLOTS - 1);
+  if (!mbar_wait(wc, empty0 + 8 * slot, ((n / GEOM_SLOTS) & 1) ^ 1, 901)) return false;
+  int4 *dst = reinterpret_cast<int4 *>(ring + slot * GEOM_SLOT_BYTES);
+  const int4 *src = reinterpret_cast<const int4 *>(&g);
+  dst[0] = src[0]; dst[1] = src[1]; dst[2] = src[2]; dst[3] = src[3];
+  asm volatile("fence.acq_rel.cta;" ::: "memory");
+  mbar_arrive(full0 + 8 * slot);
+  return true;
+}
+__device__ __forceinline__ bool geom_fetch(const WaitCtx &wc, const uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                           uint32_t n, ItemGeom &g, bool arrive) {
+  const uint32_t slot = n & (GEOM_SLOTS - 1);
+  if (!mbar_wait(wc, full0 + 8 * slot, (n / GEOM_SLOTS) & 1, 902)) return false;
+  const volatile int *src = reinterpret_cast<const volatile int *>(ring + slot * GEOM_SLOT_BYTES);
+  int *dst = reinterpret_cast<int *>(&g);
+#pragma unroll
+  for (int i = 0; i < 13; ++i) dst[i] = src[i];
+  __syncwarp();
+  if (arrive) mbar_arrive(empty0 + 8 * slot);
+  return true;
+}
+
+// The two kinds of tensor-core products of the MMA warp.
+struct Stage1Args {
+  uint32_t x_bar, x_par;   // stationary tile arrival to wait for (x_bar = 0: already waited for)
+  uint32_t y_bar, y_par;   // streamed tile arrival
+  uint64_t x_desc;
+  uint32_t y_smem, d_tmem, idesc;
+  uint32_t commit_t, commit_y, commit_x;  // barriers to signal on completion (0 = none)
+};
+template <int D>
+__device__ __forceinline__ bool bwd_stage1(const WaitCtx &wc, const Stage1Args &a) {
+  if (a.x_bar != 0 && !mbar_wait(wc, a.x_bar, a.x_par, 501)) return false;
+  if (!mbar_wait(wc, a.y_bar, a.y_par, 502)) return false;
+  tc_fence_after();
+  const uint64_t y_desc = make_smem_desc(a.y_smem, 16, 1024);
+  if (elect_one()) {
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint32_t off = (ks / 4) * (TILE * 128) + (ks % 4) * 32;
+      mma_ss(a.d_tmem, desc_advance(a.x_desc, off), desc_advance(y_desc, off), a.idesc, ks > 0);
+    }
+    tc_commit(a.commit_t);
+    if (a.commit_y != 0) tc_commit(a.commit_y);
+    if (a.commit_x != 0) tc_commit(a.commit_x);
+  }
+  __syncwarp();
+  return true;
+}
+// acc += A B with the 16-bit A tile in TMEM (K steps 0-3 in columns [0,32), 4-7 in [64,96) of its
+// 128-column region) and the streamed tile as MN-major B: 64-column blocks 16 KB apart, 16 rows
+// (one K step) = 2 KB.
+__device__ __forceinline__ void bwd_stage2(uint32_t acc_tmem, uint32_t a_tmem, uint32_t y_smem, uint32_t idesc,
+                                        uint32_t acc_on, uint32_t commit0, uint32_t commit1) {
+  const uint64_t y_mn = make_smem_desc(y_smem, TILE * 128, 1024);
+  if (elect_one()) {
+#pragma unroll
+    for (int ks = 0; ks < TILE / 16; ++ks)
+      mma_ts(acc_tmem, a_tmem + (ks / 4) * 64 + (ks % 4) * 8, desc_advance(y_mn, ks * 2048), idesc,
+             (acc_on || ks > 0) ? 1u : 0u);
+    if (commit0 != 0) tc_commit(commit0);
+    if (commit1 != 0) tc_commit(commit1);
+  }
+  __syncwarp();
 }
 
 template <int D, bool IS_BF16, bool DKDV>
@@ -375,20 +487,27 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       bool ok = true;
       Tracer tr;
       tr.init(p.trace, 0, true);
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
-      while (idx < num_items && ok) {
-        const int nidx = atomicAdd(&p.plan->next, 1);
-        ItemDesc nd = d;
-        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
-        const int h = idx % p.H;
+      ItemGeom g;
+      {
         TileItem it;
-        fill_bwd_item<DKDV>(it, p.g, d);
+        fill_bwd_item<DKDV>(it, p.g, load_desc(p.items, blockIdx.x / p.H));
+        geom_from_item(g, it, blockIdx.x);
+      }
+      ok = geom_publish(wc, sched_ring, sched_full, sched_empty, 0, g);
+      while (g.idx < num_items && ok) {
+        // claim the next (item, head) index now; its geometry is published below, right after this
+        // item's first requests, a whole item before the other warps need it
+        const int nidx = atomicAdd(&p.plan->next, 1);
+        ItemDesc nd;
+        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
+        const int h = g.idx % p.H;
+        ItemGeom ng = g;
+        ng.idx = nidx;
         tr.mark(1);
         // order of requests = order of first use: X0, Y0(0) feed G1; X1, Y1(0) feed G2
-        for (int j = 0; j < it.n_tiles; ++j, ++cnt) {
+        for (int j = 0; j < g.n_tiles; ++j, ++cnt) {
           const int s0 = cnt % Y0_STAGES, s1 = cnt % Y1_STAGES;
-          const int row = it.start + it.tile_at(j) * TILE;
+          const int row = g.start + g.tile_at(j) * TILE;
           if (j == 0) {
             ok = mbar_wait(wc, x_empty, (it_cnt & 1) ^ 1, 401);
             if (!ok) break;
@@ -396,7 +515,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             mbar_arrive_expect_tx(x_full, SM::TILE_BYTES);
 #pragma unroll
             for (int c = 0; c < SM::CHUNKS; ++c)
-              tma_load_2d(sX0 + c * SM::CHUNK_BYTES, mapX0, h * D + c * 64, it.start + it.m0, x_full);
+              tma_load_2d(sX0 + c * SM::CHUNK_BYTES, mapX0, h * D + c * 64, g.start + g.m0, x_full);
           }
           ok = mbar_wait(wc, y0_empty + 8 * s0, ((cnt / Y0_STAGES) & 1) ^ 1, 402);
           if (!ok) break;
@@ -412,7 +531,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             mbar_arrive_expect_tx(x_full + 8, SM::TILE_BYTES);
 #pragma unroll
             for (int c = 0; c < SM::CHUNKS; ++c)
-              tma_load_2d(sX1 + c * SM::CHUNK_BYTES, mapX1, h * D + c * 64, it.start + it.m0, x_full + 8);
+              tma_load_2d(sX1 + c * SM::CHUNK_BYTES, mapX1, h * D + c * 64, g.start + g.m0, x_full + 8);
           }
           ok = mbar_wait(wc, y1_empty + 8 * s1, ((cnt / Y1_STAGES) & 1) ^ 1, 403);
           if (!ok) break;
@@ -420,12 +539,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
             tma_load_2d(sY1 + s1 * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row, y1_full + 8 * s1);
+          if (j == 0) {
+            if (nidx < num_items) {
+              TileItem ni;
+              fill_bwd_item<DKDV>(ni, p.g, nd);
+              geom_from_item(ng, ni, nidx);
+            }
+            ok = geom_publish(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng);
+            if (!ok) break;
+          }
         }
         if (!ok) break;
         ++it_cnt;
-        sched_publish(wc, sched_ring, sched_full, sched_empty, it_cnt, nd.b, nd.t, nd.start, nd.len, nd.nt, nidx, ok);
-        d = nd;
-        idx = nidx;
+        g = ng;
       }
     }
   } else if (warp == 1) {
@@ -434,80 +560,55 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       constexpr uint32_t FMT = IS_BF16 ? 1u : 0u;
       const uint32_t idesc_1 = make_idesc(FMT, FMT, 0, 0, TILE, TILE);  // 128 x 128, both operands K-major
       const uint32_t idesc_2 = make_idesc(FMT, FMT, 0, 1, TILE, D);     // 128 x D, TMEM A, MN-major B
-      const uint64_t x0_desc = make_smem_desc(sX0, 16, 1024);
-      const uint64_t x1_desc = make_smem_desc(sX1, 16, 1024);
       uint32_t it_cnt = 0, cnt = 0;
       bool ok = true;
       Tracer tr;
       tr.init(p.trace, 1, lane == 0);
 
-      // G1 / G2 of streamed tile number `tile_no`: TS = X0 Y0^T (which = 0), TP = X1 Y1^T (which = 1)
-      // `first_of` >= 0: first tile of item number first_of, whose stationary tile has to have arrived;
-      // `last`: last tile of its item, after which the stationary tile has no reader left
+      // G1 (which = 0: TS = X0 Y0^T) or G2 (which = 1: TP = X1 Y1^T) of streamed tile number
+      // `tile_no`.  `first_of` >= 0: first tile of item number first_of, whose stationary tile has
+      // to have arrived; `last`: last tile of its item, after which that tile has no reader left.
       auto stage1 = [&](int which, uint32_t tile_no, int first_of, bool last) -> bool {
-        if (first_of >= 0 && !mbar_wait(wc, x_full + 8 * which, first_of & 1, 501 + 10 * which)) return false;
         const int stages = which == 0 ? Y0_STAGES : Y1_STAGES;
         const int s = tile_no % stages;
-        const uint32_t par = (tile_no / stages) & 1;
-        if (!mbar_wait(wc, (which == 0 ? y0_full : y1_full) + 8 * s, par, 502 + which)) return false;
-        tc_fence_after();
-        const uint64_t x_desc = which == 0 ? x0_desc : x1_desc;
-        const uint64_t y_desc = make_smem_desc((which == 0 ? sY0 : sY1) + s * SM::TILE_BYTES, 16, 1024);
-        if (elect_one()) {
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks / 4) * SM::CHUNK_BYTES + (ks % 4) * 32;
-            mma_ss(tmem_base + which * 128, desc_advance(x_desc, off), desc_advance(y_desc, off), idesc_1, ks > 0);
-          }
-          tc_commit(t_full + 8 * which);
-          // q-stationary launch: stage 2 does not read V again, its slot can be refilled already
-          if (!DKDV && which == 1) tc_commit(y1_empty + 8 * s);
-          if (last) tc_commit(x_empty + 8 * which);
-        }
-        __syncwarp();
-        return true;
+        Stage1Args a;
+        a.x_bar = first_of >= 0 ? x_full + 8 * which : 0u;
+        a.x_par = first_of & 1;
+        a.y_bar = (which == 0 ? y0_full : y1_full) + 8 * s;
+        a.y_par = (tile_no / stages) & 1;
+        a.x_desc = make_smem_desc(which == 0 ? sX0 : sX1, 16, 1024);
+        a.y_smem = (which == 0 ? sY0 : sY1) + s * SM::TILE_BYTES;
+        a.d_tmem = tmem_base + which * 128;
+        a.idesc = idesc_1;
+        a.commit_t = t_full + 8 * which;
+        // q-stationary launch: stage 2 does not read V again, its slot can be refilled already
+        a.commit_y = (!DKDV && which == 1) ? y1_empty + 8 * s : 0u;
+        a.commit_x = last ? x_empty + 8 * which : 0u;
+        return bwd_stage1<D>(wc, a);
       };
-      // stage 2 product with the 16-bit tile in TMEM region `src` (0 = P over the scores, 1 = dS over
-      // dP) as A operand: K steps 0-3 sit in columns [0,32), 4-7 in [64,96) of the region.  B is the
-      // streamed tile as MN-major operand: 64-column blocks 16 KB apart, 16 rows (one K step) = 2 KB.
-      auto stage2 = [&](int src, uint32_t acc_col, uint32_t y_smem, uint32_t acc_on) {
-        const uint64_t y_mn = make_smem_desc(y_smem, SM::CHUNK_BYTES, 1024);
-        if (elect_one()) {
-#pragma unroll
-          for (int ks = 0; ks < TILE / 16; ++ks)
-            mma_ts(tmem_base + acc_col, tmem_base + src * 128 + (ks / 4) * 64 + (ks % 4) * 8,
-                   desc_advance(y_mn, ks * 2048), idesc_2, (acc_on || ks > 0) ? 1u : 0u);
-        }
-        __syncwarp();
-      };
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
+
+      ItemGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
       bool pre_issued = false;  // G1 / G2 of this item's first tile were issued while the previous item finished
-      for (; idx < num_items && ok; ++it_cnt) {
-        TileItem it;
-        fill_bwd_item<DKDV>(it, p.g, d);
-        const int n = it.n_tiles;
+      for (; ok && g.idx < num_items; ++it_cnt) {
+        const int n = g.n_tiles;
         tr.mark(10);
-        // accumulator set of this item and how often it has been used before
-        const int aset = DKDV ? 0 : (int)(it_cnt & 1);
+        // accumulator of G4 and how often it has been used before: dK is always ACC1 (dV, from G3,
+        // always ACC0); dQ alternates between the two
+        const int aset = DKDV ? 1 : (int)(it_cnt & 1);
         const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
         if (!pre_issued) {
           ok = stage1(0, cnt, (int)it_cnt, n == 1) && stage1(1, cnt, (int)it_cnt, n == 1);
           if (!ok) break;
         }
         pre_issued = false;
-        ItemDesc nd = d;
-        int nidx = idx;
+        ItemGeom ng;
+        ng.idx = num_items;
         bool next_item = false;
-        int next_n = 0;
         for (int j = 0; j < n; ++j, ++cnt) {
           const int s0 = cnt % Y0_STAGES, s1 = cnt % Y1_STAGES;
           const bool has_next = j + 1 < n;
           const uint32_t acc_on = j > 0 ? 1u : 0u;
-          if (j == 0) {  // the previous user of this accumulator set must have been stored
-            ok = mbar_wait(wc, acc_empty + 8 * aset, (ause & 1) ^ 1, 504);
-            if (!ok) break;
-          }
           // ---- scores consumed (P written): G3, then the next scores
           tr.mark(12);
           ok = mbar_wait(wc, w_full, cnt & 1, 505);
@@ -515,9 +616,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tc_fence_after();
           tr.mark(14);
           if (DKDV) {
-            stage2(0, 256, sY1 + s1 * SM::TILE_BYTES, acc_on);  // dV += P^T dO
-            if (elect_one()) tc_commit(y1_empty + 8 * s1);      // dO tile has no reader left
-            __syncwarp();
+            if (j == 0) {  // dV of the previous item must have been stored
+              ok = mbar_wait(wc, acc_empty, (it_cnt & 1) ^ 1, 504);
+              if (!ok) break;
+            }
+            // dV += P^T dO; afterwards the dO tile has no reader left
+            bwd_stage2(tmem_base + 256, tmem_base, sY1 + s1 * SM::TILE_BYTES, idesc_2, acc_on, y1_empty + 8 * s1,
+                       has_next ? 0u : acc_full);
           }
           tr.mark(16);
           if (has_next) {
@@ -525,18 +630,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             if (!ok) break;
             tr.mark(18);
           } else {
-            // Last tile of the item: the score region is free from here on.  Fetch the next item
+            // Last tile of the item: the score region is free from here on.  Take the next item
             // and issue G1 of its first tile now and G2 after this item's last G4; its stationary
-            // tiles were requested when this item's last G2 was issued.
-            ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, nd.b, nd.t, nd.start, nd.len, nd.nt,
-                             nidx, lane == 0);
+            // tiles were requested as soon as this item's last G1 / G2 had been issued.
+            ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng, lane == 0);
             if (!ok) break;
-            if (nidx < num_items) {
-              TileItem ni;
-              fill_bwd_item<DKDV>(ni, p.g, nd);
-              next_n = ni.n_tiles;
+            if (ng.idx < num_items) {
               next_item = true;
-              ok = stage1(0, cnt + 1, (int)it_cnt + 1, next_n == 1);
+              ok = stage1(0, cnt + 1, (int)it_cnt + 1, ng.n_tiles == 1);
               if (!ok) break;
               tr.mark(20);
             }
@@ -547,28 +648,27 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           if (!ok) break;
           tc_fence_after();
           tr.mark(15);
-          if (DKDV) stage2(1, 384, sY0 + s0 * SM::TILE_BYTES, acc_on);               // dK += dS^T Q
-          else stage2(1, 256 + aset * 128, sY0 + s0 * SM::TILE_BYTES, acc_on);       // dQ += dS K
-          if (elect_one()) {
-            if (!has_next) tc_commit(acc_full + 8 * aset);
-            tc_commit(y0_empty + 8 * s0);  // Q | K tile has no reader left
+          if (j == 0) {  // the previous user of this accumulator (dK | dQ of the item before last) must have been stored
+            ok = mbar_wait(wc, acc_empty + 8 * aset, (ause & 1) ^ 1, 507);
+            if (!ok) break;
           }
-          __syncwarp();
+          // dK += dS^T Q  |  dQ += dS K; afterwards the Q | K tile has no reader left
+          bwd_stage2(tmem_base + 256 + aset * 128, tmem_base + 128, sY0 + s0 * SM::TILE_BYTES, idesc_2, acc_on,
+                     y0_empty + 8 * s0, has_next ? 0u : acc_full + 8 * aset);
           tr.mark(17);
           if (has_next) {
             ok = stage1(1, cnt + 1, -1, j == n - 2);
             if (!ok) break;
             tr.mark(19);
           } else if (next_item) {
-            ok = stage1(1, cnt + 1, (int)it_cnt + 1, next_n == 1);
+            ok = stage1(1, cnt + 1, (int)it_cnt + 1, ng.n_tiles == 1);
             if (!ok) break;
             tr.mark(21);
             pre_issued = true;
           }
         }
         if (!ok) break;
-        d = nd;
-        idx = nidx;
+        g = ng;
       }
     }
   } else if (warp < 10) {
@@ -586,11 +686,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     Tracer tr;
     tr.init(p.trace, 2, warp == 2 && lane == 0);
     if ((int)blockIdx.x < num_items) {
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
-      while (idx < num_items && ok) {
+      ItemGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
+      while (ok && g.idx < num_items) {
         TileItem it;
-        fill_bwd_item<DKDV>(it, p.g, d);
+        item_from_geom(it, g, p.g);
         const int L = it.m.L;
         const int own = it.m0 + row_in_tile;  // kv position (DKDV) or query position
         const bool exact_only = !it.regular || p.bias != nullptr;
@@ -628,8 +728,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         if (!ok) break;
         ++item_no;
-        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, item_no, d.b, d.t, d.start, d.len, d.nt, idx,
-                         lane == 0);
+        ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, item_no, g, lane == 0);
       }
     }
   } else {
@@ -644,46 +743,57 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     tr.init(p.trace, 3, warp == 10 && lane == 0);
     const float sc = p.attn_scale ? p.attn_scale[0] : p.inv_n;
     if ((int)blockIdx.x < num_items) {
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
-      while (idx < num_items && ok) {
-        const int h = idx % p.H;
-        TileItem it;
-        fill_bwd_item<DKDV>(it, p.g, d);
-        const int L = it.m.L;
-        const int own = it.m0 + row_in_tile;
+      ItemGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
+      while (ok && g.idx < num_items) {
+        const int h = g.idx % p.H;
+        const int L = g.L;
+        const int own = g.m0 + row_in_tile;
         const bool rv = own < L;
-        const int aset = DKDV ? 0 : (int)(it_cnt & 1);
-        const uint32_t ause = DKDV ? it_cnt : (it_cnt >> 1);
         tr.mark(40);
-        ok = mbar_wait(wc, acc_full + 8 * aset, ause & 1, 602);
-        if (!ok) break;
-        tc_fence_after();
-        tr.mark(41);
         if (DKDV) {
-          uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(it.start + own) * p.dv_rs + (int64_t)h * p.dv_hs;
-          uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(it.start + own) * p.dk_rs + (int64_t)h * p.dk_hs;
-          store_acc_rows<D, IS_BF16>(tmem_base + 256 + lane_off, sc, dvrow, rv);
-          store_acc_rows<D, IS_BF16>(tmem_base + 384 + lane_off, sc * p.alpha, dkrow, rv);
+          // dV (ACC0) is complete after the item's last G3, dK (ACC1) after its last G4; each is
+          // handed back as soon as it has been stored
+          uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(g.start + own) * p.dv_rs + (int64_t)h * p.dv_hs;
+          uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(g.start + own) * p.dk_rs + (int64_t)h * p.dk_hs;
+          ok = mbar_wait(wc, acc_full, it_cnt & 1, 602);
+          if (!ok) break;
+          tc_fence_after();
+          tr.mark(41);
+          store_acc_rows<D, IS_BF16>(tmem_base + 256 + lane_off, sc, dvrow, rv, p.wide_stores != 0);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty);
+          ok = mbar_wait(wc, acc_full + 8, it_cnt & 1, 603);
+          if (!ok) break;
+          tc_fence_after();
+          store_acc_rows<D, IS_BF16>(tmem_base + 384 + lane_off, sc * p.alpha, dkrow, rv, p.wide_stores != 0);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty + 8);
         } else {
-          uint16_t *dqrow = reinterpret_cast<uint16_t *>(p.dq) + (int64_t)(it.start + own) * p.dq_rs + (int64_t)h * p.dq_hs;
-          store_acc_rows<D, IS_BF16>(tmem_base + 256 + aset * 128 + lane_off, sc * p.alpha, dqrow, rv);
+          const int aset = (int)(it_cnt & 1);
+          uint16_t *dqrow = reinterpret_cast<uint16_t *>(p.dq) + (int64_t)(g.start + own) * p.dq_rs + (int64_t)h * p.dq_hs;
+          ok = mbar_wait(wc, acc_full + 8 * aset, (it_cnt >> 1) & 1, 602);
+          if (!ok) break;
+          tc_fence_after();
+          tr.mark(41);
+          store_acc_rows<D, IS_BF16>(tmem_base + 256 + aset * 128 + lane_off, sc * p.alpha, dqrow, rv, p.wide_stores != 0);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty + 8 * aset);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty + 8 * aset);
         tr.mark(42);
-        if (it.len > L && it.m0 + TILE >= L) {
+        if (g.len > L && g.m0 + TILE >= L) {
           if (DKDV) {
-            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, it.start, L, it.len, row_in_tile);
-            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dv), p.dv_rs, p.dv_hs, h, it.start, L, it.len, row_in_tile);
+            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dk), p.dk_rs, p.dk_hs, h, g.start, L, g.len, row_in_tile);
+            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dv), p.dv_rs, p.dv_hs, h, g.start, L, g.len, row_in_tile);
           } else {
-            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dq), p.dq_rs, p.dq_hs, h, it.start, L, it.len, row_in_tile);
+            zero_rows_beyond<D>(reinterpret_cast<uint16_t *>(p.dq), p.dq_rs, p.dq_hs, h, g.start, L, g.len, row_in_tile);
           }
         }
         ++it_cnt;
-        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt, d.b, d.t, d.start, d.len, d.nt, idx,
-                         lane == 0);
+        ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt, g, lane == 0);
       }
     }
   }
@@ -744,6 +854,13 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.alpha = a.alpha;
   p.inv_n = 1.f / (float)a.max_seq_len;
   p.H = a.H;
+  {
+    auto al32 = [](const void *q, int64_t rs, int64_t hs) {
+      return (reinterpret_cast<uintptr_t>(q) & 31) == 0 && rs % 16 == 0 && hs % 16 == 0;
+    };
+    p.wide_stores = al32(a.dq, a.dq_row_stride, a.dq_head_stride) && al32(a.dk, a.dk_row_stride, a.dk_head_stride) &&
+                    al32(a.dv_, a.dv_row_stride, a.dv_head_stride);
+  }
   p.trace = nullptr;
   const int max_items = (int)plan_max_items(a.total_L, a.B);
   const int64_t one = plan_bytes(a.total_L, a.B);

@@ -59,6 +59,7 @@ struct FwdParams {
   float half_alpha;   // alpha / 2
   float inv_n;        // 1 / max_seq_len
   int H;
+  int wide_stores;    // out rows are 32-byte aligned
   // optional timeline of CTA 0 (4 roles x TRACE_RECORDS records of {SM clock, tag}); NULL = off
   ulonglong2 *trace;
 };
@@ -615,14 +616,22 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             if (cc + 1 < D / 32) tmem_ld32(tO + (cc + 1) * 32, r[(cc + 1) & 1]);
             if (i < L) {
               const uint32_t(&v)[32] = r[cc & 1];
+              uint4 o4[4];
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
-                uint4 o4;
-                o4.x = pack2<IS_BF16>(__uint_as_float(v[8 * x + 0]) * scale, __uint_as_float(v[8 * x + 1]) * scale);
-                o4.y = pack2<IS_BF16>(__uint_as_float(v[8 * x + 2]) * scale, __uint_as_float(v[8 * x + 3]) * scale);
-                o4.z = pack2<IS_BF16>(__uint_as_float(v[8 * x + 4]) * scale, __uint_as_float(v[8 * x + 5]) * scale);
-                o4.w = pack2<IS_BF16>(__uint_as_float(v[8 * x + 6]) * scale, __uint_as_float(v[8 * x + 7]) * scale);
-                *reinterpret_cast<uint4 *>(orow + cc * 32 + x * 8) = o4;
+                o4[x].x = pack2<IS_BF16>(__uint_as_float(v[8 * x + 0]) * scale, __uint_as_float(v[8 * x + 1]) * scale);
+                o4[x].y = pack2<IS_BF16>(__uint_as_float(v[8 * x + 2]) * scale, __uint_as_float(v[8 * x + 3]) * scale);
+                o4[x].z = pack2<IS_BF16>(__uint_as_float(v[8 * x + 4]) * scale, __uint_as_float(v[8 * x + 5]) * scale);
+                o4[x].w = pack2<IS_BF16>(__uint_as_float(v[8 * x + 6]) * scale, __uint_as_float(v[8 * x + 7]) * scale);
+              }
+              // one row per thread: every lane of a store hits another 32-byte sector, so rows
+              // that are 32-byte aligned are written in whole sectors (256-bit stores)
+              if (p.wide_stores) {
+                st_global_256(orow + cc * 32, o4[0], o4[1]);
+                st_global_256(orow + cc * 32 + 16, o4[2], o4[3]);
+              } else {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) *reinterpret_cast<uint4 *>(orow + cc * 32 + x * 8) = o4[x];
               }
             }
           }
@@ -700,6 +709,7 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.half_alpha = 0.5f * a.alpha;
   p.inv_n = 1.f / (float)a.max_seq_len;
   p.H = a.H;
+  p.wide_stores = (reinterpret_cast<uintptr_t>(a.out) & 31) == 0 && a.o_row_stride % 16 == 0 && a.o_head_stride % 16 == 0;
   // B200_HSTU_TRACE=1 and a scratch buffer with TRACE_BYTES of extra room: CTA 0 records a
   // timeline of its roles behind the work list (a profiling aid, off by default)
   p.trace = nullptr;
