@@ -73,10 +73,10 @@ struct FwdSmem {
   static constexpr int K_OFF = Q_OFF + 2 * TILE_BYTES;
   static constexpr int V_OFF = K_OFF + KV_STAGES * TILE_BYTES;
   static constexpr int BAR_OFF = V_OFF + KV_STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 8 + 2 * SCHED_SLOTS;
+  static constexpr int NUM_BARS = 4 + 4 * KV_STAGES + 8 + 2 * SCHED_SLOTS;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
   static constexpr int SCHED_OFF = MISC_OFF + 64;
-  static constexpr int TOTAL = SCHED_OFF + SCHED_SLOTS * SCHED_SLOT_BYTES;
+  static constexpr int TOTAL = SCHED_OFF + SCHED_SLOTS * 128;   // ring of work items (PairGeom slots)
   // slack for manual 1024-byte alignment; at least 116 KB so that two CTAs (each of which
   // allocates all 512 TMEM columns) can never share an SM
   static constexpr int DYN_BYTES = (TOTAL + 1024) > 116 * 1024 ? (TOTAL + 1024) : 116 * 1024;
@@ -155,9 +155,71 @@ __device__ __forceinline__ void silu_chunk_exact(const uint32_t (&r)[32], uint32
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Work items travel from the producer warp to the other warps as ready-made geometry (128 bytes
+// in a 4-slot shared-memory ring): the tile ranges are worked out once per item, by the warp with
+// the most slack, a whole item ahead of their use.  Code that runs once per item is fetched
+// cold, so the less of it the consumers execute at an item boundary the shorter the boundary.
+// ---------------------------------------------------------------------------------------
+struct __align__(16) PairGeom {
+  int idx;                   // (item, head) index; >= number of (item, head) pairs: no more work
+  int start, len, nt;        // first token row, untruncated length, number of targets
+  int m0, L, u, regular;     // first row of tile A, rows that take part, first target, closed forms valid
+  int max_id, has_b, n_tiles, t_lo;
+  int n_main, extra0, extra1, a_lo;      // union of the kv tiles of A and B: [t_lo, t_lo + n_main) + extras
+  int a_hi, a_x, a_n, b_lo;              // kv tiles of A: [a_lo, a_hi) + a_x (a_n in total); likewise B
+  int b_hi, b_x, b_n, fa_lo;             // fully visible kv tiles of A: [fa_lo, fa_hi); likewise B
+  int fa_hi, fb_lo, fb_hi, pad0;
+  int pad[4];
+  __device__ __forceinline__ int tile_at(int j) const { return j < n_main ? t_lo + j : (j == n_main ? extra0 : extra1); }
+  __device__ __forceinline__ bool visits(int X, int t) const {
+    const int lo = X ? b_lo : a_lo, hi = X ? b_hi : a_hi, x = X ? b_x : a_x;
+    return (t >= lo && t < hi) || t == x;
+  }
+};
+constexpr int GEOM_INTS = 27;
+
+__device__ __forceinline__ void geom_from_pair(PairGeom &g, const PairItem &pr, int idx) {
+  g.idx = idx;
+  g.start = pr.A.start; g.len = pr.A.len; g.nt = pr.A.nt;
+  g.m0 = pr.A.m0; g.L = pr.A.m.L; g.u = pr.A.u; g.regular = pr.A.regular ? 1 : 0;
+  g.max_id = pr.A.m.max_id; g.has_b = pr.hasB ? 1 : 0; g.n_tiles = pr.n_tiles; g.t_lo = pr.t_lo;
+  g.n_main = pr.n_main; g.extra0 = pr.extra0; g.extra1 = pr.extra1;
+  g.a_lo = pr.A.t_lo; g.a_hi = pr.A.t_lo + pr.A.n_main; g.a_x = pr.A.extra_tile; g.a_n = pr.A.n_tiles;
+  g.b_lo = pr.B.t_lo; g.b_hi = pr.B.t_lo + pr.B.n_main; g.b_x = pr.B.extra_tile; g.b_n = pr.B.n_tiles;
+  const FullRange fa = full_tile_range(pr.A), fb = full_tile_range(pr.B);
+  g.fa_lo = fa.lo; g.fa_hi = fa.hi; g.fb_lo = fb.lo; g.fb_hi = fb.hi;
+  g.pad0 = 0;
+}
+// item ordinals n = 0, 1, 2, ... use slot n % SCHED_SLOTS
+__device__ __forceinline__ bool geom_publish(const WaitCtx &wc, uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                             uint32_t n, const PairGeom &g) {
+  const uint32_t slot = n & (SCHED_SLOTS - 1);
+  if (!mbar_wait(wc, empty0 + 8 * slot, ((n / SCHED_SLOTS) & 1) ^ 1, 901)) return false;
+  int4 *dst = reinterpret_cast<int4 *>(ring + slot * 128);
+  const int4 *src = reinterpret_cast<const int4 *>(&g);
+#pragma unroll
+  for (int i = 0; i < 7; ++i) dst[i] = src[i];
+  asm volatile("fence.acq_rel.cta;" ::: "memory");
+  mbar_arrive(full0 + 8 * slot);
+  return true;
+}
+__device__ __forceinline__ bool geom_fetch(const WaitCtx &wc, const uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                           uint32_t n, PairGeom &g, bool arrive) {
+  const uint32_t slot = n & (SCHED_SLOTS - 1);
+  if (!mbar_wait(wc, full0 + 8 * slot, (n / SCHED_SLOTS) & 1, 902)) return false;
+  const volatile int *src = reinterpret_cast<const volatile int *>(ring + slot * 128);
+  int *dst = reinterpret_cast<int *>(&g);
+#pragma unroll
+  for (int i = 0; i < GEOM_INTS; ++i) dst[i] = src[i];
+  __syncwarp();
+  if (arrive) mbar_arrive(empty0 + 8 * slot);
+  return true;
+}
+
 // One score tile on the element-wise path, kept out of line: it is rarely taken and several
 // times the size of the interval paths, which should stay close together in the instruction
-// cache.  Same steps as the inline paths: scores to registers, barrier, P over S.
+// cache.  Same steps as the inline path: scores to registers, P over the thread's own S columns.
 template <bool IS_BF16>
 __device__ __noinline__ void exact_tile(uint32_t tS, int wg, float half_alpha, SeqMask m, int i, int col0,
                                         const float *bias, int bias_numel) {
@@ -165,13 +227,12 @@ __device__ __noinline__ void exact_tile(uint32_t tS, int wg, float half_alpha, S
   tmem_ld32(tS + wg * 64, sreg[0]);
   tmem_ld32(tS + wg * 64 + 32, sreg[1]);
   tc_wait_ld();
-  asm volatile("bar.sync 1, 256;" ::: "memory");
   const int id_i = m.id(i);
   uint32_t packed[16];
   silu_chunk_exact<IS_BF16>(sreg[0], packed, half_alpha, m, i, id_i, col0, bias, bias_numel);
-  tmem_st16(tS + wg * 32, packed);
+  tmem_st16(tS + wg * 64, packed);
   silu_chunk_exact<IS_BF16>(sreg[1], packed, half_alpha, m, i, id_i, col0 + 32, bias, bias_numel);
-  tmem_st16(tS + wg * 32 + 16, packed);
+  tmem_st16(tS + wg * 64 + 16, packed);
 }
 
 // One partially visible score tile on the regular domain (row intervals), also out of line: the
@@ -183,7 +244,6 @@ __device__ __noinline__ void masked_tile(uint32_t tS, int wg, float half_alpha, 
   tmem_ld32(tS + wg * 64, sreg[0]);
   tmem_ld32(tS + wg * 64 + 32, sreg[1]);
   tc_wait_ld();
-  asm volatile("bar.sync 1, 256;" ::: "memory");
   RowInterval ri;
   ri.lo = lo;
   ri.hi = hi;
@@ -192,12 +252,12 @@ __device__ __noinline__ void masked_tile(uint32_t tS, int wg, float half_alpha, 
   const uint32_t b0 = row_mask_bits(ri, col0, L), b1 = row_mask_bits(ri, col0 + 32, L);
   uint32_t p0[16], p1[16];
   silu_chunk<IS_BF16, true>(sreg[0], p0, half_alpha, b0);
-  tmem_st16(tS + wg * 32, p0);
+  tmem_st16(tS + wg * 64, p0);
   silu_chunk<IS_BF16, true>(sreg[1], p1, half_alpha, b1);
-  tmem_st16(tS + wg * 32 + 16, p1);
+  tmem_st16(tS + wg * 64 + 16, p1);
 }
 
-template <int D, bool IS_BF16>
+template <int D, bool IS_BF16, bool ONE_PATH>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     hstu_attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
@@ -210,8 +270,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   const uint32_t sV = smem_base + SM::V_OFF;
   const uint32_t bars = smem_base + SM::BAR_OFF;
   // barrier map
-  const uint32_t q_full = bars + 0, q_empty = bars + 8;
-  const uint32_t k_full = bars + 16, k_empty = k_full + 8 * KV_STAGES;
+  const uint32_t q_full = bars + 0, q_empty = bars + 16;   // [2]: Q_A, Q_B
+  const uint32_t k_full = bars + 32, k_empty = k_full + 8 * KV_STAGES;
   const uint32_t v_full = k_empty + 8 * KV_STAGES, v_empty = v_full + 8 * KV_STAGES;
   const uint32_t s_full = v_empty + 8 * KV_STAGES;   // [2]: S_A, S_B ready
   const uint32_t p_full = s_full + 16;               // [2]: P_A, P_B written
@@ -228,8 +288,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(q_full + 8 * x, 1);
+      mbar_init(q_empty + 8 * x, 1);
+    }
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full + 8 * s, 1);
       mbar_init(k_empty + 8 * s, 1);
@@ -269,32 +331,38 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       bool ok = true;
       Tracer tr;
       tr.init(p.trace, 0, true);
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
-      while (idx < num_items && ok) {
-        // claim the next (item, head) index now; its descriptor is fetched and published below,
-        // after this item's loads have been issued
-        const int nidx = atomicAdd(&p.plan->next, 1);
-        const int h = idx % p.H;
+      PairGeom g;
+      {
+        const ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
+        geom_from_pair(g, pr, blockIdx.x);
+      }
+      ok = geom_publish(wc, sched_ring, sched_full, sched_empty, 0, g);
+      while (g.idx < num_items && ok) {
+        // claim the next (item, head) index now; its geometry is published below, right after this
+        // item's first requests, a whole item before the other warps need it
+        const int nidx = atomicAdd(&p.plan->next, 1);
+        ItemDesc nd;
+        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
+        const int h = g.idx % p.H;
+        PairGeom ng = g;
+        ng.idx = nidx;
         tr.mark(1);
-        ok = mbar_wait(wc, q_empty, (it_cnt & 1) ^ 1, 101);
-        if (!ok) break;
-        tr.mark(2);
-        mbar_arrive_expect_tx(q_full, (pr.hasB ? 2 : 1) * SM::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < SM::CHUNKS; ++c)
-          tma_load_2d(sQ + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, d.start + pr.A.m0, q_full);
-        if (pr.hasB) {
-#pragma unroll
-          for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sQ + SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, d.start + pr.B.m0, q_full);
-        }
-        for (int j = 0; j < pr.n_tiles; ++j, ++kv_cnt) {
+        // order of requests = order of first use: Q_A, K(0) feed S_A; Q_B feeds S_B; then V(0)
+        for (int j = 0; j < g.n_tiles; ++j, ++kv_cnt) {
           const int s = kv_cnt % KV_STAGES;
           const uint32_t par = ((kv_cnt / KV_STAGES) & 1) ^ 1;
-          const int row = d.start + pr.tile_at(j) * TILE;
+          const int row = g.start + g.tile_at(j) * TILE;
+          if (j == 0) {
+            ok = mbar_wait(wc, q_empty, (it_cnt & 1) ^ 1, 101);
+            if (!ok) break;
+            tr.mark(2);
+            mbar_arrive_expect_tx(q_full, SM::TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < SM::CHUNKS; ++c)
+              tma_load_2d(sQ + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.start + g.m0, q_full);
+          }
           ok = mbar_wait(wc, k_empty + 8 * s, par, 102);
           if (!ok) break;
           tr.mark(3);
@@ -302,6 +370,17 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
             tma_load_2d(sK + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_k, h * D + c * 64, row, k_full + 8 * s);
+          if (j == 0) {
+            // Q_B is requested for every item (a pair without a second tile reads rows that are
+            // never used), which keeps the barrier phases of the two Q buffers in step
+            ok = mbar_wait(wc, q_empty + 8, (it_cnt & 1) ^ 1, 104);
+            if (!ok) break;
+            mbar_arrive_expect_tx(q_full + 8, SM::TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < SM::CHUNKS; ++c)
+              tma_load_2d(sQ + SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.start + g.m0 + TILE,
+                          q_full + 8);
+          }
           ok = mbar_wait(wc, v_empty + 8 * s, par, 103);
           if (!ok) break;
           tr.mark(4);
@@ -309,14 +388,19 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
             tma_load_2d(sV + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_v, h * D + c * 64, row, v_full + 8 * s);
+          if (j == 0) {
+            if (nidx < num_items) {
+              PairItem np;
+              fill_pair_item(np, p.g, nd.b, nd.t, nd.start, nd.len, nd.nt);
+              geom_from_pair(ng, np, nidx);
+            }
+            ok = geom_publish(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng);
+            if (!ok) break;
+          }
         }
         if (!ok) break;
-        ItemDesc nd = d;
-        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
         ++it_cnt;
-        sched_publish(wc, sched_ring, sched_full, sched_empty, it_cnt, nd.b, nd.t, nd.start, nd.len, nd.nt, nidx, ok);
-        d = nd;
-        idx = nidx;
+        g = ng;
       }
     }
   } else if (warp == 1) {
@@ -334,8 +418,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       Tracer tr;
       tr.init(p.trace, 1, lane == 0);
 
-      // S_X = Q_X K^T for kv ring slot of global tile counter g
-      auto issue_s = [&](int X, uint32_t g) {
+      // S_X = Q_X K^T for kv ring slot of global tile counter g; `last`: Q_X has no reader left
+      auto issue_s = [&](int X, uint32_t g, bool last) {
         const int s = g % KV_STAGES;
         const uint64_t q_desc = make_smem_desc(sQ + X * SM::TILE_BYTES, 16, 1024);
         const uint64_t k_desc = make_smem_desc(sK + s * SM::TILE_BYTES, 16, 1024);
@@ -347,54 +431,67 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             mma_ss(dcol, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_s, ks > 0);
           }
           tc_commit(s_full + 8 * X);
+          if (last) tc_commit(q_empty + 8 * X);
         }
         __syncwarp();
       };
+      // a query tile that takes no part in an item (a pair without a second tile) hands its Q buffer back at once
+      auto release_q = [&](int X) {
+        if (elect_one()) tc_commit(q_empty + 8 * X);
+        __syncwarp();
+      };
 
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
+      PairGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
       bool pre_issued = false;   // the S tiles of this item's first kv tile were issued during the previous item
-      for (; idx < num_items && ok; ++it_cnt) {
-        PairItem pr;
-        fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
+      for (; ok && g.idx < num_items; ++it_cnt) {
         tr.mark(10);
-        const int n = pr.n_tiles;
-        int remaining[2] = {pr.A.n_tiles, pr.B.n_tiles};
+        const int n = g.n_tiles;
+        int remaining[2] = {g.a_n, g.b_n};
+        int s_left[2] = {g.a_n, g.b_n};      // S tiles of this item still to be issued per query tile
         bool started[2] = {false, false};
         if (!pre_issued) {
           // first kv tile: both S
-          ok = mbar_wait(wc, q_full, it_cnt & 1, 202);
-          if (!ok) break;
-          tr.mark(11);
-          const int t0 = pr.tile_at(0);
+          const int t0 = g.tile_at(0);
           ok = mbar_wait(wc, k_full + 8 * (kv_cnt % KV_STAGES), (kv_cnt / KV_STAGES) & 1, 201);
           if (!ok) break;
-          tc_fence_after();
-          if (pr.A.visits(t0)) issue_s(0, kv_cnt);
-          if (pr.hasB && pr.B.visits(t0)) issue_s(1, kv_cnt);
+#pragma unroll
+          for (int X = 0; X < 2; ++X) {
+            ok = mbar_wait(wc, q_full + 8 * X, it_cnt & 1, 202);
+            if (!ok) break;
+            tc_fence_after();
+            if (g.visits(X, t0)) {
+              --s_left[X];
+              issue_s(X, kv_cnt, s_left[X] == 0);
+            } else if (s_left[X] == 0) {
+              release_q(X);
+            }
+          }
+          if (!ok) break;
+          tr.mark(11);
           if (elect_one()) tc_commit(k_empty + 8 * (kv_cnt % KV_STAGES));
           __syncwarp();
+        } else {
+          // the first kv tile's S tiles were issued early: account for them
+          const int t0 = g.tile_at(0);
+          if (g.visits(0, t0)) --s_left[0];
+          if (g.visits(1, t0)) --s_left[1];
         }
         pre_issued = false;
-        ItemDesc nd = d;
-        int nidx = idx;
-        bool next_item = false, next_b = false;
+        PairGeom ng;
+        ng.idx = num_items;
+        bool next_item = false;
         for (int j = 0; j < n; ++j, ++kv_cnt) {
-          const int t = pr.tile_at(j);
+          const int t = g.tile_at(j);
           const bool has_next = j + 1 < n;
-          const int tn = has_next ? pr.tile_at(j + 1) : -1;
+          const int tn = has_next ? g.tile_at(j + 1) : -1;
           const int s = kv_cnt % KV_STAGES;
           const int sn = (kv_cnt + 1) % KV_STAGES;
           bool v_ready = false, kn_ready = false;
-          if (j == n - 1) {  // every S of this item has been issued
-            if (elect_one()) tc_commit(q_empty);
-            __syncwarp();
-          }
 #pragma unroll
           for (int X = 0; X < 2; ++X) {
-            const TileItem &ti = X == 0 ? pr.A : pr.B;
-            const bool here = (X == 0 || pr.hasB) && ti.visits(t);
-            const bool next = has_next && (X == 0 || pr.hasB) && ti.visits(tn);
+            const bool here = g.visits(X, t);
+            const bool next = has_next && g.visits(X, tn);
             if (here) {
               if (!started[X]) {  // O_X of the previous item must have been read out
                 ok = mbar_wait(wc, o_empty + 8 * X, (item_cnt[X] & 1) ^ 1, 203);
@@ -411,7 +508,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 tr.mark(20);
               }
               tc_fence_after();
-              // V tile: [128 kv rows][D], 64-column blocks 16 KB apart; 16 kv rows per MMA = 2 KB
+              // V tile: [128 kv rows][D], 64-column blocks 16 KB apart; 16 kv rows per MMA = 2 KB.
+              // P: K steps 0-3 sit in columns [0,32) of the score region, 4-7 in [64,96).
               const uint64_t v_desc = make_smem_desc(sV + s * SM::TILE_BYTES, SM::CHUNK_BYTES, 1024);
               const uint32_t a_tmem = tmem_base + X * 128;
               const uint32_t o_tmem = tmem_base + 256 + X * 128;
@@ -419,7 +517,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
               if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < TILE / 16; ++ks)
-                  mma_ts(o_tmem, a_tmem + ks * 8, desc_advance(v_desc, ks * 2048), idesc_o,
+                  mma_ts(o_tmem, a_tmem + (ks / 4) * 64 + (ks % 4) * 8, desc_advance(v_desc, ks * 2048), idesc_o,
                          (started[X] || ks > 0) ? 1u : 0u);
                 if (last) tc_commit(o_full + 8 * X);
               }
@@ -437,31 +535,33 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 tc_fence_after();
                 tr.mark(17);
               }
-              issue_s(X, kv_cnt + 1);
+              --s_left[X];
+              issue_s(X, kv_cnt + 1, s_left[X] == 0);
               tr.mark(18 + X);
             }
-            if (X == 0 && j == n - 1) {
-              // The S_A buffer is free from here on: fetch the next item and issue its first S_A
-              // ahead of this item's last P_B V, so that the activation warps find a score tile
-              // waiting when they finish this item.  Q of the next item is loaded as soon as the
-              // S tiles issued so far have completed (q_empty above); its first K tile goes to the
-              // ring slot after this one.
-              ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, nd.b, nd.t, nd.start, nd.len,
-                               nd.nt, nidx, lane == 0);
-              if (!ok) break;
-              if (nidx < num_items) {
-                PairItem np;
-                fill_pair_item(np, p.g, nd.b, nd.t, nd.start, nd.len, nd.nt);
-                const int nt0 = np.tile_at(0);
-                const bool next_a = np.A.visits(nt0);
-                next_b = np.hasB && np.B.visits(nt0);
-                next_item = true;
-                ok = mbar_wait(wc, q_full, (it_cnt + 1) & 1, 209);
+            if (j == n - 1) {
+              // Last kv tile: the S_X buffer is free from here on.  Take the next item (X = 0)
+              // and issue its first S_X ahead of what remains of this item, so that the
+              // activation warps find a score tile waiting when they finish this item.  Q_X of
+              // the next item was requested when this item's last S_X was issued; its first K tile
+              // goes to the ring slot after this one.
+              if (X == 0) {
+                ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng, lane == 0);
                 if (!ok) break;
-                ok = mbar_wait(wc, k_full + 8 * sn, ((kv_cnt + 1) / KV_STAGES) & 1, 210);
+                next_item = ng.idx < num_items;
+                if (next_item) {
+                  ok = mbar_wait(wc, k_full + 8 * sn, ((kv_cnt + 1) / KV_STAGES) & 1, 210);
+                  if (!ok) break;
+                }
+              }
+              if (next_item) {
+                ok = mbar_wait(wc, q_full + 8 * X, (it_cnt + 1) & 1, 209);
                 if (!ok) break;
                 tc_fence_after();
-                if (next_a) issue_s(0, kv_cnt + 1);
+                const int nt0 = ng.tile_at(0);
+                const int n_x = X ? ng.b_n : ng.a_n;
+                if (ng.visits(X, nt0)) issue_s(X, kv_cnt + 1, n_x == 1);
+                else if (n_x == 0) release_q(X);
                 tr.mark(21);
               }
             }
@@ -476,10 +576,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             ok = mbar_wait(wc, k_full + 8 * sn, ((kv_cnt + 1) / KV_STAGES) & 1, 208);
             if (!ok) break;
           }
-          if (j == n - 1 && next_item) {
-            if (next_b) issue_s(1, kv_cnt + 1);
-            pre_issued = true;
-          }
+          if (j == n - 1 && next_item) pre_issued = true;
           if (elect_one()) {
             tc_commit(v_empty + 8 * s);
             if (has_next || (j == n - 1 && next_item)) tc_commit(k_empty + 8 * sn);
@@ -487,8 +584,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           __syncwarp();
         }
         if (!ok) break;
-        d = nd;
-        idx = nidx;
+        g = ng;
       }
     }
   } else if (warp < 10) {
@@ -496,7 +592,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     // All eight warps work on one score tile at a time (A, then B, then A ...): the activation is
     // bound by the MUFU rate of the whole SM, so a tile is finished soonest - and its P handed
     // back to the tensor pipe soonest - when every warp works on it.  Warps 2-5 take columns
-    // [0,64) of the tile, warps 6-9 columns [64,128); thread = one query row.
+    // [0,64) of the tile, warps 6-9 columns [64,128); thread = one query row.  P (16-bit) goes
+    // over the first half of the columns the thread has read itself - [0,32) or [64,96) - so the
+    // warps need no barrier among themselves.
     const int wg = warp >= 6 ? 1 : 0;
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
     const int row_in_tile = quad * 32 + lane;
@@ -506,34 +604,33 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     Tracer tr;
     tr.init(p.trace, 2 + wg, quad == 2 && lane == 0);
     if ((int)blockIdx.x < num_items) {
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
+      PairGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
       uint32_t item_no = 0;
-      while (idx < num_items && ok) {
-        PairItem pr;
-        fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
-        const int L = pr.A.m.L;
-        const SeqMask m = pr.A.m;
-        const bool exact_only = !pr.A.regular || p.bias != nullptr;
-        const int iA = pr.A.m0 + row_in_tile, iB = pr.B.m0 + row_in_tile;
-        const RowInterval riA = row_interval(pr.A, iA), riB = row_interval(pr.B, iB);
-        // kv tiles on which no element of the tile pair is masked
-        FullRange frA = full_tile_range(pr.A), frB = full_tile_range(pr.B);
-        if (exact_only) frA.hi = frA.lo = frB.hi = frB.lo = 0;
-        // which kv tiles each query tile visits (B visits nothing when the pair has no second tile)
-        const int va_lo = pr.A.t_lo, va_hi = pr.A.t_lo + pr.A.n_main, va_x = pr.A.extra_tile;
-        const int vb_lo = pr.B.t_lo, vb_hi = pr.B.t_lo + pr.B.n_main, vb_x = pr.B.extra_tile;
-        const int n_tiles = pr.n_tiles, t_lo = pr.t_lo, n_main = pr.n_main, x0 = pr.extra0, x1 = pr.extra1;
+      while (ok && g.idx < num_items) {
+        const int L = g.L;
+        SeqMask m;
+        m.L = g.L; m.max_id = g.max_id; m.c = p.g.c; m.W = p.g.W; m.F = p.g.F;
+        const bool exact_only = !g.regular || p.bias != nullptr;
+        const int iA = g.m0 + row_in_tile, iB = g.m0 + TILE + row_in_tile;
+        RowInterval riA, riB;
+        {
+          TileItem ti;   // the fields row_interval() reads
+          ti.m = m;
+          ti.u = g.u;
+          riA = row_interval(ti, iA);
+          riB = row_interval(ti, iB);
+        }
+        const int n_tiles = g.n_tiles;
         for (int j = 0; j < n_tiles && ok; ++j) {
-          const int t = j < n_main ? t_lo + j : (j == n_main ? x0 : x1);
+          const int t = g.tile_at(j);
           // the loop over the two query tiles stays rolled: one copy of the hot code
 #pragma unroll 1
           for (int X = 0; X < 2; ++X) {
             const bool isb = X != 0;
-            const int v_lo = isb ? vb_lo : va_lo, v_hi = isb ? vb_hi : va_hi, v_x = isb ? vb_x : va_x;
-            if (!((t >= v_lo && t < v_hi) || t == v_x)) continue;
-            const int f_lo = isb ? frB.lo : frA.lo, f_hi = isb ? frB.hi : frA.hi;
-            const bool full = t >= f_lo && t < f_hi;
+            if (!g.visits(X, t)) continue;
+            const int f_lo = isb ? g.fb_lo : g.fa_lo, f_hi = isb ? g.fb_hi : g.fa_hi;
+            const bool full = !exact_only && t >= f_lo && t < f_hi;
             const uint32_t tS = tmem_base + X * 128 + lane_off;
             const int col0 = t * TILE + wg * 64;
             tr.mark(30);
@@ -541,25 +638,41 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             if (!ok) break;
             tc_fence_after();
             tr.mark(31);
-            if (full) {
+            if (!exact_only) {
+              // Fully and partially visible tiles share everything but the activation block
+              // itself.  ONE_PATH (short sequences, where every third tile is partially visible):
+              // the masking variant serves both, so the loop has one block that stays in the
+              // instruction cache; otherwise fully visible tiles take a variant without the
+              // per-element selects, which is what long sequences mostly run.
+              uint32_t b0 = 0xffffffffu, b1 = 0xffffffffu;
+              if (!full) {
+                RowInterval ri;
+                ri.lo = isb ? riB.lo : riA.lo;
+                ri.hi = isb ? riB.hi : riA.hi;
+                ri.ctx_hi = isb ? riB.ctx_hi : riA.ctx_hi;
+                ri.self = isb ? riB.self : riA.self;
+                b0 = row_mask_bits(ri, col0, L);
+                b1 = row_mask_bits(ri, col0 + 32, L);
+              }
               uint32_t sreg[2][32];
               tmem_ld32(tS + wg * 64, sreg[0]);
               tmem_ld32(tS + wg * 64 + 32, sreg[1]);
               tc_wait_ld();
-              // P is written over the first 64 columns of S: every warp must have its scores in
-              // registers before anyone stores
-              asm volatile("bar.sync 1, 256;" ::: "memory");
               tr.mark(32);
               // one straight-line block, so that the second half's MUFU work is scheduled under
               // the first half's packing and store
               uint32_t p0[16], p1[16];
-              silu_chunk<IS_BF16, false>(sreg[0], p0, p.half_alpha, 0xffffffffu);
-              tmem_st16(tS + wg * 32, p0);
-              silu_chunk<IS_BF16, false>(sreg[1], p1, p.half_alpha, 0xffffffffu);
-              tmem_st16(tS + wg * 32 + 16, p1);
-            } else if (!exact_only) {
-              masked_tile<IS_BF16>(tS, wg, p.half_alpha, isb ? riB.lo : riA.lo, isb ? riB.hi : riA.hi,
-                                   isb ? riB.ctx_hi : riA.ctx_hi, isb ? riB.self : riA.self, col0, L);
+              if (!ONE_PATH && full) {
+                silu_chunk<IS_BF16, false>(sreg[0], p0, p.half_alpha, b0);
+                tmem_st16(tS + wg * 64, p0);
+                silu_chunk<IS_BF16, false>(sreg[1], p1, p.half_alpha, b1);
+                tmem_st16(tS + wg * 64 + 16, p1);
+              } else {
+                silu_chunk<IS_BF16, true>(sreg[0], p0, p.half_alpha, b0);
+                tmem_st16(tS + wg * 64, p0);
+                silu_chunk<IS_BF16, true>(sreg[1], p1, p.half_alpha, b1);
+                tmem_st16(tS + wg * 64 + 16, p1);
+              }
             } else {
               exact_tile<IS_BF16>(tS, wg, p.half_alpha, m, isb ? iB : iA, col0, p.bias, p.bias_numel);
             }
@@ -574,8 +687,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         }
         if (!ok) break;
         ++item_no;
-        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, item_no, d.b, d.t, d.start, d.len, d.nt, idx,
-                         lane == 0);
+        ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, item_no, g, lane == 0);
       }
     }
   } else {
@@ -587,26 +699,24 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     uint32_t my_items[2] = {0, 0};
     bool ok = true;
     if ((int)blockIdx.x < num_items) {
-      ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
-      int idx = blockIdx.x;
+      PairGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
       uint32_t item_no = 0;
-      while (idx < num_items && ok) {
-        const int h = idx % p.H;
-        PairItem pr;
-        fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
-        const int L = pr.A.m.L;
+      while (ok && g.idx < num_items) {
+        const int h = g.idx % p.H;
+        const int L = g.L;
 #pragma unroll
         for (int X = 0; X < 2; ++X) {
-          if (X == 1 && !pr.hasB) continue;
-          const int m0 = X == 0 ? pr.A.m0 : pr.B.m0;
+          if (X == 1 && !g.has_b) continue;
+          const int m0 = g.m0 + X * TILE;
           const int i = m0 + row_in_tile;
           ok = mbar_wait(wc, o_full + 8 * X, my_items[X] & 1, 302);
           if (!ok) break;
           tc_fence_after();
           float scale = p.inv_n;
           if (p.attn_scale != nullptr && i < L)
-            scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)d.start + i];
-          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + i) * p.o_rs + (int64_t)h * p.o_hs;
+            scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)g.start + i];
+          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(g.start + i) * p.o_rs + (int64_t)h * p.o_hs;
           const uint32_t tO = tmem_base + 256 + X * 128 + lane_off;
           uint32_t r[2][32];
           tmem_ld32(tO, r[0]);
@@ -640,17 +750,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           if (lane == 0) mbar_arrive(o_empty + 8 * X);
           ++my_items[X];
           // rows at or beyond max_seq_len of an over-long sequence come back as zeros
-          if (d.len > L && m0 + TILE >= L) {
-            for (int r2 = L + row_in_tile; r2 < d.len; r2 += TILE) {
-              uint16_t *zr = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + r2) * p.o_rs + (int64_t)h * p.o_hs;
+          if (g.len > L && m0 + TILE >= L) {
+            for (int r2 = L + row_in_tile; r2 < g.len; r2 += TILE) {
+              uint16_t *zr = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(g.start + r2) * p.o_rs + (int64_t)h * p.o_hs;
               for (int x = 0; x < D; x += 8) *reinterpret_cast<uint4 *>(zr + x) = make_uint4(0, 0, 0, 0);
             }
           }
         }
         if (!ok) break;
         ++item_no;
-        ok = sched_fetch(wc, sched_ring, sched_full, sched_empty, item_no, d.b, d.t, d.start, d.len, d.nt, idx,
-                         lane == 0);
+        ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, item_no, g, lane == 0);
       }
     }
   }
@@ -674,7 +783,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
 int64_t attn_tc_fwd_workspace_bytes(const b200_hstu_attn_args &a) { return plan_bytes(a.total_L, a.B); }
 
-template <int D, bool IS_BF16>
+template <int D, bool IS_BF16, bool ONE_PATH>
 int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   using SM = FwdSmem<D>;
   if (a.workspace == nullptr || a.workspace_bytes < attn_tc_fwd_workspace_bytes(a))
@@ -728,7 +837,7 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");
-  auto kern = hstu_attn_fwd_sm100_kernel<D, IS_BF16>;
+  auto kern = hstu_attn_fwd_sm100_kernel<D, IS_BF16, ONE_PATH>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
   if (e != cudaSuccess) return check_cuda(e, "forward smem attribute");
   {
@@ -742,8 +851,13 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
 
 int attn_tc_fwd(const b200_hstu_attn_args &a, cudaStream_t st) {
   const bool bf = a.dtype == B200_HSTU_BF16;
-  if (a.dqk == 128) return bf ? launch_fwd_tc<128, true>(a, st) : launch_fwd_tc<128, false>(a, st);
-  return bf ? launch_fwd_tc<64, true>(a, st) : launch_fwd_tc<64, false>(a, st);
+  const bool one_path = a.max_seq_len <= 2048;   // see ONE_PATH in the activation loop
+  if (a.dqk == 128) {
+    if (one_path) return bf ? launch_fwd_tc<128, true, true>(a, st) : launch_fwd_tc<128, false, true>(a, st);
+    return bf ? launch_fwd_tc<128, true, false>(a, st) : launch_fwd_tc<128, false, false>(a, st);
+  }
+  if (one_path) return bf ? launch_fwd_tc<64, true, true>(a, st) : launch_fwd_tc<64, false, true>(a, st);
+  return bf ? launch_fwd_tc<64, true, false>(a, st) : launch_fwd_tc<64, false, false>(a, st);
 }
 
 }  // namespace b200hstu
