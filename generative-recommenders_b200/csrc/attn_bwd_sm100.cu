@@ -50,6 +50,8 @@ using namespace ptx;
 int make_tile_map_rows(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
                        int elem_bytes, bool is_bf16, int box_rows);
 int device_sm_count();
+void fill_pdl_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int grid, int threads, size_t smem,
+                     cudaStream_t st);
 
 namespace {
 
@@ -477,6 +479,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   // TMEM columns: TS [0,128) scores (S^T | S) then P, TP [128,256) dP (dP^T | dP) then dS,
   //   ACC0 [256,384), ACC1 [384,512);  kv-stationary: ACC0 = dV, ACC1 = dK (one set);
   //   q-stationary: ACC0 / ACC1 = dQ of even / odd items (two sets)
+  // Everything above overlapped with the kernel before this one in the stream.  The kv-stationary
+  // launch follows the planning kernel and waits for its lists here.  The q-stationary launch
+  // follows the kv-stationary one, whose outputs it does not touch and which has seen the lists
+  // complete: it starts working at once, on SMs that the first launch's CTAs have left, and only
+  // waits for that launch at its very end, so that the stream order of completion is kept.
+  if (DKDV) grid_dependency_wait();
+  allow_dependents();
   const int num_items = p.plan->num_items * p.H;
 
   if (warp == 0) {
@@ -809,6 +818,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+  if (!DKDV) grid_dependency_wait();
   // timeline: start and end time of every CTA (second half of the last role's records)
   if (p.trace != nullptr && threadIdx.x == 0 && blockIdx.x < TRACE_RECORDS / 2)
     p.trace[3 * TRACE_RECORDS + TRACE_RECORDS / 2 + blockIdx.x] = make_ulonglong2(cta_t0, globaltimer_ns());
@@ -892,7 +902,11 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pk.status = &hdr_kv->status;
     if (trace_buf != nullptr && want_trace[0] == 'd' && want_trace[1] == 'k') pk.trace = trace_buf;
     ProfileScope prof(PROF_ATTN_BWD_DKDV, st);
-    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pk);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    fill_pdl_config(&cfg, &attr, grid, BWD_THREADS, SM::DYN_BYTES, st);
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mdo, pk);
+    if (e != cudaSuccess) return check_cuda(e, "backward (dk, dv) launch");
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dk, dv)");
   }
@@ -906,7 +920,11 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     pq.status = &hdr_q->status;
     if (trace_buf != nullptr && want_trace[0] == 'd' && want_trace[1] == 'q') pq.trace = trace_buf;
     ProfileScope prof(PROF_ATTN_BWD_DQ, st);
-    kern<<<grid, BWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, mdo, pq);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    fill_pdl_config(&cfg, &attr, grid, BWD_THREADS, SM::DYN_BYTES, st);
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mdo, pq);
+    if (e != cudaSuccess) return check_cuda(e, "backward (dq) launch");
     count_launch();
     B200_CHECK_LAUNCH("tcgen05 attention backward (dq)");
   }

@@ -38,6 +38,8 @@ using namespace ptx;
 int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
                   int elem_bytes, bool is_bf16);
 int device_sm_count();
+void fill_pdl_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int grid, int threads, size_t smem,
+                     cudaStream_t st);
 
 namespace {
 
@@ -319,6 +321,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // TMEM columns: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512)
+  // everything above overlapped with the planning kernel; its list is read from here on
+  grid_dependency_wait();
   const int num_items = p.plan->num_items * p.H;
 
   if (warp == 0) {
@@ -842,7 +846,11 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   if (e != cudaSuccess) return check_cuda(e, "forward smem attribute");
   {
     ProfileScope prof(PROF_ATTN_FWD, st);
-    kern<<<grid, FWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, p);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    fill_pdl_config(&cfg, &attr, grid, FWD_THREADS, SM::DYN_BYTES, st);
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, p);
+    if (e != cudaSuccess) return check_cuda(e, "forward launch");
   }
   count_launch();
   B200_CHECK_LAUNCH("tcgen05 attention forward");

@@ -409,6 +409,9 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
 template <int KIND>
 __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams g, PlanHeader *hdr, ItemDesc *items,
                                                                  int max_items, int first_dynamic) {
+  // the attention kernel that follows may already set itself up; it waits for this grid to
+  // finish before it reads the list
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   plan_body<KIND>(g, hdr, items, max_items, first_dynamic);
 }
 
@@ -417,6 +420,7 @@ template <int KIND0, int KIND1>
 __global__ void __launch_bounds__(PLAN_THREADS) attn_plan2_kernel(AttnGeomParams g, PlanHeader *hdr0, ItemDesc *items0,
                                                                   PlanHeader *hdr1, ItemDesc *items1, int max_items,
                                                                   int first_dynamic) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (blockIdx.x == 0)
     plan_body<KIND0>(g, hdr0, items0, max_items, first_dynamic);
   else

@@ -53,6 +53,21 @@ int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, 
   return make_tile_map_rows(m, base, rows, cols, row_stride_elems, elem_bytes, is_bf16, TILE);
 }
 
+// Launch attribute that lets a kernel start before the previous kernel of the stream has finished
+// (programmatic dependent launch); the kernel itself waits where it first needs that kernel's output.
+void fill_pdl_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int grid, int threads, size_t smem,
+                     cudaStream_t st) {
+  *cfg = cudaLaunchConfig_t{};
+  cfg->gridDim = dim3((unsigned)grid);
+  cfg->blockDim = dim3((unsigned)threads);
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = st;
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
+
 int device_sm_count() {
   static int n = 0;
   if (n == 0) {

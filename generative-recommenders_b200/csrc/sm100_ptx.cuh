@@ -132,6 +132,13 @@ __device__ __forceinline__ void st_global_256(void *p, uint4 a, uint4 b) {
                : "memory");
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while the kernel
+// before it in the stream is still running; grid_dependency_wait() blocks until that kernel has
+// completed and its writes are visible.  allow_dependents() lets the next such kernel start.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------ TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
