@@ -58,7 +58,7 @@ class AttnArgs(Structure):
         ("alpha", c_float),
         ("max_attn_len", c_int32), ("contextual_seq_len", c_int32), ("min_full_attn_seq_len", c_int32),
         ("dtype", c_int32), ("impl", c_int32),
-        ("bias_by_distance", c_void_p), ("bias_numel", c_int32), ("reserved0", c_int32),
+        ("bias_by_distance", c_void_p), ("bias_numel", c_int32), ("plan_mode", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_int64),
     ]
 

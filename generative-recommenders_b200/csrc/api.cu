@@ -66,7 +66,7 @@ int attn_simt(const b200_hstu_attn_args &a, cudaStream_t st, bool bwd);
 bool attn_tc_applicable(const b200_hstu_attn_args &a, bool bwd, const char **why);
 int attn_tc_fwd(const b200_hstu_attn_args &a, cudaStream_t st);
 int attn_tc_bwd(const b200_hstu_attn_args &a, cudaStream_t st);
-int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, bool bwd);
+int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, int which);
 int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &a, cudaStream_t st);
 int quantize_e4m3_block(const void *x, int dtype, int64_t row_stride, int64_t head_stride, void *x8, float *scale,
                         const int32_t *seq_offsets, const int32_t *block_offsets, int B, int H, int d,
@@ -101,6 +101,8 @@ int validate_attn(const b200_hstu_attn_args *a, bool bwd) {
   if (a->attn_scale && a->attn_scale_numel != 1 && a->attn_scale_numel != a->total_L)
     return fail(B200_HSTU_EINVAL, "attn_scale must have 1 or total_L elements");
   if (a->bias_by_distance && a->bias_numel <= 0) return fail(B200_HSTU_EINVAL, "bias_numel must be positive");
+  if (a->plan_mode != B200_HSTU_PLAN_OWN && a->plan_mode != (bwd ? B200_HSTU_PLAN_REUSE : B200_HSTU_PLAN_FOR_BACKWARD))
+    return fail(B200_HSTU_EINVAL, "plan_mode %d is not valid for this call", (int)a->plan_mode);
   return 0;
 }
 
@@ -138,8 +140,8 @@ int b200_hstu_attn_bwd(const b200_hstu_attn_args *a, b200_hstu_stream_t stream) 
 int64_t b200_hstu_attn_workspace_bytes(const b200_hstu_attn_args *a, int backward) {
   if (a == nullptr) return 0;
   const char *why = "";
-  if (a->impl == B200_HSTU_IMPL_SIMT || !attn_tc_applicable(*a, backward != 0, &why)) return 0;
-  return attn_tc_workspace_bytes(*a, backward != 0);
+  if (a->impl == B200_HSTU_IMPL_SIMT || !attn_tc_applicable(*a, backward == 1, &why)) return 0;
+  return attn_tc_workspace_bytes(*a, backward);
 }
 
 int b200_hstu_attn_fwd_fp8(const b200_hstu_attn_fp8_args *a, b200_hstu_stream_t stream) {

@@ -878,20 +878,28 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   // launch records a timeline of its roles behind the work lists (a profiling aid, off by default)
   static const char *want_trace = getenv("B200_HSTU_TRACE");
   ulonglong2 *trace_buf = nullptr;
-  if (want_trace != nullptr && a.workspace_bytes >= 2 * one + TRACE_BYTES)
+  if (want_trace != nullptr && a.plan_mode != B200_HSTU_PLAN_REUSE && a.workspace_bytes >= 2 * one + TRACE_BYTES)
     trace_buf = reinterpret_cast<ulonglong2 *>(reinterpret_cast<uint8_t *>(a.workspace) + 2 * one);
   const int64_t upper = (int64_t)max_items * a.H;
   const int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
-  PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(a.workspace);
-  PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + one);
-  {
-    ProfileScope prof(PROF_PLAN, st);
-    attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
-        p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1),
-        max_items, grid);
+  // own lists: [kv list | q list]; lists planned by the forward: [forward list | kv list | q list]
+  const bool reuse = a.plan_mode == B200_HSTU_PLAN_REUSE;
+  if (reuse && a.workspace_bytes < 3 * one)
+    return fail(B200_HSTU_EWORKSPACE, "backward reusing the forward's lists expects its %lld-byte scratch, got %lld",
+                (long long)(3 * one), (long long)a.workspace_bytes);
+  uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace) + (reuse ? one : 0);
+  PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(ws);
+  PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(ws + one);
+  if (!reuse) {
+    {
+      ProfileScope prof(PROF_PLAN, st);
+      attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
+          p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1),
+          max_items, grid);
+    }
+    count_launch();
+    B200_CHECK_LAUNCH("attention plan (backward)");
   }
-  count_launch();
-  B200_CHECK_LAUNCH("attention plan (backward)");
   {
     auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);

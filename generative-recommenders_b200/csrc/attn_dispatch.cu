@@ -15,8 +15,10 @@ bool attn_tc_applicable(const b200_hstu_attn_args &a, bool bwd, const char **why
   return attn_tc_layout_ok(a, bwd, why);
 }
 
-int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, bool bwd) {
-  return bwd ? attn_tc_bwd_workspace_bytes(a) : attn_tc_fwd_workspace_bytes(a);
+// which: 0 = forward, 1 = backward, 2 = forward that also plans the backward
+int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, int which) {
+  if (which == 2) return attn_tc_fwd_workspace_bytes(a) + attn_tc_bwd_workspace_bytes(a);
+  return which == 1 ? attn_tc_bwd_workspace_bytes(a) : attn_tc_fwd_workspace_bytes(a);
 }
 
 }  // namespace b200hstu

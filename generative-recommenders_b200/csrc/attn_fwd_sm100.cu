@@ -829,7 +829,7 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   {
     static const bool want_trace = getenv("B200_HSTU_TRACE") != nullptr;
     const int64_t need = attn_tc_fwd_workspace_bytes(a);
-    if (want_trace && a.workspace_bytes >= need + TRACE_BYTES)
+    if (want_trace && a.plan_mode == B200_HSTU_PLAN_OWN && a.workspace_bytes >= need + TRACE_BYTES)
       p.trace = reinterpret_cast<ulonglong2 *>(reinterpret_cast<uint8_t *>(a.workspace) + need);
   }
   const int max_items = (int)plan_max_items(a.total_L, a.B);
@@ -837,7 +837,19 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   const int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {
     ProfileScope prof(PROF_PLAN, st);
-    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, grid);
+    if (a.plan_mode == B200_HSTU_PLAN_FOR_BACKWARD) {
+      // one planning launch for the whole training step: the backward's two lists go behind this one
+      const int64_t one = plan_bytes(a.total_L, a.B);
+      if (a.workspace_bytes < 3 * one)
+        return fail(B200_HSTU_EWORKSPACE, "forward that plans the backward needs %lld bytes of scratch, got %lld",
+                    (long long)(3 * one), (long long)a.workspace_bytes);
+      PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + one);
+      PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + 2 * one);
+      attn_plan3_kernel<PLAN_Q_PAIR><<<3, PLAN_THREADS, 0, st>>>(p.g, hdr, items, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1),
+                                                    hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1), max_items, grid);
+    } else {
+      attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, grid);
+    }
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");

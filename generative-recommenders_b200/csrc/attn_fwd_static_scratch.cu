@@ -67,6 +67,7 @@ int b200_hstu_attn_fwd_static_scratch(const b200_hstu_attn_args *args, b200_hstu
   b200_hstu_attn_args a = *args;
   a.workspace = nullptr;
   a.workspace_bytes = 0;
+  a.plan_mode = B200_HSTU_PLAN_OWN;   // the built-in buffer holds the forward's list only
   // size check first, on the host, before anything touches the device
   const int64_t need = b200_hstu_attn_workspace_bytes(&a, 0);
   if (need > kStaticScratchBytes)

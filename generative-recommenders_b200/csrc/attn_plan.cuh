@@ -427,6 +427,21 @@ __global__ void __launch_bounds__(PLAN_THREADS) attn_plan2_kernel(AttnGeomParams
     plan_body<KIND1>(g, hdr1, items1, max_items, first_dynamic);
 }
 
+// all three work lists of a training step in one launch (one CTA each): forward, then the
+// backward's K/V-tile and query-tile lists
+template <int KIND0>
+__global__ void __launch_bounds__(PLAN_THREADS) attn_plan3_kernel(AttnGeomParams g, PlanHeader *hdr0, ItemDesc *items0,
+                                                                  PlanHeader *hdr1, ItemDesc *items1, PlanHeader *hdr2,
+                                                                  ItemDesc *items2, int max_items, int first_dynamic) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (blockIdx.x == 0)
+    plan_body<KIND0>(g, hdr0, items0, max_items, first_dynamic);
+  else if (blockIdx.x == 1)
+    plan_body<PLAN_KV_TILE>(g, hdr1, items1, max_items, first_dynamic);
+  else
+    plan_body<PLAN_Q_TILE>(g, hdr2, items2, max_items, first_dynamic);
+}
+
 __device__ __forceinline__ ItemDesc load_desc(const ItemDesc *items, int idx) {
   const int4 *p4 = reinterpret_cast<const int4 *>(items + idx);
   int4 a = __ldg(p4), b = __ldg(p4 + 1);

@@ -63,8 +63,12 @@ def _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, 
         a.bias_numel = bias_by_distance.numel()
 
 
-def _workspace(a, backward: bool, device) -> Optional[torch.Tensor]:
-    n = _cabi.lib().b200_hstu_attn_workspace_bytes(a, 1 if backward else 0)
+_PLAN_OWN, _PLAN_FOR_BACKWARD, _PLAN_REUSE = 0, 1, 2
+
+
+def _workspace(a, which: int, device) -> Optional[torch.Tensor]:
+    """Scratch for a forward (0), a backward (1) or a forward that also plans the backward (2)."""
+    n = _cabi.lib().b200_hstu_attn_workspace_bytes(a, which)
     if n <= 0:
         return None
     ws = torch.empty(n, dtype=torch.uint8, device=device)
@@ -74,27 +78,35 @@ def _workspace(a, backward: bool, device) -> Optional[torch.Tensor]:
 
 
 def hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
-                       contextual_seq_len, min_full_attn_seq_len, bias_by_distance=None) -> torch.Tensor:
-    """One forward launch; all tensors already validated / int32 / on the device."""
+                       contextual_seq_len, min_full_attn_seq_len, bias_by_distance=None, plan_for_backward=False):
+    """One forward launch; all tensors already validated / int32 / on the device.
+
+    With ``plan_for_backward`` the planning kernel also builds the backward's work lists and the
+    scratch tensor holding them is returned next to the output (``(out, scratch)``), to be passed
+    to one ``hstu_attention_bwd`` call: one planning launch per training step instead of two."""
     L, H, _ = q.shape
     out = torch.empty((L, H, v.shape[2]), dtype=q.dtype, device=q.device)
     if L == 0:
-        return out
+        return (out, None) if plan_for_backward else out
     a = _cabi.AttnArgs()
     _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, alpha, max_attn_len,
                  contextual_seq_len, min_full_attn_seq_len, bias_by_distance)
     a.out = out.data_ptr()
     a.o_row_stride, a.o_head_stride = out.stride(0), out.stride(1)
-    ws = _workspace(a, False, q.device)  # noqa: F841  (kept alive until the launch is queued)
+    ws = _workspace(a, 2 if plan_for_backward else 0, q.device)  # kept alive until the launch is queued
+    if plan_for_backward and ws is not None:
+        a.plan_mode = _PLAN_FOR_BACKWARD
     with torch.cuda.device(q.device):
         _cabi.check(_cabi.lib().b200_hstu_attn_fwd(a, stream_ptr(q.device)), "b200_hstu_attn_fwd")
-    return out
+    return (out, ws) if plan_for_backward else out
 
 
 def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
-                       contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance=None) -> None:
+                       contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance=None,
+                       planned_scratch=None) -> None:
     """Fills caller-allocated dq / dk / dv (the ownership rule of the reference's backward,
-    triton_hstu_attention.py:3059-3079)."""
+    triton_hstu_attention.py:3059-3079).  ``planned_scratch``: the scratch a forward with
+    ``plan_for_backward`` returned for the same arguments; its lists serve one backward call."""
     if q.shape[0] == 0:
         return
     a = _cabi.AttnArgs()
@@ -106,7 +118,13 @@ def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targe
     a.dq_row_stride, a.dq_head_stride = dq.stride(0), dq.stride(1)
     a.dk_row_stride, a.dk_head_stride = dk.stride(0), dk.stride(1)
     a.dv_row_stride, a.dv_head_stride = dv.stride(0), dv.stride(1)
-    ws = _workspace(a, True, q.device)  # noqa: F841
+    reuse = planned_scratch is not None and _cabi.lib().b200_hstu_attn_workspace_bytes(a, 1) > 0
+    if reuse:
+        a.plan_mode = _PLAN_REUSE
+        a.workspace = planned_scratch.data_ptr()
+        a.workspace_bytes = planned_scratch.numel()
+    else:
+        ws = _workspace(a, 1, q.device)  # noqa: F841
     with torch.cuda.device(q.device):
         _cabi.check(_cabi.lib().b200_hstu_attn_bwd(a, stream_ptr(q.device)), "b200_hstu_attn_bwd")
 
@@ -115,8 +133,14 @@ class _HstuMhaFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, max_seq_len, alpha,
                 max_attn_len, contextual_seq_len, min_full_attn_seq_len):
+        # when a gradient will be asked for, the forward's planning launch builds the backward's
+        # work lists as well; the first backward call consumes them
+        plan = any(ctx.needs_input_grad[:3])
         out = hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
-                                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance)
+                                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance, plan_for_backward=plan)
+        ctx.planned_scratch = None
+        if plan:
+            out, ctx.planned_scratch = out
         ctx.save_for_backward(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance)
         ctx.params = (max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len)
         return out
@@ -131,8 +155,10 @@ class _HstuMhaFunction(torch.autograd.Function):
         dq = torch.empty_like(q, memory_format=torch.contiguous_format)
         dk = torch.empty_like(k, memory_format=torch.contiguous_format)
         dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+        planned, ctx.planned_scratch = ctx.planned_scratch, None   # a second backward plans for itself
         hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
-                           contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance)
+                           contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance,
+                           planned_scratch=planned)
         return dq, dk, dv, None, None, None, None, None, None, None, None, None
 
 

@@ -38,6 +38,13 @@ extern "C" {
 #define B200_HSTU_F16 2
 #define B200_HSTU_E4M3 3
 
+/* who builds the work lists the tensor-core kernels walk (b200_hstu_attn_args.plan_mode) */
+#define B200_HSTU_PLAN_OWN 0          /* every call builds its own lists in its workspace                  */
+#define B200_HSTU_PLAN_FOR_BACKWARD 1 /* forward: also build the backward's lists (one planning launch for  */
+                                      /* the whole training step); workspace of ..._workspace_bytes(a, 2)  */
+#define B200_HSTU_PLAN_REUSE 2        /* backward: workspace is that forward workspace; plan nothing.  The  */
+                                      /* lists serve one backward call; same sizes / offsets / semantics   */
+
 /* which kernel family runs the attention */
 #define B200_HSTU_IMPL_AUTO 0    /* tcgen05 when dtype/head-dim allow, else SIMT */
 #define B200_HSTU_IMPL_SIMT 1    /* fp32-accumulating CUDA-core kernels          */
@@ -87,7 +94,7 @@ typedef struct b200_hstu_attn_args {
      bias_by_distance[|i - j|] when |i - j| < bias_numel, else 0 (fp32); NULL = none */
   const float *bias_by_distance;
   int32_t bias_numel;
-  int32_t reserved0;
+  int32_t plan_mode;             /* B200_HSTU_PLAN_*; ignored by the CUDA-core kernels */
   /* scratch: see b200_hstu_attn_workspace_bytes(); contents need no initialisation */
   void *workspace;
   int64_t workspace_bytes;
@@ -123,7 +130,8 @@ int b200_hstu_attn_bwd(const b200_hstu_attn_args *args, b200_hstu_stream_t strea
 int b200_hstu_attn_fwd_static_scratch(const b200_hstu_attn_args *args, b200_hstu_stream_t stream);
 int64_t b200_hstu_attn_fwd_static_scratch_max_bytes(void);
 
-/* Bytes of scratch that fwd (backward = 0) or bwd (backward = 1) need for these sizes.
+/* Bytes of scratch that fwd (backward = 0), bwd (backward = 1) or a forward that also plans the
+   backward (backward = 2, plan_mode FOR_BACKWARD / REUSE) need for these sizes.
    Host function; depends on B, H, dqk, dv, total_L, dtype, impl only. */
 int64_t b200_hstu_attn_workspace_bytes(const b200_hstu_attn_args *args, int backward);
 

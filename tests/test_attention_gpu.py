@@ -233,6 +233,40 @@ def test_config1_full_size_forward_backward():
         assert O.rel_l2(g, r) < BF16_TOL, nm
 
 
+def test_backward_reusing_the_forward_plan_is_bit_identical():
+    """The forward's planning launch can build the backward's work lists (one launch per training
+    step).  Gradients must not depend on who planned, and a second backward through the same graph
+    (the lists are consumed by the first) must plan for itself and agree as well."""
+    from generative_recommenders_b200 import hstu_attention as HA
+    q, k, v, offs, nt, dout = _random_case(11, 5, 100, 500, 520, 2, 128, torch.bfloat16, targets=30, ctx=5)
+    q, k, v, dout = (t.to(DEV) for t in (q, k, v, dout))
+    offs32, nt32 = offs.to(DEV).to(torch.int32), nt.to(DEV).to(torch.int32)
+    args = (520, 1.0 / 128, q, k, v, offs32, nt32, None, 90, 5, 0)
+    # explicit calls: own plans
+    out0 = HA.hstu_attention_fwd(*args)
+    g0 = [torch.empty_like(t) for t in (q, k, v)]
+    HA.hstu_attention_bwd(dout, *args, *g0)
+    # explicit calls: shared plan
+    out1, scratch = HA.hstu_attention_fwd(*args, plan_for_backward=True)
+    g1 = [torch.empty_like(t) for t in (q, k, v)]
+    HA.hstu_attention_bwd(dout, *args, *g1, planned_scratch=scratch)
+    torch.cuda.synchronize()
+    assert torch.equal(out0, out1)
+    for a, b in zip(g0, g1):
+        assert torch.equal(a, b)
+    # autograd: two backward passes through one graph
+    qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = G.hstu_mha(520, 1.0 / 128, qd, kd, vd, offs32, num_targets=nt32, max_attn_len=90, contextual_seq_len=5)
+    out.backward(dout, retain_graph=True)
+    first = [t.grad.clone() for t in (qd, kd, vd)]
+    for t in (qd, kd, vd):
+        t.grad = None
+    out.backward(dout)
+    torch.cuda.synchronize()
+    for a, b, c in zip(first, (qd.grad, kd.grad, vd.grad), g0):
+        assert torch.equal(a, b) and torch.equal(a, c)
+
+
 def test_unsupported_requests_raise():
     q = torch.zeros(4, 1, 32, device=DEV)
     offs = torch.tensor([0, 4], device=DEV)
