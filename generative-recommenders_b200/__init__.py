@@ -3,7 +3,7 @@ kernels in libb200_hstu.so (C ABI in include/b200_hstu.h)."""
 
 from . import _cabi, hstu_compute
 from .common import HammerKernel
-from .hstu_attention import hstu_mha, set_attention_impl
+from .hstu_attention import delta_hstu_mha, hstu_mha, set_attention_impl
 from .hstu_attention_fp8 import hstu_mha_fp8, quantize_e4m3_block
 from .hstu_compute import (
     hstu_compute_output,
@@ -17,6 +17,7 @@ from .stu import STULayer, STULayerConfig, STUStack
 
 __all__ = [
     "HammerKernel",
+    "delta_hstu_mha",
     "hstu_mha",
     "hstu_mha_fp8",
     "quantize_e4m3_block",

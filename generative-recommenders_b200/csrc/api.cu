@@ -101,6 +101,13 @@ int validate_attn(const b200_hstu_attn_args *a, bool bwd) {
   if (a->attn_scale && a->attn_scale_numel != 1 && a->attn_scale_numel != a->total_L)
     return fail(B200_HSTU_EINVAL, "attn_scale must have 1 or total_L elements");
   if (a->bias_by_distance && a->bias_numel <= 0) return fail(B200_HSTU_EINVAL, "bias_numel must be positive");
+  if (a->delta_size < 0) return fail(B200_HSTU_EINVAL, "delta_size must not be negative");
+  if (a->delta_size > 0) {
+    if (bwd) return fail(B200_HSTU_EUNSUPPORTED, "delta attention has no backward (it is the cached inference path)");
+    if (a->attn_scale && a->attn_scale_numel != 1)
+      return fail(B200_HSTU_EINVAL, "delta attention takes a scalar attn_scale only");
+    if (a->plan_mode != B200_HSTU_PLAN_OWN) return fail(B200_HSTU_EINVAL, "delta attention plans for itself");
+  }
   if (a->plan_mode != B200_HSTU_PLAN_OWN && a->plan_mode != (bwd ? B200_HSTU_PLAN_REUSE : B200_HSTU_PLAN_FOR_BACKWARD))
     return fail(B200_HSTU_EINVAL, "plan_mode %d is not valid for this call", (int)a->plan_mode);
   return 0;
@@ -292,6 +299,7 @@ void b200_hstu_host_bwd_q_tiles(int32_t len, int32_t num_targets, int32_t max_se
   g.W = max_attn_len;
   g.c = contextual_seq_len;
   g.F = min_full_attn_seq_len;
+  g.delta = 0;
   TileItem it;
   fill_kv_item(it, g, 0, kt, 0, len, num_targets);
   *t_lo = it.t_lo;
@@ -315,6 +323,7 @@ int b200_hstu_host_interval_mask(int32_t len, int32_t num_targets, int32_t max_s
   g.W = max_attn_len;
   g.c = contextual_seq_len;
   g.F = min_full_attn_seq_len;
+  g.delta = 0;
   TileItem it;
   fill_common(it, g, 0, 0, 0, len, num_targets);
   if (!it.regular) return -1;

@@ -853,6 +853,7 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.g.W = a.max_attn_len;
   p.g.c = a.contextual_seq_len;
   p.g.F = a.min_full_attn_seq_len;
+  p.g.delta = 0;
   p.dq = a.dq; p.dk = a.dk; p.dv = a.dv_;
   p.dq_rs = a.dq_row_stride; p.dq_hs = a.dq_head_stride;
   p.dk_rs = a.dk_row_stride; p.dk_hs = a.dk_head_stride;

@@ -600,6 +600,7 @@ int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &fa, cudaStream_t st) {
   p.g.W = a.max_attn_len;
   p.g.c = a.contextual_seq_len;
   p.g.F = a.min_full_attn_seq_len;
+  p.g.delta = 0;
   PlanHeader *hdr = reinterpret_cast<PlanHeader *>(a.workspace);
   ItemDesc *items = reinterpret_cast<ItemDesc *>(hdr + 1);
   p.plan = hdr;

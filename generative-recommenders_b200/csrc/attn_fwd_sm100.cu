@@ -171,7 +171,7 @@ struct __align__(16) PairGeom {
   int n_main, extra0, extra1, a_lo;      // union of the kv tiles of A and B: [t_lo, t_lo + n_main) + extras
   int a_hi, a_x, a_n, b_lo;              // kv tiles of A: [a_lo, a_hi) + a_x (a_n in total); likewise B
   int b_hi, b_x, b_n, fa_lo;             // fully visible kv tiles of A: [fa_lo, fa_hi); likewise B
-  int fa_hi, fb_lo, fb_hi, pad0;
+  int fa_hi, fb_lo, fb_hi, q_row;        // q_row: row of tile A's first query in the q / out tensors
   int pad[4];
   __device__ __forceinline__ int tile_at(int j) const { return j < n_main ? t_lo + j : (j == n_main ? extra0 : extra1); }
   __device__ __forceinline__ bool visits(int X, int t) const {
@@ -179,9 +179,9 @@ struct __align__(16) PairGeom {
     return (t >= lo && t < hi) || t == x;
   }
 };
-constexpr int GEOM_INTS = 27;
+constexpr int GEOM_INTS = 28;
 
-__device__ __forceinline__ void geom_from_pair(PairGeom &g, const PairItem &pr, int idx) {
+__device__ __forceinline__ void geom_from_pair(PairGeom &g, const PairItem &pr, int idx, int delta) {
   g.idx = idx;
   g.start = pr.A.start; g.len = pr.A.len; g.nt = pr.A.nt;
   g.m0 = pr.A.m0; g.L = pr.A.m.L; g.u = pr.A.u; g.regular = pr.A.regular ? 1 : 0;
@@ -191,7 +191,8 @@ __device__ __forceinline__ void geom_from_pair(PairGeom &g, const PairItem &pr, 
   g.b_lo = pr.B.t_lo; g.b_hi = pr.B.t_lo + pr.B.n_main; g.b_x = pr.B.extra_tile; g.b_n = pr.B.n_tiles;
   const FullRange fa = full_tile_range(pr.A), fb = full_tile_range(pr.B);
   g.fa_lo = fa.lo; g.fa_hi = fa.hi; g.fb_lo = fb.lo; g.fb_hi = fb.hi;
-  g.pad0 = 0;
+  // cached inference: q / out hold `delta` rows per sequence; otherwise they are jagged like k / v
+  g.q_row = delta > 0 ? pr.A.b * delta + pr.A.mt * TILE : pr.A.start + pr.A.m0;
 }
 // item ordinals n = 0, 1, 2, ... use slot n % SCHED_SLOTS
 __device__ __forceinline__ bool geom_publish(const WaitCtx &wc, uint8_t *ring, uint32_t full0, uint32_t empty0,
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
-        geom_from_pair(g, pr, blockIdx.x);
+        geom_from_pair(g, pr, blockIdx.x, p.g.delta);
       }
       ok = geom_publish(wc, sched_ring, sched_full, sched_empty, 0, g);
       while (g.idx < num_items && ok) {
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             mbar_arrive_expect_tx(q_full, SM::TILE_BYTES);
 #pragma unroll
             for (int c = 0; c < SM::CHUNKS; ++c)
-              tma_load_2d(sQ + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.start + g.m0, q_full);
+              tma_load_2d(sQ + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.q_row, q_full);
           }
           ok = mbar_wait(wc, k_empty + 8 * s, par, 102);
           if (!ok) break;
@@ -382,7 +383,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             mbar_arrive_expect_tx(q_full + 8, SM::TILE_BYTES);
 #pragma unroll
             for (int c = 0; c < SM::CHUNKS; ++c)
-              tma_load_2d(sQ + SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.start + g.m0 + TILE,
+              tma_load_2d(sQ + SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.q_row + TILE,
                           q_full + 8);
           }
           ok = mbar_wait(wc, v_empty + 8 * s, par, 103);
@@ -396,7 +397,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             if (nidx < num_items) {
               PairItem np;
               fill_pair_item(np, p.g, nd.b, nd.t, nd.start, nd.len, nd.nt);
-              geom_from_pair(ng, np, nidx);
+              geom_from_pair(ng, np, nidx, p.g.delta);
             }
             ok = geom_publish(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng);
             if (!ok) break;
@@ -717,10 +718,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           ok = mbar_wait(wc, o_full + 8 * X, my_items[X] & 1, 302);
           if (!ok) break;
           tc_fence_after();
+          const bool row_ok = i >= 0 && i < L;
           float scale = p.inv_n;
-          if (p.attn_scale != nullptr && i < L)
+          if (p.attn_scale != nullptr && row_ok)
             scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)g.start + i];
-          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(g.start + i) * p.o_rs + (int64_t)h * p.o_hs;
+          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) +
+                           (int64_t)(g.q_row + X * TILE + row_in_tile) * p.o_rs + (int64_t)h * p.o_hs;
           const uint32_t tO = tmem_base + 256 + X * 128 + lane_off;
           uint32_t r[2][32];
           tmem_ld32(tO, r[0]);
@@ -728,7 +731,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           for (int cc = 0; cc < D / 32; ++cc) {
             tc_wait_ld();
             if (cc + 1 < D / 32) tmem_ld32(tO + (cc + 1) * 32, r[(cc + 1) & 1]);
-            if (i < L) {
+            if (row_ok) {
               const uint32_t(&v)[32] = r[cc & 1];
               uint4 o4[4];
 #pragma unroll
@@ -795,7 +798,8 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
                 (long long)attn_tc_fwd_workspace_bytes(a), (long long)a.workspace_bytes);
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = make_tile_map(&mq, a.q, a.total_L, (int64_t)a.H * D, a.q_row_stride, 2, IS_BF16)) != 0) return rc;
+  const int64_t q_rows = a.delta_size > 0 ? (int64_t)a.B * a.delta_size : a.total_L;
+  if ((rc = make_tile_map(&mq, a.q, q_rows, (int64_t)a.H * D, a.q_row_stride, 2, IS_BF16)) != 0) return rc;
   if ((rc = make_tile_map(&mk, a.k, a.total_L, (int64_t)a.H * D, a.k_row_stride, 2, IS_BF16)) != 0) return rc;
   if ((rc = make_tile_map(&mv, a.v, a.total_L, (int64_t)a.H * D, a.v_row_stride, 2, IS_BF16)) != 0) return rc;
   FwdParams p;
@@ -807,6 +811,7 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.g.W = a.max_attn_len;
   p.g.c = a.contextual_seq_len;
   p.g.F = a.min_full_attn_seq_len;
+  p.g.delta = a.delta_size;
   PlanHeader *hdr = reinterpret_cast<PlanHeader *>(a.workspace);
   ItemDesc *items = reinterpret_cast<ItemDesc *>(hdr + 1);
   p.plan = hdr;

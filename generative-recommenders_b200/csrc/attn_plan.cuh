@@ -40,7 +40,13 @@ struct __align__(16) ItemDesc {
 struct AttnGeomParams {
   const int32_t *seq_offsets, *num_targets;
   int B, H, max_seq_len, W, c, F;
+  int delta;   // > 0: the query rows are the last `delta` positions of each sequence (cached inference)
 };
+
+// number of 128-row query tiles of a sequence and the position of the first query row
+__host__ __device__ __forceinline__ int q_tiles_of(const AttnGeomParams &g, int L) {
+  return ((g.delta > 0 ? g.delta : L) + 127) / 128;
+}
 
 struct TileItem {
   int b, mt;              // sequence, tile index inside the sequence
@@ -65,8 +71,8 @@ __host__ __device__ __forceinline__ void fill_common(TileItem &it, const AttnGeo
   it.start = start;
   it.len = len;
   it.nt = nt;
-  it.m0 = t * TILE;
   it.m = make_seq_mask(len, g.max_seq_len, nt, g.c, g.W, g.F);
+  it.m0 = t * TILE + (g.delta > 0 ? it.m.L - g.delta : 0);
   it.u = len - nt;
   it.regular = (it.u >= g.c + 1) && (nt >= 0) && (len <= it.m.L);
 }
@@ -82,8 +88,17 @@ __host__ __device__ __forceinline__ void fill_q_item(TileItem &it, const AttnGeo
   it.n_main = t_hi - it.t_lo;
   it.extra_tile = -1;
   if (r.diag_lo >= 0) {
-    int dt = r.diag_lo / TILE;
-    if (dt >= t_hi || dt < it.t_lo) it.extra_tile = dt;
+    const int dt = r.diag_lo / TILE;
+    const int d_end = r.diag_lo + TILE < it.m.L ? r.diag_lo + TILE : it.m.L;
+    const int dt2 = (d_end - 1) / TILE;
+    if (dt2 == dt) {
+      if (dt >= t_hi || dt < it.t_lo) it.extra_tile = dt;
+    } else {
+      // a query tile that is not aligned to the kv tiles (cached inference): its diagonal block
+      // straddles two kv tiles; widen the main range over both (tiles in between are masked out)
+      if (dt2 + 1 > t_hi) t_hi = dt2 + 1;
+      it.n_main = t_hi - it.t_lo;
+    }
   }
   it.n_tiles = it.n_main + (it.extra_tile >= 0 ? 1 : 0);
 }
@@ -196,7 +211,7 @@ struct PairItem {
 __host__ __device__ __forceinline__ void fill_pair_item(PairItem &p, const AttnGeomParams &g, int b, int pair,
                                                         int start, int len, int nt) {
   fill_q_item(p.A, g, b, 2 * pair, start, len, nt);
-  const int ntiles = (p.A.m.L + TILE - 1) / TILE;
+  const int ntiles = q_tiles_of(g, p.A.m.L);
   p.hasB = (2 * pair + 1) < ntiles;
   int lo = p.A.t_lo, hi = p.A.t_lo + p.A.n_main;
   if (p.hasB) {
@@ -350,7 +365,7 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
       const int len = g.seq_offsets[b + 1] - start;
       const int nt = g.num_targets ? g.num_targets[b] : 0;
       const int L = len < g.max_seq_len ? len : g.max_seq_len;
-      const int ntiles = (L + TILE - 1) / TILE;
+      const int ntiles = KIND == PLAN_KV_TILE ? (L + TILE - 1) / TILE : q_tiles_of(g, L);
       const int nunits = KIND == PLAN_Q_PAIR ? (ntiles + 1) / 2 : ntiles;
       for (int t = tslot; t < nunits; t += TSLOTS) {
         int cost = item_cost<KIND>(g, b, t, len, nt);

@@ -33,6 +33,7 @@ struct SimtParams {
   int H, dqk, dv_dim, max_seq_len;
   float alpha;
   int W, c, F;
+  int delta;   // > 0 (forward only): q / out hold the last `delta` positions of each sequence, `delta` rows each
 };
 
 template <typename E>
@@ -106,9 +107,13 @@ __device__ __forceinline__ void zero_rows_beyond_grid(E *base, int64_t row_strid
 template <typename E, int MAXD, int MODE>
 __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams p) {
   extern __shared__ float smem[];
-  const int b = blockIdx.z, h = blockIdx.y, m0 = blockIdx.x * T;
+  const int b = blockIdx.z, h = blockIdx.y;
   const SeqGeom g = seq_geom(p, b);
-  if (m0 >= g.len) return;
+  const bool cached = MODE == 0 && p.delta > 0;
+  if ((int)blockIdx.x * T >= (cached ? p.delta : g.len)) return;
+  // position of the tile's first query inside the sequence, and its row in the q / out tensors
+  const int m0 = (int)blockIdx.x * T + (cached ? g.m.L - p.delta : 0);
+  const int64_t qrow0 = cached ? (int64_t)b * p.delta + (int)blockIdx.x * T : (int64_t)g.start + m0;
   const int dqk = p.dqk, dvd = p.dv_dim;
   const int dmax = dqk > dvd ? dqk : dvd;
   const int ld = dmax + 1;
@@ -125,11 +130,11 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
 
   const int L = g.m.L;
   if (m0 < L) {
-    const E *qp = (const E *)p.q + (int64_t)g.start * p.q_rs + (int64_t)h * p.q_hs;
+    const E *qp = (const E *)p.q + qrow0 * p.q_rs + (int64_t)h * p.q_hs;
     const E *kp = (const E *)p.k + (int64_t)g.start * p.k_rs + (int64_t)h * p.k_hs;
     const E *vp = (const E *)p.v + (int64_t)g.start * p.v_rs + (int64_t)h * p.v_hs;
     const int qrows = min(T, L - m0);
-    load_tile(Qs, ld, qp, p.q_rs, m0, qrows, dqk);
+    load_tile(Qs, ld, qp, p.q_rs, 0, qrows, dqk);
     if (MODE == 1) {
       const E *gp = (const E *)p.dout + (int64_t)g.start * p.do_rs + (int64_t)h * p.do_hs;
       load_tile(Gs, ld, gp, p.do_rs, m0, qrows, dvd);
@@ -137,7 +142,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
     const KvRange range = kv_range_for_q_tile(g.m, g.len, g.nt, m0, T);
     const int i = m0 + r;
     const int id_i = g.m.id(i);
-    const float sc = i < L ? row_scale(p, (int64_t)g.start + i) : 0.f;
+    const float sc = (i >= 0 && i < L) ? row_scale(p, (int64_t)g.start + i) : 0.f;
     for (int n0 = 0; n0 < L; n0 += T) {
       if (!tiles_overlap(range, n0)) continue;
       __syncthreads();
@@ -152,7 +157,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
         int j = n0 + cg + 4 * jj;
-        bool ok = i < L && j < L && g.m.valid_ids(i, j, id_i, g.m.id(j));
+        bool ok = i >= 0 && i < L && j < L && g.m.valid_ids(i, j, id_i, g.m.id(j));
         float x = s[jj] * p.alpha;
         if (p.bias != nullptr) {
           int dist = i > j ? i - j : j - i;
@@ -179,15 +184,16 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
     }
   }
   // rows at or beyond max_seq_len produce zeros (the reference's dense_to_jagged pads them)
-  if (MODE == 0)
-    zero_rows_beyond_grid((E *)p.out, p.o_rs, p.o_hs, h, g.start, g.len, dvd);
-  else
+  if (MODE == 0) {
+    if (!cached) zero_rows_beyond_grid((E *)p.out, p.o_rs, p.o_hs, h, g.start, g.len, dvd);
+  } else {
     zero_rows_beyond_grid((E *)p.dq, p.dq_rs, p.dq_hs, h, g.start, g.len, dqk);
+  }
   const int i = m0 + r;
-  if (i < g.len) {
+  if (i >= 0 && i < g.len) {
     E *op;
     if (MODE == 0)
-      op = (E *)p.out + (int64_t)(g.start + i) * p.o_rs + (int64_t)h * p.o_hs;
+      op = (E *)p.out + (qrow0 + r) * p.o_rs + (int64_t)h * p.o_hs;
     else
       op = (E *)p.dq + (int64_t)(g.start + i) * p.dq_rs + (int64_t)h * p.dq_hs;
 #pragma unroll
@@ -297,6 +303,7 @@ SimtParams make_params(const b200_hstu_attn_args &a) {
   p.do_hs = a.do_head_stride; p.dq_hs = a.dq_head_stride; p.dk_hs = a.dk_head_stride; p.dv_hs = a.dv_head_stride;
   p.H = a.H; p.dqk = a.dqk; p.dv_dim = a.dv; p.max_seq_len = a.max_seq_len;
   p.alpha = a.alpha; p.W = a.max_attn_len; p.c = a.contextual_seq_len; p.F = a.min_full_attn_seq_len;
+  p.delta = a.delta_size;
   return p;
 }
 
@@ -308,7 +315,8 @@ int launch_fwd(const b200_hstu_attn_args &a, cudaStream_t st) {
   auto kern = attn_q_stationary_kernel<E, MAXD, 0>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return check_cuda(e, "simt fwd smem attribute");
-  dim3 grid((unsigned)((a.max_seq_len + T - 1) / T), (unsigned)a.H, (unsigned)a.B);
+  const int q_rows = a.delta_size > 0 ? a.delta_size : a.max_seq_len;
+  dim3 grid((unsigned)((q_rows + T - 1) / T), (unsigned)a.H, (unsigned)a.B);
   kern<<<grid, NTHREADS, smem, st>>>(p);
   count_launch();
   B200_CHECK_LAUNCH("simt attention forward");

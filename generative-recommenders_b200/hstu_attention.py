@@ -48,7 +48,7 @@ def _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, 
     a.q_row_stride, a.q_head_stride = q.stride(0), q.stride(1)
     a.k_row_stride, a.k_head_stride = k.stride(0), k.stride(1)
     a.v_row_stride, a.v_head_stride = v.stride(0), v.stride(1)
-    a.total_L = L
+    a.total_L = k.shape[0]
     a.B = seq_offsets.numel() - 1
     a.H, a.dqk, a.dv = H, dqk, v.shape[2]
     a.max_seq_len = max_seq_len
@@ -219,3 +219,58 @@ def hstu_mha(
     return _HstuMhaFunction.apply(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, int(max_seq_len),
                                   float(alpha), int(max_attn_len), int(contextual_seq_len),
                                   int(min_full_attn_seq_len))
+
+
+def delta_hstu_mha(
+    max_seq_len: int,
+    alpha: float,
+    delta_q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    seq_offsets: torch.Tensor,
+    num_targets: Optional[torch.Tensor] = None,
+    max_attn_len: int = 0,
+    contextual_seq_len: int = 0,
+    kernel: HammerKernel = HammerKernel.CUDA,
+    enable_tma: bool = False,
+) -> torch.Tensor:
+    """Cached-inference attention: the last ``delta`` positions of every sequence attend to the
+    sequence's full (cached) K / V.  Same arguments, checks and result as the reference's
+    ``delta_hstu_mha`` (generative_recommenders/ops/hstu_attention.py:210-275): ``delta_q`` is
+    ``[B * delta, H, d]``, ``k`` / ``v`` are jagged over ``seq_offsets``, the result is
+    ``[B * delta, H, d_v]``.  Every sequence must be at least ``delta`` and at most ``max_seq_len``
+    long (the reference's mask gather assumes the same).  No gradient: this is the inference path.
+    """
+    _require_cuda_backend(kernel)
+    L, H, D = delta_q.shape if delta_q.dim() == 3 else (0, 0, 0)
+    B = seq_offsets.size(0) - 1
+    torch._assert(max_seq_len > 0, "max_seq_len must be larger than 0")
+    torch._assert(delta_q.dim() == 3, "delta_q must be 3-D")
+    torch._assert(B > 0 and L % B == 0, "delta_q must be padded")
+    torch._assert(k.dim() == 3, "k must be 3-D")
+    torch._assert(k.shape[1] == H, "wrong k shape[1]")
+    torch._assert(k.shape[2] == D, "wrong k shape[2]")
+    torch._assert(v.dim() == 3, "v must be 3-D")
+    torch._assert(v.shape[1] == H, "wrong v shape[1]")
+    require_cuda(delta_q, k, v, seq_offsets, num_targets)
+    if k.dtype != delta_q.dtype or v.dtype != delta_q.dtype:
+        raise TypeError("delta_q, k, v must share a dtype")
+    delta = L // B
+    out = torch.zeros((L, H, v.shape[2]), dtype=delta_q.dtype, device=delta_q.device)
+    if L == 0 or k.shape[0] == 0:
+        return out
+    q = last_dim_contiguous(delta_q.detach())
+    k = last_dim_contiguous(k.detach())
+    v = last_dim_contiguous(v.detach())
+    seq_offsets = _i32(seq_offsets)
+    num_targets = _i32(num_targets)
+    a = _cabi.AttnArgs()
+    _fill_common(a, q, k, v, seq_offsets, num_targets, None, int(max_seq_len), float(alpha), int(max_attn_len),
+                 int(contextual_seq_len), 0, None)
+    a.delta_size = delta
+    a.out = out.data_ptr()
+    a.o_row_stride, a.o_head_stride = out.stride(0), out.stride(1)
+    ws = _workspace(a, 0, q.device)  # noqa: F841  (kept alive until the launch is queued)
+    with torch.cuda.device(q.device):
+        _cabi.check(_cabi.lib().b200_hstu_attn_fwd(a, stream_ptr(q.device)), "b200_hstu_attn_fwd (delta)")
+    return out

@@ -98,6 +98,13 @@ typedef struct b200_hstu_attn_args {
   /* scratch: see b200_hstu_attn_workspace_bytes(); contents need no initialisation */
   void *workspace;
   int64_t workspace_bytes;
+  /* > 0 (forward only): q and out hold delta_size rows per sequence, [B * delta_size, H, d] - the
+     last delta_size positions of each sequence attend to its full K/V (total_L counts K/V rows).
+     Stands in for delta_hstu_mha (generative_recommenders/ops/hstu_attention.py:210-275,
+     pt_hstu_attention.py:191-251).  Every sequence must be at least delta_size and at most
+     max_seq_len long; attn_scale must be NULL or a scalar. */
+  int32_t delta_size;
+  int32_t reserved1;
 } b200_hstu_attn_args;
 
 /*

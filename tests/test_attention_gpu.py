@@ -267,6 +267,38 @@ def test_backward_reusing_the_forward_plan_is_bit_identical():
         assert torch.equal(a, b) and torch.equal(a, c)
 
 
+def test_delta_attention_fp32_matches_golden(golden):
+    """Cached-inference attention against the reference's own output (fixture made from
+    pytorch_cached_hstu_mha, pt_hstu_attention.py:191-251)."""
+    fx = golden("delta_attention.pt")
+    out = G.delta_hstu_mha(fx["N"], fx["alpha"], fx["delta_q"].to(DEV), fx["k"].to(DEV), fx["v"].to(DEV),
+                           fx["seq_offsets"].to(DEV), num_targets=fx["num_targets"].to(DEV)).cpu()
+    assert O.rel_l2(out, fx["out"]) < FP32_TOL
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+@pytest.mark.parametrize("delta,targets,ctx,W_", [(5, True, 0, 0), (64, True, 3, 0), (128, False, 0, 100), (200, True, 4, 150)])
+def test_delta_attention_bf16_matches_oracle(impl, delta, targets, ctx, W_):
+    G.set_attention_impl(impl)
+    g = torch.Generator().manual_seed(delta)
+    B, H, d, N = 5, 2, 128, 700
+    lengths = torch.randint(delta + ctx + 2, N + 1, (B,), generator=g)
+    lengths[0] = delta + ctx + 1                       # shortest legal sequence
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    nt = torch.full((B,), delta, dtype=torch.int64) if targets else None
+    if targets:
+        nt[1] = max(1, delta // 2)                     # delta rows that straddle history and targets
+    k = (torch.randn(L, H, d, generator=g) * 0.7).to(torch.bfloat16)
+    v = (torch.randn(L, H, d, generator=g) * 0.7).to(torch.bfloat16)
+    dq = (torch.randn(B * delta, H, d, generator=g) * 0.7).to(torch.bfloat16)
+    out = G.delta_hstu_mha(N, 1.0 / d, dq.to(DEV), k.to(DEV), v.to(DEV), offs.to(DEV),
+                           num_targets=None if nt is None else nt.to(DEV), max_attn_len=W_,
+                           contextual_seq_len=ctx).cpu()
+    ref = O.delta_hstu_mha(N, 1.0 / d, dq.float(), k.float(), v.float(), offs, nt, W_, ctx)
+    assert O.rel_l2(out, ref) < BF16_TOL
+
+
 def test_unsupported_requests_raise():
     q = torch.zeros(4, 1, 32, device=DEV)
     offs = torch.tensor([0, 4], device=DEV)
