@@ -68,8 +68,9 @@ struct BwdParams {
   void *dq, *dk, *dv;
   int64_t dq_rs, dq_hs, dk_rs, dk_hs, dv_rs, dv_hs;
   const float *attn_scale;  // NULL or one fp32 on the device
-  const float *bias;
+  const float *bias;       // bias_by_distance as given (element-wise path)
   int bias_numel;
+  const float *bias_ext;   // centre of the signed-distance table (see BiasTable); NULL = no bias
   float half_alpha, alpha, inv_n;
   int H;
   int wide_stores;  // dq / dk / dv rows are 32-byte aligned
@@ -124,9 +125,13 @@ __device__ __forceinline__ float2 unpack_keep(uint32_t u) {
 // Phase A on 32 score columns of one thread: P (kv-stationary launch) written over the scores,
 // silu' (zero where masked) returned in `keep`.  `bits` marks the visible columns; with
 // MASKED = false all of them are.
-template <bool IS_BF16, bool DKDV, bool MASKED>
+// BIAS: bp points at the signed-distance table entry (already halved) of this thread's row /
+// column and the chunk's first streamed position; the streamed index grows along the chunk, so the
+// distance q - k grows in the kv-stationary launch (entry bp[+k]) and shrinks in the q-stationary
+// one (entry bp[-k]).
+template <bool IS_BF16, bool DKDV, bool MASKED, bool BIAS>
 __device__ __forceinline__ void phase_a_chunk(uint32_t t_in, uint32_t t_out, float half_alpha, uint32_t bits,
-                                              uint32_t (&keep)[16]) {
+                                              uint32_t (&keep)[16], const float *bp) {
   uint32_t rs[32];
   tmem_ld32(t_in, rs);
   tc_wait_ld();
@@ -134,8 +139,13 @@ __device__ __forceinline__ void phase_a_chunk(uint32_t t_in, uint32_t t_out, flo
 #pragma unroll
   for (int x = 0; x < 16; ++x) {
     float sl0, dsl0, sl1, dsl1;
-    silu_and_grad(__uint_as_float(rs[2 * x]) * half_alpha, sl0, dsl0);
-    silu_and_grad(__uint_as_float(rs[2 * x + 1]) * half_alpha, sl1, dsl1);
+    float h0 = __uint_as_float(rs[2 * x]) * half_alpha, h1 = __uint_as_float(rs[2 * x + 1]) * half_alpha;
+    if (BIAS) {
+      h0 += __ldg(DKDV ? bp + 2 * x : bp - 2 * x);
+      h1 += __ldg(DKDV ? bp + 2 * x + 1 : bp - 2 * x - 1);
+    }
+    silu_and_grad(h0, sl0, dsl0);
+    silu_and_grad(h1, sl1, dsl1);
     if (MASKED) {
       const bool v0 = bits & (1u << (2 * x)), v1 = bits & (1u << (2 * x + 1));
       sl0 = v0 ? sl0 : 0.f;
@@ -208,9 +218,10 @@ struct ActTile {
   uint32_t parity;
   float half_alpha;
   int lane;
+  const float *bias_at;     // table entry of (this thread's row / column, first streamed position); NULL = no bias
 };
 
-template <bool IS_BF16, bool DKDV, int MODE>
+template <bool IS_BF16, bool DKDV, int MODE, bool BIAS>
 __device__ __forceinline__ bool act_tile_body(const WaitCtx &wc, const ActTile &a, uint32_t bits0, uint32_t bits1,
                                               const SeqMask &m, int own, int c0, const float *bias, int bias_numel,
                                               Tracer &tr) {
@@ -220,11 +231,17 @@ __device__ __forceinline__ bool act_tile_body(const WaitCtx &wc, const ActTile &
   tc_fence_after();
   tr.mark(31);
   if (MODE == 0) {
-    phase_a_chunk<IS_BF16, DKDV, false>(a.tS, a.tS, a.half_alpha, 0xffffffffu, keep0);
-    phase_a_chunk<IS_BF16, DKDV, false>(a.tS + 32, a.tS + 16, a.half_alpha, 0xffffffffu, keep1);
+    phase_a_chunk<IS_BF16, DKDV, false, false>(a.tS, a.tS, a.half_alpha, 0xffffffffu, keep0, nullptr);
+    phase_a_chunk<IS_BF16, DKDV, false, false>(a.tS + 32, a.tS + 16, a.half_alpha, 0xffffffffu, keep1, nullptr);
   } else if (MODE == 1) {
-    phase_a_chunk<IS_BF16, DKDV, true>(a.tS, a.tS, a.half_alpha, bits0, keep0);
-    phase_a_chunk<IS_BF16, DKDV, true>(a.tS + 32, a.tS + 16, a.half_alpha, bits1, keep1);
+    if (BIAS) {
+      phase_a_chunk<IS_BF16, DKDV, true, true>(a.tS, a.tS, a.half_alpha, bits0, keep0, a.bias_at);
+      phase_a_chunk<IS_BF16, DKDV, true, true>(a.tS + 32, a.tS + 16, a.half_alpha, bits1, keep1,
+                                               DKDV ? a.bias_at + 32 : a.bias_at - 32);
+    } else {
+      phase_a_chunk<IS_BF16, DKDV, true, false>(a.tS, a.tS, a.half_alpha, bits0, keep0, nullptr);
+      phase_a_chunk<IS_BF16, DKDV, true, false>(a.tS + 32, a.tS + 16, a.half_alpha, bits1, keep1, nullptr);
+    }
   } else {
     const int id_own = m.id(own);
     phase_a_exact_chunk<IS_BF16, DKDV>(a.tS, a.tS, a.half_alpha, m, own, id_own, c0, bias, bias_numel, keep0);
@@ -256,7 +273,7 @@ __device__ __noinline__ bool act_tile_exact(WaitCtx wc, ActTile a, SeqMask m, in
                                             int bias_numel) {
   Tracer off;
   off.init(nullptr, 0, false);
-  return act_tile_body<IS_BF16, DKDV, 2>(wc, a, 0u, 0u, m, own, c0, bias, bias_numel, off);
+  return act_tile_body<IS_BF16, DKDV, 2, false>(wc, a, 0u, 0u, m, own, c0, bias, bias_numel, off);
 }
 
 // Stores one 128 x D fp32 accumulator (TMEM) as scaled 16-bit rows of a jagged tensor.  One row
@@ -409,7 +426,7 @@ __device__ __forceinline__ void bwd_stage2(uint32_t acc_tmem, uint32_t a_tmem, u
   __syncwarp();
 }
 
-template <int D, bool IS_BF16, bool DKDV>
+template <int D, bool IS_BF16, bool DKDV, bool BIAS>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     hstu_attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -702,7 +719,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         item_from_geom(it, g, p.g);
         const int L = it.m.L;
         const int own = it.m0 + row_in_tile;  // kv position (DKDV) or query position
-        const bool exact_only = !it.regular || p.bias != nullptr;
+        const bool exact_only = !it.regular;
         ColInterval ci;
         RowInterval ri;
         if (DKDV) ci = col_interval(it, own); else ri = row_interval(it, own);
@@ -725,12 +742,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           at.parity = cnt & 1;
           at.half_alpha = p.half_alpha;
           at.lane = lane;
+          // signed distance query - key of (own row / column, first streamed position)
+          at.bias_at = BIAS ? p.bias_ext + (DKDV ? c0 - own : own - c0) : nullptr;
           if (!exact_only) {
             // one code path for fully and partially visible tiles: the tensor pipe, not the
             // activation, bounds this kernel, and code that runs once per item is slow to fetch
             const uint32_t b0 = full ? 0xffffffffu : (DKDV ? col_mask_bits(ci, c0, L) : row_mask_bits(ri, c0, L));
             const uint32_t b1 = full ? 0xffffffffu : (DKDV ? col_mask_bits(ci, c0 + 32, L) : row_mask_bits(ri, c0 + 32, L));
-            ok = act_tile_body<IS_BF16, DKDV, 1>(wc, at, b0, b1, it.m, own, c0, nullptr, 0, tr);
+            ok = act_tile_body<IS_BF16, DKDV, 1, BIAS>(wc, at, b0, b1, it.m, own, c0, nullptr, 0, tr);
           } else {
             ok = act_tile_exact<IS_BF16, DKDV>(wc, at, it.m, own, c0, p.bias, p.bias_numel);
           }
@@ -828,10 +847,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
 // scratch: two work lists (kv-stationary and q-stationary)
 int64_t attn_tc_bwd_workspace_bytes(const b200_hstu_attn_args &a) {
-  return 2 * plan_bytes(a.total_L, a.B);
+  return bias_table_bytes(a.bias_by_distance, a.max_seq_len) + 2 * plan_bytes(a.total_L, a.B);
 }
 
-template <int D, bool IS_BF16>
+template <int D, bool IS_BF16, bool BIAS>
 int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   using SM = BwdSmem<D>;
   if (a.workspace == nullptr || a.workspace_bytes < attn_tc_bwd_workspace_bytes(a))
@@ -861,6 +880,9 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.attn_scale = a.attn_scale;
   p.bias = a.bias_by_distance;
   p.bias_numel = a.bias_numel;
+  const int64_t eb = bias_table_bytes(a.bias_by_distance, a.max_seq_len);
+  BiasTable bt{a.bias_by_distance, a.bias_numel, reinterpret_cast<float *>(a.workspace), a.max_seq_len};
+  p.bias_ext = a.bias_by_distance ? bt.dst + (a.max_seq_len - 1) : nullptr;
   p.half_alpha = 0.5f * a.alpha;
   p.alpha = a.alpha;
   p.inv_n = 1.f / (float)a.max_seq_len;
@@ -879,16 +901,17 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   // launch records a timeline of its roles behind the work lists (a profiling aid, off by default)
   static const char *want_trace = getenv("B200_HSTU_TRACE");
   ulonglong2 *trace_buf = nullptr;
-  if (want_trace != nullptr && a.plan_mode != B200_HSTU_PLAN_REUSE && a.workspace_bytes >= 2 * one + TRACE_BYTES)
-    trace_buf = reinterpret_cast<ulonglong2 *>(reinterpret_cast<uint8_t *>(a.workspace) + 2 * one);
+  if (want_trace != nullptr && a.plan_mode != B200_HSTU_PLAN_REUSE && a.workspace_bytes >= eb + 2 * one + TRACE_BYTES)
+    trace_buf = reinterpret_cast<ulonglong2 *>(reinterpret_cast<uint8_t *>(a.workspace) + eb + 2 * one);
   const int64_t upper = (int64_t)max_items * a.H;
   const int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
-  // own lists: [kv list | q list]; lists planned by the forward: [forward list | kv list | q list]
+  // own scratch: [bias table | kv list | q list]; planned by the forward: [bias table | forward
+  // list | kv list | q list] (the table is the forward's too)
   const bool reuse = a.plan_mode == B200_HSTU_PLAN_REUSE;
-  if (reuse && a.workspace_bytes < 3 * one)
+  if (reuse && a.workspace_bytes < eb + 3 * one)
     return fail(B200_HSTU_EWORKSPACE, "backward reusing the forward's lists expects its %lld-byte scratch, got %lld",
-                (long long)(3 * one), (long long)a.workspace_bytes);
-  uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace) + (reuse ? one : 0);
+                (long long)(eb + 3 * one), (long long)a.workspace_bytes);
+  uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace) + eb + (reuse ? one : 0);
   PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(ws);
   PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(ws + one);
   if (!reuse) {
@@ -896,13 +919,13 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
       ProfileScope prof(PROF_PLAN, st);
       attn_plan2_kernel<PLAN_KV_TILE, PLAN_Q_TILE><<<2, PLAN_THREADS, 0, st>>>(
           p.g, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1), hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1),
-          max_items, grid);
+          max_items, grid, bt);
     }
     count_launch();
     B200_CHECK_LAUNCH("attention plan (backward)");
   }
   {
-    auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, true>;
+    auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, true, BIAS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
     if (e != cudaSuccess) return check_cuda(e, "backward smem attribute");
     BwdParams pk = p;
@@ -920,7 +943,7 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     B200_CHECK_LAUNCH("tcgen05 attention backward (dk, dv)");
   }
   {
-    auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, false>;
+    auto kern = hstu_attn_bwd_sm100_kernel<D, IS_BF16, false, BIAS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
     if (e != cudaSuccess) return check_cuda(e, "backward smem attribute");
     BwdParams pq = p;
@@ -942,8 +965,13 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
 
 int attn_tc_bwd(const b200_hstu_attn_args &a, cudaStream_t st) {
   const bool bf = a.dtype == B200_HSTU_BF16;
-  if (a.dqk == 128) return bf ? launch_bwd_tc<128, true>(a, st) : launch_bwd_tc<128, false>(a, st);
-  return bf ? launch_bwd_tc<64, true>(a, st) : launch_bwd_tc<64, false>(a, st);
+  // a relative bias has its own instantiation, so that the common case carries none of its code
+  if (a.bias_by_distance != nullptr) {
+    if (a.dqk == 128) return bf ? launch_bwd_tc<128, true, true>(a, st) : launch_bwd_tc<128, false, true>(a, st);
+    return bf ? launch_bwd_tc<64, true, true>(a, st) : launch_bwd_tc<64, false, true>(a, st);
+  }
+  if (a.dqk == 128) return bf ? launch_bwd_tc<128, true, false>(a, st) : launch_bwd_tc<128, false, false>(a, st);
+  return bf ? launch_bwd_tc<64, true, false>(a, st) : launch_bwd_tc<64, false, false>(a, st);
 }
 
 }  // namespace b200hstu

@@ -1,5 +1,5 @@
 // Chooses between the tensor-core and the CUDA-core attention kernels and sizes their scratch.
-#include "common.cuh"
+#include "attn_plan.cuh"
 
 namespace b200hstu {
 
@@ -17,7 +17,10 @@ bool attn_tc_applicable(const b200_hstu_attn_args &a, bool bwd, const char **why
 
 // which: 0 = forward, 1 = backward, 2 = forward that also plans the backward
 int64_t attn_tc_workspace_bytes(const b200_hstu_attn_args &a, int which) {
-  if (which == 2) return attn_tc_fwd_workspace_bytes(a) + attn_tc_bwd_workspace_bytes(a);
+  // the forward's and the backward's scratch share the bias table
+  if (which == 2)
+    return attn_tc_fwd_workspace_bytes(a) + attn_tc_bwd_workspace_bytes(a) -
+           bias_table_bytes(a.bias_by_distance, a.max_seq_len);
   return which == 1 ? attn_tc_bwd_workspace_bytes(a) : attn_tc_fwd_workspace_bytes(a);
 }
 

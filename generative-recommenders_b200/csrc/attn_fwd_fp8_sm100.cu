@@ -624,7 +624,7 @@ int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &fa, cudaStream_t st) {
   const int max_items = (int)plan_max_items(a.total_L, a.B);
   {
     ProfileScope prof(PROF_PLAN, st);
-    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, 0);
+    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, 0, BiasTable{nullptr, 0, nullptr, 0});
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");

@@ -56,8 +56,9 @@ struct FwdParams {
   int64_t o_rs, o_hs;
   const float *attn_scale;
   int64_t attn_scale_numel;
-  const float *bias;
+  const float *bias;       // bias_by_distance as given (element-wise path)
   int bias_numel;
+  const float *bias_ext;   // centre of the signed-distance table (see BiasTable); NULL = no bias
   float half_alpha;   // alpha / 2
   float inv_n;        // 1 / max_seq_len
   int H;
@@ -133,7 +134,26 @@ __device__ __forceinline__ void silu_chunk(const uint32_t (&r)[32], uint32_t (&p
   }
 }
 
-// Exact element-wise path: sequences outside the regular domain, or a relative bias.
+// The same with a relative position bias: bp points at the table entry of (this row, first column
+// of the chunk); the entry of column k is bp[-k] (already halved).
+template <bool IS_BF16>
+__device__ __forceinline__ void silu_chunk_bias(const uint32_t (&r)[32], uint32_t (&packed)[16], float half_alpha,
+                                                uint32_t bits, const float *bp) {
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    float h0 = fmaf(__uint_as_float(r[2 * x]), half_alpha, __ldg(bp - 2 * x));
+    float h1 = fmaf(__uint_as_float(r[2 * x + 1]), half_alpha, __ldg(bp - 2 * x - 1));
+    if (!IS_BF16) {
+      h0 = fminf(fmaxf(h0, -30000.f), 30000.f);
+      h1 = fminf(fmaxf(h1, -30000.f), 30000.f);
+    }
+    h0 = (bits & (1u << (2 * x))) ? h0 : 0.f;
+    h1 = (bits & (1u << (2 * x + 1))) ? h1 : 0.f;
+    packed[x] = silu_pair<IS_BF16>(h0, h1);
+  }
+}
+
+// Exact element-wise path: sequences outside the regular domain (with or without a bias).
 template <bool IS_BF16>
 __device__ __forceinline__ void silu_chunk_exact(const uint32_t (&r)[32], uint32_t (&packed)[16], float half_alpha,
                                               const SeqMask m, int i, int id_i, int col0, const float *bias,
@@ -260,7 +280,7 @@ __device__ __noinline__ void masked_tile(uint32_t tS, int wg, float half_alpha, 
   tmem_st16(tS + wg * 64 + 16, p1);
 }
 
-template <int D, bool IS_BF16, bool ONE_PATH>
+template <int D, bool IS_BF16, bool ONE_PATH, bool BIAS>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     hstu_attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
@@ -616,7 +636,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const int L = g.L;
         SeqMask m;
         m.L = g.L; m.max_id = g.max_id; m.c = p.g.c; m.W = p.g.W; m.F = p.g.F;
-        const bool exact_only = !g.regular || p.bias != nullptr;
+        const bool exact_only = !g.regular;
         const int iA = g.m0 + row_in_tile, iB = g.m0 + TILE + row_in_tile;
         RowInterval riA, riB;
         {
@@ -667,7 +687,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
               // one straight-line block, so that the second half's MUFU work is scheduled under
               // the first half's packing and store
               uint32_t p0[16], p1[16];
-              if (!ONE_PATH && full) {
+              if (BIAS) {
+                // signed distance of (this row, first column of the chunk)
+                const float *bp = p.bias_ext + ((isb ? iB : iA) - col0);
+                silu_chunk_bias<IS_BF16>(sreg[0], p0, p.half_alpha, b0, bp);
+                tmem_st16(tS + wg * 64, p0);
+                silu_chunk_bias<IS_BF16>(sreg[1], p1, p.half_alpha, b1, bp - 32);
+                tmem_st16(tS + wg * 64 + 16, p1);
+              } else if (!ONE_PATH && full) {
                 silu_chunk<IS_BF16, false>(sreg[0], p0, p.half_alpha, b0);
                 tmem_st16(tS + wg * 64, p0);
                 silu_chunk<IS_BF16, false>(sreg[1], p1, p.half_alpha, b1);
@@ -788,9 +815,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
 }  // namespace
 
-int64_t attn_tc_fwd_workspace_bytes(const b200_hstu_attn_args &a) { return plan_bytes(a.total_L, a.B); }
+// scratch: [bias table (if any) | work list]
+int64_t attn_tc_fwd_workspace_bytes(const b200_hstu_attn_args &a) {
+  return bias_table_bytes(a.bias_by_distance, a.max_seq_len) + plan_bytes(a.total_L, a.B);
+}
 
-template <int D, bool IS_BF16, bool ONE_PATH>
+template <int D, bool IS_BF16, bool ONE_PATH, bool BIAS>
 int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   using SM = FwdSmem<D>;
   if (a.workspace == nullptr || a.workspace_bytes < attn_tc_fwd_workspace_bytes(a))
@@ -812,7 +842,10 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.g.c = a.contextual_seq_len;
   p.g.F = a.min_full_attn_seq_len;
   p.g.delta = a.delta_size;
-  PlanHeader *hdr = reinterpret_cast<PlanHeader *>(a.workspace);
+  const int64_t eb = bias_table_bytes(a.bias_by_distance, a.max_seq_len);
+  uint8_t *lists = reinterpret_cast<uint8_t *>(a.workspace) + eb;
+  BiasTable bt{a.bias_by_distance, a.bias_numel, reinterpret_cast<float *>(a.workspace), a.max_seq_len};
+  PlanHeader *hdr = reinterpret_cast<PlanHeader *>(lists);
   ItemDesc *items = reinterpret_cast<ItemDesc *>(hdr + 1);
   p.plan = hdr;
   p.items = items;
@@ -824,6 +857,7 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.attn_scale_numel = a.attn_scale_numel;
   p.bias = a.bias_by_distance;
   p.bias_numel = a.bias_numel;
+  p.bias_ext = a.bias_by_distance ? bt.dst + (a.max_seq_len - 1) : nullptr;
   p.half_alpha = 0.5f * a.alpha;
   p.inv_n = 1.f / (float)a.max_seq_len;
   p.H = a.H;
@@ -845,20 +879,20 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
     if (a.plan_mode == B200_HSTU_PLAN_FOR_BACKWARD) {
       // one planning launch for the whole training step: the backward's two lists go behind this one
       const int64_t one = plan_bytes(a.total_L, a.B);
-      if (a.workspace_bytes < 3 * one)
+      if (a.workspace_bytes < eb + 3 * one)
         return fail(B200_HSTU_EWORKSPACE, "forward that plans the backward needs %lld bytes of scratch, got %lld",
-                    (long long)(3 * one), (long long)a.workspace_bytes);
-      PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + one);
-      PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(reinterpret_cast<uint8_t *>(a.workspace) + 2 * one);
+                    (long long)(eb + 3 * one), (long long)a.workspace_bytes);
+      PlanHeader *hdr_kv = reinterpret_cast<PlanHeader *>(lists + one);
+      PlanHeader *hdr_q = reinterpret_cast<PlanHeader *>(lists + 2 * one);
       attn_plan3_kernel<PLAN_Q_PAIR><<<3, PLAN_THREADS, 0, st>>>(p.g, hdr, items, hdr_kv, reinterpret_cast<ItemDesc *>(hdr_kv + 1),
-                                                    hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1), max_items, grid);
+                                                    hdr_q, reinterpret_cast<ItemDesc *>(hdr_q + 1), max_items, grid, bt);
     } else {
-      attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, grid);
+      attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, grid, bt);
     }
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");
-  auto kern = hstu_attn_fwd_sm100_kernel<D, IS_BF16, ONE_PATH>;
+  auto kern = hstu_attn_fwd_sm100_kernel<D, IS_BF16, ONE_PATH, BIAS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
   if (e != cudaSuccess) return check_cuda(e, "forward smem attribute");
   {
@@ -876,13 +910,19 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
 
 int attn_tc_fwd(const b200_hstu_attn_args &a, cudaStream_t st) {
   const bool bf = a.dtype == B200_HSTU_BF16;
+  // a relative bias has its own instantiation (always the single masking activation block), so that
+  // the common case carries none of its code
+  if (a.bias_by_distance != nullptr) {
+    if (a.dqk == 128) return bf ? launch_fwd_tc<128, true, true, true>(a, st) : launch_fwd_tc<128, false, true, true>(a, st);
+    return bf ? launch_fwd_tc<64, true, true, true>(a, st) : launch_fwd_tc<64, false, true, true>(a, st);
+  }
   const bool one_path = a.max_seq_len <= 2048;   // see ONE_PATH in the activation loop
   if (a.dqk == 128) {
-    if (one_path) return bf ? launch_fwd_tc<128, true, true>(a, st) : launch_fwd_tc<128, false, true>(a, st);
-    return bf ? launch_fwd_tc<128, true, false>(a, st) : launch_fwd_tc<128, false, false>(a, st);
+    if (one_path) return bf ? launch_fwd_tc<128, true, true, false>(a, st) : launch_fwd_tc<128, false, true, false>(a, st);
+    return bf ? launch_fwd_tc<128, true, false, false>(a, st) : launch_fwd_tc<128, false, false, false>(a, st);
   }
-  if (one_path) return bf ? launch_fwd_tc<64, true, true>(a, st) : launch_fwd_tc<64, false, true>(a, st);
-  return bf ? launch_fwd_tc<64, true, false>(a, st) : launch_fwd_tc<64, false, false>(a, st);
+  if (one_path) return bf ? launch_fwd_tc<64, true, true, false>(a, st) : launch_fwd_tc<64, false, true, false>(a, st);
+  return bf ? launch_fwd_tc<64, true, false, false>(a, st) : launch_fwd_tc<64, false, false, false>(a, st);
 }
 
 }  // namespace b200hstu

@@ -421,9 +421,38 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Relative position bias as the kernels read it: a table over the signed distance i - j,
+//   ext[k] = bias[|k|] / 2  for |k| < numel, else 0,   k in (-N, N),
+// so that a thread walking along a row (or a column) reads consecutive entries with constant
+// offsets from one pointer: no absolute value, no bounds test, no index arithmetic per element.
+// (The factor 1/2 is the h = x / 2 of the tanh form of SiLU.)  The table lives at the start of
+// the caller's scratch and is rebuilt by the planning launch of every call that has a bias.
+// ---------------------------------------------------------------------------------------
+struct BiasTable {
+  const float *src;   // bias_by_distance [numel]; NULL = no bias
+  int numel;
+  float *dst;         // 2 N - 1 floats
+  int N;
+};
+inline int64_t bias_table_bytes(const void *bias, int max_seq_len) {
+  if (bias == nullptr) return 0;
+  int64_t n = (2 * (int64_t)max_seq_len - 1) * (int64_t)sizeof(float);
+  return (n + 255) / 256 * 256;
+}
+__device__ __forceinline__ void build_bias_table(const BiasTable &t) {
+  if (t.src == nullptr) return;
+  for (int x = threadIdx.x; x < 2 * t.N - 1; x += blockDim.x) {
+    const int k = x - (t.N - 1);
+    const int a = k < 0 ? -k : k;
+    t.dst[x] = a < t.numel ? 0.5f * t.src[a] : 0.f;
+  }
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams g, PlanHeader *hdr, ItemDesc *items,
-                                                                 int max_items, int first_dynamic) {
+                                                                 int max_items, int first_dynamic, BiasTable bt) {
+  build_bias_table(bt);
   // the attention kernel that follows may already set itself up; it waits for this grid to
   // finish before it reads the list
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -434,8 +463,9 @@ __global__ void __launch_bounds__(PLAN_THREADS) attn_plan_kernel(AttnGeomParams 
 template <int KIND0, int KIND1>
 __global__ void __launch_bounds__(PLAN_THREADS) attn_plan2_kernel(AttnGeomParams g, PlanHeader *hdr0, ItemDesc *items0,
                                                                   PlanHeader *hdr1, ItemDesc *items1, int max_items,
-                                                                  int first_dynamic) {
+                                                                  int first_dynamic, BiasTable bt) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (blockIdx.x == 0) build_bias_table(bt);
   if (blockIdx.x == 0)
     plan_body<KIND0>(g, hdr0, items0, max_items, first_dynamic);
   else
@@ -447,8 +477,10 @@ __global__ void __launch_bounds__(PLAN_THREADS) attn_plan2_kernel(AttnGeomParams
 template <int KIND0>
 __global__ void __launch_bounds__(PLAN_THREADS) attn_plan3_kernel(AttnGeomParams g, PlanHeader *hdr0, ItemDesc *items0,
                                                                   PlanHeader *hdr1, ItemDesc *items1, PlanHeader *hdr2,
-                                                                  ItemDesc *items2, int max_items, int first_dynamic) {
+                                                                  ItemDesc *items2, int max_items, int first_dynamic,
+                                                                  BiasTable bt) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (blockIdx.x == 0) build_bias_table(bt);
   if (blockIdx.x == 0)
     plan_body<KIND0>(g, hdr0, items0, max_items, first_dynamic);
   else if (blockIdx.x == 1)
