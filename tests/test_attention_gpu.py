@@ -233,6 +233,25 @@ def test_config1_full_size_forward_backward():
         assert O.rel_l2(g, r) < BF16_TOL, nm
 
 
+@pytest.mark.parametrize("targets,ctx,W_,bias", [(0, 0, 0, False), (40, 0, 0, False), (24, 5, 300, False),
+                                                   (16, 0, 0, True)])
+def test_long_sequence_forward_variant(targets, ctx, W_, bias):
+    """max_seq_len > 2048 selects the forward's other activation layout (one warpgroup per query
+    tile, P contiguous in TMEM); same answers expected.  Lengths include a tile-aligned one and a
+    sequence too short for a second query tile."""
+    N, H, d = 2304, 2, 128
+    g = torch.Generator().manual_seed(77 + targets)
+    lengths = torch.tensor([2304, 1000, 129, 2048, 70 + targets + ctx])
+    nt = torch.full((len(lengths),), targets, dtype=torch.int64) if targets else None
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    q, k, v = ((torch.randn(L, H, d, generator=g) * 0.6).to(torch.bfloat16) for _ in range(3))
+    b = (torch.randn(N, generator=g) * 0.3) if bias else None
+    out, _ = _run(q, k, v, offs, N, 1.0 / d, nt, W_, ctx, bias=b)
+    ref, _ = _oracle(q, k, v, offs, N, 1.0 / d, nt, W_, ctx, bias=b)
+    assert O.rel_l2(out, ref) < BF16_TOL
+
+
 def test_backward_reusing_the_forward_plan_is_bit_identical():
     """The forward's planning launch can build the backward's work lists (one launch per training
     step).  Gradients must not depend on who planned, and a second backward through the same graph
