@@ -1,18 +1,23 @@
 // Jagged HSTU attention forward with FP8 (e4m3) q / k / v and per-block scales, for inference.
 //
 // q8, k8, v8 are e4m3 with one fp32 scale per (128-token block counted from the start of the
-// sequence, head); the output is bf16.  The kernel has the structure of the bf16 forward (pairs of
-// 128-row query tiles per CTA, TMA rings, TMEM accumulators, two activation warpgroups), with:
+// sequence, head); the output is bf16.  The kernel has the structure of the bf16 forward
+// (attn_fwd_sm100.cu: pairs of 128-row query tiles per persistent CTA, producer / MMA / eight
+// activation / four epilogue warps, work items and their geometry through a shared-memory ring,
+// the next item's first score tiles issued early), with:
 //   * S = Q8 K8^T as kind::f8f6f4 MMAs (K = 32 per instruction).  Because a scale block is exactly
 //     one 128-row tile, the de-scaling is one scalar per (query tile, kv tile):
 //     x = alpha * sq[q block] * sk[k block] * S.
 //   * P = SiLU(x) is written back to TMEM as a pair of e4m3 tiles, P ~ P_hi + P_lo (P_lo is the
 //     e4m3 rounding of the residual), so that P keeps about 8 bits; O += P_hi V8 + P_lo V8 are two
-//     fp8 MMAs on the same V tile (V8 is the MN-major B operand).
+//     fp8 MMAs on the same V tile (V8 is the MN-major B operand).  Each thread writes its 64
+//     columns' P_hi and P_lo (16 TMEM columns each) over the first half of the score columns it
+//     has read itself, so the activation warps need no barrier among themselves.
 //   * V's block scale is folded into P before the split, relative to the scale of the query
 //     tile's own block, times a constant that lifts typical activations into e4m3's normal range:
 //     P' = SiLU(x) * (sv[k block] / sv_ref) * 16;  out = O * sv_ref / 16 / max_seq_len.
-// Shared memory traffic per kv tile is about 60 % of the bf16 kernel's (1-byte operands).
+// Shared memory traffic per kv tile is about 60 % of the bf16 kernel's (1-byte operands), and the
+// K / V rings are four tiles deep.
 #include <stdlib.h>
 
 #include "attn_plan.cuh"
@@ -25,48 +30,37 @@ using namespace ptx;
 int make_tile_map(CUtensorMap *m, const void *base, int64_t rows, int64_t cols, int64_t row_stride_elems,
                   int elem_bytes, bool is_bf16);
 int device_sm_count();
+void fill_pdl_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int grid, int threads, size_t smem,
+                     cudaStream_t st);
 
 namespace {
 
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 448;
+constexpr int FWD_SCHED_CONSUMERS = 13;  // MMA warp, 8 activation warps, 4 epilogue warps: one arrival each
 constexpr int KV_STAGES = 4;
+constexpr float P_LIFT = 16.f;   // constant that lifts activations into e4m3's normal range
 
 struct Fp8Params {
   AttnGeomParams g;
-  const PlanHeader *plan;
+  PlanHeader *plan;
   const ItemDesc *items;
   int *status;
   void *out;
   int64_t o_rs, o_hs;
   const float *attn_scale;
   int64_t attn_scale_numel;
-  const float *bias;
+  const float *bias;       // bias_by_distance as given (element-wise path)
   int bias_numel;
+  const float *bias_ext;   // centre of the signed-distance table (see BiasTable); NULL = no bias
   float half_alpha;   // alpha / 2
   float inv_n;        // 1 / max_seq_len
   int H;
+  int wide_stores;    // out rows are 32-byte aligned
   const float *q_scale, *k_scale, *v_scale;  // [n_blocks_total, H]
   const int32_t *block_offsets;              // [B + 1]
-  // optional timeline of CTA 0 (4 roles x TRACE_RECORDS records of {ns, tag}); NULL = off
+  // optional timeline of CTA 0 (4 roles x TRACE_RECORDS records of {SM clock, tag}); NULL = off
   ulonglong2 *trace;
 };
-
-constexpr int TRACE_RECORDS = 1024;
-constexpr int64_t TRACE_BYTES = 4 * TRACE_RECORDS * (int64_t)sizeof(ulonglong2);
-
-struct Tracer {
-  ulonglong2 *buf;
-  int n;
-  __device__ __forceinline__ void init(ulonglong2 *base, int role, bool on) {
-    buf = (base != nullptr && on && blockIdx.x == 0) ? base + role * TRACE_RECORDS : nullptr;
-    n = 0;
-  }
-  __device__ __forceinline__ void mark(unsigned tag) {
-    if (buf != nullptr && n < TRACE_RECORDS) buf[n++] = make_ulonglong2(globaltimer_ns(), tag);
-  }
-};
-
-constexpr float P_LIFT = 16.f;   // constant that lifts activations into e4m3's normal range
 
 template <int D>
 struct FwdSmem {
@@ -78,9 +72,10 @@ struct FwdSmem {
   static constexpr int K_OFF = Q_OFF + 2 * TILE_BYTES;
   static constexpr int V_OFF = K_OFF + KV_STAGES * TILE_BYTES;
   static constexpr int BAR_OFF = V_OFF + KV_STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 8;
+  static constexpr int NUM_BARS = 4 + 4 * KV_STAGES + 8 + 2 * SCHED_SLOTS;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-  static constexpr int TOTAL = MISC_OFF + 64;
+  static constexpr int SCHED_OFF = MISC_OFF + 64;
+  static constexpr int TOTAL = SCHED_OFF + SCHED_SLOTS * 128;   // ring of work items (PairGeom slots)
   // slack for manual 1024-byte alignment; at least 116 KB so that two CTAs (each of which
   // allocates all 512 TMEM columns) can never share an SM
   static constexpr int DYN_BYTES = (TOTAL + 1024) > 116 * 1024 ? (TOTAL + 1024) : 116 * 1024;
@@ -110,9 +105,12 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
 
 // 32 scores -> 8 words of P_hi and 8 words of P_lo (4 e4m3 per word).
 // silu(x) = h + h tanh(h), h = x / 2, on packed f16 pairs; `gain2` = f16x2 of the lift factor.
+// h is clamped after packing (an overflow to infinity in the conversion clamps back to the bound).
+// Masked-out scores are replaced by h = 0 before the activation: silu(0) = 0 exactly.
 template <bool MASKED>
 __device__ __forceinline__ void silu_chunk_fp8(const uint32_t (&r)[32], uint32_t (&hi)[8], uint32_t (&lo)[8],
                                                float half_alpha, uint32_t gain2, uint32_t bits) {
+  const uint32_t bound = 0x77537753u, nbound = 0xf753f753u;   // +-30000 as f16x2
 #pragma unroll
   for (int w = 0; w < 8; ++w) {
     uint16_t h16[2], l16[2];
@@ -121,13 +119,13 @@ __device__ __forceinline__ void silu_chunk_fp8(const uint32_t (&r)[32], uint32_t
       const int x = 4 * w + 2 * y;
       float h0 = __uint_as_float(r[x]) * half_alpha;
       float h1 = __uint_as_float(r[x + 1]) * half_alpha;
-      h0 = fminf(fmaxf(h0, -30000.f), 30000.f);
-      h1 = fminf(fmaxf(h1, -30000.f), 30000.f);
       if (MASKED) {
         h0 = (bits & (1u << x)) ? h0 : 0.f;
         h1 = (bits & (1u << (x + 1))) ? h1 : 0.f;
       }
       uint32_t hh = to_f16x2(h0, h1), t, pp, back, res;
+      asm("min.f16x2 %0, %0, %1;" : "+r"(hh) : "r"(bound));
+      asm("max.f16x2 %0, %0, %1;" : "+r"(hh) : "r"(nbound));
       asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(hh));
       asm("fma.rn.f16x2 %0, %1, %2, %1;" : "=r"(pp) : "r"(hh), "r"(t));
       asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(pp) : "r"(pp), "r"(gain2));
@@ -160,10 +158,86 @@ __device__ __forceinline__ void mma_ts_f8(uint32_t d_tmem, uint32_t a_tmem, uint
       : "memory");
 }
 
+// validity bits of 32 columns for a sequence outside the regular domain (element-wise mask); out
+// of line: it is rarely needed and large
+__device__ __noinline__ uint32_t exact_bits(SeqMask m, int i, int col0) {
+  uint32_t bits = 0;
+  const int id_i = m.id(i);
+  for (int x = 0; x < 32; ++x) {
+    const int jj = col0 + x;
+    if (i >= 0 && i < m.L && jj < m.L && m.valid_ids(i, jj, id_i, m.id(jj))) bits |= 1u << x;
+  }
+  return bits;
+}
+
+// ---------------------------------------------------------------------------------------
+// Work items travel from the producer warp to the other warps as ready-made geometry (128 bytes
+// in a 4-slot shared-memory ring): the tile ranges are worked out once per item, by the warp with
+// the most slack, a whole item ahead of their use.  Code that runs once per item is fetched
+// cold, so the less of it the consumers execute at an item boundary the shorter the boundary.
+// ---------------------------------------------------------------------------------------
+struct __align__(16) PairGeom {
+  int idx;                   // (item, head) index; >= number of (item, head) pairs: no more work
+  int start, len, nt;        // first token row, untruncated length, number of targets
+  int m0, L, u, regular;     // first row of tile A, rows that take part, first target, closed forms valid
+  int max_id, has_b, n_tiles, t_lo;
+  int n_main, extra0, extra1, a_lo;      // union of the kv tiles of A and B: [t_lo, t_lo + n_main) + extras
+  int a_hi, a_x, a_n, b_lo;              // kv tiles of A: [a_lo, a_hi) + a_x (a_n in total); likewise B
+  int b_hi, b_x, b_n, fa_lo;             // fully visible kv tiles of A: [fa_lo, fa_hi); likewise B
+  int fa_hi, fb_lo, fb_hi, q_row;        // q_row: row of tile A's first query in the q / out tensors
+  int b, pad1, pad2, pad3;               // sequence index (row of its first block in the scale tensors comes from it)
+  __device__ __forceinline__ int tile_at(int j) const { return j < n_main ? t_lo + j : (j == n_main ? extra0 : extra1); }
+  __device__ __forceinline__ bool visits(int X, int t) const {
+    const int lo = X ? b_lo : a_lo, hi = X ? b_hi : a_hi, x = X ? b_x : a_x;
+    return (t >= lo && t < hi) || t == x;
+  }
+};
+constexpr int GEOM_INTS = 29;
+
+__device__ __forceinline__ void geom_from_pair(PairGeom &g, const PairItem &pr, int idx, int delta) {
+  g.idx = idx;
+  g.start = pr.A.start; g.len = pr.A.len; g.nt = pr.A.nt;
+  g.m0 = pr.A.m0; g.L = pr.A.m.L; g.u = pr.A.u; g.regular = pr.A.regular ? 1 : 0;
+  g.max_id = pr.A.m.max_id; g.has_b = pr.hasB ? 1 : 0; g.n_tiles = pr.n_tiles; g.t_lo = pr.t_lo;
+  g.n_main = pr.n_main; g.extra0 = pr.extra0; g.extra1 = pr.extra1;
+  g.a_lo = pr.A.t_lo; g.a_hi = pr.A.t_lo + pr.A.n_main; g.a_x = pr.A.extra_tile; g.a_n = pr.A.n_tiles;
+  g.b_lo = pr.B.t_lo; g.b_hi = pr.B.t_lo + pr.B.n_main; g.b_x = pr.B.extra_tile; g.b_n = pr.B.n_tiles;
+  const FullRange fa = full_tile_range(pr.A), fb = full_tile_range(pr.B);
+  g.fa_lo = fa.lo; g.fa_hi = fa.hi; g.fb_lo = fb.lo; g.fb_hi = fb.hi;
+  // cached inference: q / out hold `delta` rows per sequence; otherwise they are jagged like k / v
+  g.q_row = delta > 0 ? pr.A.b * delta + pr.A.mt * TILE : pr.A.start + pr.A.m0;
+  g.b = pr.A.b;
+}
+// item ordinals n = 0, 1, 2, ... use slot n % SCHED_SLOTS
+__device__ __forceinline__ bool geom_publish(const WaitCtx &wc, uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                             uint32_t n, const PairGeom &g) {
+  const uint32_t slot = n & (SCHED_SLOTS - 1);
+  if (!mbar_wait(wc, empty0 + 8 * slot, ((n / SCHED_SLOTS) & 1) ^ 1, 901)) return false;
+  int4 *dst = reinterpret_cast<int4 *>(ring + slot * 128);
+  const int4 *src = reinterpret_cast<const int4 *>(&g);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i] = src[i];
+  asm volatile("fence.acq_rel.cta;" ::: "memory");
+  mbar_arrive(full0 + 8 * slot);
+  return true;
+}
+__device__ __forceinline__ bool geom_fetch(const WaitCtx &wc, const uint8_t *ring, uint32_t full0, uint32_t empty0,
+                                           uint32_t n, PairGeom &g, bool arrive) {
+  const uint32_t slot = n & (SCHED_SLOTS - 1);
+  if (!mbar_wait(wc, full0 + 8 * slot, (n / SCHED_SLOTS) & 1, 902)) return false;
+  const volatile int *src = reinterpret_cast<const volatile int *>(ring + slot * 128);
+  int *dst = reinterpret_cast<int *>(&g);
+#pragma unroll
+  for (int i = 0; i < GEOM_INTS; ++i) dst[i] = src[i];
+  __syncwarp();
+  if (arrive) mbar_arrive(empty0 + 8 * slot);
+  return true;
+}
+
 template <int D>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     hstu_attn_fwd_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                               const __grid_constant__ CUtensorMap tmap_v, const Fp8Params p) {
+                                   const __grid_constant__ CUtensorMap tmap_v, const Fp8Params p) {
   using SM = FwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -173,13 +247,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   const uint32_t sV = smem_base + SM::V_OFF;
   const uint32_t bars = smem_base + SM::BAR_OFF;
   // barrier map
-  const uint32_t q_full = bars + 0, q_empty = bars + 8;
-  const uint32_t k_full = bars + 16, k_empty = k_full + 8 * KV_STAGES;
+  const uint32_t q_full = bars + 0, q_empty = bars + 16;   // [2]: Q_A, Q_B
+  const uint32_t k_full = bars + 32, k_empty = k_full + 8 * KV_STAGES;
   const uint32_t v_full = k_empty + 8 * KV_STAGES, v_empty = v_full + 8 * KV_STAGES;
   const uint32_t s_full = v_empty + 8 * KV_STAGES;   // [2]: S_A, S_B ready
   const uint32_t p_full = s_full + 16;               // [2]: P_A, P_B written
   const uint32_t o_full = p_full + 16;               // [2]: O_A, O_B complete
   const uint32_t o_empty = o_full + 16;              // [2]: O_A, O_B read out
+  const uint32_t sched_full = o_empty + 16;          // [SCHED_SLOTS] next work item published
+  const uint32_t sched_empty = sched_full + 8 * SCHED_SLOTS;
+  uint8_t *sched_ring = smem_gen + SM::SCHED_OFF;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + SM::MISC_OFF);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + SM::MISC_OFF + 8);
 
@@ -188,8 +265,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(q_full + 8 * x, 1);
+      mbar_init(q_empty + 8 * x, 1);
+    }
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full + 8 * s, 1);
       mbar_init(k_empty + 8 * s, 1);
@@ -198,9 +277,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(s_full + 8 * x, 1);
-      mbar_init(p_full + 8 * x, 4);
+      mbar_init(p_full + 8 * x, 8);
       mbar_init(o_full + 8 * x, 1);
       mbar_init(o_empty + 8 * x, 4);
+    }
+    for (int x = 0; x < SCHED_SLOTS; ++x) {
+      mbar_init(sched_full + 8 * x, 1);
+      mbar_init(sched_empty + 8 * x, FWD_SCHED_CONSUMERS);
     }
     fence_mbar_init();
   }
@@ -213,8 +296,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // TMEM columns: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512)
+  // everything above overlapped with the planning kernel; its list is read from here on
+  grid_dependency_wait();
   const int num_items = p.plan->num_items * p.H;
-  const int stride = gridDim.x;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -226,45 +310,76 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       bool ok = true;
       Tracer tr;
       tr.init(p.trace, 0, true);
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
-        const ItemDesc d = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
-        const int h = idx % p.H;
+      PairGeom g;
+      {
+        const ItemDesc d = load_desc(p.items, blockIdx.x / p.H);
         PairItem pr;
         fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
+        geom_from_pair(g, pr, blockIdx.x, p.g.delta);
+      }
+      ok = geom_publish(wc, sched_ring, sched_full, sched_empty, 0, g);
+      while (g.idx < num_items && ok) {
+        // claim the next (item, head) index now; its geometry is published below, right after this
+        // item's first requests, a whole item before the other warps need it
+        const int nidx = atomicAdd(&p.plan->next, 1);
+        ItemDesc nd;
+        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
+        const int h = g.idx % p.H;
+        PairGeom ng = g;
+        ng.idx = nidx;
         tr.mark(1);
-        ok = mbar_wait(wc, q_empty, (it_cnt & 1) ^ 1, 101);
-        if (!ok) break;
-        tr.mark(2);
-        mbar_arrive_expect_tx(q_full, (pr.hasB ? 2 : 1) * SM::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < SM::CHUNKS; ++c)
-          tma_load_2d(sQ + c * SM::CHUNK_BYTES, &tmap_q, h * D, d.start + pr.A.m0, q_full);
-        if (pr.hasB) {
-#pragma unroll
-          for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sQ + SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_q, h * D, d.start + pr.B.m0, q_full);
-        }
-        for (int j = 0; j < pr.n_tiles; ++j, ++kv_cnt) {
+        // order of requests = order of first use: Q_A, K(0) feed S_A; Q_B feeds S_B; then V(0)
+        for (int j = 0; j < g.n_tiles; ++j, ++kv_cnt) {
           const int s = kv_cnt % KV_STAGES;
           const uint32_t par = ((kv_cnt / KV_STAGES) & 1) ^ 1;
-          const int row = d.start + pr.tile_at(j) * TILE;
+          const int row = g.start + g.tile_at(j) * TILE;
+          if (j == 0) {
+            ok = mbar_wait(wc, q_empty, (it_cnt & 1) ^ 1, 101);
+            if (!ok) break;
+            tr.mark(2);
+            mbar_arrive_expect_tx(q_full, SM::TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < SM::CHUNKS; ++c)
+              tma_load_2d(sQ + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.q_row, q_full);
+          }
           ok = mbar_wait(wc, k_empty + 8 * s, par, 102);
           if (!ok) break;
           tr.mark(3);
           mbar_arrive_expect_tx(k_full + 8 * s, SM::TILE_BYTES);
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sK + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_k, h * D, row, k_full + 8 * s);
+            tma_load_2d(sK + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_k, h * D + c * 64, row, k_full + 8 * s);
+          if (j == 0) {
+            // Q_B is requested for every item (a pair without a second tile reads rows that are
+            // never used), which keeps the barrier phases of the two Q buffers in step
+            ok = mbar_wait(wc, q_empty + 8, (it_cnt & 1) ^ 1, 104);
+            if (!ok) break;
+            mbar_arrive_expect_tx(q_full + 8, SM::TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < SM::CHUNKS; ++c)
+              tma_load_2d(sQ + SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_q, h * D + c * 64, g.q_row + TILE,
+                          q_full + 8);
+          }
           ok = mbar_wait(wc, v_empty + 8 * s, par, 103);
           if (!ok) break;
           tr.mark(4);
           mbar_arrive_expect_tx(v_full + 8 * s, SM::TILE_BYTES);
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
-            tma_load_2d(sV + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_v, h * D, row, v_full + 8 * s);
+            tma_load_2d(sV + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_v, h * D + c * 64, row, v_full + 8 * s);
+          if (j == 0) {
+            if (nidx < num_items) {
+              PairItem np;
+              fill_pair_item(np, p.g, nd.b, nd.t, nd.start, nd.len, nd.nt);
+              geom_from_pair(ng, np, nidx, p.g.delta);
+            }
+            ok = geom_publish(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng);
+            if (!ok) break;
+          }
         }
+        if (!ok) break;
+        ++it_cnt;
+        g = ng;
       }
     }
   } else if (warp == 1) {
@@ -272,8 +387,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     // All 32 lanes run the control flow and the barrier waits, so everything that feeds the MMA
     // descriptors stays warp-uniform; one elected lane issues the tcgen05 instructions.
     if ((int)blockIdx.x < num_items) {
-      const uint32_t idesc_s = make_idesc(0, 0, 0, 0, TILE, TILE);   // e4m3 x e4m3, both K-major
-      const uint32_t idesc_o = make_idesc(0, 0, 0, 1, TILE, D);      // e4m3 P (TMEM) x MN-major e4m3 V
+      const uint32_t idesc_s = make_idesc(0, 0, 0, 0, TILE, TILE);   // S = Q K^T  (e4m3, both K-major)
+      const uint32_t idesc_o = make_idesc(0, 0, 0, 1, TILE, D);      // O = P V    (e4m3, V is MN-major)
       uint32_t it_cnt = 0, kv_cnt = 0;
       uint32_t tile_cnt[2] = {0, 0};   // S/P tiles processed so far per query tile (barrier phases)
       uint32_t item_cnt[2] = {0, 0};   // items in which the query tile took part
@@ -281,8 +396,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       Tracer tr;
       tr.init(p.trace, 1, lane == 0);
 
-      // S_X = Q_X K^T for kv ring slot of global tile counter g
-      auto issue_s = [&](int X, uint32_t g) {
+      // S_X = Q_X K^T for kv ring slot of global tile counter g; `last`: Q_X has no reader left
+      auto issue_s = [&](int X, uint32_t g, bool last) {
         const int s = g % KV_STAGES;
         const uint64_t q_desc = make_smem_desc(sQ + X * SM::TILE_BYTES, 16, 1024);
         const uint64_t k_desc = make_smem_desc(sK + s * SM::TILE_BYTES, 16, 1024);
@@ -292,50 +407,67 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           for (int ks = 0; ks < D / 32; ++ks)  // 32 e4m3 = 32 bytes per step inside the 128-byte row
             mma_ss_f8(dcol, desc_advance(q_desc, ks * 32), desc_advance(k_desc, ks * 32), idesc_s, ks > 0);
           tc_commit(s_full + 8 * X);
+          if (last) tc_commit(q_empty + 8 * X);
         }
         __syncwarp();
       };
+      // a query tile that takes no part in an item (a pair without a second tile) hands its Q buffer back at once
+      auto release_q = [&](int X) {
+        if (elect_one()) tc_commit(q_empty + 8 * X);
+        __syncwarp();
+      };
 
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride, ++it_cnt) {
-        const ItemDesc d = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
-        PairItem pr;
-        fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
+      PairGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
+      bool pre_issued = false;   // the S tiles of this item's first kv tile were issued during the previous item
+      for (; ok && g.idx < num_items; ++it_cnt) {
         tr.mark(10);
-        ok = mbar_wait(wc, q_full, it_cnt & 1, 202);
-        if (!ok) break;
-        tr.mark(11);
-        const int n = pr.n_tiles;
-        int remaining[2] = {pr.A.n_tiles, pr.B.n_tiles};
+        const int n = g.n_tiles;
+        int remaining[2] = {g.a_n, g.b_n};
+        int s_left[2] = {g.a_n, g.b_n};      // S tiles of this item still to be issued per query tile
         bool started[2] = {false, false};
-        // first kv tile: both S
-        {
-          const int t0 = pr.tile_at(0);
+        if (!pre_issued) {
+          // first kv tile: both S
+          const int t0 = g.tile_at(0);
           ok = mbar_wait(wc, k_full + 8 * (kv_cnt % KV_STAGES), (kv_cnt / KV_STAGES) & 1, 201);
           if (!ok) break;
-          tc_fence_after();
-          if (pr.A.visits(t0)) issue_s(0, kv_cnt);
-          if (pr.hasB && pr.B.visits(t0)) issue_s(1, kv_cnt);
+#pragma unroll
+          for (int X = 0; X < 2; ++X) {
+            ok = mbar_wait(wc, q_full + 8 * X, it_cnt & 1, 202);
+            if (!ok) break;
+            tc_fence_after();
+            if (g.visits(X, t0)) {
+              --s_left[X];
+              issue_s(X, kv_cnt, s_left[X] == 0);
+            } else if (s_left[X] == 0) {
+              release_q(X);
+            }
+          }
+          if (!ok) break;
+          tr.mark(11);
           if (elect_one()) tc_commit(k_empty + 8 * (kv_cnt % KV_STAGES));
           __syncwarp();
+        } else {
+          // the first kv tile's S tiles were issued early: account for them
+          const int t0 = g.tile_at(0);
+          if (g.visits(0, t0)) --s_left[0];
+          if (g.visits(1, t0)) --s_left[1];
         }
+        pre_issued = false;
+        PairGeom ng;
+        ng.idx = num_items;
+        bool next_item = false;
         for (int j = 0; j < n; ++j, ++kv_cnt) {
-          const int t = pr.tile_at(j);
+          const int t = g.tile_at(j);
           const bool has_next = j + 1 < n;
-          const int tn = has_next ? pr.tile_at(j + 1) : -1;
+          const int tn = has_next ? g.tile_at(j + 1) : -1;
           const int s = kv_cnt % KV_STAGES;
           const int sn = (kv_cnt + 1) % KV_STAGES;
           bool v_ready = false, kn_ready = false;
-          if (j == n - 1) {  // every S of this item has been issued
-            if (elect_one()) tc_commit(q_empty);
-            __syncwarp();
-          }
 #pragma unroll
           for (int X = 0; X < 2; ++X) {
-            const TileItem &ti = X == 0 ? pr.A : pr.B;
-            const bool here = (X == 0 || pr.hasB) && ti.visits(t);
-            const bool next = has_next && (X == 0 || pr.hasB) && ti.visits(tn);
+            const bool here = g.visits(X, t);
+            const bool next = has_next && g.visits(X, tn);
             if (here) {
               if (!started[X]) {  // O_X of the previous item must have been read out
                 ok = mbar_wait(wc, o_empty + 8 * X, (item_cnt[X] & 1) ^ 1, 203);
@@ -352,19 +484,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 tr.mark(20);
               }
               tc_fence_after();
-              // V tile: [128 kv rows][128 bytes]; 32 kv rows per MMA = 4 KB
+              // V tile: [128 kv rows][128 bytes]; 32 kv rows per MMA = 4 KB.  Of the score region's
+              // columns, [0,16) and [64,80) hold P_hi (K steps 0-1 and 2-3), [16,32) and [80,96) P_lo.
               const uint64_t v_desc = make_smem_desc(sV + s * SM::TILE_BYTES, SM::CHUNK_BYTES, 1024);
               const uint32_t a_tmem = tmem_base + X * 128;
               const uint32_t o_tmem = tmem_base + 256 + X * 128;
               const bool last = --remaining[X] == 0;
               if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < TILE / 32; ++ks)  // P_hi: TMEM columns [0,32) of the S region
-                  mma_ts_f8(o_tmem, a_tmem + ks * 8, desc_advance(v_desc, ks * 4096), idesc_o,
+                for (int ks = 0; ks < TILE / 32; ++ks)   // P_hi
+                  mma_ts_f8(o_tmem, a_tmem + (ks / 2) * 64 + (ks % 2) * 8, desc_advance(v_desc, ks * 4096), idesc_o,
                             (started[X] || ks > 0) ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < TILE / 32; ++ks)  // P_lo: columns [32,64)
-                  mma_ts_f8(o_tmem, a_tmem + 32 + ks * 8, desc_advance(v_desc, ks * 4096), idesc_o, 1u);
+                for (int ks = 0; ks < TILE / 32; ++ks)   // P_lo
+                  mma_ts_f8(o_tmem, a_tmem + (ks / 2) * 64 + 16 + (ks % 2) * 8, desc_advance(v_desc, ks * 4096), idesc_o,
+                            1u);
                 if (last) tc_commit(o_full + 8 * X);
               }
               __syncwarp();
@@ -381,8 +515,35 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 tc_fence_after();
                 tr.mark(17);
               }
-              issue_s(X, kv_cnt + 1);
+              --s_left[X];
+              issue_s(X, kv_cnt + 1, s_left[X] == 0);
               tr.mark(18 + X);
+            }
+            if (j == n - 1) {
+              // Last kv tile: the S_X buffer is free from here on.  Take the next item (X = 0)
+              // and issue its first S_X ahead of what remains of this item, so that the
+              // activation warps find a score tile waiting when they finish this item.  Q_X of
+              // the next item was requested when this item's last S_X was issued; its first K tile
+              // goes to the ring slot after this one.
+              if (X == 0) {
+                ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng, lane == 0);
+                if (!ok) break;
+                next_item = ng.idx < num_items;
+                if (next_item) {
+                  ok = mbar_wait(wc, k_full + 8 * sn, ((kv_cnt + 1) / KV_STAGES) & 1, 210);
+                  if (!ok) break;
+                }
+              }
+              if (next_item) {
+                ok = mbar_wait(wc, q_full + 8 * X, (it_cnt + 1) & 1, 209);
+                if (!ok) break;
+                tc_fence_after();
+                const int nt0 = ng.tile_at(0);
+                const int n_x = X ? ng.b_n : ng.a_n;
+                if (ng.visits(X, nt0)) issue_s(X, kv_cnt + 1, n_x == 1);
+                else if (n_x == 0) release_q(X);
+                tr.mark(21);
+              }
             }
           }
           if (!ok) break;
@@ -395,160 +556,218 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             ok = mbar_wait(wc, k_full + 8 * sn, ((kv_cnt + 1) / KV_STAGES) & 1, 208);
             if (!ok) break;
           }
+          if (j == n - 1 && next_item) pre_issued = true;
           if (elect_one()) {
             tc_commit(v_empty + 8 * s);
-            if (has_next) tc_commit(k_empty + 8 * sn);
+            if (has_next || (j == n - 1 && next_item)) tc_commit(k_empty + 8 * sn);
           }
           __syncwarp();
         }
+        if (!ok) break;
+        g = ng;
       }
     }
-  } else {
-    // ------------------------------------------------------------------ SiLU + epilogue warps
-    const int X = warp >= 6 ? 1 : 0;           // query tile A or B
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ activation warps
+    // All eight warps work on one score tile at a time (A, then B, then A ...): the activation is
+    // bound by the MUFU rate of the whole SM, so a tile is finished soonest - and its P handed
+    // back to the tensor pipe soonest - when every warp works on it.  Warps 2-5 take columns
+    // [0,64) of the tile, warps 6-9 columns [64,128); thread = one query row.  P (16-bit) goes
+    // over the first half of the columns the thread has read itself - [0,32) or [64,96) - so the
+    // warps need no barrier among themselves.
+    const int wg = warp >= 6 ? 1 : 0;
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const uint32_t tS = tmem_base + X * 128 + lane_off;
-    const uint32_t tO = tmem_base + 256 + X * 128 + lane_off;
-    uint32_t my_tiles = 0, my_items = 0;
+    uint32_t tiles_a = 0, tiles_b = 0;   // score tiles processed so far (barrier phases)
     bool ok = true;
     Tracer tr;
-    tr.init(p.trace, 2 + X, quad == 2 && lane == 0);
+    tr.init(p.trace, 2 + wg, quad == 2 && lane == 0);
     if ((int)blockIdx.x < num_items) {
-      ItemDesc nxt = load_desc(p.items, blockIdx.x / p.H);
-      for (int idx = blockIdx.x; idx < num_items && ok; idx += stride) {
-        const ItemDesc d = nxt;
-        if (idx + stride < num_items) nxt = load_desc(p.items, (idx + stride) / p.H);
-        const int h = idx % p.H;
-        PairItem pr;
-        fill_pair_item(pr, p.g, d.b, d.t, d.start, d.len, d.nt);
-        if (X == 1 && !pr.hasB) continue;
-        const TileItem &it = X == 0 ? pr.A : pr.B;
-        const int L = it.m.L;
-        const int i = it.m0 + row_in_tile;
-        const int id_i = it.m.id(i);
-        const RowInterval ri = row_interval(it, i);
-        const bool exact_only = !it.regular;
-        // block scales: row of this sequence's first block, then one row per 128-token tile
-        const int blk0 = p.block_offsets[d.b];
-        const float sq = p.q_scale[(int64_t)(blk0 + it.mt) * p.H + h];
-        const float sv_ref = p.v_scale[(int64_t)(blk0 + it.mt) * p.H + h];
-        const float inv_sv_ref = 1.f / sv_ref;
-        float sk_next = 0.f, sv_next = 0.f;
+      PairGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
+      uint32_t item_no = 0;
+      while (ok && g.idx < num_items) {
+        const int L = g.L;
+        SeqMask m;
+        m.L = g.L; m.max_id = g.max_id; m.c = p.g.c; m.W = p.g.W; m.F = p.g.F;
+        const bool exact_only = !g.regular;
+        const int iA = g.m0 + row_in_tile, iB = g.m0 + TILE + row_in_tile;
+        RowInterval riA, riB;
         {
-          int jf = 0;
-          while (jf < pr.n_tiles && !it.visits(pr.tile_at(jf))) ++jf;
-          if (jf < pr.n_tiles) {
-            sk_next = p.k_scale[(int64_t)(blk0 + pr.tile_at(jf)) * p.H + h];
-            sv_next = p.v_scale[(int64_t)(blk0 + pr.tile_at(jf)) * p.H + h];
+          TileItem ti;   // the fields row_interval() reads
+          ti.m = m;
+          ti.u = g.u;
+          riA = row_interval(ti, iA);
+          riB = row_interval(ti, iB);
+        }
+        const int n_tiles = g.n_tiles;
+        // block scales: row of this sequence's first block, then one row per 128-token tile.  Query
+        // side once per item; the key / value side of the next kv tile is fetched while the
+        // current one is being activated.
+        const int h = g.idx % p.H;
+        const int64_t blk0 = p.block_offsets[g.b];
+        const int mtA = g.m0 / TILE;
+        const float sqA = p.q_scale[(blk0 + mtA) * p.H + h], sqB = g.has_b ? p.q_scale[(blk0 + mtA + 1) * p.H + h] : 1.f;
+        const float inv_refA = 1.f / p.v_scale[(blk0 + mtA) * p.H + h];
+        const float inv_refB = g.has_b ? 1.f / p.v_scale[(blk0 + mtA + 1) * p.H + h] : 1.f;
+        float sk_next = p.k_scale[(blk0 + g.tile_at(0)) * p.H + h], sv_next = p.v_scale[(blk0 + g.tile_at(0)) * p.H + h];
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const int t = g.tile_at(j);
+          const float sk = sk_next, sv = sv_next;
+          if (j + 1 < n_tiles) {
+            sk_next = p.k_scale[(blk0 + g.tile_at(j + 1)) * p.H + h];
+            sv_next = p.v_scale[(blk0 + g.tile_at(j + 1)) * p.H + h];
+          }
+          // the loop over the two query tiles stays rolled: one copy of the hot code
+#pragma unroll 1
+          for (int X = 0; X < 2; ++X) {
+            const bool isb = X != 0;
+            if (!g.visits(X, t)) continue;
+            const int f_lo = isb ? g.fb_lo : g.fa_lo, f_hi = isb ? g.fb_hi : g.fa_hi;
+            const bool full = !exact_only && t >= f_lo && t < f_hi;
+            const uint32_t tS = tmem_base + X * 128 + lane_off + wg * 64;   // this thread's 64 score columns
+            const int col0 = t * TILE + wg * 64;
+            const float ha = p.half_alpha * (isb ? sqB : sqA) * sk;
+            const float gain = sv * (isb ? inv_refB : inv_refA) * P_LIFT;
+            const uint32_t gain2 = to_f16x2(gain, gain);
+            uint32_t b0 = 0xffffffffu, b1 = 0xffffffffu;
+            if (!full) {
+              if (!exact_only) {
+                RowInterval ri;
+                ri.lo = isb ? riB.lo : riA.lo;
+                ri.hi = isb ? riB.hi : riA.hi;
+                ri.ctx_hi = isb ? riB.ctx_hi : riA.ctx_hi;
+                ri.self = isb ? riB.self : riA.self;
+                b0 = row_mask_bits(ri, col0, L);
+                b1 = row_mask_bits(ri, col0 + 32, L);
+              } else {
+                b0 = exact_bits(m, isb ? iB : iA, col0);
+                b1 = exact_bits(m, isb ? iB : iA, col0 + 32);
+              }
+            }
+            tr.mark(30);
+            ok = mbar_wait(wc, s_full + 8 * X, (isb ? tiles_b : tiles_a) & 1, 301);
+            if (!ok) break;
+            tc_fence_after();
+            tr.mark(31);
+            {
+              uint32_t sreg[2][32];
+              tmem_ld32(tS, sreg[0]);
+              tmem_ld32(tS + 32, sreg[1]);
+              tc_wait_ld();
+              tr.mark(32);
+              // P_hi of the thread's 64 columns -> columns [0,16) of its own score columns, P_lo ->
+              // [16,32): both lie inside the first 32 score columns, which are in registers by now
+              uint32_t hi[8], lo[8];
+              if (full) {
+                silu_chunk_fp8<false>(sreg[0], hi, lo, ha, gain2, b0);
+                tmem_st8(tS, hi);
+                tmem_st8(tS + 16, lo);
+                silu_chunk_fp8<false>(sreg[1], hi, lo, ha, gain2, b1);
+                tmem_st8(tS + 8, hi);
+                tmem_st8(tS + 24, lo);
+              } else {
+                silu_chunk_fp8<true>(sreg[0], hi, lo, ha, gain2, b0);
+                tmem_st8(tS, hi);
+                tmem_st8(tS + 16, lo);
+                silu_chunk_fp8<true>(sreg[1], hi, lo, ha, gain2, b1);
+                tmem_st8(tS + 8, hi);
+                tmem_st8(tS + 24, lo);
+              }
+            }
+            tr.mark(37);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + 8 * X);
+            tr.mark(33);
+            if (isb) ++tiles_b; else ++tiles_a;
           }
         }
-        for (int j = 0; j < pr.n_tiles; ++j) {
-          const int t = pr.tile_at(j);
-          if (!it.visits(t)) continue;
-          const int n0 = t * TILE;
-          const bool full = !exact_only && tile_pair_is_full(it, n0);
-          const float sk = sk_next, sv = sv_next;
-          {  // fetch the scales of the next kv tile this query tile visits while working on this one
-            int jn = j + 1;
-            while (jn < pr.n_tiles && !it.visits(pr.tile_at(jn))) ++jn;
-            if (jn < pr.n_tiles) {
-              sk_next = p.k_scale[(int64_t)(blk0 + pr.tile_at(jn)) * p.H + h];
-              sv_next = p.v_scale[(int64_t)(blk0 + pr.tile_at(jn)) * p.H + h];
-            }
-          }
-          const float ha = p.half_alpha * sq * sk;
-          const float gain = sv * inv_sv_ref * P_LIFT;
-          const uint32_t gain2 = to_f16x2(gain, gain);
-          tr.mark(30);
-          ok = mbar_wait(wc, s_full + 8 * X, my_tiles & 1, 301);
+        if (!ok) break;
+        ++item_no;
+        ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, item_no, g, lane == 0);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    // O (fp32, TMEM) -> scale -> 16-bit -> global; thread = one query row, valid rows only
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    uint32_t my_items[2] = {0, 0};
+    bool ok = true;
+    if ((int)blockIdx.x < num_items) {
+      PairGeom g;
+      ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, 0, g, lane == 0);
+      uint32_t item_no = 0;
+      while (ok && g.idx < num_items) {
+        const int h = g.idx % p.H;
+        const int L = g.L;
+        // V scale of each query tile's own block (the reference the activation scaled P against)
+        const int64_t blk0 = p.block_offsets[g.b];
+        float sv_ref[2];
+        sv_ref[0] = p.v_scale[(blk0 + g.m0 / TILE) * p.H + h];
+        sv_ref[1] = g.has_b ? p.v_scale[(blk0 + g.m0 / TILE + 1) * p.H + h] : 1.f;
+#pragma unroll
+        for (int X = 0; X < 2; ++X) {
+          if (X == 1 && !g.has_b) continue;
+          const int m0 = g.m0 + X * TILE;
+          const int i = m0 + row_in_tile;
+          ok = mbar_wait(wc, o_full + 8 * X, my_items[X] & 1, 302);
           if (!ok) break;
           tc_fence_after();
-          tr.mark(31);
-          {
-            uint32_t sreg[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sreg[c]);
-            tc_wait_ld();
-            tr.mark(32);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint32_t hi[8], lo[8];
-              uint32_t bits = 0xffffffffu;
-              if (!full) {
-                if (!exact_only) {
-                  bits = row_mask_bits(ri, n0 + c * 32, L);
-                } else {  // outside the closed form: evaluate the mask element by element
-                  bits = 0;
-                  for (int x = 0; x < 32; ++x) {
-                    const int jj = n0 + c * 32 + x;
-                    if (i < L && jj < L && it.m.valid_ids(i, jj, id_i, it.m.id(jj))) bits |= 1u << x;
-                  }
-                }
-              }
-              if (full)
-                silu_chunk_fp8<false>(sreg[c], hi, lo, ha, gain2, bits);
-              else
-                silu_chunk_fp8<true>(sreg[c], hi, lo, ha, gain2, bits);
-              tmem_st8(tS + c * 8, hi);
-              tmem_st8(tS + 32 + c * 8, lo);
-            }
-          }
-          tr.mark(37);
-          tc_wait_st();
-          tr.mark(38);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(p_full + 8 * X);
-          tr.mark(33);
-          ++my_tiles;
-        }
-        if (!ok) break;
-        // epilogue: O (fp32, TMEM) -> scale -> 16-bit -> global, valid rows only
-        tr.mark(34);
-        ok = mbar_wait(wc, o_full + 8 * X, my_items & 1, 302);
-        if (!ok) break;
-        tc_fence_after();
-        tr.mark(35);
-        float scale = p.inv_n;
-        if (p.attn_scale != nullptr && i < L)
-          scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)d.start + i];
-        scale *= sv_ref * (1.f / P_LIFT);
-        uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + i) * p.o_rs + (int64_t)h * p.o_hs;
-#pragma unroll
-        for (int c0 = 0; c0 < D / 32; c0 += 2) {
+          const bool row_ok = i >= 0 && i < L;
+          float scale = p.inv_n;
+          if (p.attn_scale != nullptr && row_ok)
+            scale = p.attn_scale_numel == 1 ? p.attn_scale[0] : p.attn_scale[(int64_t)g.start + i];
+          scale *= sv_ref[X] * (1.f / P_LIFT);
+          uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) +
+                           (int64_t)(g.q_row + X * TILE + row_in_tile) * p.o_rs + (int64_t)h * p.o_hs;
+          const uint32_t tO = tmem_base + 256 + X * 128 + lane_off;
           uint32_t r[2][32];
-          tmem_ld32(tO + c0 * 32, r[0]);
-          tmem_ld32(tO + c0 * 32 + 32, r[1]);
-          tc_wait_ld();
-          if (i < L) {
+          tmem_ld32(tO, r[0]);
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
+          for (int cc = 0; cc < D / 32; ++cc) {
+            tc_wait_ld();
+            if (cc + 1 < D / 32) tmem_ld32(tO + (cc + 1) * 32, r[(cc + 1) & 1]);
+            if (row_ok) {
+              const uint32_t(&v)[32] = r[cc & 1];
+              uint4 o4[4];
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
-                uint4 o4;
-                o4.x = pack2_bf16(__uint_as_float(r[cc][8 * x + 0]) * scale, __uint_as_float(r[cc][8 * x + 1]) * scale);
-                o4.y = pack2_bf16(__uint_as_float(r[cc][8 * x + 2]) * scale, __uint_as_float(r[cc][8 * x + 3]) * scale);
-                o4.z = pack2_bf16(__uint_as_float(r[cc][8 * x + 4]) * scale, __uint_as_float(r[cc][8 * x + 5]) * scale);
-                o4.w = pack2_bf16(__uint_as_float(r[cc][8 * x + 6]) * scale, __uint_as_float(r[cc][8 * x + 7]) * scale);
-                *reinterpret_cast<uint4 *>(orow + (c0 + cc) * 32 + x * 8) = o4;
+                o4[x].x = pack2_bf16(__uint_as_float(v[8 * x + 0]) * scale, __uint_as_float(v[8 * x + 1]) * scale);
+                o4[x].y = pack2_bf16(__uint_as_float(v[8 * x + 2]) * scale, __uint_as_float(v[8 * x + 3]) * scale);
+                o4[x].z = pack2_bf16(__uint_as_float(v[8 * x + 4]) * scale, __uint_as_float(v[8 * x + 5]) * scale);
+                o4[x].w = pack2_bf16(__uint_as_float(v[8 * x + 6]) * scale, __uint_as_float(v[8 * x + 7]) * scale);
+              }
+              // one row per thread: every lane of a store hits another 32-byte sector, so rows
+              // that are 32-byte aligned are written in whole sectors (256-bit stores)
+              if (p.wide_stores) {
+                st_global_256(orow + cc * 32, o4[0], o4[1]);
+                st_global_256(orow + cc * 32 + 16, o4[2], o4[3]);
+              } else {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) *reinterpret_cast<uint4 *>(orow + cc * 32 + x * 8) = o4[x];
               }
             }
           }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(o_empty + 8 * X);
-        tr.mark(36);
-        ++my_items;
-        // rows at or beyond max_seq_len of an over-long sequence come back as zeros
-        if (d.len > L && it.m0 + TILE >= L) {
-          for (int r2 = L + row_in_tile; r2 < d.len; r2 += TILE) {
-            uint16_t *zr = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(d.start + r2) * p.o_rs + (int64_t)h * p.o_hs;
-            for (int x = 0; x < D; x += 8) *reinterpret_cast<uint4 *>(zr + x) = make_uint4(0, 0, 0, 0);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_empty + 8 * X);
+          ++my_items[X];
+          // rows at or beyond max_seq_len of an over-long sequence come back as zeros
+          if (g.len > L && m0 + TILE >= L) {
+            for (int r2 = L + row_in_tile; r2 < g.len; r2 += TILE) {
+              uint16_t *zr = reinterpret_cast<uint16_t *>(p.out) + (int64_t)(g.start + r2) * p.o_rs + (int64_t)h * p.o_hs;
+              for (int x = 0; x < D; x += 8) *reinterpret_cast<uint4 *>(zr + x) = make_uint4(0, 0, 0, 0);
+            }
           }
         }
+        if (!ok) break;
+        ++item_no;
+        ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, item_no, g, lane == 0);
       }
     }
   }
@@ -621,21 +840,27 @@ int attn_tc_fwd_fp8(const b200_hstu_attn_fp8_args &fa, cudaStream_t st) {
   p.v_scale = fa.v_scale;
   p.block_offsets = fa.block_offsets;
   p.trace = nullptr;
+  p.bias_ext = nullptr;
+  p.wide_stores = (reinterpret_cast<uintptr_t>(a.out) & 31) == 0 && a.o_row_stride % 16 == 0 && a.o_head_stride % 16 == 0;
   const int max_items = (int)plan_max_items(a.total_L, a.B);
+  const int64_t upper = (int64_t)max_items * a.H;
+  const int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {
     ProfileScope prof(PROF_PLAN, st);
-    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, 0, BiasTable{nullptr, 0, nullptr, 0});
+    attn_plan_kernel<PLAN_Q_PAIR><<<1, PLAN_THREADS, 0, st>>>(p.g, hdr, items, max_items, grid, BiasTable{nullptr, 0, nullptr, 0});
   }
   count_launch();
   B200_CHECK_LAUNCH("attention plan");
   auto kern = hstu_attn_fwd_fp8_sm100_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::DYN_BYTES);
   if (e != cudaSuccess) return check_cuda(e, "fp8 forward smem attribute");
-  int64_t upper = (int64_t)max_items * a.H;
-  int grid = (int)(upper < device_sm_count() ? upper : device_sm_count());
   {
     ProfileScope prof(PROF_ATTN_FWD_FP8, st);
-    kern<<<grid, FWD_THREADS, SM::DYN_BYTES, st>>>(mq, mk, mv, p);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    fill_pdl_config(&cfg, &attr, grid, FWD_THREADS, SM::DYN_BYTES, st);
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, p);
+    if (e != cudaSuccess) return check_cuda(e, "fp8 forward launch");
   }
   count_launch();
   B200_CHECK_LAUNCH("tcgen05 fp8 attention forward");
