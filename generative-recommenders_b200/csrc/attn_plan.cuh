@@ -359,7 +359,11 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
   constexpr int TSLOTS = 16;
   constexpr int BSLOTS = PLAN_THREADS / TSLOTS;
   const int tslot = threadIdx.x % TSLOTS, bslot = threadIdx.x / TSLOTS;
+  // the cost of the first item a thread meets is kept for the second pass (batches of up to 64
+  // sequences of up to 16 units give every thread at most one item)
+  int kept_bucket = -1;
   for (int pass = 0; pass < 2; ++pass) {
+    bool first = true;
     for (int b = bslot; b < g.B; b += BSLOTS) {
       const int start = g.seq_offsets[b];
       const int len = g.seq_offsets[b + 1] - start;
@@ -368,9 +372,16 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
       const int ntiles = KIND == PLAN_KV_TILE ? (L + TILE - 1) / TILE : q_tiles_of(g, L);
       const int nunits = KIND == PLAN_Q_PAIR ? (ntiles + 1) / 2 : ntiles;
       for (int t = tslot; t < nunits; t += TSLOTS) {
-        int cost = item_cost<KIND>(g, b, t, len, nt);
-        cost = cost < PLAN_BUCKETS - 1 ? cost : PLAN_BUCKETS - 1;
-        const int bucket = PLAN_BUCKETS - 1 - cost;  // expensive first
+        int bucket;
+        if (first && pass == 1 && kept_bucket >= 0) {
+          bucket = kept_bucket;
+        } else {
+          int cost = item_cost<KIND>(g, b, t, len, nt);
+          cost = cost < PLAN_BUCKETS - 1 ? cost : PLAN_BUCKETS - 1;
+          bucket = PLAN_BUCKETS - 1 - cost;  // expensive first
+          if (first && pass == 0) kept_bucket = bucket;
+        }
+        first = false;
         if (pass == 0) {
           atomicAdd(&hist[bucket], 1);
         } else {
