@@ -640,6 +640,35 @@ def run_stages(args):
     yc = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.0, False, True, True, "none", False, 4, 128)
     res["norm_mul_bwd"] = timed("norm_mul_bwd", lambda: torch.autograd.grad(yc, (ar, ur, wr, br), dcat, retain_graph=True),
                                 rows * D * 2 * 7 + rows * 8)
+    # jagged glue: KV-cache split / concat of [rows, H*d] K rows (last 20 rows of every sequence on
+    # the right), and the timestamp + position embedding step before layer 0
+    from generative_recommenders_b200.jagged_tensors import concat_2D_jagged, split_2D_jagged
+    from generative_recommenders_b200.position import add_timestamp_positional_embeddings
+    wl = W.config4(400)
+    lengths = wl.lengths.to(dev)
+    offs = torch.cat([lengths.new_zeros(1), torch.cumsum(lengths, 0)])
+    prime_offs = torch.cat([lengths.new_zeros(1), torch.cumsum(lengths - 20, 0)])
+    n_left = rows - 20 * len(wl.lengths)
+    res["split_2D_jagged"] = timed("jagged", lambda: split_2D_jagged(0, x, n_left, rows - n_left, None, 20, prime_offs, None),
+                                   rows * D * 2 * 2)
+    left, right = split_2D_jagged(0, x, n_left, rows - n_left, None, 20, prime_offs, None)
+    res["concat_2D_jagged"] = timed("jagged", lambda: concat_2D_jagged(0, left, right, None, 20, prime_offs, None),
+                                    rows * D * 2 * 2)
+    pos_w = torch.randn(16384 + 1, D, device=dev) * 0.1
+    ts_w = torch.randn(2048 + 1, D, device=dev) * 0.1
+    gaps = (torch.rand(rows, generator=g) * 12).exp().long().to(dev)
+    stamps = torch.cumsum(gaps, 0)  # increasing inside every sequence
+    nt = wl.num_targets.to(dev)
+    xe = x.clone().requires_grad_(True)
+    pw = pos_w.clone().requires_grad_(True)
+    tw = ts_w.clone().requires_grad_(True)
+    emb = lambda a, p_, t_: add_timestamp_positional_embeddings(  # noqa: E731
+        D ** 0.5, 16384, 0, p_, t_, offs, lengths, a, stamps, nt, False, "sqrt")
+    with torch.no_grad():
+        res["add_timestamp_positional_embeddings_fwd"] = timed("ts_pos", lambda: emb(x, pos_w, ts_w), rows * D * 2 * 2)
+    ye = emb(xe, pw, tw)
+    res["add_timestamp_positional_embeddings_bwd"] = timed(
+        "ts_pos", lambda: torch.autograd.grad(ye, (xe, pw, tw), dy, retain_graph=True), rows * D * 2 * 2)
     out = {"metric": "hstu_stage_hbm_gb_per_s", "value": res["norm_mul_fwd"]["gb_per_s"], "unit": "GB/s", "n_gpus": 1,
            "steps": args.steps, "warmup": 3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
            "config": {"workload": "stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2)" % (rows, rows * D * 2 / 1e6)},

@@ -11,8 +11,10 @@ from .hstu_compute import (
     hstu_norm_mul_dropout,
     hstu_preprocess_and_attention,
 )
+from .jagged_tensors import concat_2D_jagged, split_2D_jagged
 from .layer_norm import layer_norm
 from .mm import addmm
+from .position import add_timestamp_positional_embeddings
 from .stu import STULayer, STULayerConfig, STUStack
 
 __all__ = [
@@ -26,6 +28,9 @@ __all__ = [
     "hstu_norm_mul_dropout",
     "hstu_preprocess_and_attention",
     "layer_norm",
+    "concat_2D_jagged",
+    "split_2D_jagged",
+    "add_timestamp_positional_embeddings",
     "addmm",
     "STULayer",
     "STULayerConfig",

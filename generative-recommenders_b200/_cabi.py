@@ -30,6 +30,10 @@ EXPORTS = [
     "b200_hstu_norm_mul_fwd",
     "b200_hstu_norm_mul_bwd",
     "b200_hstu_norm_mul_bwd_workspace_bytes",
+    "b200_hstu_concat_2d_jagged",
+    "b200_hstu_split_2d_jagged",
+    "b200_hstu_add_timestamp_positional_embeddings_fwd",
+    "b200_hstu_add_timestamp_positional_embeddings_bwd",
     "b200_hstu_last_error",
     "b200_hstu_version",
     "b200_hstu_launch_count",
@@ -90,6 +94,34 @@ class NormMulArgs(Structure):
     ]
 
 
+class JaggedArgs(Structure):
+    _fields_ = [
+        ("left", c_void_p), ("right", c_void_p), ("combined", c_void_p),
+        ("offsets_left", c_void_p), ("offsets_right", c_void_p),
+        ("dense_len_left", c_int64), ("dense_len_right", c_int64),
+        ("total_rows", c_int64), ("row_bytes", c_int64),
+        ("B", c_int32), ("reserved0", c_int32),
+    ]
+
+
+class TsPosArgs(Structure):
+    _fields_ = [
+        ("seq_embeddings", c_void_p), ("pos_weight", c_void_p), ("ts_weight", c_void_p),
+        ("out", c_void_p),
+        ("d_out", c_void_p), ("d_seq_embeddings", c_void_p),
+        ("d_pos_weight", c_void_p), ("d_ts_weight", c_void_p),
+        ("seq_offsets", c_void_p), ("seq_lengths", c_void_p), ("num_targets", c_void_p), ("timestamps", c_void_p),
+        ("total_rows", c_int64),
+        ("B", c_int32), ("D", c_int32),
+        ("max_contextual_seq_len", c_int32), ("max_pos_ind", c_int32), ("ts_rows", c_int32),
+        ("ts_bucket_max", c_int32),
+        ("interleave_targets", c_int32), ("time_bucket_fn", c_int32),
+        ("alpha", c_float),
+        ("dtype", c_int32), ("table_dtype", c_int32),
+        ("reserved0", c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -145,6 +177,11 @@ def lib():
     L.b200_hstu_norm_mul_bwd.restype = ctypes.c_int
     L.b200_hstu_norm_mul_bwd_workspace_bytes.argtypes = [c_int32, c_int32, c_int32]
     L.b200_hstu_norm_mul_bwd_workspace_bytes.restype = c_int64
+    for name, struct in (("b200_hstu_concat_2d_jagged", JaggedArgs), ("b200_hstu_split_2d_jagged", JaggedArgs),
+                         ("b200_hstu_add_timestamp_positional_embeddings_fwd", TsPosArgs),
+                         ("b200_hstu_add_timestamp_positional_embeddings_bwd", TsPosArgs)):
+        getattr(L, name).argtypes = [POINTER(struct), c_void_p]
+        getattr(L, name).restype = ctypes.c_int
     L.b200_hstu_last_error.argtypes = []
     L.b200_hstu_last_error.restype = c_char_p
     L.b200_hstu_version.restype = ctypes.c_int
@@ -180,6 +217,7 @@ def launch_count():
 PROFILE_KINDS = {
     "plan": 0, "attn_fwd": 1, "attn_bwd_dkdv": 2, "attn_bwd_dq": 3, "attn_fwd_fp8": 4, "layer_norm_fwd": 5,
     "layer_norm_bwd": 6, "silu": 7, "norm_mul_fwd": 8, "norm_mul_bwd": 9, "quantize": 10, "attn_simt": 11,
+    "jagged": 12, "ts_pos": 13,
 }
 
 

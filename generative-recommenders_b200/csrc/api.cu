@@ -77,6 +77,9 @@ int layer_norm_bwd(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, c
                    const float *rstd, void *dx, int64_t dx_rs, void *dw, void *db, void *partial,
                    int64_t partial_bytes, int64_t rows, int D, int dtype, cudaStream_t st);
 int64_t stage_bwd_workspace_bytes(int cols);
+int jagged_concat_split(const b200_hstu_jagged_args &j, bool split, cudaStream_t st);
+int ts_pos_fwd(const b200_hstu_ts_pos_args &p, cudaStream_t st);
+int ts_pos_bwd(const b200_hstu_ts_pos_args &p, cudaStream_t st);
 int silu_launch(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out, int64_t out_rs, int64_t rows,
                 int width, bool bwd, int dtype, cudaStream_t st);
 int norm_mul(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st);
@@ -196,6 +199,23 @@ int b200_hstu_layer_norm_bwd(const void *dy, int64_t dy_row_stride, const void *
 }
 
 int64_t b200_hstu_layer_norm_bwd_workspace_bytes(int32_t D) { return stage_bwd_workspace_bytes(D); }
+
+int b200_hstu_concat_2d_jagged(const b200_hstu_jagged_args *args, b200_hstu_stream_t stream) {
+  if (!args) return fail(B200_HSTU_EINVAL, "concat_2D_jagged: NULL args");
+  return jagged_concat_split(*args, false, (cudaStream_t)stream);
+}
+int b200_hstu_split_2d_jagged(const b200_hstu_jagged_args *args, b200_hstu_stream_t stream) {
+  if (!args) return fail(B200_HSTU_EINVAL, "split_2D_jagged: NULL args");
+  return jagged_concat_split(*args, true, (cudaStream_t)stream);
+}
+int b200_hstu_add_timestamp_positional_embeddings_fwd(const b200_hstu_ts_pos_args *args, b200_hstu_stream_t stream) {
+  if (!args) return fail(B200_HSTU_EINVAL, "add_timestamp_positional_embeddings: NULL args");
+  return ts_pos_fwd(*args, (cudaStream_t)stream);
+}
+int b200_hstu_add_timestamp_positional_embeddings_bwd(const b200_hstu_ts_pos_args *args, b200_hstu_stream_t stream) {
+  if (!args) return fail(B200_HSTU_EINVAL, "add_timestamp_positional_embeddings: NULL args");
+  return ts_pos_bwd(*args, (cudaStream_t)stream);
+}
 
 int b200_hstu_silu_fwd(const void *x, int64_t x_row_stride, void *y, int64_t y_row_stride, int64_t rows,
                        int32_t width, int32_t dtype, b200_hstu_stream_t stream) {

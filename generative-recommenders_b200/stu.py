@@ -3,8 +3,11 @@
 Mirrors ``STULayer`` / ``STUStack`` of the reference
 (generative_recommenders/modules/stu.py:65-81, 176-356, 427-456): same configuration fields, same
 parameter names, shapes and initialisation, so a reference checkpoint loads with
-``load_state_dict``.  The KV-cache path of the reference layer (``cached_forward``,
-``update_kv_cache``) is not part of this module.
+``load_state_dict``.  The KV-cache path of the reference layer (``update_kv_cache``,
+``construct_full_kv``, ``cached_forward``; stu.py:84-173, 253-296, 358-424) is here too: a forward
+with ``kv_caching_lengths`` keeps the first ``kv_caching_lengths[b]`` rows of K and V of every
+sequence (a jagged split), ``cached_forward`` appends the new rows' K and V (a jagged concat) and
+runs ``delta_hstu_mha`` for the new rows only.
 
 One extension: ``rel_bias_table`` (``num_buckets + 1`` learnable entries, indexed by
 ``clamp(floor(ln(max(|i - j|, 1)) / 0.301), 0, num_buckets)`` of the position distance) adds the
@@ -19,7 +22,9 @@ from typing import List, Optional
 import torch
 
 from .common import HammerKernel
-from .hstu_compute import hstu_compute_output, hstu_preprocess_and_attention
+from .hstu_attention import delta_hstu_mha
+from .hstu_compute import hstu_compute_output, hstu_compute_uqvk, hstu_preprocess_and_attention
+from .jagged_tensors import concat_2D_jagged, split_2D_jagged
 
 
 @dataclass
@@ -83,6 +88,120 @@ class STULayer(torch.nn.Module):
                 torch.empty(config.rel_bias_buckets + 1).normal_(mean=0, std=0.02))
         else:
             self._rel_bias_table = None
+        self.reset_kv_cache()
+
+    def reset_kv_cache(self) -> None:
+        self.k_cache: Optional[torch.Tensor] = None
+        self.v_cache: Optional[torch.Tensor] = None
+        self.kv_caching_offsets: Optional[torch.Tensor] = None
+        self.max_kv_caching_len: int = 0
+
+    def update_kv_cache(
+        self,
+        max_seq_len: int,
+        seq_offsets: torch.Tensor,
+        k: Optional[torch.Tensor],
+        v: Optional[torch.Tensor],
+        max_kv_caching_len: int,
+        kv_caching_lengths: Optional[torch.Tensor],
+    ) -> None:
+        """Keep the first ``kv_caching_lengths[b]`` rows of K and V of every sequence (reference
+        ``_update_kv_cache``, stu.py:84-134); without ``kv_caching_lengths`` the cache stays."""
+        if kv_caching_lengths is None:
+            return
+        lengths = kv_caching_lengths.to(torch.int64)
+        offsets = torch.zeros(lengths.numel() + 1, dtype=torch.int64, device=lengths.device)
+        torch.cumsum(lengths, 0, out=offsets[1:])
+        delta_offsets = seq_offsets.to(torch.int64) - offsets
+        self.k_cache, _ = split_2D_jagged(max_seq_len=max_seq_len, values=k.flatten(1, 2), offsets_left=offsets,
+                                          offsets_right=delta_offsets, kernel=self._hammer_kernel)
+        self.v_cache, _ = split_2D_jagged(max_seq_len=max_seq_len, values=v.flatten(1, 2), offsets_left=offsets,
+                                          offsets_right=delta_offsets, kernel=self._hammer_kernel)
+        if max_kv_caching_len == 0:
+            max_kv_caching_len = int(lengths.max().item())
+        self.max_kv_caching_len = max_kv_caching_len
+        self.kv_caching_offsets = offsets
+
+    def construct_full_kv(self, delta_k: torch.Tensor, delta_v: torch.Tensor):
+        """Cached K / V of every sequence followed by its ``delta_size`` new rows (reference
+        ``_construct_full_kv``, stu.py:137-173); returns ``(k, v, max_seq_len, seq_offsets)``."""
+        if self.k_cache is None or self.v_cache is None or self.kv_caching_offsets is None:
+            raise RuntimeError("cached_forward needs a KV cache: run forward() with kv_caching_lengths first")
+        L = delta_k.shape[0]
+        B = self.kv_caching_offsets.numel() - 1
+        delta_size = L // B
+        full = []
+        for cache, delta in ((self.k_cache, delta_k), (self.v_cache, delta_v)):
+            full.append(concat_2D_jagged(max_seq_len=self.max_kv_caching_len + delta_size, values_left=cache,
+                                         values_right=delta, max_len_left=self.max_kv_caching_len,
+                                         max_len_right=delta_size, offsets_left=self.kv_caching_offsets,
+                                         offsets_right=None, kernel=self._hammer_kernel))
+        offsets = self.kv_caching_offsets + delta_size * torch.arange(B + 1, device=delta_k.device)
+        return full[0], full[1], self.max_kv_caching_len + delta_size, offsets
+
+    def cached_forward(
+        self,
+        delta_x: torch.Tensor,
+        num_targets: torch.Tensor,
+        max_kv_caching_len: int = 0,
+        kv_caching_lengths: Optional[torch.Tensor] = None,
+    ) -> torch.Tensor:
+        """The layer on the last ``delta_size`` rows of every sequence against the cached K / V
+        (reference stu.py:358-424); ``delta_x`` is ``[B * delta_size, D]``."""
+        if self._rel_bias_table is not None:
+            raise NotImplementedError("cached_forward with a relative bias table")
+        with torch.autograd.profiler.record_function("## stu_compute_uqvk ##"):
+            delta_u, delta_q, delta_k, delta_v = hstu_compute_uqvk(
+                x=delta_x,
+                norm_weight=self._input_norm_weight.to(delta_x.dtype),
+                norm_bias=self._input_norm_bias.to(delta_x.dtype),
+                norm_eps=1e-6,
+                num_heads=self._num_heads,
+                attn_dim=self._attention_dim,
+                hidden_dim=self._hidden_dim,
+                uvqk_weight=self._uvqk_weight.to(delta_x.dtype),
+                uvqk_bias=self._uvqk_beta.to(delta_x.dtype),
+                kernel=self._hammer_kernel,
+            )
+        k, v, max_seq_len, seq_offsets = self.construct_full_kv(
+            delta_k=delta_k.flatten(1, 2), delta_v=delta_v.flatten(1, 2))
+        k = k.view(-1, self._num_heads, self._attention_dim)
+        v = v.view(-1, self._num_heads, self._hidden_dim)
+        self.update_kv_cache(max_seq_len=max_seq_len, seq_offsets=seq_offsets, k=k, v=v,
+                             max_kv_caching_len=max_kv_caching_len, kv_caching_lengths=kv_caching_lengths)
+        with torch.autograd.profiler.record_function("## delta_hstu_mha ##"):
+            delta_attn_output = delta_hstu_mha(
+                max_seq_len=max_seq_len,
+                alpha=self._attn_alpha,
+                delta_q=delta_q,
+                k=k,
+                v=v,
+                seq_offsets=seq_offsets,
+                num_targets=num_targets if self._target_aware else None,
+                max_attn_len=self._max_attn_len,
+                contextual_seq_len=self._contextual_seq_len,
+                kernel=self._hammer_kernel,
+            ).view(-1, self._hidden_dim * self._num_heads)
+        with torch.autograd.profiler.record_function("## stu_compute_output ##"):
+            return hstu_compute_output(
+                attn=delta_attn_output,
+                u=delta_u,
+                x=delta_x,
+                norm_weight=self._output_norm_weight.to(delta_x.dtype),
+                norm_bias=self._output_norm_bias.to(delta_x.dtype),
+                norm_eps=1e-6,
+                dropout_ratio=self._output_dropout_ratio,
+                output_weight=self._output_weight.to(delta_x.dtype),
+                group_norm=self._use_group_norm,
+                num_heads=self._num_heads,
+                linear_dim=self._hidden_dim,
+                concat_u=True,
+                concat_x=True,
+                mul_u_activation_type="none",
+                training=self.training,
+                kernel=self._hammer_kernel,
+                recompute_y_in_backward=False,
+            )
 
     def forward(
         self,
@@ -94,13 +213,11 @@ class STULayer(torch.nn.Module):
         max_kv_caching_len: int = 0,
         kv_caching_lengths: Optional[torch.Tensor] = None,
     ) -> torch.Tensor:
-        if kv_caching_lengths is not None:
-            raise NotImplementedError("KV caching is not part of this module")
         bias = None
         if self._rel_bias_table is not None:
             bias = position_bias_by_distance(self._rel_bias_table.detach(), max_seq_len)
         with torch.autograd.profiler.record_function("## stu_preprocess_and_attention ##"):
-            u, attn_output, _, _ = hstu_preprocess_and_attention(
+            u, attn_output, k, v = hstu_preprocess_and_attention(
                 x=x,
                 norm_weight=self._input_norm_weight.to(x.dtype),
                 norm_bias=self._input_norm_bias.to(x.dtype),
@@ -123,6 +240,8 @@ class STULayer(torch.nn.Module):
                 kernel=self._hammer_kernel,
                 bias_by_distance=bias,
             )
+        self.update_kv_cache(max_seq_len=max_seq_len, seq_offsets=x_offsets, k=k, v=v,
+                             max_kv_caching_len=max_kv_caching_len, kv_caching_lengths=kv_caching_lengths)
         with torch.autograd.profiler.record_function("## stu_compute_output ##"):
             return hstu_compute_output(
                 attn=attn_output,
@@ -166,3 +285,16 @@ class STUStack(torch.nn.Module):
                       num_targets=num_targets, max_kv_caching_len=max_kv_caching_len,
                       kv_caching_lengths=kv_caching_lengths)
         return x
+
+    def cached_forward(
+        self,
+        delta_x: torch.Tensor,
+        num_targets: torch.Tensor,
+        max_kv_caching_len: int = 0,
+        kv_caching_lengths: Optional[torch.Tensor] = None,
+    ) -> torch.Tensor:
+        for layer in self._stu_layers:
+            delta_x = layer.cached_forward(delta_x=delta_x, num_targets=num_targets,
+                                           max_kv_caching_len=max_kv_caching_len,
+                                           kv_caching_lengths=kv_caching_lengths)
+        return delta_x

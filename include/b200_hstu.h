@@ -219,13 +219,65 @@ int b200_hstu_norm_mul_bwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream
 int64_t b200_hstu_norm_mul_bwd_workspace_bytes(int32_t H, int32_t V, int32_t group_norm);
 
 /*
+ * concat_2D_jagged / split_2D_jagged (generative_recommenders/ops/jagged_tensors.py:55-162;
+ * semantics of ops/pytorch/pt_jagged_tensors.py:32-160): sequence b of `combined` holds the rows
+ * of `left` for b followed by the rows of `right` for b.  Rows are `row_bytes` bytes and
+ * contiguous in all three tensors.  A side without offsets (NULL) is dense: every sequence has
+ * dense_len_* rows there.  total_rows = rows of `combined`.  concat reads left/right and writes
+ * combined; split reads combined and writes left/right.  Offsets are int64 device arrays [B + 1].
+ * Each is the other's backward.
+ */
+typedef struct b200_hstu_jagged_args {
+  void *left, *right, *combined;
+  const int64_t *offsets_left, *offsets_right;
+  int64_t dense_len_left, dense_len_right;
+  int64_t total_rows;
+  int64_t row_bytes;
+  int32_t B;
+  int32_t reserved0;
+} b200_hstu_jagged_args;
+int b200_hstu_concat_2d_jagged(const b200_hstu_jagged_args *args, b200_hstu_stream_t stream);
+int b200_hstu_split_2d_jagged(const b200_hstu_jagged_args *args, b200_hstu_stream_t stream);
+
+/*
+ * add_timestamp_positional_embeddings (generative_recommenders/ops/position.py:40-118; semantics
+ * of ops/pytorch/pt_position.py:40-160):
+ *   out[t] = alpha * seq_embeddings[t] + (ts_weight[bucket(t)] + pos_weight[index(t)])
+ * with index(t) counted back from the end of the history (targets share one index; the first
+ * max_contextual_seq_len rows use their own position) and bucket(t) = sqrt or log of the time to
+ * the sequence's last item in minutes, clamped to [0, ts_bucket_max] (the reference clamps to
+ * ts_weight.size(1) - 1) and to the table.  Index tensors are int64 device arrays; tables are
+ * [max_pos_ind, D] / [ts_rows, D], float32 or of the sequence dtype.  The backward writes
+ * d_seq_embeddings = alpha * d_out and ADDS the table gradients into the caller-zeroed fp32
+ * buffers d_pos_weight / d_ts_weight.  time_bucket_fn: 0 sqrt, 1 log.
+ */
+typedef struct b200_hstu_ts_pos_args {
+  const void *seq_embeddings, *pos_weight, *ts_weight;
+  void *out;
+  const void *d_out;       /* bwd */
+  void *d_seq_embeddings;  /* bwd */
+  float *d_pos_weight, *d_ts_weight; /* bwd, fp32, accumulated into */
+  const int64_t *seq_offsets, *seq_lengths, *num_targets, *timestamps;
+  int64_t total_rows;
+  int32_t B, D;
+  int32_t max_contextual_seq_len, max_pos_ind, ts_rows, ts_bucket_max;
+  int32_t interleave_targets, time_bucket_fn;
+  float alpha;
+  int32_t dtype, table_dtype;
+  int32_t reserved0;
+} b200_hstu_ts_pos_args;
+int b200_hstu_add_timestamp_positional_embeddings_fwd(const b200_hstu_ts_pos_args *args, b200_hstu_stream_t stream);
+int b200_hstu_add_timestamp_positional_embeddings_bwd(const b200_hstu_ts_pos_args *args, b200_hstu_stream_t stream);
+
+/*
  * Optional per-kernel timing for benchmarks.  After b200_hstu_profile_enable(1) every launch of a
  * hot kernel is bracketed by a cudaEvent pair on its launch stream; once the caller has
  * synchronised the device, b200_hstu_profile_collect(kind, out_ms, max_n) writes up to max_n
  * durations (milliseconds, oldest first, at most the 512 most recent launches since the last
  * enable) and returns how many.  Kinds: 0 work-list planning, 1 attention forward, 2 backward
  * dK/dV, 3 backward dQ, 4 fp8 forward, 5 layer_norm forward, 6 layer_norm backward, 7 SiLU
- * gating, 8 norm_mul forward, 9 norm_mul backward, 10 e4m3 quantiser, 11 CUDA-core attention.
+ * gating, 8 norm_mul forward, 9 norm_mul backward, 10 e4m3 quantiser, 11 CUDA-core attention,
+ * 12 jagged concat / split, 13 timestamp + position embeddings.
  * Enabling resets the counters; b200_hstu_profile_enable(0) turns the events off again.
  */
 void b200_hstu_profile_enable(int on);

@@ -368,6 +368,111 @@ def stu_layer(
 
 
 # --------------------------------------------------------------------------------------
+# jagged glue around the layer
+# --------------------------------------------------------------------------------------
+def _side_offsets(offsets: Optional[torch.Tensor], dense_len: Optional[int], B: int) -> torch.Tensor:
+    if offsets is not None:
+        return offsets.to(torch.int64)
+    return int(dense_len) * torch.arange(B + 1, dtype=torch.int64)
+
+
+def concat_2D_jagged(
+    values_left: torch.Tensor,
+    values_right: torch.Tensor,
+    max_len_left: Optional[int] = None,
+    max_len_right: Optional[int] = None,
+    offsets_left: Optional[torch.Tensor] = None,
+    offsets_right: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Per sequence: rows of the left tensor, then rows of the right tensor
+    (generative_recommenders/ops/pytorch/pt_jagged_tensors.py:32-113; a side without offsets has
+    ``max_len_*`` rows per sequence, :70-87).  Walks the sequences instead of padding."""
+    if offsets_left is not None:
+        B = offsets_left.numel() - 1
+    elif offsets_right is not None:
+        B = offsets_right.numel() - 1
+    else:
+        B = values_left.shape[0] // int(max_len_left)
+    ol = _side_offsets(offsets_left, max_len_left, B)
+    orr = _side_offsets(offsets_right, max_len_right, B)
+    rows = []
+    for b in range(B):
+        rows.append(values_left[int(ol[b]):int(ol[b + 1])])
+        rows.append(values_right[int(orr[b]):int(orr[b + 1])])
+    return torch.cat(rows, 0) if rows else values_left.new_zeros((0, values_left.shape[1]))
+
+
+def split_2D_jagged(
+    values: torch.Tensor,
+    max_len_left: Optional[int] = None,
+    max_len_right: Optional[int] = None,
+    offsets_left: Optional[torch.Tensor] = None,
+    offsets_right: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Inverse of :func:`concat_2D_jagged`
+    (generative_recommenders/ops/pytorch/pt_jagged_tensors.py:116-160)."""
+    B = (offsets_left if offsets_left is not None else offsets_right).numel() - 1
+    ol = _side_offsets(offsets_left, max_len_left, B)
+    orr = _side_offsets(offsets_right, max_len_right, B)
+    left, right = [], []
+    for b in range(B):
+        s = int(ol[b] + orr[b])
+        nl = int(ol[b + 1] - ol[b])
+        nr = int(orr[b + 1] - orr[b])
+        left.append(values[s:s + nl])
+        right.append(values[s + nl:s + nl + nr])
+    return torch.cat(left, 0), torch.cat(right, 0)
+
+
+def add_timestamp_positional_embeddings(
+    alpha: float,
+    max_contextual_seq_len: int,
+    pos_weight: torch.Tensor,
+    ts_weight: torch.Tensor,
+    seq_offsets: torch.Tensor,
+    seq_lengths: torch.Tensor,
+    seq_embeddings: torch.Tensor,
+    timestamps: torch.Tensor,
+    num_targets: Optional[torch.Tensor],
+    interleave_targets: bool,
+    time_bucket_fn: str = "sqrt",
+) -> torch.Tensor:
+    """``alpha * x + (ts_weight[bucket] + pos_weight[index]).to(x.dtype)`` token by token
+    (generative_recommenders/ops/position.py:71 for the scaling;
+    ops/pytorch/pt_position.py:40-73 for the position index, :96-125 for the time bucket, which the
+    reference clamps to ``ts_weight.size(1) - 1``, :98)."""
+    max_pos_ind = pos_weight.shape[0]
+    num_time_buckets = ts_weight.shape[1] - 1
+    x = seq_embeddings * alpha
+    out = torch.empty_like(x)
+    B = seq_lengths.numel()
+    for b in range(B):
+        start = int(seq_offsets[b])
+        n = int(seq_lengths[b])
+        rows = int(seq_offsets[b + 1]) - start
+        if rows == 0:
+            continue
+        p = torch.arange(rows, dtype=torch.int64)
+        if num_targets is not None:
+            high = n - int(num_targets[b]) * (2 if interleave_targets else 1)
+            idx = high - torch.clamp(p, max=high)
+        else:
+            idx = n - p
+        idx = torch.clamp(idx + max_contextual_seq_len, max=max_pos_ind - 1)
+        if max_contextual_seq_len > 0:
+            head = p < max_contextual_seq_len
+            idx = torch.where(head, p, idx)
+        ts = timestamps[start:start + rows]
+        query_time = ts[max(n - 1, 0)]
+        dt = (query_time - ts).clamp(min=1e-6) / 60.0
+        dt = torch.log(dt) if time_bucket_fn == "log" else torch.sqrt(dt)
+        bucket = torch.clamp(dt.clamp(min=0).int(), min=0, max=num_time_buckets).to(torch.int64)
+        emb = ts_weight[bucket] + pos_weight[idx]
+        out[start:start + rows] = x[start:start + rows] + emb.to(x.dtype)
+    return out
+
+
+# --------------------------------------------------------------------------------------
 # relative position bias (research layer)
 # --------------------------------------------------------------------------------------
 def bucketized_position_bias(table: torch.Tensor, N: int) -> torch.Tensor:

@@ -244,24 +244,143 @@ def make_bias():
     return dict(N=N, ts_w=mod._ts_w.detach().clone(), timestamps=ts, rab=rab[0].clone())
 
 
+def make_jagged(gr):
+    """concat_2D_jagged / split_2D_jagged and add_timestamp_positional_embeddings of the reference's
+    PyTorch implementations."""
+    from generative_recommenders.ops.pytorch.pt_jagged_tensors import (
+        pytorch_concat_2D_jagged,
+        pytorch_split_2D_jagged,
+    )
+    from generative_recommenders.ops.position import add_timestamp_positional_embeddings
+    from generative_recommenders.common import HammerKernel
+
+    g = torch.Generator().manual_seed(4242)
+    fx = dict(concat=[], split=[], ts_pos=[])
+    B, D = 6, 24
+    for kind in ("jagged_jagged", "dense_right", "dense_left", "with_empty"):
+        ll = torch.randint(0 if kind == "with_empty" else 1, 9, (B,), generator=g)
+        lr = torch.randint(0 if kind == "with_empty" else 1, 7, (B,), generator=g)
+        max_l, max_r = 9, 7
+        if kind == "dense_right":
+            lr = torch.full((B,), 4); max_r = 4
+        if kind == "dense_left":
+            ll = torch.full((B,), 3); max_l = 3
+        ol, orr = _offsets(ll), _offsets(lr)
+        left = torch.randn(int(ol[-1]), D, generator=g)
+        right = torch.randn(int(orr[-1]), D, generator=g)
+        kw = dict(max_len_left=max_l, max_len_right=max_r,
+                  offsets_left=None if kind == "dense_left" else ol,
+                  offsets_right=None if kind == "dense_right" else orr)
+        out = pytorch_concat_2D_jagged(values_left=left, values_right=right, **kw)
+        fx["concat"].append(dict(kind=kind, left=left, right=right, out=out, **kw))
+        sl, sr = pytorch_split_2D_jagged(max_seq_len=max_l + max_r, values=out, **kw)
+        fx["split"].append(dict(kind=kind, values=out, left=sl, right=sr, **kw))
+    for i, (targets, interleave, fn, ctx, dtype) in enumerate([
+            (False, False, "sqrt", 0, torch.float32), (True, False, "sqrt", 0, torch.float32),
+            (True, True, "sqrt", 0, torch.float32), (True, False, "log", 3, torch.float32),
+            (False, False, "log", 2, torch.float32), (True, False, "sqrt", 3, torch.bfloat16)]):
+        B, D, N = 5, 32, 40
+        nt = torch.randint(1, 4, (B,), generator=g)
+        lengths = torch.randint(2, 20, (B,), generator=g) + nt * (2 if interleave else 1) + ctx
+        if not targets:
+            # without num_targets the reference indexes the position table with seq_length - column for
+            # every padded column, which is negative past the end of a sequence: only full-length
+            # sequences run there
+            lengths = torch.full((B,), N)
+        offsets = _offsets(lengths)
+        total = int(offsets[-1])
+        x = torch.randn(total, D, generator=g).to(dtype)
+        # increasing timestamps per sequence, gaps from seconds to weeks
+        gaps = (torch.rand(total, generator=g) * 12).exp().long()
+        ts = torch.cat([torch.cumsum(gaps[int(offsets[b]):int(offsets[b + 1])], 0) + 1_700_000_000 for b in range(B)])
+        pos_w = torch.randn(N + ctx + 1, D, generator=g) * 0.3
+        ts_w = torch.randn(D + 17, D, generator=g) * 0.3  # the reference clamps buckets to size(1) - 1
+        out = add_timestamp_positional_embeddings(
+            alpha=D ** 0.5, max_seq_len=N, max_contextual_seq_len=ctx, position_embeddings_weight=pos_w,
+            timestamp_embeddings_weight=ts_w, seq_offsets=offsets, seq_lengths=lengths, seq_embeddings=x,
+            timestamps=ts, num_targets=nt if targets else None, interleave_targets=interleave,
+            time_bucket_fn=fn, kernel=HammerKernel.PYTORCH)
+        fx["ts_pos"].append(dict(alpha=D ** 0.5, N=N, ctx=ctx, pos_w=pos_w, ts_w=ts_w, seq_offsets=offsets,
+                                 seq_lengths=lengths, x=x, timestamps=ts, num_targets=nt if targets else None,
+                                 interleave=interleave, fn=fn, out=out))
+    return fx
+
+
+def make_cached_layer(gr):
+    """STUStack.forward with kv_caching_lengths followed by cached_forward on the last delta rows
+    (the flow of the reference's own test, modules/tests/stu_test.py:324-453), PyTorch kernels."""
+    from generative_recommenders.modules.stu import STULayer, STULayerConfig, STUStack
+    from generative_recommenders.common import HammerKernel
+    from generative_recommenders.ops.pytorch.pt_jagged_tensors import pytorch_split_2D_jagged
+
+    torch.manual_seed(777)
+    g = torch.Generator().manual_seed(777)
+    out = []
+    for ctx in (0, 3):
+        cfg = STULayerConfig(embedding_dim=32, num_heads=2, hidden_dim=16, attention_dim=16,
+                             output_dropout_ratio=0.0, causal=True, target_aware=True, max_attn_len=None,
+                             attn_alpha=None, use_group_norm=False, recompute_normed_x=False,
+                             recompute_uvqk=False, recompute_y=False, sort_by_length=False,
+                             contextual_seq_len=ctx)
+        stack = STUStack([STULayer(cfg, is_inference=True), STULayer(cfg, is_inference=True)], is_inference=True)
+        stack.recursive_setattr("_hammer_kernel", HammerKernel.PYTORCH)
+        stack.eval()
+        for p_ in stack.parameters():
+            if p_.dim() == 1:
+                p_.data.add_(torch.randn(p_.shape, generator=g) * 0.1)
+        B, delta = 4, 5
+        num_targets = torch.randint(delta, 2 * delta + 1, (B,), generator=g)
+        lengths = torch.randint(4, 30, (B,), generator=g) + num_targets + ctx
+        N = 30 + 2 * delta + ctx
+        offsets = _offsets(lengths)
+        x = torch.randn(int(offsets[-1]), 32, generator=g)
+        with torch.inference_mode():
+            ref_y = stack(x=x, x_lengths=lengths, x_offsets=offsets, max_seq_len=N, num_targets=num_targets)
+            prime_lengths = lengths - delta
+            prime_offsets = _offsets(prime_lengths)
+            _, ref_delta_y = pytorch_split_2D_jagged(max_seq_len=N, values=ref_y, max_len_left=None,
+                                                     max_len_right=delta, offsets_left=prime_offsets,
+                                                     offsets_right=None)
+            prime_x, delta_x = pytorch_split_2D_jagged(max_seq_len=N, values=x, max_len_left=None,
+                                                       max_len_right=delta, offsets_left=prime_offsets,
+                                                       offsets_right=None)
+            stack(x=prime_x, x_lengths=prime_lengths, x_offsets=prime_offsets, max_seq_len=N,
+                  num_targets=num_targets - delta, max_kv_caching_len=N - delta,
+                  kv_caching_lengths=lengths - delta)
+            delta_y = stack.cached_forward(delta_x=delta_x, num_targets=num_targets)
+        out.append(dict(ctx=ctx, H=2, A=16, V=16, D=32, N=N, delta=delta,
+                        state={k_: v_.detach().clone() for k_, v_ in stack.state_dict().items()},
+                        lengths=lengths, seq_offsets=offsets, num_targets=num_targets, x=x,
+                        full_y=ref_y.clone(), full_delta_y=ref_delta_y.clone(), cached_delta_y=delta_y.clone()))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
+    ap.add_argument("--only", default="", help="comma-separated fixture names to (re)generate; default all")
     args = ap.parse_args()
+    only = set(filter(None, args.only.split(",")))
     gr = reference_shims.import_reference(args.reference)
     from generative_recommenders.ops.pytorch import pt_hstu_attention as ref_ops
 
     torch.set_num_threads(4)
-    attn = {}
-    for name, p in attention_cases():
-        attn[name] = make_attention(ref_ops, name, p)
-        print("attention", name, tuple(attn[name]["q"].shape))
-    torch.save(attn, os.path.join(HERE, "attention.pt"))
-    torch.save(make_masks(ref_ops), os.path.join(HERE, "masks.pt"))
-    torch.save(make_stages(gr), os.path.join(HERE, "stages.pt"))
-    torch.save(make_layer(gr), os.path.join(HERE, "stu_layer.pt"))
-    torch.save(make_delta(ref_ops), os.path.join(HERE, "delta_attention.pt"))
-    torch.save(make_bias(), os.path.join(HERE, "rel_bias.pt"))
+
+    def want(name):
+        return not only or name in only
+
+    if want("attention"):
+        attn = {}
+        for name, p in attention_cases():
+            attn[name] = make_attention(ref_ops, name, p)
+            print("attention", name, tuple(attn[name]["q"].shape))
+        torch.save(attn, os.path.join(HERE, "attention.pt"))
+    for name, fn in (("masks", lambda: make_masks(ref_ops)), ("stages", lambda: make_stages(gr)),
+                     ("stu_layer", lambda: make_layer(gr)), ("delta_attention", lambda: make_delta(ref_ops)),
+                     ("rel_bias", make_bias), ("jagged", lambda: make_jagged(gr)),
+                     ("stu_cached", lambda: make_cached_layer(gr))):
+        if want(name):
+            torch.save(fn(), os.path.join(HERE, name + ".pt"))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".pt"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

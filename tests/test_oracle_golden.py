@@ -124,3 +124,46 @@ def test_fp8_block_quant_roundtrip():
     assert boffs.tolist() == [0, 1, 1, 4, 6] and sc.shape == (6, 2)
     xd = O.dequantize_e4m3_block(xq, sc, boffs, off)
     assert O.rel_l2(xd, x) < 0.04
+
+
+def test_jagged_concat_split_match_reference(golden):
+    fx = golden("jagged.pt")
+    assert len(fx["concat"]) == 4 and len(fx["split"]) == 4
+    for c in fx["concat"]:
+        out = O.concat_2D_jagged(c["left"], c["right"], c["max_len_left"], c["max_len_right"], c["offsets_left"],
+                                 c["offsets_right"])
+        assert torch.equal(out, c["out"]), c["kind"]
+    for c in fx["split"]:
+        left, right = O.split_2D_jagged(c["values"], c["max_len_left"], c["max_len_right"], c["offsets_left"],
+                                        c["offsets_right"])
+        assert torch.equal(left, c["left"]) and torch.equal(right, c["right"]), c["kind"]
+
+
+def test_timestamp_positional_embeddings_match_reference(golden):
+    cases = golden("jagged.pt")["ts_pos"]
+    assert len(cases) == 6
+    for c in cases:
+        out = O.add_timestamp_positional_embeddings(
+            c["alpha"], c["ctx"], c["pos_w"], c["ts_w"], c["seq_offsets"], c["seq_lengths"], c["x"],
+            c["timestamps"], c["num_targets"], c["interleave"], c["fn"])
+        assert torch.equal(out, c["out"]), (c["fn"], c["ctx"], c["interleave"])
+
+
+def test_cached_layer_fixture_is_consistent(golden):
+    """The reference's cached forward reproduces the last rows of its full forward, and the oracle's
+    full forward reproduces both."""
+    for c in golden("stu_cached.pt"):
+        torch.testing.assert_close(c["cached_delta_y"], c["full_delta_y"], rtol=1e-4, atol=1e-5)
+        h = c["x"]
+        for layer in range(2):
+            pre = "_stu_layers.%d._" % layer
+            params = {n: c["state"][pre + n] for n in ("input_norm_weight", "input_norm_bias", "uvqk_weight",
+                                                        "uvqk_beta", "output_norm_weight", "output_norm_bias",
+                                                        "output_weight")}
+            h = O.stu_layer(h, c["seq_offsets"], c["N"], c["num_targets"], params, c["H"], c["A"], c["V"],
+                            contextual_seq_len=c["ctx"])
+        torch.testing.assert_close(h, c["full_y"], rtol=1e-4, atol=1e-5)
+        prime = c["seq_offsets"][1:] - c["seq_offsets"][:-1] - c["delta"]
+        off = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(prime, 0)])
+        _, tail = O.split_2D_jagged(h, None, c["delta"], off, None)
+        torch.testing.assert_close(tail, c["cached_delta_y"], rtol=1e-4, atol=1e-5)
