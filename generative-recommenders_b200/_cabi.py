@@ -30,6 +30,9 @@ EXPORTS = [
     "b200_hstu_norm_mul_fwd",
     "b200_hstu_norm_mul_bwd",
     "b200_hstu_norm_mul_bwd_workspace_bytes",
+    "b200_hstu_ln_linear_silu_fwd",
+    "b200_hstu_ln_linear_workspace_bytes",
+    "b200_hstu_ln_linear_supported",
     "b200_hstu_concat_2d_jagged",
     "b200_hstu_split_2d_jagged",
     "b200_hstu_add_timestamp_positional_embeddings_fwd",
@@ -91,6 +94,20 @@ class NormMulArgs(Structure):
         ("concat_u", c_int32), ("concat_x", c_int32), ("act", c_int32), ("group_norm", c_int32),
         ("eps", c_float),
         ("dtype", c_int32),
+    ]
+
+
+class LnLinearArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("norm_weight", c_void_p), ("norm_bias", c_void_p), ("weight", c_void_p), ("bias", c_void_p),
+        ("out", c_void_p), ("u", c_void_p),
+        ("mean", c_void_p), ("rstd", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
+        ("x_row_stride", c_int64), ("out_row_stride", c_int64), ("u_row_stride", c_int64),
+        ("M", c_int64),
+        ("D", c_int32), ("N", c_int32), ("silu_cols", c_int32),
+        ("eps", c_float),
+        ("dtype", c_int32), ("reserved0", c_int32),
     ]
 
 
@@ -182,6 +199,12 @@ def lib():
                          ("b200_hstu_add_timestamp_positional_embeddings_bwd", TsPosArgs)):
         getattr(L, name).argtypes = [POINTER(struct), c_void_p]
         getattr(L, name).restype = ctypes.c_int
+    L.b200_hstu_ln_linear_silu_fwd.argtypes = [POINTER(LnLinearArgs), c_void_p]
+    L.b200_hstu_ln_linear_silu_fwd.restype = ctypes.c_int
+    L.b200_hstu_ln_linear_workspace_bytes.argtypes = [c_int32, c_int32]
+    L.b200_hstu_ln_linear_workspace_bytes.restype = c_int64
+    L.b200_hstu_ln_linear_supported.argtypes = [c_int32] * 4
+    L.b200_hstu_ln_linear_supported.restype = ctypes.c_int
     L.b200_hstu_last_error.argtypes = []
     L.b200_hstu_last_error.restype = c_char_p
     L.b200_hstu_version.restype = ctypes.c_int
@@ -217,7 +240,7 @@ def launch_count():
 PROFILE_KINDS = {
     "plan": 0, "attn_fwd": 1, "attn_bwd_dkdv": 2, "attn_bwd_dq": 3, "attn_fwd_fp8": 4, "layer_norm_fwd": 5,
     "layer_norm_bwd": 6, "silu": 7, "norm_mul_fwd": 8, "norm_mul_bwd": 9, "quantize": 10, "attn_simt": 11,
-    "jagged": 12, "ts_pos": 13,
+    "jagged": 12, "ts_pos": 13, "ln_linear_prep": 14, "ln_linear": 15,
 }
 
 

@@ -80,6 +80,9 @@ int64_t stage_bwd_workspace_bytes(int cols);
 int jagged_concat_split(const b200_hstu_jagged_args &j, bool split, cudaStream_t st);
 int ts_pos_fwd(const b200_hstu_ts_pos_args &p, cudaStream_t st);
 int ts_pos_bwd(const b200_hstu_ts_pos_args &p, cudaStream_t st);
+int ln_linear_fwd(const b200_hstu_ln_linear_args &a, cudaStream_t st);
+int64_t ln_linear_workspace_bytes(int D, int N);
+bool ln_linear_supported(int D, int N, int silu_cols, int dtype, const char **why);
 int silu_launch(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out, int64_t out_rs, int64_t rows,
                 int width, bool bwd, int dtype, cudaStream_t st);
 int norm_mul(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st);
@@ -199,6 +202,19 @@ int b200_hstu_layer_norm_bwd(const void *dy, int64_t dy_row_stride, const void *
 }
 
 int64_t b200_hstu_layer_norm_bwd_workspace_bytes(int32_t D) { return stage_bwd_workspace_bytes(D); }
+
+int b200_hstu_ln_linear_silu_fwd(const b200_hstu_ln_linear_args *args, b200_hstu_stream_t stream) {
+  if (!args) return fail(B200_HSTU_EINVAL, "ln_linear: NULL args");
+  return ln_linear_fwd(*args, (cudaStream_t)stream);
+}
+int64_t b200_hstu_ln_linear_workspace_bytes(int32_t D, int32_t N) {
+  if (D <= 0 || N <= 0) return 0;
+  return ln_linear_workspace_bytes(D, N);
+}
+int b200_hstu_ln_linear_supported(int32_t D, int32_t N, int32_t silu_cols, int32_t dtype) {
+  const char *why = "";
+  return ln_linear_supported(D, N, silu_cols, dtype, &why) ? 1 : 0;
+}
 
 int b200_hstu_concat_2d_jagged(const b200_hstu_jagged_args *args, b200_hstu_stream_t stream) {
   if (!args) return fail(B200_HSTU_EINVAL, "concat_2D_jagged: NULL args");

@@ -28,7 +28,8 @@ inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_
 enum ProfileKind {
   PROF_PLAN = 0, PROF_ATTN_FWD = 1, PROF_ATTN_BWD_DKDV = 2, PROF_ATTN_BWD_DQ = 3, PROF_ATTN_FWD_FP8 = 4,
   PROF_LN_FWD = 5, PROF_LN_BWD = 6, PROF_SILU = 7, PROF_NORM_MUL_FWD = 8, PROF_NORM_MUL_BWD = 9,
-  PROF_QUANT = 10, PROF_ATTN_SIMT = 11, PROF_JAGGED = 12, PROF_TS_POS = 13, PROF_KINDS = 14
+  PROF_QUANT = 10, PROF_ATTN_SIMT = 11, PROF_JAGGED = 12, PROF_TS_POS = 13,
+  PROF_LN_LINEAR_PREP = 14, PROF_LN_LINEAR = 15, PROF_KINDS = 16
 };
 struct ProfileScope {
   int kind;

@@ -48,6 +48,107 @@ class _SiluColumnsFunction(torch.autograd.Function):
         return dx, None
 
 
+def _fused_uqvk_supported(x, uvqk_weight, hv) -> bool:
+    if x.dtype not in (torch.bfloat16, torch.float16) or x.dim() != 2 or x.shape[0] == 0:
+        return False
+    if x.stride(-1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        return False
+    D, N = uvqk_weight.shape
+    return bool(_cabi.lib().b200_hstu_ln_linear_supported(D, N, hv, dtype_code(x)))
+
+
+class _FusedUqvkFunction(torch.autograd.Function):
+    """``uvqk = LN(x) W + b`` and ``u = SiLU(uvqk[:, :hv])`` from one tensor-core kernel
+    (csrc/ln_linear_sm100.cu).  The backward recomputes ``LN(x)`` from the saved row statistics
+    (the reference's ``recompute_normed_x_in_backward``,
+    generative_recommenders/ops/triton/triton_hstu_preprocess_and_attention.py:122-127, 185-203) and
+    uses library GEMMs for the two weight / input products."""
+
+    @staticmethod
+    def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, hv):
+        M, D = x.shape
+        N = weight.shape[1]
+        nw = norm_weight.to(x.dtype).contiguous()
+        nb = norm_bias.to(x.dtype).contiguous()
+        w = weight.to(x.dtype).contiguous()
+        b = bias.to(x.dtype).contiguous()
+        uvqk = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        u = torch.empty((M, hv), dtype=x.dtype, device=x.device)
+        mean = torch.empty(M, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+        nbytes = _cabi.lib().b200_hstu_ln_linear_workspace_bytes(D, N)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        a = _cabi.LnLinearArgs()
+        a.x, a.norm_weight, a.norm_bias, a.weight, a.bias = (x.data_ptr(), nw.data_ptr(), nb.data_ptr(),
+                                                              w.data_ptr(), b.data_ptr())
+        a.out, a.u, a.mean, a.rstd = uvqk.data_ptr(), u.data_ptr(), mean.data_ptr(), rstd.data_ptr()
+        a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+        a.x_row_stride, a.out_row_stride, a.u_row_stride = x.stride(0), uvqk.stride(0), u.stride(0)
+        a.M, a.D, a.N, a.silu_cols = M, D, N, hv
+        a.eps, a.dtype = eps, dtype_code(x)
+        with torch.cuda.device(x.device):
+            _cabi.check(_cabi.lib().b200_hstu_ln_linear_silu_fwd(a, stream_ptr(x.device)),
+                        "b200_hstu_ln_linear_silu_fwd")
+        ctx.save_for_backward(x, nw, nb, w, uvqk, mean, rstd)
+        ctx.cfg = (eps, hv, norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
+        ctx.mark_non_differentiable(mean, rstd)
+        return uvqk, u, mean, rstd
+
+    @staticmethod
+    def backward(ctx, d_uvqk, du, _dmean, _drstd):
+        x, nw, nb, w, uvqk, mean, rstd = ctx.saved_tensors
+        eps, hv, nw_dtype, nb_dtype, w_dtype, b_dtype = ctx.cfg
+        M, D = x.shape
+        N = w.shape[1]
+        lib = _cabi.lib()
+        dt = dtype_code(x)
+        st = stream_ptr(x.device)
+        if d_uvqk is None:
+            d_uvqk = torch.zeros((M, N), dtype=x.dtype, device=x.device)
+        elif not d_uvqk.is_contiguous():
+            d_uvqk = d_uvqk.contiguous()
+        else:
+            d_uvqk = d_uvqk.clone()
+        with torch.cuda.device(x.device):
+            if du is not None:
+                if du.stride(-1) != 1:
+                    du = du.contiguous()
+                # d(pre-activation u) = du * SiLU'(uvqk[:, :hv]), written over the unused u columns
+                _cabi.check(lib.b200_hstu_silu_bwd(du.data_ptr(), du.stride(0), uvqk.data_ptr(), uvqk.stride(0),
+                                                   d_uvqk.data_ptr(), d_uvqk.stride(0), M, hv, dt, st),
+                            "b200_hstu_silu_bwd")
+            else:
+                d_uvqk[:, :hv].zero_()
+            normed = torch.empty_like(x)
+            _cabi.check(lib.b200_hstu_layer_norm_fwd(x.data_ptr(), x.stride(0), nw.data_ptr(), nb.data_ptr(),
+                                                     normed.data_ptr(), normed.stride(0), None, None, M, D, eps, dt, st),
+                        "b200_hstu_layer_norm_fwd")
+            dw = normed.t() @ d_uvqk
+            db = d_uvqk.sum(0)
+            dnormed = d_uvqk @ w.t()
+            dx = torch.empty_like(x)
+            dnw = torch.empty(D, dtype=x.dtype, device=x.device)
+            dnb = torch.empty(D, dtype=x.dtype, device=x.device)
+            nbytes = lib.b200_hstu_layer_norm_bwd_workspace_bytes(D)
+            partial = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+            _cabi.check(lib.b200_hstu_layer_norm_bwd(dnormed.data_ptr(), dnormed.stride(0), x.data_ptr(), x.stride(0),
+                                                     nw.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                                     dx.stride(0), dnw.data_ptr(), dnb.data_ptr(), partial.data_ptr(),
+                                                     nbytes, M, D, dt, st),
+                        "b200_hstu_layer_norm_bwd")
+        return dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None
+
+
+_FUSED_UQVK = True
+
+
+def set_fused_uqvk(on: bool) -> None:
+    """Switch between the fused tensor-core uvqk stage (default, where the shapes allow it) and the
+    three separate stages (LayerNorm kernel, library GEMM, SiLU kernel)."""
+    global _FUSED_UQVK
+    _FUSED_UQVK = bool(on)
+
+
 def hstu_compute_uqvk(
     x: torch.Tensor,
     norm_weight: torch.Tensor,
@@ -64,10 +165,13 @@ def hstu_compute_uqvk(
     ``[L, H, d]`` views of the uvqk buffer (generative_recommenders/ops/hstu_compute.py:54-104)."""
     _require_cuda_backend(kernel)
     require_cuda(x, norm_weight, norm_bias, uvqk_weight, uvqk_bias)
-    normed_x = layer_norm(x, weight=norm_weight, bias=norm_bias, eps=norm_eps, kernel=kernel)
-    uvqk = addmm(uvqk_bias, normed_x, uvqk_weight, kernel)
     hv, ha = hidden_dim * num_heads, attn_dim * num_heads
-    u = _SiluColumnsFunction.apply(uvqk[:, :hv], hv)
+    if _FUSED_UQVK and _fused_uqvk_supported(x, uvqk_weight, hv):
+        uvqk, u, _, _ = _FusedUqvkFunction.apply(x, norm_weight, norm_bias, float(norm_eps), uvqk_weight, uvqk_bias, hv)
+    else:
+        normed_x = layer_norm(x, weight=norm_weight, bias=norm_bias, eps=norm_eps, kernel=kernel)
+        uvqk = addmm(uvqk_bias, normed_x, uvqk_weight, kernel)
+        u = _SiluColumnsFunction.apply(uvqk[:, :hv], hv)
     v = uvqk[:, hv : 2 * hv].view(-1, num_heads, hidden_dim)
     q = uvqk[:, 2 * hv : 2 * hv + ha].view(-1, num_heads, attn_dim)
     k = uvqk[:, 2 * hv + ha :].view(-1, num_heads, attn_dim)

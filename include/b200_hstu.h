@@ -219,6 +219,36 @@ int b200_hstu_norm_mul_bwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream
 int64_t b200_hstu_norm_mul_bwd_workspace_bytes(int32_t H, int32_t V, int32_t group_norm);
 
 /*
+ * The uvqk stage as one tensor-core kernel (generative_recommenders/ops/hstu_compute.py:54-104:
+ * layer_norm -> addmm -> split -> silu):
+ *   out = LayerNorm(x; norm_weight, norm_bias, eps) * weight + bias      [M, N]
+ *   u   = SiLU(out[:, :silu_cols])                                       [M, silu_cols]  (if u != NULL)
+ * x [M, D], weight [D, N] row-major and contiguous, bias [N] (may be NULL), all of `dtype` (bf16 or
+ * f16).  mean / rstd (fp32 [M], may be NULL) receive the row statistics for the backward.
+ * Supported: D a multiple of 64 up to 512, N a multiple of 64, silu_cols a multiple of 32,
+ * 16-byte aligned tensors and row strides (b200_hstu_ln_linear_supported() tells; other shapes
+ * return B200_HSTU_EUNSUPPORTED and the caller runs the three separate stages).  Row strides in
+ * elements.  workspace: b200_hstu_ln_linear_workspace_bytes(D, N) bytes, contents need no
+ * initialisation.
+ */
+typedef struct b200_hstu_ln_linear_args {
+  const void *x, *norm_weight, *norm_bias, *weight, *bias;
+  void *out, *u;
+  float *mean, *rstd;
+  void *workspace;
+  int64_t workspace_bytes;
+  int64_t x_row_stride, out_row_stride, u_row_stride;
+  int64_t M;
+  int32_t D, N, silu_cols;
+  float eps;
+  int32_t dtype;
+  int32_t reserved0;
+} b200_hstu_ln_linear_args;
+int b200_hstu_ln_linear_silu_fwd(const b200_hstu_ln_linear_args *args, b200_hstu_stream_t stream);
+int64_t b200_hstu_ln_linear_workspace_bytes(int32_t D, int32_t N);
+int b200_hstu_ln_linear_supported(int32_t D, int32_t N, int32_t silu_cols, int32_t dtype);
+
+/*
  * concat_2D_jagged / split_2D_jagged (generative_recommenders/ops/jagged_tensors.py:55-162;
  * semantics of ops/pytorch/pt_jagged_tensors.py:32-160): sequence b of `combined` holds the rows
  * of `left` for b followed by the rows of `right` for b.  Rows are `row_bytes` bytes and
@@ -277,7 +307,8 @@ int b200_hstu_add_timestamp_positional_embeddings_bwd(const b200_hstu_ts_pos_arg
  * enable) and returns how many.  Kinds: 0 work-list planning, 1 attention forward, 2 backward
  * dK/dV, 3 backward dQ, 4 fp8 forward, 5 layer_norm forward, 6 layer_norm backward, 7 SiLU
  * gating, 8 norm_mul forward, 9 norm_mul backward, 10 e4m3 quantiser, 11 CUDA-core attention,
- * 12 jagged concat / split, 13 timestamp + position embeddings.
+ * 12 jagged concat / split, 13 timestamp + position embeddings, 14 preparation of the fused uvqk
+ * stage, 15 fused uvqk stage.
  * Enabling resets the counters; b200_hstu_profile_enable(0) turns the events off again.
  */
 void b200_hstu_profile_enable(int on);

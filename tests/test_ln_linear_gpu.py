@@ -1,0 +1,94 @@
+"""The fused uvqk stage (LayerNorm -> linear -> split -> SiLU as one tcgen05 kernel) against the
+oracle's fp32 evaluation and against the three separate stages."""
+
+import importlib
+
+import pytest
+import torch
+
+from oracle import hstu_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+G = importlib.import_module("generative-recommenders_b200")
+HC = importlib.import_module("generative-recommenders_b200.hstu_compute")
+DEV = "cuda"
+
+
+def _inputs(M, D, H, A, V, dtype, seed, shift=0.0):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(M, D, generator=g) * 1.5 + shift).to(dtype)
+    nw = (1.0 + 0.2 * torch.randn(D, generator=g)).to(dtype)
+    nb = (0.1 * torch.randn(D, generator=g)).to(dtype)
+    N = (2 * V + 2 * A) * H
+    W = (torch.randn(D, N, generator=g) / D ** 0.5).to(dtype)
+    b = (0.1 * torch.randn(N, generator=g)).to(dtype)
+    return x, nw, nb, W, b
+
+
+@pytest.mark.parametrize("M,D,H,A,V", [(1, 64, 2, 16, 16), (127, 64, 2, 32, 32), (128, 128, 2, 64, 64),
+                                       (300, 256, 4, 64, 64), (1000, 512, 4, 128, 128), (333, 512, 2, 128, 96),
+                                       (4500, 256, 4, 128, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_uqvk_matches_oracle(M, D, H, A, V, dtype):
+    x, nw, nb, W, b = _inputs(M, D, H, A, V, dtype, seed=M + D)
+    ref = O.hstu_compute_uqvk(x.float(), nw.float(), nb.float(), 1e-6, H, A, V, W.float(), b.float())
+    HC.set_fused_uqvk(True)
+    assert HC._fused_uqvk_supported(x.to(DEV), W.to(DEV), V * H)
+    n0 = G._cabi.launch_count()
+    got = G.hstu_compute_uqvk(x.to(DEV), nw.to(DEV), nb.to(DEV), 1e-6, H, A, V, W.to(DEV), b.to(DEV))
+    assert G._cabi.launch_count() - n0 == 2  # preparation + fused kernel
+    for name, a, r in zip("uqkv", got, ref):
+        assert a.shape == r.shape
+        assert O.rel_l2(a.float().cpu(), r) < 1e-2, name
+    HC.set_fused_uqvk(False)
+    sep = G.hstu_compute_uqvk(x.to(DEV), nw.to(DEV), nb.to(DEV), 1e-6, H, A, V, W.to(DEV), b.to(DEV))
+    HC.set_fused_uqvk(True)
+    for name, a, r_, r in zip("uqkv", got, sep, ref):
+        # the fused kernel multiplies the exact rows of x: it is at least as close to fp32 as the
+        # separate stages, which round LN(x) to 16 bits first
+        assert O.rel_l2(a.float().cpu(), r) <= 1.2 * O.rel_l2(r_.float().cpu(), r) + 1e-4, name
+
+
+def test_fused_uqvk_large_mean_rows():
+    """Rows with |mean| >> std: the statistics use shifted sums, the epilogue subtracts mean * c1."""
+    x, nw, nb, W, b = _inputs(500, 256, 2, 64, 64, torch.bfloat16, seed=9, shift=40.0)
+    ref = O.hstu_compute_uqvk(x.float(), nw.float(), nb.float(), 1e-6, 2, 64, 64, W.float(), b.float())
+    got = G.hstu_compute_uqvk(x.to(DEV), nw.to(DEV), nb.to(DEV), 1e-6, 2, 64, 64, W.to(DEV), b.to(DEV))
+    for a, r in zip(got, ref):
+        assert O.rel_l2(a.float().cpu(), r) < 2e-2
+
+
+def test_fused_uqvk_gradients_match_separate_stages():
+    M, D, H, A, V = 700, 256, 2, 64, 64
+    x, nw, nb, W, b = _inputs(M, D, H, A, V, torch.bfloat16, seed=4)
+    g = torch.Generator().manual_seed(1)
+    grads = [torch.randn(M, V * H, generator=g), torch.randn(M, H, A, generator=g), torch.randn(M, H, A, generator=g),
+             torch.randn(M, H, V, generator=g)]
+    res = {}
+    for fused in (True, False):
+        HC.set_fused_uqvk(fused)
+        leaves = [t.to(DEV).requires_grad_(True) for t in (x, nw, nb, W, b)]
+        outs = G.hstu_compute_uqvk(leaves[0], leaves[1], leaves[2], 1e-6, H, A, V, leaves[3], leaves[4])
+        torch.autograd.backward(list(outs), [t.to(DEV).to(torch.bfloat16) for t in grads])
+        res[fused] = [t.grad.float().cpu() for t in leaves]
+    HC.set_fused_uqvk(True)
+    # fp32 reference through the oracle
+    leaves = [t.float().requires_grad_(True) for t in (x, nw, nb, W, b)]
+    outs = O.hstu_compute_uqvk(leaves[0], leaves[1], leaves[2], 1e-6, H, A, V, leaves[3], leaves[4])
+    torch.autograd.backward(list(outs), [t.to(torch.bfloat16).float() for t in grads])
+    for name, a, s_, r in zip(("dx", "dnw", "dnb", "dW", "db"), res[True], res[False], leaves):
+        assert O.rel_l2(a, r.grad) < 2e-2, name
+        assert O.rel_l2(a, s_) < 2e-2, name
+
+
+def test_fused_uqvk_unsupported_shapes_take_the_separate_stages():
+    x, nw, nb, W, b = _inputs(50, 32, 2, 16, 16, torch.bfloat16, seed=2)   # D = 32
+    assert not HC._fused_uqvk_supported(x.to(DEV), W.to(DEV), 32)
+    ref = O.hstu_compute_uqvk(x.float(), nw.float(), nb.float(), 1e-6, 2, 16, 16, W.float(), b.float())
+    got = G.hstu_compute_uqvk(x.to(DEV), nw.to(DEV), nb.to(DEV), 1e-6, 2, 16, 16, W.to(DEV), b.to(DEV))
+    for a, r in zip(got, ref):
+        assert O.rel_l2(a.float().cpu(), r) < 1e-2
+    a = G._cabi.LnLinearArgs()
+    a.D, a.N, a.M, a.dtype = 32, 128, 4, G._cabi.BF16
+    assert G._cabi.lib().b200_hstu_ln_linear_silu_fwd(a, None) == -2
