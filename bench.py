@@ -669,6 +669,46 @@ def run_stages(args):
     ye = emb(xe, pw, tw)
     res["add_timestamp_positional_embeddings_bwd"] = timed(
         "ts_pos", lambda: torch.autograd.grad(ye, (xe, pw, tw), dy, retain_graph=True), rows * D * 2 * 2)
+    # the uvqk stage: one fused tensor-core kernel against LayerNorm kernel + library GEMM + SiLU kernel
+    from generative_recommenders_b200 import hstu_compute as HC
+    H_, d_ = 4, 128
+    Wu = (torch.randn(D, 4 * H_ * d_, generator=g) / D ** 0.5).to(torch.bfloat16).to(dev)
+    bu = mk(4 * H_ * d_)
+    uq_rows = int(W.config1().total_tokens)
+    xs = x[:uq_rows]
+    uq = {}
+    for name, fused in (("fused", True), ("separate", False)):
+        HC.set_fused_uqvk(fused)
+        with torch.no_grad():
+            fn = lambda: G.hstu_compute_uqvk(xs, w_, b_, 1e-6, H_, d_, d_, Wu, bu)  # noqa: E731
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(20)]
+            for s_, e_ in ev:
+                s_.record()
+                fn()
+                e_.record()
+            torch.cuda.synchronize()
+        ms = sorted(s_.elapsed_time(e_) for s_, e_ in ev)[10]
+        uq[name] = {"ms": round(ms, 4), "tflops": round(2.0 * uq_rows * D * Wu.shape[1] / (ms * 1e-3) / 1e12, 1)}
+    HC.set_fused_uqvk(True)
+    _cabi.profile_enable(True)
+    with torch.no_grad():
+        for _ in range(10):
+            G.hstu_compute_uqvk(xs, w_, b_, 1e-6, H_, d_, d_, Wu, bu)
+    torch.cuda.synchronize()
+    kk = _cabi.profile_collect("ln_linear")
+    kp = _cabi.profile_collect("ln_linear_prep")
+    _cabi.profile_enable(False)
+    kms = sorted(kk)[len(kk) // 2]
+    uq["fused"]["kernel_ms"] = round(kms, 4)
+    uq["fused"]["prep_ms"] = round(sorted(kp)[len(kp) // 2], 4)
+    uq["fused"]["kernel_tflops"] = round(2.0 * uq_rows * D * Wu.shape[1] / (kms * 1e-3) / 1e12, 1)
+    uq["fused"]["kernel_frac_of_bf16_peak"] = round(uq["fused"]["kernel_tflops"] / peaks["bf16_tflops"], 3)
+    uq["rows"] = uq_rows
+    uq["shape"] = "x [%d, %d] -> uvqk [%d, %d], u [%d, %d]" % (uq_rows, D, uq_rows, Wu.shape[1], uq_rows, H_ * d_)
+    res["uvqk_stage"] = uq
     out = {"metric": "hstu_stage_hbm_gb_per_s", "value": res["norm_mul_fwd"]["gb_per_s"], "unit": "GB/s", "n_gpus": 1,
            "steps": args.steps, "warmup": 3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
            "config": {"workload": "stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2)" % (rows, rows * D * 2 / 1e6)},

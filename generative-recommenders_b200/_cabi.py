@@ -107,7 +107,7 @@ class LnLinearArgs(Structure):
         ("M", c_int64),
         ("D", c_int32), ("N", c_int32), ("silu_cols", c_int32),
         ("eps", c_float),
-        ("dtype", c_int32), ("reserved0", c_int32),
+        ("dtype", c_int32), ("weights_prepared", c_int32),
     ]
 
 

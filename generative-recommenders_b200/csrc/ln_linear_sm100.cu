@@ -47,7 +47,7 @@ constexpr int LL_B_BOX = LL_KC * 128; // bytes of one W' box (64 k x 64 n)
 constexpr int LL_B_STAGE = 4 * LL_B_BOX;
 constexpr int LL_MAX_STAGES = 4;
 constexpr int LL_MAX_KC = 8;          // D <= 512
-constexpr int LL_MISC = 1024;         // barriers, TMEM slot, abort flag
+constexpr int LL_MISC = 2048;         // barriers, TMEM slot, abort flag | per-warp c1 / c2 staging
 constexpr int LL_SMEM_LIMIT = 232448;
 
 struct LLParams {
@@ -83,24 +83,35 @@ template <bool IS_BF16> __device__ __forceinline__ float2 unpack2(uint32_t w) {
 
 // ---------------------------------------------------------------------------------------
 // preparation: W' = gamma (.) W, c1 = column sums of W', c2 = beta W + bias
-// grid: N / 32 CTAs of 256 threads; thread (kg = tid / 32, col = tid % 32) covers rows kg, kg + 8, ...
+// grid: N / 32 CTAs of 512 threads; thread (kg = tid / 32, col = tid % 32) covers rows kg, kg + 16, ...
 // ---------------------------------------------------------------------------------------
 template <typename E>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 ln_linear_prep_kernel(const E *__restrict__ W, const E *__restrict__ gamma, const E *__restrict__ beta,
                       const E *__restrict__ bias, E *__restrict__ Wp, float *__restrict__ c1, float *__restrict__ c2,
                       int *status, int D, int N) {
-  __shared__ float s1[8][32], s2[8][32];
+  __shared__ float s1[16][32], s2[16][32];
   const int col = blockIdx.x * 32 + (threadIdx.x & 31);
   const int kg = threadIdx.x >> 5;
   float a1 = 0.f, a2 = 0.f;
   if (col < N) {
-    for (int k = kg; k < D; k += 8) {
-      const float w = to_f32(W[(int64_t)k * N + col]);
-      const E wp = from_f32<E>(w * to_f32(gamma[k]));
-      Wp[(int64_t)k * N + col] = wp;
-      a1 += to_f32(wp);
-      a2 = fmaf(to_f32(beta[k]), w, a2);
+    for (int k0 = kg; k0 < D; k0 += 16 * 8) {
+      float w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int k = k0 + 16 * i;
+        w[i] = k < D ? to_f32(W[(int64_t)k * N + col]) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int k = k0 + 16 * i;
+        if (k < D) {
+          const E wp = from_f32<E>(w[i] * to_f32(gamma[k]));
+          Wp[(int64_t)k * N + col] = wp;
+          a1 += to_f32(wp);
+          a2 = fmaf(to_f32(beta[k]), w[i], a2);
+        }
+      }
     }
   }
   s1[kg][threadIdx.x & 31] = a1;
@@ -109,7 +120,7 @@ ln_linear_prep_kernel(const E *__restrict__ W, const E *__restrict__ gamma, cons
   if (kg == 0 && col < N) {
     float t1 = 0.f, t2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 16; ++i) {
       t1 += s1[i][threadIdx.x];
       t2 += s2[i][threadIdx.x];
     }
@@ -142,6 +153,7 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
   const uint32_t acc_empty = acc_full + 16;               // [2]
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc_gen + 512);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(misc_gen + 520);
+  float *s_c = reinterpret_cast<float *>(misc_gen + 1024);  // per epilogue warp: c1[32], c2[32]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wc{abort_flag, p.status};
@@ -257,6 +269,14 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int row_in_blk = q * 32 + lane;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    float *my_c1 = s_c + q * 64, *my_c2 = my_c1 + 32;
+    float nxt1[LL_BN / 32], nxt2[LL_BN / 32];  // c1 / c2 of the next column tile, one column per lane
+#pragma unroll
+    for (int cc = 0; cc < LL_BN / 32; ++cc) {
+      const int col = cc * 32 + lane;
+      nxt1[cc] = col < p.N ? __ldg(p.c1 + col) : 0.f;
+      nxt2[cc] = col < p.N ? __ldg(p.c2 + col) : 0.f;
+    }
     uint32_t tcount = 0;
     int it = 0;
     bool ok = true;
@@ -274,7 +294,7 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const uint4 *line = reinterpret_cast<const uint4 *>(smem_gen + (sA - base) + kc * LL_A_SUB + row_in_blk * 128);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint4 v = line[j];
+          const uint4 v = line[(j + lane) & 7];  // rows are 128 bytes apart: rotate to spread the banks
           const uint32_t w[4] = {v.x, v.y, v.z, v.w};
           if (kc == 0 && j == 0) shift = unpack2<IS_BF16>(w[0]).x;
 #pragma unroll
@@ -311,21 +331,47 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const uint32_t tacc = tmem_base + buf * LL_BN + lane_off;
         uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + row * p.out_rs + n0;
         uint16_t *urow = p.u ? reinterpret_cast<uint16_t *>(p.u) + row * p.u_rs + n0 : nullptr;
-        for (int cc = 0; cc < nt / 32; ++cc) {
-          uint32_t r[32];
-          tmem_ld32(tacc + cc * 32, r);
+        const int chunks = nt / 32;
+        uint32_t r[2][32];
+        tmem_ld32(tacc, r[0]);
+        // c1 / c2: one column per lane and chunk, fetched a whole tile ahead (an L2 round trip is
+        // longer than a chunk's work), broadcast to the warp through its own 256 bytes of shared memory
+        float cur1[LL_BN / 32], cur2[LL_BN / 32];
+#pragma unroll
+        for (int cc = 0; cc < LL_BN / 32; ++cc) {
+          cur1[cc] = nxt1[cc];
+          cur2[cc] = nxt2[cc];
+        }
+        {
+          const int nn0 = (n + 1 < n_tiles ? n + 1 : 0) * LL_BN;
+#pragma unroll
+          for (int cc = 0; cc < LL_BN / 32; ++cc) {
+            const int col = nn0 + cc * 32 + lane;
+            nxt1[cc] = col < p.N ? __ldg(p.c1 + col) : 0.f;
+            nxt2[cc] = col < p.N ? __ldg(p.c2 + col) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int cc = 0; cc < LL_BN / 32; ++cc) {  // unrolled: r[][] stays in registers
+          if (cc >= chunks) break;
+          __syncwarp();
+          my_c1[lane] = cur1[cc];
+          my_c2[lane] = cur2[cc];
+          __syncwarp();
           tc_wait_ld();
+          if (cc + 1 < chunks) tmem_ld32(tacc + (cc + 1) * 32, r[(cc + 1) & 1]);
           if (row_ok) {
-            const float4 *c1v = reinterpret_cast<const float4 *>(p.c1 + n0 + cc * 32);
-            const float4 *c2v = reinterpret_cast<const float4 *>(p.c2 + n0 + cc * 32);
+            const uint32_t(&acc)[32] = r[cc & 1];
+            const float4 *c1v = reinterpret_cast<const float4 *>(my_c1);
+            const float4 *c2v = reinterpret_cast<const float4 *>(my_c2);
             float val[32];
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
-              const float4 a = __ldg(c1v + x), b = __ldg(c2v + x);
-              val[4 * x + 0] = fmaf(rstd, __uint_as_float(r[4 * x + 0]), fmaf(neg_mr, a.x, b.x));
-              val[4 * x + 1] = fmaf(rstd, __uint_as_float(r[4 * x + 1]), fmaf(neg_mr, a.y, b.y));
-              val[4 * x + 2] = fmaf(rstd, __uint_as_float(r[4 * x + 2]), fmaf(neg_mr, a.z, b.z));
-              val[4 * x + 3] = fmaf(rstd, __uint_as_float(r[4 * x + 3]), fmaf(neg_mr, a.w, b.w));
+              const float4 a = c1v[x], b = c2v[x];
+              val[4 * x + 0] = fmaf(rstd, __uint_as_float(acc[4 * x + 0]), fmaf(neg_mr, a.x, b.x));
+              val[4 * x + 1] = fmaf(rstd, __uint_as_float(acc[4 * x + 1]), fmaf(neg_mr, a.y, b.y));
+              val[4 * x + 2] = fmaf(rstd, __uint_as_float(acc[4 * x + 2]), fmaf(neg_mr, a.z, b.z));
+              val[4 * x + 3] = fmaf(rstd, __uint_as_float(acc[4 * x + 3]), fmaf(neg_mr, a.w, b.w));
             }
             uint4 o4[4];
 #pragma unroll
@@ -347,16 +393,16 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
               uint4 u4[4];
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
-                float s[8];
+                float sl[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                   const float h = 0.5f * round16<IS_BF16>(val[8 * x + e]);
-                  s[e] = fmaf(h, tanh_approx(h), h);
+                  sl[e] = fmaf(h, tanh_approx(h), h);
                 }
-                u4[x].x = pack2<IS_BF16>(s[0], s[1]);
-                u4[x].y = pack2<IS_BF16>(s[2], s[3]);
-                u4[x].z = pack2<IS_BF16>(s[4], s[5]);
-                u4[x].w = pack2<IS_BF16>(s[6], s[7]);
+                u4[x].x = pack2<IS_BF16>(sl[0], sl[1]);
+                u4[x].y = pack2<IS_BF16>(sl[2], sl[3]);
+                u4[x].z = pack2<IS_BF16>(sl[4], sl[5]);
+                u4[x].w = pack2<IS_BF16>(sl[6], sl[7]);
               }
               if (wide) {
                 st_global_256(urow + cc * 32, u4[0], u4[1]);
@@ -420,9 +466,9 @@ static int ln_linear_t(const b200_hstu_ln_linear_args &a, cudaStream_t st) {
   E *Wp = reinterpret_cast<E *>(ws + 256);
   float *c1 = reinterpret_cast<float *>(ws + 256 + align256((int64_t)a.D * a.N * 2));
   float *c2 = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(c1) + align256((int64_t)a.N * 4));
-  {
+  if (!a.weights_prepared) {
     ProfileScope prof(PROF_LN_LINEAR_PREP, st);
-    ln_linear_prep_kernel<E><<<(a.N + 31) / 32, 256, 0, st>>>(
+    ln_linear_prep_kernel<E><<<(a.N + 31) / 32, 512, 0, st>>>(
         (const E *)a.weight, (const E *)a.norm_weight, (const E *)a.norm_bias, (const E *)a.bias, Wp, c1, c2, status,
         a.D, a.N);
     count_launch();

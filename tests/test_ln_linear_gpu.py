@@ -26,7 +26,7 @@ def _inputs(M, D, H, A, V, dtype, seed, shift=0.0):
     return x, nw, nb, W, b
 
 
-@pytest.mark.parametrize("M,D,H,A,V", [(1, 64, 2, 16, 16), (127, 64, 2, 32, 32), (128, 128, 2, 64, 64),
+@pytest.mark.parametrize("M,D,H,A,V", [(1, 64, 2, 32, 32), (127, 64, 2, 32, 32), (128, 128, 2, 64, 64),
                                        (300, 256, 4, 64, 64), (1000, 512, 4, 128, 128), (333, 512, 2, 128, 96),
                                        (4500, 256, 4, 128, 128)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
