@@ -81,6 +81,75 @@ template <bool IS_BF16> __device__ __forceinline__ float2 unpack2(uint32_t w) {
   return __half22float2(*reinterpret_cast<__half2 *>(&w));
 }
 
+// element i of an 8-entry register array, without indexing it dynamically
+__device__ __forceinline__ float pick8(const float (&a)[8], int i) {
+  float v = a[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) v = (i == k) ? a[k] : v;
+  return v;
+}
+
+// One 32-column chunk of the epilogue for one row: rstd * (acc - mean * c1) + c2 -> 16 bits -> out,
+// and SiLU of the rounded value -> u for the first silu_cols columns.
+template <bool IS_BF16> struct EpiChunk {
+  float rstd, neg_mr;
+  float *my_c1, *my_c2;   // this warp's staging area: c1[32], c2[32]
+  uint16_t *orow, *urow;  // this row at the tile's first column (urow may be NULL)
+  int silu_left;          // silu_cols - first column of the tile
+  int lane;
+  bool row_ok, wide;
+  __device__ __forceinline__ void run(const uint32_t (&acc)[32], int cc, float c1_lane, float c2_lane) const {
+    __syncwarp();
+    my_c1[lane] = c1_lane;
+    my_c2[lane] = c2_lane;
+    __syncwarp();
+    if (!row_ok) return;
+    const float4 *c1v = reinterpret_cast<const float4 *>(my_c1);
+    const float4 *c2v = reinterpret_cast<const float4 *>(my_c2);
+    float val[32];
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      const float4 a = c1v[x], b = c2v[x];
+      val[4 * x + 0] = fmaf(rstd, __uint_as_float(acc[4 * x + 0]), fmaf(neg_mr, a.x, b.x));
+      val[4 * x + 1] = fmaf(rstd, __uint_as_float(acc[4 * x + 1]), fmaf(neg_mr, a.y, b.y));
+      val[4 * x + 2] = fmaf(rstd, __uint_as_float(acc[4 * x + 2]), fmaf(neg_mr, a.z, b.z));
+      val[4 * x + 3] = fmaf(rstd, __uint_as_float(acc[4 * x + 3]), fmaf(neg_mr, a.w, b.w));
+    }
+    uint4 o4[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      o4[x].x = pack2<IS_BF16>(val[8 * x + 0], val[8 * x + 1]);
+      o4[x].y = pack2<IS_BF16>(val[8 * x + 2], val[8 * x + 3]);
+      o4[x].z = pack2<IS_BF16>(val[8 * x + 4], val[8 * x + 5]);
+      o4[x].w = pack2<IS_BF16>(val[8 * x + 6], val[8 * x + 7]);
+    }
+    store64(orow + cc * 32, o4);
+    if (urow != nullptr && cc * 32 < silu_left) {
+      // SiLU of the value as stored (rounded to 16 bits), silu(v) = h + h tanh(h), h = v / 2
+      uint4 u4[4];
+      uint32_t *uw = reinterpret_cast<uint32_t *>(u4);
+      const uint32_t *ow = reinterpret_cast<const uint32_t *>(o4);
+#pragma unroll
+      for (int x = 0; x < 16; ++x) {
+        const float2 v2 = unpack2<IS_BF16>(ow[x]);
+        const float h0 = 0.5f * v2.x, h1 = 0.5f * v2.y;
+        uw[x] = pack2<IS_BF16>(fmaf(h0, tanh_approx(h0), h0), fmaf(h1, tanh_approx(h1), h1));
+      }
+      store64(urow + cc * 32, u4);
+    }
+  }
+  // 64 bytes of one row: whole 32-byte sectors when the row is aligned for it
+  __device__ __forceinline__ void store64(uint16_t *dst, const uint4 (&v)[4]) const {
+    if (wide) {
+      st_global_256(dst, v[0], v[1]);
+      st_global_256(dst + 16, v[2], v[3]);
+    } else {
+#pragma unroll
+      for (int x = 0; x < 4; ++x) *reinterpret_cast<uint4 *>(dst + x * 8) = v[x];
+    }
+  }
+};
+
 // ---------------------------------------------------------------------------------------
 // preparation: W' = gamma (.) W, c1 = column sums of W', c2 = beta W + bias
 // grid: N / 32 CTAs of 512 threads; thread (kg = tid / 32, col = tid % 32) covers rows kg, kg + 16, ...
@@ -190,23 +259,23 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     if (elect_one()) {
       prefetch_tmap(&tmap_x);
       prefetch_tmap(&tmap_w);
-      uint32_t bcount = 0;  // W' stages issued so far
+      uint32_t slot = 0, sphase = 0;  // ring position of the next W' stage and the parity of its round
       int it = 0;
       bool ok = true;
       for (int blk = blockIdx.x; blk < num_blocks && ok; blk += gridDim.x, ++it) {
         const int total_b = n_tiles * KC;
-        int issued = 0;
+        int issued = 0, bn = 0, bk = 0;
         auto issue_b = [&](int upto) {
-          for (; issued < upto && ok; ++issued, ++bcount) {
-            const int n = issued / KC, kc = issued - n * KC;
-            const uint32_t s = bcount % ST, round = bcount / ST;
-            ok = mbar_wait(wc, b_empty + 8 * s, (round & 1) ^ 1, 1101);
+          for (; issued < upto && ok; ++issued) {
+            ok = mbar_wait(wc, b_empty + 8 * slot, sphase ^ 1, 1101);
             if (!ok) break;
-            const int n0 = n * LL_BN;
+            const int n0 = bn * LL_BN;
             const int boxes = (p.N - n0) >= LL_BN ? 4 : (p.N - n0) / 64;
-            mbar_arrive_expect_tx(b_full + 8 * s, boxes * LL_B_BOX);
-            for (int bx = 0; bx < boxes; ++bx)
-              tma_load_2d(sB + s * LL_B_STAGE + bx * LL_B_BOX, &tmap_w, n0 + bx * 64, kc * LL_KC, b_full + 8 * s);
+            const uint32_t full = b_full + 8 * slot, dst = sB + slot * LL_B_STAGE;
+            mbar_arrive_expect_tx(full, boxes * LL_B_BOX);
+            for (int bx = 0; bx < boxes; ++bx) tma_load_2d(dst + bx * LL_B_BOX, &tmap_w, n0 + bx * 64, bk * LL_KC, full);
+            if (++bk == KC) { bk = 0; ++bn; }
+            if (++slot == (uint32_t)ST) { slot = 0; sphase ^= 1; }
           }
         };
         // the first stages of W' do not depend on the x buffer: request them before waiting for it
@@ -226,9 +295,11 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     // ------------------------------------------------------------------ MMA issue
     if (elect_one()) {
       constexpr uint32_t FMT = IS_BF16 ? 1u : 0u;
-      uint32_t bcount = 0, tcount = 0;
+      uint32_t slot = 0, sphase = 0, tcount = 0;
       int it = 0;
       bool ok = true;
+      const uint64_t a_desc0 = make_smem_desc(sA, 16, 1024);
+      const uint64_t b_desc0 = make_smem_desc(sB, LL_B_BOX, 1024);
       for (int blk = blockIdx.x; blk < num_blocks && ok; blk += gridDim.x, ++it) {
         for (int n = 0; n < n_tiles && ok; ++n, ++tcount) {
           const int n0 = n * LL_BN;
@@ -239,22 +310,22 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
           if (!ok) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * LL_BN;
-          for (int kc = 0; kc < KC && ok; ++kc, ++bcount) {
-            const uint32_t s = bcount % ST, round = bcount / ST;
+          for (int kc = 0; kc < KC; ++kc) {
             if (n == 0) {
               ok = mbar_wait(wc, a_full + 8 * kc, it & 1, 1202);
               if (!ok) break;
             }
-            ok = mbar_wait(wc, b_full + 8 * s, round & 1, 1203);
+            ok = mbar_wait(wc, b_full + 8 * slot, sphase, 1203);
             if (!ok) break;
             tc_fence_after();
-            const uint64_t a_desc = make_smem_desc(sA + kc * LL_A_SUB, 16, 1024);
-            const uint64_t b_desc = make_smem_desc(sB + s * LL_B_STAGE, LL_B_BOX, 1024);
+            const uint64_t a_desc = desc_advance(a_desc0, kc * LL_A_SUB);
+            const uint64_t b_desc = desc_advance(b_desc0, slot * LL_B_STAGE);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
               mma_ss(d_tmem, desc_advance(a_desc, ks * 32), desc_advance(b_desc, ks * 2048), idesc,
                      (kc | ks) != 0);
-            tc_commit(b_empty + 8 * s);
+            tc_commit(b_empty + 8 * slot);
+            if (++slot == (uint32_t)ST) { slot = 0; sphase ^= 1; }
           }
           if (!ok) break;
           tc_commit(acc_full + 8 * buf);
@@ -332,8 +403,6 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         uint16_t *orow = reinterpret_cast<uint16_t *>(p.out) + row * p.out_rs + n0;
         uint16_t *urow = p.u ? reinterpret_cast<uint16_t *>(p.u) + row * p.u_rs + n0 : nullptr;
         const int chunks = nt / 32;
-        uint32_t r[2][32];
-        tmem_ld32(tacc, r[0]);
         // c1 / c2: one column per lane and chunk, fetched a whole tile ahead (an L2 round trip is
         // longer than a chunk's work), broadcast to the warp through its own 256 bytes of shared memory
         float cur1[LL_BN / 32], cur2[LL_BN / 32];
@@ -351,67 +420,19 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             nxt2[cc] = col < p.N ? __ldg(p.c2 + col) : 0.f;
           }
         }
-#pragma unroll
-        for (int cc = 0; cc < LL_BN / 32; ++cc) {  // unrolled: r[][] stays in registers
-          if (cc >= chunks) break;
-          __syncwarp();
-          my_c1[lane] = cur1[cc];
-          my_c2[lane] = cur2[cc];
-          __syncwarp();
+        // The loop stays rolled (two chunks per trip for the register double buffer): the epilogue
+        // shares its instruction cache with the MMA and producer threads, whose loops must stay hot.
+        EpiChunk<IS_BF16> ec{rstd, neg_mr, my_c1, my_c2, orow, urow, p.silu_cols - n0, lane, row_ok, wide};
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tacc, r0);
+        for (int cc = 0; cc < chunks; cc += 2) {
           tc_wait_ld();
-          if (cc + 1 < chunks) tmem_ld32(tacc + (cc + 1) * 32, r[(cc + 1) & 1]);
-          if (row_ok) {
-            const uint32_t(&acc)[32] = r[cc & 1];
-            const float4 *c1v = reinterpret_cast<const float4 *>(my_c1);
-            const float4 *c2v = reinterpret_cast<const float4 *>(my_c2);
-            float val[32];
-#pragma unroll
-            for (int x = 0; x < 8; ++x) {
-              const float4 a = c1v[x], b = c2v[x];
-              val[4 * x + 0] = fmaf(rstd, __uint_as_float(acc[4 * x + 0]), fmaf(neg_mr, a.x, b.x));
-              val[4 * x + 1] = fmaf(rstd, __uint_as_float(acc[4 * x + 1]), fmaf(neg_mr, a.y, b.y));
-              val[4 * x + 2] = fmaf(rstd, __uint_as_float(acc[4 * x + 2]), fmaf(neg_mr, a.z, b.z));
-              val[4 * x + 3] = fmaf(rstd, __uint_as_float(acc[4 * x + 3]), fmaf(neg_mr, a.w, b.w));
-            }
-            uint4 o4[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              o4[x].x = pack2<IS_BF16>(val[8 * x + 0], val[8 * x + 1]);
-              o4[x].y = pack2<IS_BF16>(val[8 * x + 2], val[8 * x + 3]);
-              o4[x].z = pack2<IS_BF16>(val[8 * x + 4], val[8 * x + 5]);
-              o4[x].w = pack2<IS_BF16>(val[8 * x + 6], val[8 * x + 7]);
-            }
-            if (wide) {
-              st_global_256(orow + cc * 32, o4[0], o4[1]);
-              st_global_256(orow + cc * 32 + 16, o4[2], o4[3]);
-            } else {
-#pragma unroll
-              for (int x = 0; x < 4; ++x) *reinterpret_cast<uint4 *>(orow + cc * 32 + x * 8) = o4[x];
-            }
-            if (urow != nullptr && n0 + cc * 32 < p.silu_cols) {
-              // SiLU of the value as stored (rounded to 16 bits), silu(v) = h + h tanh(h), h = v / 2
-              uint4 u4[4];
-#pragma unroll
-              for (int x = 0; x < 4; ++x) {
-                float sl[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const float h = 0.5f * round16<IS_BF16>(val[8 * x + e]);
-                  sl[e] = fmaf(h, tanh_approx(h), h);
-                }
-                u4[x].x = pack2<IS_BF16>(sl[0], sl[1]);
-                u4[x].y = pack2<IS_BF16>(sl[2], sl[3]);
-                u4[x].z = pack2<IS_BF16>(sl[4], sl[5]);
-                u4[x].w = pack2<IS_BF16>(sl[6], sl[7]);
-              }
-              if (wide) {
-                st_global_256(urow + cc * 32, u4[0], u4[1]);
-                st_global_256(urow + cc * 32 + 16, u4[2], u4[3]);
-              } else {
-#pragma unroll
-                for (int x = 0; x < 4; ++x) *reinterpret_cast<uint4 *>(urow + cc * 32 + x * 8) = u4[x];
-              }
-            }
+          if (cc + 1 < chunks) tmem_ld32(tacc + (cc + 1) * 32, r1);
+          ec.run(r0, cc, pick8(cur1, cc), pick8(cur2, cc));
+          if (cc + 1 < chunks) {
+            tc_wait_ld();
+            if (cc + 2 < chunks) tmem_ld32(tacc + (cc + 2) * 32, r0);
+            ec.run(r1, cc + 1, pick8(cur1, cc + 1), pick8(cur2, cc + 1));
           }
         }
         tc_fence_before();

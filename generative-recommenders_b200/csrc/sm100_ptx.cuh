@@ -84,39 +84,6 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx &ctx, uint32_t bar, uint
   }
 }
 
-// The same bounded wait as a pure spin on mbarrier.test_wait (never suspends the thread): for a
-// single elected thread whose wake-up latency sits on the critical path of a pipeline.
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-__device__ __forceinline__ bool mbar_wait_spin(const WaitCtx &ctx, uint32_t bar, uint32_t parity, int site) {
-  uint64_t t0 = 0;
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((++spins & 1023u) == 0) {
-      if (*ctx.abort_flag) return false;
-      uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > WAIT_LIMIT_NS) {
-        *ctx.abort_flag = 1;
-        if (ctx.status) atomicCAS(ctx.status, 0, site);
-        return false;
-      }
-    }
-  }
-}
-
 // ------------------------------------------------------------------ work ring (see attn_plan.cuh)
 // slot layout: int4 {b, t, start, len}, int4 {nt, idx, 0, 0}
 __device__ __forceinline__ void sched_publish(const WaitCtx &wc, uint8_t *ring, uint32_t full0, uint32_t empty0,

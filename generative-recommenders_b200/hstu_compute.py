@@ -65,9 +65,10 @@ class _FusedUqvkFunction(torch.autograd.Function):
     uses library GEMMs for the two weight / input products."""
 
     @staticmethod
-    def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, hv):
+    def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, num_heads, attn_dim, hidden_dim):
         M, D = x.shape
         N = weight.shape[1]
+        hv, ha = hidden_dim * num_heads, attn_dim * num_heads
         nw = norm_weight.to(x.dtype).contiguous()
         nb = norm_bias.to(x.dtype).contiguous()
         w = weight.to(x.dtype).contiguous()
@@ -90,30 +91,34 @@ class _FusedUqvkFunction(torch.autograd.Function):
             _cabi.check(_cabi.lib().b200_hstu_ln_linear_silu_fwd(a, stream_ptr(x.device)),
                         "b200_hstu_ln_linear_silu_fwd")
         ctx.save_for_backward(x, nw, nb, w, uvqk, mean, rstd)
-        ctx.cfg = (eps, hv, norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
-        ctx.mark_non_differentiable(mean, rstd)
-        return uvqk, u, mean, rstd
+        ctx.cfg = (eps, hv, ha, norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
+        # q, k, v are views of the uvqk buffer, handed out as separate results so that the backward
+        # receives their gradients one by one instead of three zero-padded [M, N] sums
+        v = uvqk[:, hv:2 * hv].view(M, num_heads, hidden_dim)
+        q = uvqk[:, 2 * hv:2 * hv + ha].view(M, num_heads, attn_dim)
+        k = uvqk[:, 2 * hv + ha:].view(M, num_heads, attn_dim)
+        return u, q, k, v
 
     @staticmethod
-    def backward(ctx, d_uvqk, du, _dmean, _drstd):
+    def backward(ctx, du, dq, dk, dv):
         x, nw, nb, w, uvqk, mean, rstd = ctx.saved_tensors
-        eps, hv, nw_dtype, nb_dtype, w_dtype, b_dtype = ctx.cfg
+        eps, hv, ha, nw_dtype, nb_dtype, w_dtype, b_dtype = ctx.cfg
         M, D = x.shape
         N = w.shape[1]
         lib = _cabi.lib()
         dt = dtype_code(x)
         st = stream_ptr(x.device)
-        if d_uvqk is None:
-            d_uvqk = torch.zeros((M, N), dtype=x.dtype, device=x.device)
-        elif not d_uvqk.is_contiguous():
-            d_uvqk = d_uvqk.contiguous()
-        else:
-            d_uvqk = d_uvqk.clone()
+        d_uvqk = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        for lo, width, g in ((hv, hv, dv), (2 * hv, ha, dq), (2 * hv + ha, ha, dk)):
+            if g is None:
+                d_uvqk[:, lo:lo + width].zero_()
+            else:
+                d_uvqk[:, lo:lo + width].copy_(g.reshape(M, width))
         with torch.cuda.device(x.device):
             if du is not None:
                 if du.stride(-1) != 1:
                     du = du.contiguous()
-                # d(pre-activation u) = du * SiLU'(uvqk[:, :hv]), written over the unused u columns
+                # d(pre-activation u) = du * SiLU'(uvqk[:, :hv])
                 _cabi.check(lib.b200_hstu_silu_bwd(du.data_ptr(), du.stride(0), uvqk.data_ptr(), uvqk.stride(0),
                                                    d_uvqk.data_ptr(), d_uvqk.stride(0), M, hv, dt, st),
                             "b200_hstu_silu_bwd")
@@ -136,7 +141,7 @@ class _FusedUqvkFunction(torch.autograd.Function):
                                                      dx.stride(0), dnw.data_ptr(), dnb.data_ptr(), partial.data_ptr(),
                                                      nbytes, M, D, dt, st),
                         "b200_hstu_layer_norm_bwd")
-        return dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None
+        return dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None, None, None
 
 
 _FUSED_UQVK = True
@@ -167,7 +172,8 @@ def hstu_compute_uqvk(
     require_cuda(x, norm_weight, norm_bias, uvqk_weight, uvqk_bias)
     hv, ha = hidden_dim * num_heads, attn_dim * num_heads
     if _FUSED_UQVK and _fused_uqvk_supported(x, uvqk_weight, hv):
-        uvqk, u, _, _ = _FusedUqvkFunction.apply(x, norm_weight, norm_bias, float(norm_eps), uvqk_weight, uvqk_bias, hv)
+        return _FusedUqvkFunction.apply(x, norm_weight, norm_bias, float(norm_eps), uvqk_weight, uvqk_bias,
+                                        num_heads, attn_dim, hidden_dim)
     else:
         normed_x = layer_norm(x, weight=norm_weight, bias=norm_bias, eps=norm_eps, kernel=kernel)
         uvqk = addmm(uvqk_bias, normed_x, uvqk_weight, kernel)
