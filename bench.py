@@ -593,6 +593,66 @@ def run_fp8(args):
     print(json.dumps(out), flush=True)
 
 
+def _uvqk_stage(dev, peaks, steps):
+    """The uvqk stage at configs[1]'s token count (D = 512, H = 4, d = 128): one fused tensor-core
+    kernel against LayerNorm kernel + library GEMM + SiLU kernel, forward only."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi, hstu_compute as HC, workloads as W
+
+    D, H_, d_ = 512, 4, 128
+    g = torch.Generator().manual_seed(5)
+    mk = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16).to(dev)  # noqa: E731
+    uq_rows = int(W.config1().total_tokens)
+    xs, w_, b_ = mk(uq_rows, D), mk(D), mk(D)
+    Wu = (torch.randn(D, 4 * H_ * d_, generator=g) / D ** 0.5).to(torch.bfloat16).to(dev)
+    bu = mk(4 * H_ * d_)
+    uq = {}
+    for name, fused in (("fused", True), ("separate", False)):
+        HC.set_fused_uqvk(fused)
+        with torch.no_grad():
+            fn = lambda: G.hstu_compute_uqvk(xs, w_, b_, 1e-6, H_, d_, d_, Wu, bu)  # noqa: E731
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            for s_, e_ in ev:
+                s_.record()
+                fn()
+                e_.record()
+            torch.cuda.synchronize()
+        ms = sorted(s_.elapsed_time(e_) for s_, e_ in ev)[steps // 2]
+        uq[name] = {"ms": round(ms, 4), "tflops": round(2.0 * uq_rows * D * Wu.shape[1] / (ms * 1e-3) / 1e12, 1)}
+    HC.set_fused_uqvk(True)
+    _cabi.profile_enable(True)
+    with torch.no_grad():
+        for _ in range(max(steps, 3)):
+            G.hstu_compute_uqvk(xs, w_, b_, 1e-6, H_, d_, d_, Wu, bu)
+    torch.cuda.synchronize()
+    kk = _cabi.profile_collect("ln_linear")
+    kp = _cabi.profile_collect("ln_linear_prep")
+    _cabi.profile_enable(False)
+    kms = sorted(kk)[len(kk) // 2]
+    uq["fused"]["kernel_ms"] = round(kms, 4)
+    uq["fused"]["prep_ms"] = round(sorted(kp)[len(kp) // 2], 4)
+    uq["fused"]["kernel_tflops"] = round(2.0 * uq_rows * D * Wu.shape[1] / (kms * 1e-3) / 1e12, 1)
+    uq["fused"]["kernel_frac_of_bf16_peak"] = round(uq["fused"]["kernel_tflops"] / peaks["bf16_tflops"], 3)
+    uq["rows"] = uq_rows
+    uq["shape"] = "x [%d, %d] -> uvqk [%d, %d], u [%d, %d]" % (uq_rows, D, uq_rows, Wu.shape[1], uq_rows, H_ * d_)
+    return uq
+
+
+def run_uvqk(args):
+    """``--workload uvqk``: the fused uvqk stage alone (a small case for profiling)."""
+    world, rank, local_rank, dev, dist = _dist_setup()
+    peaks, peak_kind = load_peaks()
+    uq = _uvqk_stage(dev, peaks, max(3, min(args.steps, 30)))
+    out = {"metric": "hstu_uvqk_stage_tflops", "value": uq["fused"]["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": 3, "ms_per_step": uq["fused"]["ms"], "higher_is_better": True,
+           "dtype": "bf16", "data": "synthetic", "config": {"workload": "uvqk stage forward, " + uq["shape"]},
+           "bf16_peak_tflops": peaks["bf16_tflops"], "peak_source": peak_kind + " (cuBLAS bf16 burst)", "uvqk_stage": uq}
+    print(json.dumps(out), flush=True)
+
+
 def run_stages(args):
     """Achieved HBM GB/s of the memory-bound stage kernels (bf16, D = H*dv = 512, rows = tokens of
     configs[4]'s first 400 sequences), from the library's per-kernel events."""
@@ -669,46 +729,7 @@ def run_stages(args):
     ye = emb(xe, pw, tw)
     res["add_timestamp_positional_embeddings_bwd"] = timed(
         "ts_pos", lambda: torch.autograd.grad(ye, (xe, pw, tw), dy, retain_graph=True), rows * D * 2 * 2)
-    # the uvqk stage: one fused tensor-core kernel against LayerNorm kernel + library GEMM + SiLU kernel
-    from generative_recommenders_b200 import hstu_compute as HC
-    H_, d_ = 4, 128
-    Wu = (torch.randn(D, 4 * H_ * d_, generator=g) / D ** 0.5).to(torch.bfloat16).to(dev)
-    bu = mk(4 * H_ * d_)
-    uq_rows = int(W.config1().total_tokens)
-    xs = x[:uq_rows]
-    uq = {}
-    for name, fused in (("fused", True), ("separate", False)):
-        HC.set_fused_uqvk(fused)
-        with torch.no_grad():
-            fn = lambda: G.hstu_compute_uqvk(xs, w_, b_, 1e-6, H_, d_, d_, Wu, bu)  # noqa: E731
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(20)]
-            for s_, e_ in ev:
-                s_.record()
-                fn()
-                e_.record()
-            torch.cuda.synchronize()
-        ms = sorted(s_.elapsed_time(e_) for s_, e_ in ev)[10]
-        uq[name] = {"ms": round(ms, 4), "tflops": round(2.0 * uq_rows * D * Wu.shape[1] / (ms * 1e-3) / 1e12, 1)}
-    HC.set_fused_uqvk(True)
-    _cabi.profile_enable(True)
-    with torch.no_grad():
-        for _ in range(10):
-            G.hstu_compute_uqvk(xs, w_, b_, 1e-6, H_, d_, d_, Wu, bu)
-    torch.cuda.synchronize()
-    kk = _cabi.profile_collect("ln_linear")
-    kp = _cabi.profile_collect("ln_linear_prep")
-    _cabi.profile_enable(False)
-    kms = sorted(kk)[len(kk) // 2]
-    uq["fused"]["kernel_ms"] = round(kms, 4)
-    uq["fused"]["prep_ms"] = round(sorted(kp)[len(kp) // 2], 4)
-    uq["fused"]["kernel_tflops"] = round(2.0 * uq_rows * D * Wu.shape[1] / (kms * 1e-3) / 1e12, 1)
-    uq["fused"]["kernel_frac_of_bf16_peak"] = round(uq["fused"]["kernel_tflops"] / peaks["bf16_tflops"], 3)
-    uq["rows"] = uq_rows
-    uq["shape"] = "x [%d, %d] -> uvqk [%d, %d], u [%d, %d]" % (uq_rows, D, uq_rows, Wu.shape[1], uq_rows, H_ * d_)
-    res["uvqk_stage"] = uq
+    res["uvqk_stage"] = _uvqk_stage(dev, peaks, 20)
     out = {"metric": "hstu_stage_hbm_gb_per_s", "value": res["norm_mul_fwd"]["gb_per_s"], "unit": "GB/s", "n_gpus": 1,
            "steps": args.steps, "warmup": 3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
            "config": {"workload": "stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2)" % (rows, rows * D * 2 / 1e6)},
@@ -723,7 +744,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config1",
-                    choices=["config1", "config3", "config3_fp8", "config2_stack", "config4_stack", "stages"])
+                    choices=["config1", "config3", "config3_fp8", "config2_stack", "config4_stack", "stages", "uvqk"])
     ap.add_argument("--graph", action="store_true", help="config2_stack: replay the step from a CUDA graph")
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (stack workloads)")
     ap.add_argument("--fwd-only", action="store_true", help="time the forward alone (inference)")
@@ -734,6 +755,8 @@ def main():
         run_stack(args)
     elif args.workload == "stages":
         run_stages(args)
+    elif args.workload == "uvqk":
+        run_uvqk(args)
     elif args.workload == "config3_fp8":
         run_fp8(args)
     else:
