@@ -270,18 +270,37 @@ __global__ void __launch_bounds__(WARPS * 32) layer_norm_bwd_kernel(
   reduce_columns_to_partial(db, smem, prow + D, D, lane, warp);
 }
 
-// out[which][e] = sum_b partial[b][which][e]   (which in {0,1}); one thread per column
+// out[which][e] = sum_b partial[b][which][e]   (which in {0,1}).  A CTA takes 32 columns; its
+// eight warps split the partial rows (four loads in flight each) and are added up in a fixed
+// order, so the result does not depend on timing.
 template <typename E>
-__global__ void reduce_partial_kernel(const float *__restrict__ partial, int nblocks, int D, E *__restrict__ out0,
-                                      E *__restrict__ out1) {
-  int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= 2 * D) return;
+__global__ void __launch_bounds__(256) reduce_partial_kernel(const float *__restrict__ partial, int nblocks, int D,
+                                                             E *__restrict__ out0, E *__restrict__ out1) {
+  __shared__ float part[8][33];
+  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int e = blockIdx.x * 32 + lane;
+  const int64_t stride = 2 * (int64_t)D;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(int64_t)b * 2 * D + e];
-  if (e < D) {
-    if (out0) out0[e] = from_f32<E>(s);
-  } else {
-    if (out1) out1[e - D] = from_f32<E>(s);
+  if (e < 2 * D) {
+    int b = g;
+    for (; b + 24 < nblocks; b += 32) {
+      const float v0 = partial[(int64_t)b * stride + e], v1 = partial[(int64_t)(b + 8) * stride + e];
+      const float v2 = partial[(int64_t)(b + 16) * stride + e], v3 = partial[(int64_t)(b + 24) * stride + e];
+      s += (v0 + v1) + (v2 + v3);
+    }
+    for (; b < nblocks; b += 8) s += partial[(int64_t)b * stride + e];
+  }
+  part[g][lane] = s;
+  __syncthreads();
+  if (g == 0 && e < 2 * D) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += part[i][lane];
+    if (e < D) {
+      if (out0) out0[e] = from_f32<E>(t);
+    } else {
+      if (out1) out1[e - D] = from_f32<E>(t);
+    }
   }
 }
 
@@ -747,7 +766,7 @@ int ln_bwd_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const v
   });
   count_launch();
   B200_CHECK_LAUNCH("layer_norm backward");
-  reduce_partial_kernel<E><<<(2 * D + 255) / 256, 256, 0, st>>>((const float *)partial, grid, D, (E *)dw, (E *)db);
+  reduce_partial_kernel<E><<<(2 * D + 31) / 32, 256, 0, st>>>((const float *)partial, grid, D, (E *)dw, (E *)db);
   count_launch();
   B200_CHECK_LAUNCH("layer_norm backward (reduce)");
   return 0;
@@ -830,7 +849,7 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     group_norm_mul_kernel<E, true><<<grid, WARPS * 32, smem, st>>>(p);
     count_launch();
     B200_CHECK_LAUNCH("group_norm_mul backward");
-    reduce_partial_kernel<E><<<(2 * a.H + 255) / 256, 256, 0, st>>>(p.partial, grid, a.H, (E *)a.dweight,
+    reduce_partial_kernel<E><<<(2 * a.H + 31) / 32, 256, 0, st>>>(p.partial, grid, a.H, (E *)a.dweight,
                                                                     (E *)a.dbias);
     count_launch();
     B200_CHECK_LAUNCH("group_norm_mul backward (reduce)");
@@ -866,7 +885,7 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
   });
   count_launch();
   B200_CHECK_LAUNCH("norm_mul backward");
-  reduce_partial_kernel<E><<<(2 * D + 255) / 256, 256, 0, st>>>(p.partial, grid, D, (E *)a.dweight, (E *)a.dbias);
+  reduce_partial_kernel<E><<<(2 * D + 31) / 32, 256, 0, st>>>(p.partial, grid, D, (E *)a.dweight, (E *)a.dbias);
   count_launch();
   B200_CHECK_LAUNCH("norm_mul backward (reduce)");
   return 0;

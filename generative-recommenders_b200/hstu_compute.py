@@ -57,39 +57,84 @@ def _fused_uqvk_supported(x, uvqk_weight, hv) -> bool:
     return bool(_cabi.lib().b200_hstu_ln_linear_supported(D, N, hv, dtype_code(x)))
 
 
+def _fused_uqvk_launch(x, nw, nb, eps, w, b, hv):
+    """One launch of the fused kernel: returns (uvqk [M, N], u [M, hv], mean [M], rstd [M])."""
+    M, D = x.shape
+    N = w.shape[1]
+    uvqk = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    u = torch.empty((M, hv), dtype=x.dtype, device=x.device)
+    mean = torch.empty(M, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    nbytes = _cabi.lib().b200_hstu_ln_linear_workspace_bytes(D, N)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    a = _cabi.LnLinearArgs()
+    a.x, a.norm_weight, a.norm_bias, a.weight, a.bias = (x.data_ptr(), nw.data_ptr(), nb.data_ptr(),
+                                                          w.data_ptr(), b.data_ptr())
+    a.out, a.u, a.mean, a.rstd = uvqk.data_ptr(), u.data_ptr(), mean.data_ptr(), rstd.data_ptr()
+    a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+    a.x_row_stride, a.out_row_stride, a.u_row_stride = x.stride(0), uvqk.stride(0), u.stride(0)
+    a.M, a.D, a.N, a.silu_cols = M, D, N, hv
+    a.eps, a.dtype = eps, dtype_code(x)
+    with torch.cuda.device(x.device):
+        _cabi.check(_cabi.lib().b200_hstu_ln_linear_silu_fwd(a, stream_ptr(x.device)),
+                    "b200_hstu_ln_linear_silu_fwd")
+    return uvqk, u, mean, rstd
+
+
+def _fused_uqvk_backward(x, nw, nb, w, uvqk, mean, rstd, eps, hv, du, d_uvqk):
+    """Backward of the fused stage.  ``d_uvqk`` [M, N] already holds the gradients of the v, q, k
+    columns; the u columns are filled here (``du * SiLU'``).  Recomputes ``LN(x)`` from the saved
+    statistics (the reference's ``recompute_normed_x_in_backward``,
+    generative_recommenders/ops/triton/triton_hstu_preprocess_and_attention.py:122-127, 185-203)
+    and uses library GEMMs.  Returns (dx, d_norm_weight, d_norm_bias, d_weight, d_bias)."""
+    M, D = x.shape
+    lib = _cabi.lib()
+    dt = dtype_code(x)
+    st = stream_ptr(x.device)
+    with torch.cuda.device(x.device):
+        if du is not None:
+            if du.stride(-1) != 1:
+                du = du.contiguous()
+            _cabi.check(lib.b200_hstu_silu_bwd(du.data_ptr(), du.stride(0), uvqk.data_ptr(), uvqk.stride(0),
+                                               d_uvqk.data_ptr(), d_uvqk.stride(0), M, hv, dt, st),
+                        "b200_hstu_silu_bwd")
+        else:
+            d_uvqk[:, :hv].zero_()
+        normed = torch.empty_like(x)
+        _cabi.check(lib.b200_hstu_layer_norm_fwd(x.data_ptr(), x.stride(0), nw.data_ptr(), nb.data_ptr(),
+                                                 normed.data_ptr(), normed.stride(0), None, None, M, D, eps, dt, st),
+                    "b200_hstu_layer_norm_fwd")
+        dw = normed.t() @ d_uvqk
+        # column sums on the tensor cores: cheaper than a strided reduction over [M, N]
+        db = (torch.ones((1, M), dtype=x.dtype, device=x.device) @ d_uvqk).view(-1)
+        dnormed = d_uvqk @ w.t()
+        dx = torch.empty_like(x)
+        dnw = torch.empty(D, dtype=x.dtype, device=x.device)
+        dnb = torch.empty(D, dtype=x.dtype, device=x.device)
+        nbytes = lib.b200_hstu_layer_norm_bwd_workspace_bytes(D)
+        partial = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        _cabi.check(lib.b200_hstu_layer_norm_bwd(dnormed.data_ptr(), dnormed.stride(0), x.data_ptr(), x.stride(0),
+                                                 nw.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                                 dx.stride(0), dnw.data_ptr(), dnb.data_ptr(), partial.data_ptr(),
+                                                 nbytes, M, D, dt, st),
+                    "b200_hstu_layer_norm_bwd")
+    return dx, dnw, dnb, dw, db
+
+
 class _FusedUqvkFunction(torch.autograd.Function):
     """``uvqk = LN(x) W + b`` and ``u = SiLU(uvqk[:, :hv])`` from one tensor-core kernel
-    (csrc/ln_linear_sm100.cu).  The backward recomputes ``LN(x)`` from the saved row statistics
-    (the reference's ``recompute_normed_x_in_backward``,
-    generative_recommenders/ops/triton/triton_hstu_preprocess_and_attention.py:122-127, 185-203) and
-    uses library GEMMs for the two weight / input products."""
+    (csrc/ln_linear_sm100.cu)."""
 
     @staticmethod
     def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, num_heads, attn_dim, hidden_dim):
-        M, D = x.shape
-        N = weight.shape[1]
+        M = x.shape[0]
         hv, ha = hidden_dim * num_heads, attn_dim * num_heads
         nw = norm_weight.to(x.dtype).contiguous()
         nb = norm_bias.to(x.dtype).contiguous()
         w = weight.to(x.dtype).contiguous()
         b = bias.to(x.dtype).contiguous()
-        uvqk = torch.empty((M, N), dtype=x.dtype, device=x.device)
-        u = torch.empty((M, hv), dtype=x.dtype, device=x.device)
-        mean = torch.empty(M, dtype=torch.float32, device=x.device)
-        rstd = torch.empty(M, dtype=torch.float32, device=x.device)
-        nbytes = _cabi.lib().b200_hstu_ln_linear_workspace_bytes(D, N)
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
-        a = _cabi.LnLinearArgs()
-        a.x, a.norm_weight, a.norm_bias, a.weight, a.bias = (x.data_ptr(), nw.data_ptr(), nb.data_ptr(),
-                                                              w.data_ptr(), b.data_ptr())
-        a.out, a.u, a.mean, a.rstd = uvqk.data_ptr(), u.data_ptr(), mean.data_ptr(), rstd.data_ptr()
-        a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
-        a.x_row_stride, a.out_row_stride, a.u_row_stride = x.stride(0), uvqk.stride(0), u.stride(0)
-        a.M, a.D, a.N, a.silu_cols = M, D, N, hv
-        a.eps, a.dtype = eps, dtype_code(x)
-        with torch.cuda.device(x.device):
-            _cabi.check(_cabi.lib().b200_hstu_ln_linear_silu_fwd(a, stream_ptr(x.device)),
-                        "b200_hstu_ln_linear_silu_fwd")
+        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv)
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(x, nw, nb, w, uvqk, mean, rstd)
         ctx.cfg = (eps, hv, ha, norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
         # q, k, v are views of the uvqk buffer, handed out as separate results so that the backward
@@ -103,45 +148,80 @@ class _FusedUqvkFunction(torch.autograd.Function):
     def backward(ctx, du, dq, dk, dv):
         x, nw, nb, w, uvqk, mean, rstd = ctx.saved_tensors
         eps, hv, ha, nw_dtype, nb_dtype, w_dtype, b_dtype = ctx.cfg
-        M, D = x.shape
-        N = w.shape[1]
-        lib = _cabi.lib()
-        dt = dtype_code(x)
-        st = stream_ptr(x.device)
+        M, N = uvqk.shape
         d_uvqk = torch.empty((M, N), dtype=x.dtype, device=x.device)
         for lo, width, g in ((hv, hv, dv), (2 * hv, ha, dq), (2 * hv + ha, ha, dk)):
             if g is None:
                 d_uvqk[:, lo:lo + width].zero_()
             else:
                 d_uvqk[:, lo:lo + width].copy_(g.reshape(M, width))
-        with torch.cuda.device(x.device):
-            if du is not None:
-                if du.stride(-1) != 1:
-                    du = du.contiguous()
-                # d(pre-activation u) = du * SiLU'(uvqk[:, :hv])
-                _cabi.check(lib.b200_hstu_silu_bwd(du.data_ptr(), du.stride(0), uvqk.data_ptr(), uvqk.stride(0),
-                                                   d_uvqk.data_ptr(), d_uvqk.stride(0), M, hv, dt, st),
-                            "b200_hstu_silu_bwd")
-            else:
-                d_uvqk[:, :hv].zero_()
-            normed = torch.empty_like(x)
-            _cabi.check(lib.b200_hstu_layer_norm_fwd(x.data_ptr(), x.stride(0), nw.data_ptr(), nb.data_ptr(),
-                                                     normed.data_ptr(), normed.stride(0), None, None, M, D, eps, dt, st),
-                        "b200_hstu_layer_norm_fwd")
-            dw = normed.t() @ d_uvqk
-            db = d_uvqk.sum(0)
-            dnormed = d_uvqk @ w.t()
-            dx = torch.empty_like(x)
-            dnw = torch.empty(D, dtype=x.dtype, device=x.device)
-            dnb = torch.empty(D, dtype=x.dtype, device=x.device)
-            nbytes = lib.b200_hstu_layer_norm_bwd_workspace_bytes(D)
-            partial = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
-            _cabi.check(lib.b200_hstu_layer_norm_bwd(dnormed.data_ptr(), dnormed.stride(0), x.data_ptr(), x.stride(0),
-                                                     nw.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
-                                                     dx.stride(0), dnw.data_ptr(), dnb.data_ptr(), partial.data_ptr(),
-                                                     nbytes, M, D, dt, st),
-                        "b200_hstu_layer_norm_bwd")
+        dx, dnw, dnb, dw, db = _fused_uqvk_backward(x, nw, nb, w, uvqk, mean, rstd, eps, hv, du, d_uvqk)
         return dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None, None, None
+
+
+class _FusedPreprocessAttentionFunction(torch.autograd.Function):
+    """The fused uvqk stage and the attention as one autograd node: the attention backward writes
+    dq / dk / dv straight into the column blocks of ``d_uvqk``, which then feeds the stage's
+    backward GEMMs - no gradient copies in between.  Returns (u, attn [M, H, dv], k, v)."""
+
+    @staticmethod
+    def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, num_heads, attn_dim, hidden_dim, seq_offsets,
+                num_targets, bias_by_distance, max_seq_len, alpha, max_attn_len, contextual_seq_len):
+        from .hstu_attention import hstu_attention_fwd
+
+        M = x.shape[0]
+        hv, ha = hidden_dim * num_heads, attn_dim * num_heads
+        nw = norm_weight.to(x.dtype).contiguous()
+        nb = norm_bias.to(x.dtype).contiguous()
+        w = weight.to(x.dtype).contiguous()
+        b = bias.to(x.dtype).contiguous()
+        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv)
+        v = uvqk[:, hv:2 * hv].view(M, num_heads, hidden_dim)
+        q = uvqk[:, 2 * hv:2 * hv + ha].view(M, num_heads, attn_dim)
+        k = uvqk[:, 2 * hv + ha:].view(M, num_heads, attn_dim)
+        plan = any(ctx.needs_input_grad[:6])
+        ctx.set_materialize_grads(False)  # k / v usually get no gradient: do not add zeros for them
+        out = hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, None, max_attn_len,
+                                 contextual_seq_len, 0, bias_by_distance, plan_for_backward=plan)
+        ctx.planned_scratch = None
+        if plan:
+            out, ctx.planned_scratch = out
+        ctx.save_for_backward(x, nw, nb, w, uvqk, mean, rstd, seq_offsets, num_targets, bias_by_distance)
+        ctx.cfg = (eps, num_heads, attn_dim, hidden_dim, max_seq_len, alpha, max_attn_len, contextual_seq_len,
+                   norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
+        return u, out, k, v
+
+    @staticmethod
+    def backward(ctx, du, dattn, dk_ext, dv_ext):
+        from .hstu_attention import hstu_attention_bwd
+
+        x, nw, nb, w, uvqk, mean, rstd, seq_offsets, num_targets, bias_by_distance = ctx.saved_tensors
+        (eps, H, A, V, max_seq_len, alpha, max_attn_len, contextual_seq_len,
+         nw_dtype, nb_dtype, w_dtype, b_dtype) = ctx.cfg
+        M, N = uvqk.shape
+        hv, ha = V * H, A * H
+        d_uvqk = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        dv = d_uvqk[:, hv:2 * hv].view(M, H, V)
+        dq = d_uvqk[:, 2 * hv:2 * hv + ha].view(M, H, A)
+        dk = d_uvqk[:, 2 * hv + ha:].view(M, H, A)
+        if dattn is None:
+            d_uvqk[:, hv:].zero_()
+        else:
+            if dattn.stride(-1) != 1 or dattn.stride(1) != dattn.shape[2]:
+                dattn = dattn.contiguous()
+            v_ = uvqk[:, hv:2 * hv].view(M, H, V)
+            q_ = uvqk[:, 2 * hv:2 * hv + ha].view(M, H, A)
+            k_ = uvqk[:, 2 * hv + ha:].view(M, H, A)
+            planned, ctx.planned_scratch = ctx.planned_scratch, None
+            hstu_attention_bwd(dattn, max_seq_len, alpha, q_, k_, v_, seq_offsets, num_targets, None, max_attn_len,
+                               contextual_seq_len, 0, dq, dk, dv, bias_by_distance, planned_scratch=planned)
+        if dk_ext is not None:
+            dk.add_(dk_ext)
+        if dv_ext is not None:
+            dv.add_(dv_ext)
+        dx, dnw, dnb, dw, db = _fused_uqvk_backward(x, nw, nb, w, uvqk, mean, rstd, eps, hv, du, d_uvqk)
+        return (dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None, None, None,
+                None, None, None, None, None, None, None)
 
 
 _FUSED_UQVK = True
@@ -346,6 +426,21 @@ def hstu_preprocess_and_attention(
         "uvqk_weight.shape[1] must equal 2 * num_heads * (hidden_dim + attn_dim)",
     )
     torch._assert(causal is True, "only causal attention is supported.")
+    hv = hidden_dim * num_heads
+    if (_FUSED_UQVK and x.is_cuda and _fused_uqvk_supported(x, uvqk_weight, hv)
+            and attn_dim == hidden_dim and attn_dim in (64, 128)):
+        # one autograd node for the stage and the attention (see _FusedPreprocessAttentionFunction)
+        from .hstu_attention import _i32
+        require_cuda(x, norm_weight, norm_bias, uvqk_weight, uvqk_bias, seq_offsets, num_targets, bias_by_distance)
+        offs = _i32(seq_offsets)
+        nt = _i32(num_targets)
+        if nt is not None and nt.numel() != offs.numel() - 1:
+            raise RuntimeError("num_targets must have one entry per sequence")
+        rab = None if bias_by_distance is None else bias_by_distance.to(torch.float32).contiguous()
+        u, attn, k, v = _FusedPreprocessAttentionFunction.apply(
+            x, norm_weight, norm_bias, float(norm_eps), uvqk_weight, uvqk_bias, num_heads, attn_dim, hidden_dim,
+            offs, nt, rab, int(max_seq_len), float(attn_alpha), int(max_attn_len), int(contextual_seq_len))
+        return u, attn.view(-1, hidden_dim * num_heads), k, v
     u, q, k, v = hstu_compute_uqvk(
         x=x, norm_weight=norm_weight, norm_bias=norm_bias, norm_eps=norm_eps, num_heads=num_heads,
         attn_dim=attn_dim, hidden_dim=hidden_dim, uvqk_weight=uvqk_weight, uvqk_bias=uvqk_bias, kernel=kernel,

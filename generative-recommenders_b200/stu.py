@@ -47,11 +47,20 @@ class STULayerConfig:
     rel_bias_buckets: int = 0  # extension: > 0 adds a bucketised relative position bias
 
 
+_BUCKETS = {}  # (n, buckets, device) -> bucket index of every distance: the same for all layers and steps
+
+
 def position_bias_by_distance(table: torch.Tensor, n: int) -> torch.Tensor:
     """``bias[dist] = table[bucket(dist)]`` for ``dist`` in ``[0, n)`` (fp32)."""
     nb = table.numel() - 1
-    d = torch.arange(n, device=table.device, dtype=torch.float32).clamp(min=1.0)
-    bucket = torch.clamp((torch.log(d) / 0.301).long(), min=0, max=nb)
+    key = (n, nb, table.device)
+    bucket = _BUCKETS.get(key)
+    if bucket is None:
+        d = torch.arange(n, device=table.device, dtype=torch.float32).clamp(min=1.0)
+        bucket = torch.clamp((torch.log(d) / 0.301).long(), min=0, max=nb)
+        if len(_BUCKETS) > 64:
+            _BUCKETS.clear()
+        _BUCKETS[key] = bucket
     return table.to(torch.float32)[bucket].contiguous()
 
 
