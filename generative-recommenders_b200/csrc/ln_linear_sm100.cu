@@ -62,6 +62,7 @@ struct LLParams {
   int D, N, silu_cols;
   int kc;                 // D / 64
   int stages;
+  int nsplit;             // CTAs sharing one row block, each with its own range of column tiles
   float eps;
 };
 
@@ -250,8 +251,12 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_blocks = (int)((p.M + LL_BM - 1) / LL_BM);
+  // work units: (row block, split) - with fewer row blocks than SMs the column tiles of a block
+  // are divided among nsplit CTAs (each loads the x block and computes the statistics itself)
   const int n_tiles = (p.N + LL_BN - 1) / LL_BN;
+  const int num_units = (int)((p.M + LL_BM - 1) / LL_BM) * p.nsplit;
+  auto tile_lo = [&](int unit) { return ((unit % p.nsplit) * n_tiles) / p.nsplit; };
+  auto tile_hi = [&](int unit) { return ((unit % p.nsplit + 1) * n_tiles) / p.nsplit; };
   const int KC = p.kc, ST = p.stages;
 
   if (warp == 0) {
@@ -262,9 +267,10 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       uint32_t slot = 0, sphase = 0;  // ring position of the next W' stage and the parity of its round
       int it = 0;
       bool ok = true;
-      for (int blk = blockIdx.x; blk < num_blocks && ok; blk += gridDim.x, ++it) {
-        const int total_b = n_tiles * KC;
-        int issued = 0, bn = 0, bk = 0;
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
+        const int blk = unit / p.nsplit;
+        const int total_b = (tile_hi(unit) - tile_lo(unit)) * KC;
+        int issued = 0, bn = tile_lo(unit), bk = 0;
         auto issue_b = [&](int upto) {
           for (; issued < upto && ok; ++issued) {
             ok = mbar_wait(wc, b_empty + 8 * slot, sphase ^ 1, 1101);
@@ -300,8 +306,9 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       bool ok = true;
       const uint64_t a_desc0 = make_smem_desc(sA, 16, 1024);
       const uint64_t b_desc0 = make_smem_desc(sB, LL_B_BOX, 1024);
-      for (int blk = blockIdx.x; blk < num_blocks && ok; blk += gridDim.x, ++it) {
-        for (int n = 0; n < n_tiles && ok; ++n, ++tcount) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
+        const int n_lo = tile_lo(unit), n_hi = tile_hi(unit);
+        for (int n = n_lo; n < n_hi && ok; ++n, ++tcount) {
           const int n0 = n * LL_BN;
           const int nt = (p.N - n0) >= LL_BN ? LL_BN : (p.N - n0);
           const uint32_t idesc = make_idesc(FMT, FMT, 0, 1, LL_BM, (uint32_t)nt);
@@ -311,7 +318,7 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * LL_BN;
           for (int kc = 0; kc < KC; ++kc) {
-            if (n == 0) {
+            if (n == n_lo) {
               ok = mbar_wait(wc, a_full + 8 * kc, it & 1, 1202);
               if (!ok) break;
             }
@@ -331,7 +338,7 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
           tc_commit(acc_full + 8 * buf);
         }
         // nobody waits for the x buffer after this CTA's last block
-        if (ok && blk + (int)gridDim.x < num_blocks) tc_commit(a_empty);
+        if (ok && unit + (int)gridDim.x < num_units) tc_commit(a_empty);
       }
     }
     __syncwarp();
@@ -353,7 +360,11 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     bool ok = true;
     const bool wide = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0 && (p.out_rs & 15) == 0 &&
                       (p.u == nullptr || ((reinterpret_cast<uintptr_t>(p.u) & 31) == 0 && (p.u_rs & 15) == 0));
-    for (int blk = blockIdx.x; blk < num_blocks && ok; blk += gridDim.x, ++it) {
+    int nxt_tile = 0;  // the column tile whose c1 / c2 are in nxt1 / nxt2
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
+      const int blk = unit / p.nsplit;
+      const int n_lo = tile_lo(unit), n_hi = tile_hi(unit);
+      const bool first_split = unit % p.nsplit == 0;
       const int64_t row = (int64_t)blk * LL_BM + row_in_blk;
       const bool row_ok = row < p.M;
       // ---- row statistics from the x block in shared memory (shifted sums; the order of the
@@ -387,15 +398,23 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       const float var = fmaxf(s2 * inv_d - m_sh * m_sh, 0.f);
       const float rstd = rsqrtf(var + p.eps);
       if (row_ok) {
-        if (p.mean) p.mean[row] = mean;
-        if (p.rstd) p.rstd[row] = rstd;
+        if (p.mean && first_split) p.mean[row] = mean;
+        if (p.rstd && first_split) p.rstd[row] = rstd;
       }
       const float neg_mr = -mean * rstd;
       // ---- epilogue of every column tile of this block
-      for (int n = 0; n < n_tiles && ok; ++n, ++tcount) {
+      for (int n = n_lo; n < n_hi && ok; ++n, ++tcount) {
         const int n0 = n * LL_BN;
         const int nt = (p.N - n0) >= LL_BN ? LL_BN : (p.N - n0);
         const uint32_t buf = tcount & 1;
+        if (nxt_tile != n) {  // first tile of a unit that does not continue the previous one
+#pragma unroll
+          for (int cc = 0; cc < LL_BN / 32; ++cc) {
+            const int col = n0 + cc * 32 + lane;
+            nxt1[cc] = col < p.N ? __ldg(p.c1 + col) : 0.f;
+            nxt2[cc] = col < p.N ? __ldg(p.c2 + col) : 0.f;
+          }
+        }
         ok = mbar_wait(wc, acc_full + 8 * buf, (tcount >> 1) & 1, 1302);
         if (!ok) break;
         tc_fence_after();
@@ -412,7 +431,8 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
           cur2[cc] = nxt2[cc];
         }
         {
-          const int nn0 = (n + 1 < n_tiles ? n + 1 : 0) * LL_BN;
+          nxt_tile = n + 1 < n_hi ? n + 1 : tile_lo(unit + (int)gridDim.x);
+          const int nn0 = nxt_tile * LL_BN;
 #pragma unroll
           for (int cc = 0; cc < LL_BN / 32; ++cc) {
             const int col = nn0 + cc * 32 + lane;
@@ -521,7 +541,15 @@ static int ln_linear_t(const b200_hstu_ln_linear_args &a, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return check_cuda(e, "ln_linear smem attribute");
   const int64_t blocks = (a.M + LL_BM - 1) / LL_BM;
-  const int grid = (int)(blocks < device_sm_count() ? blocks : device_sm_count());
+  const int n_tiles = (a.N + LL_BN - 1) / LL_BN;
+  int nsplit = 1;
+  if (blocks < device_sm_count()) {
+    nsplit = (int)(device_sm_count() / blocks);
+    nsplit = nsplit > n_tiles ? n_tiles : nsplit;
+  }
+  p.nsplit = nsplit;
+  const int64_t units = blocks * nsplit;
+  const int grid = (int)(units < device_sm_count() ? units : device_sm_count());
   {
     ProfileScope prof(PROF_LN_LINEAR, st);
     kern<<<grid, LL_THREADS, smem, st>>>(mx, mw, p);
