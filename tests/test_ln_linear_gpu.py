@@ -92,3 +92,47 @@ def test_fused_uqvk_unsupported_shapes_take_the_separate_stages():
     a = G._cabi.LnLinearArgs()
     a.D, a.N, a.M, a.dtype = 32, 128, 4, G._cabi.BF16
     assert G._cabi.lib().b200_hstu_ln_linear_silu_fwd(a, None) == -2
+
+
+@pytest.mark.parametrize("ctx,W_", [(0, 0), (4, 50)])
+def test_fused_layer_gradients_match_oracle(ctx, W_):
+    """A bf16 STU layer through the single autograd node (fused uvqk stage + attention, whose
+    backward writes dq / dk / dv into the stage's gradient buffer): output, input gradient and all
+    parameter gradients against fp32 autograd through the oracle, and against the separate stages."""
+    torch.manual_seed(5)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    D, H, d = 256, 2, 128
+    cfg = G.STULayerConfig(embedding_dim=D, num_heads=H, hidden_dim=d, attention_dim=d, output_dropout_ratio=0.0,
+                           contextual_seq_len=ctx, max_attn_len=W_)
+    layer = G.STULayer(cfg).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        for p_ in layer.parameters():
+            if p_.dim() == 1:
+                p_.add_(0.1 * torch.randn_like(p_))
+    lengths = torch.tensor([130, 300, 17, 257, 64])
+    nt = torch.tensor([3, 20, 1, 9, 5])
+    offs = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(lengths, 0)])
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(int(offs[-1]), D, generator=g).bfloat16()
+    dy = torch.randn(int(offs[-1]), D, generator=g).bfloat16()
+    res = {}
+    for fused in (True, False):
+        HC.set_fused_uqvk(fused)
+        layer.zero_grad()
+        xin = x.to(DEV).requires_grad_(True)
+        n0 = G._cabi.launch_count()
+        y = layer(xin, lengths.to(DEV), offs.to(DEV), 320, nt.to(DEV))
+        y.backward(dy.to(DEV))
+        res[fused] = (y.detach().float().cpu(), xin.grad.float().cpu(),
+                      {n: p_.grad.float().cpu() for n, p_ in layer.named_parameters()}, G._cabi.launch_count() - n0)
+    HC.set_fused_uqvk(True)
+    params = {n[1:]: p_.detach().float().cpu().requires_grad_(True) for n, p_ in layer.named_parameters()}
+    xr = x.float().requires_grad_(True)
+    ref = O.stu_layer(xr, offs, 320, nt, params, H, d, d, max_attn_len=W_, contextual_seq_len=ctx)
+    ref.backward(dy.float())
+    y, dx, grads, _ = res[True]
+    assert O.rel_l2(y, ref.detach()) < 2e-2
+    assert O.rel_l2(dx, xr.grad) < 3e-2
+    for n, gr in grads.items():
+        assert O.rel_l2(gr, params[n[1:]].grad) < 3e-2, n
+        assert O.rel_l2(gr, res[False][2][n]) < 3e-2, n
