@@ -210,12 +210,18 @@ struct PairItem {
 
 __host__ __device__ __forceinline__ void fill_pair_item(PairItem &p, const AttnGeomParams &g, int b, int pair,
                                                         int start, int len, int nt) {
-  fill_q_item(p.A, g, b, 2 * pair, start, len, nt);
-  const int ntiles = q_tiles_of(g, p.A.m.L);
-  p.hasB = (2 * pair + 1) < ntiles;
+  // With an odd number of query tiles the tile left without a partner is the FIRST one (a single
+  // kv tile), not the last and most expensive one: a query tile on its own cannot overlap its
+  // score products with its activation and runs ~1.6x longer per kv tile.
+  const int L = len < g.max_seq_len ? len : g.max_seq_len;
+  const int ntiles = q_tiles_of(g, L);
+  const bool odd = (ntiles & 1) != 0;
+  const int first = odd ? (pair == 0 ? 0 : 2 * pair - 1) : 2 * pair;
+  fill_q_item(p.A, g, b, first, start, len, nt);
+  p.hasB = !(odd && pair == 0) && (first + 1) < ntiles;
   int lo = p.A.t_lo, hi = p.A.t_lo + p.A.n_main;
   if (p.hasB) {
-    fill_q_item(p.B, g, b, 2 * pair + 1, start, len, nt);
+    fill_q_item(p.B, g, b, first + 1, start, len, nt);
     lo = p.B.t_lo < lo ? p.B.t_lo : lo;
     int bh = p.B.t_lo + p.B.n_main;
     hi = bh > hi ? bh : hi;
@@ -332,7 +338,8 @@ __host__ __device__ __forceinline__ int item_cost(const AttnGeomParams &g, int b
   if (KIND == PLAN_Q_PAIR) {
     PairItem p;
     fill_pair_item(p, g, b, t, 0, len, nt);
-    return p.A.n_tiles + p.B.n_tiles;
+    // a query tile without a partner takes about 1.6x as long per kv tile
+    return p.hasB ? p.A.n_tiles + p.B.n_tiles : (p.A.n_tiles * 8 + 4) / 5;
   } else if (KIND == PLAN_Q_TILE) {
     TileItem it;
     fill_q_item(it, g, b, t, 0, len, nt);
