@@ -124,35 +124,51 @@ __device__ __forceinline__ void row_stats(const Row<E, MAXV> &x, int D, int lane
 // ---------------------------------------------------------------------------------------
 // LayerNorm
 // ---------------------------------------------------------------------------------------
+// Registers bound the number of resident warps, and with it the bytes in flight: on the vector
+// path weight and bias stay packed (16-byte vectors, converted where they are used) and the kernel
+// is compiled for three resident CTAs (four cost more in spills than they gain).
 template <typename E, int MAXV>
-__global__ void __launch_bounds__(WARPS * 32) layer_norm_fwd_kernel(const E *__restrict__ x, int64_t x_rs,
-                                                                    const E *__restrict__ w,
-                                                                    const E *__restrict__ b, E *__restrict__ y,
-                                                                    int64_t y_rs, float *__restrict__ mean_out,
-                                                                    float *__restrict__ rstd_out, int64_t rows,
-                                                                    int D, float eps, bool vec_ok) {
+__global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 3 : (MAXV <= 4 ? 2 : 1)) layer_norm_fwd_kernel(
+    const E *__restrict__ x, int64_t x_rs, const E *__restrict__ w, const E *__restrict__ b, E *__restrict__ y,
+    int64_t y_rs, float *__restrict__ mean_out, float *__restrict__ rstd_out, int64_t rows, int D, float eps,
+    bool vec_ok) {
   constexpr int EV = VecInfo<E>::EV;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  Row<E, MAXV> wr, br;
-  wr.load(w, D, lane, vec_ok);
-  br.load(b, D, lane, vec_ok);
   const int64_t step = (int64_t)gridDim.x * WARPS;
   int64_t row = (int64_t)blockIdx.x * WARPS + warp;
   constexpr bool PF = MAXV <= 4;  // one-row-ahead prefetch only while the registers allow it
-  const bool pf = PF && vec_ok;
-  RawRow<E, PF ? MAXV : 1> nxt;
-  if (pf && row < rows) nxt.load(x + row * x_rs, D, lane);
-  for (; row < rows; row += step) {
-    Row<E, MAXV> xr;
-    bool loaded = false;
-    if constexpr (PF) {
-      if (pf) {
-        nxt.unpack(xr);
-        if (row + step < rows) nxt.load(x + (row + step) * x_rs, D, lane);
-        loaded = true;
+  if (PF && vec_ok) {
+    RawRow<E, PF ? MAXV : 1> wraw, braw, nxt;
+    wraw.load(w, D, lane);
+    braw.load(b, D, lane);
+    if (row < rows) nxt.load(x + row * x_rs, D, lane);
+    for (; row < rows; row += step) {
+      Row<E, PF ? MAXV : 1> xr;
+      nxt.unpack(xr);
+      if (row + step < rows) nxt.load(x + (row + step) * x_rs, D, lane);
+      float mean, rstd;
+      row_stats(xr, D, lane, eps, mean, rstd);
+#pragma unroll
+      for (int k = 0; k < (PF ? MAXV : 1); ++k) {
+        const E *pw = reinterpret_cast<const E *>(&wraw.v[k]);
+        const E *pb = reinterpret_cast<const E *>(&braw.v[k]);
+#pragma unroll
+        for (int t = 0; t < EV; ++t) xr.v[k][t] = (xr.v[k][t] - mean) * rstd * to_f32(pw[t]) + to_f32(pb[t]);
+      }
+      xr.store(y + row * y_rs, D, lane, true);
+      if (lane == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (rstd_out) rstd_out[row] = rstd;
       }
     }
-    if (!loaded) xr.load(x + row * x_rs, D, lane, vec_ok);
+    return;
+  }
+  Row<E, MAXV> wr, br;
+  wr.load(w, D, lane, vec_ok);
+  br.load(b, D, lane, vec_ok);
+  for (; row < rows; row += step) {
+    Row<E, MAXV> xr;
+    xr.load(x + row * x_rs, D, lane, vec_ok);
     float mean, rstd;
     row_stats(xr, D, lane, eps, mean, rstd);
 #pragma unroll
@@ -190,7 +206,7 @@ __device__ __forceinline__ void reduce_columns_to_partial(const Row<E, MAXV> &ac
 }
 
 template <typename E, int MAXV>
-__global__ void __launch_bounds__(WARPS * 32) layer_norm_bwd_kernel(
+__global__ void __launch_bounds__(WARPS * 32, 2) layer_norm_bwd_kernel(
     const E *__restrict__ dy, int64_t dy_rs, const E *__restrict__ x, int64_t x_rs, const E *__restrict__ w,
     const float *__restrict__ mean_in, const float *__restrict__ rstd_in, E *__restrict__ dx, int64_t dx_rs,
     float *__restrict__ partial, int64_t rows, int D, bool vec_ok) {
