@@ -45,7 +45,7 @@ constexpr int LL_KC = 64;             // K per shared-memory sub-tile / stage
 constexpr int LL_A_SUB = LL_BM * 128; // bytes of one x sub-tile (128 rows x 64 elements)
 constexpr int LL_B_BOX = LL_KC * 128; // bytes of one W' box (64 k x 64 n)
 constexpr int LL_B_STAGE = 4 * LL_B_BOX;
-constexpr int LL_MAX_STAGES = 4;
+constexpr int LL_MAX_STAGES = 6;
 constexpr int LL_MAX_KC = 8;          // D <= 512
 constexpr int LL_MISC = 2048;         // barriers, TMEM slot, abort flag | per-warp c1 / c2 staging
 constexpr int LL_SMEM_LIMIT = 232448;
