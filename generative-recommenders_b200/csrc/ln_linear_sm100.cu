@@ -11,7 +11,7 @@
 //                                                 c2[n] = sum_k beta[k] W[k, n] + bias[n]
 // so the tensor cores multiply the raw rows of x (exact 16-bit products, fp32 accumulation) and the
 // per-row statistics are only needed by the epilogue; they are computed from the x tile in shared
-// memory while the first products run.  W', c1 and c2 come from a small preparation kernel.
+// memory while the first products run.  W', c1 and c2 come from two small preparation launches.
 //
 // One CTA per SM walks 128-row blocks of x:
 //   warp 0      producer: TMA loads of the x block (all of K, D / 64 sub-tiles of 128 x 64) and of W'
@@ -152,47 +152,80 @@ template <bool IS_BF16> struct EpiChunk {
 };
 
 // ---------------------------------------------------------------------------------------
-// preparation: W' = gamma (.) W, c1 = column sums of W', c2 = beta W + bias
-// grid: N / 32 CTAs of 512 threads; thread (kg = tid / 32, col = tid % 32) covers rows kg, kg + 16, ...
+// preparation: W' = gamma (.) W, c1 = column sums of W', c2 = beta W + bias, in two small launches:
+//   1. grid (N / 256, D / 32): a CTA takes 32 rows x 256 columns of W (16-byte vectors, 8 columns
+//      per lane, 4 rows per warp), writes W' and its partial column sums part[split][{c1, c2}][N]
+//   2. one thread per column adds the partial sums in a fixed order (and the bias)
 // ---------------------------------------------------------------------------------------
+constexpr int PREP_ROWS = 32, PREP_COLS = 256;
+
 template <typename E>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(256)
 ln_linear_prep_kernel(const E *__restrict__ W, const E *__restrict__ gamma, const E *__restrict__ beta,
-                      const E *__restrict__ bias, E *__restrict__ Wp, float *__restrict__ c1, float *__restrict__ c2,
-                      int *status, int D, int N) {
-  __shared__ float s1[16][32], s2[16][32];
-  const int col = blockIdx.x * 32 + (threadIdx.x & 31);
-  const int kg = threadIdx.x >> 5;
-  float a1 = 0.f, a2 = 0.f;
-  if (col < N) {
-    for (int k0 = kg; k0 < D; k0 += 16 * 8) {
-      float w[8];
+                      E *__restrict__ Wp, float *__restrict__ part, int D, int N) {
+  __shared__ float s1[8][PREP_COLS], s2[8][PREP_COLS];
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  const int col0 = blockIdx.x * PREP_COLS + lane * 8;
+  const int k0 = blockIdx.y * PREP_ROWS;
+  float a1[8], a2[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int k = k0 + 16 * i;
-        w[i] = k < D ? to_f32(W[(int64_t)k * N + col]) : 0.f;
-      }
+  for (int t = 0; t < 8; ++t) a1[t] = a2[t] = 0.f;
+  if (col0 < N) {  // N is a multiple of 64, so a lane's 8 columns are all in or all out
+    uint4 raw[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int k = k0 + 16 * i;
-        if (k < D) {
-          const E wp = from_f32<E>(w[i] * to_f32(gamma[k]));
-          Wp[(int64_t)k * N + col] = wp;
-          a1 += to_f32(wp);
-          a2 = fmaf(to_f32(beta[k]), w[i], a2);
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + wp + 8 * i;
+      raw[i] = k < D ? __ldg(reinterpret_cast<const uint4 *>(W + (int64_t)k * N + col0)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + wp + 8 * i;
+      if (k < D) {
+        const float gk = to_f32(gamma[k]), bk = to_f32(beta[k]);
+        const E *pe = reinterpret_cast<const E *>(&raw[i]);
+        uint4 outv;
+        E *po = reinterpret_cast<E *>(&outv);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const float w = to_f32(pe[t]);
+          po[t] = from_f32<E>(w * gk);
+          a1[t] += to_f32(po[t]);
+          a2[t] = fmaf(bk, w, a2[t]);
         }
+        *reinterpret_cast<uint4 *>(Wp + (int64_t)k * N + col0) = outv;
       }
     }
   }
-  s1[kg][threadIdx.x & 31] = a1;
-  s2[kg][threadIdx.x & 31] = a2;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    s1[wp][lane * 8 + t] = a1[t];
+    s2[wp][lane * 8 + t] = a2[t];
+  }
   __syncthreads();
-  if (kg == 0 && col < N) {
+  const int c = threadIdx.x, col = blockIdx.x * PREP_COLS + c;
+  if (col < N) {
     float t1 = 0.f, t2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      t1 += s1[i][threadIdx.x];
-      t2 += s2[i][threadIdx.x];
+    for (int i = 0; i < 8; ++i) {
+      t1 += s1[i][c];
+      t2 += s2[i][c];
+    }
+    float *dst = part + (int64_t)blockIdx.y * 2 * N;
+    dst[col] = t1;
+    dst[N + col] = t2;
+  }
+}
+
+template <typename E>
+__global__ void __launch_bounds__(256)
+ln_linear_prep_sum_kernel(const float *__restrict__ part, int splits, const E *__restrict__ bias,
+                          float *__restrict__ c1, float *__restrict__ c2, int *status, int N) {
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col < N) {
+    float t1 = 0.f, t2 = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      t1 += part[(int64_t)s * 2 * N + col];
+      t2 += part[(int64_t)s * 2 * N + N + col];
     }
     c1[col] = t1;
     c2[col] = t2 + (bias ? to_f32(bias[col]) : 0.f);
@@ -495,9 +528,10 @@ bool ln_linear_supported(int D, int N, int silu_cols, int dtype, const char **wh
   return true;
 }
 
-// workspace: [status (256 B) | W' | c1 | c2]
+// workspace: [status (256 B) | W' | c1 | c2 | partial column sums of the preparation]
 int64_t ln_linear_workspace_bytes(int D, int N) {
-  return 256 + align256((int64_t)D * N * 2) + 2 * align256((int64_t)N * 4);
+  const int splits = (D + PREP_ROWS - 1) / PREP_ROWS;
+  return 256 + align256((int64_t)D * N * 2) + 2 * align256((int64_t)N * 4) + align256((int64_t)splits * 2 * N * 4);
 }
 
 template <typename E, bool IS_BF16>
@@ -509,11 +543,17 @@ static int ln_linear_t(const b200_hstu_ln_linear_args &a, cudaStream_t st) {
   float *c2 = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(c1) + align256((int64_t)a.N * 4));
   if (!a.weights_prepared) {
     ProfileScope prof(PROF_LN_LINEAR_PREP, st);
-    ln_linear_prep_kernel<E><<<(a.N + 31) / 32, 512, 0, st>>>(
-        (const E *)a.weight, (const E *)a.norm_weight, (const E *)a.norm_bias, (const E *)a.bias, Wp, c1, c2, status,
-        a.D, a.N);
+    float *part = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(c2) + align256((int64_t)a.N * 4));
+    const int splits = (a.D + PREP_ROWS - 1) / PREP_ROWS;
+    dim3 grid((a.N + PREP_COLS - 1) / PREP_COLS, splits);
+    ln_linear_prep_kernel<E><<<grid, 256, 0, st>>>((const E *)a.weight, (const E *)a.norm_weight,
+                                                   (const E *)a.norm_bias, Wp, part, a.D, a.N);
     count_launch();
     B200_CHECK_LAUNCH("ln_linear_prep_kernel");
+    ln_linear_prep_sum_kernel<E><<<(a.N + 255) / 256, 256, 0, st>>>(part, splits, (const E *)a.bias, c1, c2, status,
+                                                                    a.N);
+    count_launch();
+    B200_CHECK_LAUNCH("ln_linear_prep_sum_kernel");
   }
   CUtensorMap mx, mw;
   int rc;
@@ -568,7 +608,7 @@ int ln_linear_fwd(const b200_hstu_ln_linear_args &a, cudaStream_t st) {
   if (!a.x || !a.norm_weight || !a.norm_bias || !a.weight || !a.out)
     return fail(B200_HSTU_EINVAL, "ln_linear: NULL tensor");
   auto al16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-  if (!al16(a.x) || !al16(a.out) || (a.u && !al16(a.u)) || !al16(a.workspace) || a.x_row_stride % 8 ||
+  if (!al16(a.x) || !al16(a.out) || (a.u && !al16(a.u)) || !al16(a.workspace) || !al16(a.weight) || a.x_row_stride % 8 ||
       a.out_row_stride % 8 || (a.u && a.u_row_stride % 8))
     return fail(B200_HSTU_EUNSUPPORTED, "ln_linear: tensors must be 16-byte aligned with 16-byte row strides");
   if (a.workspace == nullptr || a.workspace_bytes < ln_linear_workspace_bytes(a.D, a.N))
