@@ -1,6 +1,7 @@
 """The LayerNorm + linear stages around the attention, with the reference's signatures
 (generative_recommenders/ops/hstu_compute.py:54-335)."""
 
+import weakref
 from typing import Optional, Tuple
 
 import torch
@@ -57,7 +58,31 @@ def _fused_uqvk_supported(x, uvqk_weight, hv) -> bool:
     return bool(_cabi.lib().b200_hstu_ln_linear_supported(D, N, hv, dtype_code(x)))
 
 
-def _fused_uqvk_launch(x, nw, nb, eps, w, b, hv):
+# Inference only: the workspace of the fused kernel holds what the preparation launches derive from
+# the four parameter tensors (W' = diag(gamma) W and two column vectors).  While those tensors are
+# alive and unmodified (same objects, same storage, same version counters) the workspace is kept
+# and the preparation is skipped.
+_PREPARED = {}
+
+
+def _prepared_workspace(nw, nb, w, b, nbytes, device, allow_cache):
+    # only module parameters are worth remembering (a cast copy made for one call never comes back)
+    if (not allow_cache or not isinstance(w, torch.nn.Parameter)
+            or torch.cuda.is_current_stream_capturing()):
+        return torch.empty(nbytes, dtype=torch.uint8, device=device), False
+    key = id(w)
+    sig = tuple((id(t), t.data_ptr(), t._version) for t in (w, nw, nb, b))
+    hit = _PREPARED.get(key)
+    if hit is not None and hit[0]() is w and hit[1] == sig and hit[2].numel() == nbytes:
+        return hit[2], True
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    if len(_PREPARED) > 256:
+        _PREPARED.clear()
+    _PREPARED[key] = (weakref.ref(w), sig, ws)
+    return ws, False
+
+
+def _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, allow_cache=False):
     """One launch of the fused kernel: returns (uvqk [M, N], u [M, hv], mean [M], rstd [M])."""
     M, D = x.shape
     N = w.shape[1]
@@ -66,8 +91,9 @@ def _fused_uqvk_launch(x, nw, nb, eps, w, b, hv):
     mean = torch.empty(M, dtype=torch.float32, device=x.device)
     rstd = torch.empty(M, dtype=torch.float32, device=x.device)
     nbytes = _cabi.lib().b200_hstu_ln_linear_workspace_bytes(D, N)
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    ws, prepared = _prepared_workspace(nw, nb, w, b, nbytes, x.device, allow_cache)
     a = _cabi.LnLinearArgs()
+    a.weights_prepared = 1 if prepared else 0
     a.x, a.norm_weight, a.norm_bias, a.weight, a.bias = (x.data_ptr(), nw.data_ptr(), nb.data_ptr(),
                                                           w.data_ptr(), b.data_ptr())
     a.out, a.u, a.mean, a.rstd = uvqk.data_ptr(), u.data_ptr(), mean.data_ptr(), rstd.data_ptr()
@@ -133,7 +159,7 @@ class _FusedUqvkFunction(torch.autograd.Function):
         nb = norm_bias.to(x.dtype).contiguous()
         w = weight.to(x.dtype).contiguous()
         b = bias.to(x.dtype).contiguous()
-        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv)
+        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, not any(ctx.needs_input_grad))
         ctx.set_materialize_grads(False)
         ctx.save_for_backward(x, nw, nb, w, uvqk, mean, rstd)
         ctx.cfg = (eps, hv, ha, norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
@@ -175,7 +201,7 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
         nb = norm_bias.to(x.dtype).contiguous()
         w = weight.to(x.dtype).contiguous()
         b = bias.to(x.dtype).contiguous()
-        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv)
+        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, not any(ctx.needs_input_grad))
         v = uvqk[:, hv:2 * hv].view(M, num_heads, hidden_dim)
         q = uvqk[:, 2 * hv:2 * hv + ha].view(M, num_heads, attn_dim)
         k = uvqk[:, 2 * hv + ha:].view(M, num_heads, attn_dim)

@@ -136,3 +136,38 @@ def test_fused_layer_gradients_match_oracle(ctx, W_):
     for n, gr in grads.items():
         assert O.rel_l2(gr, params[n[1:]].grad) < 3e-2, n
         assert O.rel_l2(gr, res[False][2][n]) < 3e-2, n
+
+
+def test_prepared_weights_are_reused_only_while_unchanged():
+    """Inference with module parameters: the preparation launches are skipped while the parameter
+    tensors are the same unmodified objects, and come back after an in-place update or when a
+    gradient is wanted."""
+    x, nw, nb, W, b = (t.to(DEV) for t in _inputs(300, 256, 2, 64, 64, torch.bfloat16, seed=3))
+    nw, nb, W, b = (torch.nn.Parameter(t, requires_grad=False) for t in (nw, nb, W, b))
+    call = lambda: G.hstu_compute_uqvk(x, nw, nb, 1e-6, 2, 64, 64, W, b)  # noqa: E731
+    first = call()
+    n0 = G._cabi.launch_count()
+    again = call()
+    assert G._cabi.launch_count() - n0 == 1  # the fused kernel alone
+    for a_, b_ in zip(first, again):
+        assert torch.equal(a_, b_)
+    with torch.no_grad():
+        W.mul_(2.0)
+    n0 = G._cabi.launch_count()
+    changed = call()
+    assert G._cabi.launch_count() - n0 == 3
+    assert not torch.equal(changed[1], first[1])
+    ref = O.hstu_compute_uqvk(x.float().cpu(), nw.float().cpu(), nb.float().cpu(), 1e-6, 2, 64, 64,
+                              W.detach().float().cpu(), b.float().cpu())
+    for a_, r_ in zip(changed, ref):
+        assert O.rel_l2(a_.float().cpu(), r_) < 1e-2
+    W.requires_grad_(True)   # training: always prepared afresh
+    call()
+    n0 = G._cabi.launch_count()
+    call()
+    assert G._cabi.launch_count() - n0 == 3
+    # plain tensors (e.g. a cast made for one call) are never remembered
+    n0 = G._cabi.launch_count()
+    G.hstu_compute_uqvk(x, nw.data, nb.data, 1e-6, 2, 64, 64, W.detach().clone(), b.data)
+    G.hstu_compute_uqvk(x, nw.data, nb.data, 1e-6, 2, 64, 64, W.detach().clone(), b.data)
+    assert G._cabi.launch_count() - n0 == 6
