@@ -521,14 +521,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       }
       ok = geom_publish(wc, sched_ring, sched_full, sched_empty, 0, g);
       while (g.idx < num_items && ok) {
-        // claim the next (item, head) index now; its geometry is published below, right after this
-        // item's first requests, a whole item before the other warps need it
-        const int nidx = atomicAdd(&p.plan->next, 1);
+        // The next (item, head) index is claimed while this item's tiles are requested: the
+        // atomic goes out after the first requests, its result is first read one tile later (to
+        // fetch the item's descriptor) and the geometry is computed and published another tile
+        // later - the round trips never sit between two items' requests.
+        int nidx = num_items;
         ItemDesc nd;
-        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
         const int h = g.idx % p.H;
+        const int n_req = g.n_tiles;
+        const int j_desc = n_req > 1 ? 1 : 0, j_geom = n_req > 2 ? 2 : n_req - 1;
         ItemGeom ng = g;
-        ng.idx = nidx;
         tr.mark(1);
         // order of requests = order of first use: X0, Y0(0) feed G1; X1, Y1(0) feed G2
         for (int j = 0; j < g.n_tiles; ++j, ++cnt) {
@@ -565,7 +567,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
             tma_load_2d(sY1 + s1 * SM::TILE_BYTES + c * SM::CHUNK_BYTES, mapY1, h * D + c * 64, row, y1_full + 8 * s1);
-          if (j == 0) {
+          if (j == 0) nidx = atomicAdd(&p.plan->next, 1);
+          if (j == j_desc && nidx < num_items) nd = load_desc(p.items, nidx / p.H);
+          if (j == j_geom) {
+            ng.idx = nidx;
             if (nidx < num_items) {
               TileItem ni;
               fill_bwd_item<DKDV>(ni, p.g, nd);

@@ -365,14 +365,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
       ok = geom_publish(wc, sched_ring, sched_full, sched_empty, 0, g);
       while (g.idx < num_items && ok) {
-        // claim the next (item, head) index now; its geometry is published below, right after this
-        // item's first requests, a whole item before the other warps need it
-        const int nidx = atomicAdd(&p.plan->next, 1);
+        // The next (item, head) index is claimed while this item's tiles are requested: the
+        // atomic goes out after the first requests, its result is first read one tile later (to
+        // fetch the item's descriptor) and the geometry is computed and published another tile
+        // later - the round trips never sit between two items' requests.
+        int nidx = num_items;
         ItemDesc nd;
-        if (nidx < num_items) nd = load_desc(p.items, nidx / p.H);
         const int h = g.idx % p.H;
+        const int n_req = g.n_tiles;
+        const int j_desc = n_req > 1 ? 1 : 0, j_geom = n_req > 2 ? 2 : n_req - 1;
         PairGeom ng = g;
-        ng.idx = nidx;
         tr.mark(1);
         // order of requests = order of first use: Q_A, K(0) feed S_A; Q_B feeds S_B; then V(0)
         for (int j = 0; j < g.n_tiles; ++j, ++kv_cnt) {
@@ -413,7 +415,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
           for (int c = 0; c < SM::CHUNKS; ++c)
             tma_load_2d(sV + s * SM::TILE_BYTES + c * SM::CHUNK_BYTES, &tmap_v, h * D + c * 64, row, v_full + 8 * s);
-          if (j == 0) {
+          if (j == 0) nidx = atomicAdd(&p.plan->next, 1);
+          if (j == j_desc && nidx < num_items) nd = load_desc(p.items, nidx / p.H);
+          if (j == j_geom) {
+            ng.idx = nidx;
             if (nidx < num_items) {
               PairItem np;
               fill_pair_item(np, p.g, nd.b, nd.t, nd.start, nd.len, nd.nt);

@@ -286,6 +286,98 @@ __global__ void __launch_bounds__(WARPS * 32, 2) layer_norm_bwd_kernel(
   reduce_columns_to_partial(db, smem, prow + D, D, lane, warp);
 }
 
+// The same backward with the two column accumulators (dweight, dbias) of every warp in shared
+// memory instead of registers: 64 registers fewer per thread, so three CTAs instead of two fit an
+// SM and more rows are in flight.  Vector path only (aligned pointers and strides, MAXV <= 2).
+// Shared memory: [2][WARPS][MAXV * EV / 4][32] float4, each lane touching only its own entries.
+template <typename E, int MAXV>
+__global__ void __launch_bounds__(WARPS * 32, 3) layer_norm_bwd_smem_kernel(
+    const E *__restrict__ dy, int64_t dy_rs, const E *__restrict__ x, int64_t x_rs, const E *__restrict__ w,
+    const float *__restrict__ mean_in, const float *__restrict__ rstd_in, E *__restrict__ dx, int64_t dx_rs,
+    float *__restrict__ partial, int64_t rows, int D) {
+  constexpr int EV = VecInfo<E>::EV;
+  constexpr int Q = EV / 4;
+  constexpr int PER_WARP = MAXV * Q * 32;  // float4 entries per warp and accumulator
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float4 *accw = reinterpret_cast<float4 *>(smem) + (size_t)warp * PER_WARP;
+  float4 *accb = reinterpret_cast<float4 *>(smem) + (size_t)(WARPS + warp) * PER_WARP;
+#pragma unroll
+  for (int i = 0; i < MAXV * Q; ++i) {
+    accw[i * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+    accb[i * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  RawRow<E, MAXV> wraw, nx, ng;
+  wraw.load(w, D, lane);
+  const float invD = 1.f / (float)D;
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  float nmean = 0.f, nrstd = 0.f;
+  if (row < rows) {
+    nx.load(x + row * x_rs, D, lane);
+    ng.load(dy + row * dy_rs, D, lane);
+    nmean = mean_in[row];
+    nrstd = rstd_in[row];
+  }
+  for (; row < rows; row += step) {
+    Row<E, MAXV> xr, gr;
+    nx.unpack(xr);
+    ng.unpack(gr);
+    const float mean = nmean, rstd = nrstd;
+    if (row + step < rows) {
+      nx.load(x + (row + step) * x_rs, D, lane);
+      ng.load(dy + (row + step) * dy_rs, D, lane);
+      nmean = mean_in[row + step];
+      nrstd = rstd_in[row + step];
+    }
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const E *pw = reinterpret_cast<const E *>(&wraw.v[k]);
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        float4 aw = accw[(k * Q + q) * 32 + lane], ab = accb[(k * Q + q) * 32 + lane];
+        float *paw = reinterpret_cast<float *>(&aw), *pab = reinterpret_cast<float *>(&ab);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int t = q * 4 + c;
+          const int e = (k * 32 + lane) * EV + t;
+          const float xhat = e < D ? (xr.v[k][t] - mean) * rstd : 0.f;
+          const float g = gr.v[k][t];
+          paw[c] += g * xhat;
+          pab[c] += g;
+          const float gw = g * to_f32(pw[t]);
+          xr.v[k][t] = xhat;
+          gr.v[k][t] = gw;
+          c1 += gw * xhat;
+          c2 += gw;
+        }
+        accw[(k * Q + q) * 32 + lane] = aw;
+        accb[(k * Q + q) * 32 + lane] = ab;
+      }
+    }
+    c1 = warp_sum(c1) * invD;
+    c2 = warp_sum(c2) * invD;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) gr.v[k][t] = (gr.v[k][t] - c2 - xr.v[k][t] * c1) * rstd;
+    gr.store(dx + row * dx_rs, D, lane, true);
+  }
+  __syncthreads();
+  float *prow = partial + (int64_t)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * D; i += WARPS * 32) {
+    const int which = i >= D ? 1 : 0;
+    const int e = i - which * D;
+    const int t = e % EV, l = (e / EV) & 31, k = e / (EV * 32);
+    const int idx = (((k * Q + t / 4) * 32 + l) << 2) + (t & 3);
+    float sum = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < WARPS; ++wv) sum += smem[(size_t)(which * WARPS + wv) * PER_WARP * 4 + idx];
+    prow[i] = sum;
+  }
+}
+
 // out[which][e] = sum_b partial[b][which][e]   (which in {0,1}).  A CTA takes 32 columns; its
 // eight warps split the partial rows (four loads in flight each) and are added up in a fixed
 // order, so the result does not depend on timing.
@@ -774,6 +866,23 @@ int ln_bwd_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const v
                 dy_rs % EV == 0 && dx_rs % EV == 0;
   size_t smem = (size_t)WARPS * D * sizeof(float);
   ProfileScope prof(PROF_LN_BWD, st);
+  const int maxv = pick_maxv<E>(D);
+  if (vec_ok && D % EV == 0 && maxv <= 2) {
+    // accumulators in shared memory, three resident CTAs
+    const size_t acc_bytes = (size_t)2 * WARPS * maxv * (EV / 4) * 32 * sizeof(float4);
+    if (maxv == 1)
+      layer_norm_bwd_smem_kernel<E, 1><<<grid, WARPS * 32, acc_bytes, st>>>(
+          (const E *)dy, dy_rs, (const E *)x, x_rs, (const E *)w, mean, rstd, (E *)dx, dx_rs, (float *)partial, rows, D);
+    else
+      layer_norm_bwd_smem_kernel<E, 2><<<grid, WARPS * 32, acc_bytes, st>>>(
+          (const E *)dy, dy_rs, (const E *)x, x_rs, (const E *)w, mean, rstd, (E *)dx, dx_rs, (float *)partial, rows, D);
+    count_launch();
+    B200_CHECK_LAUNCH("layer_norm backward");
+    reduce_partial_kernel<E><<<(2 * D + 31) / 32, 256, 0, st>>>((const float *)partial, grid, D, (E *)dw, (E *)db);
+    count_launch();
+    B200_CHECK_LAUNCH("layer_norm backward (reduce)");
+    return 0;
+  }
   DISPATCH_MAXV(pick_maxv<E>(D), {
     auto kern = layer_norm_bwd_kernel<E, MV>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
