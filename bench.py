@@ -653,6 +653,49 @@ def run_uvqk(args):
     print(json.dumps(out), flush=True)
 
 
+def run_layer_norm(args):
+    """``--workload layer_norm``: LayerNorm forward / backward alone on [655 360, 512] bf16 (671 MB per
+    tensor, larger than L2; about 3 GB on the device - a case sized for profiling)."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi
+
+    world, rank, local_rank, dev, dist = _dist_setup()
+    peaks, peak_kind = load_peaks()
+    rows, D = 655360, 512
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(rows, D, generator=g).to(torch.bfloat16).to(dev)
+    dy = torch.randn(rows, D, generator=g).to(torch.bfloat16).to(dev)
+    w_ = torch.randn(D, generator=g).to(torch.bfloat16).to(dev)
+    b_ = torch.randn(D, generator=g).to(torch.bfloat16).to(dev)
+    xr, wr, br = (t.clone().requires_grad_(True) for t in (x, w_, b_))
+    y = G.layer_norm(xr, wr, br, 1e-6)
+    steps = max(3, min(args.steps, 30))
+    res = {}
+    for kind, fn, nbytes in (("layer_norm_fwd", lambda: G.layer_norm(x, w_, b_, 1e-6), rows * D * 2 * 2 + rows * 8),
+                             ("layer_norm_bwd", lambda: torch.autograd.grad(y, (xr, wr, br), dy, retain_graph=True),
+                              rows * D * 2 * 3 + rows * 8)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        _cabi.profile_enable(True)
+        for _ in range(steps):
+            fn()
+        torch.cuda.synchronize()
+        v = _cabi.profile_collect(kind)
+        _cabi.profile_enable(False)
+        ms = sorted(v)[len(v) // 2]
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res[kind] = {"ms": round(ms, 4), "bytes": int(nbytes), "gb_per_s": round(gbs, 1),
+                     "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+    out = {"metric": "layer_norm_hbm_gb_per_s", "value": res["layer_norm_fwd"]["gb_per_s"], "unit": "GB/s", "n_gpus": 1,
+           "steps": steps, "warmup": 3, "ms_per_step": res["layer_norm_fwd"]["ms"], "higher_is_better": True,
+           "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "LayerNorm forward / backward, rows=%d, D=%d (tensors of %.0f MB, larger than L2)"
+                                  % (rows, D, rows * D * 2 / 1e6)},
+           "hbm_peak_gb_per_s": peaks["hbm_gbs"], "peak_source": peak_kind + " (copy)", "stages": res}
+    print(json.dumps(out), flush=True)
+
+
 def run_stages(args):
     """Achieved HBM GB/s of the memory-bound stage kernels (bf16, D = H*dv = 512, rows = tokens of
     configs[4]'s first 400 sequences), from the library's per-kernel events."""
@@ -744,7 +787,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config1",
-                    choices=["config1", "config3", "config3_fp8", "config2_stack", "config4_stack", "stages", "uvqk"])
+                    choices=["config1", "config3", "config3_fp8", "config2_stack", "config4_stack", "stages", "uvqk", "layer_norm"])
     ap.add_argument("--graph", action="store_true", help="config2_stack: replay the step from a CUDA graph")
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (stack workloads)")
     ap.add_argument("--fwd-only", action="store_true", help="time the forward alone (inference)")
@@ -757,6 +800,8 @@ def main():
         run_stages(args)
     elif args.workload == "uvqk":
         run_uvqk(args)
+    elif args.workload == "layer_norm":
+        run_layer_norm(args)
     elif args.workload == "config3_fp8":
         run_fp8(args)
     else:
