@@ -108,6 +108,7 @@ class LnLinearArgs(Structure):
         ("D", c_int32), ("N", c_int32), ("silu_cols", c_int32),
         ("eps", c_float),
         ("dtype", c_int32), ("weights_prepared", c_int32),
+        ("skip_pre_activation", c_int32), ("reserved0", c_int32),
     ]
 
 

@@ -63,6 +63,7 @@ struct LLParams {
   int kc;                 // D / 64
   int stages;
   int nsplit;             // CTAs sharing one row block, each with its own range of column tiles
+  int skip_pre;           // leave out[:, :silu_cols] unwritten
   float eps;
 };
 
@@ -98,7 +99,7 @@ template <bool IS_BF16> struct EpiChunk {
   uint16_t *orow, *urow;  // this row at the tile's first column (urow may be NULL)
   int silu_left;          // silu_cols - first column of the tile
   int lane;
-  bool row_ok, wide;
+  bool row_ok, wide, skip_pre;
   __device__ __forceinline__ void run(const uint32_t (&acc)[32], int cc, float c1_lane, float c2_lane) const {
     __syncwarp();
     my_c1[lane] = c1_lane;
@@ -124,8 +125,9 @@ template <bool IS_BF16> struct EpiChunk {
       o4[x].z = pack2<IS_BF16>(val[8 * x + 4], val[8 * x + 5]);
       o4[x].w = pack2<IS_BF16>(val[8 * x + 6], val[8 * x + 7]);
     }
-    store64(orow + cc * 32, o4);
-    if (urow != nullptr && cc * 32 < silu_left) {
+    const bool is_u = urow != nullptr && cc * 32 < silu_left;
+    if (!(skip_pre && is_u)) store64(orow + cc * 32, o4);
+    if (is_u) {
       // SiLU of the value as stored (rounded to 16 bits), silu(v) = h + h tanh(h), h = v / 2
       uint4 u4[4];
       uint32_t *uw = reinterpret_cast<uint32_t *>(u4);
@@ -475,7 +477,8 @@ ln_linear_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         }
         // The loop stays rolled (two chunks per trip for the register double buffer): the epilogue
         // shares its instruction cache with the MMA and producer threads, whose loops must stay hot.
-        EpiChunk<IS_BF16> ec{rstd, neg_mr, my_c1, my_c2, orow, urow, p.silu_cols - n0, lane, row_ok, wide};
+        EpiChunk<IS_BF16> ec{rstd, neg_mr, my_c1, my_c2, orow, urow, p.silu_cols - n0, lane, row_ok, wide,
+                             p.skip_pre != 0};
         uint32_t r0[32], r1[32];
         tmem_ld32(tacc, r0);
         for (int cc = 0; cc < chunks; cc += 2) {
@@ -588,6 +591,7 @@ static int ln_linear_t(const b200_hstu_ln_linear_args &a, cudaStream_t st) {
     nsplit = nsplit > n_tiles ? n_tiles : nsplit;
   }
   p.nsplit = nsplit;
+  p.skip_pre = (a.skip_pre_activation && a.u) ? 1 : 0;
   const int64_t units = blocks * nsplit;
   const int grid = (int)(units < device_sm_count() ? units : device_sm_count());
   {

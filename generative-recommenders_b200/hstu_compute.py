@@ -94,6 +94,7 @@ def _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, allow_cache=False):
     ws, prepared = _prepared_workspace(nw, nb, w, b, nbytes, x.device, allow_cache)
     a = _cabi.LnLinearArgs()
     a.weights_prepared = 1 if prepared else 0
+    a.skip_pre_activation = 1 if allow_cache else 0   # no gradient wanted: nobody reads the pre-activation u
     a.x, a.norm_weight, a.norm_bias, a.weight, a.bias = (x.data_ptr(), nw.data_ptr(), nb.data_ptr(),
                                                           w.data_ptr(), b.data_ptr())
     a.out, a.u, a.mean, a.rstd = uvqk.data_ptr(), u.data_ptr(), mean.data_ptr(), rstd.data_ptr()

@@ -244,6 +244,9 @@ typedef struct b200_hstu_ln_linear_args {
   int32_t dtype;
   int32_t weights_prepared; /* 1: workspace still holds what an earlier call derived from the same
                                norm_weight / norm_bias / weight / bias values; skips that step */
+  int32_t skip_pre_activation; /* 1 (needs u): out[:, :silu_cols] is left unwritten - only the backward
+                                  reads those columns */
+  int32_t reserved0;
 } b200_hstu_ln_linear_args;
 int b200_hstu_ln_linear_silu_fwd(const b200_hstu_ln_linear_args *args, b200_hstu_stream_t stream);
 int64_t b200_hstu_ln_linear_workspace_bytes(int32_t D, int32_t N);
