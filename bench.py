@@ -11,7 +11,8 @@ only collectives are the barrier / max-reduction used for timing.
 One JSON line is printed by rank 0.  ``value`` is whole-job TFLOP/s of forward + backward counted
 with the nominal causal formula 3.5 * 4*H*d*sum(L^2)/2, measured with CUDA events with the
 inputs resident in HBM.  ``e2e`` is the same metric through the public ``hstu_mha`` with pinned
-host tensors copied in and results copied out inside the timed region.  ``roofline`` describes
+host tensors copied in and results copied out inside the timed region, every step (upload,
+compute and download run on three streams, so consecutive steps overlap).  ``roofline`` describes
 the dominant kernel, ``cpu_baseline`` the CPU oracle timed on the host cores on a bounded
 sample.
 """
@@ -207,26 +208,58 @@ def run_ours(args):
             kernel_ms[kind] = sum(vals) / len(vals)
     _cabi.profile_enable(False)
 
-    # ---- end to end through the public API from pinned host memory
+    # ---- end to end through the public API from pinned host memory.  Every step copies its inputs
+    # host -> device and its results device -> host; the three parts run on three streams (upload,
+    # compute, download) with double-buffered device inputs, so that step i + 1 uploads while step i
+    # computes and step i - 1 downloads - the way an input pipeline feeds a training loop.
     e2e_steps = max(3, min(args.steps, 20))
     res_host = [torch.empty_like(t).pin_memory() for t in ((q,) if fwd_only else (q, q, k, v))]
+    host_in = [hq, hk, hv] + ([] if fwd_only else [hdo])
+    dev_in = [[torch.empty_like(t, device=dev) for t in host_in] for _ in range(2)]
+    s_comp = torch.cuda.current_stream(dev)
+    s_up, s_down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    computed = [None, None]     # event: the step that read dev_in[slot] has finished
+    state = {"i": 0, "last_down": None}
 
     def e2e_step():
-        qd = hq.to(dev, non_blocking=True); kd = hk.to(dev, non_blocking=True)
-        vd = hv.to(dev, non_blocking=True)
-        dod = None if fwd_only else hdo.to(dev, non_blocking=True)
-        out, grads = step(qd, kd, vd, dod)
-        res_host[0].copy_(out, non_blocking=True)
-        if grads is not None:
-            for dst, g in zip(res_host[1:], grads):
-                dst.copy_(g, non_blocking=True)
+        i = state["i"]
+        slot = i & 1
+        with torch.cuda.stream(s_up):
+            if computed[slot] is not None:
+                s_up.wait_event(computed[slot])
+            for dst, src in zip(dev_in[slot], host_in):
+                dst.copy_(src, non_blocking=True)
+            uploaded = torch.cuda.Event()
+            uploaded.record(s_up)
+        s_comp.wait_event(uploaded)
+        bufs = [t.detach() for t in dev_in[slot]]   # fresh aliases: step() marks its inputs as leaves
+        out, grads = step(bufs[0], bufs[1], bufs[2], None if fwd_only else bufs[3])
+        done = torch.cuda.Event()
+        done.record(s_comp)
+        computed[slot] = done
+        results = [out] + (list(grads) if grads is not None else [])
+        with torch.cuda.stream(s_down):
+            s_down.wait_event(done)
+            for dst, g_ in zip(res_host, results):
+                g_.record_stream(s_down)
+                dst.copy_(g_, non_blocking=True)
+            fin = torch.cuda.Event()
+            fin.record(s_down)
+        state["last_down"] = fin
+        state["i"] = i + 1
+
+    def e2e_drain():
+        if state["last_down"] is not None:
+            s_comp.wait_event(state["last_down"])
 
     e2e_step()
+    e2e_drain()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    e2e_drain()
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
