@@ -177,3 +177,41 @@ def test_cached_forward_bf16_matches_full_forward():
         delta_y = stack.cached_forward(delta_x, nt)
         _, full_tail = J.split_2D_jagged(N, full, None, None, None, delta, prime_offsets, None)
     assert O.rel_l2(delta_y, full_tail) < 2e-2
+
+
+def test_full_size_round_trips():
+    """Size-independent properties at the benchmark's size (1.4 M rows of 1 KB): split(concat) is the
+    identity, concat(split) is the identity, and the embedding op is affine in its input."""
+    from generative_recommenders_b200 import workloads as W
+    w = W.config4(400)
+    lengths = w.lengths.to(DEV)
+    B = lengths.numel()
+    offs = torch.cat([lengths.new_zeros(1), torch.cumsum(lengths, 0)])
+    prime = torch.cat([lengths.new_zeros(1), torch.cumsum(lengths - 20, 0)])
+    rows = int(offs[-1])
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = torch.randn(rows, 512, device=DEV, generator=g).to(torch.bfloat16)
+    left, right = J.split_2D_jagged(0, x, None, None, None, 20, prime, None)
+    assert left.shape[0] == rows - 20 * B and right.shape[0] == 20 * B
+    back = J.concat_2D_jagged(0, left, right, None, 20, prime, None)
+    assert torch.equal(back, x)
+    # last 20 rows of every sequence, checked directly for a few sequences
+    for b in (0, B // 2, B - 1):
+        assert torch.equal(right[20 * b:20 * b + 20], x[int(offs[b + 1]) - 20:int(offs[b + 1])])
+    del left, right, back
+    pos_w = torch.randn(16385, 512, device=DEV, generator=g) * 0.1
+    ts_w = torch.randn(2049, 512, device=DEV, generator=g) * 0.1
+    stamps = torch.cumsum((torch.rand(rows, device=DEV, generator=g) * 10).exp().long(), 0)
+    nt = w.num_targets.to(DEV)
+    f = lambda a, alpha: P.add_timestamp_positional_embeddings(  # noqa: E731
+        alpha, 16384, 0, pos_w, ts_w, offs, lengths, a, stamps, nt, False, "sqrt")
+    xf = x.float()
+    e0 = f(torch.zeros_like(xf), 1.0)          # the embedding term alone
+    y = f(xf, 2.0)
+    assert torch.allclose(y, 2.0 * xf + e0, rtol=1e-6, atol=1e-6)
+    # every row of the embedding term is a sum of one row of each table: spot-check the last token
+    # of every sequence (time bucket 0, position index = number of targets -> clamped formula)
+    last = offs[1:] - 1
+    high = lengths - nt
+    idx = high - torch.minimum(lengths - 1, high)
+    assert torch.allclose(e0[last], ts_w[0].unsqueeze(0) + pos_w[idx], rtol=1e-6, atol=1e-6)

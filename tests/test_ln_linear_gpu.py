@@ -171,3 +171,22 @@ def test_prepared_weights_are_reused_only_while_unchanged():
     G.hstu_compute_uqvk(x, nw.data, nb.data, 1e-6, 2, 64, 64, W.detach().clone(), b.data)
     G.hstu_compute_uqvk(x, nw.data, nb.data, 1e-6, 2, 64, 64, W.detach().clone(), b.data)
     assert G._cabi.launch_count() - n0 == 6
+
+
+def test_fused_uqvk_full_size_matches_separate_stages():
+    """configs[1]'s token count, D = 512, N = 2048: the fused kernel against the separate stages
+    (element-wise within 16-bit rounding of two different evaluation orders) and u == SiLU(uvqk)."""
+    from generative_recommenders_b200 import workloads as W
+    M = int(W.config1().total_tokens)
+    x, nw, nb, Wt, b = (t.to(DEV) for t in _inputs(M, 512, 4, 128, 128, torch.bfloat16, seed=77))
+    with torch.no_grad():
+        HC.set_fused_uqvk(True)
+        fu = G.hstu_compute_uqvk(x, nw, nb, 1e-6, 4, 128, 128, Wt, b)
+        HC.set_fused_uqvk(False)
+        se = G.hstu_compute_uqvk(x, nw, nb, 1e-6, 4, 128, 128, Wt, b)
+        HC.set_fused_uqvk(True)
+    for name, a_, s_ in zip("uqkv", fu, se):
+        assert a_.shape == s_.shape
+        assert O.rel_l2(a_.float(), s_.float()) < 6e-3, name
+        assert (a_.float() - s_.float()).abs().max() < 0.25, name
+    assert not torch.isnan(fu[0]).any()
