@@ -11,7 +11,12 @@ from .hstu_compute import (
     hstu_norm_mul_dropout,
     hstu_preprocess_and_attention,
 )
-from .jagged_tensors import concat_2D_jagged, split_2D_jagged
+from .jagged_tensors import (
+    concat_2D_jagged,
+    hstu_concat_l2_embeddings,
+    hstu_split_l2_embeddings,
+    split_2D_jagged,
+)
 from .layer_norm import layer_norm
 from .mm import addmm
 from .position import add_timestamp_positional_embeddings
@@ -30,6 +35,8 @@ __all__ = [
     "layer_norm",
     "concat_2D_jagged",
     "split_2D_jagged",
+    "hstu_split_l2_embeddings",
+    "hstu_concat_l2_embeddings",
     "add_timestamp_positional_embeddings",
     "addmm",
     "STULayer",

@@ -118,7 +118,7 @@ class JaggedArgs(Structure):
         ("offsets_left", c_void_p), ("offsets_right", c_void_p),
         ("dense_len_left", c_int64), ("dense_len_right", c_int64),
         ("total_rows", c_int64), ("row_bytes", c_int64),
-        ("B", c_int32), ("reserved0", c_int32),
+        ("B", c_int32), ("right_rows_first", c_int32),
     ]
 
 

@@ -6,7 +6,9 @@
 //    `left` for b followed by the rows of `right` for b.  One kernel does both directions: a CTA
 //    takes 64 combined rows, one thread per row finds the row's sequence (binary search over
 //    offsets_left + offsets_right) and its partner row, then all threads move the rows in 16-byte
-//    pieces.  Either side may be dense (no offsets: every sequence has `dense_len` rows).
+//    pieces.  Either side may be dense (no offsets: every sequence has `dense_len` rows).  With
+//    right_rows_first = c the first c rows of every sequence belong to `right`
+//    (hstu_split_l2_embeddings / hstu_concat_l2_embeddings, ops/jagged_tensors.py:165-227).
 //
 //  * add_timestamp_positional_embeddings (ops/position.py:40-118;
 //    ops/pytorch/pt_position.py:40-160): out = alpha * x + (ts_emb[bucket] + pos_emb[index]),
@@ -25,6 +27,7 @@ struct JaggedArgs {
   const int64_t *off_l;  // [B + 1] or nullptr (dense: dense_l rows per sequence)
   const int64_t *off_r;
   int64_t dense_l, dense_r;
+  int shift;             // rows of `right` that come BEFORE the rows of `left` in every sequence
   int B;
   int64_t total;  // combined rows
   char *left, *right, *comb;
@@ -50,7 +53,9 @@ __global__ void __launch_bounds__(JAG_THREADS) jagged_rows_kernel(JaggedArgs a) 
     const int64_t ol = side_off(a.off_l, a.dense_l, lo), orr = side_off(a.off_r, a.dense_r, lo);
     const int64_t len_l = side_off(a.off_l, a.dense_l, lo + 1) - ol;
     const int64_t pos = g - ol - orr;
-    partner[threadIdx.x] = pos < len_l ? ol + pos : ~(orr + pos - len_l);
+    // sequence layout: right[0, shift) | left | right[shift, ...)
+    partner[threadIdx.x] = pos < a.shift ? ~(orr + pos)
+                           : (pos < a.shift + len_l ? ol + (pos - a.shift) : ~(orr + pos - len_l));
   }
   __syncthreads();
   const int per_row = (int)(a.row_bytes / (int64_t)sizeof(V));
@@ -373,7 +378,8 @@ int ts_pos_bwd_t(const TsPosArgs &a, const void *dy, void *dx, float *d_pos, flo
 }  // namespace
 
 int jagged_concat_split(const b200_hstu_jagged_args &j, bool split, cudaStream_t st) {
-  if (j.B < 0 || j.total_rows < 0 || j.row_bytes <= 0) return fail(B200_HSTU_EINVAL, "jagged: negative size");
+  if (j.B < 0 || j.total_rows < 0 || j.row_bytes <= 0 || j.right_rows_first < 0)
+    return fail(B200_HSTU_EINVAL, "jagged: negative size");
   if (!j.offsets_left && !j.offsets_right && (j.dense_len_left < 0 || j.dense_len_right < 0))
     return fail(B200_HSTU_EINVAL, "jagged: a side without offsets needs its dense length");
   if (j.total_rows == 0 || j.B == 0) return 0;
@@ -384,6 +390,7 @@ int jagged_concat_split(const b200_hstu_jagged_args &j, bool split, cudaStream_t
   a.off_r = j.offsets_right;
   a.dense_l = j.dense_len_left;
   a.dense_r = j.dense_len_right;
+  a.shift = j.right_rows_first;
   a.B = j.B;
   a.total = j.total_rows;
   a.left = (char *)j.left;

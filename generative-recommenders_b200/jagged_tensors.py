@@ -22,7 +22,7 @@ def _offsets_arg(off: Optional[torch.Tensor], device) -> Optional[torch.Tensor]:
     return off.to(device=device, dtype=torch.int64).contiguous()
 
 
-def _args(left, right, combined, off_l, off_r, dense_l, dense_r, B):
+def _args(left, right, combined, off_l, off_r, dense_l, dense_r, B, shift=0):
     a = _cabi.JaggedArgs()
     a.left, a.right, a.combined = left.data_ptr(), right.data_ptr(), combined.data_ptr()
     a.offsets_left = off_l.data_ptr() if off_l is not None else None
@@ -32,13 +32,14 @@ def _args(left, right, combined, off_l, off_r, dense_l, dense_r, B):
     a.total_rows = combined.shape[0]
     a.row_bytes = combined.shape[1] * combined.element_size()
     a.B = B
+    a.right_rows_first = int(shift)
     return a
 
 
-def _run(split: bool, left, right, combined, off_l, off_r, dense_l, dense_r, B) -> None:
+def _run(split: bool, left, right, combined, off_l, off_r, dense_l, dense_r, B, shift=0) -> None:
     if combined.shape[0] == 0 or combined.shape[1] == 0:
         return
-    a = _args(left, right, combined, off_l, off_r, dense_l, dense_r, B)
+    a = _args(left, right, combined, off_l, off_r, dense_l, dense_r, B, shift)
     fn = _cabi.lib().b200_hstu_split_2d_jagged if split else _cabi.lib().b200_hstu_concat_2d_jagged
     with torch.cuda.device(combined.device):
         _cabi.check(fn(a, stream_ptr(combined.device)),
@@ -47,43 +48,43 @@ def _run(split: bool, left, right, combined, off_l, off_r, dense_l, dense_r, B) 
 
 class _Concat2DJagged(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, left, right, off_l, off_r, dense_l, dense_r, B):
+    def forward(ctx, left, right, off_l, off_r, dense_l, dense_r, B, shift=0):
         left = left.contiguous()
         right = right.contiguous()
         out = torch.empty((left.shape[0] + right.shape[0], left.shape[1]), dtype=left.dtype, device=left.device)
-        _run(False, left, right, out, off_l, off_r, dense_l, dense_r, B)
-        ctx.meta = (off_l, off_r, dense_l, dense_r, B, left.shape[0], right.shape[0])
+        _run(False, left, right, out, off_l, off_r, dense_l, dense_r, B, shift)
+        ctx.meta = (off_l, off_r, dense_l, dense_r, B, left.shape[0], right.shape[0], shift)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        off_l, off_r, dense_l, dense_r, B, n_l, n_r = ctx.meta
+        off_l, off_r, dense_l, dense_r, B, n_l, n_r, shift = ctx.meta
         d_out = d_out.contiguous()
         d_left = torch.empty((n_l, d_out.shape[1]), dtype=d_out.dtype, device=d_out.device)
         d_right = torch.empty((n_r, d_out.shape[1]), dtype=d_out.dtype, device=d_out.device)
-        _run(True, d_left, d_right, d_out, off_l, off_r, dense_l, dense_r, B)
-        return d_left, d_right, None, None, None, None, None
+        _run(True, d_left, d_right, d_out, off_l, off_r, dense_l, dense_r, B, shift)
+        return d_left, d_right, None, None, None, None, None, None
 
 
 class _Split2DJagged(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, values, off_l, off_r, dense_l, dense_r, B, n_l, n_r):
+    def forward(ctx, values, off_l, off_r, dense_l, dense_r, B, n_l, n_r, shift=0):
         values = values.contiguous()
         left = torch.empty((n_l, values.shape[1]), dtype=values.dtype, device=values.device)
         right = torch.empty((n_r, values.shape[1]), dtype=values.dtype, device=values.device)
-        _run(True, left, right, values, off_l, off_r, dense_l, dense_r, B)
-        ctx.meta = (off_l, off_r, dense_l, dense_r, B)
+        _run(True, left, right, values, off_l, off_r, dense_l, dense_r, B, shift)
+        ctx.meta = (off_l, off_r, dense_l, dense_r, B, shift)
         return left, right
 
     @staticmethod
     def backward(ctx, d_left, d_right):
-        off_l, off_r, dense_l, dense_r, B = ctx.meta
+        off_l, off_r, dense_l, dense_r, B, shift = ctx.meta
         d_left = d_left.contiguous()
         d_right = d_right.contiguous()
         d_values = torch.empty((d_left.shape[0] + d_right.shape[0], d_left.shape[1]), dtype=d_left.dtype,
                                device=d_left.device)
-        _run(False, d_left, d_right, d_values, off_l, off_r, dense_l, dense_r, B)
-        return d_values, None, None, None, None, None, None, None
+        _run(False, d_left, d_right, d_values, off_l, off_r, dense_l, dense_r, B, shift)
+        return d_values, None, None, None, None, None, None, None, None
 
 
 def concat_2D_jagged(
@@ -180,3 +181,48 @@ def split_2D_jagged(
     return _Split2DJagged.apply(values, off_l, off_r,
                                 max_len_left if off_l is None else 0,
                                 max_len_right if off_r is None else 0, B, n_l, n_r)
+
+
+def hstu_split_l2_embeddings(
+    max_seq_len: int,
+    x: torch.Tensor,
+    prefix_offsets: torch.Tensor,
+    l2_offsets: torch.Tensor,
+    contextual_seq_len: int,
+    kernel: HammerKernel = HammerKernel.CUDA,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(prefix_x, l2_x)``: every sequence of ``x`` is ``contextual_seq_len`` rows of the l2 part, then
+    the prefix rows, then the rest of the l2 part
+    (generative_recommenders/ops/jagged_tensors.py:165-192)."""
+    _require_cuda_backend(kernel)
+    require_cuda(x, prefix_offsets, l2_offsets)
+    torch._assert(x.dim() == 2, "x must be 2D")
+    off_l = _offsets_arg(prefix_offsets, x.device)
+    off_r = _offsets_arg(l2_offsets, x.device)
+    torch._assert(off_l.numel() == off_r.numel(), "prefix_offsets and l2_offsets must describe the same batch")
+    n_l = int(off_l[-1].item())
+    return _Split2DJagged.apply(x, off_l, off_r, 0, 0, off_l.numel() - 1, n_l, x.shape[0] - n_l,
+                                int(contextual_seq_len))
+
+
+def hstu_concat_l2_embeddings(
+    max_prefix_len: int,
+    prefix_x: torch.Tensor,
+    prefix_offsets: torch.Tensor,
+    max_l2_len: int,
+    l2_x: torch.Tensor,
+    l2_offsets: torch.Tensor,
+    contextual_seq_len: int,
+    kernel: HammerKernel = HammerKernel.CUDA,
+) -> torch.Tensor:
+    """The inverse of :func:`hstu_split_l2_embeddings`
+    (generative_recommenders/ops/jagged_tensors.py:195-227)."""
+    _require_cuda_backend(kernel)
+    require_cuda(prefix_x, l2_x, prefix_offsets, l2_offsets)
+    torch._assert(prefix_x.dim() == 2 and l2_x.dim() == 2, "prefix_x and l2_x must be 2D")
+    torch._assert(prefix_x.shape[1] == l2_x.shape[1] and prefix_x.dtype == l2_x.dtype,
+                  "prefix_x and l2_x must have the same width and dtype")
+    off_l = _offsets_arg(prefix_offsets, prefix_x.device)
+    off_r = _offsets_arg(l2_offsets, prefix_x.device)
+    torch._assert(off_l.numel() == off_r.numel(), "prefix_offsets and l2_offsets must describe the same batch")
+    return _Concat2DJagged.apply(prefix_x, l2_x, off_l, off_r, 0, 0, off_l.numel() - 1, int(contextual_seq_len))

@@ -259,7 +259,10 @@ int b200_hstu_ln_linear_supported(int32_t D, int32_t N, int32_t silu_cols, int32
  * contiguous in all three tensors.  A side without offsets (NULL) is dense: every sequence has
  * dense_len_* rows there.  total_rows = rows of `combined`.  concat reads left/right and writes
  * combined; split reads combined and writes left/right.  Offsets are int64 device arrays [B + 1].
- * Each is the other's backward.
+ * Each is the other's backward.  right_rows_first = c > 0 gives the layout of
+ * hstu_split_l2_embeddings / hstu_concat_l2_embeddings (ops/jagged_tensors.py:165-227): the first c
+ * rows of every sequence of `combined` are the first c rows of `right` for that sequence, then come
+ * the rows of `left`, then the rest of `right` (every sequence needs at least c rows in `right`).
  */
 typedef struct b200_hstu_jagged_args {
   void *left, *right, *combined;
@@ -268,7 +271,7 @@ typedef struct b200_hstu_jagged_args {
   int64_t total_rows;
   int64_t row_bytes;
   int32_t B;
-  int32_t reserved0;
+  int32_t right_rows_first;
 } b200_hstu_jagged_args;
 int b200_hstu_concat_2d_jagged(const b200_hstu_jagged_args *args, b200_hstu_stream_t stream);
 int b200_hstu_split_2d_jagged(const b200_hstu_jagged_args *args, b200_hstu_stream_t stream);

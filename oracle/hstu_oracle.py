@@ -424,6 +424,40 @@ def split_2D_jagged(
     return torch.cat(left, 0), torch.cat(right, 0)
 
 
+def hstu_split_l2_embeddings(
+    x: torch.Tensor, prefix_offsets: torch.Tensor, l2_offsets: torch.Tensor, contextual_seq_len: int
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per sequence ``x = [l2[:c] | prefix | l2[c:]]`` -> ``(prefix, l2)``
+    (generative_recommenders/ops/pytorch/pt_jagged_tensors.py:163-199)."""
+    c = contextual_seq_len
+    B = prefix_offsets.numel() - 1
+    pre, l2 = [], []
+    for b in range(B):
+        s = int(prefix_offsets[b] + l2_offsets[b])
+        npre = int(prefix_offsets[b + 1] - prefix_offsets[b])
+        nl2 = int(l2_offsets[b + 1] - l2_offsets[b])
+        l2.append(x[s:s + c])
+        pre.append(x[s + c:s + c + npre])
+        l2.append(x[s + c + npre:s + npre + nl2])
+    return torch.cat(pre, 0), torch.cat(l2, 0)
+
+
+def hstu_concat_l2_embeddings(
+    prefix_x: torch.Tensor, prefix_offsets: torch.Tensor, l2_x: torch.Tensor, l2_offsets: torch.Tensor,
+    contextual_seq_len: int,
+) -> torch.Tensor:
+    """Inverse of :func:`hstu_split_l2_embeddings`
+    (generative_recommenders/ops/pytorch/pt_jagged_tensors.py:202-243)."""
+    c = contextual_seq_len
+    B = prefix_offsets.numel() - 1
+    rows = []
+    for b in range(B):
+        p0, p1 = int(prefix_offsets[b]), int(prefix_offsets[b + 1])
+        l0, l1 = int(l2_offsets[b]), int(l2_offsets[b + 1])
+        rows += [l2_x[l0:l0 + c], prefix_x[p0:p1], l2_x[l0 + c:l1]]
+    return torch.cat(rows, 0)
+
+
 def add_timestamp_positional_embeddings(
     alpha: float,
     max_contextual_seq_len: int,

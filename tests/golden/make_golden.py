@@ -275,6 +275,24 @@ def make_jagged(gr):
         fx["concat"].append(dict(kind=kind, left=left, right=right, out=out, **kw))
         sl, sr = pytorch_split_2D_jagged(max_seq_len=max_l + max_r, values=out, **kw)
         fx["split"].append(dict(kind=kind, values=out, left=sl, right=sr, **kw))
+    from generative_recommenders.ops.pytorch.pt_jagged_tensors import (
+        pytorch_hstu_concat_l2_embeddings,
+        pytorch_hstu_split_l2_embeddings,
+    )
+    fx["l2"] = []
+    for ctx in (0, 3):
+        B, D = 6, 16
+        lp = torch.randint(0, 9, (B,), generator=g)
+        l2 = torch.randint(ctx, ctx + 7, (B,), generator=g)
+        po, lo = _offsets(lp), _offsets(l2)
+        prefix_x = torch.randn(int(po[-1]), D, generator=g)
+        l2_x = torch.randn(int(lo[-1]), D, generator=g)
+        x = pytorch_hstu_concat_l2_embeddings(max_prefix_len=9, prefix_x=prefix_x, prefix_offsets=po,
+                                              max_l2_len=ctx + 7, l2_x=l2_x, l2_offsets=lo, contextual_seq_len=ctx)
+        sp, sl = pytorch_hstu_split_l2_embeddings(max_seq_len=9 + ctx + 7, x=x, prefix_offsets=po, l2_offsets=lo,
+                                                  contextual_seq_len=ctx)
+        fx["l2"].append(dict(ctx=ctx, prefix_x=prefix_x, l2_x=l2_x, prefix_offsets=po, l2_offsets=lo, x=x,
+                             split_prefix=sp, split_l2=sl))
     for i, (targets, interleave, fn, ctx, dtype) in enumerate([
             (False, False, "sqrt", 0, torch.float32), (True, False, "sqrt", 0, torch.float32),
             (True, True, "sqrt", 0, torch.float32), (True, False, "log", 3, torch.float32),

@@ -215,3 +215,18 @@ def test_full_size_round_trips():
     high = lengths - nt
     idx = high - torch.minimum(lengths - 1, high)
     assert torch.allclose(e0[last], ts_w[0].unsqueeze(0) + pos_w[idx], rtol=1e-6, atol=1e-6)
+
+
+def test_l2_embedding_split_concat_golden_and_grads(golden):
+    for c in golden("jagged.pt")["l2"]:
+        po, lo = c["prefix_offsets"].to(DEV), c["l2_offsets"].to(DEV)
+        px = c["prefix_x"].to(DEV).requires_grad_(True)
+        lx = c["l2_x"].to(DEV).requires_grad_(True)
+        x = J.hstu_concat_l2_embeddings(9, px, po, c["ctx"] + 7, lx, lo, c["ctx"])
+        assert torch.equal(x.detach().cpu(), c["x"]), c["ctx"]
+        p, l = J.hstu_split_l2_embeddings(16 + c["ctx"], x.detach(), po, lo, c["ctx"])
+        assert torch.equal(p.cpu(), c["split_prefix"]) and torch.equal(l.cpu(), c["split_l2"])
+        d = torch.randn_like(x)
+        x.backward(d)
+        dp, dl = O.hstu_split_l2_embeddings(d.cpu(), c["prefix_offsets"], c["l2_offsets"], c["ctx"])
+        assert torch.equal(px.grad.cpu(), dp) and torch.equal(lx.grad.cpu(), dl)

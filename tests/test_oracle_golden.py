@@ -167,3 +167,14 @@ def test_cached_layer_fixture_is_consistent(golden):
         off = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(prime, 0)])
         _, tail = O.split_2D_jagged(h, None, c["delta"], off, None)
         torch.testing.assert_close(tail, c["cached_delta_y"], rtol=1e-4, atol=1e-5)
+
+
+def test_l2_embedding_split_concat_match_reference(golden):
+    cases = golden("jagged.pt")["l2"]
+    assert len(cases) == 2
+    for c in cases:
+        x = O.hstu_concat_l2_embeddings(c["prefix_x"], c["prefix_offsets"], c["l2_x"], c["l2_offsets"], c["ctx"])
+        assert torch.equal(x, c["x"]), c["ctx"]
+        p, l = O.hstu_split_l2_embeddings(c["x"], c["prefix_offsets"], c["l2_offsets"], c["ctx"])
+        assert torch.equal(p, c["split_prefix"]) and torch.equal(l, c["split_l2"])
+        assert torch.equal(p, c["prefix_x"]) and torch.equal(l, c["l2_x"])
