@@ -20,6 +20,7 @@ from .jagged_tensors import (
 from .layer_norm import layer_norm
 from .mm import addmm
 from .position import add_timestamp_positional_embeddings
+from .positional_encoder import HSTUPositionalEncoder
 from .stu import STULayer, STULayerConfig, STUStack
 
 __all__ = [
@@ -39,6 +40,7 @@ __all__ = [
     "hstu_concat_l2_embeddings",
     "add_timestamp_positional_embeddings",
     "addmm",
+    "HSTUPositionalEncoder",
     "STULayer",
     "STULayerConfig",
     "STUStack",

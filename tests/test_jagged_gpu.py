@@ -230,3 +230,33 @@ def test_l2_embedding_split_concat_golden_and_grads(golden):
         x.backward(d)
         dp, dl = O.hstu_split_l2_embeddings(d.cpu(), c["prefix_offsets"], c["l2_offsets"], c["ctx"])
         assert torch.equal(px.grad.cpu(), dp) and torch.equal(lx.grad.cpu(), dl)
+
+
+def test_positional_encoder_module_matches_oracle():
+    """The module in front of layer 0 (reference modules/positional_encoder.py): parameters as the
+    reference names them, output and gradients against the oracle."""
+    torch.manual_seed(4)
+    D, N, ctx = 64, 200, 3
+    enc = G.HSTUPositionalEncoder(num_position_buckets=N + ctx + 1, num_time_buckets=2048, embedding_dim=D,
+                                  contextual_seq_len=ctx).to(DEV)
+    assert set(dict(enc.named_parameters())) == {"_position_embeddings_weight", "_timestamp_embeddings_weight"}
+    g = torch.Generator().manual_seed(8)
+    nt = torch.randint(0, 4, (9,), generator=g)
+    lengths = torch.randint(1, 150, (9,), generator=g) + nt + ctx
+    offs = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(lengths, 0)])
+    total = int(offs[-1])
+    x = torch.randn(total, D, generator=g)
+    ts = torch.cat([torch.cumsum((torch.rand(int(n), generator=g) * 11).exp().long(), 0) for n in lengths])
+    xg = x.to(DEV).requires_grad_(True)
+    y = enc(N, lengths.to(DEV), offs.to(DEV), ts.to(DEV), xg, nt.to(DEV))
+    pw = enc._position_embeddings_weight.detach().cpu().requires_grad_(True)
+    tw = enc._timestamp_embeddings_weight.detach().cpu().requires_grad_(True)
+    xr = x.clone().requires_grad_(True)
+    ref = O.add_timestamp_positional_embeddings(D ** 0.5, ctx, pw, tw, offs, lengths, xr, ts, nt, False, "sqrt")
+    assert torch.equal(y.detach().cpu(), ref.detach())
+    d = torch.randn(total, D, generator=g)
+    y.backward(d.to(DEV))
+    ref.backward(d)
+    assert torch.equal(xg.grad.cpu(), xr.grad)
+    torch.testing.assert_close(enc._position_embeddings_weight.grad.cpu(), pw.grad, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(enc._timestamp_embeddings_weight.grad.cpu(), tw.grad, rtol=1e-4, atol=2e-3)
