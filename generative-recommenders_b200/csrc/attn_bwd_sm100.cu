@@ -725,10 +725,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int L = it.m.L;
         const int own = it.m0 + row_in_tile;  // kv position (DKDV) or query position
         const bool exact_only = !it.regular;
-        ColInterval ci;
-        RowInterval ri;
-        if (DKDV) ci = col_interval(it, own); else ri = row_interval(it, own);
         for (int j = 0; j < it.n_tiles && ok; ++j, ++cnt) {
+          // The thread's mask interval is worked out again for every tile although it only depends
+          // on the item: code that runs once per item is fetched cold (several thousand cycles of
+          // instruction-cache misses per item), code inside the tile loop stays resident.
+          int own_j = own;
+          asm volatile("" : "+r"(own_j));   // keeps the compiler from hoisting it out of the loop
+          ColInterval ci;
+          RowInterval ri;
+          if (DKDV) ci = col_interval(it, own_j); else ri = row_interval(it, own_j);
           const int o0 = it.tile_at(j) * TILE;  // first position of the streamed tile
           bool full;
           if (DKDV) {  // streamed = query tile o0, stationary = kv tile it.m0; all query rows must exist
