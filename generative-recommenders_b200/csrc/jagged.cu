@@ -52,10 +52,14 @@ __global__ void __launch_bounds__(JAG_THREADS) jagged_rows_kernel(JaggedArgs a) 
     }
     const int64_t ol = side_off(a.off_l, a.dense_l, lo), orr = side_off(a.off_r, a.dense_r, lo);
     const int64_t len_l = side_off(a.off_l, a.dense_l, lo + 1) - ol;
+    const int64_t len_r = side_off(a.off_r, a.dense_r, lo + 1) - orr;
     const int64_t pos = g - ol - orr;
     // sequence layout: right[0, shift) | left | right[shift, ...)
-    partner[threadIdx.x] = pos < a.shift ? ~(orr + pos)
-                           : (pos < a.shift + len_l ? ol + (pos - a.shift) : ~(orr + pos - len_l));
+    int64_t pr = pos < a.shift ? ~(orr + pos)
+                               : (pos < a.shift + len_l ? ol + (pos - a.shift) : ~(orr + pos - len_l));
+    // a row the offsets do not account for (inconsistent arguments) is skipped, never dereferenced
+    if (pos < 0 || pos >= len_l + len_r) pr = INT64_MIN;
+    partner[threadIdx.x] = pr;
   }
   __syncthreads();
   const int per_row = (int)(a.row_bytes / (int64_t)sizeof(V));
@@ -73,6 +77,7 @@ __global__ void __launch_bounds__(JAG_THREADS) jagged_rows_kernel(JaggedArgs a) 
       if (i < n) {
         const int r = i / per_row, c = i - r * per_row;
         const int64_t p = partner[r];
+        if (p == INT64_MIN) continue;
         char *side = p >= 0 ? a.left + p * a.row_bytes : a.right + (~p) * a.row_bytes;
         if (SPLIT) {
           val[u] = comb_in[i];
@@ -140,9 +145,12 @@ __device__ __forceinline__ void ts_pos_indices(const TsPosArgs &a, int64_t g, in
   }
   idx += a.max_contextual_seq_len;
   if (idx > a.max_pos_ind - 1) idx = a.max_pos_ind - 1;
-  if (p < a.max_contextual_seq_len) idx = p;
+  if (p < a.max_contextual_seq_len) idx = p < a.max_pos_ind ? p : a.max_pos_ind - 1;
+  if (idx < 0) idx = 0;  // only with seq_lengths smaller than the rows the offsets give: stay inside the table
   pos_ind = (int)idx;
-  const int64_t last = n - 1 > 0 ? n - 1 : 0;
+  const int64_t rows_b = a.seq_offsets[lo + 1] - start;
+  int64_t last = n - 1 > 0 ? n - 1 : 0;
+  if (last > rows_b - 1) last = rows_b - 1;  // same: stay inside the sequence
   const int64_t dt = a.timestamps[start + last] - a.timestamps[g];
   float f = fmaxf((float)dt, 1e-6f);
   f = __fdiv_rn(f, 60.0f);
