@@ -65,8 +65,11 @@ struct WaitCtx {
   int *status;               // global: first failing site is recorded here (0 = ok)
 };
 
-__device__ __forceinline__ bool mbar_wait(const WaitCtx &ctx, uint32_t bar, uint32_t parity, int site) {
-  if (mbar_try_wait(bar, parity)) return true;
+// The spinning part is one out-of-line function: inlined at every wait it added ~10 KB to
+// kernels that are about as large as the instruction cache (110-135 KB).
+static __device__ __noinline__ bool mbar_wait_slow(volatile int *abort_flag, int *status, uint32_t bar, uint32_t parity,
+                                            int site) {
+  const WaitCtx ctx{abort_flag, status};
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
@@ -82,6 +85,11 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx &ctx, uint32_t bar, uint
       }
     }
   }
+}
+
+__device__ __forceinline__ bool mbar_wait(const WaitCtx &ctx, uint32_t bar, uint32_t parity, int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(ctx.abort_flag, ctx.status, bar, parity, site);
 }
 
 // ------------------------------------------------------------------ work ring (see attn_plan.cuh)
