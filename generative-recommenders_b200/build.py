@@ -26,6 +26,10 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
 ]
+# B200_HSTU_TRACE_BUILD=1 compiles the in-kernel timeline marks in (a profiling aid; the marks sit in
+# the hot loops, so the default build leaves them out); rebuild with force after changing it
+if os.environ.get("B200_HSTU_TRACE_BUILD"):
+    NVCC_FLAGS.append("-DB200_HSTU_TRACE_BUILD")
 
 
 def _nvcc():

@@ -457,7 +457,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + SM::MISC_OFF + 8);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wc{abort_flag, p.status};
+#ifdef B200_HSTU_TRACE_BUILD
   const uint64_t cta_t0 = p.trace != nullptr ? globaltimer_ns() : 0;
+#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -848,9 +850,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     tmem_dealloc(tmem_base, 512);
   }
   if (!DKDV) grid_dependency_wait();
+#ifdef B200_HSTU_TRACE_BUILD
   // timeline: start and end time of every CTA (second half of the last role's records)
   if (p.trace != nullptr && threadIdx.x == 0 && blockIdx.x < TRACE_RECORDS / 2)
     p.trace[3 * TRACE_RECORDS + TRACE_RECORDS / 2 + blockIdx.x] = make_ulonglong2(cta_t0, globaltimer_ns());
+#endif
 }
 
 }  // namespace

@@ -272,6 +272,10 @@ __device__ __forceinline__ float tanh_approx(float x) {
 constexpr int TRACE_RECORDS = 1024;
 constexpr int64_t TRACE_BYTES = 4 * TRACE_RECORDS * (int64_t)sizeof(ulonglong2);
 
+// Compiled in only with -DB200_HSTU_TRACE_BUILD (build.py: B200_HSTU_TRACE_BUILD=1): the marks sit
+// in the hot loops, and these kernels are as large as the instruction cache - every instruction
+// that is not needed costs time.
+#ifdef B200_HSTU_TRACE_BUILD
 struct Tracer {
   ulonglong2 *buf;
   int n;
@@ -283,6 +287,12 @@ struct Tracer {
     if (buf != nullptr && n < TRACE_RECORDS) buf[n++] = make_ulonglong2((unsigned long long)clock64(), tag);
   }
 };
+#else
+struct Tracer {
+  __device__ __forceinline__ void init(ulonglong2 *, int, bool) {}
+  __device__ __forceinline__ void mark(unsigned) {}
+};
+#endif
 
 }  // namespace ptx
 }  // namespace b200hstu
