@@ -658,22 +658,36 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                        has_next ? 0u : acc_full);
           }
           tr.mark(16);
-          if (has_next) {
-            ok = stage1(0, cnt + 1, -1, j == n - 2);
-            if (!ok) break;
-            tr.mark(18);
-          } else {
-            // Last tile of the item: the score region is free from here on.  Take the next item
-            // and issue G1 of its first tile now and G2 after this item's last G4; its stationary
-            // tiles were requested as soon as this item's last G1 / G2 had been issued.
+          // What follows this tile: the item's next tile, or - at the item's last tile, when the
+          // score region is free from here on - the first tile of the next item, whose stationary
+          // tiles were requested as soon as this item's last G1 / G2 had been issued.  G1 of it is
+          // issued now, G2 after this tile's G4.  The kv-stationary launch, whose code is the
+          // largest, serves both cases from one issue site; the q-stationary launch is faster with
+          // two.
+          bool issue_next = has_next;
+          int first_of = -1;
+          bool next_last = j == n - 2;
+          if (!has_next) {
             ok = geom_fetch(wc, sched_ring, sched_full, sched_empty, it_cnt + 1, ng, lane == 0);
             if (!ok) break;
             if (ng.idx < num_items) {
               next_item = true;
-              ok = stage1(0, cnt + 1, (int)it_cnt + 1, ng.n_tiles == 1);
-              if (!ok) break;
-              tr.mark(20);
+              issue_next = true;
+              first_of = (int)it_cnt + 1;
+              next_last = ng.n_tiles == 1;
             }
+          }
+          if (DKDV) {
+            if (issue_next) {
+              ok = stage1(0, cnt + 1, first_of, next_last);
+              if (!ok) break;
+            }
+          } else if (has_next) {
+            ok = stage1(0, cnt + 1, -1, j == n - 2);
+            if (!ok) break;
+          } else if (next_item) {
+            ok = stage1(0, cnt + 1, (int)it_cnt + 1, ng.n_tiles == 1);
+            if (!ok) break;
           }
           // ---- dS written: G4, then the next dP
           tr.mark(13);
@@ -689,14 +703,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           bwd_stage2(tmem_base + 256 + aset * 128, tmem_base + 128, sY0 + s0 * SM::TILE_BYTES, idesc_2, acc_on,
                      y0_empty + 8 * s0, has_next ? 0u : acc_full + 8 * aset);
           tr.mark(17);
-          if (has_next) {
+          if (DKDV) {
+            if (issue_next) {
+              ok = stage1(1, cnt + 1, first_of, next_last);
+              if (!ok) break;
+              if (!has_next) pre_issued = true;
+            }
+          } else if (has_next) {
             ok = stage1(1, cnt + 1, -1, j == n - 2);
             if (!ok) break;
-            tr.mark(19);
           } else if (next_item) {
             ok = stage1(1, cnt + 1, (int)it_cnt + 1, ng.n_tiles == 1);
             if (!ok) break;
-            tr.mark(21);
             pre_issued = true;
           }
         }
