@@ -814,21 +814,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           // handed back as soon as it has been stored
           uint16_t *dvrow = reinterpret_cast<uint16_t *>(p.dv) + (int64_t)(g.start + own) * p.dv_rs + (int64_t)h * p.dv_hs;
           uint16_t *dkrow = reinterpret_cast<uint16_t *>(p.dk) + (int64_t)(g.start + own) * p.dk_rs + (int64_t)h * p.dk_hs;
-          ok = mbar_wait(wc, acc_full, it_cnt & 1, 602);
+          // one copy of the store code serves both accumulators
+#pragma unroll 1
+          for (int acc = 0; acc < 2 && ok; ++acc) {
+            ok = mbar_wait(wc, acc_full + 8 * acc, it_cnt & 1, 602 + acc);
+            if (!ok) break;
+            tc_fence_after();
+            store_acc_rows<D, IS_BF16>(tmem_base + 256 + acc * 128 + lane_off, acc ? sc * p.alpha : sc,
+                                       acc ? dkrow : dvrow, rv, p.wide_stores != 0);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+          }
           if (!ok) break;
-          tc_fence_after();
-          tr.mark(41);
-          store_acc_rows<D, IS_BF16>(tmem_base + 256 + lane_off, sc, dvrow, rv, p.wide_stores != 0);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty);
-          ok = mbar_wait(wc, acc_full + 8, it_cnt & 1, 603);
-          if (!ok) break;
-          tc_fence_after();
-          store_acc_rows<D, IS_BF16>(tmem_base + 384 + lane_off, sc * p.alpha, dkrow, rv, p.wide_stores != 0);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty + 8);
         } else {
           const int aset = (int)(it_cnt & 1);
           uint16_t *dqrow = reinterpret_cast<uint16_t *>(p.dq) + (int64_t)(g.start + own) * p.dq_rs + (int64_t)h * p.dq_hs;

@@ -733,7 +733,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    uint32_t my_items[2] = {0, 0};
+    uint32_t items_a = 0, items_b = 0;   // items in which each query tile took part (barrier phases)
     bool ok = true;
     if ((int)blockIdx.x < num_items) {
       PairGeom g;
@@ -742,12 +742,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       while (ok && g.idx < num_items) {
         const int h = g.idx % p.H;
         const int L = g.L;
-#pragma unroll
+        // rolled: one copy of the store code serves both query tiles
+#pragma unroll 1
         for (int X = 0; X < 2; ++X) {
           if (X == 1 && !g.has_b) continue;
           const int m0 = g.m0 + X * TILE;
           const int i = m0 + row_in_tile;
-          ok = mbar_wait(wc, o_full + 8 * X, my_items[X] & 1, 302);
+          ok = mbar_wait(wc, o_full + 8 * X, (X ? items_b : items_a) & 1, 302);
           if (!ok) break;
           tc_fence_after();
           const bool row_ok = i >= 0 && i < L;
@@ -787,7 +788,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(o_empty + 8 * X);
-          ++my_items[X];
+          if (X) ++items_b; else ++items_a;
           // rows at or beyond max_seq_len of an over-long sequence come back as zeros
           if (g.len > L && m0 + TILE >= L) {
             for (int r2 = L + row_in_tile; r2 < g.len; r2 += TILE) {
