@@ -755,14 +755,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           RowInterval ri;
           if (DKDV) ci = col_interval(it, own_j); else ri = row_interval(it, own_j);
           const int o0 = it.tile_at(j) * TILE;  // first position of the streamed tile
-          bool full;
-          if (DKDV) {  // streamed = query tile o0, stationary = kv tile it.m0; all query rows must exist
-            TileItem qi = it;
-            qi.m0 = o0;
-            full = !exact_only && tile_pair_is_full(qi, it.m0) && (o0 + TILE <= L);
-          } else {
-            full = !exact_only && tile_pair_is_full(it, o0);
-          }
           const int c0 = o0 + wg * 64;  // first streamed position of this thread's 64 columns
           ActTile at;
           at.tS = tS;
@@ -777,8 +769,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           if (!exact_only) {
             // one code path for fully and partially visible tiles: the tensor pipe, not the
             // activation, bounds this kernel, and code that runs once per item is slow to fetch
-            const uint32_t b0 = full ? 0xffffffffu : (DKDV ? col_mask_bits(ci, c0, L) : row_mask_bits(ri, c0, L));
-            const uint32_t b1 = full ? 0xffffffffu : (DKDV ? col_mask_bits(ci, c0 + 32, L) : row_mask_bits(ri, c0 + 32, L));
+            // kv-stationary launch: the interval mask is all ones on a fully visible tile, no separate
+            // test for those (it would evaluate the tile pair); q-stationary launch: the test is
+            // cheap and saves the mask words
+            uint32_t b0, b1;
+            if (DKDV) {
+              b0 = col_mask_bits(ci, c0, L);
+              b1 = col_mask_bits(ci, c0 + 32, L);
+            } else {
+              const bool full = tile_pair_is_full(it, o0);
+              b0 = full ? 0xffffffffu : row_mask_bits(ri, c0, L);
+              b1 = full ? 0xffffffffu : row_mask_bits(ri, c0 + 32, L);
+            }
             ok = act_tile_body<IS_BF16, DKDV, 1, BIAS>(wc, at, b0, b1, it.m, own, c0, nullptr, 0, tr);
           } else {
             ok = act_tile_exact<IS_BF16, DKDV>(wc, at, it.m, own, c0, p.bias, p.bias_numel);
