@@ -330,3 +330,85 @@ def test_unsupported_requests_raise():
     G.set_attention_impl("tcgen05")
     with pytest.raises(RuntimeError):  # fp32 has no tensor-core path: loud error, no silent fallback
         G.hstu_mha(8, 1.0, q, q, q, offs)
+
+
+def test_config3_full_size_properties():
+    """BASELINE configs[3] (256 sequences up to 8192 tokens, window 1024, 256 targets) at full
+    size.  The oracle checks sampled sequences - the shortest, a median one and, for one head, a
+    maximum-length one; size-independent properties cover the rest: a second run and a run of the
+    sampled sequences alone give the same bits as the full batch (rows of a sequence depend on
+    nothing outside it, whatever the work list looks like), and the result is linear in v
+    (doubling v doubles every output bit-exactly)."""
+    w = W.config3()
+    q, k, v = w.qkv(device=DEV)
+    offs_d, nt_d = w.seq_offsets.to(DEV), w.num_targets.to(DEV)
+
+    def run(q_, k_, v_, offs_, nt_):
+        return G.hstu_mha(w.max_seq_len, w.alpha, q_, k_, v_, offs_, num_targets=nt_, max_attn_len=w.max_attn_len,
+                          contextual_seq_len=w.contextual_seq_len)
+
+    out = run(q, k, v, offs_d, nt_d)
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, run(q, k, v, offs_d, nt_d))
+    assert torch.equal(run(q, k, v * 2, offs_d, nt_d), out * 2)
+
+    order = torch.argsort(w.lengths)
+    picks = [int(order[0]), int(order[len(order) // 2]), int(order[-1])]
+    assert int(w.lengths[picks[-1]]) == w.max_seq_len
+    rows = torch.cat([torch.arange(int(w.seq_offsets[b]), int(w.seq_offsets[b + 1])) for b in picks]).to(DEV)
+    sub = W.subset(w, picks)
+    out_sub = run(q[rows], k[rows], v[rows], sub.seq_offsets.to(DEV), sub.num_targets.to(DEV))
+    assert torch.equal(out_sub, out[rows])
+
+    for n, b in enumerate(picks):
+        lo, hi = int(w.seq_offsets[b]), int(w.seq_offsets[b + 1])
+        heads = slice(0, 1) if n == 2 else slice(0, w.num_heads)   # the 8192-token sequence: one head
+        one = W.subset(w, [b])
+        ref = O.hstu_mha(w.max_seq_len, w.alpha, q[lo:hi, heads].float().cpu(), k[lo:hi, heads].float().cpu(),
+                         v[lo:hi, heads].float().cpu(), one.seq_offsets, num_targets=one.num_targets,
+                         max_attn_len=w.max_attn_len, contextual_seq_len=w.contextual_seq_len)
+        assert O.rel_l2(out[lo:hi, heads].cpu(), ref) < BF16_TOL, b
+
+
+def test_config4_full_size_properties():
+    """BASELINE configs[4]'s attention (2048 sequences up to 16 384 tokens, 3.5 M tokens, H = 8,
+    contextual prefix 16, 64 targets) at full size: element offsets pass 2^31 here.  Same
+    properties as for configs[3]; the sampled sequences include the last one of the batch (the
+    highest row offsets), the oracle checks the shortest, a median one and the last."""
+    w = W.config4()
+    L, H, d = w.total_tokens, w.num_heads, w.attn_dim
+    assert L * H * d > 2 ** 31
+    g = torch.Generator(device=DEV).manual_seed(w.seed)
+    q, k, v = (torch.randn(L, H, d, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16) for _ in range(3))
+    offs_d, nt_d = w.seq_offsets.to(DEV), w.num_targets.to(DEV)
+
+    def run(q_, k_, v_, offs_, nt_):
+        return G.hstu_mha(w.max_seq_len, w.alpha, q_, k_, v_, offs_, num_targets=nt_, max_attn_len=w.max_attn_len,
+                          contextual_seq_len=w.contextual_seq_len)
+
+    out = run(q, k, v, offs_d, nt_d)
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, run(q, k, v, offs_d, nt_d))
+    v2 = v * 2
+    out2 = run(q, k, v2, offs_d, nt_d)
+    del v2
+    assert torch.equal(out2, out * 2)
+    del out2
+
+    order = torch.argsort(w.lengths)
+    last = len(w.lengths) - 1
+    picks = [int(order[0]), int(order[len(order) // 2]), int(order[-1]), last]
+    assert int(w.lengths[picks[2]]) == w.max_seq_len
+    rows = torch.cat([torch.arange(int(w.seq_offsets[b]), int(w.seq_offsets[b + 1])) for b in picks]).to(DEV)
+    sub = W.subset(w, picks)
+    out_sub = run(q[rows], k[rows], v[rows], sub.seq_offsets.to(DEV), sub.num_targets.to(DEV))
+    assert torch.equal(out_sub, out[rows])
+
+    for b in (picks[0], picks[1], last):
+        lo, hi = int(w.seq_offsets[b]), int(w.seq_offsets[b + 1])
+        heads = slice(0, H) if hi - lo <= 2048 else slice(H - 1, H)
+        one = W.subset(w, [b])
+        ref = O.hstu_mha(w.max_seq_len, w.alpha, q[lo:hi, heads].float().cpu(), k[lo:hi, heads].float().cpu(),
+                         v[lo:hi, heads].float().cpu(), one.seq_offsets, num_targets=one.num_targets,
+                         max_attn_len=w.max_attn_len, contextual_seq_len=w.contextual_seq_len)
+        assert O.rel_l2(out[lo:hi, heads].cpu(), ref) < BF16_TOL, b
