@@ -412,3 +412,47 @@ def test_config4_full_size_properties():
                          v[lo:hi, heads].float().cpu(), one.seq_offsets, num_targets=one.num_targets,
                          max_attn_len=w.max_attn_len, contextual_seq_len=w.contextual_seq_len)
         assert O.rel_l2(out[lo:hi, heads].cpu(), ref) < BF16_TOL, b
+
+
+def test_config2_full_size_backward_properties():
+    """BASELINE configs[2]'s attention (training: 128 sequences up to 4096 tokens, H = 4,
+    contextual prefix 6, targets) forward + backward at full size: gradients of sampled sequences
+    run alone carry the same bits as in the full batch, doubling dout doubles dq, dk, dv
+    bit-exactly, and the oracle checks the shortest, a median and the longest sequence."""
+    w = W.config2_attention()
+    q, k, v, do = w.qkv(device=DEV, with_dout=True)
+    nt_all = None if w.num_targets is None else w.num_targets.to(DEV)
+
+    def run(q_, k_, v_, do_, offs_, nt_):
+        q_, k_, v_ = (t.detach().clone().requires_grad_(True) for t in (q_, k_, v_))
+        out = G.hstu_mha(w.max_seq_len, w.alpha, q_, k_, v_, offs_, num_targets=nt_, max_attn_len=w.max_attn_len,
+                         contextual_seq_len=w.contextual_seq_len)
+        out.backward(do_)
+        return out.detach(), q_.grad, k_.grad, v_.grad
+
+    full = run(q, k, v, do, w.seq_offsets.to(DEV), nt_all)
+    for t in full:
+        assert torch.isfinite(t.float()).all()
+    twice = run(q, k, v, do * 2, w.seq_offsets.to(DEV), nt_all)
+    for a, b in zip(full[1:], twice[1:]):
+        assert torch.equal(a * 2, b)
+
+    order = torch.argsort(w.lengths)
+    picks = [int(order[0]), int(order[len(order) // 2]), int(order[-1])]
+    rows = torch.cat([torch.arange(int(w.seq_offsets[b]), int(w.seq_offsets[b + 1])) for b in picks]).to(DEV)
+    sub = W.subset(w, picks)
+    alone = run(q[rows], k[rows], v[rows], do[rows], sub.seq_offsets.to(DEV),
+                None if sub.num_targets is None else sub.num_targets.to(DEV))
+    for a, b in zip(alone, full):
+        assert torch.equal(a, b[rows])
+
+    for b in picks:
+        lo, hi = int(w.seq_offsets[b]), int(w.seq_offsets[b + 1])
+        heads = slice(0, w.num_heads) if hi - lo <= 2048 else slice(0, 1)
+        one = W.subset(w, [b])
+        ref, rgrads = _oracle(q[lo:hi, heads].cpu(), k[lo:hi, heads].cpu(), v[lo:hi, heads].cpu(), one.seq_offsets,
+                              w.max_seq_len, w.alpha, one.num_targets, w.max_attn_len, w.contextual_seq_len,
+                              dout=do[lo:hi, heads].cpu())
+        assert O.rel_l2(full[0][lo:hi, heads].cpu(), ref) < BF16_TOL, b
+        for gr, rg, nm in zip(full[1:], rgrads, "qkv"):
+            assert O.rel_l2(gr[lo:hi, heads].cpu(), rg) < BF16_TOL, (b, nm)

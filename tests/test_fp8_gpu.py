@@ -63,3 +63,29 @@ def test_fp8_forward(case):
     assert torch.isfinite(out.float()).all()
     assert e_kernel < 1e-2, e_kernel   # arithmetic of the kernel itself: bf16-level
     assert e_total < 5e-2, e_total     # acceptance bound for fp8 against the unquantised fp32 result
+
+
+def test_fp8_config3_full_size():
+    """BASELINE configs[3] at full size through the FP8 forward: within the FP8 bound of the bf16
+    kernel's result on the same inputs (itself checked against the oracle at this size), the same
+    bits on a second run, and linear in the V scales (doubling them doubles the output exactly)."""
+    w = W.config3()
+    q, k, v = w.qkv(device=DEV)
+    offs_d, nt_d = w.seq_offsets.to(DEV), w.num_targets.to(DEV)
+    ref = G.hstu_mha(w.max_seq_len, w.alpha, q, k, v, offs_d, num_targets=nt_d, max_attn_len=w.max_attn_len,
+                     contextual_seq_len=w.contextual_seq_len)
+    q8, qs, bo = G.quantize_e4m3_block(q, offs_d)
+    k8, ks, _ = G.quantize_e4m3_block(k, offs_d)
+    v8, vs, _ = G.quantize_e4m3_block(v, offs_d)
+
+    def run(vs_):
+        return G.hstu_mha_fp8(w.max_seq_len, w.alpha, q8, k8, v8, qs, ks, vs_, bo, offs_d, num_targets=nt_d,
+                              max_attn_len=w.max_attn_len, contextual_seq_len=w.contextual_seq_len)
+
+    out = run(vs)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, run(vs))
+    assert torch.equal(run(vs * 2), out * 2)
+    err = float((out.float() - ref.float()).norm() / ref.float().norm())
+    assert err < 5e-2, err
