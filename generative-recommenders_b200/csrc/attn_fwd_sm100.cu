@@ -97,14 +97,16 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 
 // tanh and fma on two packed 16-bit values: one MUFU and one FMA-pipe instruction per pair
 template <bool IS_BF16>
-__device__ __forceinline__ uint32_t silu_pair(float h0, float h1) {
+__device__ __forceinline__ uint32_t silu_pair(float h0, float h1, uint32_t keep = 0xffffffffu) {
   uint32_t hh, t, r;
   if (IS_BF16) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hh) : "f"(h1), "f"(h0));
+    hh &= keep;
     asm("tanh.approx.bf16x2 %0, %1;" : "=r"(t) : "r"(hh));
     asm("fma.rn.bf16x2 %0, %1, %2, %1;" : "=r"(r) : "r"(hh), "r"(t));
   } else {
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hh) : "f"(h1), "f"(h0));
+    hh &= keep;
     asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(hh));
     asm("fma.rn.f16x2 %0, %1, %2, %1;" : "=r"(r) : "r"(hh), "r"(t));
   }
@@ -115,22 +117,47 @@ __device__ __forceinline__ uint32_t silu_pair(float h0, float h1) {
 // 16-bit pairs (the result is rounded to 16 bits for the tensor core anyway).  Masked-out scores
 // are replaced by h = 0 before the activation: silu(0) = 0 exactly.  fp16 inputs are clamped so
 // that the activation cannot overflow the format.
+// The 32 visibility bits of a chunk as eight shifted copies: copy s has bit 8i + 7 - s in the sign
+// position of byte i, from where a byte permute in sign-replication mode turns two bits into the
+// 16-bit lane masks of a packed pair - 3 instructions per pair instead of a test and a select per
+// element.
+struct PairMasks {
+  uint32_t sh[8];
+  __device__ __forceinline__ explicit PairMasks(uint32_t bits) {
+#pragma unroll
+    for (int s = 0; s < 8; ++s) sh[s] = bits << s;
+  }
+  // lane mask of elements (2x, 2x + 1): 0xffff in the half whose bit is set
+  __device__ __forceinline__ uint32_t pair(int x) const {
+    const int i = x / 4, s = 7 - (2 * x) % 8;
+    const uint32_t sel = ((0xCu + i) << 12) | ((0xCu + i) << 8) | ((8u + i) << 4) | (8u + i);
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(sh[s]), "r"(sh[s - 1]), "r"(sel));
+    return d;
+  }
+};
+
+// two fp32 products in one instruction (packed fp32 arithmetic of sm_100): {a0, a1} * s
+__device__ __forceinline__ void mul2(float a0, float a1, float s, float &d0, float &d1) {
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\t"
+      "mul.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(s));
+}
+
 template <bool IS_BF16, bool MASKED>
 __device__ __forceinline__ void silu_chunk(const uint32_t (&r)[32], uint32_t (&packed)[16], float half_alpha,
                                            uint32_t bits) {
+  const PairMasks pm(bits);
 #pragma unroll
   for (int x = 0; x < 16; ++x) {
-    float h0 = __uint_as_float(r[2 * x]) * half_alpha;
-    float h1 = __uint_as_float(r[2 * x + 1]) * half_alpha;
+    float h0, h1;
+    mul2(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]), half_alpha, h0, h1);
     if (!IS_BF16) {
       h0 = fminf(fmaxf(h0, -30000.f), 30000.f);
       h1 = fminf(fmaxf(h1, -30000.f), 30000.f);
     }
-    if (MASKED) {
-      h0 = (bits & (1u << (2 * x))) ? h0 : 0.f;
-      h1 = (bits & (1u << (2 * x + 1))) ? h1 : 0.f;
-    }
-    packed[x] = silu_pair<IS_BF16>(h0, h1);
+    packed[x] = MASKED ? silu_pair<IS_BF16>(h0, h1, pm.pair(x)) : silu_pair<IS_BF16>(h0, h1);
   }
 }
 
@@ -139,6 +166,7 @@ __device__ __forceinline__ void silu_chunk(const uint32_t (&r)[32], uint32_t (&p
 template <bool IS_BF16>
 __device__ __forceinline__ void silu_chunk_bias(const uint32_t (&r)[32], uint32_t (&packed)[16], float half_alpha,
                                                 uint32_t bits, const float *bp) {
+  const PairMasks pm(bits);
 #pragma unroll
   for (int x = 0; x < 16; ++x) {
     float h0 = fmaf(__uint_as_float(r[2 * x]), half_alpha, __ldg(bp - 2 * x));
@@ -147,9 +175,7 @@ __device__ __forceinline__ void silu_chunk_bias(const uint32_t (&r)[32], uint32_
       h0 = fminf(fmaxf(h0, -30000.f), 30000.f);
       h1 = fminf(fmaxf(h1, -30000.f), 30000.f);
     }
-    h0 = (bits & (1u << (2 * x))) ? h0 : 0.f;
-    h1 = (bits & (1u << (2 * x + 1))) ? h1 : 0.f;
-    packed[x] = silu_pair<IS_BF16>(h0, h1);
+    packed[x] = silu_pair<IS_BF16>(h0, h1, pm.pair(x));
   }
 }
 
