@@ -106,26 +106,25 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
 // 32 scores -> 8 words of P_hi and 8 words of P_lo (4 e4m3 per word).
 // silu(x) = h + h tanh(h), h = x / 2, on packed f16 pairs; `gain2` = f16x2 of the lift factor.
 // h is clamped after packing (an overflow to infinity in the conversion clamps back to the bound).
-// Masked-out scores are replaced by h = 0 before the activation: silu(0) = 0 exactly.
+// Masked-out scores are replaced by h = 0 (a lane mask on the packed pair) before the activation:
+// silu(0) = 0 exactly.
 template <bool MASKED>
 __device__ __forceinline__ void silu_chunk_fp8(const uint32_t (&r)[32], uint32_t (&hi)[8], uint32_t (&lo)[8],
                                                float half_alpha, uint32_t gain2, uint32_t bits) {
   const uint32_t bound = 0x77537753u, nbound = 0xf753f753u;   // +-30000 as f16x2
+  const PairMasks pm(bits);
 #pragma unroll
   for (int w = 0; w < 8; ++w) {
     uint16_t h16[2], l16[2];
 #pragma unroll
     for (int y = 0; y < 2; ++y) {
       const int x = 4 * w + 2 * y;
-      float h0 = __uint_as_float(r[x]) * half_alpha;
-      float h1 = __uint_as_float(r[x + 1]) * half_alpha;
-      if (MASKED) {
-        h0 = (bits & (1u << x)) ? h0 : 0.f;
-        h1 = (bits & (1u << (x + 1))) ? h1 : 0.f;
-      }
+      float h0, h1;
+      mul2(__uint_as_float(r[x]), __uint_as_float(r[x + 1]), half_alpha, h0, h1);
       uint32_t hh = to_f16x2(h0, h1), t, pp, back, res;
       asm("min.f16x2 %0, %0, %1;" : "+r"(hh) : "r"(bound));
       asm("max.f16x2 %0, %0, %1;" : "+r"(hh) : "r"(nbound));
+      if (MASKED) hh &= pm.pair(x / 2);
       asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(hh));
       asm("fma.rn.f16x2 %0, %1, %2, %1;" : "=r"(pp) : "r"(hh), "r"(t));
       asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(pp) : "r"(pp), "r"(gain2));

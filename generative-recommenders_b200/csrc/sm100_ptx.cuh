@@ -295,4 +295,34 @@ struct Tracer {
 #endif
 
 }  // namespace ptx
+
+// ------------------------------------------------------------------ activation helpers
+// The 32 visibility bits of a chunk as eight shifted copies: copy s has bit 8i + 7 - s in the sign
+// position of byte i, from where a byte permute in sign-replication mode turns two bits into the
+// 16-bit lane masks of a packed pair - 3 instructions per pair instead of a test and a select per
+// element.
+struct PairMasks {
+  uint32_t sh[8];
+  __device__ __forceinline__ explicit PairMasks(uint32_t bits) {
+#pragma unroll
+    for (int s = 0; s < 8; ++s) sh[s] = bits << s;
+  }
+  // lane mask of elements (2x, 2x + 1): 0xffff in the half whose bit is set
+  __device__ __forceinline__ uint32_t pair(int x) const {
+    const int i = x / 4, s = 7 - (2 * x) % 8;
+    const uint32_t sel = ((0xCu + i) << 12) | ((0xCu + i) << 8) | ((8u + i) << 4) | (8u + i);
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(sh[s]), "r"(sh[s - 1]), "r"(sel));
+    return d;
+  }
+};
+
+// two fp32 products in one instruction (packed fp32 arithmetic of sm_100): {a0, a1} * s
+__device__ __forceinline__ void mul2(float a0, float a1, float s, float &d0, float &d1) {
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\t"
+      "mul.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(s));
+}
+
 }  // namespace b200hstu
