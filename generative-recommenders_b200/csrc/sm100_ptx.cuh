@@ -324,5 +324,20 @@ __device__ __forceinline__ void mul2(float a0, float a1, float s, float &d0, flo
       : "=f"(d0), "=f"(d1)
       : "f"(a0), "f"(a1), "f"(s));
 }
+// {a0, a1} * {b0, b1}
+__device__ __forceinline__ void mul2v(float a0, float a1, float b0, float b1, float &d0, float &d1) {
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// {a0, a1} * {b0, b1} + {c0, c1}
+__device__ __forceinline__ void fma2(float a0, float a1, float b0, float b1, float c0, float c1, float &d0,
+                                     float &d1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
 
 }  // namespace b200hstu
