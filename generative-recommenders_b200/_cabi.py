@@ -68,6 +68,7 @@ class AttnArgs(Structure):
         ("bias_by_distance", c_void_p), ("bias_numel", c_int32), ("plan_mode", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_int64),
         ("delta_size", c_int32), ("reserved1", c_int32),
+        ("d_bias_by_distance", c_void_p),
     ]
 
 

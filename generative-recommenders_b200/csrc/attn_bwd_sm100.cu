@@ -71,6 +71,7 @@ struct BwdParams {
   const float *bias;       // bias_by_distance as given (element-wise path)
   int bias_numel;
   const float *bias_ext;   // centre of the signed-distance table (see BiasTable); NULL = no bias
+  float *dbias;            // q-stationary launch, optional: gradient of `bias` (fp32 [bias_numel], accumulated into)
   float half_alpha, alpha, inv_n;
   int H;
   int wide_stores;  // dq / dk / dv rows are 32-byte aligned
@@ -241,6 +242,43 @@ __device__ __forceinline__ void phase_b_chunk(uint32_t t_in, uint32_t t_out, con
   tmem_st16(t_out, dk);
 }
 
+// Phase B of the q-stationary launch when the gradient of the relative bias is wanted: the same dS,
+// and its sums along the diagonals of the chunk (query - key distance constant).  Lane l of the
+// warp owns query row l of 32 consecutive rows, register x holds key column x of the chunk, so the
+// element (l, x) belongs to diagonal l - x.  Rotating register x by x lanes brings every element
+// of diagonal m to lane m mod 32: lane l collects diagonal l (elements that did not wrap around) and
+// diagonal l - 32 (those that did) - which are the distances of the lane's own row to the chunk's
+// first column and to the column 32 before it.  Two fp32 atomics per lane and chunk then add the
+// sums (times the attention scale, which the 16-bit dS does not carry) to the gradient.  Rows
+// beyond the sequence hold scores of the next sequence's tokens: they are cleared first.
+template <bool IS_BF16>
+__device__ __forceinline__ void phase_b_chunk_dbias(uint32_t t_in, uint32_t t_out, const uint32_t (&keep)[16],
+                                                    float *dbias, int bias_numel, int dist, bool row_valid, int lane,
+                                                    float sc) {
+  uint32_t rp[32];
+  tmem_ld32(t_in, rp);
+  tc_wait_ld();
+  uint32_t dk[16];
+  float pos = 0.f, neg = 0.f;
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    const float2 g = unpack_keep(keep[x]);
+    float d0, d1;
+    mul2v(__uint_as_float(rp[2 * x]), __uint_as_float(rp[2 * x + 1]), g.x, g.y, d0, d1);
+    dk[x] = pack2h(d0, d1, IS_BF16);
+    d0 = row_valid ? d0 : 0.f;
+    d1 = row_valid ? d1 : 0.f;
+    const float r0 = __shfl_sync(0xffffffffu, d0, (lane + 2 * x) & 31);
+    const float r1 = __shfl_sync(0xffffffffu, d1, (lane + 2 * x + 1) & 31);
+    if (lane + 2 * x < 32) pos += r0; else neg += r0;
+    if (lane + 2 * x + 1 < 32) pos += r1; else neg += r1;
+  }
+  tmem_st16(t_out, dk);
+  const int a0 = dist < 0 ? -dist : dist, a1 = dist - 32 < 0 ? 32 - dist : dist - 32;
+  if (pos != 0.f && a0 < bias_numel) atomicAdd(dbias + a0, pos * sc);
+  if (neg != 0.f && a1 < bias_numel) atomicAdd(dbias + a1, neg * sc);
+}
+
 // What the activation warps do for one streamed tile: phase A, hand the score region back, phase
 // B, hand the dP region back.  MODE 0: every element visible; 1: per-row / per-column bit masks;
 // 2: element-wise mask and bias.
@@ -251,6 +289,11 @@ struct ActTile {
   float half_alpha;
   int lane;
   const float *bias_at;     // table entry of (this thread's row / column, first streamed position); NULL = no bias
+  float *dbias;             // q-stationary launch: gradient of the bias wanted (NULL = no)
+  int dbias_numel;
+  const float *sc_ptr;      // attention scale on the device, or NULL (1 / max_seq_len, in inv_n)
+  float inv_n;
+  bool row_valid;           // this thread's query row lies inside the sequence
 };
 
 template <bool IS_BF16, bool DKDV, int MODE, bool BIAS>
@@ -289,8 +332,15 @@ __device__ __forceinline__ bool act_tile_body(const WaitCtx &wc, const ActTile &
   if (!mbar_wait(wc, a.t_full + 8, a.parity, 603)) return false;
   tc_fence_after();
   tr.mark(32);
-  phase_b_chunk<IS_BF16, !DKDV>(a.tP, a.tP, keep0);
-  phase_b_chunk<IS_BF16, !DKDV>(a.tP + 32, a.tP + 16, keep1);
+  if (!DKDV && a.dbias != nullptr) {
+    const float sc = a.sc_ptr != nullptr ? a.sc_ptr[0] : a.inv_n;
+    phase_b_chunk_dbias<IS_BF16>(a.tP, a.tP, keep0, a.dbias, a.dbias_numel, own - c0, a.row_valid, a.lane, sc);
+    phase_b_chunk_dbias<IS_BF16>(a.tP + 32, a.tP + 16, keep1, a.dbias, a.dbias_numel, own - c0 - 32, a.row_valid,
+                                 a.lane, sc);
+  } else {
+    phase_b_chunk<IS_BF16, !DKDV>(a.tP, a.tP, keep0);
+    phase_b_chunk<IS_BF16, !DKDV>(a.tP + 32, a.tP + 16, keep1);
+  }
   tc_wait_st();
   tc_fence_before();
   __syncwarp();
@@ -798,6 +848,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           at.lane = lane;
           // signed distance query - key of (own row / column, first streamed position)
           at.bias_at = BIAS ? p.bias_ext + (DKDV ? c0 - own : own - c0) : nullptr;
+          // only the bias instantiation of the q-stationary launch carries the bias-gradient code
+          at.dbias = (BIAS && !DKDV) ? p.dbias : nullptr;
+          at.dbias_numel = p.bias_numel;
+          at.sc_ptr = p.attn_scale;
+          at.inv_n = p.inv_n;
+          at.row_valid = own < L;
           if (!exact_only) {
             // one code path for fully and partially visible tiles: the tensor pipe, not the
             // activation, bounds this kernel, and code that runs once per item is slow to fetch
@@ -946,7 +1002,8 @@ int launch_bwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.bias_numel = a.bias_numel;
   const int64_t eb = bias_table_bytes(a.bias_by_distance, a.max_seq_len);
   BiasTable bt{a.bias_by_distance, a.bias_numel, reinterpret_cast<float *>(a.workspace), a.max_seq_len};
-  p.bias_ext = a.bias_by_distance ? bt.dst + (a.max_seq_len - 1) : nullptr;
+  p.bias_ext = a.bias_by_distance ? bt.centre() : nullptr;
+  p.dbias = a.bias_by_distance ? a.d_bias_by_distance : nullptr;
   p.half_alpha = 0.5f * a.alpha;
   p.alpha = a.alpha;
   p.inv_n = 1.f / (float)a.max_seq_len;

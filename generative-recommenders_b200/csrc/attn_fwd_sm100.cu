@@ -861,7 +861,7 @@ int launch_fwd_tc(const b200_hstu_attn_args &a, cudaStream_t st) {
   p.attn_scale_numel = a.attn_scale_numel;
   p.bias = a.bias_by_distance;
   p.bias_numel = a.bias_numel;
-  p.bias_ext = a.bias_by_distance ? bt.dst + (a.max_seq_len - 1) : nullptr;
+  p.bias_ext = a.bias_by_distance ? bt.centre() : nullptr;
   p.half_alpha = 0.5f * a.alpha;
   p.inv_n = 1.f / (float)a.max_seq_len;
   p.H = a.H;

@@ -11,20 +11,25 @@
 // Properties a user must know:
 //   * The array is 1 MiB and lives in every CUDA context that loads the library, from load until
 //     the process exits.
-//   * It is big enough for total_L / 128 + B + 1 <= 32 766 work items (for example 4 M tokens in
-//     up to ~1000 sequences); larger batches are rejected with B200_HSTU_EWORKSPACE and must go
-//     through b200_hstu_attn_fwd() with caller scratch.
+//   * It is big enough for total_L / 128 + B + 1 <= 32 767 work items (for example 4 M tokens in
+//     up to ~1000 sequences).  With a relative bias (bias_by_distance) the signed-distance table
+//     comes out of the same array, 8 * (roundup128(max_seq_len) + 256) bytes rounded up to 256, and
+//     the item limit shrinks by that many bytes / 32.  Larger batches are rejected with
+//     B200_HSTU_EWORKSPACE and must go through b200_hstu_attn_fwd() with caller scratch.
 //   * The first call on each device looks up the array's device address
-//     (cudaGetSymbolAddress); make that first call outside any stream capture.  Later calls only
-//     launch kernels.
+//     (cudaGetSymbolAddress) and remembers it for the life of the process; make that first call
+//     outside any stream capture.  Every call queues one 16-byte memset (the list header) and the
+//     two kernels.  Resetting the device (cudaDeviceReset) invalidates the remembered address:
+//     a process that resets a device must not use this entry point on it afterwards.
 //   * There is one array per device, shared by all calls and all streams.  Calls are safe back to
 //     back on one stream; two calls that can overlap on the GPU (different streams without an
-//     ordering between them) race on the work list.  The array keeps the previous call's list;
-//     each call rewrites the header before it is read, nothing else is carried over.
+//     ordering between them) race on the work list.  The array keeps the previous call's list and
+//     bias table; the header (item count, status word, claim counter) is cleared by every call and
+//     rewritten by its planning kernel, the table is rebuilt, nothing else is carried over.
 //   * No cudaMalloc / cudaFree / allocating library call is made, on the first call or later.
 #include <mutex>
 
-#include "common.cuh"
+#include "attn_plan.cuh"
 
 namespace {
 
@@ -73,14 +78,17 @@ int b200_hstu_attn_fwd_static_scratch(const b200_hstu_attn_args *args, b200_hstu
   if (need > kStaticScratchBytes)
     return b200hstu::fail(B200_HSTU_EWORKSPACE,
                           "this batch needs %lld bytes of scratch but the built-in buffer holds %lld "
-                          "(total_L / 128 + B + 1 must stay below 32767); use b200_hstu_attn_fwd with caller scratch",
+                          "(32 bytes per work item, total_L / 128 + B + 1 of them, plus the bias table if any); "
+                          "use b200_hstu_attn_fwd with caller scratch",
                           (long long)need, (long long)kStaticScratchBytes);
   if (need > 0) {
     void *ptr = nullptr;
     int st = scratch_address(&ptr);
     if (st != 0) return st;
-    // the header (item count, status word) must not carry over from the previous call
-    cudaError_t e = cudaMemsetAsync(ptr, 0, 256, (cudaStream_t)stream);
+    // The list header (item count, status word, claim counter) must not carry over from the
+    // previous call.  Layout of the scratch: [bias table (if any) | header | items].
+    unsigned char *hdr = static_cast<unsigned char *>(ptr) + b200hstu::bias_table_bytes(a.bias_by_distance, a.max_seq_len);
+    cudaError_t e = cudaMemsetAsync(hdr, 0, sizeof(b200hstu::PlanHeader), (cudaStream_t)stream);
     if (e != cudaSuccess) return b200hstu::check_cuda(e, "clearing the static scratch header");
     a.workspace = ptr;
     a.workspace_bytes = kStaticScratchBytes;

@@ -441,27 +441,37 @@ __device__ __forceinline__ void plan_body(const AttnGeomParams &g, PlanHeader *h
 
 // ---------------------------------------------------------------------------------------
 // Relative position bias as the kernels read it: a table over the signed distance i - j,
-//   ext[k] = bias[|k|] / 2  for |k| < numel, else 0,   k in (-N, N),
+//   ext[k] = bias[|k|] / 2  for |k| < numel, else 0,   k in (-P, P),
 // so that a thread walking along a row (or a column) reads consecutive entries with constant
 // offsets from one pointer: no absolute value, no bounds test, no index arithmetic per element.
 // (The factor 1/2 is the h = x / 2 of the tanh form of SiLU.)  The table lives at the start of
 // the caller's scratch and is rebuilt by the planning launch of every call that has a bias.
+//
+// P covers every distance a thread can form, not only those of valid pairs: rows and columns of a
+// tile beyond the end of a sequence (up to the next multiple of 128, plus the second query tile of
+// a forward pair that does not exist, plus the offset of an unaligned query tile of the cached-
+// inference forward) are read before they are masked, so P = roundup128(N) + 256.
 // ---------------------------------------------------------------------------------------
 struct BiasTable {
   const float *src;   // bias_by_distance [numel]; NULL = no bias
   int numel;
-  float *dst;         // 2 N - 1 floats
-  int N;
+  float *dst;         // 2 P - 1 floats
+  int N;              // max_seq_len
+  __host__ __device__ __forceinline__ int half_width() const { return (N + 127) / 128 * 128 + 256; }
+  // the entry of distance 0
+  __host__ __device__ __forceinline__ const float *centre() const { return dst + (half_width() - 1); }
 };
 inline int64_t bias_table_bytes(const void *bias, int max_seq_len) {
   if (bias == nullptr) return 0;
-  int64_t n = (2 * (int64_t)max_seq_len - 1) * (int64_t)sizeof(float);
+  const int64_t P = ((int64_t)max_seq_len + 127) / 128 * 128 + 256;
+  int64_t n = (2 * P - 1) * (int64_t)sizeof(float);
   return (n + 255) / 256 * 256;
 }
 __device__ __forceinline__ void build_bias_table(const BiasTable &t) {
   if (t.src == nullptr) return;
-  for (int x = threadIdx.x; x < 2 * t.N - 1; x += blockDim.x) {
-    const int k = x - (t.N - 1);
+  const int P = t.half_width();
+  for (int x = threadIdx.x; x < 2 * P - 1; x += blockDim.x) {
+    const int k = x - (P - 1);
     const int a = k < 0 ? -k : k;
     t.dst[x] = a < t.numel ? 0.5f * t.src[a] : 0.f;
   }

@@ -11,6 +11,7 @@
 // generative_recommenders/ops/triton/triton_hstu_attention.py:1905-2020):
 //   x = alpha * q.k (+ bias[|i-j|]);  P = silu(x) * scale * mask;  O = P V
 //   dV = P^T dO;  dP = dO V^T;  dS = dP * silu'(x) * scale * mask;  dQ = alpha dS K;  dK = alpha dS^T Q
+//   dbias[d] = sum of dS over the pairs with |i - j| = d (all heads and sequences), when asked for
 #include "common.cuh"
 
 namespace b200hstu {
@@ -28,6 +29,7 @@ struct SimtParams {
   int64_t attn_scale_numel;
   const float *bias;
   int bias_numel;
+  float *dbias;   // backward, optional: gradient of `bias`, accumulated with atomics
   int64_t q_rs, k_rs, v_rs, o_rs, do_rs, dq_rs, dk_rs, dv_rs;
   int64_t q_hs, k_hs, v_hs, o_hs, do_hs, dq_hs, dk_hs, dv_hs;
   int H, dqk, dv_dim, max_seq_len;
@@ -167,11 +169,20 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
         if (MODE == 0) {
           val = ok ? siluf_(x) * sc : 0.f;
         } else {
-          val = ok ? dp[jj] * dsiluf_(x) * sc * p.alpha : 0.f;
+          val = ok ? dp[jj] * dsiluf_(x) * sc : 0.f;   // dS; alpha is applied to the finished dQ row
         }
         Ps[r * (T + 1) + cg + 4 * jj] = val;
       }
       __syncthreads();
+      if (MODE == 1 && p.dbias != nullptr && threadIdx.x < 2 * T - 1) {
+        // one thread per diagonal of the 32 x 32 tile: rows - columns = m
+        const int m = (int)threadIdx.x - (T - 1);
+        float sum = 0.f;
+        for (int rr = m > 0 ? m : 0; rr < T && rr - m < T; ++rr) sum += Ps[rr * (T + 1) + rr - m];
+        int dist = m0 - n0 + m;
+        dist = dist < 0 ? -dist : dist;
+        if (sum != 0.f && dist < p.bias_numel) atomicAdd(p.dbias + dist, sum);
+      }
       const float *Bm = MODE == 0 ? Vs : Ks;
       for (int j = 0; j < T; ++j) {
         float pv = Ps[r * (T + 1) + j];
@@ -196,10 +207,11 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
       op = (E *)p.out + (qrow0 + r) * p.o_rs + (int64_t)h * p.o_hs;
     else
       op = (E *)p.dq + (int64_t)(g.start + i) * p.dq_rs + (int64_t)h * p.dq_hs;
+    const float fin = MODE == 1 ? p.alpha : 1.f;
 #pragma unroll
     for (int cc = 0; cc < MAXD / 4; ++cc) {
       int x = cg + 4 * cc;
-      if (x < out_d) op[x] = from_f32<E>(acc_o[cc]);
+      if (x < out_d) op[x] = from_f32<E>(acc_o[cc] * fin);
     }
   }
 }
@@ -297,6 +309,7 @@ SimtParams make_params(const b200_hstu_attn_args &a) {
   p.seq_offsets = a.seq_offsets; p.num_targets = a.num_targets;
   p.attn_scale = a.attn_scale; p.attn_scale_numel = a.attn_scale_numel;
   p.bias = a.bias_by_distance; p.bias_numel = a.bias_numel;
+  p.dbias = a.bias_by_distance != nullptr ? a.d_bias_by_distance : nullptr;
   p.q_rs = a.q_row_stride; p.k_rs = a.k_row_stride; p.v_rs = a.v_row_stride; p.o_rs = a.o_row_stride;
   p.do_rs = a.do_row_stride; p.dq_rs = a.dq_row_stride; p.dk_rs = a.dk_row_stride; p.dv_rs = a.dv_row_stride;
   p.q_hs = a.q_head_stride; p.k_hs = a.k_head_stride; p.v_hs = a.v_head_stride; p.o_hs = a.o_head_stride;

@@ -103,10 +103,12 @@ def hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, at
 
 def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
                        contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance=None,
-                       planned_scratch=None) -> None:
+                       planned_scratch=None, d_bias=None) -> None:
     """Fills caller-allocated dq / dk / dv (the ownership rule of the reference's backward,
     triton_hstu_attention.py:3059-3079).  ``planned_scratch``: the scratch a forward with
-    ``plan_for_backward`` returned for the same arguments; its lists serve one backward call."""
+    ``plan_for_backward`` returned for the same arguments; its lists serve one backward call.
+    ``d_bias``: zero-filled fp32 tensor shaped like ``bias_by_distance``; the gradient of the
+    bias is added into it."""
     if q.shape[0] == 0:
         return
     a = _cabi.AttnArgs()
@@ -118,6 +120,8 @@ def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targe
     a.dq_row_stride, a.dq_head_stride = dq.stride(0), dq.stride(1)
     a.dk_row_stride, a.dk_head_stride = dk.stride(0), dk.stride(1)
     a.dv_row_stride, a.dv_head_stride = dv.stride(0), dv.stride(1)
+    if d_bias is not None and bias_by_distance is not None:
+        a.d_bias_by_distance = d_bias.data_ptr()
     reuse = planned_scratch is not None and _cabi.lib().b200_hstu_attn_workspace_bytes(a, 1) > 0
     if reuse:
         a.plan_mode = _PLAN_REUSE
@@ -135,7 +139,7 @@ class _HstuMhaFunction(torch.autograd.Function):
                 max_attn_len, contextual_seq_len, min_full_attn_seq_len):
         # when a gradient will be asked for, the forward's planning launch builds the backward's
         # work lists as well; the first backward call consumes them
-        plan = any(ctx.needs_input_grad[:3])
+        plan = any(ctx.needs_input_grad[:3]) or ctx.needs_input_grad[6]
         out = hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
                                  contextual_seq_len, min_full_attn_seq_len, bias_by_distance, plan_for_backward=plan)
         ctx.planned_scratch = None
@@ -156,10 +160,13 @@ class _HstuMhaFunction(torch.autograd.Function):
         dk = torch.empty_like(k, memory_format=torch.contiguous_format)
         dv = torch.empty_like(v, memory_format=torch.contiguous_format)
         planned, ctx.planned_scratch = ctx.planned_scratch, None   # a second backward plans for itself
+        d_bias = None
+        if bias_by_distance is not None and ctx.needs_input_grad[6]:
+            d_bias = torch.zeros_like(bias_by_distance)
         hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
                            contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance,
-                           planned_scratch=planned)
-        return dq, dk, dv, None, None, None, None, None, None, None, None, None
+                           planned_scratch=planned, d_bias=d_bias)
+        return dq, dk, dv, None, None, None, d_bias, None, None, None, None, None
 
 
 def hstu_mha(
@@ -188,7 +195,8 @@ def hstu_mha(
     ``sort_by_length`` and ``enable_tma`` are accepted and ignored: work is always scheduled
     longest-first and K/V always stream through TMA.  ``bias_by_distance`` is an extension
     (fp32 ``[n]``: a relative-position bias added to ``alpha * q.k`` before SiLU, indexed by
-    ``|i - j|``, shared by all heads; no gradient is produced for it).
+    ``|i - j|``, shared by all heads; differentiable - the research model trains the tables it is
+    gathered from, generative_recommenders/research/modeling/sequential/hstu.py:65-143).
     """
     _require_cuda_backend(kernel)
     torch._assert(max_seq_len > 0, "max_seq_len must be larger than 0")
@@ -215,7 +223,7 @@ def hstu_mha(
         if attn_scale.numel() not in (1, q.shape[0]):
             raise RuntimeError("attn_scale must be a scalar or have one entry per token")
     if bias_by_distance is not None:
-        bias_by_distance = bias_by_distance.to(torch.float32).contiguous()
+        bias_by_distance = bias_by_distance.to(torch.float32).reshape(-1).contiguous()
     return _HstuMhaFunction.apply(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, int(max_seq_len),
                                   float(alpha), int(max_attn_len), int(contextual_seq_len),
                                   int(min_full_attn_seq_len))

@@ -66,13 +66,18 @@ _PREPARED = {}
 
 
 def _prepared_workspace(nw, nb, w, b, nbytes, device, allow_cache):
-    # only module parameters are worth remembering (a cast copy made for one call never comes back)
-    if (not allow_cache or not isinstance(w, torch.nn.Parameter)
-            or torch.cuda.is_current_stream_capturing()):
+    # Only module parameters are worth remembering, and only when all four tensors are the
+    # parameters themselves: a cast copy made for one call never comes back, and its id / address /
+    # version can recur on a later, different copy.
+    if (not allow_cache or torch.cuda.is_current_stream_capturing()
+            or not all(isinstance(t, torch.nn.Parameter) for t in (w, nw, nb, b))):
         return torch.empty(nbytes, dtype=torch.uint8, device=device), False
     key = id(w)
-    sig = tuple((id(t), t.data_ptr(), t._version) for t in (w, nw, nb, b))
+    stream = torch.cuda.current_stream(device).cuda_stream
+    sig = tuple((id(t), t.data_ptr(), t._version) for t in (w, nw, nb, b)) + (stream,)
     hit = _PREPARED.get(key)
+    # the workspace was prepared on `stream`; a call on another stream is not ordered after that
+    # preparation, so it prepares (and then owns) a new one
     if hit is not None and hit[0]() is w and hit[1] == sig and hit[2].numel() == nbytes:
         return hit[2], True
     ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
@@ -153,14 +158,15 @@ class _FusedUqvkFunction(torch.autograd.Function):
     (csrc/ln_linear_sm100.cu)."""
 
     @staticmethod
-    def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, num_heads, attn_dim, hidden_dim):
+    def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, num_heads, attn_dim, hidden_dim, grad_mode=True):
         M = x.shape[0]
         hv, ha = hidden_dim * num_heads, attn_dim * num_heads
         nw = norm_weight.to(x.dtype).contiguous()
         nb = norm_bias.to(x.dtype).contiguous()
         w = weight.to(x.dtype).contiguous()
         b = bias.to(x.dtype).contiguous()
-        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, not any(ctx.needs_input_grad))
+        no_grad = not (grad_mode and any(ctx.needs_input_grad))
+        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, no_grad)
         ctx.set_materialize_grads(False)
         ctx.save_for_backward(x, nw, nb, w, uvqk, mean, rstd)
         ctx.cfg = (eps, hv, ha, norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
@@ -183,7 +189,7 @@ class _FusedUqvkFunction(torch.autograd.Function):
             else:
                 d_uvqk[:, lo:lo + width].copy_(g.reshape(M, width))
         dx, dnw, dnb, dw, db = _fused_uqvk_backward(x, nw, nb, w, uvqk, mean, rstd, eps, hv, du, d_uvqk)
-        return dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None, None, None
+        return dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None, None, None, None
 
 
 class _FusedPreprocessAttentionFunction(torch.autograd.Function):
@@ -193,7 +199,7 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, num_heads, attn_dim, hidden_dim, seq_offsets,
-                num_targets, bias_by_distance, max_seq_len, alpha, max_attn_len, contextual_seq_len):
+                num_targets, bias_by_distance, max_seq_len, alpha, max_attn_len, contextual_seq_len, grad_mode=True):
         from .hstu_attention import hstu_attention_fwd
 
         M = x.shape[0]
@@ -202,11 +208,12 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
         nb = norm_bias.to(x.dtype).contiguous()
         w = weight.to(x.dtype).contiguous()
         b = bias.to(x.dtype).contiguous()
-        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, not any(ctx.needs_input_grad))
+        no_grad = not (grad_mode and any(ctx.needs_input_grad))
+        uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, no_grad)
         v = uvqk[:, hv:2 * hv].view(M, num_heads, hidden_dim)
         q = uvqk[:, 2 * hv:2 * hv + ha].view(M, num_heads, attn_dim)
         k = uvqk[:, 2 * hv + ha:].view(M, num_heads, attn_dim)
-        plan = any(ctx.needs_input_grad[:6])
+        plan = not no_grad and (any(ctx.needs_input_grad[:6]) or ctx.needs_input_grad[11])
         ctx.set_materialize_grads(False)  # k / v usually get no gradient: do not add zeros for them
         out = hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, None, max_attn_len,
                                  contextual_seq_len, 0, bias_by_distance, plan_for_backward=plan)
@@ -231,6 +238,7 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
         dv = d_uvqk[:, hv:2 * hv].view(M, H, V)
         dq = d_uvqk[:, 2 * hv:2 * hv + ha].view(M, H, A)
         dk = d_uvqk[:, 2 * hv + ha:].view(M, H, A)
+        d_bias = None
         if dattn is None:
             d_uvqk[:, hv:].zero_()
         else:
@@ -240,15 +248,18 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
             q_ = uvqk[:, 2 * hv:2 * hv + ha].view(M, H, A)
             k_ = uvqk[:, 2 * hv + ha:].view(M, H, A)
             planned, ctx.planned_scratch = ctx.planned_scratch, None
+            if bias_by_distance is not None and ctx.needs_input_grad[11]:
+                d_bias = torch.zeros_like(bias_by_distance)
             hstu_attention_bwd(dattn, max_seq_len, alpha, q_, k_, v_, seq_offsets, num_targets, None, max_attn_len,
-                               contextual_seq_len, 0, dq, dk, dv, bias_by_distance, planned_scratch=planned)
+                               contextual_seq_len, 0, dq, dk, dv, bias_by_distance, planned_scratch=planned,
+                               d_bias=d_bias)
         if dk_ext is not None:
             dk.add_(dk_ext)
         if dv_ext is not None:
             dv.add_(dv_ext)
         dx, dnw, dnb, dw, db = _fused_uqvk_backward(x, nw, nb, w, uvqk, mean, rstd, eps, hv, du, d_uvqk)
         return (dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None, None, None,
-                None, None, None, None, None, None, None)
+                None, None, d_bias, None, None, None, None, None)
 
 
 _FUSED_UQVK = True
@@ -280,7 +291,7 @@ def hstu_compute_uqvk(
     hv, ha = hidden_dim * num_heads, attn_dim * num_heads
     if _FUSED_UQVK and _fused_uqvk_supported(x, uvqk_weight, hv):
         return _FusedUqvkFunction.apply(x, norm_weight, norm_bias, float(norm_eps), uvqk_weight, uvqk_bias,
-                                        num_heads, attn_dim, hidden_dim)
+                                        num_heads, attn_dim, hidden_dim, torch.is_grad_enabled())
     else:
         normed_x = layer_norm(x, weight=norm_weight, bias=norm_bias, eps=norm_eps, kernel=kernel)
         uvqk = addmm(uvqk_bias, normed_x, uvqk_weight, kernel)
@@ -463,10 +474,11 @@ def hstu_preprocess_and_attention(
         nt = _i32(num_targets)
         if nt is not None and nt.numel() != offs.numel() - 1:
             raise RuntimeError("num_targets must have one entry per sequence")
-        rab = None if bias_by_distance is None else bias_by_distance.to(torch.float32).contiguous()
+        rab = None if bias_by_distance is None else bias_by_distance.to(torch.float32).reshape(-1).contiguous()
         u, attn, k, v = _FusedPreprocessAttentionFunction.apply(
             x, norm_weight, norm_bias, float(norm_eps), uvqk_weight, uvqk_bias, num_heads, attn_dim, hidden_dim,
-            offs, nt, rab, int(max_seq_len), float(attn_alpha), int(max_attn_len), int(contextual_seq_len))
+            offs, nt, rab, int(max_seq_len), float(attn_alpha), int(max_attn_len), int(contextual_seq_len),
+            torch.is_grad_enabled())
         return u, attn.view(-1, hidden_dim * num_heads), k, v
     u, q, k, v = hstu_compute_uqvk(
         x=x, norm_weight=norm_weight, norm_bias=norm_bias, norm_eps=norm_eps, num_heads=num_heads,

@@ -12,8 +12,9 @@ runs ``delta_hstu_mha`` for the new rows only.
 One extension: ``rel_bias_table`` (``num_buckets + 1`` learnable entries, indexed by
 ``clamp(floor(ln(max(|i - j|, 1)) / 0.301), 0, num_buckets)`` of the position distance) adds the
 research model's bucketised relative bias (generative_recommenders/research/modeling/sequential/
-hstu.py:86-143, 610-613 with the time bias off) to the attention scores.  The attention kernels
-produce no gradient for the table.
+hstu.py:86-143, 610-613 with the time bias off) to the attention scores.  The table is trained like
+the reference's: the attention backward returns the gradient per distance, autograd scatters it
+to the buckets.
 """
 
 from dataclasses import dataclass
@@ -224,7 +225,7 @@ class STULayer(torch.nn.Module):
     ) -> torch.Tensor:
         bias = None
         if self._rel_bias_table is not None:
-            bias = position_bias_by_distance(self._rel_bias_table.detach(), max_seq_len)
+            bias = position_bias_by_distance(self._rel_bias_table, max_seq_len)
         with torch.autograd.profiler.record_function("## stu_preprocess_and_attention ##"):
             u, attn_output, k, v = hstu_preprocess_and_attention(
                 x=x,

@@ -105,6 +105,12 @@ typedef struct b200_hstu_attn_args {
      max_seq_len long; attn_scale must be NULL or a scalar. */
   int32_t delta_size;
   int32_t reserved1;
+  /* bwd only, optional: gradient of bias_by_distance, fp32 [bias_numel].  The backward ADDS into this
+     caller-zeroed buffer (fp32 atomics: the sum over pairs, heads and sequences of dL/dscore at each
+     |i - j|; the order of the additions, and with it the last bits, varies from run to run).  NULL =
+     not wanted.  The research model trains these tables
+     (generative_recommenders/research/modeling/sequential/hstu.py:65-143, 203-211). */
+  float *d_bias_by_distance;
 } b200_hstu_attn_args;
 
 /*
@@ -128,8 +134,10 @@ int b200_hstu_attn_bwd(const b200_hstu_attn_args *args, b200_hstu_stream_t strea
  * allocator at hand).  Same arguments and result as b200_hstu_attn_fwd(), but args->workspace is
  * ignored: the work list lives in a 1 MiB array inside the library's device image (held by every
  * context that loads the library until exit).  Batches needing more (total_L / 128 + B + 1 >
- * 32 766 items) are rejected with B200_HSTU_EWORKSPACE.  The first call on a device looks the
- * array up with cudaGetSymbolAddress - make it outside any stream capture; no call allocates.
+ * 32 767 items of 32 bytes; a bias_by_distance table takes 8 * (roundup128(max_seq_len) + 256)
+ * bytes of the same array) are rejected with B200_HSTU_EWORKSPACE.  The first call on a device
+ * looks the array up with cudaGetSymbolAddress - make it outside any stream capture; no call
+ * allocates.
  * One array per device is shared by all calls: back-to-back calls on one stream are fine, calls
  * that may overlap on the GPU race.  This entry point has no counterpart in the reference (its
  * ops allocate their scratch per call through torch).
@@ -139,7 +147,8 @@ int64_t b200_hstu_attn_fwd_static_scratch_max_bytes(void);
 
 /* Bytes of scratch that fwd (backward = 0), bwd (backward = 1) or a forward that also plans the
    backward (backward = 2, plan_mode FOR_BACKWARD / REUSE) need for these sizes.
-   Host function; depends on B, H, dqk, dv, total_L, dtype, impl only. */
+   Host function; depends on B, H, dqk, dv, total_L, dtype, impl, and - through the table of a
+   relative bias - on whether bias_by_distance is set and on max_seq_len. */
 int64_t b200_hstu_attn_workspace_bytes(const b200_hstu_attn_args *args, int backward);
 
 /*

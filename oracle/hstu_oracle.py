@@ -576,3 +576,32 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     den = b.norm().item()
     num = (a - b).norm().item()
     return num / den if den > 0 else num
+
+
+def per_sequence_rel_l2(a: torch.Tensor, b: torch.Tensor, seq_offsets: torch.Tensor) -> float:
+    """Largest ``rel_l2`` over the sequences of a jagged tensor (rows ``seq_offsets[s] ..
+    seq_offsets[s+1]``), so that a short sequence cannot hide behind the norm of the long ones.  A
+    sequence whose reference rows are all zero contributes its absolute error."""
+    a = a.detach().to(torch.float64).cpu()
+    b = b.detach().to(torch.float64).cpu()
+    offs = seq_offsets.to(torch.int64).cpu().tolist()
+    worst = 0.0
+    for s, e in zip(offs[:-1], offs[1:]):
+        if e <= s:
+            continue
+        den = b[s:e].norm().item()
+        num = (a[s:e] - b[s:e]).norm().item()
+        worst = max(worst, num / den if den > 0 else num)
+    return worst
+
+
+def max_abs_ratio(a: torch.Tensor, b: torch.Tensor) -> float:
+    """``max|a - b| / max|b|``: the largest element-wise error in units of the largest reference
+    element (0 for empty tensors)."""
+    if b.numel() == 0:
+        return 0.0
+    a = a.detach().to(torch.float64).cpu()
+    b = b.detach().to(torch.float64).cpu()
+    den = b.abs().max().item()
+    num = (a - b).abs().max().item()
+    return num / den if den > 0 else num

@@ -244,6 +244,42 @@ def make_bias():
     return dict(N=N, ts_w=mod._ts_w.detach().clone(), timestamps=ts, rab=rab[0].clone())
 
 
+def make_bias_attention():
+    """The research model's attention with a learnable relative position bias
+    (research/modeling/sequential/hstu.py: ``RelativePositionalBias`` :65-83,
+    ``_hstu_attention_maybe_from_cache`` :150-229): output, and the gradients of q, k, v and of
+    the bias weights ``_w`` (one weight per signed distance).  The mask is plain causal."""
+    from generative_recommenders.research.modeling.sequential.hstu import (
+        RelativePositionalBias,
+        _hstu_attention_maybe_from_cache,
+    )
+    g = torch.Generator().manual_seed(31)
+    torch.manual_seed(31)
+    N, H, A, V = 48, 2, 16, 16
+    lengths = torch.tensor([48, 7, 30, 1, 19])
+    offsets = _offsets(lengths)
+    L = int(offsets[-1])
+    q = torch.randn(L, H * A, generator=g).requires_grad_(True)
+    k = torch.randn(L, H * A, generator=g).requires_grad_(True)
+    v = torch.randn(L, H * V, generator=g).requires_grad_(True)
+    dout = torch.randn(L, H * V, generator=g)
+    mod = RelativePositionalBias(max_seq_len=N)
+    with torch.no_grad():
+        mod._w.mul_(20.0)   # std 0.4: large enough to matter next to q.k
+    causal = torch.tril(torch.ones(N, N))
+    ts = torch.zeros(len(lengths), N, dtype=torch.int64)
+    out, _, _ = _hstu_attention_maybe_from_cache(
+        num_heads=H, attention_dim=A, linear_dim=V, q=q, k=k, v=v, cached_q=None, cached_k=None,
+        delta_x_offsets=None, x_offsets=offsets, all_timestamps=ts, invalid_attn_mask=causal,
+        rel_attn_bias=mod)
+    out.backward(dout)
+    with torch.no_grad():
+        rab = mod(ts)[0].clone()
+    return dict(N=N, H=H, A=A, V=V, seq_offsets=offsets, q=q.detach().clone(), k=k.detach().clone(),
+                v=v.detach().clone(), dout=dout, w=mod._w.detach().clone(), rab=rab, out=out.detach().clone(),
+                dq=q.grad.clone(), dk=k.grad.clone(), dv=v.grad.clone(), dw=mod._w.grad.clone())
+
+
 def make_jagged(gr):
     """concat_2D_jagged / split_2D_jagged and add_timestamp_positional_embeddings of the reference's
     PyTorch implementations."""
@@ -395,7 +431,8 @@ def main():
         torch.save(attn, os.path.join(HERE, "attention.pt"))
     for name, fn in (("masks", lambda: make_masks(ref_ops)), ("stages", lambda: make_stages(gr)),
                      ("stu_layer", lambda: make_layer(gr)), ("delta_attention", lambda: make_delta(ref_ops)),
-                     ("rel_bias", make_bias), ("jagged", lambda: make_jagged(gr)),
+                     ("rel_bias", make_bias), ("rel_bias_attention", make_bias_attention),
+                     ("jagged", lambda: make_jagged(gr)),
                      ("stu_cached", lambda: make_cached_layer(gr))):
         if want(name):
             torch.save(fn(), os.path.join(HERE, name + ".pt"))

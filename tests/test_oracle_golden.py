@@ -116,6 +116,40 @@ def test_position_bias_matches_reference(golden):
     assert b[i, j] == fx["ts_w"][int(torch.log(torch.tensor(7.0)) / 0.301)]
 
 
+def _bias_attention_inputs(fx):
+    """q, k, v as [L, H, d] leaves and the per-distance bias the fixture's weights stand for:
+    the research module puts w[N - 1 - (i - j)] at (i, j) of its [N, N] bias for i >= j."""
+    N, H, A, V = fx["N"], fx["H"], fx["A"], fx["V"]
+    L = fx["q"].shape[0]
+    q = fx["q"].view(L, H, A).clone().requires_grad_(True)
+    k = fx["k"].view(L, H, A).clone().requires_grad_(True)
+    v = fx["v"].view(L, H, V).clone().requires_grad_(True)
+    bias = fx["w"][N - 1 - torch.arange(N)].clone().requires_grad_(True)
+    return q, k, v, bias
+
+
+def test_attention_with_learnable_bias_matches_reference(golden):
+    """The oracle's ``rel_bias`` path - output and the gradients of q, k, v and of the bias itself -
+    against the research model's attention with a ``RelativePositionalBias`` (fixture
+    rel_bias_attention.pt)."""
+    fx = golden("rel_bias_attention.pt")
+    N = fx["N"]
+    q, k, v, bias = _bias_attention_inputs(fx)
+    i = torch.arange(N)
+    rb = bias[(i.view(N, 1) - i.view(1, N)).abs()]
+    torch.testing.assert_close(torch.tril(rb), torch.tril(fx["rab"]))
+    out = O.hstu_mha(N, 1.0, q, k, v, fx["seq_offsets"], rel_bias=rb)
+    L = q.shape[0]
+    torch.testing.assert_close(out.reshape(L, -1), fx["out"], rtol=1e-5, atol=1e-6)
+    out.backward(fx["dout"].view_as(out))
+    torch.testing.assert_close(q.grad.reshape(L, -1), fx["dq"], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(k.grad.reshape(L, -1), fx["dk"], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(v.grad.reshape(L, -1), fx["dv"], rtol=1e-5, atol=1e-6)
+    # weights of negative distances (j > i) never reach a causal score
+    torch.testing.assert_close(bias.grad, fx["dw"][N - 1 - torch.arange(N)], rtol=1e-4, atol=1e-6)
+    assert fx["dw"][N:].abs().max() == 0
+
+
 def test_fp8_block_quant_roundtrip():
     g = torch.Generator().manual_seed(0)
     off = torch.tensor([0, 5, 5, 300, 431])

@@ -7,6 +7,7 @@ import torch
 
 import generative_recommenders_b200 as G
 from oracle import hstu_oracle as O
+import parity_metrics as PM
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -165,4 +166,6 @@ def test_bf16_stack_with_relative_bias_runs_and_matches_oracle():
     i = torch.arange(512).view(-1, 1); j = torch.arange(512).view(1, -1)
     rb = bias[(i - j).abs()]
     ref = O.stu_layer(x.float(), offs, 512, nt, params, 2, 128, 128, contextual_seq_len=6, rel_bias=rb)
-    assert O.rel_l2(y, ref) < 2e-2
+    params16 = {n: p.bfloat16() for n, p in params.items()}
+    ref16 = O.stu_layer(x, offs, 512, nt, params16, 2, 128, 128, contextual_seq_len=6, rel_bias=rb)
+    PM.check_vs_bf16_reference("bf16_layer_with_bias", y, ref, ref16.float())

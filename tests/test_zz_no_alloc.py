@@ -21,9 +21,9 @@ DEV = "cuda:0"
 TOL = 1e-2  # the bf16 tolerance of the attention tests
 
 
-def _args(q, k, v, out, offs, nt, N, alpha):
+def _args(q, k, v, out, offs, nt, N, alpha, bias=None):
     a = _cabi.AttnArgs()
-    _fill_common(a, q, k, v, offs, nt, None, N, alpha, 0, 0, 0, None)
+    _fill_common(a, q, k, v, offs, nt, None, N, alpha, 0, 0, 0, bias)
     a.impl = _cabi.IMPL_AUTO
     a.out = out.data_ptr()
     a.o_row_stride, a.o_head_stride = out.stride(0), out.stride(1)
@@ -67,6 +67,38 @@ def test_static_scratch_forward_matches_regular_forward_twice():
         # and both agree with the oracle
         oracle = O.hstu_mha(N, alpha, q.float().cpu(), k.float().cpu(), v.float().cpu(), offs.cpu().long(),
                             num_targets=nt.cpu().long())
+        assert O.rel_l2(out, oracle) < TOL
+
+
+def test_static_scratch_forward_with_relative_bias():
+    """With a relative bias the built-in array holds the signed-distance table in front of the work
+    list.  A call with a bias, then one without, then one with another bias, back to back: every
+    call rebuilds what it reads, so each must match the regular entry point bit for bit."""
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(5)
+    N, alpha = 520, 1.0 / 128
+    for seed, lengths, targets, with_bias in [(7, [300, 77, 513], [9, 3, 20], True), (8, [450, 129], [4, 0], False),
+                                              (9, [64, 520], [1, 30], True)]:
+        q, k, v, offs, nt = _case(seed, lengths, targets)
+        bias = (torch.randn(N, generator=g) * 0.3).to(DEV) if with_bias else None
+        ref_out = torch.empty_like(v)
+        a = _args(q, k, v, ref_out, offs, nt, N, alpha, bias)
+        n = lib.b200_hstu_attn_workspace_bytes(a, 0)
+        ws = torch.empty(max(int(n), 1), dtype=torch.uint8, device=DEV)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), n
+        _cabi.check(lib.b200_hstu_attn_fwd(a, stream), "b200_hstu_attn_fwd")
+        out = torch.full_like(v, float("nan"))
+        b = _args(q, k, v, out, offs, nt, N, alpha, bias)
+        _cabi.check(lib.b200_hstu_attn_fwd_static_scratch(b, stream), "b200_hstu_attn_fwd_static_scratch")
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref_out)
+        rb = None
+        if with_bias:
+            i = torch.arange(N)
+            rb = bias.cpu()[(i.view(N, 1) - i.view(1, N)).abs()]
+        oracle = O.hstu_mha(N, alpha, q.float().cpu(), k.float().cpu(), v.float().cpu(), offs.cpu().long(),
+                            num_targets=nt.cpu().long(), rel_bias=rb)
         assert O.rel_l2(out, oracle) < TOL
 
 
