@@ -120,20 +120,58 @@ def rank_shard(w, rank, world):
     return sub
 
 
+def pin_rank_to_cores(local_rank, world):
+    """Give every rank of a multi-GPU run its own share of the host cores (the step is a few
+    hundred microseconds long: a launching thread that migrates, or shares a core with another
+    rank's sampler thread, shows up as idle time on its GPU).  Returns the cores, or None."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        if world <= 1 or len(cores) < 2 * world:
+            return None
+        per = len(cores) // world
+        mine = cores[local_rank * per:(local_rank + 1) * per]
+        os.sched_setaffinity(0, mine)
+        torch.set_num_threads(max(1, min(per, 8)))
+        return mine
+    except Exception:
+        return None
+
+
+def dist_stats(x, _unused=None):
+    """min / max / mean over steps of a list of per-step milliseconds."""
+    s = sorted(x)
+    n = len(s)
+    return {"median": round(s[n // 2], 5), "min": round(s[0], 5), "p90": round(s[min(n - 1, (9 * n) // 10)], 5),
+            "mean": round(sum(s) / n, 5), "n": n}
+
+
+def capture_step(step, inputs, dev):
+    """One forward + backward of the public API captured into a CUDA graph; replaying it launches
+    the same kernels with no host work in between.  Returns (graph, outputs) or (None, None)."""
+    try:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step(*inputs)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            res = step(*inputs)
+        return graph, res
+    except Exception as ex:  # pragma: no cover - depends on the driver
+        sys.stderr.write("bench: CUDA graph capture of the step failed (%s); timing eager launches\n" % ex)
+        torch.cuda.synchronize()
+        return None, None
+
+
 def run_ours(args):
     import generative_recommenders_b200 as G
     from generative_recommenders_b200 import _cabi
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, local_rank, dev, dist = _dist_setup()
+    cores = pin_rank_to_cores(local_rank, world)
     w_all = make_workload(world, args.workload)
     w = rank_shard(w_all, rank, world)
     fwd_only = args.workload == "config3" or args.fwd_only
@@ -165,25 +203,51 @@ def run_ours(args):
         step(dq_, dk_, dv_, ddo)
     barrier()
 
-    # ---- device-resident timing: per-step CUDA events, L2 flushed (untimed) between steps
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # ---- device-resident timing.  A step is one forward + backward through the public API; it is
+    # captured once into a CUDA graph and replayed, so that the timed region holds the kernels and
+    # nothing of the host (eager launches of a 0.2 ms step are bound by the Python / autograd
+    # dispatch of the slowest rank; they are timed further down and reported next to this).
+    # Per-step CUDA events, L2 flushed (untimed) between steps; --steps K is repeated for as many
+    # rounds as it takes to fill half a second, every step of every round is timed.
+    graph = None
+    if not args.eager:
+        graph, _ = capture_step(step, (dq_.detach().clone(), dk_.detach().clone(), dv_.detach().clone(), ddo), dev)
+    run = graph.replay if graph is not None else (lambda: step(dq_, dk_, dv_, ddo))
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    run()
+    torch.cuda.synchronize()
+    est_ms = max(1e-3, (time.perf_counter() - t0) * 1e3)
+    rounds = int(max(1, min(400, -(-500.0 // (args.steps * est_ms)))))
+    if dist is not None:   # every rank times the same number of steps
+        r_ = torch.tensor([rounds], device=dev)
+        dist.all_reduce(r_, op=dist.ReduceOp.MAX)
+        rounds = int(r_.item())
+    n_timed = rounds * args.steps
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_timed)]
     launches0 = _cabi.launch_count()
     with ClockSampler(local_rank) as clocks:
         barrier()
         for s, e in ev:
             flush.zero_()
             s.record()
-            step(dq_, dk_, dv_, ddo)
+            run()
             e.record()
         barrier()
     launches = _cabi.launch_count() - launches0
-    ms_total = sum(s.elapsed_time(e) for s, e in ev)
+    step_ms = [s.elapsed_time(e) for s, e in ev]
+    ms_total = sum(step_ms)
+    launches_per_step = 2 if fwd_only else 4   # planning + forward (+ the two backward launches)
+    if graph is not None:
+        launches = launches_per_step * n_timed   # replayed launches are not seen by the library's counter
 
-    # ---- forward / backward separately, with the library's per-kernel event timing switched on
-    # (CUDA events recorded by the library around each kernel on the launch stream)
+    # ---- eager launches: forward / backward separately, with the library's per-kernel event timing
+    # switched on (CUDA events recorded by the library around each kernel on the launch stream)
     _cabi.profile_enable(True)
     fe = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-          for _ in range(min(args.steps, 50))]
+          for _ in range(max(20, min(args.steps, 100)))]
     for a, b, c in fe:
         flush.zero_()
         qd = dq_.detach().requires_grad_(not fwd_only); kd = dk_.detach().requires_grad_(not fwd_only)
@@ -201,11 +265,13 @@ def run_ours(args):
     torch.cuda.synchronize()
     fwd_ms = sorted(a.elapsed_time(b) for a, b, c in fe)[len(fe) // 2]
     bwd_ms = sorted(b.elapsed_time(c) for a, b, c in fe)[len(fe) // 2]
-    kernel_ms = {}
+    eager_ms = sorted(a.elapsed_time(c) for a, b, c in fe)[len(fe) // 2]
+    kernel_ms, kernel_stats = {}, {}
     for kind in ("plan", "attn_fwd", "attn_bwd_dkdv", "attn_bwd_dq"):
         vals = _cabi.profile_collect(kind)
         if vals:
             kernel_ms[kind] = sum(vals) / len(vals)
+            kernel_stats[kind] = dist_stats(vals, None)
     _cabi.profile_enable(False)
 
     # ---- end to end through the public API from pinned host memory.  Every step copies its inputs
@@ -267,6 +333,38 @@ def run_ours(args):
     h2d = sum(t.numel() for t in ((q, k, v) if fwd_only else (q, k, v, do))) * elem
     d2h = sum(t.numel() for t in res_host) * elem
 
+    # ---- validation across ranks: every rank hands the rows of one of its sequences (inputs and
+    # the output it computed) to rank 0, which runs those sequences again as one batch on its own GPU;
+    # a sequence's rows do not depend on what else is in the batch, so the bits must agree.  This
+    # gather is the only collective that touches data, and it is outside every timed region.
+    validated = None
+    with torch.no_grad():
+        mine_out = G.hstu_mha(N, alpha, dq_.detach(), dk_.detach(), dv_.detach(), offs, **kw)
+        pick = int(torch.argmax(w.lengths))    # this rank's longest sequence
+        lo_, hi_ = int(w.seq_offsets[pick]), int(w.seq_offsets[pick + 1])
+        pack = torch.zeros((4, N) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
+        for i_, t_ in enumerate((dq_, dk_, dv_, mine_out)):
+            pack[i_, :hi_ - lo_] = t_.detach()[lo_:hi_]
+        meta = torch.tensor([hi_ - lo_, 0 if w.num_targets is None else int(w.num_targets[pick])], dtype=torch.int64, device=dev)
+        if dist is not None:
+            packs = [torch.empty_like(pack) for _ in range(world)]
+            metas = [torch.empty_like(meta) for _ in range(world)]
+            dist.all_gather(packs, pack)
+            dist.all_gather(metas, meta)
+        else:
+            packs, metas = [pack], [meta]
+        if rank == 0:
+            lens = torch.stack(metas)[:, 0].cpu()
+            vo = torch.cat([lens.new_zeros(1), torch.cumsum(lens, 0)]).to(torch.int32).to(dev)
+            vnt = None if w.num_targets is None else torch.stack(metas)[:, 1].to(torch.int32).to(dev)
+            cat = [torch.cat([p_[i_, :int(n_)] for p_, n_ in zip(packs, lens)]) for i_ in range(4)]
+            again = G.hstu_mha(N, alpha, cat[0], cat[1], cat[2], vo, num_targets=vnt, max_attn_len=w.max_attn_len,
+                               contextual_seq_len=w.contextual_seq_len)
+            torch.cuda.synchronize()
+            validated = {"ok": bool(torch.equal(again, cat[3])), "sequences": int(world), "rows": int(lens.sum()),
+                         "how": "rows of one sequence per rank gathered%s and recomputed on rank 0: bit-identical" %
+                                (" over NCCL" if dist is not None else "")}
+
     # ---- reduce over ranks: time = max, work = sum
     # FLOP count: the reference bench's causal formula 4*H*d*sum(L^2)/2; with a local window that
     # formula counts pairs the mask removes (configs[3]: 4x too many), so such workloads count the
@@ -274,16 +372,25 @@ def run_ours(args):
     use_exact = w.max_attn_len > 0
     flops_fwd = 4.0 * w.num_heads * w.attn_dim * w.exact_pairs() if use_exact else w.causal_flops_fwd()
     mult = 1.0 if fwd_only else 3.5
-    stats = torch.tensor([ms_total, e2e_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
-    work = torch.tensor([flops_fwd, float(w.total_tokens), float(launches)], dtype=torch.float64, device=dev)
+    lsq = float((w.lengths.double() ** 2).sum())
+    mine = torch.tensor([ms_total / n_timed, e2e_ms, fwd_ms, bwd_ms, eager_ms, kernel_ms.get("plan", 0.0),
+                         kernel_ms.get("attn_fwd", 0.0), kernel_ms.get("attn_bwd_dkdv", 0.0),
+                         kernel_ms.get("attn_bwd_dq", 0.0), float(w.total_tokens), lsq, flops_fwd, float(launches)],
+                        dtype=torch.float64, device=dev)
     if dist is not None:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(work, op=dist.ReduceOp.SUM)
-    ms_total, e2e_ms, fwd_ms, bwd_ms = stats.tolist()
-    flops_fwd_all, tokens_all, launches_all = work.tolist()
-    ms_per_step = ms_total / args.steps
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        allr = torch.stack(allr).cpu()
+    else:
+        allr = mine.cpu().view(1, -1)
+    ms_per_step, e2e_ms, fwd_ms_max, bwd_ms_max = (float(allr[:, i_].max()) for i_ in range(4))
+    flops_fwd_all, tokens_all, launches_all = float(allr[:, 11].sum()), float(allr[:, 9].sum()), float(allr[:, 12].sum())
     value = mult * flops_fwd_all / (ms_per_step * 1e-3) / 1e12
     e2e_value = mult * flops_fwd_all / (e2e_ms * 1e-3) / 1e12
+    fields = ["step_ms", "e2e_ms", "fwd_ms_eager", "bwd_ms_eager", "step_ms_eager", "plan_kernel_ms", "fwd_kernel_ms",
+              "dkdv_kernel_ms", "dq_kernel_ms", "tokens", "sum_L2"]
+    ranks = {f_: {"min": round(float(allr[:, i_].min()), 5), "max": round(float(allr[:, i_].max()), 5),
+                  "argmax": int(allr[:, i_].argmax())} for i_, f_ in enumerate(fields)}
 
     peaks, peak_kind = load_peaks()
     # dominant kernel of the step and its roofline (rank 0's share of the work).  Algorithmic FLOPs
@@ -309,15 +416,39 @@ def run_ours(args):
             traffic = json.load(open(tpath)).get(dom_name, {}).get(w.name)
         except Exception:
             traffic = None
+    csum = clocks.summary()
+    mhz = csum.get("sm_mhz") or 0
+    per_kernel = {}
+    for k_ in algo:
+        if k_ in kernel_ms:
+            tf = algo[k_] * flops_fwd / (kernel_ms[k_] * 1e-3) / 1e12
+            per_kernel[k_] = {"ms": kernel_stats[k_], "algorithmic_tflops": round(tf, 1),
+                              "frac": round(tf / peaks["bf16_tflops"], 4),
+                              "frac_sustained": round(tf / peaks["bf16_tflops_sustained"], 4),
+                              "ms_x_mhz": round(kernel_stats[k_]["median"] * mhz, 2)}
+    if not fwd_only and "attn_bwd_dkdv" in kernel_ms and "attn_bwd_dq" in kernel_ms:
+        tb = 2.5 * flops_fwd / ((kernel_ms["attn_bwd_dkdv"] + kernel_ms["attn_bwd_dq"]) * 1e-3) / 1e12
+        per_kernel["backward_both_launches"] = {"algorithmic_tflops": round(tb, 1), "frac": round(tb / peaks["bf16_tflops"], 4),
+                                                "frac_sustained": round(tb / peaks["bf16_tflops_sustained"], 4)}
     roofline = {"kernel": dom_name, "bound": "tensor", "achieved": round(ach, 2), "peak": peaks["bf16_tflops"],
                 "unit": "TFLOP/s", "frac": round(ach / peaks["bf16_tflops"], 4), "traffic": traffic,
-                "peak_source": peak_kind + " (cuBLAS bf16 burst)", "launch_ms": round(dom_ms, 4),
-                "flops_per_launch": dom_flops,
+                "frac_sustained": round(ach / peaks["bf16_tflops_sustained"], 4),
+                "peak_source": peak_kind + " (cuBLAS bf16 burst; frac_sustained: the seconds-long loop under the power cap)",
+                "launch_ms": round(dom_ms, 4), "flops_per_launch": dom_flops,
                 "flops_model": ("F = 4*H*d*(visible (q,k) pairs)" if use_exact else "nominal causal F = 4*H*d*sum(L^2)/2") +
                                "; fwd F, bwd dK/dV kernel 2F, bwd dQ kernel 0.5F",
-                "kernel_ms": {k_: round(v_, 4) for k_, v_ in kernel_ms.items()}}
+                "kernel_ms": {k_: round(v_, 4) for k_, v_ in kernel_ms.items()}, "kernels": per_kernel}
 
-    out = None
+    # ---- further records on the same line: the other configurations and the stage kernels
+    blocks = {}
+    if args.blocks != "none" and args.workload == "config1" and not args.fwd_only:
+        del dev_in, res_host, flush, ev
+        torch.cuda.empty_cache()
+        if world == 1:
+            blocks["config3"] = block_config3(dev, peaks, args)
+            blocks["stages"] = block_stages(dev, peaks, args)
+        blocks["config4"] = block_config4(world, rank, dev, dist, args)
+
     if rank == 0:
         out = {
             "metric": "hstu_mha_%s_tflops%s" % ("fwd" if fwd_only else "fwd_bwd", "_exact_pairs" if use_exact else ""),
@@ -327,8 +458,14 @@ def run_ours(args):
             "config": {"workload": "configs[%s]: hstu_mha %s, B=%d seqs/GPU, H=%d, d=%d, N=%d, targets, bf16" % (
                 "3" if args.workload == "config3" else "1", "fwd" if fwd_only else "fwd+bwd", len(w.lengths), w.num_heads, w.attn_dim, N),
                 "global_batch": len(w_all.lengths), "tokens": int(tokens_all), "seq_len": N,
-                "parallelism": "sequence-sharded x%d, no collective" % world,
-                "l2": "256 MiB memset between timed steps (untimed)"},
+                "parallelism": "sequence-sharded x%d by token count, no collective" % world,
+                "l2": "256 MiB memset between timed steps (untimed)",
+                "launch": ("one CUDA graph per step (forward + backward of hstu_mha captured through the public API), replayed"
+                           if graph is not None else "eager launches through the public API"),
+                "timed_steps": "%d rounds x %d steps, every step timed with its own CUDA events" % (rounds, args.steps),
+                "host_cores_per_rank": None if cores is None else len(cores)},
+            "step_ms": dist_stats(step_ms, None),
+            "step_ms_eager": round(eager_ms, 5),
             "tokens_per_s": round(tokens_all / (ms_per_step * 1e-3), 1),
             "fwd_tflops": round(flops_fwd / (fwd_ms * 1e-3) / 1e12, 2),
             "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
@@ -337,18 +474,46 @@ def run_ours(args):
             "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 4)},
             "gpu_launches": int(launches_all),
-            "clocks": clocks.summary(),
+            "clocks": csum,
             "roofline": roofline,
+            "ranks": ranks,
+            "validated": validated,
         }
+        out.update(blocks)
         if world == 1:
             out["cpu_baseline"] = cpu_baseline(w, fwd_only)
         print(json.dumps(out), flush=True)
     if dist is not None:
+        dist.barrier()
         dist.destroy_process_group()
 
 
-def cpu_oracle_step(w, idx, fwd_only):
-    """One pass of the CPU oracle over the sequences ``idx`` of workload ``w``; returns
+def reference_attention():
+    """``pytorch_hstu_mha`` of the unmodified reference when its file has been placed under
+    ``oracle/_ref`` (``python oracle/make_ref.py``, done by ``__graft_entry__.build()`` wherever a
+    checkout of the reference is present), else None.  The two fbgemm data-movement ops it calls come
+    from ``oracle/reference_shims.py``."""
+    import importlib.util
+
+    path = os.path.join(ROOT, "oracle", "_ref", "pt_hstu_attention.py")
+    if not os.path.exists(path):
+        return None
+    try:
+        from oracle import reference_shims
+
+        reference_shims.install()
+        spec = importlib.util.spec_from_file_location("_ref_pt_hstu_attention", path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod.pytorch_hstu_mha
+    except Exception as ex:  # pragma: no cover
+        sys.stderr.write("bench: could not load oracle/_ref (%s); timing the oracle port instead\n" % ex)
+        return None
+
+
+def cpu_step(w, idx, fwd_only, ref_fn):
+    """One pass of the CPU implementation over the sequences ``idx`` of workload ``w`` - the
+    reference's own ``pytorch_hstu_mha`` when ``ref_fn`` is given, else the oracle port; returns
     (seconds, nominal forward FLOPs of those sequences)."""
     from generative_recommenders_b200 import workloads as W
     from oracle import hstu_oracle as O
@@ -358,73 +523,88 @@ def cpu_oracle_step(w, idx, fwd_only):
     q, k, v, do = (t.float() for t in (q, k, v, do))
     if not fwd_only:
         q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    fn = ref_fn if ref_fn is not None else O.hstu_mha
     t0 = time.perf_counter()
-    out = O.hstu_mha(sub.max_seq_len, sub.alpha, q, k, v, sub.seq_offsets, num_targets=sub.num_targets,
-                     max_attn_len=sub.max_attn_len, contextual_seq_len=sub.contextual_seq_len)
+    out = fn(sub.max_seq_len, sub.alpha, q, k, v, sub.seq_offsets, num_targets=sub.num_targets,
+             max_attn_len=sub.max_attn_len, contextual_seq_len=sub.contextual_seq_len)
     if not fwd_only:
         out.backward(do)
     dt = time.perf_counter() - t0
     return dt, sub.causal_flops_fwd()
 
 
-def cpu_sample(w, budget_pairs=4.0e7):
-    """The bounded sample the CPU legs run: the first sequences of the workload whose (q, k) pair
-    count stays within ``budget_pairs`` (all 64 sequences of configs[1]; a handful of configs[3])."""
+def cpu_sample(w, padded, budget=4.0e7):
+    """The bounded sample the CPU legs run: the first sequences of the workload.  The oracle port
+    walks the sequences (work ~ L^2 / 2 pairs per sequence and head): as many as keep the pair count
+    within ``budget`` - all 64 sequences of configs[1], a handful of configs[3].  The reference
+    pads every sequence to max_seq_len (work and memory ~ H * N^2 per sequence whatever its length):
+    as many as keep one [n, H, N, N] fp32 tensor within ``budget`` elements, at least one."""
+    if padded:
+        n = int(budget // (w.num_heads * float(w.max_seq_len) ** 2))
+        return list(range(max(1, min(n, len(w.lengths)))))
     idx, pairs = [], 0.0
     for i, L in enumerate(w.lengths.tolist()):
         L = min(int(L), w.max_seq_len)
-        if idx and pairs + 0.5 * L * L > budget_pairs:
+        if idx and pairs + 0.5 * L * L > budget:
             break
         idx.append(i)
         pairs += 0.5 * L * L
     return idx
 
 
-def cpu_baseline(w, fwd_only, seconds=8.0, max_passes=200):
-    """The oracle port on the host cores: passes over the bounded sample until ``seconds`` of CPU
-    work have been timed."""
+def _use_all_host_threads():
+    # torchrun pins OMP_NUM_THREADS=1; the CPU legs may use every host core this process may run on
     try:
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     except Exception:
-        pass
-    idx = cpu_sample(w)
-    cpu_oracle_step(w, idx[:2], fwd_only)  # warm-up
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+
+
+def cpu_baseline(w, fwd_only, seconds=8.0, max_passes=200):
+    """The reference's CPU implementation of the path on the host cores (the unmodified
+    ``pytorch_hstu_mha`` when ``oracle/_ref`` is there, else the oracle port): passes over the
+    bounded sample until ``seconds`` of CPU work have been timed."""
+    _use_all_host_threads()
+    ref_fn = reference_attention()
+    idx = cpu_sample(w, ref_fn is not None)
+    cpu_step(w, idx[:1], fwd_only, ref_fn)  # warm-up
     tot_t = tot_f = 0.0
     passes = 0
     while passes < max_passes and tot_t < seconds:
-        dt, f = cpu_oracle_step(w, idx, fwd_only)
+        dt, f = cpu_step(w, idx, fwd_only, ref_fn)
         tot_t += dt
         tot_f += f
         passes += 1
     mult = 1.0 if fwd_only else 3.5
     return {"value": round(mult * tot_f / tot_t / 1e12, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-            "kind": "port",
-            "sample": "first %d sequences of the workload, fp32 oracle, %d passes, %.1f s" % (len(idx), passes, tot_t)}
+            "kind": "reference" if ref_fn is not None else "port",
+            "sample": "first %d sequences of the workload, fp32, %s, %d passes, %.1f s" % (
+                len(idx), "unmodified pytorch_hstu_mha (pads to [n, H, N, N])" if ref_fn is not None
+                else "oracle port (walks the sequences: faster than the reference's padded form)", passes, tot_t)}
 
 
 def run_reference(args):
-    """The reference's own CPU implementation of the path, as restated by the oracle (the
-    reference checkout itself does not travel to the GPU box), with all host threads."""
+    """The reference's own CPU implementation of the path with all host threads: the unmodified
+    ``pytorch_hstu_mha`` when ``oracle/_ref`` holds its file, else its restatement in ``oracle/``.
+    The same sequences and the same number of steps whatever the number of GPUs asked for (rank 0
+    alone runs; the other ranks leave at once)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # torchrun pins OMP_NUM_THREADS=1; the CPU arm may use every host core
-    try:
-        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
-    except Exception:
-        torch.set_num_threads(max(1, os.cpu_count() or 1))
-    w = make_workload(world, args.workload)
+    _use_all_host_threads()
+    w = make_workload(1, args.workload)
     fwd_only = args.workload == "config3" or args.fwd_only
-    idx = cpu_sample(w)
+    ref_fn = reference_attention()
+    idx = cpu_sample(w, ref_fn is not None)
     n = len(idx)
-    for _ in range(min(args.warmup, 2)):
-        cpu_oracle_step(w, idx[:2], fwd_only)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_step(w, idx[:1], fwd_only, ref_fn)
     steps = max(1, min(args.steps, 100))
     tot_t = tot_f = 0.0
     done = 0
     for _ in range(steps):
-        dt, f = cpu_oracle_step(w, idx, fwd_only)
+        dt, f = cpu_step(w, idx, fwd_only, ref_fn)
         tot_t += dt
         tot_f += f
         done += 1
@@ -433,14 +613,16 @@ def run_reference(args):
     steps = done
     mult = 1.0 if fwd_only else 3.5
     val = mult * tot_f / tot_t / 1e12
+    kind = "reference" if ref_fn is not None else "port"
+    what = "unmodified pytorch_hstu_mha" if ref_fn is not None else "oracle port"
     line = {
         "impl": "reference", "metric": "hstu_mha_%s_tflops" % ("fwd" if fwd_only else "fwd_bwd"),
-        "value": round(val, 5), "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 2),
+        "value": round(val, 5), "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": max(1, min(args.warmup, 2)),
         "ms_per_step": round(tot_t / steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[%s]: hstu_mha, CPU PyTorch path (oracle port), first %d sequences per step" % (
-            "3" if fwd_only else "1", n)},
-        "cpu_baseline": {"value": round(val, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+        "config": {"workload": "configs[%s]: hstu_mha, CPU PyTorch path (%s), first %d sequences per step" % (
+            "3" if fwd_only else "1", what, n)},
+        "cpu_baseline": {"value": round(val, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
                          "sample": "first %d sequences per step" % n},
         "e2e": {"value": round(val, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -448,7 +630,13 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+_DIST = {}
+
+
 def _dist_setup():
+    """(world, rank, local_rank, device, torch.distributed or None); initialises NCCL once."""
+    if _DIST:
+        return _DIST["v"]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -459,7 +647,132 @@ def _dist_setup():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
-    return world, rank, local_rank, dev, dist
+    _DIST["v"] = (world, rank, local_rank, dev, dist)
+    return _DIST["v"]
+
+
+def _median_ms(fn, steps, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s_, e_ in ev:
+        s_.record()
+        fn()
+        e_.record()
+    torch.cuda.synchronize()
+    return sorted(s_.elapsed_time(e_) for s_, e_ in ev)[steps // 2]
+
+
+def block_config3(dev, peaks, args):
+    """configs[3] on one GPU: the inference forward in bf16 and with e4m3 q / k / v on the same
+    tensors (151 MB per bf16 tensor: larger than L2), TFLOP/s over the visible (q, k) pairs."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi, workloads as W
+
+    w = W.config3(256)
+    q, k, v = w.qkv(device=dev)
+    offs = w.seq_offsets.to(torch.int32).to(dev)
+    nt = w.num_targets.to(torch.int32).to(dev)
+    kw = dict(num_targets=nt, max_attn_len=w.max_attn_len)
+    q8, qs, bo = G.quantize_e4m3_block(q, offs)
+    k8, ks, _ = G.quantize_e4m3_block(k, offs)
+    v8, vs, _ = G.quantize_e4m3_block(v, offs)
+    exact = 4.0 * w.num_heads * w.attn_dim * w.exact_pairs()
+    res = {"workload": "configs[3]: inference forward, B=256, N=8192, H=4, d=128, window 1024, 256 targets",
+           "tokens": w.total_tokens, "flops_model": "4*H*d*(visible (q,k) pairs)"}
+    with torch.no_grad():
+        _cabi.profile_enable(True)
+        ms16 = _median_ms(lambda: G.hstu_mha(w.max_seq_len, w.alpha, q, k, v, offs, **kw), 15)
+        ms8 = _median_ms(lambda: G.hstu_mha_fp8(w.max_seq_len, w.alpha, q8, k8, v8, qs, ks, vs, bo, offs, **kw), 15)
+        k16, k8_ = _cabi.profile_collect("attn_fwd"), _cabi.profile_collect("attn_fwd_fp8")
+        _cabi.profile_enable(False)
+        o16 = G.hstu_mha(w.max_seq_len, w.alpha, q, k, v, offs, **kw)
+        o8 = G.hstu_mha_fp8(w.max_seq_len, w.alpha, q8, k8, v8, qs, ks, vs, bo, offs, **kw)
+        err = float((o8.float() - o16.float()).norm() / o16.float().norm())
+    for name, ms, kk, peak in (("bf16", ms16, k16, peaks["bf16_tflops"]), ("fp8", ms8, k8_, 2.0 * peaks["bf16_tflops"])):
+        kms = sorted(kk)[len(kk) // 2] if kk else ms
+        tf = exact / (kms * 1e-3) / 1e12
+        res[name] = {"ms": round(ms, 4), "kernel_ms": round(kms, 4), "tflops_exact_pairs": round(tf, 1),
+                     "frac": round(tf / peak, 4), "tokens_per_s": round(w.total_tokens / (ms * 1e-3), 1)}
+    res["bf16"]["peak"] = "measured cuBLAS bf16 burst"
+    res["fp8"]["peak"] = "2 x the measured bf16 burst (no fp8 GEMM was measured on this pool)"
+    res["fp8"]["rel_l2_vs_bf16_kernel"] = round(err, 5)
+    return res
+
+
+def block_stages(dev, peaks, args):
+    """Achieved HBM GB/s of the memory-bound stage kernels and TFLOP/s of the fused uvqk stage."""
+    res = stage_kernels(dev, peaks, 10)
+    out = {"workload": res.pop("_workload"), "hbm_peak_gb_per_s": peaks["hbm_gbs"]}
+    for name, r in res.items():
+        if name == "uvqk_stage":
+            out[name] = {"fused_ms": r["fused"]["ms"], "separate_ms": r["separate"]["ms"],
+                         "kernel_tflops": r["fused"]["kernel_tflops"],
+                         "frac_of_bf16_peak": r["fused"]["kernel_frac_of_bf16_peak"], "shape": r["shape"]}
+        else:
+            out[name] = {"gb_per_s": r["gb_per_s"], "frac": r["frac_of_hbm_peak"], "ms": r["ms"]}
+    return out
+
+
+def block_config4(world, rank, dev, dist, args):
+    """configs[4]: the fixed batch of 2048 sequences through the 4-layer stack (D = 1024, H = 8,
+    d = 128, inference forward), split over the ranks at sequence granularity - once by token count
+    (the split the configuration names) and once by estimated cost (linear stages + attention) -
+    with no collective on the data path: strong scaling, tokens/s = all tokens / slowest rank."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import sharding, workloads as W
+
+    w_all = W.config4(args.batch or 2048)
+    D, layers, H, d = 1024, 4, 8, 128
+    cfg = G.STULayerConfig(embedding_dim=D, num_heads=H, hidden_dim=d, attention_dim=d, output_dropout_ratio=0.0,
+                           contextual_seq_len=16)
+    torch.manual_seed(20264)
+    stack = G.STUStack([G.STULayer(cfg) for _ in range(layers)]).to(dev).to(torch.bfloat16)
+    stack.train(False)
+    # cost of a sequence of length L in units of one token of the linear stages; the attention runs
+    # at about half the GEMMs' efficiency
+    per_token = 2.0 * D * 4 * H * d + 2.0 * 3 * H * d * D
+    cq = 2.0 * (4.0 * H * d / 2.0) / per_token
+    splits = [("by_tokens", 0.0)] + ([("by_cost", cq)] if world > 1 else [])
+    res = {"workload": "configs[4]: 4-layer HSTU stack inference forward, D=1024, H=8, d=128, B=%d, N=16384, "
+                       "64 targets, contextual 16, bf16" % len(w_all.lengths),
+           "tokens": w_all.total_tokens, "scaling": "strong", "parallelism": "sequence-sharded x%d, no collective" % world}
+    for name, c in splits:
+        bins = sharding.partition_by_tokens(w_all.lengths.tolist(), world, c)
+        w = W.subset(w_all, bins[rank]) if world > 1 else w_all
+        g = torch.Generator(device=dev).manual_seed(w_all.seed + 7 + rank)
+        x = torch.randn(w.total_tokens, D, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        lengths = w.lengths.to(dev)
+        offs = w.seq_offsets.to(torch.int32).to(dev)
+        nt = w.num_targets.to(torch.int32).to(dev)
+        with torch.no_grad():
+            fn = lambda: stack(x, lengths, offs, w.max_seq_len, nt)  # noqa: E731
+            fn()
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+            ms = _median_ms(fn, 3, warm=0)
+        lsq = float((w.lengths.double() ** 2).sum())
+        mine = torch.tensor([ms, float(w.total_tokens), lsq], dtype=torch.float64, device=dev)
+        if dist is not None:
+            allr = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(allr, mine)
+            allr = torch.stack(allr).cpu()
+        else:
+            allr = mine.cpu().view(1, -1)
+        slow = float(allr[:, 0].max())
+        res[name] = {"tokens_per_s": round(w_all.total_tokens / (slow * 1e-3), 1), "ms": round(slow, 3),
+                     "rank_ms": {"min": round(float(allr[:, 0].min()), 3), "max": round(slow, 3),
+                                 "argmax": int(allr[:, 0].argmax())},
+                     "rank_tokens": {"min": int(allr[:, 1].min()), "max": int(allr[:, 1].max())},
+                     "rank_sum_L2": {"min": float(allr[:, 2].min()), "max": float(allr[:, 2].max())}}
+        del x
+        torch.cuda.empty_cache()
+    best = max((k_ for k_ in ("by_tokens", "by_cost") if k_ in res), key=lambda k_: res[k_]["tokens_per_s"])
+    res["tokens_per_s"] = res[best]["tokens_per_s"]
+    res["best_split"] = best
+    return res
 
 
 def run_stack(args):
@@ -755,13 +1068,12 @@ def run_layer_norm(args):
     print(json.dumps(out), flush=True)
 
 
-def run_stages(args):
+def stage_kernels(dev, peaks, steps):
     """Achieved HBM GB/s of the memory-bound stage kernels (bf16, D = H*dv = 512, rows = tokens of
     configs[4]'s first 400 sequences), from the library's per-kernel events."""
     import generative_recommenders_b200 as G
     from generative_recommenders_b200 import _cabi, workloads as W
 
-    world, rank, local_rank, dev, dist = _dist_setup()
     rows = int(W.config4(400).total_tokens)
     D = 512
     g = torch.Generator().manual_seed(5)
@@ -770,14 +1082,13 @@ def run_stages(args):
     w_, b_ = mk(D), mk(D)
     uvqk = mk(rows, 4 * D)
     attn, u, dcat = mk(rows, D), mk(rows, D), mk(rows, 3 * D)
-    peaks, peak_kind = load_peaks()
 
     def timed(kind, fn, nbytes):
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
         _cabi.profile_enable(True)
-        for _ in range(max(5, min(args.steps, 30))):
+        for _ in range(max(5, min(steps, 30))):
             fn()
         torch.cuda.synchronize()
         v = _cabi.profile_collect(kind)
@@ -832,9 +1143,19 @@ def run_stages(args):
     res["add_timestamp_positional_embeddings_bwd"] = timed(
         "ts_pos", lambda: torch.autograd.grad(ye, (xe, pw, tw), dy, retain_graph=True), rows * D * 2 * 2)
     res["uvqk_stage"] = _uvqk_stage(dev, peaks, 20)
+    res["_workload"] = "stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2)" % (rows, rows * D * 2 / 1e6)
+    return res
+
+
+def run_stages(args):
+    """``--workload stages``: the stage kernels alone."""
+    world, rank, local_rank, dev, dist = _dist_setup()
+    peaks, peak_kind = load_peaks()
+    res = stage_kernels(dev, peaks, args.steps)
+    workload = res.pop("_workload")
     out = {"metric": "hstu_stage_hbm_gb_per_s", "value": res["norm_mul_fwd"]["gb_per_s"], "unit": "GB/s", "n_gpus": 1,
            "steps": args.steps, "warmup": 3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-           "config": {"workload": "stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2)" % (rows, rows * D * 2 / 1e6)},
+           "config": {"workload": workload},
            "hbm_peak_gb_per_s": peaks["hbm_gbs"], "peak_source": peak_kind + " (copy)", "stages": res}
     print(json.dumps(out), flush=True)
 
@@ -850,6 +1171,9 @@ def main():
     ap.add_argument("--graph", action="store_true", help="config2_stack: replay the step from a CUDA graph")
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (stack workloads)")
     ap.add_argument("--fwd-only", action="store_true", help="time the forward alone (inference)")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of replaying a CUDA graph of the step")
+    ap.add_argument("--blocks", default="all", choices=["all", "none"],
+                    help="none: leave out the configs[3] / stage-kernel / configs[4] records (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -305,7 +305,7 @@ int b200_hstu_profile_collect(int kind, float *out_ms, int max_n) {
 }
 
 const char *b200_hstu_last_error(void) { return g_err; }
-int b200_hstu_version(void) { return 100; }
+int b200_hstu_version(void) { return 101; }
 int64_t b200_hstu_launch_count(void) { return (int64_t)g_launches.load(); }
 
 /* Host utility for tooling and tests: the kv range a query tile visits (the block-skipping

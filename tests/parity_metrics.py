@@ -13,8 +13,8 @@ from oracle import hstu_oracle as O
 
 # half-precision kernels against the fp32 oracle on the same (already rounded) inputs
 HALF_TOL = 1e-2        # global relative L2
-HALF_SEQ_TOL = 2e-2    # worst single sequence (a one-token sequence has one score: nothing averages out)
-HALF_MAX_TOL = 2e-2    # max |error| / max |reference|
+HALF_SEQ_TOL = 1e-2    # worst single sequence (measured: 5e-3 on a one-token sequence)
+HALF_MAX_TOL = 1e-2    # max |error| / max |reference| (measured: 6e-3)
 # fp32 kernels against fp32 fixtures: accumulation order only
 F32_TOL = 2e-4
 F32_SEQ_TOL = 5e-4

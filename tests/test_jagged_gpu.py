@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from oracle import hstu_oracle as O
-import parity_metrics as P
+import parity_metrics as PM
 
 pytestmark = pytest.mark.gpu
 
@@ -186,8 +186,8 @@ def test_cached_forward_bf16_matches_full_forward():
             h = O.stu_layer(h, offs.cpu(), N, nt.cpu(), prm, H, A, V, contextual_seq_len=ctx)
         return O.split_2D_jagged(h, None, delta, prime_offsets.cpu(), None)[1].float()
     ref32, ref16 = oracle_tail(torch.float32), oracle_tail(torch.bfloat16)
-    P.check_vs_bf16_reference("cached_bf16_full_route", full_tail, ref32, ref16)
-    P.check_vs_bf16_reference("cached_bf16_delta_route", delta_y, ref32, ref16)
+    PM.check_vs_bf16_reference("cached_bf16_full_route", full_tail, ref32, ref16)
+    PM.check_vs_bf16_reference("cached_bf16_delta_route", delta_y, ref32, ref16)
 
 
 def test_full_size_round_trips():

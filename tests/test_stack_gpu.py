@@ -72,22 +72,34 @@ def _config2_reduced_batch():
     return lengths_all[pick], nt_all[pick]
 
 
-def _run_stack_case(name, layers, lengths, nt, use_checkpoint):
+# The gradient of a bias table is a sum over all (query, key) pairs of all heads and sequences, with
+# heavy cancellation (sum of |terms| / |sum of terms| is 13 on the 2000-token case measured for
+# this test), so it amplifies the ~3e-3 rounding noise of the 16-bit attention output that reaches
+# it through the output LayerNorm's backward: for fixed inputs the kernel's bias gradient is within
+# 2e-4 of the oracle (test_relative_bias_backward_and_bias_gradient), inside a 16-bit stack it is
+# 0.9e-2 .. 2.7e-2 away, the oracle run in bf16 0.7e-2 .. 1.3e-2.  Two 16-bit evaluation orders of
+# such a sum differ by more than the 1.25 allowed elsewhere; the fp32 run of the same case pins the
+# logic tightly.
+TABLE_SLACK = 2.5
+
+
+def _run_stack_case(name, layers, lengths, nt, use_checkpoint, dtype=torch.bfloat16):
     torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
     D, H, d, N, ctx, nb = 512, 4, 128, 4096, 6, 128
     offs = W._offsets(lengths)
     L = int(offs[-1])
     cfg = G.STULayerConfig(embedding_dim=D, num_heads=H, hidden_dim=d, attention_dim=d, output_dropout_ratio=0.0,
                            contextual_seq_len=ctx, rel_bias_buckets=nb)
     torch.manual_seed(20262)
-    stack = G.STUStack([G.STULayer(cfg) for _ in range(layers)]).to(DEV).to(torch.bfloat16)
+    stack = G.STUStack([G.STULayer(cfg) for _ in range(layers)]).to(DEV).to(dtype)
     _perturb_vectors(stack, 1)
     with torch.no_grad():
         for layer in stack._stu_layers:
             layer._rel_bias_table.mul_(10.0)   # std 0.2: a bias that matters next to q.k / sqrt(d)
     g = torch.Generator().manual_seed(7)
-    x = torch.randn(L, D, generator=g).bfloat16()
-    dy = torch.randn(L, D, generator=g).bfloat16()
+    x = torch.randn(L, D, generator=g).to(dtype)
+    dy = torch.randn(L, D, generator=g).to(dtype)
 
     xin = x.to(DEV).requires_grad_(True)
     n0 = G._cabi.launch_count()
@@ -101,6 +113,16 @@ def _run_stack_case(name, layers, lengths, nt, use_checkpoint):
     x32 = x.float().requires_grad_(True)
     ref = oracle_stack(x32, offs, N, nt, p32, H, d, ctx, bias_buckets=nb, use_checkpoint=use_checkpoint)
     ref.backward(dy.float())
+    if dtype == torch.float32:
+        # fp32 kernels (CUDA-core attention, LayerNorm / SiLU kernels, fp32 library GEMMs): the
+        # composite logic at accumulation-order tolerance
+        tol = dict(tol=2e-3, seq_tol=2e-3, max_tol=2e-3)
+        P.check((name, "fp32", "y"), y, ref.detach(), offs, **tol)
+        P.check((name, "fp32", "dx"), xin.grad, x32.grad, offs, **tol)
+        for li, layer in enumerate(stack._stu_layers):
+            for n, p_ in layer.named_parameters():
+                P.check((name, "fp32", li, n), p_.grad, p32[li][n[1:]].grad, None, **tol)
+        return
     # the reference's own arithmetic in bf16: the same oracle code on 16-bit tensors, run on the
     # device (bf16 matrix products are slow on host cores without bf16 units)
     p16 = _layer_params(stack, torch.bfloat16, DEV)
@@ -113,24 +135,28 @@ def _run_stack_case(name, layers, lengths, nt, use_checkpoint):
     for li, layer in enumerate(stack._stu_layers):
         for n, p_ in layer.named_parameters():
             assert p_.grad is not None, (li, n)
-            P.check_vs_bf16_reference((name, li, n), p_.grad, p32[li][n[1:]].grad, p16[li][n[1:]].grad)
+            P.check_vs_bf16_reference((name, li, n), p_.grad, p32[li][n[1:]].grad, p16[li][n[1:]].grad,
+                                      slack=TABLE_SLACK if n == "_rel_bias_table" else 1.25)
 
 
-def test_config2_stack_forward_backward_all_parameter_gradients():
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_config2_stack_forward_backward_all_parameter_gradients(dtype):
     """configs[2] at full depth and width (8 layers, D = 512, H = 4, d = 128, 128-bucket learned
     relative bias, contextual prefix 6, targets, max_seq_len 4096), bf16, on a reduced batch of its
     seeded sequences: y, dx and the gradient of every parameter of every layer - the bias tables
-    included - against autograd through the composite oracle."""
+    included - against autograd through the composite oracle.  The fp32 run of the same stack (the
+    CUDA-core attention kernels) checks the composition at 2e-3."""
     lengths, nt = _config2_reduced_batch()
-    _run_stack_case("config2_stack", 8, lengths, nt, use_checkpoint=False)
+    _run_stack_case("config2_stack", 8, lengths, nt, use_checkpoint=False, dtype=dtype)
 
 
-def test_config2_layers_with_a_4096_token_sequence():
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_config2_layers_with_a_4096_token_sequence(dtype):
     """The same layer configuration on a sequence at the length distribution's upper clip (4096
     tokens = max_seq_len: 32 tiles, the long-sequence kernel variants) next to a mid-sized and a
     minimal one; two layers keep the CPU oracle at some ten seconds."""
     _run_stack_case("config2_4096", 2, torch.tensor([4096, 300, 16]), torch.tensor([64, 20, 9]),
-                    use_checkpoint=False)
+                    use_checkpoint=False, dtype=dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
