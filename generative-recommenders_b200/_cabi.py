@@ -20,6 +20,8 @@ EXPORTS = [
     "b200_hstu_attn_workspace_bytes",
     "b200_hstu_attn_fwd_static_scratch",
     "b200_hstu_attn_fwd_static_scratch_max_bytes",
+    "b200_hstu_attn_status_async",
+    "b200_hstu_selftest_bounded_wait",
     "b200_hstu_attn_fwd_fp8",
     "b200_hstu_quantize_e4m3_block",
     "b200_hstu_layer_norm_fwd",
@@ -95,6 +97,8 @@ class NormMulArgs(Structure):
         ("concat_u", c_int32), ("concat_x", c_int32), ("act", c_int32), ("group_norm", c_int32),
         ("eps", c_float),
         ("dtype", c_int32),
+        ("dropout_ratio", c_float), ("reserved0", c_int32),
+        ("dropout_seed", c_void_p),
     ]
 
 
@@ -163,6 +167,10 @@ def lib():
     L.b200_hstu_attn_fwd_static_scratch.restype = ctypes.c_int
     L.b200_hstu_attn_fwd_static_scratch_max_bytes.argtypes = []
     L.b200_hstu_attn_fwd_static_scratch_max_bytes.restype = c_int64
+    L.b200_hstu_attn_status_async.argtypes = [POINTER(AttnArgs), ctypes.c_int, POINTER(c_int32), c_void_p]
+    L.b200_hstu_attn_status_async.restype = ctypes.c_int
+    L.b200_hstu_selftest_bounded_wait.argtypes = [c_void_p, c_void_p, c_void_p]
+    L.b200_hstu_selftest_bounded_wait.restype = ctypes.c_int
     L.b200_hstu_attn_workspace_bytes.argtypes = [POINTER(AttnArgs), ctypes.c_int]
     L.b200_hstu_attn_workspace_bytes.restype = c_int64
     L.b200_hstu_attn_fwd_fp8.argtypes = [POINTER(AttnFp8Args), c_void_p]

@@ -65,10 +65,11 @@ struct WaitCtx {
   int *status;               // global: first failing site is recorded here (0 = ok)
 };
 
-// The spinning part is one out-of-line function: inlined at every wait it added ~10 KB to
-// kernels that are about as large as the instruction cache (110-135 KB).
-static __device__ __noinline__ bool mbar_wait_slow(volatile int *abort_flag, int *status, uint32_t bar, uint32_t parity,
-                                            int site) {
+// The spinning part.  LIMIT_NS is a template argument so that the self-test kernel
+// (selftest.cu) can run the very same loop with a millisecond limit.
+template <uint64_t LIMIT_NS>
+__device__ __forceinline__ bool mbar_wait_loop(volatile int *abort_flag, int *status, uint32_t bar, uint32_t parity,
+                                               int site) {
   const WaitCtx ctx{abort_flag, status};
   uint64_t t0 = 0;
   uint32_t spins = 0;
@@ -78,13 +79,20 @@ static __device__ __noinline__ bool mbar_wait_slow(volatile int *abort_flag, int
       if (*ctx.abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > WAIT_LIMIT_NS) {
+      if (now - t0 > LIMIT_NS) {
         *ctx.abort_flag = 1;
         if (ctx.status) atomicCAS(ctx.status, 0, site);
         return false;
       }
     }
   }
+}
+
+// In the kernels it is one out-of-line function: inlined at every wait it added ~10 KB to
+// kernels that are about as large as the instruction cache (110-135 KB).
+static __device__ __noinline__ bool mbar_wait_slow(volatile int *abort_flag, int *status, uint32_t bar, uint32_t parity,
+                                            int site) {
+  return mbar_wait_loop<WAIT_LIMIT_NS>(abort_flag, status, bar, parity, site);
 }
 
 __device__ __forceinline__ bool mbar_wait(const WaitCtx &ctx, uint32_t bar, uint32_t parity, int site) {

@@ -524,14 +524,91 @@ struct NormMulParams {
   int H, V, concat_u, concat_x, act, group_norm;
   float eps;
   bool vec_ok;
+  // dropout over the whole (concatenated) output row, generated in the kernel
+  const unsigned long long *drop_seed;  // device; NULL = no dropout
+  uint32_t drop_thr;                    // an element is dropped when its 16 random bits are below this
+  float drop_scale;                     // 65536 / (65536 - drop_thr)
+};
+
+// ---------------------------------------------------------------------------------------
+// Dropout mask: counter-based, so that the backward regenerates the forward's mask from the seed
+// instead of reading it from memory.  Element idx of the [rows, width] output matrix takes the
+// (idx % 8)-th 16-bit piece of Philox4x32-10(key = seed, counter = idx / 8): one generator call
+// serves the eight 16-bit elements of a 16-byte vector, and the mask does not depend on the
+// element type or on how rows are spread over threads.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void philox4x32_10(uint32_t k0, uint32_t k1, uint32_t c0, uint32_t c1, uint32_t (&o)[4]) {
+  uint32_t c2 = 0, c3 = 0;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  o[0] = c0; o[1] = c1; o[2] = c2; o[3] = c3;
+}
+
+struct Dropout {
+  uint32_t k0, k1, thr;
+  float scale;
+  __device__ __forceinline__ void init(const NormMulParams &p) {
+    const unsigned long long s = *p.drop_seed;
+    k0 = (uint32_t)s;
+    k1 = (uint32_t)(s >> 32);
+    thr = p.drop_thr;
+    scale = p.drop_scale;
+  }
+  __device__ __forceinline__ float one(float v, uint64_t idx) const {
+    uint32_t o[4];
+    const uint64_t g = idx >> 3;
+    philox4x32_10(k0, k1, (uint32_t)g, (uint32_t)(g >> 32), o);
+    const int j = (int)(idx & 7);
+    const uint32_t r = (o[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+    return r >= thr ? v * scale : 0.f;
+  }
+  // the D elements of one part of a row, whose first element has index `base` in the output matrix
+  template <typename E, int MAXV>
+  __device__ __forceinline__ void apply(Row<E, MAXV> &r, uint64_t base, int D, int lane) const {
+    constexpr int EV = VecInfo<E>::EV;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int e0 = (k * 32 + lane) * EV;
+      if (e0 >= D) continue;
+      const uint64_t idx0 = base + (uint64_t)e0;
+      if ((idx0 & (EV - 1)) == 0 && e0 + EV <= D) {
+        uint32_t o[4];
+        const uint64_t g = idx0 >> 3;
+        philox4x32_10(k0, k1, (uint32_t)g, (uint32_t)(g >> 32), o);
+        const int j0 = (int)(idx0 & 7);   // 0, or 4 for the second half of a group of 32-bit elements
+#pragma unroll
+        for (int t = 0; t < EV; ++t) {
+          const int j = j0 + t;
+          const uint32_t rr = (o[(j >> 1) & 3] >> (16 * (j & 1))) & 0xffffu;
+          r.v[k][t] = rr >= thr ? r.v[k][t] * scale : 0.f;
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < EV; ++t)
+          if (e0 + t < D) r.v[k][t] = one(r.v[k][t], idx0 + t);
+      }
+    }
+  }
 };
 
 // LayerNorm flavour: one warp per row of D = H * V elements.
-template <typename E, int MAXV>
+template <typename E, int MAXV, bool DROPOUT>
 __global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_kernel(NormMulParams p) {
   constexpr int EV = VecInfo<E>::EV;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int D = p.H * p.V;
+  Dropout drop;
+  if (DROPOUT) drop.init(p);
+  const int width = D * (1 + (p.concat_u ? 1 : 0) + (p.concat_x ? 1 : 0));
   Row<E, MAXV> wr, br;
   wr.load((const E *)p.w, D, lane, p.vec_ok);
   br.load((const E *)p.b, D, lane, p.vec_ok);
@@ -567,13 +644,26 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_kernel(NormMulParams 
     float mean, rstd;
     row_stats(xr, D, lane, p.eps, mean, rstd);
     E *orow = (E *)p.out + row * p.out_rs;
+    const uint64_t rbase = (uint64_t)row * (uint64_t)width;   // index of the row's first element
     int off = 0;
     if (p.concat_u) {
-      ur.store(orow, D, lane, p.vec_ok);
+      if (DROPOUT) {
+        Row<E, MAXV> du_ = ur;
+        drop.apply(du_, rbase, D, lane);
+        du_.store(orow, D, lane, p.vec_ok);
+      } else {
+        ur.store(orow, D, lane, p.vec_ok);
+      }
       off += D;
     }
     if (p.concat_x) {
-      xr.store(orow + off, D, lane, p.vec_ok);
+      if (DROPOUT) {
+        Row<E, MAXV> dx_ = xr;
+        drop.apply(dx_, rbase + off, D, lane);
+        dx_.store(orow + off, D, lane, p.vec_ok);
+      } else {
+        xr.store(orow + off, D, lane, p.vec_ok);
+      }
       off += D;
     }
 #pragma unroll
@@ -581,6 +671,7 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_kernel(NormMulParams 
 #pragma unroll
       for (int t = 0; t < EV; ++t)
         xr.v[k][t] = act_f(ur.v[k][t], p.act) * ((xr.v[k][t] - mean) * rstd * wr.v[k][t] + br.v[k][t]);
+    if (DROPOUT) drop.apply(xr, rbase + off, D, lane);
     xr.store(orow + off, D, lane, p.vec_ok);
     if (lane == 0) {
       if (p.mean) p.mean[row] = mean;
@@ -589,12 +680,15 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_kernel(NormMulParams 
   }
 }
 
-template <typename E, int MAXV>
+template <typename E, int MAXV, bool DROPOUT>
 __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams p) {
   constexpr int EV = VecInfo<E>::EV;
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int D = p.H * p.V;
+  Dropout drop;
+  if (DROPOUT) drop.init(p);
+  const int width = D * (1 + (p.concat_u ? 1 : 0) + (p.concat_x ? 1 : 0));
   Row<E, MAXV> wr, br, dw, db;
   wr.load((const E *)p.w, D, lane, p.vec_ok);
   br.load((const E *)p.b, D, lane, p.vec_ok);
@@ -649,6 +743,9 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
       mean = p.mean[row];
       rstd = p.rstd[row];
     }
+    // the forward's mask, regenerated: the gradient of a dropped element is zero, of a kept one scaled
+    const uint64_t rbase = (uint64_t)row * (uint64_t)width;
+    if (DROPOUT) drop.apply(gy, rbase + off_y, D, lane);
     float c1 = 0.f, c2 = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k)
@@ -681,6 +778,7 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
       } else {
         tmp.load(grow, D, lane, p.vec_ok);
       }
+      if (DROPOUT) drop.apply(tmp, rbase, D, lane);
 #pragma unroll
       for (int k = 0; k < MAXV; ++k)
 #pragma unroll
@@ -692,6 +790,7 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
       } else {
         tmp.load(grow + off_x, D, lane, p.vec_ok);
       }
+      if (DROPOUT) drop.apply(tmp, rbase + off_x, D, lane);
 #pragma unroll
       for (int k = 0; k < MAXV; ++k)
 #pragma unroll
@@ -947,6 +1046,17 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
   p.dout_rs = a.dout_row_stride; p.dattn_rs = a.dattn_row_stride; p.du_rs = a.du_row_stride;
   p.rows = a.rows; p.H = a.H; p.V = a.V; p.concat_u = a.concat_u; p.concat_x = a.concat_x; p.act = a.act;
   p.group_norm = a.group_norm; p.eps = a.eps;
+  p.drop_seed = nullptr; p.drop_thr = 0; p.drop_scale = 1.f;
+  const bool dropout = a.dropout_seed != nullptr && a.dropout_ratio > 0.f;
+  if (dropout) {
+    if (a.group_norm) return fail(B200_HSTU_EUNSUPPORTED, "norm_mul: in-kernel dropout is not built for the group-norm variant");
+    if (!(a.dropout_ratio < 1.f)) return fail(B200_HSTU_EINVAL, "norm_mul: dropout_ratio must be below 1");
+    uint32_t thr = (uint32_t)(a.dropout_ratio * 65536.f + 0.5f);
+    thr = thr > 65535u ? 65535u : thr;
+    p.drop_seed = reinterpret_cast<const unsigned long long *>(a.dropout_seed);
+    p.drop_thr = thr;
+    p.drop_scale = 65536.f / (float)(65536u - thr);
+  }
   const int D = a.H * a.V;
   if (a.rows == 0) {
     if (bwd) {  // dweight / dbias of an empty batch are zeros
@@ -989,7 +1099,11 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     int64_t nblk = (a.rows + WARPS - 1) / WARPS;
     int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
     ProfileScope prof(PROF_NORM_MUL_FWD, st);
-    DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV><<<grid, WARPS * 32, 0, st>>>(p)));
+    if (dropout) {
+      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, true><<<grid, WARPS * 32, 0, st>>>(p)));
+    } else {
+      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, false><<<grid, WARPS * 32, 0, st>>>(p)));
+    }
     count_launch();
     B200_CHECK_LAUNCH("norm_mul forward");
     return 0;
@@ -1003,11 +1117,19 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     return fail(B200_HSTU_EWORKSPACE, "norm_mul backward: scratch too small");
   size_t smem = (size_t)WARPS * D * sizeof(float);
   ProfileScope prof(PROF_NORM_MUL_BWD, st);
-  DISPATCH_MAXV(pick_maxv<E>(D), {
-    auto kern = norm_mul_bwd_kernel<E, MV>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, WARPS * 32, smem, st>>>(p);
-  });
+  if (dropout) {
+    DISPATCH_MAXV(pick_maxv<E>(D), {
+      auto kern = norm_mul_bwd_kernel<E, MV, true>;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      kern<<<grid, WARPS * 32, smem, st>>>(p);
+    });
+  } else {
+    DISPATCH_MAXV(pick_maxv<E>(D), {
+      auto kern = norm_mul_bwd_kernel<E, MV, false>;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      kern<<<grid, WARPS * 32, smem, st>>>(p);
+    });
+  }
   count_launch();
   B200_CHECK_LAUNCH("norm_mul backward");
   reduce_partial_kernel<E><<<(2 * D + 31) / 32, 256, 0, st>>>(p.partial, grid, D, (E *)a.dweight, (E *)a.dbias);

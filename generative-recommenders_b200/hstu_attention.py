@@ -5,6 +5,8 @@ value) and the autograd wrapper of its GPU backends
 (generative_recommenders/ops/triton/triton_hstu_attention.py:2978-3092).
 """
 
+import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -65,6 +67,36 @@ def _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, 
 
 _PLAN_OWN, _PLAN_FOR_BACKWARD, _PLAN_REUSE = 0, 1, 2
 
+# B200_HSTU_CHECK_STATUS=1: after every tensor-core attention launch, wait for it and read the status
+# words of its work lists back; a bounded wait that gave up inside the kernel (which then returned
+# early, leaving its output incomplete) becomes a RuntimeError instead of passing silently.  A
+# debugging aid: it synchronises the stream after every call.
+_CHECK_STATUS = os.environ.get("B200_HSTU_CHECK_STATUS", "0") not in ("", "0")
+
+
+def set_status_check(on: bool) -> None:
+    global _CHECK_STATUS
+    _CHECK_STATUS = bool(on)
+
+
+def attention_status(a, which: int, device):
+    """Status words ``[forward, backward dK/dV, backward dQ]`` of the launches that used the scratch
+    in ``a`` (0 = ran to completion, otherwise the id of the wait that gave up); waits for the stream."""
+    host = torch.zeros(3, dtype=torch.int32).pin_memory()
+    with torch.cuda.device(device):
+        _cabi.check(_cabi.lib().b200_hstu_attn_status_async(
+            a, which, ctypes.cast(host.data_ptr(), ctypes.POINTER(ctypes.c_int32)), stream_ptr(device)),
+            "b200_hstu_attn_status_async")
+        torch.cuda.current_stream(device).synchronize()
+    return host.tolist()
+
+
+def _raise_on_status(a, which, device, what):
+    st = attention_status(a, which, device)
+    if any(st):
+        raise RuntimeError("%s: a bounded wait inside the kernel gave up (status forward / dK,dV / dQ = %s); "
+                           "the output is incomplete" % (what, st))
+
 
 def _workspace(a, which: int, device) -> Optional[torch.Tensor]:
     """Scratch for a forward (0), a backward (1) or a forward that also plans the backward (2)."""
@@ -98,6 +130,8 @@ def hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, at
         a.plan_mode = _PLAN_FOR_BACKWARD
     with torch.cuda.device(q.device):
         _cabi.check(_cabi.lib().b200_hstu_attn_fwd(a, stream_ptr(q.device)), "b200_hstu_attn_fwd")
+    if _CHECK_STATUS and ws is not None:
+        _raise_on_status(a, 0, q.device, "b200_hstu_attn_fwd")
     return (out, ws) if plan_for_backward else out
 
 
@@ -131,6 +165,8 @@ def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targe
         ws = _workspace(a, 1, q.device)  # noqa: F841
     with torch.cuda.device(q.device):
         _cabi.check(_cabi.lib().b200_hstu_attn_bwd(a, stream_ptr(q.device)), "b200_hstu_attn_bwd")
+    if _CHECK_STATUS and a.workspace:
+        _raise_on_status(a, 2 if reuse else 1, q.device, "b200_hstu_attn_bwd")
 
 
 class _HstuMhaFunction(torch.autograd.Function):

@@ -304,7 +304,8 @@ def hstu_compute_uqvk(
 
 class _NormMulFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm):
+    def forward(ctx, attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm,
+                dropout_ratio=0.0, dropout_seed=None):
         rows = attn.shape[0]
         D = num_heads * linear_dim
         if attn.stride(-1) != 1:
@@ -328,17 +329,19 @@ class _NormMulFunction(torch.autograd.Function):
         a.rows, a.H, a.V = rows, num_heads, linear_dim
         a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
         a.eps, a.dtype = eps, dtype_code(attn)
+        if dropout_seed is not None and dropout_ratio > 0.0:
+            a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
         if rows > 0:
             with torch.cuda.device(attn.device):
                 _cabi.check(_cabi.lib().b200_hstu_norm_mul_fwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_fwd")
-        ctx.save_for_backward(attn, u, weight, bias, mean, rstd)
-        ctx.cfg = (eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm)
+        ctx.save_for_backward(attn, u, weight, bias, mean, rstd, dropout_seed)
+        ctx.cfg = (eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm, dropout_ratio)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        attn, u, weight, bias, mean, rstd = ctx.saved_tensors
-        eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm = ctx.cfg
+        attn, u, weight, bias, mean, rstd, dropout_seed = ctx.saved_tensors
+        eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm, dropout_ratio = ctx.cfg
         rows = attn.shape[0]
         if dout.stride(-1) != 1:
             dout = dout.contiguous()
@@ -359,9 +362,11 @@ class _NormMulFunction(torch.autograd.Function):
         a.rows, a.H, a.V = rows, num_heads, linear_dim
         a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
         a.eps, a.dtype = eps, dtype_code(attn)
+        if dropout_seed is not None and dropout_ratio > 0.0:   # the kernel regenerates the forward's mask
+            a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
         with torch.cuda.device(attn.device):
             _cabi.check(_cabi.lib().b200_hstu_norm_mul_bwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_bwd")
-        return dattn, du, dw, db, None, None, None, None, None, None, None
+        return dattn, du, dw, db, None, None, None, None, None, None, None, None, None
 
 
 def hstu_norm_mul_dropout(
@@ -378,9 +383,16 @@ def hstu_norm_mul_dropout(
     group_norm: bool = False,
     num_heads: int = 1,
     linear_dim: int = -1,
+    dropout_seed: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """``dropout(cat([u, attn, act(u) * Norm(attn)]))`` - the input of the output linear
-    (generative_recommenders/ops/pytorch/pt_hstu_linear.py:23-82)."""
+    (generative_recommenders/ops/pytorch/pt_hstu_linear.py:23-82).
+
+    In training the dropout mask is generated inside the kernel (counter-based Philox keyed by
+    ``dropout_seed``, a one-element int64 tensor on the device; drawn from torch's CUDA generator when
+    not given) and regenerated by the backward, like the reference's GPU path
+    (ops/triton/triton_hstu_linear.py:365-492); the mask bits are this library's own.  The
+    group-norm variant applies ``torch.nn.functional.dropout`` afterwards."""
     if mul_u_activation_type not in _ACT:
         raise ValueError("mul_u_activation_type must be one of none / sigmoid / silu")
     if group_norm and concat_u != concat_x:
@@ -389,10 +401,16 @@ def hstu_norm_mul_dropout(
     act = 0 if group_norm else _ACT[mul_u_activation_type]
     if linear_dim <= 0:
         linear_dim = attn.shape[1] // num_heads
+    drop = training and dropout_ratio > 0.0
+    fused_drop = drop and not group_norm and dropout_ratio < 1.0
+    if fused_drop and dropout_seed is None:
+        # from torch's CUDA generator: reproducible under torch.manual_seed, and a fresh value on every
+        # replay when the step is captured in a CUDA graph
+        dropout_seed = torch.randint(0, 2 ** 62, (1,), dtype=torch.int64, device=attn.device)
     y = _NormMulFunction.apply(attn, u, norm_weight, norm_bias, float(norm_eps), int(num_heads), int(linear_dim),
-                               bool(concat_u), bool(concat_x), act, bool(group_norm))
-    if training and dropout_ratio > 0.0:
-        # the mask comes from torch's generator, exactly like the reference's F.dropout (:77-81)
+                               bool(concat_u), bool(concat_x), act, bool(group_norm),
+                               float(dropout_ratio) if fused_drop else 0.0, dropout_seed if fused_drop else None)
+    if drop and not fused_drop:
         y = torch.nn.functional.dropout(y, p=dropout_ratio, training=True)
     return y
 

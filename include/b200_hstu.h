@@ -152,6 +152,28 @@ int64_t b200_hstu_attn_fwd_static_scratch_max_bytes(void);
 int64_t b200_hstu_attn_workspace_bytes(const b200_hstu_attn_args *args, int backward);
 
 /*
+ * Status of the tensor-core launches.  Every wait inside those kernels is bounded (2 s without
+ * progress); a wait that gives up records its site id (> 0) in the status word of the launch's
+ * work list and the kernel returns early, leaving its output incomplete.  This call queues, on
+ * `stream`, copies of the status words of the launches that used args->workspace into
+ * host_status[3] - [0] forward, [1] backward dK/dV launch, [2] backward dQ launch; entries that
+ * the call does not cover are set to 0 - which the caller reads after synchronising the stream
+ * (pinned host memory keeps the copies asynchronous).  `which`: 0 = a forward's workspace, 1 = a
+ * backward's, 2 = the workspace of a forward that planned the backward (all three).  Same args as
+ * the launch.  The CUDA-core kernels have no waits: all zeros.  No counterpart in the reference
+ * (its kernels spin without a limit, generative_recommenders/ops/triton/triton_attention_utils.py:42-48).
+ */
+int b200_hstu_attn_status_async(const b200_hstu_attn_args *args, int which, int32_t *host_status,
+                                b200_hstu_stream_t stream);
+
+/*
+ * Self-test of the bounded wait: a one-warp kernel waits, with the limit shortened to 1 ms, on a
+ * barrier nobody arrives at; the wait expires, records site 777 in *status_dev (device int32,
+ * cleared first) and the time it waited in *elapsed_ns_dev (device uint64), and the kernel returns.
+ */
+int b200_hstu_selftest_bounded_wait(int32_t *status_dev, uint64_t *elapsed_ns_dev, b200_hstu_stream_t stream);
+
+/*
  * FP8 (e4m3) forward for inference with per-block scales: q8/k8/v8 are
  * [total_L, H, d] e4m3 (contiguous heads), *_scale are fp32 [n_blocks_total, H] where
  * sequence b owns rows block_offsets[b] .. block_offsets[b+1], one row per 128 tokens
@@ -207,6 +229,13 @@ int b200_hstu_silu_bwd(const void *dy, int64_t dy_row_stride, const void *x, int
  * linear (generative_recommenders/ops/pytorch/pt_hstu_linear.py:23-82).  attn, u: [rows, H*V];
  * out: [rows, (1 + concat_u + concat_x) * H*V].  act: 0 none, 1 sigmoid, 2 silu.  group_norm: 0 =
  * LayerNorm over H*V (weight/bias [H*V]), 1 = per-head normalisation (weight/bias [H]).
+ * Dropout (training; pt_hstu_linear.py:77-81 applies F.dropout to the concatenated row, the
+ * reference's GPU path generates the mask inside its kernel, ops/triton/triton_hstu_linear.py:
+ * 365-492): with dropout_seed != NULL and 0 < dropout_ratio < 1 every element of the output row is
+ * zeroed with probability round(dropout_ratio * 65536) / 65536 and the others are scaled by the
+ * inverse keep probability.  Element idx = row * width + column uses the (idx % 8)-th 16-bit piece
+ * of Philox4x32-10(key = *dropout_seed, counter = idx / 8, 0, 0); the backward, given the same
+ * seed, regenerates the mask (nothing is stored).  Not built for group_norm = 1.
  */
 typedef struct b200_hstu_norm_mul_args {
   const void *attn, *u, *weight, *bias;
@@ -222,6 +251,9 @@ typedef struct b200_hstu_norm_mul_args {
   int32_t concat_u, concat_x, act, group_norm;
   float eps;
   int32_t dtype;
+  float dropout_ratio;               /* 0 = no dropout */
+  int32_t reserved0;
+  const int64_t *dropout_seed;       /* device, one int64 (read by the kernels); NULL = no dropout */
 } b200_hstu_norm_mul_args;
 int b200_hstu_norm_mul_fwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream_t stream);
 int b200_hstu_norm_mul_bwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream_t stream);

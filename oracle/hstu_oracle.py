@@ -605,3 +605,46 @@ def max_abs_ratio(a: torch.Tensor, b: torch.Tensor) -> float:
     den = b.abs().max().item()
     num = (a - b).abs().max().item()
     return num / den if den > 0 else num
+
+
+# --------------------------------------------------------------------------------------
+# dropout mask of the output stage (no reference arithmetic exists for the mask bits: the
+# reference draws them from torch's or Triton's generator; this states the format the CUDA
+# kernels use, so that a test can replay a mask)
+# --------------------------------------------------------------------------------------
+def philox4x32_10(key: int, counters):
+    """Philox4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3",
+    SC'11) for 64-bit ``key`` and an array of 64-bit ``counters`` (the upper two counter words
+    are zero); returns a ``[n, 4]`` uint32 array."""
+    import numpy as np
+
+    c = np.asarray(counters, dtype=np.uint64)
+    m32 = np.uint64(0xFFFFFFFF)
+    c0, c1 = c & m32, c >> np.uint64(32)
+    c2 = np.zeros_like(c0)
+    c3 = np.zeros_like(c0)
+    k0, k1 = np.uint64(key & 0xFFFFFFFF), np.uint64((key >> 32) & 0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c0
+        p1 = np.uint64(0xCD9E8D57) * c2
+        hi0, lo0 = p0 >> np.uint64(32), p0 & m32
+        hi1, lo1 = p1 >> np.uint64(32), p1 & m32
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ k0) & m32, lo1, (hi0 ^ c3 ^ k1) & m32, lo0
+        k0 = (k0 + np.uint64(0x9E3779B9)) & m32
+        k1 = (k1 + np.uint64(0xBB67AE85)) & m32
+    return np.stack([c0, c1, c2, c3], axis=-1).astype(np.uint32)
+
+
+def dropout_keep_mask(seed: int, rows: int, width: int, dropout_ratio: float) -> torch.Tensor:
+    """Boolean ``[rows, width]`` keep-mask of the output stage's dropout and the scale of the kept
+    elements: element ``idx = row * width + col`` is dropped when the ``(idx % 8)``-th 16-bit piece
+    of ``Philox4x32-10(key=seed, counter=idx // 8)`` is below ``round(dropout_ratio * 65536)``."""
+    import numpy as np
+
+    thr = min(int(dropout_ratio * 65536.0 + 0.5), 65535)
+    n = rows * width
+    groups = (n + 7) // 8
+    words = philox4x32_10(seed, np.arange(groups, dtype=np.uint64))          # [groups, 4]
+    pieces = np.stack([words & 0xFFFF, words >> 16], axis=-1).reshape(groups, 8)  # piece j: word j // 2, half j % 2
+    keep = (pieces.reshape(-1)[:n] >= thr).reshape(rows, width)
+    return torch.from_numpy(keep), 65536.0 / (65536 - thr)

@@ -32,6 +32,8 @@ def test_struct_layout_matches_header():
     # the structs are plain C: spot-check the sizes the Python mirror computes
     assert ctypes.sizeof(_cabi.AttnArgs) % 8 == 0
     assert _cabi.AttnArgs.total_L.offset == 8 * 12 + 8 * 16
+    # ... delta_size, reserved1, then the optional bias gradient as the last field
+    assert _cabi.AttnArgs.d_bias_by_distance.offset == ctypes.sizeof(_cabi.AttnArgs) - 8
     assert ctypes.sizeof(_cabi.AttnFp8Args) == ctypes.sizeof(_cabi.AttnArgs) + 32
 
 
@@ -55,6 +57,11 @@ def test_bad_arguments_are_rejected_on_the_host():
     assert lib.b200_hstu_norm_mul_fwd(n, None) == -1
     assert lib.b200_hstu_layer_norm_fwd(None, 0, None, None, None, 0, None, None, 4, 0, 1e-5, 0, None) == -1
     assert lib.b200_hstu_layer_norm_bwd_workspace_bytes(512) > 0
+    st = (ctypes.c_int32 * 3)(5, 5, 5)
+    assert lib.b200_hstu_attn_status_async(None, 0, st, None) == -1
+    assert lib.b200_hstu_attn_status_async(a, 3, st, None) == -1
+    assert lib.b200_hstu_attn_status_async(a, 0, st, None) == 0 and list(st) == [0, 0, 0]   # no workspace: nothing to read
+    assert lib.b200_hstu_selftest_bounded_wait(None, None, None) == -1
 
 
 def test_host_mask_matches_reference_masks(golden):

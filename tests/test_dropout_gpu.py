@@ -1,0 +1,96 @@
+"""Dropout of the output stage, generated inside the norm-mul kernels: the mask replayed from its
+seed by the oracle's Philox, forward and backward, and the public ops with dropout on."""
+
+import pytest
+import torch
+
+import generative_recommenders_b200 as G
+from oracle import hstu_oracle as O
+import parity_metrics as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.mark.parametrize("dtype,H,V,concat", [
+    (torch.bfloat16, 4, 128, (True, True)),     # the layer's own configuration: [u | attn | y], 1536 columns
+    (torch.bfloat16, 2, 64, (False, False)),
+    (torch.float16, 2, 96, (True, False)),
+    (torch.float32, 2, 64, (True, True)),       # 4 elements per 16-byte vector: half a generator call each
+    (torch.bfloat16, 2, 34, (True, True)),      # H*V = 68: rows not made of whole vectors (element-wise path)
+])
+def test_dropout_mask_replay_forward_backward(dtype, H, V, concat):
+    g = torch.Generator().manual_seed(11)
+    rows, D, p = 333, H * V, 0.3
+    attn = torch.randn(rows, D, generator=g).to(dtype)
+    u = torch.randn(rows, D, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(D, generator=g)).to(dtype)
+    mult = 1 + int(concat[0]) + int(concat[1])
+    dy = torch.randn(rows, mult * D, generator=g).to(dtype)
+    seed = torch.tensor([0x1234_5678_9ABC_DEF], dtype=torch.int64, device=DEV)
+    ld = [t.to(DEV).requires_grad_(True) for t in (attn, u, w, b)]
+    y = G.hstu_norm_mul_dropout(ld[0], ld[1], ld[2], ld[3], 1e-6, p, True, concat[0], concat[1], "none", False, H, V,
+                                dropout_seed=seed)
+    y.backward(dy.to(DEV))
+    keep, scale = O.dropout_keep_mask(int(seed.item()), rows, mult * D, p)
+    assert abs(float(keep.float().mean()) - (1 - p)) < 0.01
+    lr = [t.float().requires_grad_(True) for t in (attn, u, w, b)]
+    yr = O.norm_mul_dropout(lr[0], lr[1], lr[2], lr[3], 1e-6, concat[0], concat[1], "none", False, H, V)
+    yr = yr * keep * scale
+    yr.backward(dy.float())
+    # the zeros are where the replayed mask puts them (a kept element is zero with probability ~0)
+    assert torch.equal(y.detach().cpu() == 0, ~keep | (yr.detach() == 0))
+    tol = dict(tol=2e-4, max_tol=5e-4) if dtype == torch.float32 else {}
+    P.check(("dropout", str(dtype), H, V, concat, "y"), y, yr.detach(), **tol)
+    for a, r, nm in zip(ld, lr, ("dattn", "du", "dw", "db")):
+        P.check(("dropout", str(dtype), H, V, concat, nm), a.grad, r.grad, **tol)
+    # the same seed gives the same bits, another seed another mask
+    y2 = G.hstu_norm_mul_dropout(ld[0], ld[1], ld[2], ld[3], 1e-6, p, True, concat[0], concat[1], "none", False, H, V,
+                                 dropout_seed=seed)
+    y3 = G.hstu_norm_mul_dropout(ld[0], ld[1], ld[2], ld[3], 1e-6, p, True, concat[0], concat[1], "none", False, H, V,
+                                 dropout_seed=seed + 1)
+    assert torch.equal(y, y2) and not torch.equal(y, y3)
+
+
+def test_compute_output_with_dropout():
+    """``hstu_compute_output`` in training mode: one launch produces the dropped-out concat (no
+    separate dropout pass), the keep fraction is 1 - p, results are reproducible under
+    ``torch.manual_seed`` and differ from call to call, and eval mode is untouched."""
+    g = torch.Generator().manual_seed(2)
+    rows, H, V, D, p = 2000, 4, 128, 512, 0.3
+    attn, u = (torch.randn(rows, H * V, generator=g).bfloat16().to(DEV) for _ in range(2))
+    x = torch.randn(rows, D, generator=g).bfloat16().to(DEV)
+    nw, nb = torch.ones(H * V, device=DEV).bfloat16(), torch.zeros(H * V, device=DEV).bfloat16()
+    Wo = (torch.randn(3 * H * V, D, generator=g) / 40).bfloat16().to(DEV)
+
+    def run(training):
+        return G.hstu_compute_output(attn, u, x, nw, nb, 1e-6, Wo, H, V, p, training, True, True, "none", False, False)
+
+    torch.manual_seed(5)
+    a1 = run(True)
+    a2 = run(True)
+    torch.manual_seed(5)
+    b1 = run(True)
+    assert torch.equal(a1, b1) and not torch.equal(a1, a2)
+    ref = O.hstu_compute_output(attn.float().cpu(), u.float().cpu(), x.float().cpu(), nw.float().cpu(), nb.float().cpu(),
+                                1e-6, Wo.float().cpu(), H, V, True, True)
+    P.check("compute_output_eval", run(False), ref)
+    n0 = G._cabi.launch_count()
+    y = G.hstu_norm_mul_dropout(attn, u, nw, nb, 1e-6, p, True, True, True, "none", False, H, V)
+    assert G._cabi.launch_count() - n0 == 1
+    frac = float((y != 0).float().mean())
+    assert abs(frac - (1 - p)) < 5e-3, frac
+    # E[dropout(y)] = y: the mean over many elements stays put
+    y0 = G.hstu_norm_mul_dropout(attn, u, nw, nb, 1e-6, 0.0, False, True, True, "none", False, H, V)
+    assert abs(float(y.float().abs().mean()) / float(y0.float().abs().mean()) - 1.0) < 2e-2
+
+
+def test_group_norm_variant_keeps_torch_dropout():
+    g = torch.Generator().manual_seed(3)
+    rows, H, V = 400, 4, 32
+    attn, u = (torch.randn(rows, H * V, generator=g).bfloat16().to(DEV) for _ in range(2))
+    w, b = torch.ones(H, device=DEV).bfloat16(), torch.zeros(H, device=DEV).bfloat16()
+    y = G.hstu_norm_mul_dropout(attn, u, w, b, 1e-6, 0.5, True, True, True, "none", True, H, V)
+    frac = float((y != 0).float().mean())
+    assert 0.45 < frac < 0.55

@@ -150,6 +150,18 @@ def test_attention_with_learnable_bias_matches_reference(golden):
     assert fx["dw"][N:].abs().max() == 0
 
 
+def test_philox_known_answer_and_mask_fraction():
+    """Philox4x32-10 against the published known-answer vector (counter 0, key 0 ->
+    6627e8d5 e169c58d bc57ac4c 9b00dbd8, Random123's kat_vectors), and the dropout mask built on it."""
+    assert [int(x) for x in O.philox4x32_10(0, [0])[0]] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    keep, scale = O.dropout_keep_mask(99, 500, 1536, 0.3)
+    assert keep.shape == (500, 1536)
+    assert abs(float(keep.float().mean()) - 0.7) < 3e-3
+    assert abs(scale - 1 / 0.7) < 1e-4
+    keep2, _ = O.dropout_keep_mask(100, 500, 1536, 0.3)
+    assert not torch.equal(keep, keep2)
+
+
 def test_fp8_block_quant_roundtrip():
     g = torch.Generator().manual_seed(0)
     off = torch.tensor([0, 5, 5, 300, 431])
