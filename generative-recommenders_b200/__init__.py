@@ -22,6 +22,7 @@ from .mm import addmm
 from .position import add_timestamp_positional_embeddings
 from .positional_encoder import HSTUPositionalEncoder
 from .stu import STULayer, STULayerConfig, STUStack
+from .integration import install, uninstall
 
 __all__ = [
     "HammerKernel",
@@ -45,4 +46,6 @@ __all__ = [
     "STULayerConfig",
     "STUStack",
     "set_attention_impl",
+    "install",
+    "uninstall",
 ]
