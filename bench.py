@@ -787,8 +787,11 @@ def run_stack(args):
     train = args.workload == "config2_stack"
     if train:
         w_all = W.config2_attention(args.batch or 128)
+        # 8 505 tokens: activations are kept (the recompute switches, which trade memory for one more
+        # launch of two kernels per layer in the backward, are off); the bias tables are trained
         D, layers, cfg = 512, 8, G.STULayerConfig(embedding_dim=512, num_heads=4, hidden_dim=128, attention_dim=128,
-                                                  output_dropout_ratio=0.0, contextual_seq_len=6, rel_bias_buckets=128)
+                                                  output_dropout_ratio=0.0, contextual_seq_len=6, rel_bias_buckets=128,
+                                                  recompute_normed_x=False, recompute_uvqk=False, recompute_y=False)
     else:
         w_all = W.config4(args.batch or 2048)
         D, layers, cfg = 1024, 4, G.STULayerConfig(embedding_dim=1024, num_heads=8, hidden_dim=128, attention_dim=128,
@@ -1113,6 +1116,14 @@ def stage_kernels(dev, peaks, steps):
     yc = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.0, False, True, True, "none", False, 4, 128)
     res["norm_mul_bwd"] = timed("norm_mul_bwd", lambda: torch.autograd.grad(yc, (ar, ur, wr, br), dcat, retain_graph=True),
                                 rows * D * 2 * 7 + rows * 8)
+    # training: the dropout mask is generated inside the same kernels (same algorithmic bytes; a
+    # separate dropout pass would move another 6 * D * 2 bytes per row and keep a mask)
+    seed = torch.tensor([20260], dtype=torch.int64, device=dev)
+    res["norm_mul_fwd_dropout"] = timed("norm_mul_fwd", lambda: G.hstu_norm_mul_dropout(
+        attn, u, w_, b_, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed), rows * D * 2 * 5 + rows * 8)
+    yd = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed)
+    res["norm_mul_bwd_dropout"] = timed("norm_mul_bwd", lambda: torch.autograd.grad(yd, (ar, ur, wr, br), dcat, retain_graph=True),
+                                        rows * D * 2 * 7 + rows * 8)
     # jagged glue: KV-cache split / concat of [rows, H*d] K rows (last 20 rows of every sequence on
     # the right), and the timestamp + position embedding step before layer 0
     from generative_recommenders_b200.jagged_tensors import concat_2D_jagged, split_2D_jagged

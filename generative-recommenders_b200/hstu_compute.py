@@ -199,7 +199,8 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, norm_weight, norm_bias, eps, weight, bias, num_heads, attn_dim, hidden_dim, seq_offsets,
-                num_targets, bias_by_distance, max_seq_len, alpha, max_attn_len, contextual_seq_len, grad_mode=True):
+                num_targets, bias_by_distance, max_seq_len, alpha, max_attn_len, contextual_seq_len, grad_mode=True,
+                recompute_uvqk=False):
         from .hstu_attention import hstu_attention_fwd
 
         M = x.shape[0]
@@ -220,7 +221,13 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
         ctx.planned_scratch = None
         if plan:
             out, ctx.planned_scratch = out
-        ctx.save_for_backward(x, nw, nb, w, uvqk, mean, rstd, seq_offsets, num_targets, bias_by_distance)
+        # recompute_uvqk: the [M, 4 H d] projection - the largest activation of the layer - is not kept;
+        # the backward runs the fused kernel once more (the reference's recompute_uvqk_in_backward,
+        # generative_recommenders/ops/triton/triton_hstu_preprocess_and_attention.py:122-127, 185-203).
+        # k and v go out as views of that buffer either way: it lives on only while the caller keeps them
+        # (the layer does so for its KV cache, otherwise it drops them at once).
+        keep = None if (recompute_uvqk and not no_grad) else uvqk
+        ctx.save_for_backward(x, nw, nb, w, b, keep, mean, rstd, seq_offsets, num_targets, bias_by_distance)
         ctx.cfg = (eps, num_heads, attn_dim, hidden_dim, max_seq_len, alpha, max_attn_len, contextual_seq_len,
                    norm_weight.dtype, norm_bias.dtype, weight.dtype, bias.dtype)
         return u, out, k, v
@@ -229,11 +236,13 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
     def backward(ctx, du, dattn, dk_ext, dv_ext):
         from .hstu_attention import hstu_attention_bwd
 
-        x, nw, nb, w, uvqk, mean, rstd, seq_offsets, num_targets, bias_by_distance = ctx.saved_tensors
+        x, nw, nb, w, b, uvqk, mean, rstd, seq_offsets, num_targets, bias_by_distance = ctx.saved_tensors
         (eps, H, A, V, max_seq_len, alpha, max_attn_len, contextual_seq_len,
          nw_dtype, nb_dtype, w_dtype, b_dtype) = ctx.cfg
-        M, N = uvqk.shape
         hv, ha = V * H, A * H
+        if uvqk is None:   # not kept: one more launch of the fused kernel
+            uvqk, _, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, False)
+        M, N = uvqk.shape
         d_uvqk = torch.empty((M, N), dtype=x.dtype, device=x.device)
         dv = d_uvqk[:, hv:2 * hv].view(M, H, V)
         dq = d_uvqk[:, 2 * hv:2 * hv + ha].view(M, H, A)
@@ -259,7 +268,7 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
             dv.add_(dv_ext)
         dx, dnw, dnb, dw, db = _fused_uqvk_backward(x, nw, nb, w, uvqk, mean, rstd, eps, hv, du, d_uvqk)
         return (dx, dnw.to(nw_dtype), dnb.to(nb_dtype), None, dw.to(w_dtype), db.to(b_dtype), None, None, None,
-                None, None, d_bias, None, None, None, None, None)
+                None, None, d_bias, None, None, None, None, None, None)
 
 
 _FUSED_UQVK = True
@@ -302,38 +311,77 @@ def hstu_compute_uqvk(
     return u, q, k, v
 
 
+def _norm_mul_forward(attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm,
+                      dropout_ratio, dropout_seed):
+    """One launch of the norm-mul kernel; returns ``(out, mean, rstd)`` (inputs already contiguous in
+    their last dimension, weight / bias already of the activation dtype)."""
+    rows = attn.shape[0]
+    D = num_heads * linear_dim
+    if group_norm:
+        mult = 3 if (concat_u and concat_x) else 1
+    else:
+        mult = 1 + int(concat_u) + int(concat_x)
+    out = torch.empty((rows, mult * D), dtype=attn.dtype, device=attn.device)
+    groups = num_heads if group_norm else 1
+    mean = torch.empty(rows * groups, dtype=torch.float32, device=attn.device)
+    rstd = torch.empty(rows * groups, dtype=torch.float32, device=attn.device)
+    a = _cabi.NormMulArgs()
+    a.attn, a.u, a.weight, a.bias = attn.data_ptr(), u.data_ptr(), weight.data_ptr(), bias.data_ptr()
+    a.out, a.mean, a.rstd = out.data_ptr(), mean.data_ptr(), rstd.data_ptr()
+    a.attn_row_stride, a.u_row_stride, a.out_row_stride = attn.stride(0), u.stride(0), out.stride(0)
+    a.rows, a.H, a.V = rows, num_heads, linear_dim
+    a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
+    a.eps, a.dtype = eps, dtype_code(attn)
+    if dropout_seed is not None and dropout_ratio > 0.0:
+        a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
+    if rows > 0:
+        with torch.cuda.device(attn.device):
+            _cabi.check(_cabi.lib().b200_hstu_norm_mul_fwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_fwd")
+    return out, mean, rstd
+
+
+def _norm_mul_backward(dout, attn, u, weight, bias, mean, rstd, eps, num_heads, linear_dim, concat_u, concat_x, act,
+                       group_norm, dropout_ratio, dropout_seed):
+    """Backward of the norm-mul kernel; returns ``(dattn, du, dweight, dbias)``."""
+    rows = attn.shape[0]
+    if dout.stride(-1) != 1:
+        dout = dout.contiguous()
+    dattn = torch.empty((rows, num_heads * linear_dim), dtype=attn.dtype, device=attn.device)
+    du = torch.empty_like(dattn)
+    dw = torch.empty_like(weight)
+    db = torch.empty_like(bias)
+    nbytes = _cabi.lib().b200_hstu_norm_mul_bwd_workspace_bytes(num_heads, linear_dim, int(group_norm))
+    partial = torch.empty(nbytes, dtype=torch.uint8, device=attn.device)
+    a = _cabi.NormMulArgs()
+    a.attn, a.u, a.weight, a.bias = attn.data_ptr(), u.data_ptr(), weight.data_ptr(), bias.data_ptr()
+    a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
+    a.dout, a.dattn, a.du = dout.data_ptr(), dattn.data_ptr(), du.data_ptr()
+    a.dweight, a.dbias = dw.data_ptr(), db.data_ptr()
+    a.partial, a.partial_bytes = partial.data_ptr(), nbytes
+    a.attn_row_stride, a.u_row_stride = attn.stride(0), u.stride(0)
+    a.dout_row_stride, a.dattn_row_stride, a.du_row_stride = dout.stride(0), dattn.stride(0), du.stride(0)
+    a.rows, a.H, a.V = rows, num_heads, linear_dim
+    a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
+    a.eps, a.dtype = eps, dtype_code(attn)
+    if dropout_seed is not None and dropout_ratio > 0.0:   # the kernel regenerates the forward's mask
+        a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
+    with torch.cuda.device(attn.device):
+        _cabi.check(_cabi.lib().b200_hstu_norm_mul_bwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_bwd")
+    return dattn, du, dw, db
+
+
 class _NormMulFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm,
                 dropout_ratio=0.0, dropout_seed=None):
-        rows = attn.shape[0]
-        D = num_heads * linear_dim
         if attn.stride(-1) != 1:
             attn = attn.contiguous()
         if u.stride(-1) != 1:
             u = u.contiguous()
         weight = weight.to(attn.dtype).contiguous()
         bias = bias.to(attn.dtype).contiguous()
-        if group_norm:
-            mult = 3 if (concat_u and concat_x) else 1
-        else:
-            mult = 1 + int(concat_u) + int(concat_x)
-        out = torch.empty((rows, mult * D), dtype=attn.dtype, device=attn.device)
-        groups = num_heads if group_norm else 1
-        mean = torch.empty(rows * groups, dtype=torch.float32, device=attn.device)
-        rstd = torch.empty(rows * groups, dtype=torch.float32, device=attn.device)
-        a = _cabi.NormMulArgs()
-        a.attn, a.u, a.weight, a.bias = attn.data_ptr(), u.data_ptr(), weight.data_ptr(), bias.data_ptr()
-        a.out, a.mean, a.rstd = out.data_ptr(), mean.data_ptr(), rstd.data_ptr()
-        a.attn_row_stride, a.u_row_stride, a.out_row_stride = attn.stride(0), u.stride(0), out.stride(0)
-        a.rows, a.H, a.V = rows, num_heads, linear_dim
-        a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
-        a.eps, a.dtype = eps, dtype_code(attn)
-        if dropout_seed is not None and dropout_ratio > 0.0:
-            a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
-        if rows > 0:
-            with torch.cuda.device(attn.device):
-                _cabi.check(_cabi.lib().b200_hstu_norm_mul_fwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_fwd")
+        out, mean, rstd = _norm_mul_forward(attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act,
+                                            group_norm, dropout_ratio, dropout_seed)
         ctx.save_for_backward(attn, u, weight, bias, mean, rstd, dropout_seed)
         ctx.cfg = (eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm, dropout_ratio)
         return out
@@ -341,32 +389,55 @@ class _NormMulFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         attn, u, weight, bias, mean, rstd, dropout_seed = ctx.saved_tensors
-        eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm, dropout_ratio = ctx.cfg
-        rows = attn.shape[0]
+        dattn, du, dw, db = _norm_mul_backward(dout, attn, u, weight, bias, mean, rstd, *ctx.cfg, dropout_seed)
+        return dattn, du, dw, db, None, None, None, None, None, None, None, None, None
+
+
+class _OutputStageFunction(torch.autograd.Function):
+    """The whole output stage, ``x + dropout(cat([u, attn, act(u) * Norm(attn)])) @ W``, as one autograd
+    node that keeps its inputs and the row statistics only: the concatenated activation (three
+    times as wide as ``attn``) is recomputed in the backward by one more launch of the norm-mul
+    kernel - with the same dropout seed, hence the same mask - before the two backward GEMMs read it.
+    This is the reference's ``recompute_y_in_backward``
+    (generative_recommenders/ops/triton/triton_hstu_linear.py:1895-2040)."""
+
+    @staticmethod
+    def forward(ctx, attn, u, x, weight, bias, output_weight, eps, num_heads, linear_dim, concat_u, concat_x, act,
+                group_norm, dropout_ratio, dropout_seed):
+        if attn.stride(-1) != 1:
+            attn = attn.contiguous()
+        if u.stride(-1) != 1:
+            u = u.contiguous()
+        w = weight.to(attn.dtype).contiguous()
+        b = bias.to(attn.dtype).contiguous()
+        wo = output_weight.to(x.dtype)
+        cfg = (eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm, dropout_ratio)
+        y, mean, rstd = _norm_mul_forward(attn, u, w, b, *cfg, dropout_seed)
+        out = torch.addmm(x, y, wo)
+        ctx.save_for_backward(attn, u, w, b, wo, mean, rstd, dropout_seed)
+        ctx.cfg = cfg
+        ctx.dtypes = (weight.dtype, bias.dtype, output_weight.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        attn, u, w, b, wo, mean, rstd, dropout_seed = ctx.saved_tensors
+        y, _, _ = _norm_mul_forward(attn, u, w, b, *ctx.cfg, dropout_seed)
         if dout.stride(-1) != 1:
             dout = dout.contiguous()
-        dattn = torch.empty((rows, num_heads * linear_dim), dtype=attn.dtype, device=attn.device)
-        du = torch.empty_like(dattn)
-        dw = torch.empty_like(weight)
-        db = torch.empty_like(bias)
-        nbytes = _cabi.lib().b200_hstu_norm_mul_bwd_workspace_bytes(num_heads, linear_dim, int(group_norm))
-        partial = torch.empty(nbytes, dtype=torch.uint8, device=attn.device)
-        a = _cabi.NormMulArgs()
-        a.attn, a.u, a.weight, a.bias = attn.data_ptr(), u.data_ptr(), weight.data_ptr(), bias.data_ptr()
-        a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
-        a.dout, a.dattn, a.du = dout.data_ptr(), dattn.data_ptr(), du.data_ptr()
-        a.dweight, a.dbias = dw.data_ptr(), db.data_ptr()
-        a.partial, a.partial_bytes = partial.data_ptr(), nbytes
-        a.attn_row_stride, a.u_row_stride = attn.stride(0), u.stride(0)
-        a.dout_row_stride, a.dattn_row_stride, a.du_row_stride = dout.stride(0), dattn.stride(0), du.stride(0)
-        a.rows, a.H, a.V = rows, num_heads, linear_dim
-        a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
-        a.eps, a.dtype = eps, dtype_code(attn)
-        if dropout_seed is not None and dropout_ratio > 0.0:   # the kernel regenerates the forward's mask
-            a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
-        with torch.cuda.device(attn.device):
-            _cabi.check(_cabi.lib().b200_hstu_norm_mul_bwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_bwd")
-        return dattn, du, dw, db, None, None, None, None, None, None, None, None, None
+        d_wo = y.t() @ dout
+        del y
+        dy = dout @ wo.t()
+        dattn, du, dw, db = _norm_mul_backward(dy, attn, u, w, b, mean, rstd, *ctx.cfg, dropout_seed)
+        wdt, bdt, odt = ctx.dtypes
+        return (dattn, du, dout, dw.to(wdt), db.to(bdt), d_wo.to(odt), None, None, None, None, None, None, None, None,
+                None)
+
+
+def _draw_dropout_seed(device) -> torch.Tensor:
+    # from torch's CUDA generator: reproducible under torch.manual_seed, and a fresh value on every
+    # replay when the step is captured in a CUDA graph
+    return torch.randint(0, 2 ** 62, (1,), dtype=torch.int64, device=device)
 
 
 def hstu_norm_mul_dropout(
@@ -404,9 +475,7 @@ def hstu_norm_mul_dropout(
     drop = training and dropout_ratio > 0.0
     fused_drop = drop and not group_norm and dropout_ratio < 1.0
     if fused_drop and dropout_seed is None:
-        # from torch's CUDA generator: reproducible under torch.manual_seed, and a fresh value on every
-        # replay when the step is captured in a CUDA graph
-        dropout_seed = torch.randint(0, 2 ** 62, (1,), dtype=torch.int64, device=attn.device)
+        dropout_seed = _draw_dropout_seed(attn.device)
     y = _NormMulFunction.apply(attn, u, norm_weight, norm_bias, float(norm_eps), int(num_heads), int(linear_dim),
                                bool(concat_u), bool(concat_x), act, bool(group_norm),
                                float(dropout_ratio) if fused_drop else 0.0, dropout_seed if fused_drop else None)
@@ -437,9 +506,22 @@ def hstu_compute_output(
     """``x + dropout(cat([u, attn, act(u) * Norm(attn)])) @ W_out``
     (generative_recommenders/ops/hstu_compute.py:107-214,
     generative_recommenders/ops/pytorch/pt_hstu_linear.py:85-120).
-    ``recompute_y_in_backward`` is accepted for signature compatibility; y is always kept."""
+    With ``recompute_y_in_backward`` the stage is one autograd node that does not keep the
+    concatenated activation (see ``_OutputStageFunction``)."""
     _require_cuda_backend(kernel)
     require_cuda(attn, u, x, norm_weight, norm_bias, output_weight)
+    if recompute_y_in_backward and torch.is_grad_enabled() and mul_u_activation_type in _ACT and attn.shape[0] > 0:
+        g_ = bool(group_norm)
+        cu, cx = bool(concat_u), bool(concat_x)
+        if g_ and cu != cx:
+            cu = cx = False
+        drop = training and dropout_ratio > 0.0
+        if not (drop and g_):   # the group-norm variant draws its mask with torch's dropout: kept on the plain path
+            seed = _draw_dropout_seed(attn.device) if (drop and dropout_ratio < 1.0) else None
+            ld = linear_dim if linear_dim > 0 else attn.shape[1] // num_heads
+            return _OutputStageFunction.apply(attn, u, x, norm_weight, norm_bias, output_weight, float(norm_eps),
+                                              int(num_heads), int(ld), cu, cx, 0 if g_ else _ACT[mul_u_activation_type],
+                                              g_, float(dropout_ratio) if seed is not None else 0.0, seed)
     y = hstu_norm_mul_dropout(attn, u, norm_weight, norm_bias, norm_eps, dropout_ratio, training, concat_u, concat_x,
                               mul_u_activation_type, group_norm, num_heads, linear_dim)
     return addmm(x, y, output_weight.to(x.dtype), kernel)
@@ -496,7 +578,7 @@ def hstu_preprocess_and_attention(
         u, attn, k, v = _FusedPreprocessAttentionFunction.apply(
             x, norm_weight, norm_bias, float(norm_eps), uvqk_weight, uvqk_bias, num_heads, attn_dim, hidden_dim,
             offs, nt, rab, int(max_seq_len), float(attn_alpha), int(max_attn_len), int(contextual_seq_len),
-            torch.is_grad_enabled())
+            torch.is_grad_enabled(), bool(recompute_uvqk_in_backward))
         return u, attn.view(-1, hidden_dim * num_heads), k, v
     u, q, k, v = hstu_compute_uqvk(
         x=x, norm_weight=norm_weight, norm_bias=norm_bias, norm_eps=norm_eps, num_heads=num_heads,

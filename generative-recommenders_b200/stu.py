@@ -51,8 +51,27 @@ class STULayerConfig:
 _BUCKETS = {}  # (n, buckets, device) -> bucket index of every distance: the same for all layers and steps
 
 
+class _BucketGather(torch.autograd.Function):
+    """``table[bucket]`` in fp32 whose backward is one ``index_add_`` (a single kernel of atomic
+    adds) instead of the sort-based scatter autograd uses for a general index."""
+
+    @staticmethod
+    def forward(ctx, table, bucket):
+        ctx.save_for_backward(bucket)
+        ctx.shape, ctx.dtype = table.shape, table.dtype
+        return table.detach().to(torch.float32)[bucket].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        (bucket,) = ctx.saved_tensors
+        d = torch.zeros(ctx.shape, dtype=torch.float32, device=g.device)
+        d.index_add_(0, bucket, g.to(torch.float32))
+        return d.to(ctx.dtype), None
+
+
 def position_bias_by_distance(table: torch.Tensor, n: int) -> torch.Tensor:
-    """``bias[dist] = table[bucket(dist)]`` for ``dist`` in ``[0, n)`` (fp32)."""
+    """``bias[dist] = table[bucket(dist)]`` for ``dist`` in ``[0, n)`` (fp32); differentiable with
+    respect to ``table``."""
     nb = table.numel() - 1
     key = (n, nb, table.device)
     bucket = _BUCKETS.get(key)
@@ -62,7 +81,7 @@ def position_bias_by_distance(table: torch.Tensor, n: int) -> torch.Tensor:
         if len(_BUCKETS) > 64:
             _BUCKETS.clear()
         _BUCKETS[key] = bucket
-    return table.to(torch.float32)[bucket].contiguous()
+    return _BucketGather.apply(table, bucket)
 
 
 class STULayer(torch.nn.Module):
@@ -82,6 +101,9 @@ class STULayer(torch.nn.Module):
         self._use_group_norm = config.use_group_norm
         self._sort_by_length = config.sort_by_length
         self._contextual_seq_len = config.contextual_seq_len
+        self._recompute_normed_x = config.recompute_normed_x
+        self._recompute_uvqk = config.recompute_uvqk
+        self._recompute_y = config.recompute_y
         H, dv, dqk, D = self._num_heads, self._hidden_dim, self._attention_dim, self._embedding_dim
         self._uvqk_weight = torch.nn.Parameter(torch.empty((D, (dv * 2 + dqk * 2) * H)))
         torch.nn.init.xavier_uniform_(self._uvqk_weight)
@@ -244,8 +266,8 @@ class STULayer(torch.nn.Module):
                 num_targets=num_targets if self._target_aware else None,
                 max_attn_len=self._max_attn_len,
                 contextual_seq_len=self._contextual_seq_len,
-                recompute_uvqk_in_backward=False,
-                recompute_normed_x_in_backward=False,
+                recompute_uvqk_in_backward=self._recompute_uvqk,
+                recompute_normed_x_in_backward=self._recompute_normed_x,
                 sort_by_length=self._sort_by_length,
                 kernel=self._hammer_kernel,
                 bias_by_distance=bias,
@@ -270,7 +292,7 @@ class STULayer(torch.nn.Module):
                 mul_u_activation_type="none",
                 training=self.training,
                 kernel=self._hammer_kernel,
-                recompute_y_in_backward=False,
+                recompute_y_in_backward=self._recompute_y,
             )
 
 

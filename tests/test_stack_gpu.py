@@ -197,3 +197,43 @@ def test_target_invariance(dtype):
     tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(y1[perm], y0, **tol)
     torch.testing.assert_close(dx1[perm], dx0, **tol)
+
+
+def test_recompute_flags_change_memory_not_results():
+    """``recompute_uvqk`` / ``recompute_y`` (the reference's STULayerConfig fields, modules/stu.py:77-79)
+    drop the two widest activations of a layer - the [L, 4 H d] projection and the [L, 3 H d] input
+    of the output linear - and rebuild them in the backward with the same kernels: every result
+    carries the same bits, dropout included (the mask is regenerated from the same seed), and the
+    memory held between forward and backward shrinks."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    D, H, d = 512, 4, 128
+    g = torch.Generator().manual_seed(9)
+    lengths = torch.randint(200, 900, (12,), generator=g)
+    nt = torch.randint(1, 30, (12,), generator=g)
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    x = torch.randn(L, D, generator=g).bfloat16().to(DEV)
+    dy = torch.randn(L, D, generator=g).bfloat16().to(DEV)
+    res, held = {}, {}
+    for rec in (False, True):
+        cfg = G.STULayerConfig(embedding_dim=D, num_heads=H, hidden_dim=d, attention_dim=d, output_dropout_ratio=0.3,
+                               contextual_seq_len=3, recompute_normed_x=rec, recompute_uvqk=rec, recompute_y=rec)
+        torch.manual_seed(1)
+        stack = G.STUStack([G.STULayer(cfg) for _ in range(2)]).to(DEV).to(torch.bfloat16)
+        stack.train(True)
+        xin = x.clone().requires_grad_(True)
+        torch.manual_seed(77)        # the dropout seeds come from torch's generator
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        y = stack(xin, lengths.to(DEV), offs.to(DEV), 1024, nt.to(DEV))
+        torch.cuda.synchronize()
+        held[rec] = torch.cuda.memory_allocated() - base
+        y.backward(dy)
+        torch.cuda.synchronize()
+        res[rec] = [y.detach(), xin.grad] + [p_.grad for p_ in stack.parameters()]
+    for a, b in zip(res[False], res[True]):
+        assert torch.equal(a, b)
+    assert float((res[True][0] == res[False][0]).float().mean()) == 1.0
+    # per layer the projection (2048 columns) and the concat (1536) go, of ~7 D columns kept otherwise
+    assert held[True] < 0.7 * held[False], held
