@@ -445,6 +445,8 @@ def run_ours(args):
         del dev_in, res_host, flush, ev
         torch.cuda.empty_cache()
         if world == 1:
+            blocks["reference_gpu"] = block_reference_gpu(dev, w, args)
+            torch.cuda.empty_cache()
             blocks["config3"] = block_config3(dev, peaks, args)
             blocks["stages"] = block_stages(dev, peaks, args)
         blocks["config4"] = block_config4(world, rank, dev, dist, args)
@@ -698,6 +700,76 @@ def block_config3(dev, peaks, args):
     res["bf16"]["peak"] = "measured cuBLAS bf16 burst"
     res["fp8"]["peak"] = "2 x the measured bf16 burst (no fp8 GEMM was measured on this pool)"
     res["fp8"]["rel_l2_vs_bf16_kernel"] = round(err, 5)
+    return res
+
+
+def block_reference_gpu(dev, w, args):
+    """The reference's own GPU paths on the same batch, same GPU, same run (files placed under
+    ``oracle/_ref`` by ``oracle/make_ref.py``; nothing of this library is on their path): its PyTorch
+    implementation (``pytorch_hstu_mha``, which pads to ``[B, H, N, N]``) forward and forward +
+    backward, and the forward of its Triton kernel (``triton_hstu_mha``, autotuned by Triton itself).
+    The Triton backward is left out: its sequence-parallel configurations wait on a lock in device
+    memory without a bound (ops/triton/triton_attention_utils.py:42-48)."""
+    ref_root = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "generative_recommenders")):
+        return {"unavailable": "oracle/_ref holds no copy of the reference (python oracle/make_ref.py --reference ...)"}
+    res = {"workload": "the run's configs[1] batch, bf16"}
+    q, k, v, do = (t.to(dev) for t in w.qkv(with_dout=True))
+    offs = w.seq_offsets.to(dev)
+    nt = None if w.num_targets is None else w.num_targets.to(dev)
+    flops = w.causal_flops_fwd()
+    try:
+        from oracle import reference_shims
+
+        reference_shims.install()
+        if ref_root not in sys.path:
+            sys.path.insert(0, ref_root)
+        from generative_recommenders.ops.pytorch.pt_hstu_attention import pytorch_hstu_mha
+
+        def pt_fwd():
+            with torch.no_grad():
+                return pytorch_hstu_mha(w.max_seq_len, w.alpha, q, k, v, offs, num_targets=nt,
+                                        max_attn_len=w.max_attn_len, contextual_seq_len=w.contextual_seq_len)
+
+        def pt_step():
+            qd, kd, vd = (t.detach().requires_grad_(True) for t in (q, k, v))
+            out = pytorch_hstu_mha(w.max_seq_len, w.alpha, qd, kd, vd, offs, num_targets=nt,
+                                   max_attn_len=w.max_attn_len, contextual_seq_len=w.contextual_seq_len)
+            out.backward(do)
+
+        ms_f, ms_s = _median_ms(pt_fwd, 5), _median_ms(pt_step, 5)
+        res["pytorch_gpu"] = {"fwd_ms": round(ms_f, 4), "fwd_bwd_ms": round(ms_s, 4),
+                              "fwd_tflops": round(flops / (ms_f * 1e-3) / 1e12, 2),
+                              "fwd_bwd_tflops": round(3.5 * flops / (ms_s * 1e-3) / 1e12, 2)}
+    except Exception as ex:  # pragma: no cover
+        res["pytorch_gpu"] = {"unavailable": "%s: %s" % (type(ex).__name__, str(ex)[:200])}
+    torch.cuda.empty_cache()
+    if os.environ.get("B200_HSTU_SKIP_REFERENCE_TRITON"):
+        res["triton_fwd"] = {"unavailable": "skipped on request (B200_HSTU_SKIP_REFERENCE_TRITON)"}
+        return res
+    try:
+        from generative_recommenders.ops.triton.triton_hstu_attention import triton_hstu_mha
+
+        def tr_fwd():
+            with torch.no_grad():
+                return triton_hstu_mha(w.max_seq_len, w.alpha, q, k, v, offs, num_targets=nt, max_attn_len=w.max_attn_len,
+                                       contextual_seq_len=w.contextual_seq_len, sort_by_length=True)
+
+        t0 = time.perf_counter()
+        out = tr_fwd()            # autotuning happens here
+        torch.cuda.synchronize()
+        tune_s = time.perf_counter() - t0
+        ms = _median_ms(tr_fwd, 20)
+        import generative_recommenders_b200 as G
+
+        with torch.no_grad():
+            ours = G.hstu_mha(w.max_seq_len, w.alpha, q, k, v, offs, num_targets=nt, max_attn_len=w.max_attn_len,
+                              contextual_seq_len=w.contextual_seq_len)
+        err = float((out.float() - ours.float()).norm() / ours.float().norm())
+        res["triton_fwd"] = {"ms": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 2),
+                             "autotune_s": round(tune_s, 1), "rel_l2_vs_this_library": round(err, 5)}
+    except Exception as ex:  # pragma: no cover
+        res["triton_fwd"] = {"unavailable": "%s: %s" % (type(ex).__name__, str(ex)[:200])}
     return res
 
 
