@@ -220,7 +220,7 @@ def run_ours(args):
     run()
     torch.cuda.synchronize()
     est_ms = max(1e-3, (time.perf_counter() - t0) * 1e3)
-    rounds = int(max(1, min(400, -(-500.0 // (args.steps * est_ms)))))
+    rounds = int(max(1, min(400, -(-500.0 // (args.steps * est_ms))))) if args.rounds <= 0 else args.rounds
     if dist is not None:   # every rank times the same number of steps
         r_ = torch.tensor([rounds], device=dev)
         dist.all_reduce(r_, op=dist.ReduceOp.MAX)
@@ -1255,6 +1255,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (stack workloads)")
     ap.add_argument("--fwd-only", action="store_true", help="time the forward alone (inference)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of replaying a CUDA graph of the step")
+    ap.add_argument("--rounds", type=int, default=0,
+                    help="rounds of --steps timed steps (default: as many as fill half a second; profiling runs pass 1)")
     ap.add_argument("--blocks", default="all", choices=["all", "none"],
                     help="none: leave out the configs[3] / stage-kernel / configs[4] records (profiling runs)")
     args = ap.parse_args()
