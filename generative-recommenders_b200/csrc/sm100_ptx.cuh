@@ -133,7 +133,7 @@ __device__ __forceinline__ bool sched_fetch(const WaitCtx &wc, const uint8_t *ri
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-// 2-D tiled load global -> shared, completion on an mbarrier (no multicast)
+// 2-D tiled load global -> shared of this CTA, completion on an mbarrier
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *m, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
