@@ -150,7 +150,8 @@ __host__ __device__ __forceinline__ FullRange full_tile_range(const TileItem &it
 }
 
 // q tiles that the kv tile `kt` of a sequence has to visit (backward, kv-stationary): a
-// conservative contiguous range [t_lo, t_hi) plus, when contextual rows exist, tile 0.
+// conservative contiguous range [t_lo, t_hi) plus, when contextual rows exist and fit one tile,
+// tile 0.
 __host__ __device__ __forceinline__ void fill_kv_item(TileItem &it, const AttnGeomParams &g, int b, int kt, int start,
                                                       int len, int nt) {
   fill_common(it, g, b, kt, start, len, nt);
@@ -185,7 +186,16 @@ __host__ __device__ __forceinline__ void fill_kv_item(TileItem &it, const AttnGe
       if (t_hi < kt + 1) t_hi = kt + 1;
       if (t_hi > ntiles) t_hi = ntiles;
     }
-    if (g.c > 0 && kt > 0 && n0 < it.u) it.extra_tile = 0;  // contextual rows see every non-target column
+    if (g.c > 0 && n0 < it.u) {
+      // contextual rows see every non-target column.  They sit in query tile 0 when the prefix
+      // fits one tile; a longer prefix occupies several tiles, and the walk then starts at the
+      // first tile (the element-wise mask clears the rows in between)
+      if (g.c <= TILE) {
+        if (kt > 0) it.extra_tile = 0;
+      } else {
+        t_lo = 0;
+      }
+    }
   }
   it.t_lo = t_lo;
   it.n_main = t_hi - t_lo;

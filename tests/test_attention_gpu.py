@@ -119,6 +119,11 @@ CASES = [
     (4, 1, 260, 270, 3, 64, 9, 3, 0, 0),
     (4, 120, 300, 310, 2, 64, 0, 0, 64, 0),
     (4, 120, 300, 320, 2, 128, 10, 4, 70, 33),
+    # contextual prefix longer than one 128-row tile (its rows sit in several query tiles), alone,
+    # with targets, and with a window / full-attention tail
+    (4, 150, 500, 640, 2, 128, 0, 130, 0, 0),
+    (4, 150, 500, 700, 1, 128, 25, 260, 100, 0),
+    (3, 100, 400, 600, 2, 64, 12, 130, 16, 40),
 ]
 
 

@@ -118,10 +118,11 @@ def test_backward_tile_rule_never_drops_a_valid_pair():
     rng = random.Random(99)
     T = 128
     skipped = 0
-    for _ in range(150):
+    for _ in range(220):
         N = 700
         L = rng.randint(1, N)
-        c = rng.choice([0, 0, 2, 7])
+        # contextual prefixes inside one tile, ending on a tile boundary and spanning several tiles
+        c = rng.choice([0, 0, 2, 7, 127, 128, 130, 260, 400])
         t = rng.randint(0, max(0, min(L - 1, 150)))
         W = rng.choice([0, 0, 3, 100, 130, 300])
         F = rng.choice([0, 0, 40]) if W > 0 else 0
