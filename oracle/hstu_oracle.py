@@ -34,15 +34,21 @@ def valid_attn_mask(
     contextual_seq_len: int = 0,
     min_full_attn_seq_len: int = 0,
     device: Optional[torch.device] = None,
+    seq_len: Optional[int] = None,
 ) -> torch.Tensor:
     """Boolean ``[L, L]`` mask of one sequence of length ``L``.
 
     Follows generative_recommenders/ops/pytorch/pt_hstu_attention.py:33-84
     (``_get_valid_attn_mask`` with ``causal=True``), restricted to the ``[L, L]``
     corner that survives ``dense_to_jagged`` (pt_hstu_attention.py:183-187).
+
+    ``seq_len`` is the length the reference derives ``max_ids`` from: the difference of
+    the sequence's offsets (pt_hstu_attention.py:44,170-172), which for a sequence longer
+    than ``max_seq_len`` is larger than the ``L`` rows that ``jagged_to_padded_dense``
+    keeps.  Defaults to ``L``.
     """
     ids = torch.arange(L, device=device, dtype=torch.int64)
-    max_id = L
+    max_id = L if seq_len is None else seq_len
     if contextual_seq_len > 0:  # :45-48
         ids = torch.clamp(ids - contextual_seq_len + 1, min=0)
         max_id = max_id - contextual_seq_len + 1
@@ -169,6 +175,7 @@ def hstu_mha(
             contextual_seq_len=contextual_seq_len,
             min_full_attn_seq_len=min_full_attn_seq_len,
             device=q.device,
+            seq_len=e - s,
         )
         p = p * mask.unsqueeze(0)
         ob = torch.einsum("hxy,hyv->hxv", p, vb).transpose(0, 1)  # [L, H, V]

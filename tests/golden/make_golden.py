@@ -64,6 +64,20 @@ def attention_cases():
     # truncation: sequences longer than max_seq_len
     cases.append(("truncate", dict(seed=901, B=4, lo=20, hi=60, N=40, H=2, A=16, V=16, std=1.0,
                                    targets=0, ctx=0, W=0, F=0, alpha=0.25, grads=False)))
+    # truncation together with what depends on the sequence length: the reference takes max_ids from
+    # the untruncated lengths (pt_hstu_attention.py:44), so targets, the contextual prefix and the
+    # full-attention tail of a truncated sequence refer to positions beyond max_seq_len
+    trunc = dict(B=6, lo=20, hi=60, N=40, H=2, A=16, V=16, std=1.0, alpha=0.25, grads=True)
+    for i, (nm, v) in enumerate([
+        ("truncate_targets", dict(targets=7, ctx=0, W=0, F=0)),
+        ("truncate_all", dict(targets=7, ctx=3, W=9, F=5)),
+        ("truncate_window_full", dict(targets=0, ctx=0, W=6, F=9)),
+        ("truncate_ctx_window", dict(targets=0, ctx=4, W=8, F=0)),
+    ]):
+        d = dict(trunc)
+        d.update(v)
+        d["seed"] = 902 + i
+        cases.append((nm, d))
     return cases
 
 
@@ -75,10 +89,11 @@ def make_attention(ref_ops, name, p):
         num_targets = torch.randint(1, p["targets"] + 1, (p["B"],), generator=g)
         # history + contextual must stay non-empty: lengths are history + ctx + targets
         lengths = lengths + num_targets + p["ctx"]
-        lengths = torch.clamp(lengths, max=p["N"]) if name != "truncate" else lengths
+        lengths = torch.clamp(lengths, max=p["N"]) if not name.startswith("truncate") else lengths
         num_targets = torch.minimum(num_targets, torch.clamp(lengths - p["ctx"] - 1, min=0))
     elif p["ctx"] > 0:
-        lengths = torch.clamp(lengths + p["ctx"], max=p["N"])
+        lengths = lengths + p["ctx"]
+        lengths = torch.clamp(lengths, max=p["N"]) if not name.startswith("truncate") else lengths
     offsets = _offsets(lengths)
     L = int(offsets[-1])
     q = (torch.randn(L, p["H"], p["A"], generator=g) * p["std"]).requires_grad_(True)
@@ -102,7 +117,9 @@ def make_masks(ref_ops):
     """Reference masks for a grid of (L, targets, ctx, W, F), stored as uint8 [L, L]."""
     out = []
     N = 24
-    for L, t, c, W, Fm in itertools.product([1, 2, 7, 13, 24], [None, 0, 1, 4], [0, 1, 3], [0, 1, 5], [0, 2, 6]):
+    # lengths 29 and 41 exceed N: the sequence is truncated to N rows while max_ids keeps the full length
+    for L, t, c, W, Fm in itertools.product([1, 2, 7, 13, 24, 29, 41], [None, 0, 1, 4], [0, 1, 3], [0, 1, 5],
+                                            [0, 2, 6]):
         if W == 0 and Fm > 0:
             continue
         tt = 0 if t is None else t
@@ -114,7 +131,8 @@ def make_masks(ref_ops):
             num_targets=None if t is None else torch.tensor([t]),
             max_attn_len=W, contextual_seq_len=c, min_full_attn_seq_len=Fm,
         )
-        out.append(dict(L=L, t=t, c=c, W=W, F=Fm, mask=m.expand(1, N, N)[0, :L, :L].to(torch.uint8).clone()))
+        Lt = min(L, N)
+        out.append(dict(L=L, t=t, c=c, W=W, F=Fm, mask=m.expand(1, N, N)[0, :Lt, :Lt].to(torch.uint8).clone()))
     return out
 
 

@@ -72,8 +72,9 @@ def test_host_mask_matches_reference_masks(golden):
         else:
             t = c["t"]
         L = c["L"]
-        got = torch.tensor([[lib.b200_hstu_host_mask(L, t, 24, c["c"], c["W"], c["F"], i, j) for j in range(L)]
-                            for i in range(L)], dtype=torch.uint8).view(L, L)
+        Lt = c["mask"].shape[0]      # min(L, 24)
+        got = torch.tensor([[lib.b200_hstu_host_mask(L, t, 24, c["c"], c["W"], c["F"], i, j) for j in range(Lt)]
+                            for i in range(Lt)], dtype=torch.uint8).view(Lt, Lt)
         assert torch.equal(got, c["mask"]), c
 
 
@@ -96,9 +97,7 @@ def test_block_skipping_rule_never_drops_a_valid_pair(T):
         W = rng.choice([0, 0, 1, 5, 17, 60])
         F = rng.choice([0, 0, 4]) if W > 0 else 0
         Lt = min(L, N)
-        mask = O.valid_attn_mask(Lt, t, True, W, c, F)
-        if L > N:  # truncated sequences keep max_id from the full length
-            continue
+        mask = O.valid_attn_mask(Lt, t, True, W, c, F, seq_len=L)  # truncated: max_id from the full length
         for m0 in range(0, Lt, T):
             lo, hi, dg = _range(lib, L, t, N, c, W, F, m0, T)
             rows = mask[m0:m0 + T]

@@ -13,8 +13,10 @@ def test_masks_match_reference(golden):
     cases = golden("masks.pt")
     assert len(cases) > 300
     for c in cases:
-        m = O.valid_attn_mask(c["L"], num_targets=c["t"] or 0, has_targets=c["t"] is not None,
-                              max_attn_len=c["W"], contextual_seq_len=c["c"], min_full_attn_seq_len=c["F"])
+        rows = c["mask"].shape[0]    # min(L, 24): sequences longer than the padded length are truncated
+        m = O.valid_attn_mask(rows, num_targets=c["t"] or 0, has_targets=c["t"] is not None,
+                              max_attn_len=c["W"], contextual_seq_len=c["c"], min_full_attn_seq_len=c["F"],
+                              seq_len=c["L"])
         assert torch.equal(m.to(torch.uint8), c["mask"]), c
 
 

@@ -1,0 +1,241 @@
+"""Seeded random sweep of the attention entry points against the oracle run on the device in fp32.
+
+The parameters are drawn from pools that sit on the edges of the kernels' tiling: lengths, windows,
+contextual prefixes and target counts of one less than, equal to and one more than the 128-row
+tile (and two tiles), prefixes longer than the padded length, sequences longer than
+``max_seq_len`` (truncated by the reference, with ``max_ids`` still taken from the full length),
+empty sequences, sequences outside the regular domain (history shorter than the contextual
+prefix), bias tables shorter than the sequences, both kernel families.  Each case checks the
+output and every gradient globally and per sequence.  About 1700 small cases run in half a minute;
+the same generator with a time budget instead of a count found the two defects that the
+hand-written cases had missed (a contextual prefix spanning several tiles in the K/V-stationary
+backward; truncated sequences with targets in the oracle)."""
+
+import random
+
+import pytest
+import torch
+
+import generative_recommenders_b200 as G
+from generative_recommenders_b200 import workloads as W
+from oracle import hstu_oracle as O
+import parity_metrics as PM
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rel(a, r):
+    a = a.detach().float()
+    r = r.detach().float()
+    assert torch.isfinite(a).all()
+    den = float(r.norm())
+    return float((a - r).norm()) / den if den > 0 else float(a.norm())
+
+
+def _attention_case(rng):
+    seed = rng.randrange(10 ** 9)
+    g = torch.Generator().manual_seed(seed)
+    dtype = rng.choice([torch.bfloat16, torch.bfloat16, torch.float16, torch.float32])
+    dim = rng.choice([128, 128, 64, 32] if dtype != torch.float32 else [128, 64, 32])
+    heads = rng.choice([1, 2, 3, 4])
+    max_len = rng.choice([64, 128, 129, 255, 256, 257, 384, 500, 640, 1024])
+    if dtype == torch.float32 or dim < 64:
+        max_len = min(max_len, 400)
+    batch = rng.randint(1, 8)
+    ctx = rng.choice([0, 0, 1, 5, 127, 128, 130, 256, 300])
+    window = rng.choice([0, 0, 1, 16, 127, 128, 129, 255, 256, 1000])
+    full_tail = rng.choice([0, 0, 1, 64, 200]) if window else 0
+    has_targets = rng.random() < 0.6
+    tmax = rng.choice([1, 12, 130, 300])
+    with_bias = rng.random() < 0.3
+    irregular = rng.random() < 0.2
+    over = 40 if rng.random() < 0.15 else 0         # sequences longer than max_seq_len
+    impl = rng.choice(["auto", "auto", "tcgen05", "simt"])
+    if impl == "tcgen05" and (dtype == torch.float32 or dim < 64):
+        impl = "auto"
+    if impl == "simt" and max_len > 640:
+        impl = "auto"
+    lengths = torch.randint(0 if irregular else 1, max_len + 1 + over, (batch,), generator=g)
+    nt = None
+    if has_targets:
+        nt = torch.randint(1, tmax + 1, (batch,), generator=g)
+        if irregular:
+            nt = torch.minimum(nt, lengths)
+        else:
+            lengths = torch.clamp(lengths + nt + ctx, max=max_len + over)
+            lengths = torch.clamp(lengths, min=min(ctx + 2, max_len))
+            nt = torch.minimum(nt, torch.clamp(lengths - ctx - 1, min=0))
+    elif not irregular and ctx > 0:
+        lengths = torch.clamp(lengths, min=min(ctx + 1, max_len))
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    if L == 0:
+        return None
+    std = rng.choice([0.5, 0.8, 1.0])
+    q, k, v, dout = ((torch.randn(L, heads, dim, generator=g) * std).to(dtype) for _ in range(4))
+    scale = None
+    pick = rng.random()
+    if pick < 0.2:
+        scale = torch.tensor(0.013)
+    elif pick < 0.3 and impl != "tcgen05":           # per-token scale: CUDA-core backward
+        scale = torch.rand(L, generator=g) * 0.02 + 0.001
+    bias = None
+    if with_bias:
+        bias = torch.randn(rng.choice([max_len, max(1, max_len // 3)]), generator=g) * 0.3
+    regular = bool(((lengths - (0 if nt is None else nt)) >= ctx + 1).all()) and bool((lengths <= max_len).all())
+    name = dict(seed=seed, dtype=str(dtype), dim=dim, heads=heads, max_len=max_len, ctx=ctx, window=window,
+                full_tail=full_tail, impl=impl, bias=None if bias is None else bias.numel(),
+                lengths=lengths.tolist(), targets=None if nt is None else nt.tolist(),
+                scale=None if scale is None else scale.numel())
+
+    G.set_attention_impl(impl)
+    alpha = 1.0 / dim ** 0.5
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    bd = None if bias is None else bias.to(DEV).requires_grad_(True)
+    offs_d = offs.to(DEV)
+    nt_d = None if nt is None else nt.to(DEV)
+    sc_d = None if scale is None else scale.to(DEV)
+    out = G.hstu_mha(max_len, alpha, qd, kd, vd, offs_d, num_targets=nt_d, max_attn_len=window,
+                     contextual_seq_len=ctx, min_full_attn_seq_len=full_tail, attn_scale=sc_d, bias_by_distance=bd)
+    out.backward(dout.to(DEV))
+
+    q32, k32, v32 = (t.float().to(DEV).requires_grad_(True) for t in (q, k, v))
+    rb = b32 = None
+    if bias is not None:
+        b32 = bias.to(DEV).clone().requires_grad_(True)
+        i = torch.arange(max_len, device=DEV).view(-1, 1)
+        j = torch.arange(max_len, device=DEV).view(1, -1)
+        d = (i - j).abs()
+        rb = torch.where(d < bias.numel(), b32[d.clamp(max=bias.numel() - 1)], torch.zeros((), device=DEV))
+    ref = O.hstu_mha(max_len, alpha, q32, k32, v32, offs_d, num_targets=nt_d, max_attn_len=window,
+                     contextual_seq_len=ctx, min_full_attn_seq_len=full_tail, attn_scale=sc_d, rel_bias=rb)
+    ref.backward(dout.float().to(DEV))
+
+    tol = PM.F32_TOL if dtype == torch.float32 else PM.HALF_TOL
+    worst = {}
+    for nm, a, r in (("out", out, ref), ("dq", qd.grad, q32.grad), ("dk", kd.grad, k32.grad),
+                     ("dv", vd.grad, v32.grad)):
+        e = _rel(a, r)
+        ps = O.per_sequence_rel_l2(a, r, offs)
+        worst[nm] = max(e, ps)
+        assert e <= tol, (nm, e, name)
+        assert ps <= 1.5 * tol, (nm, "per sequence", ps, name)
+    if bias is not None:
+        assert torch.isfinite(bd.grad).all(), name
+        if regular and L >= 64:
+            # a table entry sums signed terms over every pair at its distance; on the degenerate
+            # sequences only a handful of pairs remain and the sum can cancel to nothing
+            e = _rel(bd.grad, b32.grad)
+            worst["dbias"] = e
+            assert e <= 2.5 * tol, ("dbias", e, name)
+    return worst
+
+
+def test_attention_sweep():
+    rng = random.Random(20260)
+    worst = {}
+    done = 0
+    for _ in range(1200):
+        w = _attention_case(rng)
+        if w is None:
+            continue
+        done += 1
+        for k_, v_ in w.items():
+            worst[k_] = max(worst.get(k_, 0.0), v_)
+    G.set_attention_impl("auto")
+    PM._note(("sweep", "attention", done), worst)
+    assert done > 1100
+
+
+def test_cached_attention_sweep():
+    rng = random.Random(20261)
+    worst = 0.0
+    done = 0
+    for _ in range(400):
+        seed = rng.randrange(10 ** 9)
+        g = torch.Generator().manual_seed(seed)
+        dtype = rng.choice([torch.bfloat16, torch.float16, torch.float32])
+        d = rng.choice([128, 64]) if dtype != torch.float32 else rng.choice([32, 64])
+        H = rng.choice([1, 2, 4])
+        delta = rng.choice([1, 5, 64, 127, 128, 129, 200, 300])
+        ctx = rng.choice([0, 0, 3, 130])
+        window = rng.choice([0, 0, 16, 100, 128, 300])
+        N = rng.choice([400, 700, 1100])
+        if dtype == torch.float32:
+            N, delta = 400, min(delta, 129)
+        if delta + ctx + 2 > N:
+            continue
+        B = rng.randint(1, 6)
+        lengths = torch.randint(delta + ctx + 1, N + 1, (B,), generator=g)
+        offs = W._offsets(lengths)
+        L = int(offs[-1])
+        nt = torch.randint(1, delta + 1, (B,), generator=g) if rng.random() < 0.6 else None
+        impl = "auto" if dtype == torch.float32 else rng.choice(["auto", "tcgen05", "simt"])
+        G.set_attention_impl(impl)
+        k = (torch.randn(L, H, d, generator=g) * 0.7).to(dtype)
+        v = (torch.randn(L, H, d, generator=g) * 0.7).to(dtype)
+        dq = (torch.randn(B * delta, H, d, generator=g) * 0.7).to(dtype)
+        nt_d = None if nt is None else nt.to(DEV)
+        out = G.delta_hstu_mha(N, 1.0 / d, dq.to(DEV), k.to(DEV), v.to(DEV), offs.to(DEV), num_targets=nt_d,
+                               max_attn_len=window, contextual_seq_len=ctx)
+        ref = O.delta_hstu_mha(N, 1.0 / d, dq.float().to(DEV), k.float().to(DEV), v.float().to(DEV), offs.to(DEV),
+                               nt_d, window, ctx)
+        name = dict(seed=seed, dtype=str(dtype), d=d, H=H, delta=delta, ctx=ctx, window=window, N=N, impl=impl,
+                    lengths=lengths.tolist(), targets=None if nt is None else nt.tolist())
+        tol = PM.F32_TOL if dtype == torch.float32 else PM.HALF_TOL
+        e = _rel(out, ref)
+        ps = O.per_sequence_rel_l2(out, ref, delta * torch.arange(B + 1))
+        assert e <= tol and ps <= 1.5 * tol, (e, ps, name)
+        worst = max(worst, e, ps)
+        done += 1
+    G.set_attention_impl("auto")
+    PM._note(("sweep", "cached_attention", done), {"out": worst})
+    assert done > 300
+
+
+def test_fp8_sweep():
+    """The e4m3 forward against the oracle on the de-quantised tensors (the arithmetic of the kernel
+    itself; the error of the quantisation against unquantised inputs is a property of the format
+    and is bounded on full-size inputs elsewhere)."""
+    rng = random.Random(20262)
+    worst = 0.0
+    for _ in range(150):
+        seed = rng.randrange(10 ** 9)
+        g = torch.Generator().manual_seed(seed)
+        B = rng.randint(1, 6)
+        N = rng.choice([256, 1024, 2048])
+        H = rng.choice([1, 2, 4])
+        ctx = rng.choice([0, 0, 3, 130])
+        window = rng.choice([0, 0, 16, 100, 128, 300, 1024])
+        lengths = torch.randint(1, N + 1, (B,), generator=g)
+        nt = None
+        if rng.random() < 0.6:
+            nt = torch.randint(1, rng.choice([2, 30, 257]), (B,), generator=g)
+            lengths = torch.clamp(lengths + nt + ctx, max=N)
+            lengths = torch.clamp(lengths, min=min(ctx + 2, N))
+            nt = torch.minimum(nt, torch.clamp(lengths - ctx - 1, min=0))
+        elif ctx:
+            lengths = torch.clamp(lengths, min=ctx + 1)
+        offs = W._offsets(lengths)
+        L = int(offs[-1])
+        q, k, v = (torch.randn(L, H, 128, generator=g) for _ in range(3))
+        offs_d = offs.to(DEV)
+        nt_d = None if nt is None else nt.to(DEV)
+        q8, qs, bo = G.quantize_e4m3_block(q.to(DEV), offs_d)
+        k8, ks, _ = G.quantize_e4m3_block(k.to(DEV), offs_d)
+        v8, vs, _ = G.quantize_e4m3_block(v.to(DEV), offs_d)
+        out = G.hstu_mha_fp8(N, 1.0 / 128, q8, k8, v8, qs, ks, vs, bo, offs_d, num_targets=nt_d,
+                             max_attn_len=window, contextual_seq_len=ctx)
+        nblk = int(bo[-1])
+        deq = [O.dequantize_e4m3_block(t8.cpu(), s[:nblk].cpu(), bo.cpu().long(), offs).to(DEV)
+               for t8, s in ((q8, qs), (k8, ks), (v8, vs))]
+        ref = O.hstu_mha(N, 1.0 / 128, deq[0], deq[1], deq[2], offs_d, num_targets=nt_d, max_attn_len=window,
+                         contextual_seq_len=ctx)
+        name = dict(seed=seed, N=N, H=H, ctx=ctx, window=window, lengths=lengths.tolist(),
+                    targets=None if nt is None else nt.tolist())
+        e = _rel(out, ref)
+        ps = O.per_sequence_rel_l2(out, ref, offs)
+        assert e <= PM.HALF_TOL and ps <= 2 * PM.HALF_TOL, (e, ps, name)
+        worst = max(worst, e, ps)
+    PM._note(("sweep", "fp8"), {"vs_dequantised": worst})
