@@ -61,15 +61,34 @@ def _fused_uqvk_supported(x, uvqk_weight, hv) -> bool:
 # Inference only: the workspace of the fused kernel holds what the preparation launches derive from
 # the four parameter tensors (W' = diag(gamma) W and two column vectors).  While those tensors are
 # alive and unmodified (same objects, same storage, same version counters) the workspace is kept
-# and the preparation is skipped.
+# and the preparation is skipped.  The version counter sees optimizer steps, load_state_dict and
+# every other in-place operation on the parameter itself; it does NOT see a write through
+# ``param.data`` (``param.data.copy_(new)``), which shares the storage but not the counter.  Code
+# that refreshes weights that way calls ``clear_prepared_weights()`` afterwards, or switches the
+# cache off with ``set_prepared_weights_cache(False)``.
 _PREPARED = {}
+_PREPARED_ON = True
+
+
+def clear_prepared_weights() -> None:
+    """Forget every cached preparation of the fused uvqk stage (see the comment above)."""
+    _PREPARED.clear()
+
+
+def set_prepared_weights_cache(on: bool) -> None:
+    """Keep (default) or never keep the derived weights of the fused uvqk stage between
+    inference calls."""
+    global _PREPARED_ON
+    _PREPARED_ON = bool(on)
+    if not on:
+        _PREPARED.clear()
 
 
 def _prepared_workspace(nw, nb, w, b, nbytes, device, allow_cache):
     # Only module parameters are worth remembering, and only when all four tensors are the
     # parameters themselves: a cast copy made for one call never comes back, and its id / address /
     # version can recur on a later, different copy.
-    if (not allow_cache or torch.cuda.is_current_stream_capturing()
+    if (not allow_cache or not _PREPARED_ON or torch.cuda.is_current_stream_capturing()
             or not all(isinstance(t, torch.nn.Parameter) for t in (w, nw, nb, b))):
         return torch.empty(nbytes, dtype=torch.uint8, device=device), False
     key = id(w)

@@ -182,6 +182,23 @@ def test_prepared_weights_are_reused_only_while_unchanged():
     G.hstu_compute_uqvk(x, nw.data, nb.data, 1e-6, 2, 64, 64, W.detach().clone(), b.data)
     G.hstu_compute_uqvk(x, nw.data, nb.data, 1e-6, 2, 64, 64, W.detach().clone(), b.data)
     assert G._cabi.launch_count() - n0 == 6
+    # a write through .data leaves the version counter alone: the documented remedy is an explicit
+    # clear (or the cache switched off), after which the new weights are in use
+    W.requires_grad_(False)
+    before = call()
+    W.data.mul_(0.5)
+    HC.clear_prepared_weights()
+    after = call()
+    assert not torch.equal(before[1], after[1])
+    ref = O.hstu_compute_uqvk(x.float().cpu(), nw.float().cpu(), nb.float().cpu(), 1e-6, 2, 64, 64,
+                              W.detach().float().cpu(), b.float().cpu())
+    assert O.rel_l2(after[1].float().cpu(), ref[1]) < 1e-2
+    HC.set_prepared_weights_cache(False)
+    n0 = G._cabi.launch_count()
+    call()
+    call()
+    assert G._cabi.launch_count() - n0 == 6
+    HC.set_prepared_weights_cache(True)
 
 
 def test_fused_uqvk_full_size_matches_separate_stages():
