@@ -190,7 +190,9 @@ class _HstuMhaFunction(torch.autograd.Function):
         q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance = ctx.saved_tensors
         max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len = ctx.params
         dout = last_dim_contiguous(dout)
-        if dout.stride(1) != dout.shape[2]:
+        # heads side by side, rows not overlapping (a gradient that autograd expanded from a reduced
+        # tensor - the backward of ``out.sum(0)`` - has row stride 0)
+        if dout.stride(1) != dout.shape[2] or dout.stride(0) < dout.shape[1] * dout.shape[2]:
             dout = dout.contiguous()
         dq = torch.empty_like(q, memory_format=torch.contiguous_format)
         dk = torch.empty_like(k, memory_format=torch.contiguous_format)

@@ -49,10 +49,17 @@ class _SiluColumnsFunction(torch.autograd.Function):
         return dx, None
 
 
+def _aligned16(t: torch.Tensor) -> torch.Tensor:
+    """``t`` itself when its first element sits on a 16-byte boundary (what the tensor-core kernel's
+    bulk loads need), else a fresh copy - a contiguous slice of a flat parameter buffer can start
+    anywhere."""
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
 def _fused_uqvk_supported(x, uvqk_weight, hv) -> bool:
     if x.dtype not in (torch.bfloat16, torch.float16) or x.dim() != 2 or x.shape[0] == 0:
         return False
-    if x.stride(-1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+    if x.stride(-1) != 1 or x.stride(0) % 8 or x.stride(0) < x.shape[1] or x.data_ptr() % 16:
         return False
     D, N = uvqk_weight.shape
     return bool(_cabi.lib().b200_hstu_ln_linear_supported(D, N, hv, dtype_code(x)))
@@ -182,7 +189,7 @@ class _FusedUqvkFunction(torch.autograd.Function):
         hv, ha = hidden_dim * num_heads, attn_dim * num_heads
         nw = norm_weight.to(x.dtype).contiguous()
         nb = norm_bias.to(x.dtype).contiguous()
-        w = weight.to(x.dtype).contiguous()
+        w = _aligned16(weight.to(x.dtype).contiguous())
         b = bias.to(x.dtype).contiguous()
         no_grad = not (grad_mode and any(ctx.needs_input_grad))
         uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, no_grad)
@@ -226,7 +233,7 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
         hv, ha = hidden_dim * num_heads, attn_dim * num_heads
         nw = norm_weight.to(x.dtype).contiguous()
         nb = norm_bias.to(x.dtype).contiguous()
-        w = weight.to(x.dtype).contiguous()
+        w = _aligned16(weight.to(x.dtype).contiguous())
         b = bias.to(x.dtype).contiguous()
         no_grad = not (grad_mode and any(ctx.needs_input_grad))
         uvqk, u, mean, rstd = _fused_uqvk_launch(x, nw, nb, eps, w, b, hv, no_grad)
@@ -270,7 +277,8 @@ class _FusedPreprocessAttentionFunction(torch.autograd.Function):
         if dattn is None:
             d_uvqk[:, hv:].zero_()
         else:
-            if dattn.stride(-1) != 1 or dattn.stride(1) != dattn.shape[2]:
+            if (dattn.stride(-1) != 1 or dattn.stride(1) != dattn.shape[2]
+                    or dattn.stride(0) < dattn.shape[1] * dattn.shape[2]):
                 dattn = dattn.contiguous()
             v_ = uvqk[:, hv:2 * hv].view(M, H, V)
             q_ = uvqk[:, 2 * hv:2 * hv + ha].view(M, H, A)

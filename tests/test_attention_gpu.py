@@ -209,6 +209,21 @@ def test_non_contiguous_qkv_views():
     P.check("views", out.cpu(), ref, offs)
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+def test_expanded_output_gradient(impl):
+    """``out.sum(0)`` hands the backward a gradient whose rows all alias one row (row stride 0)."""
+    G.set_attention_impl(impl)
+    q, k, v, offs, nt, _ = _random_case(31, 4, 50, 300, 300, 2, 128, torch.bfloat16, std=0.7)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    out = G.hstu_mha(300, 0.09, leaves[0], leaves[1], leaves[2], offs.to(DEV))
+    w = torch.randn(2, 128, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    (out.sum(0) * w).sum().backward()      # no cast in between: the expanded gradient arrives as it is
+    dout = w.cpu().expand(q.shape[0], 2, 128).contiguous()
+    _, rgrads = _oracle(q, k, v, offs, 300, 0.09, dout=dout)
+    for g_, r, nm in zip(leaves, rgrads, ("dq", "dk", "dv")):
+        P.check(("expanded_dout", impl, nm), g_.grad.cpu(), r, offs)
+
+
 def test_attn_scale_and_truncation_fp32():
     G.set_attention_impl("simt")
     g = torch.Generator().manual_seed(8)

@@ -51,6 +51,35 @@ def test_fused_uqvk_matches_oracle(M, D, H, A, V, dtype):
         assert O.rel_l2(a.float().cpu(), r) <= 1.2 * O.rel_l2(r_.float().cpu(), r) + 1e-4, name
 
 
+def test_fused_uqvk_parameters_sliced_from_a_flat_buffer():
+    """All four parameters as contiguous slices of one flat buffer that start off the 16-byte grid
+    (flattened-parameter training setups hand such views to the ops): same results as with
+    separately allocated parameters, forward and backward."""
+    M, D, H, A, V = 300, 256, 2, 64, 64
+    x, nw, nb, W, b = (t.to(DEV) for t in _inputs(M, D, H, A, V, torch.bfloat16, seed=21))
+    flat = torch.zeros(3 + nw.numel() + 1 + nb.numel() + 3 + W.numel() + 5 + b.numel(), dtype=torch.bfloat16, device=DEV)
+    views, at = [], 3
+    for t, gap in ((nw, 1), (nb, 3), (W, 5), (b, 0)):
+        v = flat[at:at + t.numel()].view(t.shape)
+        v.copy_(t)
+        views.append(v.requires_grad_(True))
+        at += t.numel() + gap
+    assert views[2].data_ptr() % 16 != 0 and views[2].is_contiguous()
+    plain = [t.clone().requires_grad_(True) for t in (nw, nb, W, b)]
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    got = G.hstu_compute_uqvk(xa, views[0], views[1], 1e-6, H, A, V, views[2], views[3])
+    want = G.hstu_compute_uqvk(xb, plain[0], plain[1], 1e-6, H, A, V, plain[2], plain[3])
+    g = torch.Generator().manual_seed(5)
+    douts = [torch.randn(o.shape, generator=g).bfloat16().to(DEV) for o in want]
+    torch.autograd.backward(list(got), douts)
+    torch.autograd.backward(list(want), douts)
+    for a_, b_ in zip(got, want):
+        assert torch.equal(a_, b_)
+    assert torch.equal(xa.grad, xb.grad)
+    for a_, b_ in zip(views, plain):
+        assert torch.equal(a_.grad, b_.grad)
+
+
 def test_fused_uqvk_large_mean_rows():
     """Rows with |mean| >> std: the statistics use shifted sums, the epilogue subtracts mean * c1."""
     x, nw, nb, W, b = _inputs(500, 256, 2, 64, 64, torch.bfloat16, seed=9, shift=40.0)
