@@ -7,11 +7,13 @@ tile (and two tiles), prefixes longer than the padded length, sequences longer t
 empty sequences, sequences outside the regular domain (history shorter than the contextual
 prefix), bias tables shorter than the sequences, both kernel families.  Each case checks the
 output and every gradient globally and per sequence.  About 1700 small cases run in half a minute;
-the same generator with a time budget instead of a count found the two defects that the
-hand-written cases had missed (a contextual prefix spanning several tiles in the K/V-stationary
+the same generator with a time budget instead of a count (``B200_HSTU_SWEEP_SECONDS``) found the
+two defects that the hand-written cases had missed (a contextual prefix spanning several tiles in the K/V-stationary
 backward; truncated sequences with targets in the oracle)."""
 
+import os
 import random
+import time
 
 import pytest
 import torch
@@ -132,11 +134,21 @@ def _attention_case(rng):
     return worst
 
 
+def _budget():
+    """(seed, seconds): ``B200_HSTU_SWEEP_SECONDS`` turns the fixed number of cases into a time budget
+    and ``B200_HSTU_SWEEP_SEED`` picks another stream of cases - the long runs behind the numbers in
+    the module's description."""
+    return int(os.environ.get("B200_HSTU_SWEEP_SEED", "20260")), float(os.environ.get("B200_HSTU_SWEEP_SECONDS", "0"))
+
+
 def test_attention_sweep():
-    rng = random.Random(20260)
+    seed, seconds = _budget()
+    rng = random.Random(seed)
     worst = {}
-    done = 0
-    for _ in range(1200):
+    done = drawn = 0
+    t0 = time.time()
+    while (time.time() - t0 < seconds) if seconds > 0 else (drawn < 1200):
+        drawn += 1
         w = _attention_case(rng)
         if w is None:
             continue
