@@ -226,3 +226,30 @@ def test_l2_embedding_split_concat_match_reference(golden):
         p, l = O.hstu_split_l2_embeddings(c["x"], c["prefix_offsets"], c["l2_offsets"], c["ctx"])
         assert torch.equal(p, c["split_prefix"]) and torch.equal(l, c["split_l2"])
         assert torch.equal(p, c["prefix_x"]) and torch.equal(l, c["l2_x"])
+
+
+def _reference_checkout():
+    """A checkout of the reference next to this repository (or named by HSTU_REFERENCE), if any."""
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for cand in (os.environ.get("HSTU_REFERENCE"), os.path.join(os.path.dirname(root), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "generative_recommenders", "ops", "pytorch", "pt_hstu_attention.py")):
+            return cand
+    return None
+
+
+@pytest.mark.skipif(_reference_checkout() is None, reason="no checkout of the reference on this machine")
+def test_oracle_agrees_with_the_reference_on_random_inputs():
+    """Beyond the fixtures: 1500 seeded random cases of attention (forward and backward), cached
+    attention, the uvqk stage and the output stage, the unmodified reference against the oracle
+    (oracle/cross_check_reference.py, in a process of its own so that the reference package does
+    not stay imported here)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "oracle", "cross_check_reference.py"),
+                        "--reference", _reference_checkout(), "--cases", "1500"], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "mismatches 0" in r.stdout
