@@ -5,7 +5,8 @@
 TEST INFRASTRUCTURE ONLY.  The golden fixtures pin the oracle on a fixed set of inputs; this script
 draws as many more as asked for - attention forward and backward (every mask feature, targets that
 reach beyond the history, sequences longer than ``max_seq_len``, empty sequences, scalar and
-per-token scales), cached attention, the uvqk stage and all variants of the output stage - runs the
+per-token scales), cached attention, the uvqk stage, all variants of the output stage, jagged
+concat / split in every layout and the timestamp + position embeddings - runs the
 reference's own PyTorch functions on them (CPU, fp32, through ``reference_shims.py``) and compares.
 The oracle uses the same torch primitives in the same order, so the two agree to rounding (1e-5 is
 the bound; measured 1e-6 or exactly 0).  Exit status 0 = all cases agree.
@@ -128,6 +129,77 @@ def uqvk_case(rng, ops, kernel):
     return max(_max_diff(a.reshape(-1), w_.reshape(-1)) for a, w_ in zip(got, want)), ("uqvk", rows, H, A, V, D)
 
 
+def jagged_case(rng, jag):
+    g = torch.Generator().manual_seed(rng.randrange(10 ** 9))
+    B, D = rng.randint(1, 8), rng.choice([1, 5, 16])
+    kind = rng.choice(["jagged_jagged", "dense_right", "dense_left", "l2"])
+    if kind == "l2":
+        ctx = rng.choice([0, 2, 3])
+        lp = torch.randint(0, 9, (B,), generator=g)
+        l2 = torch.randint(ctx, ctx + 7, (B,), generator=g)
+        po, lo = _offsets(lp), _offsets(l2)
+        prefix_x = torch.randn(int(po[-1]), D, generator=g)
+        l2_x = torch.randn(int(lo[-1]), D, generator=g)
+        want = jag.pytorch_hstu_concat_l2_embeddings(max_prefix_len=9, prefix_x=prefix_x, prefix_offsets=po,
+                                                     max_l2_len=ctx + 7, l2_x=l2_x, l2_offsets=lo,
+                                                     contextual_seq_len=ctx)
+        wp, wl = jag.pytorch_hstu_split_l2_embeddings(max_seq_len=9 + ctx + 7, x=want, prefix_offsets=po,
+                                                      l2_offsets=lo, contextual_seq_len=ctx)
+        got = O.hstu_concat_l2_embeddings(prefix_x, po, l2_x, lo, ctx)
+        gp, gl = O.hstu_split_l2_embeddings(want, po, lo, ctx)
+        ok = torch.equal(got, want) and torch.equal(gp, wp) and torch.equal(gl, wl)
+        return (0.0 if ok else 1.0), ("jagged", kind, ctx, lp.tolist(), l2.tolist())
+    max_l, max_r = 9, 7
+    ll = torch.randint(0, max_l + 1, (B,), generator=g)
+    lr = torch.randint(0, max_r + 1, (B,), generator=g)
+    if kind == "dense_right":
+        max_r = rng.randint(1, 5)
+        lr = torch.full((B,), max_r)
+    if kind == "dense_left":
+        max_l = rng.randint(1, 5)
+        ll = torch.full((B,), max_l)
+    ol, orr = _offsets(ll), _offsets(lr)
+    left = torch.randn(int(ol[-1]), D, generator=g)
+    right = torch.randn(int(orr[-1]), D, generator=g)
+    kw = dict(max_len_left=max_l, max_len_right=max_r, offsets_left=None if kind == "dense_left" else ol,
+              offsets_right=None if kind == "dense_right" else orr)
+    want = jag.pytorch_concat_2D_jagged(values_left=left, values_right=right, **kw)
+    wl, wr = jag.pytorch_split_2D_jagged(max_seq_len=max_l + max_r, values=want, **kw)
+    got = O.concat_2D_jagged(left, right, **kw)
+    gl, gr_ = O.split_2D_jagged(want, **kw)
+    ok = torch.equal(got, want) and torch.equal(gl, wl) and torch.equal(gr_, wr)
+    return (0.0 if ok else 1.0), ("jagged", kind, ll.tolist(), lr.tolist())
+
+
+def position_case(rng, pos, kernel):
+    g = torch.Generator().manual_seed(rng.randrange(10 ** 9))
+    B, D, N = rng.randint(1, 6), rng.choice([8, 32]), 40
+    ctx = rng.choice([0, 2, 3])
+    fn = rng.choice(["sqrt", "log"])
+    targets = rng.random() < 0.7
+    interleave = targets and rng.random() < 0.3
+    nt = torch.randint(1, 4, (B,), generator=g)
+    lengths = torch.randint(2, 20, (B,), generator=g) + nt * (2 if interleave else 1) + ctx
+    if not targets:
+        # without num_targets the reference indexes the position table with negative numbers past the
+        # end of a sequence: only full-length sequences run there
+        lengths = torch.full((B,), N)
+    offsets = _offsets(lengths)
+    total = int(offsets[-1])
+    x = torch.randn(total, D, generator=g)
+    gaps = (torch.rand(total, generator=g) * 12).exp().long()
+    ts = torch.cat([torch.cumsum(gaps[int(offsets[b]):int(offsets[b + 1])], 0) + 1_700_000_000 for b in range(B)])
+    pos_w = torch.randn(N + ctx + 1, D, generator=g) * 0.3
+    ts_w = torch.randn(D + 17, D, generator=g) * 0.3
+    want = pos.add_timestamp_positional_embeddings(
+        alpha=D ** 0.5, max_seq_len=N, max_contextual_seq_len=ctx, position_embeddings_weight=pos_w,
+        timestamp_embeddings_weight=ts_w, seq_offsets=offsets, seq_lengths=lengths, seq_embeddings=x, timestamps=ts,
+        num_targets=nt if targets else None, interleave_targets=interleave, time_bucket_fn=fn, kernel=kernel)
+    got = O.add_timestamp_positional_embeddings(D ** 0.5, ctx, pos_w, ts_w, offsets, lengths, x, ts,
+                                                nt if targets else None, interleave, fn)
+    return _max_diff(got, want), ("position", fn, ctx, targets, interleave, lengths.tolist())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -139,12 +211,16 @@ def main():
     from generative_recommenders.ops import hstu_compute as ref_ops
     from generative_recommenders.ops.pytorch import pt_hstu_attention as ref_attn
     from generative_recommenders.ops.pytorch import pt_hstu_linear as ref_lin
+    from generative_recommenders.ops.pytorch import pt_jagged_tensors as ref_jag
+    from generative_recommenders.ops import position as ref_pos
 
     torch.set_num_threads(4)
     rng = random.Random(args.seed)
     kinds = [lambda: attention_case(rng, ref_attn)] * 3 + [lambda: cached_case(rng, ref_attn),
                                                            lambda: output_case(rng, ref_lin),
-                                                           lambda: uqvk_case(rng, ref_ops, HammerKernel.PYTORCH)]
+                                                           lambda: uqvk_case(rng, ref_ops, HammerKernel.PYTORCH),
+                                                           lambda: jagged_case(rng, ref_jag),
+                                                           lambda: position_case(rng, ref_pos, HammerKernel.PYTORCH)]
     worst, bad, done = {}, 0, 0
     for _ in range(args.cases):
         r = rng.choice(kinds)()
