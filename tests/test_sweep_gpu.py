@@ -1,4 +1,5 @@
-"""Seeded random sweep of the attention entry points against the oracle run on the device in fp32.
+"""Seeded random sweeps: the attention entry points against the oracle run on the device in fp32, and
+(at the end of the file) the stage kernels and whole layers against the oracle on the host.
 
 The parameters are drawn from pools that sit on the edges of the kernels' tiling: lengths, windows,
 contextual prefixes and target counts of one less than, equal to and one more than the 128-row
@@ -279,3 +280,250 @@ def test_many_short_sequences(impl):
     G.set_attention_impl("auto")
     for nm, a, r in (("out", out, ref), ("dq", qd.grad, q32.grad), ("dk", kd.grad, k32.grad), ("dv", vd.grad, v32.grad)):
         PM.check(("many_short", impl, nm), a, r, offs, seq_tol=2e-2, max_tol=2e-2)
+
+
+# ---------------------------------------------------------------------------------------
+# the stages and whole layers
+# ---------------------------------------------------------------------------------------
+def _check_all(kind, desc, errs, tol):
+    for k_, v_ in errs.items():
+        lim = tol[k_] if isinstance(tol, dict) else tol
+        assert v_ <= lim, (kind, k_, v_, lim, desc)
+    return max(errs.values()) if errs else 0.0
+
+
+def _dtype(rng):
+    return rng.choice([torch.bfloat16, torch.bfloat16, torch.float16, torch.float32])
+
+
+def _layer_norm_case(rng):
+    seed = rng.randrange(10 ** 9)
+    g = torch.Generator().manual_seed(seed)
+    dtype = _dtype(rng)
+    D = rng.choice([8, 24, 64, 100, 128, 136, 250, 256, 512, 1000, 1024])
+    rows = rng.choice([0, 1, 2, 31, 33, 100, 777, 3000])
+    x = (torch.randn(rows, D, generator=g) * rng.choice([0.1, 1.0, 5.0]) + rng.choice([0.0, 0.3, 3.0])).to(dtype)
+    w, b = torch.randn(D, generator=g).to(dtype), torch.randn(D, generator=g).to(dtype)
+    dy = torch.randn(rows, D, generator=g).to(dtype)
+    eps = rng.choice([1e-6, 1e-5])
+    if rng.random() < 0.3:   # rows of a wider buffer
+        big = torch.zeros(rows, D + 8, dtype=dtype, device=DEV)
+        big[:, :D] = x.to(DEV)
+        xd = big[:, :D].detach().requires_grad_(True)
+    else:
+        xd = x.to(DEV).requires_grad_(True)
+    wd, bd = (t.to(DEV).requires_grad_(True) for t in (w, b))
+    y = G.layer_norm(xd, wd, bd, eps)
+    y.backward(dy.to(DEV))
+    xr, wr, br = (t.float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (D,), wr, br, eps)
+    yr.backward(dy.float())
+    errs = {"y": _rel(y.cpu(), yr), "dx": _rel(xd.grad.cpu(), xr.grad)}
+    if rows > 0:
+        errs.update(dw=_rel(wd.grad.cpu(), wr.grad), db=_rel(bd.grad.cpu(), br.grad))
+    return _check_all("layer_norm", dict(seed=seed, dtype=str(dtype), D=D, rows=rows), errs,
+                      PM.F32_TOL if dtype == torch.float32 else PM.HALF_TOL)
+
+
+def _norm_mul_case(rng):
+    seed = rng.randrange(10 ** 9)
+    g = torch.Generator().manual_seed(seed)
+    dtype = _dtype(rng)
+    H, V = rng.choice([1, 2, 4, 8]), rng.choice([8, 16, 34, 64, 96, 128, 256])
+    if H * V > (1024 if dtype == torch.float32 else 2048):
+        H = 1
+    rows = rng.choice([1, 2, 33, 100, 700, 2000])
+    cu, cx = rng.choice([(True, True), (False, False), (True, False), (False, True)])
+    act = rng.choice(["none", "silu", "sigmoid"])
+    gn = rng.random() < 0.25
+    p = 0.0 if gn else rng.choice([0.0, 0.0, 0.1, 0.5])
+    if gn:
+        act = "none"
+    Dm = H * V
+    attn, u = (torch.randn(rows, Dm, generator=g).to(dtype) for _ in range(2))
+    w = (1 + 0.1 * torch.randn(H if gn else Dm, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(H if gn else Dm, generator=g)).to(dtype)
+    mult = 1 if (gn and cu != cx) else 1 + int(cu) + int(cx)
+    dy = torch.randn(rows, mult * Dm, generator=g).to(dtype)
+    seed_t = torch.tensor([seed * 7919 + 13], dtype=torch.int64, device=DEV)
+    ld = [t.to(DEV).requires_grad_(True) for t in (attn, u, w, b)]
+    y = G.hstu_norm_mul_dropout(ld[0], ld[1], ld[2], ld[3], 1e-6, p, p > 0, cu, cx, act, gn, H, V, dropout_seed=seed_t)
+    y.backward(dy.to(DEV))
+    lr = [t.float().requires_grad_(True) for t in (attn, u, w, b)]
+    yr = O.norm_mul_dropout(lr[0], lr[1], lr[2], lr[3], 1e-6, cu, cx, act, gn, H, V)
+    if p > 0:
+        keep, scale = O.dropout_keep_mask(int(seed_t.item()), rows, mult * Dm, p)
+        yr = yr * keep * scale
+    yr.backward(dy.float())
+    tol = PM.F32_TOL if dtype == torch.float32 else PM.HALF_TOL
+    errs = {"y": _rel(y.cpu(), yr)}
+    for a, r, nm in zip(ld, lr, ("dattn", "du", "dw", "db")):
+        errs[nm] = _rel(a.grad.cpu(), r.grad)
+    return _check_all("norm_mul", dict(seed=seed, dtype=str(dtype), H=H, V=V, rows=rows, cu=cu, cx=cx, act=act, gn=gn, p=p),
+                      errs, {"y": tol, "dattn": tol, "du": tol, "dw": 2 * tol, "db": 2 * tol})
+
+
+def _uqvk_case(rng):
+    seed = rng.randrange(10 ** 9)
+    g = torch.Generator().manual_seed(seed)
+    dtype = _dtype(rng)
+    D, H = rng.choice([32, 64, 136, 256, 512, 1024]), rng.choice([1, 2, 4])
+    A, V = rng.choice([16, 64, 128]), rng.choice([16, 64, 128])
+    rows = rng.choice([1, 5, 127, 128, 129, 500, 1500])
+    x = torch.randn(rows, D, generator=g).to(dtype)
+    nw, nb = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype), (0.1 * torch.randn(D, generator=g)).to(dtype)
+    Wt = (torch.randn(D, 2 * H * (A + V), generator=g) / D ** 0.5).to(dtype)
+    bias = (0.1 * torch.randn(2 * H * (A + V), generator=g)).to(dtype)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (x, nw, nb, Wt, bias)]
+    outs = G.hstu_compute_uqvk(leaves[0], leaves[1], leaves[2], 1e-6, H, A, V, leaves[3], leaves[4])
+    douts = [torch.randn(o.shape, generator=g).to(dtype) for o in outs]
+    torch.autograd.backward(list(outs), [d.to(DEV) for d in douts])
+    lr = [t.float().requires_grad_(True) for t in (x, nw, nb, Wt, bias)]
+    refs = O.hstu_compute_uqvk(lr[0], lr[1], lr[2], 1e-6, H, A, V, lr[3], lr[4])
+    torch.autograd.backward(list(refs), [d.float() for d in douts])
+    tol = 5e-4 if dtype == torch.float32 else PM.HALF_TOL
+    errs = {nm: _rel(a.cpu(), r) for nm, a, r in zip("uqkv", outs, refs)}
+    for nm, a, r in zip(("dx", "dnw", "dnb", "dW", "dbias"), leaves, lr):
+        errs[nm] = _rel(a.grad.cpu(), r.grad)
+    return _check_all("uqvk", dict(seed=seed, dtype=str(dtype), D=D, H=H, A=A, V=V, rows=rows), errs,
+                      {k_: (3 * tol if k_ in ("dnw", "dnb") else tol) for k_ in errs})
+
+
+def _output_case(rng):
+    seed = rng.randrange(10 ** 9)
+    g = torch.Generator().manual_seed(seed)
+    dtype = _dtype(rng)
+    D, H, V = rng.choice([32, 64, 136, 512, 1024]), rng.choice([1, 2, 4]), rng.choice([16, 64, 128])
+    rows = rng.choice([1, 5, 128, 129, 500, 1500])
+    cu, cx = rng.choice([(True, True), (False, False), (True, False)])
+    act = rng.choice(["none", "silu", "sigmoid"])
+    recompute = rng.random() < 0.5
+    mult = 1 + int(cu) + int(cx)
+    attn, u = (torch.randn(rows, H * V, generator=g).to(dtype) for _ in range(2))
+    x = torch.randn(rows, D, generator=g).to(dtype)
+    nw, nb = (1 + 0.1 * torch.randn(H * V, generator=g)).to(dtype), (0.1 * torch.randn(H * V, generator=g)).to(dtype)
+    Wo = (torch.randn(mult * H * V, D, generator=g) / (mult * H * V) ** 0.5).to(dtype)
+    dout = torch.randn(rows, D, generator=g).to(dtype)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (attn, u, x, nw, nb, Wo)]
+    o = G.hstu_compute_output(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], 1e-6, leaves[5], H, V, 0.0, False,
+                              cu, cx, act, False, recompute)
+    o.backward(dout.to(DEV))
+    lr = [t.float().requires_grad_(True) for t in (attn, u, x, nw, nb, Wo)]
+    r = O.hstu_compute_output(lr[0], lr[1], lr[2], lr[3], lr[4], 1e-6, lr[5], H, V, cu, cx, act)
+    r.backward(dout.float())
+    tol = 5e-4 if dtype == torch.float32 else PM.HALF_TOL
+    errs = {"out": _rel(o.cpu(), r)}
+    for nm, a, rr in zip(("dattn", "du", "dx", "dnw", "dnb", "dWo"), leaves, lr):
+        errs[nm] = _rel(a.grad.cpu(), rr.grad)
+    return _check_all("output", dict(seed=seed, dtype=str(dtype), D=D, H=H, V=V, rows=rows, cu=cu, cx=cx, act=act,
+                                     recompute=recompute), errs,
+                      {k_: (3 * tol if k_ in ("dnw", "dnb") else tol) for k_ in errs})
+
+
+def _jagged_case(rng):
+    seed = rng.randrange(10 ** 9)
+    g = torch.Generator().manual_seed(seed)
+    dtype = _dtype(rng)
+    width, B = rng.choice([1, 3, 8, 24, 64, 100, 512, 520]), rng.randint(1, 40)
+    ml, mr = rng.choice([1, 7, 200]), rng.choice([1, 5, 50])
+    ll, lr_ = torch.randint(0, ml + 1, (B,), generator=g), torch.randint(0, mr + 1, (B,), generator=g)
+    ol, orr = W._offsets(ll), W._offsets(lr_)
+    left = torch.randn(int(ol[-1]), width, generator=g).to(dtype)
+    right = torch.randn(int(orr[-1]), width, generator=g).to(dtype)
+    ref = O.concat_2D_jagged(left, right, None, None, ol, orr)
+    out = G.concat_2D_jagged(ml + mr, left.to(DEV), right.to(DEV), ml, mr, ol.to(DEV), orr.to(DEV))
+    sl, sr = G.split_2D_jagged(ml + mr, out, None, None, None, None, ol.to(DEV), orr.to(DEV))
+    assert torch.equal(out.cpu(), ref) and torch.equal(sl.cpu(), left) and torch.equal(sr.cpu(), right), \
+        dict(seed=seed, dtype=str(dtype), width=width, B=B, ml=ml, mr=mr)
+    return 0.0
+
+
+def test_stage_sweep():
+    """LayerNorm, the norm-mul kernel in all its variants (with the dropout mask replayed from its
+    seed), the uvqk stage (fused where the shape allows), the output stage and the jagged row movers
+    on drawn shapes: odd widths, single rows, rows of wider buffers, all three dtypes."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    seed, seconds = _budget()
+    rng = random.Random(seed + 1)
+    kinds = [_layer_norm_case] * 2 + [_norm_mul_case] * 3 + [_uqvk_case] * 2 + [_output_case] * 2 + [_jagged_case]
+    worst = {}
+    t0 = time.time()
+    done = 0
+    while (time.time() - t0 < seconds) if seconds > 0 else (done < 1500):
+        fn = rng.choice(kinds)
+        e = fn(rng)
+        worst[fn.__name__] = max(worst.get(fn.__name__, 0.0), e)
+        done += 1
+    PM._note(("sweep", "stages", done), worst)
+
+
+def test_layer_sweep():
+    """Whole STU layers in training mode - drawn widths, heads, lengths, contextual prefix, window,
+    targets, bucketised relative bias - against the oracle's composite: output, input gradient and
+    every parameter gradient."""
+    from generative_recommenders_b200.stu import position_bias_by_distance
+    torch.backends.cuda.matmul.allow_tf32 = False
+    seed0, seconds = _budget()
+    rng = random.Random(seed0 + 2)
+    t0 = time.time()
+    done = 0
+    worst = {}
+    while (time.time() - t0 < seconds) if seconds > 0 else (done < 400):
+        seed = rng.randrange(10 ** 9)
+        g = torch.Generator().manual_seed(seed)
+        dtype = rng.choice([torch.bfloat16, torch.float32])
+        if dtype == torch.float32:
+            D, H, A = rng.choice([32, 64]), rng.choice([1, 2, 4]), rng.choice([16, 32])
+            N = rng.choice([64, 200, 400])
+        else:
+            D, H, A = rng.choice([64, 256, 512]), rng.choice([1, 2, 4]), rng.choice([64, 128])
+            N = rng.choice([128, 300, 700])
+        V = A
+        B = rng.randint(1, 6)
+        ctx, Wn = rng.choice([0, 0, 3, 130]), rng.choice([0, 0, 20, 128])
+        if ctx + 2 > N:
+            ctx = 0
+        has_t = rng.random() < 0.6
+        lengths = torch.randint(1, N + 1, (B,), generator=g)
+        nt = None
+        if has_t:
+            nt = torch.randint(1, 10, (B,), generator=g)
+            lengths = torch.clamp(lengths + nt + ctx, max=N)
+            lengths = torch.clamp(lengths, min=min(ctx + 2, N))
+            nt = torch.minimum(nt, torch.clamp(lengths - ctx - 1, min=0))
+        elif ctx:
+            lengths = torch.clamp(lengths, min=ctx + 1)
+        offs = W._offsets(lengths)
+        L = int(offs[-1])
+        buckets = rng.choice([0, 0, 128])
+        torch.manual_seed(seed)
+        cfg = G.STULayerConfig(embedding_dim=D, num_heads=H, hidden_dim=V, attention_dim=A, output_dropout_ratio=0.0,
+                               target_aware=has_t, max_attn_len=Wn, contextual_seq_len=ctx, rel_bias_buckets=buckets)
+        layer = G.STULayer(cfg).to(DEV).to(dtype).train()
+        x = torch.randn(L, D, generator=g).to(dtype)
+        dy = torch.randn(L, D, generator=g).to(dtype)
+        xd = x.to(DEV).requires_grad_(True)
+        y = layer(xd, lengths.to(DEV), offs.to(DEV), N, None if nt is None else nt.to(DEV))
+        y.backward(dy.to(DEV))
+        params = {n[1:]: p.detach().float().cpu().requires_grad_(True) for n, p in layer.named_parameters()}
+        rb = None
+        if buckets:
+            bias = position_bias_by_distance(params["rel_bias_table"], N)
+            i, j = torch.arange(N).view(-1, 1), torch.arange(N).view(1, -1)
+            rb = bias[(i - j).abs()]
+        xr = x.float().requires_grad_(True)
+        ref = O.stu_layer(xr, offs, N, nt, params, H, A, V, max_attn_len=Wn, contextual_seq_len=ctx, rel_bias=rb)
+        ref.backward(dy.float())
+        tol = 1e-3 if dtype == torch.float32 else 1.5e-2
+        desc = dict(seed=seed, dtype=str(dtype), D=D, H=H, A=A, N=N, ctx=ctx, W=Wn, targets=has_t, buckets=buckets,
+                    lengths=lengths.tolist())
+        errs = {"y": _rel(y.cpu(), ref), "dx": _rel(xd.grad.cpu(), xr.grad)}
+        for n, p in layer.named_parameters():
+            if p.grad is not None and params[n[1:]].grad is not None:
+                errs["d" + n[1:]] = _rel(p.grad.cpu(), params[n[1:]].grad)
+        lims = {k_: (4 * tol if ("norm" in k_ or "bias_table" in k_) else 2 * tol if k_.startswith("d") else tol) for k_ in errs}
+        _check_all("layer", desc, errs, lims)
+        for k_, v_ in errs.items():
+            worst[k_] = max(worst.get(k_, 0.0), v_)
+        done += 1
+    PM._note(("sweep", "layers", done), worst)
