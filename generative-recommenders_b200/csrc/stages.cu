@@ -600,9 +600,12 @@ struct Dropout {
   }
 };
 
-// LayerNorm flavour: one warp per row of D = H * V elements.
+// LayerNorm flavour: one warp per row of D = H * V elements.  With dropout the generator's ten
+// dependent rounds make the kernel latency-bound; rows of up to two vectors per lane are compiled
+// for two resident CTAs (128 registers instead of 158: 3.1 instead of 2.3 TB/s at D = 512), wider
+// rows would spill.
 template <typename E, int MAXV, bool DROPOUT>
-__global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_kernel(NormMulParams p) {
+__global__ void __launch_bounds__(WARPS * 32, (DROPOUT && MAXV <= 2) ? 2 : 1) norm_mul_fwd_kernel(NormMulParams p) {
   constexpr int EV = VecInfo<E>::EV;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int D = p.H * p.V;
