@@ -1193,9 +1193,17 @@ def stage_kernels(dev, peaks, steps):
     seed = torch.tensor([20260], dtype=torch.int64, device=dev)
     res["norm_mul_fwd_dropout"] = timed("norm_mul_fwd", lambda: G.hstu_norm_mul_dropout(
         attn, u, w_, b_, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed), rows * D * 2 * 5 + rows * 8)
+    # backward: reads the mask bits the forward kept (one bit per output element, + 3 * D / 8 bytes per
+    # row each way), or - with nothing kept - runs the generator again
     yd = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed)
     res["norm_mul_bwd_dropout"] = timed("norm_mul_bwd", lambda: torch.autograd.grad(yd, (ar, ur, wr, br), dcat, retain_graph=True),
-                                        rows * D * 2 * 7 + rows * 8)
+                                        rows * D * 2 * 7 + rows * 8 + rows * 3 * D // 8)
+    G.hstu_compute.set_store_dropout_mask(False)
+    yd = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed)
+    G.hstu_compute.set_store_dropout_mask(True)
+    res["norm_mul_bwd_dropout_regenerated"] = timed(
+        "norm_mul_bwd", lambda: torch.autograd.grad(yd, (ar, ur, wr, br), dcat, retain_graph=True), rows * D * 2 * 7 + rows * 8)
+    del yd
     # jagged glue: KV-cache split / concat of [rows, H*d] K rows (last 20 rows of every sequence on
     # the right), and the timestamp + position embedding step before layer 0
     from generative_recommenders_b200.jagged_tensors import concat_2D_jagged, split_2D_jagged

@@ -32,6 +32,7 @@ EXPORTS = [
     "b200_hstu_norm_mul_fwd",
     "b200_hstu_norm_mul_bwd",
     "b200_hstu_norm_mul_bwd_workspace_bytes",
+    "b200_hstu_norm_mul_dropout_mask_bytes",
     "b200_hstu_ln_linear_silu_fwd",
     "b200_hstu_ln_linear_workspace_bytes",
     "b200_hstu_ln_linear_supported",
@@ -99,6 +100,7 @@ class NormMulArgs(Structure):
         ("dtype", c_int32),
         ("dropout_ratio", c_float), ("reserved0", c_int32),
         ("dropout_seed", c_void_p),
+        ("dropout_mask", c_void_p),
     ]
 
 
@@ -204,6 +206,8 @@ def lib():
     L.b200_hstu_norm_mul_bwd.restype = ctypes.c_int
     L.b200_hstu_norm_mul_bwd_workspace_bytes.argtypes = [c_int32, c_int32, c_int32]
     L.b200_hstu_norm_mul_bwd_workspace_bytes.restype = c_int64
+    L.b200_hstu_norm_mul_dropout_mask_bytes.argtypes = [POINTER(NormMulArgs)]
+    L.b200_hstu_norm_mul_dropout_mask_bytes.restype = c_int64
     for name, struct in (("b200_hstu_concat_2d_jagged", JaggedArgs), ("b200_hstu_split_2d_jagged", JaggedArgs),
                          ("b200_hstu_add_timestamp_positional_embeddings_fwd", TsPosArgs),
                          ("b200_hstu_add_timestamp_positional_embeddings_bwd", TsPosArgs)):

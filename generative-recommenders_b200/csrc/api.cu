@@ -86,6 +86,7 @@ bool ln_linear_supported(int D, int N, int silu_cols, int dtype, const char **wh
 int silu_launch(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out, int64_t out_rs, int64_t rows,
                 int width, bool bwd, int dtype, cudaStream_t st);
 int norm_mul(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st);
+int64_t norm_mul_dropout_mask_bytes(const b200_hstu_norm_mul_args &a);
 
 namespace {
 
@@ -286,6 +287,11 @@ int64_t b200_hstu_norm_mul_bwd_workspace_bytes(int32_t H, int32_t V, int32_t gro
   return stage_bwd_workspace_bytes(group_norm ? H : H * V);
 }
 
+int64_t b200_hstu_norm_mul_dropout_mask_bytes(const b200_hstu_norm_mul_args *a) {
+  if (a == nullptr || a->rows <= 0) return 0;
+  return norm_mul_dropout_mask_bytes(*a);
+}
+
 void b200_hstu_profile_enable(int on) {
   g_prof.on = on != 0;
   for (int k = 0; k < PROF_KINDS; ++k) g_prof.count[k] = 0;
@@ -305,7 +311,7 @@ int b200_hstu_profile_collect(int kind, float *out_ms, int max_n) {
 }
 
 const char *b200_hstu_last_error(void) { return g_err; }
-int b200_hstu_version(void) { return 101; }
+int b200_hstu_version(void) { return 102; }
 int64_t b200_hstu_launch_count(void) { return (int64_t)g_launches.load(); }
 
 /* Host utility for tooling and tests: the kv range a query tile visits (the block-skipping

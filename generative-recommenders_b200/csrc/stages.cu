@@ -528,6 +528,9 @@ struct NormMulParams {
   const unsigned long long *drop_seed;  // device; NULL = no dropout
   uint32_t drop_thr;                    // an element is dropped when its 16 random bits are below this
   float drop_scale;                     // 65536 / (65536 - drop_thr)
+  // optional: the mask as bits (element idx = bit idx % 8 of byte idx / 8, set = kept), written by the
+  // forward and read by the backward instead of running the generator again
+  uint8_t *mask;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -572,8 +575,11 @@ struct Dropout {
     return r >= thr ? v * scale : 0.f;
   }
   // the D elements of one part of a row, whose first element has index `base` in the output matrix
+  // `mask_out` (only with whole 8-element vectors, see norm_mul_mask_bytes): the keep bits of every
+  // vector also go to memory, one byte each
   template <typename E, int MAXV>
-  __device__ __forceinline__ void apply(Row<E, MAXV> &r, uint64_t base, int D, int lane) const {
+  __device__ __forceinline__ void apply(Row<E, MAXV> &r, uint64_t base, int D, int lane,
+                                        uint8_t *mask_out = nullptr) const {
     constexpr int EV = VecInfo<E>::EV;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
@@ -585,12 +591,15 @@ struct Dropout {
         const uint64_t g = idx0 >> 3;
         philox4x32_10(k0, k1, (uint32_t)g, (uint32_t)(g >> 32), o);
         const int j0 = (int)(idx0 & 7);   // 0, or 4 for the second half of a group of 32-bit elements
+        uint32_t kept = 0;
 #pragma unroll
         for (int t = 0; t < EV; ++t) {
           const int j = j0 + t;
           const uint32_t rr = (o[(j >> 1) & 3] >> (16 * (j & 1))) & 0xffffu;
+          kept |= (rr >= thr ? 1u : 0u) << t;
           r.v[k][t] = rr >= thr ? r.v[k][t] * scale : 0.f;
         }
+        if (EV == 8 && mask_out != nullptr) mask_out[g] = (uint8_t)kept;
       } else {
 #pragma unroll
         for (int t = 0; t < EV; ++t)
@@ -600,12 +609,50 @@ struct Dropout {
   }
 };
 
+// The same from stored bits (whole 8-element vectors only).
+template <typename E, int MAXV>
+__device__ __forceinline__ void apply_stored_mask(Row<E, MAXV> &r, uint64_t base, int D, int lane, const uint8_t *mask,
+                                                  float scale) {
+  constexpr int EV = VecInfo<E>::EV;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int e0 = (k * 32 + lane) * EV;
+    if (e0 >= D) continue;
+    const uint32_t kept = mask[(base + (uint64_t)e0) >> 3];
+#pragma unroll
+    for (int t = 0; t < EV; ++t) r.v[k][t] = (kept >> t) & 1u ? r.v[k][t] * scale : 0.f;
+  }
+}
+
+// The same with the bytes of a lane's vectors already in registers.  Each byte stays in a register of
+// its own until it is used: any arithmetic on a loaded byte at the point of the load would make the
+// warp wait for the load there, which is what prefetching the next row's bytes is meant to avoid.
+template <int MAXV>
+struct MaskBytes {
+  uint32_t b[MAXV];
+  __device__ __forceinline__ void load(const uint8_t *mask, uint64_t base, int D, int lane) {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int e0 = (k * 32 + lane) * 8;
+      b[k] = e0 < D ? (uint32_t)__ldg(mask + ((base + (uint64_t)e0) >> 3)) : 0u;
+    }
+  }
+  template <typename E>
+  __device__ __forceinline__ void apply(Row<E, MAXV> &r, float scale) const {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < VecInfo<E>::EV; ++t) r.v[k][t] = (b[k] >> t) & 1u ? r.v[k][t] * scale : 0.f;
+  }
+};
+
 // LayerNorm flavour: one warp per row of D = H * V elements.  With dropout the generator's ten
 // dependent rounds make the kernel latency-bound; rows of up to two vectors per lane are compiled
-// for two resident CTAs (128 registers instead of 158: 3.1 instead of 2.3 TB/s at D = 512), wider
-// rows would spill.
+// for two resident CTAs (128 registers instead of 158: 3.1 instead of 2.3 TB/s at D = 512; without
+// dropout 128 instead of 161: 6.2 instead of 5.4 TB/s), wider rows would spill and are left to the
+// compiler's own choice (0 = no minimum).
 template <typename E, int MAXV, bool DROPOUT>
-__global__ void __launch_bounds__(WARPS * 32, (DROPOUT && MAXV <= 2) ? 2 : 1) norm_mul_fwd_kernel(NormMulParams p) {
+__global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_kernel(NormMulParams p) {
   constexpr int EV = VecInfo<E>::EV;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int D = p.H * p.V;
@@ -652,7 +699,7 @@ __global__ void __launch_bounds__(WARPS * 32, (DROPOUT && MAXV <= 2) ? 2 : 1) no
     if (p.concat_u) {
       if (DROPOUT) {
         Row<E, MAXV> du_ = ur;
-        drop.apply(du_, rbase, D, lane);
+        drop.apply(du_, rbase, D, lane, p.mask);
         du_.store(orow, D, lane, p.vec_ok);
       } else {
         ur.store(orow, D, lane, p.vec_ok);
@@ -662,7 +709,7 @@ __global__ void __launch_bounds__(WARPS * 32, (DROPOUT && MAXV <= 2) ? 2 : 1) no
     if (p.concat_x) {
       if (DROPOUT) {
         Row<E, MAXV> dx_ = xr;
-        drop.apply(dx_, rbase + off, D, lane);
+        drop.apply(dx_, rbase + off, D, lane, p.mask);
         dx_.store(orow + off, D, lane, p.vec_ok);
       } else {
         xr.store(orow + off, D, lane, p.vec_ok);
@@ -674,7 +721,7 @@ __global__ void __launch_bounds__(WARPS * 32, (DROPOUT && MAXV <= 2) ? 2 : 1) no
 #pragma unroll
       for (int t = 0; t < EV; ++t)
         xr.v[k][t] = act_f(ur.v[k][t], p.act) * ((xr.v[k][t] - mean) * rstd * wr.v[k][t] + br.v[k][t]);
-    if (DROPOUT) drop.apply(xr, rbase + off, D, lane);
+    if (DROPOUT) drop.apply(xr, rbase + off, D, lane, p.mask);
     xr.store(orow + off, D, lane, p.vec_ok);
     if (lane == 0) {
       if (p.mean) p.mean[row] = mean;
@@ -683,14 +730,15 @@ __global__ void __launch_bounds__(WARPS * 32, (DROPOUT && MAXV <= 2) ? 2 : 1) no
   }
 }
 
-template <typename E, int MAXV, bool DROPOUT>
+// DROPOUT: 0 = none, 1 = the forward's mask regenerated from the seed, 2 = read from p.mask
+template <typename E, int MAXV, int DROPOUT>
 __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams p) {
   constexpr int EV = VecInfo<E>::EV;
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int D = p.H * p.V;
   Dropout drop;
-  if (DROPOUT) drop.init(p);
+  if (DROPOUT == 1) drop.init(p);
   const int width = D * (1 + (p.concat_u ? 1 : 0) + (p.concat_x ? 1 : 0));
   Row<E, MAXV> wr, br, dw, db;
   wr.load((const E *)p.w, D, lane, p.vec_ok);
@@ -707,9 +755,16 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
   constexpr int RV = PF ? MAXV : 1;
   RawRow<E, RV> nx, nu, ngy, ngu, ngx;
   float nmean = 0.f, nrstd = 0.f;
+  MaskBytes<RV> nmy, nmu, nmx;  // stored mask bytes of the prefetched row's parts (a dependent load otherwise)
   auto prefetch = [&](int64_t r) {
     if constexpr (PF) {
       const E *grow = (const E *)p.dout + r * p.dout_rs;
+      if constexpr (DROPOUT == 2) {
+        const uint64_t rb = (uint64_t)r * (uint64_t)width;
+        nmy.load(p.mask, rb + off_y, D, lane);
+        if (p.concat_u) nmu.load(p.mask, rb, D, lane);
+        if (p.concat_x) nmx.load(p.mask, rb + off_x, D, lane);
+      }
       nx.load((const E *)p.attn + r * p.attn_rs, D, lane);
       nu.load((const E *)p.u + r * p.u_rs, D, lane);
       ngy.load(grow + off_y, D, lane);
@@ -724,10 +779,12 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
     Row<E, MAXV> xr, ur, gy, tmp;
     RawRow<E, RV> cgu, cgx;  // this row's concat gradients (the prefetch buffers get overwritten below)
     float mean, rstd;
+    MaskBytes<RV> cmy, cmu, cmx;
     const E *grow = (const E *)p.dout + row * p.dout_rs;
     bool loaded = false;
     if constexpr (PF) {
       if (pf) {
+        if constexpr (DROPOUT == 2) cmy = nmy, cmu = nmu, cmx = nmx;
         nx.unpack(xr);
         nu.unpack(ur);
         ngy.unpack(gy);
@@ -748,7 +805,11 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
     }
     // the forward's mask, regenerated: the gradient of a dropped element is zero, of a kept one scaled
     const uint64_t rbase = (uint64_t)row * (uint64_t)width;
-    if (DROPOUT) drop.apply(gy, rbase + off_y, D, lane);
+    if (DROPOUT == 1) drop.apply(gy, rbase + off_y, D, lane);
+    if constexpr (DROPOUT == 2) {
+      if (PF && loaded) { if constexpr (PF) cmy.apply(gy, p.drop_scale); }
+      else apply_stored_mask(gy, rbase + off_y, D, lane, p.mask, p.drop_scale);
+    }
     float c1 = 0.f, c2 = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k)
@@ -781,7 +842,11 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
       } else {
         tmp.load(grow, D, lane, p.vec_ok);
       }
-      if (DROPOUT) drop.apply(tmp, rbase, D, lane);
+      if (DROPOUT == 1) drop.apply(tmp, rbase, D, lane);
+      if constexpr (DROPOUT == 2) {
+        if (PF && loaded) { if constexpr (PF) cmu.apply(tmp, p.drop_scale); }
+        else apply_stored_mask(tmp, rbase, D, lane, p.mask, p.drop_scale);
+      }
 #pragma unroll
       for (int k = 0; k < MAXV; ++k)
 #pragma unroll
@@ -793,7 +858,11 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
       } else {
         tmp.load(grow + off_x, D, lane, p.vec_ok);
       }
-      if (DROPOUT) drop.apply(tmp, rbase + off_x, D, lane);
+      if (DROPOUT == 1) drop.apply(tmp, rbase + off_x, D, lane);
+      if constexpr (DROPOUT == 2) {
+        if (PF && loaded) { if constexpr (PF) cmx.apply(tmp, p.drop_scale); }
+        else apply_stored_mask(tmp, rbase + off_x, D, lane, p.mask, p.drop_scale);
+      }
 #pragma unroll
       for (int k = 0; k < MAXV; ++k)
 #pragma unroll
@@ -1038,6 +1107,20 @@ int silu_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void *out
   return 0;
 }
 
+// Bytes of the optional dropout mask of these arguments: one bit per element of the [rows, width]
+// output, or 0 where it cannot be used (group norm, 32-bit elements, rows that are not made of whole
+// aligned 8-element vectors).
+int64_t norm_mul_mask_bytes(const b200_hstu_norm_mul_args &a) {
+  if (a.group_norm || a.dtype == B200_HSTU_F32 || !(a.dropout_ratio > 0.f)) return 0;
+  const int64_t D = (int64_t)a.H * a.V;
+  if (D % 8 != 0 || D > max_row_elems<__nv_bfloat16>()) return 0;
+  if (!aligned16(a.attn) || !aligned16(a.u) || !aligned16(a.weight) || !aligned16(a.bias) || !aligned16(a.out) ||
+      a.attn_row_stride % 8 || a.u_row_stride % 8 || a.out_row_stride % 8)
+    return 0;
+  const int64_t width = D * (1 + (a.concat_u ? 1 : 0) + (a.concat_x ? 1 : 0));
+  return a.rows * width / 8;
+}
+
 template <typename E>
 int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
   constexpr int EV = VecInfo<E>::EV;
@@ -1060,6 +1143,7 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     p.drop_thr = thr;
     p.drop_scale = 65536.f / (float)(65536u - thr);
   }
+  p.mask = nullptr;
   const int D = a.H * a.V;
   if (a.rows == 0) {
     if (bwd) {  // dweight / dbias of an empty batch are zeros
@@ -1101,6 +1185,11 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     p.vec_ok = vec_ok;
     int64_t nblk = (a.rows + WARPS - 1) / WARPS;
     int grid = (int)(nblk < (int64_t)num_sms() * 8 ? nblk : (int64_t)num_sms() * 8);
+    if (dropout && a.dropout_mask != nullptr) {
+      if (norm_mul_mask_bytes(a) == 0)
+        return fail(B200_HSTU_EUNSUPPORTED, "norm_mul: a stored dropout mask needs 16-bit elements, aligned rows and H*V %% 8 == 0");
+      p.mask = a.dropout_mask;
+    }
     ProfileScope prof(PROF_NORM_MUL_FWD, st);
     if (dropout) {
       DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, true><<<grid, WARPS * 32, 0, st>>>(p)));
@@ -1120,15 +1209,24 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     return fail(B200_HSTU_EWORKSPACE, "norm_mul backward: scratch too small");
   size_t smem = (size_t)WARPS * D * sizeof(float);
   ProfileScope prof(PROF_NORM_MUL_BWD, st);
-  if (dropout) {
+  if (dropout && a.dropout_mask != nullptr) {
+    if (!vec_ok || EV != 8 || norm_mul_mask_bytes(a) == 0)
+      return fail(B200_HSTU_EUNSUPPORTED, "norm_mul backward: a stored dropout mask needs 16-bit elements, aligned rows and H*V %% 8 == 0");
+    p.mask = a.dropout_mask;
     DISPATCH_MAXV(pick_maxv<E>(D), {
-      auto kern = norm_mul_bwd_kernel<E, MV, true>;
+      auto kern = norm_mul_bwd_kernel<E, MV, 2>;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      kern<<<grid, WARPS * 32, smem, st>>>(p);
+    });
+  } else if (dropout) {
+    DISPATCH_MAXV(pick_maxv<E>(D), {
+      auto kern = norm_mul_bwd_kernel<E, MV, 1>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       kern<<<grid, WARPS * 32, smem, st>>>(p);
     });
   } else {
     DISPATCH_MAXV(pick_maxv<E>(D), {
-      auto kern = norm_mul_bwd_kernel<E, MV, false>;
+      auto kern = norm_mul_bwd_kernel<E, MV, 0>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       kern<<<grid, WARPS * 32, smem, st>>>(p);
     });
@@ -1166,6 +1264,7 @@ int silu_launch(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, void
                 int width, bool bwd, int dtype, cudaStream_t st) {
   DISPATCH_DTYPE(dtype, (silu_t<E>(dy, dy_rs, x, x_rs, out, out_rs, rows, width, bwd, st)));
 }
+int64_t norm_mul_dropout_mask_bytes(const b200_hstu_norm_mul_args &a) { return norm_mul_mask_bytes(a); }
 int norm_mul(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
   DISPATCH_DTYPE(a.dtype, (norm_mul_t<E>(a, bwd, st)));
 }

@@ -339,7 +339,7 @@ def hstu_compute_uqvk(
 
 
 def _norm_mul_forward(attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm,
-                      dropout_ratio, dropout_seed):
+                      dropout_ratio, dropout_seed, want_mask=False):
     """One launch of the norm-mul kernel; returns ``(out, mean, rstd)`` (inputs already contiguous in
     their last dimension, weight / bias already of the activation dtype)."""
     rows = attn.shape[0]
@@ -359,17 +359,28 @@ def _norm_mul_forward(attn, u, weight, bias, eps, num_heads, linear_dim, concat_
     a.rows, a.H, a.V = rows, num_heads, linear_dim
     a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
     a.eps, a.dtype = eps, dtype_code(attn)
+    mask = None
     if dropout_seed is not None and dropout_ratio > 0.0:
         a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
+        if want_mask and rows > 0:
+            # one bit per output element, for a backward that reads the mask instead of running the
+            # generator again (where the library can store it: 16-bit elements, whole aligned vectors)
+            nbytes = _cabi.lib().b200_hstu_norm_mul_dropout_mask_bytes(a)
+            if nbytes > 0:
+                mask = torch.empty(nbytes, dtype=torch.uint8, device=attn.device)
+                a.dropout_mask = mask.data_ptr()
     if rows > 0:
         with torch.cuda.device(attn.device):
             _cabi.check(_cabi.lib().b200_hstu_norm_mul_fwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_fwd")
+    if want_mask:
+        return out, mean, rstd, mask
     return out, mean, rstd
 
 
 def _norm_mul_backward(dout, attn, u, weight, bias, mean, rstd, eps, num_heads, linear_dim, concat_u, concat_x, act,
-                       group_norm, dropout_ratio, dropout_seed):
-    """Backward of the norm-mul kernel; returns ``(dattn, du, dweight, dbias)``."""
+                       group_norm, dropout_ratio, dropout_seed, dropout_mask=None):
+    """Backward of the norm-mul kernel; returns ``(dattn, du, dweight, dbias)``.  ``dropout_mask``: the
+    bits the forward stored; without them the kernel regenerates the mask from the seed."""
     rows = attn.shape[0]
     if dout.stride(-1) != 1:
         dout = dout.contiguous()
@@ -390,11 +401,24 @@ def _norm_mul_backward(dout, attn, u, weight, bias, mean, rstd, eps, num_heads, 
     a.rows, a.H, a.V = rows, num_heads, linear_dim
     a.concat_u, a.concat_x, a.act, a.group_norm = int(concat_u), int(concat_x), act, int(group_norm)
     a.eps, a.dtype = eps, dtype_code(attn)
-    if dropout_seed is not None and dropout_ratio > 0.0:   # the kernel regenerates the forward's mask
+    if dropout_seed is not None and dropout_ratio > 0.0:   # the forward's mask: stored bits, or regenerated
         a.dropout_ratio, a.dropout_seed = dropout_ratio, dropout_seed.data_ptr()
+        if dropout_mask is not None and dout.data_ptr() % 16 == 0 and dout.stride(0) % 8 == 0:
+            a.dropout_mask = dropout_mask.data_ptr()
     with torch.cuda.device(attn.device):
         _cabi.check(_cabi.lib().b200_hstu_norm_mul_bwd(a, stream_ptr(attn.device)), "b200_hstu_norm_mul_bwd")
     return dattn, du, dw, db
+
+
+# The forward of the norm-mul stage keeps its dropout mask as bits (6 % of the output's bytes) for the
+# backward by default; switched off, the backward regenerates the mask from the seed (nothing stored,
+# about twice the backward time).  With recompute_y the mask is never stored.
+_STORE_DROPOUT_MASK = True
+
+
+def set_store_dropout_mask(on: bool) -> None:
+    global _STORE_DROPOUT_MASK
+    _STORE_DROPOUT_MASK = bool(on)
 
 
 class _NormMulFunction(torch.autograd.Function):
@@ -407,16 +431,19 @@ class _NormMulFunction(torch.autograd.Function):
             u = u.contiguous()
         weight = weight.to(attn.dtype).contiguous()
         bias = bias.to(attn.dtype).contiguous()
-        out, mean, rstd = _norm_mul_forward(attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x, act,
-                                            group_norm, dropout_ratio, dropout_seed)
-        ctx.save_for_backward(attn, u, weight, bias, mean, rstd, dropout_seed)
+        keep_mask = _STORE_DROPOUT_MASK and any(ctx.needs_input_grad)   # (grad mode is off inside forward())
+        out, mean, rstd, mask = _norm_mul_forward(attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x,
+                                                  act, group_norm, dropout_ratio, dropout_seed, want_mask=True) \
+            if keep_mask else _norm_mul_forward(attn, u, weight, bias, eps, num_heads, linear_dim, concat_u, concat_x,
+                                                act, group_norm, dropout_ratio, dropout_seed) + (None,)
+        ctx.save_for_backward(attn, u, weight, bias, mean, rstd, dropout_seed, mask)
         ctx.cfg = (eps, num_heads, linear_dim, concat_u, concat_x, act, group_norm, dropout_ratio)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        attn, u, weight, bias, mean, rstd, dropout_seed = ctx.saved_tensors
-        dattn, du, dw, db = _norm_mul_backward(dout, attn, u, weight, bias, mean, rstd, *ctx.cfg, dropout_seed)
+        attn, u, weight, bias, mean, rstd, dropout_seed, mask = ctx.saved_tensors
+        dattn, du, dw, db = _norm_mul_backward(dout, attn, u, weight, bias, mean, rstd, *ctx.cfg, dropout_seed, mask)
         return dattn, du, dw, db, None, None, None, None, None, None, None, None, None
 
 

@@ -1,14 +1,20 @@
 """Import shim: the package directory is named ``generative-recommenders_b200`` (not a valid
-Python identifier), so ``import generative_recommenders_b200`` loads it from here."""
+Python identifier), so ``import generative_recommenders_b200`` gives that package from here.
 
-import importlib.util
+Both names refer to the same module objects (the package and every submodule it has imported), so
+module-level state - the prepared-weights cache, the switches of ``hstu_compute`` - exists once
+however the package was reached."""
+
+import importlib
 import os
 import sys
 
-_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "generative-recommenders_b200")
-_spec = importlib.util.spec_from_file_location(
-    __name__, os.path.join(_dir, "__init__.py"), submodule_search_locations=[_dir]
-)
-_mod = importlib.util.module_from_spec(_spec)
+_root = os.path.dirname(os.path.abspath(__file__))
+if _root not in sys.path:
+    sys.path.insert(0, _root)
+_real = "generative-recommenders_b200"
+_mod = importlib.import_module(_real)
 sys.modules[__name__] = _mod
-_spec.loader.exec_module(_mod)
+for _k, _v in list(sys.modules.items()):
+    if _k.startswith(_real + "."):
+        sys.modules[__name__ + _k[len(_real):]] = _v

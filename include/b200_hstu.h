@@ -254,10 +254,19 @@ typedef struct b200_hstu_norm_mul_args {
   float dropout_ratio;               /* 0 = no dropout */
   int32_t reserved0;
   const int64_t *dropout_seed;       /* device, one int64 (read by the kernels); NULL = no dropout */
+  /* optional, with dropout: the mask as bits, b200_hstu_norm_mul_dropout_mask_bytes() bytes (element
+     idx = row * width + col is bit idx % 8 of byte idx / 8; set = kept).  The forward writes it next
+     to the output; a backward that is given it reads it instead of running the generator again
+     (ten dependent rounds per 8 elements: the regenerating backward takes twice as long).  NULL =
+     nothing stored, the backward regenerates the mask from the seed. */
+  uint8_t *dropout_mask;
 } b200_hstu_norm_mul_args;
 int b200_hstu_norm_mul_fwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream_t stream);
 int b200_hstu_norm_mul_bwd(const b200_hstu_norm_mul_args *args, b200_hstu_stream_t stream);
 int64_t b200_hstu_norm_mul_bwd_workspace_bytes(int32_t H, int32_t V, int32_t group_norm);
+/* Bytes of args->dropout_mask for the forward arguments given, or 0 where a stored mask cannot be used
+   (group norm, 32-bit elements, rows not made of whole 16-byte aligned vectors, no dropout). */
+int64_t b200_hstu_norm_mul_dropout_mask_bytes(const b200_hstu_norm_mul_args *args);
 
 /*
  * The uvqk stage as one tensor-core kernel (generative_recommenders/ops/hstu_compute.py:54-104:

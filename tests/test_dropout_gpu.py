@@ -94,3 +94,48 @@ def test_group_norm_variant_keeps_torch_dropout():
     y = G.hstu_norm_mul_dropout(attn, u, w, b, 1e-6, 0.5, True, True, True, "none", True, H, V)
     frac = float((y != 0).float().mean())
     assert 0.45 < frac < 0.55
+
+
+@pytest.mark.parametrize("dtype,H,V,concat", [
+    (torch.bfloat16, 4, 128, (True, True)),
+    (torch.float16, 2, 96, (True, False)),
+    (torch.bfloat16, 2, 64, (False, False)),
+    (torch.bfloat16, 2, 34, (True, True)),      # rows not made of whole vectors: no mask is stored
+    (torch.float32, 2, 64, (True, True)),       # 32-bit elements: no mask is stored
+])
+def test_stored_mask_and_regenerated_mask_give_the_same_backward(dtype, H, V, concat):
+    """The forward keeps its dropout mask as bits for the backward where it can; a backward that
+    regenerates the mask from the seed instead produces the same gradients bit for bit."""
+    import importlib
+    HC = G.hstu_compute
+    assert HC is importlib.import_module("generative-recommenders_b200.hstu_compute")   # one module under both names
+    g = torch.Generator().manual_seed(3)
+    rows, D, p = 517, H * V, 0.25
+    attn = torch.randn(rows, D, generator=g).to(dtype)
+    u = torch.randn(rows, D, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(D, generator=g)).to(dtype)
+    mult = 1 + int(concat[0]) + int(concat[1])
+    dy = torch.randn(rows, mult * D, generator=g).to(dtype).to(DEV)
+    seed = torch.tensor([987654321], dtype=torch.int64, device=DEV)
+    results = []
+    can_store = dtype != torch.float32 and D % 8 == 0
+    for store in (True, False):
+        HC.set_store_dropout_mask(store)
+        ld = [t.to(DEV).requires_grad_(True) for t in (attn, u, w, b)]
+        n0 = G._cabi.launch_count()
+        y = G.hstu_norm_mul_dropout(ld[0], ld[1], ld[2], ld[3], 1e-6, p, True, concat[0], concat[1], "silu", False, H, V,
+                                    dropout_seed=seed)
+        saved = y.grad_fn.saved_tensors
+        assert (saved[-1] is not None) == (store and can_store)      # the mask bits, where they can be kept
+        if saved[-1] is not None:
+            assert saved[-1].numel() == rows * mult * D // 8
+            kept = torch.count_nonzero(y.detach().reshape(-1) != 0)
+            bits = sum(int(torch.count_nonzero(saved[-1] & (1 << i))) for i in range(8))
+            assert abs(bits - int(kept)) <= 8            # a kept element that is exactly zero is as good as never
+        y.backward(dy)
+        results.append([y.detach()] + [t.grad for t in ld])
+        assert G._cabi.launch_count() - n0 == 3      # forward, backward, reduction of the weight gradients
+    HC.set_store_dropout_mask(True)
+    for a_, b_ in zip(*results):
+        assert torch.equal(a_, b_)
