@@ -1100,6 +1100,62 @@ def run_uvqk(args):
     print(json.dumps(out), flush=True)
 
 
+def run_norm_mul(args):
+    """``--workload norm_mul``: the output stage's norm-mul kernel alone on [131 072, 512] bf16 with the
+    ``[u | attn | y]`` concatenation (the two inputs 134 MB each, the output and its gradient 403 MB each,
+    about 1.5 GB on the device - a case sized for profiling): forward and backward without dropout, with
+    dropout, and the backward once from the forward's stored mask bits and once regenerating the mask."""
+    import generative_recommenders_b200 as G
+    from generative_recommenders_b200 import _cabi
+
+    world, rank, local_rank, dev, dist = _dist_setup()
+    peaks, peak_kind = load_peaks()
+    rows, H, V = 131072, 4, 128
+    D = H * V
+    g = torch.Generator().manual_seed(5)
+    mk = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16).to(dev)  # noqa: E731
+    attn, u, w_, b_, dcat = mk(rows, D), mk(rows, D), mk(D), mk(D), mk(rows, 3 * D)
+    ar, ur, wr, br = (t.clone().requires_grad_(True) for t in (attn, u, w_, b_))
+    seed = torch.tensor([20260], dtype=torch.int64, device=dev)
+    fwd = lambda p, *t: G.hstu_norm_mul_dropout(*t, 1e-6, p, p > 0, True, True, "none", False, H, V,  # noqa: E731
+                                                dropout_seed=seed if p > 0 else None)
+    y_plain = fwd(0.0, ar, ur, wr, br)
+    y_bits = fwd(0.3, ar, ur, wr, br)
+    G.hstu_compute.set_store_dropout_mask(False)
+    y_regen = fwd(0.3, ar, ur, wr, br)
+    G.hstu_compute.set_store_dropout_mask(True)
+    bwd = lambda y: torch.autograd.grad(y, (ar, ur, wr, br), dcat, retain_graph=True)  # noqa: E731
+    fb, bb = rows * D * 2 * 5 + rows * 8, rows * D * 2 * 7 + rows * 8
+    steps = max(3, min(args.steps, 30))
+    res = {}
+    for name, kind, fn, nbytes in (("fwd", "norm_mul_fwd", lambda: fwd(0.0, attn, u, w_, b_), fb),
+                                   ("bwd", "norm_mul_bwd", lambda: bwd(y_plain), bb),
+                                   ("fwd_dropout", "norm_mul_fwd", lambda: fwd(0.3, attn, u, w_, b_), fb),
+                                   ("fwd_dropout_keeping_bits", "norm_mul_fwd", lambda: fwd(0.3, ar, ur, wr, br),
+                                    fb + rows * 3 * D // 8),
+                                   ("bwd_dropout_stored_bits", "norm_mul_bwd", lambda: bwd(y_bits), bb + rows * 3 * D // 8),
+                                   ("bwd_dropout_regenerated", "norm_mul_bwd", lambda: bwd(y_regen), bb)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        _cabi.profile_enable(True)
+        for _ in range(steps):
+            fn()
+        torch.cuda.synchronize()
+        v = _cabi.profile_collect(kind)
+        _cabi.profile_enable(False)
+        ms = sorted(v)[len(v) // 2]
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res[name] = {"ms": round(ms, 4), "bytes": int(nbytes), "gb_per_s": round(gbs, 1),
+                     "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+    out = {"metric": "norm_mul_hbm_gb_per_s", "value": res["fwd"]["gb_per_s"], "unit": "GB/s", "n_gpus": 1,
+           "steps": steps, "warmup": 3, "ms_per_step": res["fwd"]["ms"], "higher_is_better": True,
+           "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "norm-mul forward / backward, rows=%d, D=%d, [u | attn | y] output" % (rows, D)},
+           "hbm_peak_gb_per_s": peaks["hbm_gbs"], "peak_source": peak_kind + " (copy)", "stages": res}
+    print(json.dumps(out), flush=True)
+
+
 def run_layer_norm(args):
     """``--workload layer_norm``: LayerNorm forward / backward alone on [655 360, 512] bf16 (671 MB per
     tensor, larger than L2; about 3 GB on the device - a case sized for profiling)."""
@@ -1258,7 +1314,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config1",
-                    choices=["config1", "config3", "config3_fp8", "config2_stack", "config4_stack", "stages", "uvqk", "layer_norm"])
+                    choices=["config1", "config3", "config3_fp8", "config2_stack", "config4_stack", "stages", "uvqk", "layer_norm", "norm_mul"])
     ap.add_argument("--graph", action="store_true", help="config2_stack: replay the step from a CUDA graph")
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (stack workloads)")
     ap.add_argument("--fwd-only", action="store_true", help="time the forward alone (inference)")
@@ -1278,6 +1334,8 @@ def main():
         run_uvqk(args)
     elif args.workload == "layer_norm":
         run_layer_norm(args)
+    elif args.workload == "norm_mul":
+        run_norm_mul(args)
     elif args.workload == "config3_fp8":
         run_fp8(args)
     else:
