@@ -70,8 +70,9 @@ class AttnArgs(Structure):
         ("dtype", c_int32), ("impl", c_int32),
         ("bias_by_distance", c_void_p), ("bias_numel", c_int32), ("plan_mode", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_int64),
-        ("delta_size", c_int32), ("reserved1", c_int32),
+        ("delta_size", c_int32), ("dropout_ratio", c_float),
         ("d_bias_by_distance", c_void_p),
+        ("dropout_seed", c_void_p),
     ]
 
 

@@ -115,6 +115,10 @@ int validate_attn(const b200_hstu_attn_args *a, bool bwd) {
       return fail(B200_HSTU_EINVAL, "delta attention takes a scalar attn_scale only");
     if (a->plan_mode != B200_HSTU_PLAN_OWN) return fail(B200_HSTU_EINVAL, "delta attention plans for itself");
   }
+  if (a->dropout_ratio < 0.f || !(a->dropout_ratio < 1.f))
+    return fail(B200_HSTU_EINVAL, "dropout_ratio must be at least 0 and below 1");
+  if (a->dropout_ratio > 0.f && a->dropout_seed != nullptr && a->delta_size > 0)
+    return fail(B200_HSTU_EUNSUPPORTED, "delta attention is the inference path: no dropout");
   if (a->plan_mode != B200_HSTU_PLAN_OWN && a->plan_mode != (bwd ? B200_HSTU_PLAN_REUSE : B200_HSTU_PLAN_FOR_BACKWARD))
     return fail(B200_HSTU_EINVAL, "plan_mode %d is not valid for this call", (int)a->plan_mode);
   return 0;
@@ -167,6 +171,8 @@ int b200_hstu_attn_fwd_fp8(const b200_hstu_attn_fp8_args *a, b200_hstu_stream_t 
   if (base.B == 0 || base.total_L == 0) return 0;
   if (!a->q_scale || !a->k_scale || !a->v_scale || !a->block_offsets)
     return fail(B200_HSTU_EINVAL, "fp8 scales / block_offsets is NULL");
+  if (base.dropout_ratio > 0.f && base.dropout_seed != nullptr)
+    return fail(B200_HSTU_EUNSUPPORTED, "the fp8 forward has no dropout");
   return attn_tc_fwd_fp8(*a, (cudaStream_t)stream);
 }
 
@@ -311,7 +317,7 @@ int b200_hstu_profile_collect(int kind, float *out_ms, int max_n) {
 }
 
 const char *b200_hstu_last_error(void) { return g_err; }
-int b200_hstu_version(void) { return 102; }
+int b200_hstu_version(void) { return 103; }
 int64_t b200_hstu_launch_count(void) { return (int64_t)g_launches.load(); }
 
 /* Host utility for tooling and tests: the kv range a query tile visits (the block-skipping

@@ -8,6 +8,10 @@ int64_t attn_tc_fwd_workspace_bytes(const b200_hstu_attn_args &a);
 int64_t attn_tc_bwd_workspace_bytes(const b200_hstu_attn_args &a);
 
 bool attn_tc_applicable(const b200_hstu_attn_args &a, bool bwd, const char **why) {
+  if (a.dropout_ratio > 0.f && a.dropout_seed != nullptr) {
+    *why = "dropout on the attention weights is only handled by the CUDA-core kernels";
+    return false;
+  }
   if (bwd && a.attn_scale != nullptr && a.attn_scale_numel > 1) {
     *why = "per-token attn_scale is only handled by the CUDA-core backward";
     return false;

@@ -12,6 +12,9 @@
 //   x = alpha * q.k (+ bias[|i-j|]);  P = silu(x) * scale * mask;  O = P V
 //   dV = P^T dO;  dP = dO V^T;  dS = dP * silu'(x) * scale * mask;  dQ = alpha dS K;  dK = alpha dS^T Q
 //   dbias[d] = sum of dS over the pairs with |i - j| = d (all heads and sequences), when asked for
+// Optional dropout on P (pt_hstu_attention.py:180-181: after scale and mask, before P V): P and dP are
+// multiplied by keep(i, h, j) / (1 - ratio), the mask a pure function of the seed and the element's
+// index, so that the three kernels agree on it without storing it.
 #include "common.cuh"
 
 namespace b200hstu {
@@ -36,6 +39,29 @@ struct SimtParams {
   float alpha;
   int W, c, F;
   int delta;   // > 0 (forward only): q / out hold the last `delta` positions of each sequence, `delta` rows each
+  const unsigned long long *drop_seed;   // device; NULL = no dropout
+  uint32_t drop_thr;                      // a weight is dropped when its 16 random bits are below this
+  float drop_scale;                       // 65536 / (65536 - drop_thr)
+};
+
+// Dropout factor of the weight of (query row `token` of the jagged tensor, head h, key position j).
+struct DropMask {
+  uint32_t k0, k1, thr;
+  float scale;
+  bool on;
+  __device__ __forceinline__ void init(const SimtParams &p) {
+    on = p.drop_seed != nullptr;
+    thr = p.drop_thr;
+    scale = p.drop_scale;
+    const unsigned long long s = on ? *p.drop_seed : 0ull;
+    k0 = (uint32_t)s;
+    k1 = (uint32_t)(s >> 32);
+  }
+  __device__ __forceinline__ float factor(const SimtParams &p, int64_t token, int h, int j) const {
+    if (!on) return 1.f;
+    const uint64_t idx = ((uint64_t)token * (uint64_t)p.H + (uint64_t)h) * (uint64_t)p.max_seq_len + (uint64_t)j;
+    return philox_keep(k0, k1, idx, thr) ? scale : 0.f;
+  }
 };
 
 template <typename E>
@@ -131,6 +157,8 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
   for (int i = 0; i < MAXD / 4; ++i) acc_o[i] = 0.f;
 
   const int L = g.m.L;
+  DropMask drop;
+  drop.init(p);
   if (m0 < L) {
     const E *qp = (const E *)p.q + qrow0 * p.q_rs + (int64_t)h * p.q_hs;
     const E *kp = (const E *)p.k + (int64_t)g.start * p.k_rs + (int64_t)h * p.k_hs;
@@ -171,6 +199,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_q_stationary_kernel(SimtParams 
         } else {
           val = ok ? dp[jj] * dsiluf_(x) * sc : 0.f;   // dS; alpha is applied to the finished dQ row
         }
+        if (ok && drop.on) val *= drop.factor(p, (int64_t)g.start + i, h, j);
         Ps[r * (T + 1) + cg + 4 * jj] = val;
       }
       __syncthreads();
@@ -239,6 +268,8 @@ __global__ void __launch_bounds__(NTHREADS) attn_kv_stationary_bwd_kernel(SimtPa
 #pragma unroll
   for (int i = 0; i < MAXD / 4; ++i) acc_dk[i] = acc_dv[i] = 0.f;
   const int L = g.m.L;
+  DropMask drop;
+  drop.init(p);
   if (n0 < L) {
     const E *qp = (const E *)p.q + (int64_t)g.start * p.q_rs + (int64_t)h * p.q_hs;
     const E *kp = (const E *)p.k + (int64_t)g.start * p.k_rs + (int64_t)h * p.k_hs;
@@ -270,8 +301,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_kv_stationary_bwd_kernel(SimtPa
           int dist = i > j ? i - j : j - i;
           if (dist < p.bias_numel) x += p.bias[dist];
         }
-        Ps[r * (T + 1) + cg + 4 * jj] = ok ? siluf_(x) * sc : 0.f;
-        Ss[r * (T + 1) + cg + 4 * jj] = ok ? dp[jj] * dsiluf_(x) * sc * p.alpha : 0.f;
+        const float keep = (ok && drop.on) ? drop.factor(p, (int64_t)g.start + i, h, j) : 1.f;
+        Ps[r * (T + 1) + cg + 4 * jj] = ok ? siluf_(x) * sc * keep : 0.f;
+        Ss[r * (T + 1) + cg + 4 * jj] = ok ? dp[jj] * dsiluf_(x) * sc * p.alpha * keep : 0.f;
       }
       __syncthreads();
       // this thread now owns kv row `r` (of the stationary tile) and columns cg + 4 cc
@@ -317,6 +349,14 @@ SimtParams make_params(const b200_hstu_attn_args &a) {
   p.H = a.H; p.dqk = a.dqk; p.dv_dim = a.dv; p.max_seq_len = a.max_seq_len;
   p.alpha = a.alpha; p.W = a.max_attn_len; p.c = a.contextual_seq_len; p.F = a.min_full_attn_seq_len;
   p.delta = a.delta_size;
+  p.drop_seed = nullptr; p.drop_thr = 0; p.drop_scale = 1.f;
+  if (a.dropout_ratio > 0.f && a.dropout_seed != nullptr) {   // (the ratio's range is checked by the caller)
+    uint32_t thr = (uint32_t)(a.dropout_ratio * 65536.f + 0.5f);
+    if (thr > 65535u) thr = 65535u;
+    p.drop_seed = (const unsigned long long *)a.dropout_seed;
+    p.drop_thr = thr;
+    p.drop_scale = 65536.f / (float)(65536u - thr);
+  }
   return p;
 }
 

@@ -161,4 +161,33 @@ __host__ __device__ __forceinline__ KvRange kv_range_for_q_tile(const SeqMask &m
   return r;
 }
 
+// Philox4x32-10 (counter c0, c1, 0, 0; key k0, k1): the counter-based generator behind both dropout
+// masks (output stage and attention weights), so that a backward kernel regenerates the forward's
+// mask from the seed.
+__device__ __forceinline__ void philox4x32_10(uint32_t k0, uint32_t k1, uint32_t c0, uint32_t c1, uint32_t (&o)[4]) {
+  uint32_t c2 = 0, c3 = 0;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  o[0] = c0; o[1] = c1; o[2] = c2; o[3] = c3;
+}
+
+// Element idx of a mask takes the (idx % 8)-th 16-bit piece of the generator's output for counter
+// idx / 8 and is kept when that piece is at least `thr` = round(ratio * 65536).
+__device__ __forceinline__ bool philox_keep(uint32_t k0, uint32_t k1, uint64_t idx, uint32_t thr) {
+  uint32_t o[4];
+  const uint64_t g = idx >> 3;
+  philox4x32_10(k0, k1, (uint32_t)g, (uint32_t)(g >> 32), o);
+  const int j = (int)(idx & 7);
+  return ((o[j >> 1] >> (16 * (j & 1))) & 0xffffu) >= thr;
+}
+
 }  // namespace b200hstu

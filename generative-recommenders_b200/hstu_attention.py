@@ -39,7 +39,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, alpha, max_attn_len,
-                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance):
+                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance, dropout_pr=0.0, dropout_seed=None):
     L, H, dqk = q.shape
     a.q, a.k, a.v = _ptr(q), _ptr(k), _ptr(v)
     a.seq_offsets = _ptr(seq_offsets)
@@ -63,6 +63,9 @@ def _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, 
     if bias_by_distance is not None:
         a.bias_by_distance = bias_by_distance.data_ptr()
         a.bias_numel = bias_by_distance.numel()
+    if dropout_seed is not None and dropout_pr > 0.0:
+        a.dropout_ratio = dropout_pr
+        a.dropout_seed = dropout_seed.data_ptr()
 
 
 _PLAN_OWN, _PLAN_FOR_BACKWARD, _PLAN_REUSE = 0, 1, 2
@@ -110,7 +113,8 @@ def _workspace(a, which: int, device) -> Optional[torch.Tensor]:
 
 
 def hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
-                       contextual_seq_len, min_full_attn_seq_len, bias_by_distance=None, plan_for_backward=False):
+                       contextual_seq_len, min_full_attn_seq_len, bias_by_distance=None, plan_for_backward=False,
+                       dropout_pr=0.0, dropout_seed=None):
     """One forward launch; all tensors already validated / int32 / on the device.
 
     With ``plan_for_backward`` the planning kernel also builds the backward's work lists and the
@@ -122,7 +126,7 @@ def hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, at
         return (out, None) if plan_for_backward else out
     a = _cabi.AttnArgs()
     _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, alpha, max_attn_len,
-                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance)
+                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance, dropout_pr, dropout_seed)
     a.out = out.data_ptr()
     a.o_row_stride, a.o_head_stride = out.stride(0), out.stride(1)
     ws = _workspace(a, 2 if plan_for_backward else 0, q.device)  # kept alive until the launch is queued
@@ -137,7 +141,7 @@ def hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, at
 
 def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
                        contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance=None,
-                       planned_scratch=None, d_bias=None) -> None:
+                       planned_scratch=None, d_bias=None, dropout_pr=0.0, dropout_seed=None) -> None:
     """Fills caller-allocated dq / dk / dv (the ownership rule of the reference's backward,
     triton_hstu_attention.py:3059-3079).  ``planned_scratch``: the scratch a forward with
     ``plan_for_backward`` returned for the same arguments; its lists serve one backward call.
@@ -147,7 +151,7 @@ def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targe
         return
     a = _cabi.AttnArgs()
     _fill_common(a, q, k, v, seq_offsets, num_targets, attn_scale, max_seq_len, alpha, max_attn_len,
-                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance)
+                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance, dropout_pr, dropout_seed)
     a.dout = dout.data_ptr()
     a.dq, a.dk, a.dv_ = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     a.do_row_stride, a.do_head_stride = dout.stride(0), dout.stride(1)
@@ -172,23 +176,24 @@ def hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targe
 class _HstuMhaFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, max_seq_len, alpha,
-                max_attn_len, contextual_seq_len, min_full_attn_seq_len):
+                max_attn_len, contextual_seq_len, min_full_attn_seq_len, dropout_pr=0.0, dropout_seed=None):
         # when a gradient will be asked for, the forward's planning launch builds the backward's
         # work lists as well; the first backward call consumes them
         plan = any(ctx.needs_input_grad[:3]) or ctx.needs_input_grad[6]
         out = hstu_attention_fwd(max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
-                                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance, plan_for_backward=plan)
+                                 contextual_seq_len, min_full_attn_seq_len, bias_by_distance, plan_for_backward=plan,
+                                 dropout_pr=dropout_pr, dropout_seed=dropout_seed)
         ctx.planned_scratch = None
         if plan:
             out, ctx.planned_scratch = out
-        ctx.save_for_backward(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance)
-        ctx.params = (max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len)
+        ctx.save_for_backward(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, dropout_seed)
+        ctx.params = (max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len, dropout_pr)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance = ctx.saved_tensors
-        max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len = ctx.params
+        q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, dropout_seed = ctx.saved_tensors
+        max_seq_len, alpha, max_attn_len, contextual_seq_len, min_full_attn_seq_len, dropout_pr = ctx.params
         dout = last_dim_contiguous(dout)
         # heads side by side, rows not overlapping (a gradient that autograd expanded from a reduced
         # tensor - the backward of ``out.sum(0)`` - has row stride 0)
@@ -203,8 +208,8 @@ class _HstuMhaFunction(torch.autograd.Function):
             d_bias = torch.zeros_like(bias_by_distance)
         hstu_attention_bwd(dout, max_seq_len, alpha, q, k, v, seq_offsets, num_targets, attn_scale, max_attn_len,
                            contextual_seq_len, min_full_attn_seq_len, dq, dk, dv, bias_by_distance,
-                           planned_scratch=planned, d_bias=d_bias)
-        return dq, dk, dv, None, None, None, d_bias, None, None, None, None, None
+                           planned_scratch=planned, d_bias=d_bias, dropout_pr=dropout_pr, dropout_seed=dropout_seed)
+        return dq, dk, dv, None, None, None, d_bias, None, None, None, None, None, None, None
 
 
 def hstu_mha(
@@ -226,9 +231,18 @@ def hstu_mha(
     kernel: HammerKernel = HammerKernel.CUDA,
     enable_tma: bool = False,
     bias_by_distance: Optional[torch.Tensor] = None,
+    dropout_seed: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Jagged HSTU attention; same arguments, checks and result as the reference's
     ``hstu_mha`` (generative_recommenders/ops/hstu_attention.py:101-207).
+
+    ``dropout_pr`` (in training): dropout on the attention weights after scale and mask, as the
+    reference's PyTorch path applies it (ops/pytorch/pt_hstu_attention.py:180-181).  The mask is
+    generated inside the CUDA-core kernels from a counter-based generator keyed by ``dropout_seed``
+    (an extension: a one-element int64 tensor on the device, drawn from torch's CUDA generator when
+    not given) and regenerated by the backward; the tensor-core kernels do not take part (no layer
+    of the reference passes a non-zero rate, ops/hstu_compute.py:327-328), so such a call runs at
+    CUDA-core speed.
 
     ``sort_by_length`` and ``enable_tma`` are accepted and ignored: work is always scheduled
     longest-first and K/V always stream through TMA.  ``bias_by_distance`` is an extension
@@ -244,8 +258,9 @@ def hstu_mha(
     torch._assert(v.shape[0] == q.shape[0], "wrong v shape[0]")
     torch._assert(v.shape[1] == q.shape[1], "wrong v shape[1]")
     torch._assert(causal, "only support causal attention")
-    if dropout_pr > 1e-6 and training:
-        raise NotImplementedError("attention dropout is not implemented (the HSTU layer never uses it)")
+    drop = float(dropout_pr) if (training and dropout_pr > 0.0) else 0.0
+    if drop > 1.0:
+        raise ValueError("dropout probability has to be between 0 and 1")
     require_cuda(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance)
     if k.dtype != q.dtype or v.dtype != q.dtype:
         raise TypeError("q, k, v must share a dtype")
@@ -262,9 +277,24 @@ def hstu_mha(
             raise RuntimeError("attn_scale must be a scalar or have one entry per token")
     if bias_by_distance is not None:
         bias_by_distance = bias_by_distance.to(torch.float32).reshape(-1).contiguous()
-    return _HstuMhaFunction.apply(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, int(max_seq_len),
-                                  float(alpha), int(max_attn_len), int(contextual_seq_len),
-                                  int(min_full_attn_seq_len))
+    if drop >= 1.0:      # everything dropped (torch's dropout returns zeros for p = 1)
+        drop = 0.0
+        zero_all = True
+    else:
+        zero_all = False
+    if drop > 0.0:
+        if dropout_seed is None:
+            # from torch's CUDA generator: reproducible under torch.manual_seed
+            dropout_seed = torch.randint(0, 2 ** 62, (1,), dtype=torch.int64, device=q.device)
+        require_cuda(dropout_seed)
+        if dropout_seed.dtype != torch.int64 or dropout_seed.numel() != 1:
+            raise TypeError("dropout_seed must be a one-element int64 tensor")
+    else:
+        dropout_seed = None
+    out = _HstuMhaFunction.apply(q, k, v, seq_offsets, num_targets, attn_scale, bias_by_distance, int(max_seq_len),
+                                 float(alpha), int(max_attn_len), int(contextual_seq_len),
+                                 int(min_full_attn_seq_len), drop, dropout_seed)
+    return out * 0 if zero_all else out
 
 
 def delta_hstu_mha(

@@ -104,13 +104,23 @@ typedef struct b200_hstu_attn_args {
      pt_hstu_attention.py:191-251).  Every sequence must be at least delta_size and at most
      max_seq_len long; attn_scale must be NULL or a scalar. */
   int32_t delta_size;
-  int32_t reserved1;
+  /* > 0 (with dropout_seed): dropout on the attention weights - after scale and mask, before the
+     product with V - as the reference's PyTorch path applies it
+     (generative_recommenders/ops/pytorch/pt_hstu_attention.py:180-181); must be below 1.  The weight
+     of query row r (a row of q), head h and key position j inside the sequence is element
+     idx = (r * H + h) * max_seq_len + j of the mask: dropped when the (idx % 8)-th 16-bit piece of
+     Philox4x32-10(key = *dropout_seed, counter = idx / 8) is below round(dropout_ratio * 65536), scaled by
+     the inverse keep probability otherwise.  A backward call with the same ratio and seed regenerates
+     the mask.  CUDA-core kernels only: impl = AUTO takes them, impl = TCGEN05 is refused; not with
+     delta_size. */
+  float dropout_ratio;
   /* bwd only, optional: gradient of bias_by_distance, fp32 [bias_numel].  The backward ADDS into this
      caller-zeroed buffer (fp32 atomics: the sum over pairs, heads and sequences of dL/dscore at each
      |i - j|; the order of the additions, and with it the last bits, varies from run to run).  NULL =
      not wanted.  The research model trains these tables
      (generative_recommenders/research/modeling/sequential/hstu.py:65-143, 203-211). */
   float *d_bias_by_distance;
+  const uint64_t *dropout_seed;    /* device, one value; NULL = no dropout */
 } b200_hstu_attn_args;
 
 /*

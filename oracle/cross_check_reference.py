@@ -3,7 +3,8 @@
     python oracle/cross_check_reference.py --reference /path/to/generative-recommenders [--cases 3000] [--seed 0]
 
 TEST INFRASTRUCTURE ONLY.  The golden fixtures pin the oracle on a fixed set of inputs; this script
-draws as many more as asked for - attention forward and backward (every mask feature, targets that
+draws as many more as asked for - attention forward and backward (every mask feature, dropout on the
+weights with the reference's own mask, targets that
 reach beyond the history, sequences longer than ``max_seq_len``, empty sequences, scalar and
 per-token scales), cached attention, the uvqk stage, all variants of the output stage, jagged
 concat / split in every layout, the timestamp + position embeddings and whole STU layers (output
@@ -39,6 +40,11 @@ def _max_diff(a, b):
     return float((a.detach() - b.detach()).abs().max()) if a.numel() else 0.0
 
 
+def _scaled_diff(a, b):
+    # a parameter gradient sums over every token: its size, not 1, is the scale fp32 rounding refers to
+    return _max_diff(a, b) / max(1.0, float(b.detach().abs().max())) if a.numel() else 0.0
+
+
 def attention_case(rng, ref):
     g = torch.Generator().manual_seed(rng.randrange(10 ** 9))
     N = rng.choice([8, 24, 40, 64])
@@ -63,16 +69,29 @@ def attention_case(rng, ref):
     dout = torch.randn(L, H, V, generator=g)
     pick = rng.random()
     sc = torch.tensor(0.37) if pick < 0.2 else (torch.rand(L, generator=g) if pick < 0.4 else None)
-    want = ref.pytorch_hstu_mha(N, 0.25, q, k, v, offs, True, 0.0, False, nt, sc, W, ctx, F)
+    # dropout on the weights: the reference draws its mask with F.dropout on the padded [B, H, N, N]
+    # weights - its only use of the generator - so the same seed and shape reproduce the mask here
+    drop = rng.choice([0.0, 0.0, 0.0, 0.1, 0.5])
+    keep = None
+    if drop > 0:
+        seed = rng.randrange(10 ** 9)
+        torch.manual_seed(seed)
+        dense = torch.nn.functional.dropout(torch.ones(B, H, N, N), drop, True) != 0
+        keep = torch.zeros(L, H, N, dtype=torch.bool)
+        for b in range(B):
+            n = min(int(lengths[b]), N)
+            keep[int(offs[b]):int(offs[b]) + n] = dense[b, :, :n].transpose(0, 1)
+        torch.manual_seed(seed)
+    want = ref.pytorch_hstu_mha(N, 0.25, q, k, v, offs, True, drop, drop > 0, nt, sc, W, ctx, F)
     want.backward(dout)
     wg = [t.grad.clone() for t in (q, k, v)]
     for t in (q, k, v):
         t.grad = None
     got = O.hstu_mha(N, 0.25, q, k, v, offs, num_targets=nt, attn_scale=sc, max_attn_len=W, contextual_seq_len=ctx,
-                     min_full_attn_seq_len=F)
+                     min_full_attn_seq_len=F, dropout_pr=drop, dropout_keep=keep)
     got.backward(dout)
     e = max([_max_diff(got, want)] + [_max_diff(t.grad, w_) for t, w_ in zip((q, k, v), wg)])
-    return e, ("attention", N, lengths.tolist(), None if nt is None else nt.tolist(), ctx, W, F)
+    return e, ("attention", N, lengths.tolist(), None if nt is None else nt.tolist(), ctx, W, F, drop)
 
 
 def cached_case(rng, ref):
@@ -233,7 +252,7 @@ def layer_case(rng, stu, kernel):
     got = O.stu_layer(x, offs, N, nt if ta else None, params, H, A, A, max_attn_len=W, contextual_seq_len=ctx)
     got.backward(dy)
     e = max([_max_diff(got, want), _max_diff(x.grad, wdx)] +
-            [_max_diff(params[n[1:]].grad, p_.grad) for n, p_ in layer.named_parameters()])
+            [_scaled_diff(params[n[1:]].grad, p_.grad) for n, p_ in layer.named_parameters()])
     return e, ("layer", D, H, A, ctx, W, ta, lengths.tolist(), nt.tolist())
 
 

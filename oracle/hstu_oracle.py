@@ -126,6 +126,7 @@ def hstu_mha(
     min_full_attn_seq_len: int = 0,
     rel_bias: Optional[torch.Tensor] = None,
     compute_dtype: Optional[torch.dtype] = None,
+    dropout_keep: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Jagged HSTU attention, ``out[i] = sum_j mask(i,j) * SiLU(alpha q_i.k_j) * s * v_j``.
 
@@ -139,9 +140,16 @@ def hstu_mha(
 
     ``compute_dtype`` upcasts q/k/v first (use ``torch.float32`` to get the fp32
     answer for bf16 inputs); the result is returned in that dtype.
+
+    Dropout on the weights (``F.dropout(qk_attn, p, training)`` after the mask, :180-181): the
+    reference draws its mask from torch's generator, so a comparison needs the mask from outside -
+    ``dropout_keep``, boolean ``[L_total, H, max_seq_len]`` (query row, head, key position);
+    kept weights are scaled by ``1 / (1 - dropout_pr)`` like ``F.dropout`` does (to compare with
+    the kernels, whose mask drops a weight with probability ``round(p * 65536) / 65536``, pass
+    that ratio).
     """
     assert causal, "only causal attention exists in the reference (hstu_attention.py:128)"
-    assert dropout_pr == 0.0, "attention dropout is outside the restated path"
+    assert (dropout_pr == 0.0) == (dropout_keep is None), "dropout needs its keep mask, and only dropout does"
     if compute_dtype is not None:
         q, k, v = q.to(compute_dtype), k.to(compute_dtype), v.to(compute_dtype)
     L_total, H, _ = q.shape
@@ -178,6 +186,9 @@ def hstu_mha(
             seq_len=e - s,
         )
         p = p * mask.unsqueeze(0)
+        if dropout_keep is not None:
+            keep = dropout_keep[s : s + L, :, :L].transpose(0, 1).to(p.device)  # [H, L, L]
+            p = p * keep.to(p.dtype) / (1.0 - dropout_pr)
         ob = torch.einsum("hxy,hyv->hxv", p, vb).transpose(0, 1)  # [L, H, V]
         if L < e - s:  # rows beyond max_seq_len come back as zeros from dense_to_jagged
             ob = torch.cat([ob, ob.new_zeros(e - s - L, H, ob.shape[2])], dim=0)

@@ -32,8 +32,10 @@ def test_struct_layout_matches_header():
     # the structs are plain C: spot-check the sizes the Python mirror computes
     assert ctypes.sizeof(_cabi.AttnArgs) % 8 == 0
     assert _cabi.AttnArgs.total_L.offset == 8 * 12 + 8 * 16
-    # ... delta_size, reserved1, then the optional bias gradient as the last field
-    assert _cabi.AttnArgs.d_bias_by_distance.offset == ctypes.sizeof(_cabi.AttnArgs) - 8
+    # ... delta_size, dropout_ratio, the optional bias gradient, then the dropout seed as the last field
+    assert _cabi.AttnArgs.dropout_ratio.offset == _cabi.AttnArgs.delta_size.offset + 4
+    assert _cabi.AttnArgs.d_bias_by_distance.offset == ctypes.sizeof(_cabi.AttnArgs) - 16
+    assert _cabi.AttnArgs.dropout_seed.offset == ctypes.sizeof(_cabi.AttnArgs) - 8
     assert ctypes.sizeof(_cabi.AttnFp8Args) == ctypes.sizeof(_cabi.AttnArgs) + 32
 
 

@@ -139,3 +139,109 @@ def test_stored_mask_and_regenerated_mask_give_the_same_backward(dtype, H, V, co
     HC.set_store_dropout_mask(True)
     for a_, b_ in zip(*results):
         assert torch.equal(a_, b_)
+
+
+# ---------------------------------------------------------------------------------------------
+# dropout on the attention weights (CUDA-core kernels)
+# ---------------------------------------------------------------------------------------------
+def _attention_inputs(dtype, seed=4, N=200, H=2, d=32, with_targets=True):
+    from generative_recommenders_b200 import workloads as W
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.tensor([200, 37, 1, 150, 96])
+    nt = torch.tensor([3, 2, 0, 9, 1]) if with_targets else None
+    offs = W._offsets(lengths)
+    L = int(offs[-1])
+    q, k, v, dout = ((torch.randn(L, H, d, generator=g) * 0.8).to(dtype) for _ in range(4))
+    return N, lengths, nt, offs, q, k, v, dout
+
+
+@pytest.mark.parametrize("dtype,ctx,window,p", [
+    (torch.float32, 0, 0, 0.3),
+    (torch.float32, 3, 40, 0.5),
+    (torch.bfloat16, 0, 0, 0.1),
+    (torch.bfloat16, 2, 64, 0.3),
+    (torch.float16, 0, 33, 0.25),
+])
+def test_attention_dropout_mask_replay(dtype, ctx, window, p):
+    """``hstu_mha(dropout_pr=p, training=True)``: the mask - element ``(row * H + h) * max_seq_len + j``
+    of the counter-based generator - is replayed by the oracle, which applies it where the reference
+    does (after scale and mask); output and all three gradients agree, the same seed gives the same
+    bits and another seed another mask."""
+    N, lengths, nt, offs, q, k, v, dout = _attention_inputs(dtype)
+    H, d = q.shape[1], q.shape[2]
+    L = q.shape[0]
+    alpha = 1.0 / d ** 0.5
+    seed = torch.tensor([0x0BAD_5EED_1234], dtype=torch.int64, device=DEV)
+    ld = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    n0 = G._cabi.launch_count()
+    out = G.hstu_mha(N, alpha, ld[0], ld[1], ld[2], offs.to(DEV), dropout_pr=p, training=True, num_targets=nt.to(DEV),
+                     max_attn_len=window, contextual_seq_len=ctx, dropout_seed=seed)
+    out.backward(dout.to(DEV))
+    assert G._cabi.launch_count() - n0 == 3          # forward, dQ, dK / dV: CUDA-core kernels, no planning launch
+    keep, scale = O.dropout_keep_mask(int(seed.item()), L * H, N, p)
+    keep = keep.view(L, H, N)
+    eff = 1.0 - 1.0 / scale                         # the ratio the 16-bit threshold realises
+    assert abs(eff - p) < 1e-4
+    lr = [t.float().requires_grad_(True) for t in (q, k, v)]
+    ref = O.hstu_mha(N, alpha, lr[0], lr[1], lr[2], offs, dropout_pr=eff, num_targets=nt, max_attn_len=window,
+                     contextual_seq_len=ctx, dropout_keep=keep)
+    ref.backward(dout.float())
+    plain = O.hstu_mha(N, alpha, q.float(), k.float(), v.float(), offs, num_targets=nt, max_attn_len=window,
+                       contextual_seq_len=ctx)
+    assert float((ref.detach() - plain).norm() / plain.norm()) > 0.1      # the mask matters
+    name = ("attention dropout", str(dtype), ctx, window, p)
+    chk = P.check_f32 if dtype == torch.float32 else P.check
+    chk(name + ("out",), out, ref.detach(), offs)
+    for a, r, nm in zip(ld, lr, ("dq", "dk", "dv")):
+        chk(name + (nm,), a.grad, r.grad, offs)
+    with torch.no_grad():
+        again = G.hstu_mha(N, alpha, ld[0], ld[1], ld[2], offs.to(DEV), dropout_pr=p, training=True,
+                           num_targets=nt.to(DEV), max_attn_len=window, contextual_seq_len=ctx, dropout_seed=seed)
+        other = G.hstu_mha(N, alpha, ld[0], ld[1], ld[2], offs.to(DEV), dropout_pr=p, training=True,
+                           num_targets=nt.to(DEV), max_attn_len=window, contextual_seq_len=ctx, dropout_seed=seed + 1)
+    assert torch.equal(again, out.detach()) and not torch.equal(other, out.detach())
+
+
+def test_attention_dropout_modes():
+    """Eval mode ignores the rate; without a seed one is drawn from torch's generator (reproducible
+    under ``torch.manual_seed``); p = 1 returns zeros like ``F.dropout``; the tensor-core kernels
+    refuse instead of silently dropping nothing; the bias gradient sees the mask."""
+    N, lengths, nt, offs, q, k, v, dout = _attention_inputs(torch.bfloat16, H=2, d=64, with_targets=False)
+    alpha = 0.125
+    qd, kd, vd, od = q.to(DEV), k.to(DEV), v.to(DEV), offs.to(DEV)
+    base = G.hstu_mha(N, alpha, qd, kd, vd, od)
+    assert torch.equal(G.hstu_mha(N, alpha, qd, kd, vd, od, dropout_pr=0.4, training=False), base)
+    torch.manual_seed(5)
+    a = G.hstu_mha(N, alpha, qd, kd, vd, od, dropout_pr=0.4, training=True)
+    b = G.hstu_mha(N, alpha, qd, kd, vd, od, dropout_pr=0.4, training=True)
+    torch.manual_seed(5)
+    c = G.hstu_mha(N, alpha, qd, kd, vd, od, dropout_pr=0.4, training=True)
+    assert torch.equal(a, c) and not torch.equal(a, b) and not torch.equal(a, base)
+    assert float(G.hstu_mha(N, alpha, qd, kd, vd, od, dropout_pr=1.0, training=True).abs().max()) == 0.0
+    with pytest.raises(ValueError):
+        G.hstu_mha(N, alpha, qd, kd, vd, od, dropout_pr=1.5, training=True)
+    G.set_attention_impl("tcgen05")
+    try:
+        with pytest.raises(RuntimeError, match="CUDA-core"):
+            G.hstu_mha(N, alpha, qd, kd, vd, od, dropout_pr=0.4, training=True)
+    finally:
+        G.set_attention_impl("auto")
+    # relative bias with dropout: the table's gradient against the oracle's
+    L, H = q.shape[0], q.shape[1]
+    g = torch.Generator().manual_seed(9)
+    bias = torch.randn(N, generator=g) * 0.3
+    seed = torch.tensor([77], dtype=torch.int64, device=DEV)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    bd = bias.to(DEV).requires_grad_(True)
+    out = G.hstu_mha(N, alpha, leaves[0], leaves[1], leaves[2], od, dropout_pr=0.25, training=True,
+                     bias_by_distance=bd, dropout_seed=seed)
+    out.backward(dout.to(DEV))
+    keep, scale = O.dropout_keep_mask(77, L * H, N, 0.25)
+    lr = [t.float().requires_grad_(True) for t in (q, k, v)]
+    br = bias.clone().requires_grad_(True)
+    i, j = torch.arange(N).view(-1, 1), torch.arange(N).view(1, -1)
+    ref = O.hstu_mha(N, alpha, lr[0], lr[1], lr[2], offs, dropout_pr=1.0 - 1.0 / scale, rel_bias=br[(i - j).abs()],
+                     dropout_keep=keep.view(L, H, N))
+    ref.backward(dout.float())
+    P.check(("attention dropout", "bias", "out"), out, ref.detach(), offs)
+    assert O.rel_l2(bd.grad, br.grad) < 2.5e-2

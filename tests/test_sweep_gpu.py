@@ -87,10 +87,17 @@ def _attention_case(rng):
     if with_bias:
         bias = torch.randn(rng.choice([max_len, max(1, max_len // 3)]), generator=g) * 0.3
     regular = bool(((lengths - (0 if nt is None else nt)) >= ctx + 1).all()) and bool((lengths <= max_len).all())
+    # dropout on the weights (CUDA-core kernels only), the mask replayed for the oracle from its seed
+    drop, keep, seed_t = 0.0, None, None
+    if impl != "tcgen05" and L * heads * max_len <= 4_000_000 and rng.random() < 0.15:
+        drop = rng.choice([0.1, 0.3, 0.5])
+        seed_t = torch.tensor([seed * 31 + 7], dtype=torch.int64, device=DEV)
+        keep, keep_scale = O.dropout_keep_mask(int(seed_t.item()), L * heads, max_len, drop)
+        keep = keep.view(L, heads, max_len).to(DEV)
     name = dict(seed=seed, dtype=str(dtype), dim=dim, heads=heads, max_len=max_len, ctx=ctx, window=window,
                 full_tail=full_tail, impl=impl, bias=None if bias is None else bias.numel(),
                 lengths=lengths.tolist(), targets=None if nt is None else nt.tolist(),
-                scale=None if scale is None else scale.numel())
+                scale=None if scale is None else scale.numel(), drop=drop)
 
     G.set_attention_impl(impl)
     alpha = 1.0 / dim ** 0.5
@@ -100,7 +107,8 @@ def _attention_case(rng):
     nt_d = None if nt is None else nt.to(DEV)
     sc_d = None if scale is None else scale.to(DEV)
     out = G.hstu_mha(max_len, alpha, qd, kd, vd, offs_d, num_targets=nt_d, max_attn_len=window,
-                     contextual_seq_len=ctx, min_full_attn_seq_len=full_tail, attn_scale=sc_d, bias_by_distance=bd)
+                     contextual_seq_len=ctx, min_full_attn_seq_len=full_tail, attn_scale=sc_d, bias_by_distance=bd,
+                     dropout_pr=drop, training=True, dropout_seed=seed_t)
     out.backward(dout.to(DEV))
 
     q32, k32, v32 = (t.float().to(DEV).requires_grad_(True) for t in (q, k, v))
@@ -112,7 +120,8 @@ def _attention_case(rng):
         d = (i - j).abs()
         rb = torch.where(d < bias.numel(), b32[d.clamp(max=bias.numel() - 1)], torch.zeros((), device=DEV))
     ref = O.hstu_mha(max_len, alpha, q32, k32, v32, offs_d, num_targets=nt_d, max_attn_len=window,
-                     contextual_seq_len=ctx, min_full_attn_seq_len=full_tail, attn_scale=sc_d, rel_bias=rb)
+                     contextual_seq_len=ctx, min_full_attn_seq_len=full_tail, attn_scale=sc_d, rel_bias=rb,
+                     dropout_pr=(1.0 - 1.0 / keep_scale) if drop else 0.0, dropout_keep=keep)
     ref.backward(dout.float().to(DEV))
 
     tol = PM.F32_TOL if dtype == torch.float32 else PM.HALF_TOL
