@@ -1120,19 +1120,26 @@ def run_norm_mul(args):
     fwd = lambda p, *t: G.hstu_norm_mul_dropout(*t, 1e-6, p, p > 0, True, True, "none", False, H, V,  # noqa: E731
                                                 dropout_seed=seed if p > 0 else None)
     y_plain = fwd(0.0, ar, ur, wr, br)
-    y_bits = fwd(0.3, ar, ur, wr, br)
-    G.hstu_compute.set_store_dropout_mask(False)
     y_regen = fwd(0.3, ar, ur, wr, br)
     G.hstu_compute.set_store_dropout_mask(True)
+    y_bits = fwd(0.3, ar, ur, wr, br)
+    G.hstu_compute.set_store_dropout_mask(False)
     bwd = lambda y: torch.autograd.grad(y, (ar, ur, wr, br), dcat, retain_graph=True)  # noqa: E731
+
+    def fwd_bits():
+        G.hstu_compute.set_store_dropout_mask(True)
+        try:
+            return fwd(0.3, ar, ur, wr, br)
+        finally:
+            G.hstu_compute.set_store_dropout_mask(False)
+
     fb, bb = rows * D * 2 * 5 + rows * 8, rows * D * 2 * 7 + rows * 8
     steps = max(3, min(args.steps, 30))
     res = {}
     for name, kind, fn, nbytes in (("fwd", "norm_mul_fwd", lambda: fwd(0.0, attn, u, w_, b_), fb),
                                    ("bwd", "norm_mul_bwd", lambda: bwd(y_plain), bb),
                                    ("fwd_dropout", "norm_mul_fwd", lambda: fwd(0.3, attn, u, w_, b_), fb),
-                                   ("fwd_dropout_keeping_bits", "norm_mul_fwd", lambda: fwd(0.3, ar, ur, wr, br),
-                                    fb + rows * 3 * D // 8),
+                                   ("fwd_dropout_keeping_bits", "norm_mul_fwd", lambda: fwd_bits(), fb + rows * 3 * D // 8),
                                    ("bwd_dropout_stored_bits", "norm_mul_bwd", lambda: bwd(y_bits), bb + rows * 3 * D // 8),
                                    ("bwd_dropout_regenerated", "norm_mul_bwd", lambda: bwd(y_regen), bb)):
         for _ in range(3):
@@ -1249,16 +1256,20 @@ def stage_kernels(dev, peaks, steps):
     seed = torch.tensor([20260], dtype=torch.int64, device=dev)
     res["norm_mul_fwd_dropout"] = timed("norm_mul_fwd", lambda: G.hstu_norm_mul_dropout(
         attn, u, w_, b_, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed), rows * D * 2 * 5 + rows * 8)
-    # backward: reads the mask bits the forward kept (one bit per output element, + 3 * D / 8 bytes per
-    # row each way), or - with nothing kept - runs the generator again
+    # backward: regenerates the mask from the seed (the default), or - switched on - reads the bits the
+    # forward kept (one bit per output element, + 3 * D / 8 bytes per row each way)
     yd = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed)
     res["norm_mul_bwd_dropout"] = timed("norm_mul_bwd", lambda: torch.autograd.grad(yd, (ar, ur, wr, br), dcat, retain_graph=True),
-                                        rows * D * 2 * 7 + rows * 8 + rows * 3 * D // 8)
-    G.hstu_compute.set_store_dropout_mask(False)
-    yd = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed)
+                                        rows * D * 2 * 7 + rows * 8)
     G.hstu_compute.set_store_dropout_mask(True)
-    res["norm_mul_bwd_dropout_regenerated"] = timed(
-        "norm_mul_bwd", lambda: torch.autograd.grad(yd, (ar, ur, wr, br), dcat, retain_graph=True), rows * D * 2 * 7 + rows * 8)
+    res["norm_mul_fwd_dropout_keeping_bits"] = timed("norm_mul_fwd", lambda: G.hstu_norm_mul_dropout(
+        ar, ur, wr, br, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed),
+        rows * D * 2 * 5 + rows * 8 + rows * 3 * D // 8)
+    yd = G.hstu_norm_mul_dropout(ar, ur, wr, br, 1e-6, 0.3, True, True, True, "none", False, 4, 128, dropout_seed=seed)
+    G.hstu_compute.set_store_dropout_mask(False)
+    res["norm_mul_bwd_dropout_stored_bits"] = timed(
+        "norm_mul_bwd", lambda: torch.autograd.grad(yd, (ar, ur, wr, br), dcat, retain_graph=True),
+        rows * D * 2 * 7 + rows * 8 + rows * 3 * D // 8)
     del yd
     # jagged glue: KV-cache split / concat of [rows, H*d] K rows (last 20 rows of every sequence on
     # the right), and the timestamp + position embedding step before layer 0

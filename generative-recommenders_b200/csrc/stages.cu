@@ -558,10 +558,12 @@ struct Dropout {
     const uint32_t r = (o[j >> 1] >> (16 * (j & 1))) & 0xffffu;
     return r >= thr ? v * scale : 0.f;
   }
-  // the D elements of one part of a row, whose first element has index `base` in the output matrix
-  // `mask_out` (only with whole 8-element vectors, see norm_mul_mask_bytes): the keep bits of every
-  // vector also go to memory, one byte each
-  template <typename E, int MAXV>
+  // the D elements of one part of a row, whose first element has index `base` in the output matrix.
+  // WHOLE: D is a multiple of the vector width, so that every vector is one aligned group of the
+  // generator (no element-wise path in the code at all - it is most of the code otherwise, and these
+  // kernels run few enough warps to feel the instruction cache).  STORE (only with WHOLE and 8-element
+  // vectors, see norm_mul_mask_bytes): the keep bits of every vector also go to memory, one byte each.
+  template <bool WHOLE, bool STORE, typename E, int MAXV>
   __device__ __forceinline__ void apply(Row<E, MAXV> &r, uint64_t base, int D, int lane,
                                         uint8_t *mask_out = nullptr) const {
     constexpr int EV = VecInfo<E>::EV;
@@ -570,20 +572,34 @@ struct Dropout {
       const int e0 = (k * 32 + lane) * EV;
       if (e0 >= D) continue;
       const uint64_t idx0 = base + (uint64_t)e0;
-      if ((idx0 & (EV - 1)) == 0 && e0 + EV <= D) {
+      if (WHOLE || ((idx0 & (EV - 1)) == 0 && e0 + EV <= D)) {
         uint32_t o[4];
         const uint64_t g = idx0 >> 3;
         philox4x32_10(k0, k1, (uint32_t)g, (uint32_t)(g >> 32), o);
-        const int j0 = (int)(idx0 & 7);   // 0, or 4 for the second half of a group of 32-bit elements
-        uint32_t kept = 0;
+        if constexpr (EV == 8) {
+          // two pieces per word: the high one compares in place, the low one after a shift
+          const uint32_t thr_hi = thr << 16;
+          uint32_t kept = 0;
 #pragma unroll
-        for (int t = 0; t < EV; ++t) {
-          const int j = j0 + t;
-          const uint32_t rr = (o[(j >> 1) & 3] >> (16 * (j & 1))) & 0xffffu;
-          kept |= (rr >= thr ? 1u : 0u) << t;
-          r.v[k][t] = rr >= thr ? r.v[k][t] * scale : 0.f;
+          for (int w = 0; w < 4; ++w) {
+            const bool lo = (o[w] << 16) >= thr_hi, hi = o[w] >= thr_hi;
+            r.v[k][2 * w] = lo ? r.v[k][2 * w] * scale : 0.f;
+            r.v[k][2 * w + 1] = hi ? r.v[k][2 * w + 1] * scale : 0.f;
+            if (STORE) {
+              if (lo) kept |= 1u << (2 * w);
+              if (hi) kept |= 2u << (2 * w);
+            }
+          }
+          if (STORE) mask_out[g] = (uint8_t)kept;
+        } else {
+          const int j0 = (int)(idx0 & 7);   // 0, or 4 for the second half of a group of 32-bit elements
+#pragma unroll
+          for (int t = 0; t < EV; ++t) {
+            const int j = j0 + t;
+            const uint32_t rr = (o[(j >> 1) & 3] >> (16 * (j & 1))) & 0xffffu;
+            r.v[k][t] = rr >= thr ? r.v[k][t] * scale : 0.f;
+          }
         }
-        if (EV == 8 && mask_out != nullptr) mask_out[g] = (uint8_t)kept;
       } else {
 #pragma unroll
         for (int t = 0; t < EV; ++t)
@@ -635,8 +651,10 @@ struct MaskBytes {
 // for two resident CTAs (128 registers instead of 158: 3.1 instead of 2.3 TB/s at D = 512; without
 // dropout 128 instead of 161: 6.2 instead of 5.4 TB/s), wider rows would spill and are left to the
 // compiler's own choice (0 = no minimum).
-template <typename E, int MAXV, bool DROPOUT>
+// DROPOUT: 0 = none, 1 = any row width, 2 = rows of whole vectors, 3 = the same and the mask bits stored
+template <typename E, int MAXV, int DROPOUT>
 __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_kernel(NormMulParams p) {
+  constexpr bool WHOLE = DROPOUT >= 2, STORE = DROPOUT == 3 && VecInfo<E>::EV == 8;
   constexpr int EV = VecInfo<E>::EV;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int D = p.H * p.V;
@@ -683,7 +701,7 @@ __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_ke
     if (p.concat_u) {
       if (DROPOUT) {
         Row<E, MAXV> du_ = ur;
-        drop.apply(du_, rbase, D, lane, p.mask);
+        drop.template apply<WHOLE, STORE>(du_, rbase, D, lane, p.mask);
         du_.store(orow, D, lane, p.vec_ok);
       } else {
         ur.store(orow, D, lane, p.vec_ok);
@@ -693,7 +711,7 @@ __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_ke
     if (p.concat_x) {
       if (DROPOUT) {
         Row<E, MAXV> dx_ = xr;
-        drop.apply(dx_, rbase + off, D, lane, p.mask);
+        drop.template apply<WHOLE, STORE>(dx_, rbase + off, D, lane, p.mask);
         dx_.store(orow + off, D, lane, p.vec_ok);
       } else {
         xr.store(orow + off, D, lane, p.vec_ok);
@@ -705,7 +723,7 @@ __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_ke
 #pragma unroll
       for (int t = 0; t < EV; ++t)
         xr.v[k][t] = act_f(ur.v[k][t], p.act) * ((xr.v[k][t] - mean) * rstd * wr.v[k][t] + br.v[k][t]);
-    if (DROPOUT) drop.apply(xr, rbase + off, D, lane, p.mask);
+    if (DROPOUT) drop.template apply<WHOLE, STORE>(xr, rbase + off, D, lane, p.mask);
     xr.store(orow + off, D, lane, p.vec_ok);
     if (lane == 0) {
       if (p.mean) p.mean[row] = mean;
@@ -714,15 +732,17 @@ __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_ke
   }
 }
 
-// DROPOUT: 0 = none, 1 = the forward's mask regenerated from the seed, 2 = read from p.mask
+// DROPOUT: 0 = none, 1 = the forward's mask regenerated from the seed, 2 = read from p.mask,
+// 3 = regenerated, rows of whole vectors
 template <typename E, int MAXV, int DROPOUT>
 __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams p) {
   constexpr int EV = VecInfo<E>::EV;
+  constexpr bool REGEN = DROPOUT == 1 || DROPOUT == 3, WHOLE = DROPOUT == 3;
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int D = p.H * p.V;
   Dropout drop;
-  if (DROPOUT == 1) drop.init(p);
+  if (REGEN) drop.init(p);
   const int width = D * (1 + (p.concat_u ? 1 : 0) + (p.concat_x ? 1 : 0));
   Row<E, MAXV> wr, br, dw, db;
   wr.load((const E *)p.w, D, lane, p.vec_ok);
@@ -789,7 +809,7 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
     }
     // the forward's mask, regenerated: the gradient of a dropped element is zero, of a kept one scaled
     const uint64_t rbase = (uint64_t)row * (uint64_t)width;
-    if (DROPOUT == 1) drop.apply(gy, rbase + off_y, D, lane);
+    if (REGEN) drop.template apply<WHOLE, false>(gy, rbase + off_y, D, lane);
     if constexpr (DROPOUT == 2) {
       if (PF && loaded) { if constexpr (PF) cmy.apply(gy, p.drop_scale); }
       else apply_stored_mask(gy, rbase + off_y, D, lane, p.mask, p.drop_scale);
@@ -826,7 +846,7 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
       } else {
         tmp.load(grow, D, lane, p.vec_ok);
       }
-      if (DROPOUT == 1) drop.apply(tmp, rbase, D, lane);
+      if (REGEN) drop.template apply<WHOLE, false>(tmp, rbase, D, lane);
       if constexpr (DROPOUT == 2) {
         if (PF && loaded) { if constexpr (PF) cmu.apply(tmp, p.drop_scale); }
         else apply_stored_mask(tmp, rbase, D, lane, p.mask, p.drop_scale);
@@ -842,7 +862,7 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
       } else {
         tmp.load(grow + off_x, D, lane, p.vec_ok);
       }
-      if (DROPOUT == 1) drop.apply(tmp, rbase + off_x, D, lane);
+      if (REGEN) drop.template apply<WHOLE, false>(tmp, rbase + off_x, D, lane);
       if constexpr (DROPOUT == 2) {
         if (PF && loaded) { if constexpr (PF) cmx.apply(tmp, p.drop_scale); }
         else apply_stored_mask(tmp, rbase + off_x, D, lane, p.mask, p.drop_scale);
@@ -1175,10 +1195,14 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
       p.mask = a.dropout_mask;
     }
     ProfileScope prof(PROF_NORM_MUL_FWD, st);
-    if (dropout) {
-      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, true><<<grid, WARPS * 32, 0, st>>>(p)));
+    if (dropout && p.mask != nullptr) {
+      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, 3><<<grid, WARPS * 32, 0, st>>>(p)));
+    } else if (dropout && D % EV == 0) {
+      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, 2><<<grid, WARPS * 32, 0, st>>>(p)));
+    } else if (dropout) {
+      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, 1><<<grid, WARPS * 32, 0, st>>>(p)));
     } else {
-      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, false><<<grid, WARPS * 32, 0, st>>>(p)));
+      DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, 0><<<grid, WARPS * 32, 0, st>>>(p)));
     }
     count_launch();
     B200_CHECK_LAUNCH("norm_mul forward");
@@ -1199,6 +1223,12 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     p.mask = a.dropout_mask;
     DISPATCH_MAXV(pick_maxv<E>(D), {
       auto kern = norm_mul_bwd_kernel<E, MV, 2>;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      kern<<<grid, WARPS * 32, smem, st>>>(p);
+    });
+  } else if (dropout && D % EV == 0) {
+    DISPATCH_MAXV(pick_maxv<E>(D), {
+      auto kern = norm_mul_bwd_kernel<E, MV, 3>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       kern<<<grid, WARPS * 32, smem, st>>>(p);
     });

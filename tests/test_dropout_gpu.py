@@ -136,7 +136,7 @@ def test_stored_mask_and_regenerated_mask_give_the_same_backward(dtype, H, V, co
         y.backward(dy)
         results.append([y.detach()] + [t.grad for t in ld])
         assert G._cabi.launch_count() - n0 == 3      # forward, backward, reduction of the weight gradients
-    HC.set_store_dropout_mask(True)
+    HC.set_store_dropout_mask(False)
     for a_, b_ in zip(*results):
         assert torch.equal(a_, b_)
 
