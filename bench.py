@@ -1301,7 +1301,27 @@ def stage_kernels(dev, peaks, steps):
     res["add_timestamp_positional_embeddings_bwd"] = timed(
         "ts_pos", lambda: torch.autograd.grad(ye, (xe, pw, tw), dy, retain_graph=True), rows * D * 2 * 2)
     res["uvqk_stage"] = _uvqk_stage(dev, peaks, 20)
-    res["_workload"] = "stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2)" % (rows, rows * D * 2 / 1e6)
+    # the same stage kernels at configs[4]'s width (D = H * dv = 1024: four 16-byte vectors per lane), half the rows
+    del ye, left, right, yc, y
+    rows2, D2 = rows // 2, 1024
+    x2, dy2, w2, b2 = mk(rows2, D2), mk(rows2, D2), mk(D2), mk(D2)
+    u2, dcat2 = mk(rows2, D2), mk(rows2, 3 * D2)
+    x2r, u2r, w2r, b2r = (t.clone().requires_grad_(True) for t in (x2, u2, w2, b2))
+    res["layer_norm_fwd_d1024"] = timed("layer_norm_fwd", lambda: G.layer_norm(x2, w2, b2, 1e-6), rows2 * D2 * 2 * 2 + rows2 * 8)
+    y2 = G.layer_norm(x2r, w2r, b2r, 1e-6)
+    res["layer_norm_bwd_d1024"] = timed("layer_norm_bwd", lambda: torch.autograd.grad(y2, (x2r, w2r, b2r), dy2, retain_graph=True),
+                                        rows2 * D2 * 2 * 3 + rows2 * 8)
+    nm2 = lambda p_, *t: G.hstu_norm_mul_dropout(*t, 1e-6, p_, p_ > 0, True, True, "none", False, 8, 128,  # noqa: E731
+                                                 dropout_seed=seed if p_ > 0 else None)
+    res["norm_mul_fwd_d1024"] = timed("norm_mul_fwd", lambda: nm2(0.0, x2, u2, w2, b2), rows2 * D2 * 2 * 5 + rows2 * 8)
+    res["norm_mul_fwd_dropout_d1024"] = timed("norm_mul_fwd", lambda: nm2(0.3, x2, u2, w2, b2), rows2 * D2 * 2 * 5 + rows2 * 8)
+    for name, p_ in (("norm_mul_bwd_d1024", 0.0), ("norm_mul_bwd_dropout_d1024", 0.3)):
+        yc2 = nm2(p_, x2r, u2r, w2r, b2r)
+        res[name] = timed("norm_mul_bwd", lambda: torch.autograd.grad(yc2, (x2r, u2r, w2r, b2r), dcat2, retain_graph=True),
+                          rows2 * D2 * 2 * 7 + rows2 * 8)
+        del yc2
+    res["_workload"] = ("stage kernels, rows=%d, D=H*dv=512 (tensors of %.0f MB, larger than L2); *_d1024: rows=%d, D=1024"
+                        % (rows, rows * D * 2 / 1e6, rows2))
     return res
 
 

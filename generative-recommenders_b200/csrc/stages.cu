@@ -288,10 +288,12 @@ __global__ void __launch_bounds__(WARPS * 32, 2) layer_norm_bwd_kernel(
 
 // The same backward with the two column accumulators (dweight, dbias) of every warp in shared
 // memory instead of registers: 64 registers fewer per thread, so three CTAs instead of two fit an
-// SM and more rows are in flight.  Vector path only (aligned pointers and strides, MAXV <= 2).
+// SM and more rows are in flight (two CTAs for rows of four vectors per lane, which without this
+// would neither fit a prefetched row into the registers nor a second CTA onto the SM).  Vector path
+// only (aligned pointers and strides, MAXV <= 4).
 // Shared memory: [2][WARPS][MAXV * EV / 4][32] float4, each lane touching only its own entries.
 template <typename E, int MAXV>
-__global__ void __launch_bounds__(WARPS * 32, 3) layer_norm_bwd_smem_kernel(
+__global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 3 : 2) layer_norm_bwd_smem_kernel(
     const E *__restrict__ dy, int64_t dy_rs, const E *__restrict__ x, int64_t x_rs, const E *__restrict__ w,
     const float *__restrict__ mean_in, const float *__restrict__ rstd_in, E *__restrict__ dx, int64_t dx_rs,
     float *__restrict__ partial, int64_t rows, int D) {
@@ -666,7 +668,7 @@ __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_ke
   br.load((const E *)p.b, D, lane, p.vec_ok);
   const int64_t step = (int64_t)gridDim.x * WARPS;
   int64_t row = (int64_t)blockIdx.x * WARPS + warp;
-  constexpr bool PF = MAXV <= 2;
+  constexpr bool PF = MAXV <= 4;
   const bool pf = PF && p.vec_ok;
   RawRow<E, PF ? MAXV : 1> nx, nu;
   if constexpr (PF) {
@@ -880,6 +882,139 @@ __global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_kernel(NormMulParams 
   reduce_columns_to_partial(db, smem, prow + D, D, lane, warp);
 }
 
+// The same backward for rows of four vectors per lane (D = 1024 in 16-bit elements), which the kernel
+// above can only run without its prefetch and at the edge of spilling: the column accumulators
+// (dweight, dbias) of every warp live in shared memory, weight and bias are read from a packed copy
+// in shared memory, and the registers so freed hold the next row's five raw inputs.  Vector path only
+// (aligned pointers and strides, D a multiple of the vector width).  DROPOUT: 0 = none, 3 = the
+// forward's mask regenerated from the seed.
+// Shared memory: [2][WARPS][MAXV * EV / 4][32] float4 accumulators, then weight and bias as
+// [2][MAXV * 32] 16-byte vectors.
+template <typename E, int MAXV, int DROPOUT>
+__global__ void __launch_bounds__(WARPS * 32) norm_mul_bwd_wide_kernel(NormMulParams p) {
+  constexpr int EV = VecInfo<E>::EV;
+  constexpr int Q = EV / 4;
+  constexpr int PER_WARP = MAXV * Q * 32;  // float4 entries per warp and accumulator
+  constexpr bool REGEN = DROPOUT == 3;
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = p.H * p.V;
+  float4 *accw = reinterpret_cast<float4 *>(smem) + (size_t)warp * PER_WARP;
+  float4 *accb = reinterpret_cast<float4 *>(smem) + (size_t)(WARPS + warp) * PER_WARP;
+  uint4 *wb = reinterpret_cast<uint4 *>(reinterpret_cast<float4 *>(smem) + (size_t)2 * WARPS * PER_WARP);
+#pragma unroll
+  for (int i = 0; i < MAXV * Q; ++i) {
+    accw[i * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+    accb[i * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int i = threadIdx.x; i < MAXV * 32; i += WARPS * 32) {
+    const bool in = (i + 1) * EV <= D;
+    wb[i] = in ? __ldg(reinterpret_cast<const uint4 *>((const E *)p.w + (size_t)i * EV)) : make_uint4(0, 0, 0, 0);
+    wb[MAXV * 32 + i] = in ? __ldg(reinterpret_cast<const uint4 *>((const E *)p.b + (size_t)i * EV)) : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  Dropout drop;
+  if (REGEN) drop.init(p);
+  const int width = D * (1 + (p.concat_u ? 1 : 0) + (p.concat_x ? 1 : 0));
+  const float invD = 1.f / (float)D;
+  const int off_x = p.concat_u ? D : 0;
+  const int off_y = off_x + (p.concat_x ? D : 0);
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  RawRow<E, MAXV> nx, nu, ngy, ngu, ngx;
+  float nmean = 0.f, nrstd = 0.f;
+  auto prefetch = [&](int64_t r) {
+    const E *grow = (const E *)p.dout + r * p.dout_rs;
+    nx.load((const E *)p.attn + r * p.attn_rs, D, lane);
+    nu.load((const E *)p.u + r * p.u_rs, D, lane);
+    ngy.load(grow + off_y, D, lane);
+    if (p.concat_u) ngu.load(grow, D, lane);
+    if (p.concat_x) ngx.load(grow + off_x, D, lane);
+    nmean = p.mean[r];
+    nrstd = p.rstd[r];
+  };
+  if (row < p.rows) prefetch(row);
+  for (; row < p.rows; row += step) {
+    Row<E, MAXV> xr, ur, gy;
+    nx.unpack(xr);
+    nu.unpack(ur);
+    ngy.unpack(gy);
+    const RawRow<E, MAXV> cgu = ngu, cgx = ngx;  // this row's concat gradients (the prefetch overwrites the buffers)
+    const float mean = nmean, rstd = nrstd;
+    if (row + step < p.rows) prefetch(row + step);
+    const uint64_t rbase = (uint64_t)row * (uint64_t)width;
+    if (REGEN) drop.template apply<true, false>(gy, rbase + off_y, D, lane);
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const uint4 wraw = wb[k * 32 + lane], braw = wb[MAXV * 32 + k * 32 + lane];
+      const E *pw = reinterpret_cast<const E *>(&wraw), *pb = reinterpret_cast<const E *>(&braw);
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        float4 aw = accw[(k * Q + q) * 32 + lane], ab = accb[(k * Q + q) * 32 + lane];
+        float *paw = reinterpret_cast<float *>(&aw), *pab = reinterpret_cast<float *>(&ab);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int t = q * 4 + c;
+          const int e = (k * 32 + lane) * EV + t;
+          const float w_ = to_f32(pw[t]);
+          const float xhat = e < D ? (xr.v[k][t] - mean) * rstd : 0.f;
+          const float ln = xhat * w_ + to_f32(pb[t]);
+          const float uu = ur.v[k][t];
+          const float g = gy.v[k][t];
+          const float ga = g * act_f(uu, p.act);      // gradient w.r.t. the normalised value
+          ur.v[k][t] = g * ln * dact_f(uu, p.act);    // du (y part)
+          paw[c] += ga * xhat;
+          pab[c] += ga;
+          const float gw = ga * w_;
+          xr.v[k][t] = xhat;
+          gy.v[k][t] = gw;
+          c1 += gw * xhat;
+          c2 += gw;
+        }
+        accw[(k * Q + q) * 32 + lane] = aw;
+        accb[(k * Q + q) * 32 + lane] = ab;
+      }
+    }
+    c1 = warp_sum(c1) * invD;
+    c2 = warp_sum(c2) * invD;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+      for (int t = 0; t < EV; ++t) gy.v[k][t] = (gy.v[k][t] - c2 - xr.v[k][t] * c1) * rstd;
+    if (p.concat_u) {
+      cgu.unpack(xr);   // (the normalised row is no longer needed)
+      if (REGEN) drop.template apply<true, false>(xr, rbase, D, lane);
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+        for (int t = 0; t < EV; ++t) ur.v[k][t] += xr.v[k][t];
+    }
+    if (p.concat_x) {
+      cgx.unpack(xr);
+      if (REGEN) drop.template apply<true, false>(xr, rbase + off_x, D, lane);
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+        for (int t = 0; t < EV; ++t) gy.v[k][t] += xr.v[k][t];
+    }
+    ur.store((E *)p.du + row * p.du_rs, D, lane, true);
+    gy.store((E *)p.dattn + row * p.dattn_rs, D, lane, true);
+  }
+  __syncthreads();
+  float *prow = p.partial + (int64_t)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * D; i += WARPS * 32) {
+    const int which = i >= D ? 1 : 0;
+    const int e = i - which * D;
+    const int t = e % EV, l = (e / EV) & 31, k = e / (EV * 32);
+    const int idx = (((k * Q + t / 4) * 32 + l) << 2) + (t & 3);
+    float sum = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < WARPS; ++wv) sum += smem[(size_t)(which * WARPS + wv) * PER_WARP * 4 + idx];
+    prow[i] = sum;
+  }
+}
+
 // Group-norm flavour (statistics per head; weight / bias are per-head scalars): one warp per
 // (row, head), scalar loads.  Used by the `group_norm=True` variant of the output stage only.
 template <typename E, bool BWD>
@@ -1042,15 +1177,25 @@ int ln_bwd_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const v
   size_t smem = (size_t)WARPS * D * sizeof(float);
   ProfileScope prof(PROF_LN_BWD, st);
   const int maxv = pick_maxv<E>(D);
-  if (vec_ok && D % EV == 0 && maxv <= 2) {
-    // accumulators in shared memory, three resident CTAs
+  if (vec_ok && D % EV == 0 && maxv <= 4) {
+    // accumulators in shared memory, three (two for four vectors per lane) resident CTAs
     const size_t acc_bytes = (size_t)2 * WARPS * maxv * (EV / 4) * 32 * sizeof(float4);
-    if (maxv == 1)
+    if (maxv == 1) {
       layer_norm_bwd_smem_kernel<E, 1><<<grid, WARPS * 32, acc_bytes, st>>>(
           (const E *)dy, dy_rs, (const E *)x, x_rs, (const E *)w, mean, rstd, (E *)dx, dx_rs, (float *)partial, rows, D);
-    else
+    } else if (maxv == 2) {
       layer_norm_bwd_smem_kernel<E, 2><<<grid, WARPS * 32, acc_bytes, st>>>(
           (const E *)dy, dy_rs, (const E *)x, x_rs, (const E *)w, mean, rstd, (E *)dx, dx_rs, (float *)partial, rows, D);
+    } else {
+      auto kern = layer_norm_bwd_smem_kernel<E, 4>;
+      grid = num_sms() * 2;   // two resident CTAs: one wave of the grid-stride loop
+      if (acc_bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)acc_bytes);
+        if (e != cudaSuccess) return check_cuda(e, "layer_norm backward smem attribute");
+      }
+      kern<<<grid, WARPS * 32, acc_bytes, st>>>((const E *)dy, dy_rs, (const E *)x, x_rs, (const E *)w, mean, rstd,
+                                                (E *)dx, dx_rs, (float *)partial, rows, D);
+    }
     count_launch();
     B200_CHECK_LAUNCH("layer_norm backward");
     reduce_partial_kernel<E><<<(2 * D + 31) / 32, 256, 0, st>>>((const float *)partial, grid, D, (E *)dw, (E *)db);
@@ -1217,7 +1362,14 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
     return fail(B200_HSTU_EWORKSPACE, "norm_mul backward: scratch too small");
   size_t smem = (size_t)WARPS * D * sizeof(float);
   ProfileScope prof(PROF_NORM_MUL_BWD, st);
-  if (dropout && a.dropout_mask != nullptr) {
+  if (vec_ok && D % EV == 0 && pick_maxv<E>(D) == 4 && !(dropout && a.dropout_mask != nullptr)) {
+    // rows of four vectors per lane: accumulators and weights in shared memory, prefetched rows
+    const size_t wide_smem = (size_t)2 * WARPS * 4 * (EV / 4) * 32 * sizeof(float4) + (size_t)2 * 4 * 32 * sizeof(uint4);
+    auto kern = dropout ? norm_mul_bwd_wide_kernel<E, 4, 3> : norm_mul_bwd_wide_kernel<E, 4, 0>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide_smem);
+    if (e != cudaSuccess) return check_cuda(e, "norm_mul backward smem attribute");
+    kern<<<grid, WARPS * 32, wide_smem, st>>>(p);
+  } else if (dropout && a.dropout_mask != nullptr) {
     if (!vec_ok || EV != 8 || norm_mul_mask_bytes(a) == 0)
       return fail(B200_HSTU_EUNSUPPORTED, "norm_mul backward: a stored dropout mask needs 16-bit elements, aligned rows and H*V %% 8 == 0");
     p.mask = a.dropout_mask;
