@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 3 : (MAXV <= 4 ? 2 : 1
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t step = (int64_t)gridDim.x * WARPS;
   int64_t row = (int64_t)blockIdx.x * WARPS + warp;
-  constexpr bool PF = MAXV <= 4;  // one-row-ahead prefetch only while the registers allow it
+  constexpr bool PF = MAXV <= 8;  // one-row-ahead prefetch (every width: the packed weights leave room for it)
   if (PF && vec_ok) {
     RawRow<E, PF ? MAXV : 1> wraw, braw, nxt;
     wraw.load(w, D, lane);
@@ -290,10 +290,10 @@ __global__ void __launch_bounds__(WARPS * 32, 2) layer_norm_bwd_kernel(
 // memory instead of registers: 64 registers fewer per thread, so three CTAs instead of two fit an
 // SM and more rows are in flight (two CTAs for rows of four vectors per lane, which without this
 // would neither fit a prefetched row into the registers nor a second CTA onto the SM).  Vector path
-// only (aligned pointers and strides, MAXV <= 4).
+// only (aligned pointers and strides); eight vectors per lane run one CTA per SM.
 // Shared memory: [2][WARPS][MAXV * EV / 4][32] float4, each lane touching only its own entries.
 template <typename E, int MAXV>
-__global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 3 : 2) layer_norm_bwd_smem_kernel(
+__global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 3 : (MAXV <= 4 ? 2 : 1)) layer_norm_bwd_smem_kernel(
     const E *__restrict__ dy, int64_t dy_rs, const E *__restrict__ x, int64_t x_rs, const E *__restrict__ w,
     const float *__restrict__ mean_in, const float *__restrict__ rstd_in, E *__restrict__ dx, int64_t dx_rs,
     float *__restrict__ partial, int64_t rows, int D) {
@@ -1177,7 +1177,7 @@ int ln_bwd_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const v
   size_t smem = (size_t)WARPS * D * sizeof(float);
   ProfileScope prof(PROF_LN_BWD, st);
   const int maxv = pick_maxv<E>(D);
-  if (vec_ok && D % EV == 0 && maxv <= 4) {
+  if (vec_ok && D % EV == 0) {
     // accumulators in shared memory, three (two for four vectors per lane) resident CTAs
     const size_t acc_bytes = (size_t)2 * WARPS * maxv * (EV / 4) * 32 * sizeof(float4);
     if (maxv == 1) {
@@ -1187,8 +1187,8 @@ int ln_bwd_t(const void *dy, int64_t dy_rs, const void *x, int64_t x_rs, const v
       layer_norm_bwd_smem_kernel<E, 2><<<grid, WARPS * 32, acc_bytes, st>>>(
           (const E *)dy, dy_rs, (const E *)x, x_rs, (const E *)w, mean, rstd, (E *)dx, dx_rs, (float *)partial, rows, D);
     } else {
-      auto kern = layer_norm_bwd_smem_kernel<E, 4>;
-      grid = num_sms() * 2;   // two resident CTAs: one wave of the grid-stride loop
+      auto kern = maxv == 4 ? layer_norm_bwd_smem_kernel<E, 4> : layer_norm_bwd_smem_kernel<E, 8>;
+      grid = num_sms() * (maxv == 4 ? 2 : 1);   // two / one resident CTAs: one wave of the grid-stride loop
       if (acc_bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)acc_bytes);
         if (e != cudaSuccess) return check_cuda(e, "layer_norm backward smem attribute");

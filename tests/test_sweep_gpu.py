@@ -309,7 +309,7 @@ def _layer_norm_case(rng):
     seed = rng.randrange(10 ** 9)
     g = torch.Generator().manual_seed(seed)
     dtype = _dtype(rng)
-    D = rng.choice([8, 24, 64, 100, 128, 136, 250, 256, 512, 1000, 1024])
+    D = rng.choice([8, 24, 64, 100, 128, 136, 250, 256, 512, 1000, 1024, 2048])
     rows = rng.choice([0, 1, 2, 31, 33, 100, 777, 3000])
     x = (torch.randn(rows, D, generator=g) * rng.choice([0.1, 1.0, 5.0]) + rng.choice([0.0, 0.3, 3.0])).to(dtype)
     w, b = torch.randn(D, generator=g).to(dtype), torch.randn(D, generator=g).to(dtype)
