@@ -734,6 +734,100 @@ __global__ void __launch_bounds__(WARPS * 32, MAXV <= 2 ? 2 : 0) norm_mul_fwd_ke
   }
 }
 
+// The same forward for rows of eight vectors per lane (D = 2048 in 16-bit elements), which do not fit
+// the registers as fp32 values next to a prefetched row: the row and the next one stay packed (raw
+// 16-byte vectors) and are unpacked vector by vector - twice for the statistics, once for the
+// output -, weight and bias are read where they are used (they stay in L1).  Vector path only
+// (aligned pointers and strides, D a multiple of the vector width).  DROPOUT: 0 = none, 2 = on.
+template <typename E, int MAXV, int DROPOUT>
+__global__ void __launch_bounds__(WARPS * 32) norm_mul_fwd_packed_kernel(NormMulParams p) {
+  constexpr int EV = VecInfo<E>::EV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = p.H * p.V;
+  Dropout drop;
+  if (DROPOUT) drop.init(p);
+  const int width = D * (1 + (p.concat_u ? 1 : 0) + (p.concat_x ? 1 : 0));
+  const float invD = 1.f / (float)D;
+  const int64_t step = (int64_t)gridDim.x * WARPS;
+  int64_t row = (int64_t)blockIdx.x * WARPS + warp;
+  RawRow<E, MAXV> nx, nu;
+  if (row < p.rows) {
+    nx.load((const E *)p.attn + row * p.attn_rs, D, lane);
+    nu.load((const E *)p.u + row * p.u_rs, D, lane);
+  }
+  for (; row < p.rows; row += step) {
+    const RawRow<E, MAXV> cx = nx, cu = nu;
+    if (row + step < p.rows) {
+      nx.load((const E *)p.attn + (row + step) * p.attn_rs, D, lane);
+      nu.load((const E *)p.u + (row + step) * p.u_rs, D, lane);
+    }
+    // statistics as in row_stats(): mean first, then the centred second moment
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const E *px = reinterpret_cast<const E *>(&cx.v[k]);
+#pragma unroll
+      for (int t = 0; t < EV; ++t) sum += to_f32(px[t]);   // vectors beyond the row hold zeros
+    }
+    const float mean = warp_sum(sum) * invD;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const E *px = reinterpret_cast<const E *>(&cx.v[k]);
+      const bool in = (k * 32 + lane) * EV < D;
+#pragma unroll
+      for (int t = 0; t < EV; ++t) {
+        const float d = in ? to_f32(px[t]) - mean : 0.f;
+        q += d * d;
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) * invD + p.eps);
+    E *orow = (E *)p.out + row * p.out_rs;
+    const uint64_t rbase = (uint64_t)row * (uint64_t)width;
+    const int off_x = p.concat_u ? D : 0;
+    const int off_y = off_x + (p.concat_x ? D : 0);
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int e0 = (k * 32 + lane) * EV;
+      if (e0 >= D) continue;
+      Row<E, 1> fx, fu, fy;
+      const E *px = reinterpret_cast<const E *>(&cx.v[k]), *pu = reinterpret_cast<const E *>(&cu.v[k]);
+      const uint4 wraw = __ldg(reinterpret_cast<const uint4 *>((const E *)p.w + e0));
+      const uint4 braw = __ldg(reinterpret_cast<const uint4 *>((const E *)p.b + e0));
+      const E *pw = reinterpret_cast<const E *>(&wraw), *pb = reinterpret_cast<const E *>(&braw);
+#pragma unroll
+      for (int t = 0; t < EV; ++t) {
+        fx.v[0][t] = to_f32(px[t]);
+        fu.v[0][t] = to_f32(pu[t]);
+        fy.v[0][t] = act_f(fu.v[0][t], p.act) * ((fx.v[0][t] - mean) * rstd * to_f32(pw[t]) + to_f32(pb[t]));
+      }
+      // (Row<E, 1> places its one vector at lane * EV: the pointers below are shifted to vector k)
+      if (p.concat_u) {
+        if (DROPOUT) {
+          drop.template apply<true, false>(fu, rbase + (uint64_t)(k * 32 * EV), D - k * 32 * EV, lane);
+          fu.store(orow + k * 32 * EV, D - k * 32 * EV, lane, true);
+        } else {
+          *reinterpret_cast<uint4 *>(orow + e0) = cu.v[k];
+        }
+      }
+      if (p.concat_x) {
+        if (DROPOUT) {
+          drop.template apply<true, false>(fx, rbase + (uint64_t)(off_x + k * 32 * EV), D - k * 32 * EV, lane);
+          fx.store(orow + off_x + k * 32 * EV, D - k * 32 * EV, lane, true);
+        } else {
+          *reinterpret_cast<uint4 *>(orow + off_x + e0) = cx.v[k];
+        }
+      }
+      if (DROPOUT) drop.template apply<true, false>(fy, rbase + (uint64_t)(off_y + k * 32 * EV), D - k * 32 * EV, lane);
+      fy.store(orow + off_y + k * 32 * EV, D - k * 32 * EV, lane, true);
+    }
+    if (lane == 0) {
+      if (p.mean) p.mean[row] = mean;
+      if (p.rstd) p.rstd[row] = rstd;
+    }
+  }
+}
+
 // DROPOUT: 0 = none, 1 = the forward's mask regenerated from the seed, 2 = read from p.mask,
 // 3 = regenerated, rows of whole vectors
 template <typename E, int MAXV, int DROPOUT>
@@ -1340,7 +1434,11 @@ int norm_mul_t(const b200_hstu_norm_mul_args &a, bool bwd, cudaStream_t st) {
       p.mask = a.dropout_mask;
     }
     ProfileScope prof(PROF_NORM_MUL_FWD, st);
-    if (dropout && p.mask != nullptr) {
+    if (vec_ok && D % EV == 0 && pick_maxv<E>(D) == 8 && p.mask == nullptr) {
+      // rows of eight vectors per lane: packed rows, unpacked vector by vector
+      if (dropout) norm_mul_fwd_packed_kernel<E, 8, 2><<<grid, WARPS * 32, 0, st>>>(p);
+      else norm_mul_fwd_packed_kernel<E, 8, 0><<<grid, WARPS * 32, 0, st>>>(p);
+    } else if (dropout && p.mask != nullptr) {
       DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, 3><<<grid, WARPS * 32, 0, st>>>(p)));
     } else if (dropout && D % EV == 0) {
       DISPATCH_MAXV(pick_maxv<E>(D), (norm_mul_fwd_kernel<E, MV, 2><<<grid, WARPS * 32, 0, st>>>(p)));
