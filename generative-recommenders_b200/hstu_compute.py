@@ -412,9 +412,9 @@ def _norm_mul_backward(dout, attn, u, weight, bias, mean, rstd, eps, num_heads, 
 
 # By default the backward of the norm-mul stage regenerates the dropout mask from the seed and nothing
 # is stored.  Switched on, the forward also writes the mask as bits (6 % of the output's bytes) and the
-# backward reads them: measured on B200 that backward is 4 % faster and that forward 8 % slower (both
-# kernels are bound by instruction issue at the occupancy their registers allow), so it is off.  With
-# recompute_y the mask is never stored.
+# backward reads them: measured on B200 that forward is 8 % slower and that backward between 4 % and
+# 28 % faster from run to run (both kernels are bound by instruction issue at the occupancy their
+# registers allow and follow the SM clock), so it is off.  With recompute_y the mask is never stored.
 _STORE_DROPOUT_MASK = False
 
 
