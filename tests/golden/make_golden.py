@@ -427,6 +427,38 @@ def make_cached_layer(gr):
     return out
 
 
+def make_attention_dropout(ref_ops):
+    """``pytorch_hstu_mha(dropout_pr > 0, training=True)``: the reference draws its mask with ``F.dropout``
+    on the padded ``[B, H, N, N]`` weights - its only use of the generator - so the same seed and shape
+    give the mask, which is stored next to the outputs as ``keep`` ``[L, H, N]`` (query row, head, key
+    position) for an implementation that takes the mask from outside."""
+    cases = []
+    for i, (drop, ctx, W, with_targets) in enumerate([(0.1, 0, 0, False), (0.5, 2, 9, True), (0.3, 0, 0, True)]):
+        g = torch.Generator().manual_seed(700 + i)
+        B, N, H, A, V = 3, 40, 2, 8, 8
+        lengths = torch.randint(4, N + 1, (B,), generator=g)
+        nt = torch.randint(1, 4, (B,), generator=g) if with_targets else None
+        offsets = _offsets(lengths)
+        L = int(offsets[-1])
+        q, k = (torch.randn(L, H, A, generator=g, requires_grad=True) for _ in range(2))
+        v = torch.randn(L, H, V, generator=g, requires_grad=True)
+        dout = torch.randn(L, H, V, generator=g)
+        seed = 4100 + i
+        torch.manual_seed(seed)
+        dense = torch.nn.functional.dropout(torch.ones(B, H, N, N), drop, True) != 0
+        keep = torch.zeros(L, H, N, dtype=torch.bool)
+        for b in range(B):
+            n = int(lengths[b])
+            keep[int(offsets[b]):int(offsets[b]) + n] = dense[b, :, :n].transpose(0, 1)
+        torch.manual_seed(seed)
+        out = ref_ops.pytorch_hstu_mha(N, 0.3, q, k, v, offsets, True, drop, True, nt, None, W, ctx, 0)
+        out.backward(dout)
+        cases.append(dict(N=N, alpha=0.3, q=q.detach(), k=k.detach(), v=v.detach(), seq_offsets=offsets, num_targets=nt,
+                          max_attn_len=W, ctx=ctx, dropout_pr=drop, keep=keep, dout=dout, out=out.detach(),
+                          dq=q.grad.clone(), dk=k.grad.clone(), dv=v.grad.clone()))
+    return cases
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -451,7 +483,8 @@ def main():
                      ("stu_layer", lambda: make_layer(gr)), ("delta_attention", lambda: make_delta(ref_ops)),
                      ("rel_bias", make_bias), ("rel_bias_attention", make_bias_attention),
                      ("jagged", lambda: make_jagged(gr)),
-                     ("stu_cached", lambda: make_cached_layer(gr))):
+                     ("stu_cached", lambda: make_cached_layer(gr)),
+                     ("attention_dropout", lambda: make_attention_dropout(ref_ops))):
         if want(name):
             torch.save(fn(), os.path.join(HERE, name + ".pt"))
     for f in sorted(os.listdir(HERE)):

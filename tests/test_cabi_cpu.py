@@ -52,6 +52,16 @@ def test_bad_arguments_are_rejected_on_the_host():
     assert lib.b200_hstu_attn_fwd(a, None) == -1
     a.dtype = _cabi.F32
     assert lib.b200_hstu_attn_fwd(a, None) == -1  # q is NULL
+    # a dropout rate outside [0, 1) is refused on the host, before anything is launched (the pointers
+    # below are never followed: validation only asks whether they are NULL)
+    a.q = a.k = a.v = a.out = a.seq_offsets = 256
+    a.dropout_ratio = 1.0
+    assert lib.b200_hstu_attn_fwd(a, None) == -1
+    assert b"dropout_ratio" in lib.b200_hstu_last_error()
+    a.dropout_ratio = -0.5
+    assert lib.b200_hstu_attn_fwd(a, None) == -1
+    a.dropout_ratio = 0.0
+    a.q = a.k = a.v = a.out = a.seq_offsets = None
     a.B = 0  # an empty batch is a no-op
     assert lib.b200_hstu_attn_fwd(a, None) == 0
     n = _cabi.NormMulArgs()

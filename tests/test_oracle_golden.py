@@ -55,6 +55,26 @@ def test_attention_matches_reference(golden):
             torch.testing.assert_close(v.grad, fx["dv"], rtol=1e-5, atol=1e-6, msg=name)
 
 
+def test_attention_dropout_matches_reference(golden):
+    """Dropout on the weights: with the mask the reference itself drew (kept in the fixture), the
+    oracle reproduces the reference's output and gradients - the mask goes on after scale and
+    validity mask, kept weights are scaled by 1 / (1 - p)."""
+    cases = golden("attention_dropout.pt")
+    assert len(cases) == 3
+    for c in cases:
+        q, k, v = (c[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
+        out = O.hstu_mha(c["N"], c["alpha"], q, k, v, c["seq_offsets"], dropout_pr=c["dropout_pr"],
+                         num_targets=c["num_targets"], max_attn_len=c["max_attn_len"], contextual_seq_len=c["ctx"],
+                         dropout_keep=c["keep"])
+        out.backward(c["dout"])
+        torch.testing.assert_close(out, c["out"], rtol=1e-5, atol=1e-6)
+        for a, n in ((q, "dq"), (k, "dk"), (v, "dv")):
+            torch.testing.assert_close(a.grad, c[n], rtol=1e-5, atol=1e-6)
+        plain = O.hstu_mha(c["N"], c["alpha"], c["q"], c["k"], c["v"], c["seq_offsets"], num_targets=c["num_targets"],
+                           max_attn_len=c["max_attn_len"], contextual_seq_len=c["ctx"])
+        assert float((plain - c["out"]).abs().max()) > 1e-3      # the mask matters
+
+
 def test_delta_attention_matches_reference(golden):
     fx = golden("delta_attention.pt")
     out = O.delta_hstu_mha(fx["N"], fx["alpha"], fx["delta_q"], fx["k"], fx["v"], fx["seq_offsets"],
